@@ -1,0 +1,148 @@
+/*
+ * znn_cuda.h -- C ABI of libznn_cuda.so: the B200 (sm_100a) implementation of
+ * the dense-contraction hot path of chen-gz/znn.
+ *
+ * Every entry point is what the reference's host code would bind for one loop
+ * of its hot path; the comment on each names the reference code it replaces
+ * (paths are inside the reference project).  Conventions:
+ *   - all tensor pointers are DEVICE pointers to contiguous row-major fp32
+ *     unless a comment says otherwise; the caller owns every buffer;
+ *   - every call returns 0 on success or a negative ZNN_ERR_* code, never
+ *     aborts; znn_last_error() gives the text for the calling host thread;
+ *   - calls enqueue work on the calling thread's stream (znn_set_stream) and
+ *     return without waiting; znn_sync() waits;
+ *   - "accumulate" arguments follow the reference's backward arms, which add
+ *     into the input gradients (+=): a NULL gradient pointer means the input
+ *     has requires_grad == false and that arm is skipped.
+ * There is no CPU fallback: without a CUDA device every compute call fails.
+ */
+#ifndef ZNN_CUDA_H
+#define ZNN_CUDA_H
+#include <stddef.h>
+#include <stdint.h>
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define ZNN_OK 0
+#define ZNN_ERR_INVALID (-1)  /* bad argument */
+#define ZNN_ERR_CUDA (-2)     /* a CUDA runtime/driver call failed */
+#define ZNN_ERR_NOMEM (-3)
+#define ZNN_ERR_DEVICE_WAIT (-4) /* a bounded device-side wait expired */
+#define ZNN_ERR_NCCL (-5)
+#define ZNN_ERR_UNSUPPORTED (-6)
+
+/* bits of the device status word (znn_device_status) */
+#define ZNN_DEV_TMA_WAIT_EXPIRED 1
+#define ZNN_DEV_MMA_WAIT_EXPIRED 2
+#define ZNN_DEV_EPI_WAIT_EXPIRED 4
+
+/* same constants as src/cblas.zig:5-8 */
+#define ZNN_ROW_MAJOR 101
+#define ZNN_COL_MAJOR 102
+#define ZNN_NO_TRANS 111
+#define ZNN_TRANS 112
+
+/* ---- runtime (the reference allocates with Zig allocators: src/autodiff.zig:1301-1326,
+ *      src/nn.zig:1352-1377; these are the device equivalents) ---- */
+int znn_init(int device);                 /* select device, create per-device state */
+int znn_device_count(int* count);
+int znn_set_stream(void* cuda_stream);    /* cudaStream_t to launch on (NULL = shim-owned stream) */
+int znn_get_stream(void** cuda_stream);
+int znn_sync(void);
+int znn_malloc(void** ptr, size_t bytes);
+int znn_free(void* ptr);
+int znn_memset(void* ptr, int value, size_t bytes);
+int znn_memcpy_h2d(void* dst, const void* src, size_t bytes);   /* async on the stream */
+int znn_memcpy_d2h(void* dst, const void* src, size_t bytes);   /* waits for completion */
+int znn_memcpy_d2d(void* dst, const void* src, size_t bytes);
+int znn_last_error(char* buf, size_t buflen);
+int znn_device_status(int* status, int clear); /* syncs, reads (and clears) the device status word */
+int znn_gemm_workspace_reserve(size_t bytes);  /* pre-size the GEMM scratch (avoids cudaMalloc later) */
+
+/* ---- GEMM: replaces cblas_sgemm (src/cblas.zig:11-96; prototype :17-34) at its 8 call
+ *      sites (src/tensor.zig:181,721; src/autodiff.zig:117,513,604,624,1143,1163).
+ *      Row-major only, like the reference (cblas.zig:53).  Results carry fp32 accuracy:
+ *      large shapes run 3xTF32 split-precision tcgen05 MMAs, small/ragged ones fp32 FMAs. */
+int znn_sgemm(int order, int trans_a, int trans_b, int M, int N, int K, float alpha,
+              const float* A, int lda, const float* B, int ldb, float beta, float* C, int ldc);
+/* The per-(batch,head) sgemm loops of BatchMatMul (src/autodiff.zig:485-531, :1117-1182)
+ * as one call; strides are in elements between consecutive slices. */
+int znn_sgemm_batched_strided(int trans_a, int trans_b, int M, int N, int K, float alpha,
+                              const float* A, int lda, long long stride_a,
+                              const float* B, int ldb, long long stride_b, float beta,
+                              float* C, int ldc, long long stride_c, int batch);
+/* path: 0 = automatic, 1 = fp32 FMA kernel, 2 = tcgen05 one CTA per tile, 3 = tcgen05 CTA pairs */
+int znn_gemm_set_path(int path);
+int znn_gemm_last_path(void);
+
+/* ---- row-wise operators: the arms of Op.forward (src/autodiff.zig:107-575) and
+ *      Op.backward (:579-1231) ---- */
+/* AddBias: src/autodiff.zig:134-147 / :652-672 */
+int znn_add_bias_fwd(const float* A, const float* bias, float* C, int M, int N);
+int znn_add_bias_bwd(const float* dC, float* dA, float* dbias, int M, int N);
+/* Relu: :148-154 / :681-691 */
+int znn_relu_fwd(const float* A, float* C, size_t n);
+int znn_relu_bwd(const float* A, const float* dC, float* dA, size_t n);
+/* Gelu (exact erf form): :156-165 / :699-716 */
+int znn_gelu_fwd(const float* A, float* C, size_t n);
+int znn_gelu_bwd(const float* A, const float* dC, float* dA, size_t n);
+/* SoftmaxCrossEntropy: :196-238 / :758-774; probs is the M x N buffer the reference keeps in
+ * OpContext; loss is one device float.  Targets are int32 (the reference's []const u8 cannot
+ * hold a vocabulary above 255); the _u8 form takes the reference's type. */
+int znn_softmax_xent_fwd(const float* logits, const int32_t* targets, float* probs, float* loss, int M, int N);
+int znn_softmax_xent_fwd_u8(const float* logits, const uint8_t* targets, float* probs, float* loss, int M, int N);
+int znn_softmax_xent_bwd(const float* probs, const int32_t* targets, float* dlogits, int M, int N);
+int znn_softmax_xent_bwd_u8(const float* probs, const uint8_t* targets, float* dlogits, int M, int N);
+/* Softmax over the last dimension: :435-461 / :1054-1076 */
+int znn_softmax_fwd(const float* A, float* C, size_t rows, int D);
+int znn_softmax_bwd(const float* Y, const float* dY, float* dA, size_t rows, int D);
+/* Fused form of mulScalar + causal -1e9 mask add + softmax as CausalSelfAttention runs them
+ * (src/nn.zig:835-886); the mask is applied by index and never materialised.
+ * S and P are nslices x T x T. Backward is the chain softmax -> add -> mulScalar
+ * (src/autodiff.zig:1054-1076, :914-928, :895-904): dS += scale * P * (dP - sum(dP*P)). */
+int znn_causal_softmax_fwd(const float* S, float scale, float* P, int nslices, int T);
+int znn_causal_softmax_bwd(const float* P, const float* dP, float scale, float* dS, int nslices, int T);
+/* RmsNorm: :462-484 / :1077-1116 */
+int znn_rmsnorm_fwd(const float* X, const float* G, float eps, float* Y, size_t rows, int D);
+int znn_rmsnorm_bwd(const float* X, const float* G, const float* dY, float eps, float* dX, float* dG, size_t rows, int D);
+/* LayerNorm: no counterpart in the reference (it only has RmsNorm); biased variance,
+ * eps inside the square root. */
+int znn_layernorm_fwd(const float* X, const float* G, const float* B, float eps, float* Y, size_t rows, int D);
+int znn_layernorm_bwd(const float* X, const float* G, const float* dY, float eps, float* dX, float* dG, float* dB, size_t rows, int D);
+/* Conv2D, NCHW, stride 1: src/tensor.zig:523-585, src/autodiff.zig:339-388 / :929-995.
+ * pad = 0 is the reference; pad > 0 (zero padding) is an extension. bias may be NULL. */
+int znn_conv2d_fwd(const float* X, const float* W, const float* bias, float* Y,
+                   int N, int Ci, int H, int Wd, int Co, int KH, int KW, int pad);
+int znn_conv2d_bwd(const float* X, const float* W, const float* dY, float* dX, float* dW, float* dbias,
+                   int N, int Ci, int H, int Wd, int Co, int KH, int KW, int pad);
+/* MaxPool2D: :389-434 / :996-1053. idx (may be NULL) receives, per output, the offset inside
+ * the (n,c) input plane of the first maximum in (ph,pw) order. */
+int znn_maxpool2d_fwd(const float* X, float* Y, int32_t* idx, int N, int C, int H, int W, int pool, int stride);
+int znn_maxpool2d_bwd(const float* X, const float* dY, float* dX, int N, int C, int H, int W, int pool, int stride);
+/* Embedding (ids carried as fp32, as in the reference): :532-553 / :1183-1207.
+ * The backward scatter-add is deterministic: rows with the same id are summed in (b,t) order. */
+int znn_embedding_fwd(const float* W, const float* ids, float* Y, size_t n, int D, int vocab);
+int znn_embedding_bwd(const float* ids, const float* dY, float* dW, size_t n, int D, int vocab);
+/* Transpose of two dims of a rank<=8 tensor: :276-302 / :848-876 (bwd accumulates) */
+int znn_transpose_fwd(const float* A, float* C, const int64_t* dims, int rank, int d0, int d1);
+int znn_transpose_bwd(const float* dC, float* dA, const int64_t* dims, int rank, int d0, int d1);
+/* Add :331-338, gradient pass-through accumulate (Reshape/Add/AddScalar backward :831-839,
+ * :905-928), MulScalar :315-322 / :895-904 */
+int znn_add_fwd(const float* A, const float* B, float* C, size_t n);
+int znn_accumulate(const float* src, float* dst, size_t n);
+int znn_mul_scalar_fwd(const float* A, float v, float* C, size_t n);
+int znn_mul_scalar_bwd(const float* dC, float v, float* dA, size_t n);
+/* argmax over dim 0 or 1 of an M x N tensor, first maximum wins, result as fp32:
+ * src/tensor.zig:813-851 (and the greedy pick of examples/transformer_gpt.zig:135-142) */
+int znn_argmax(const float* A, float* out, int M, int N, int dim);
+/* SGD with optional momentum: src/optim.zig:50-66. v may be NULL when momentum == 0.
+ * grad_scale multiplies the gradient first (1.0 = reference; 1/world for data parallel). */
+int znn_sgd_step(float* w, const float* g, float* v, float lr, float momentum, float grad_scale, size_t n);
+/* fill helpers (src/tensor.zig:354-379 fills; used for dC = 1 seeds and zeroGrad) */
+int znn_fill(float* dst, float value, size_t n);
+
+#ifdef __cplusplus
+}
+#endif
+#endif

@@ -1,0 +1,151 @@
+"""znn_sgemm (the cblas_sgemm boundary) against the CPU oracle and an fp64 arbiter.
+
+Bar (from the workload definition): normwise relative error <= 1e-5 against the
+reference sgemm on N(0,1) inputs, for the forward product and both backward
+products, on every code path: fp32-FMA kernel (1), tcgen05 one-CTA tiles (2),
+tcgen05 CTA-pair tiles (3) and the automatic choice (0).
+"""
+import numpy as np
+import pytest
+
+pytestmark = pytest.mark.gpu
+
+NT, T = 111, 112
+TOL = 1e-5
+
+
+@pytest.fixture(scope="module")
+def ops():
+    from znn_b200 import ops as _ops
+    _ops.init(0)
+    yield _ops
+    _ops.set_gemm_path(0)
+
+
+def rel_err(got, want):
+    got, want = np.asarray(got, np.float64), np.asarray(want, np.float64)
+    return float(np.linalg.norm(got - want) / max(1e-30, np.linalg.norm(want)))
+
+
+def make(ta, tb, M, N, K, seed, lda_pad=0, ldb_pad=0):
+    r = np.random.default_rng(seed)
+    a_shape = (M, K + lda_pad) if ta == NT else (K, M + lda_pad)
+    b_shape = (K, N + ldb_pad) if tb == NT else (N, K + ldb_pad)
+    return r.standard_normal(a_shape, np.float32), r.standard_normal(b_shape, np.float32)
+
+
+def run_case(ops, zo, path, ta, tb, M, N, K, alpha=1.0, beta=0.0, lda_pad=0, ldb_pad=0, ldc_pad=0, seed=0):
+    A, B = make(ta, tb, M, N, K, seed, lda_pad, ldb_pad)
+    r = np.random.default_rng(seed + 1)
+    C0 = r.standard_normal((M, N + ldc_pad), np.float32)
+    lda, ldb, ldc = A.shape[1], B.shape[1], N + ldc_pad
+    want = C0.copy()
+    zo.sgemm(ta, tb, M, N, K, alpha, A, lda, B, ldb, beta, want, ldc, naive=True)
+    got = C0.copy()
+    ops.set_gemm_path(path)
+    ops.sgemm(ta, tb, M, N, K, alpha, A, lda, B, ldb, beta, got, ldc)
+    if path != 0:
+        assert ops.last_gemm_path() == path
+    if ldc_pad:  # columns beyond N are not touched
+        np.testing.assert_array_equal(got[:, N:], C0[:, N:])
+    e = rel_err(got[:, :N], want[:, :N])
+    assert e <= TOL, f"path {path} {ta},{tb} {M}x{N}x{K} alpha={alpha} beta={beta}: rel err {e:.3e} vs oracle"
+    return got
+
+
+SMALL = [(2, 2, 3), (1, 1, 1), (64, 10, 784), (64, 128, 784), (33, 65, 17), (128, 256, 32), (130, 258, 70),
+         (256, 256, 256), (200, 64, 96), (300, 72, 1000)]
+
+
+@pytest.mark.parametrize("path", [1, 2, 3])
+@pytest.mark.parametrize("M,N,K", SMALL)
+def test_forward_nn(ops, zo, path, M, N, K):
+    run_case(ops, zo, path, NT, NT, M, N, K, seed=M + N + K)
+
+
+@pytest.mark.parametrize("path", [1, 2, 3])
+@pytest.mark.parametrize("ta,tb", [(NT, T), (T, NT), (T, T)])
+@pytest.mark.parametrize("M,N,K", [(64, 10, 784), (130, 258, 70), (256, 128, 512)])
+def test_transposed_accumulate(ops, zo, path, ta, tb, M, N, K):
+    """The backward calls: dA += dC.B^T (NoTrans,Trans) and dB += A^T.dC (Trans,NoTrans), beta = 1."""
+    run_case(ops, zo, path, ta, tb, M, N, K, beta=1.0, seed=7 * M + N)
+
+
+@pytest.mark.parametrize("path", [1, 2, 3])
+def test_alpha_beta_and_leading_dimensions(ops, zo, path):
+    run_case(ops, zo, path, NT, NT, 150, 90, 200, alpha=0.5, beta=-2.0, lda_pad=3, ldb_pad=5, ldc_pad=7, seed=3)
+    run_case(ops, zo, path, T, T, 129, 257, 65, alpha=2.0, beta=0.0, lda_pad=1, ldb_pad=2, ldc_pad=1, seed=4)
+
+
+def test_beta_zero_ignores_old_c(ops):
+    """beta == 0 must overwrite C even when it holds NaN (the reference memsets, cblas.zig:56-60)."""
+    r = np.random.default_rng(5)
+    for path in (1, 2, 3):
+        A, B = r.standard_normal((128, 64), np.float32), r.standard_normal((64, 256), np.float32)
+        Cm = np.full((128, 256), np.nan, np.float32)
+        ops.set_gemm_path(path)
+        ops.sgemm(NT, NT, 128, 256, 64, 1.0, A, 64, B, 256, 0.0, Cm, 256)
+        assert np.isfinite(Cm).all()
+
+
+def test_degenerate(ops, zo):
+    ops.set_gemm_path(0)
+    Cm = np.ones((4, 5), np.float32)
+    A, B = np.ones((4, 1), np.float32), np.ones((1, 5), np.float32)
+    ops.sgemm(NT, NT, 4, 5, 0, 1.0, A, 1, B, 5, 0.0, Cm, 5)      # K == 0: C = beta*C
+    assert (Cm == 0).all()
+    Cm = np.full((4, 5), 3.0, np.float32)
+    ops.sgemm(NT, NT, 4, 5, 1, 0.0, A, 1, B, 5, 0.5, Cm, 5)      # alpha == 0
+    assert (Cm == 1.5).all()
+    ops.sgemm(NT, NT, 0, 5, 1, 1.0, A, 1, B, 5, 0.0, Cm, 5)      # empty M: no-op
+
+
+@pytest.mark.parametrize("path", [1, 2, 3])
+def test_batched(ops, zo, path):
+    """BatchMatMul forward/backward shapes of attention (per (b,h) slices)."""
+    r = np.random.default_rng(11)
+    nb, Tn, hs = 6, 96, 64
+    q = r.standard_normal((nb, Tn, hs), np.float32)
+    kt = r.standard_normal((nb, hs, Tn), np.float32)
+    ops.set_gemm_path(path)
+    got = ops.batch_matmul_fwd(q, kt)
+    want = zo.batch_matmul_fwd(q, kt)
+    assert rel_err(got, want) <= TOL
+    dC = r.standard_normal((nb, Tn, Tn), np.float32)
+    g = [np.zeros_like(q), np.zeros_like(kt)]
+    h = [np.zeros_like(q), np.zeros_like(kt)]
+    ops.batch_matmul_bwd(q, kt, dC, g[0], g[1])
+    zo.batch_matmul_bwd(q, kt, dC, h[0], h[1])
+    assert rel_err(g[0], h[0]) <= TOL and rel_err(g[1], h[1]) <= TOL
+
+
+@pytest.mark.parametrize("path", [2, 3, 0])
+@pytest.mark.parametrize("M,N,K", [(512, 512, 512), (1024, 1024, 1024), (64, 4096, 4096), (4096, 64, 4096)])
+def test_sweep_shapes_vs_fp64(ops, zo, path, M, N, K):
+    """Workload-definition sweep shapes that the fp64 arbiter finishes quickly on the CPU."""
+    A, B = make(NT, NT, M, N, K, seed=M ^ N ^ K)
+    ops.set_gemm_path(path)
+    got = ops.matmul_fwd(A, B)
+    exact = A.astype(np.float64) @ B.astype(np.float64)
+    e = rel_err(got, exact)
+    assert e <= TOL, f"{M}x{N}x{K} path {path}: rel err {e:.3e} vs fp64"
+    dC = np.random.default_rng(9).standard_normal((M, N), np.float32)
+    dA, dB = np.zeros_like(A), np.zeros_like(B)
+    ops.matmul_bwd(A, B, dC, dA, dB)
+    assert rel_err(dA, dC.astype(np.float64) @ B.astype(np.float64).T) <= TOL
+    assert rel_err(dB, A.astype(np.float64).T @ dC.astype(np.float64)) <= TOL
+
+
+def test_full_size_rows_vs_fp64(ops):
+    """8192^3: sampled output rows against exact arithmetic, plus linearity in A."""
+    n = 8192
+    r = np.random.default_rng(8192)
+    A, B = r.standard_normal((n, n), np.float32), r.standard_normal((n, n), np.float32)
+    ops.set_gemm_path(0)
+    got = ops.matmul_fwd(A, B)
+    rows = r.choice(n, 24, replace=False)
+    exact = A[rows].astype(np.float64) @ B.astype(np.float64)
+    e = rel_err(got[rows], exact)
+    assert e <= TOL, f"8192^3 sampled rows: rel err {e:.3e} vs fp64"
+    got2 = ops.matmul_fwd(A * np.float32(2.0), B)   # scaling by a power of two is exact
+    np.testing.assert_array_equal(got2, got * np.float32(2.0))

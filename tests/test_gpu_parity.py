@@ -1,0 +1,304 @@
+"""Row-wise / conv / pooling operators: CUDA (through the C ABI) against the CPU
+oracle on the same seeded inputs, including ragged and unaligned sizes.
+
+Tolerances: integer/index results (argmax, MaxPool indices) bit-exact; Conv2D
+forward bit-exact (same summation order and rounding points as the reference
+loops); everything else relative 1e-5 of the result's scale.
+"""
+import numpy as np
+import pytest
+
+pytestmark = pytest.mark.gpu
+
+RTOL = 1e-5
+
+
+@pytest.fixture(scope="module")
+def ops():
+    from znn_b200 import ops as _ops
+    _ops.init(0)
+    return _ops
+
+
+def close(got, want, rtol=RTOL, what=""):
+    got, want = np.asarray(got, np.float64), np.asarray(want, np.float64)
+    assert got.shape == want.shape, (what, got.shape, want.shape)
+    scale = max(1e-30, float(np.abs(want).max())) if want.size else 1.0
+    err = float(np.abs(got - want).max()) if want.size else 0.0
+    assert err <= rtol * scale + 1e-12, f"{what}: max abs err {err:.3e} vs scale {scale:.3e} (rel {err / scale:.3e})"
+
+
+def rng(seed):
+    return np.random.default_rng(seed)
+
+
+@pytest.mark.parametrize("M,N", [(1, 1), (2, 3), (64, 10), (100, 128), (257, 769), (8, 4096)])
+def test_add_bias(ops, zo, M, N):
+    r = rng(M * 1000 + N)
+    A, b = r.standard_normal((M, N), np.float32), r.standard_normal(N, np.float32)
+    np.testing.assert_array_equal(ops.add_bias_fwd(A, b), zo.add_bias_fwd(A, b))
+    dC = r.standard_normal((M, N), np.float32)
+    dA0, db0 = r.standard_normal((M, N), np.float32), r.standard_normal(N, np.float32)
+    dA1, db1, dA2, db2 = dA0.copy(), db0.copy(), dA0.copy(), db0.copy()
+    ops.add_bias_bwd(dC, dA1, db1)
+    zo.add_bias_bwd(dC, dA2, db2)
+    np.testing.assert_array_equal(dA1, dA2)
+    close(db1, db2, what="dbias")
+    db3, db4 = db0.copy(), db0.copy()
+    ops.add_bias_bwd(dC, None, db3)   # input without requires_grad
+    zo.add_bias_bwd(dC, None, db4)
+    close(db3, db4, what="dbias (no dA)")
+
+
+@pytest.mark.parametrize("n", [1, 5, 1024, 4099, 1 << 20])
+def test_relu_gelu(ops, zo, n):
+    r = rng(n)
+    A = (r.standard_normal(n, np.float32) * 2.0).astype(np.float32)
+    A[::7] = 0.0
+    np.testing.assert_array_equal(ops.relu_fwd(A), zo.relu_fwd(A))
+    close(ops.gelu_fwd(A), zo.gelu_fwd(A), what="gelu")
+    dC = r.standard_normal(n, np.float32)
+    base = r.standard_normal(n, np.float32)
+    g1, g2 = base.copy(), base.copy()
+    ops.relu_bwd(A, dC, g1)
+    zo.relu_bwd(A, dC, g2)
+    np.testing.assert_array_equal(g1, g2)
+    g1, g2 = base.copy(), base.copy()
+    ops.gelu_bwd(A, dC, g1)
+    zo.gelu_bwd(A, dC, g2)
+    close(g1, g2, what="gelu bwd")
+
+
+@pytest.mark.parametrize("M,N", [(1, 2), (64, 10), (256, 10), (33, 255), (16, 8192), (5, 1000)])
+def test_softmax_xent(ops, zo, M, N):
+    r = rng(M * 7 + N)
+    X = (r.standard_normal((M, N), np.float32) * 3.0).astype(np.float32)
+    t = r.integers(0, N, M).astype(np.int32)
+    l1, p1 = ops.softmax_xent_fwd(X, t)
+    l2, p2 = zo.softmax_xent_fwd(X, t)
+    close(p1, p2, what="probs")
+    close(l1, l2, what="loss")
+    d0 = r.standard_normal((M, N), np.float32)
+    d1, d2 = d0.copy(), d0.copy()
+    ops.softmax_xent_bwd(p2, t, d1)
+    zo.softmax_xent_bwd(p2, t, d2)
+    close(d1, d2, what="dlogits")
+    if N <= 256:  # the reference's u8 targets
+        l3, p3 = ops.softmax_xent_fwd(X, t.astype(np.uint8), u8=True)
+        np.testing.assert_array_equal(p3, p1)
+        np.testing.assert_array_equal(l3, l1)
+
+
+def test_softmax_xent_clip(ops, zo):
+    """The target's probability underflows: the loss clips at -log(1e-15)."""
+    X = np.array([[200.0, -200.0], [0.0, 1.0]], np.float32)
+    t = np.array([1, 1], np.int32)
+    l1, _ = ops.softmax_xent_fwd(X, t)
+    l2, _ = zo.softmax_xent_fwd(X, t)
+    close(l1, l2, what="clipped loss")
+
+
+@pytest.mark.parametrize("rows,D", [(1, 1), (6, 3), (64, 256), (40, 1000), (3, 5000)])
+def test_softmax_rows(ops, zo, rows, D):
+    r = rng(rows + D)
+    X = (r.standard_normal((rows, D), np.float32) * 4.0).astype(np.float32)
+    Y1, Y2 = ops.softmax_fwd(X), zo.softmax_fwd(X)
+    close(Y1, Y2, what="softmax")
+    dY = r.standard_normal((rows, D), np.float32)
+    d0 = r.standard_normal((rows, D), np.float32)
+    d1, d2 = d0.copy(), d0.copy()
+    ops.softmax_bwd(Y2, dY, d1)
+    zo.softmax_bwd(Y2, dY, d2)
+    close(d1, d2, what="softmax bwd")
+
+
+@pytest.mark.parametrize("ns,T", [(1, 1), (3, 5), (4, 64), (2, 256), (1, 1024), (2, 100)])
+def test_causal_softmax(ops, zo, ns, T):
+    """Fused scale + causal mask + softmax against the reference's three separate ops."""
+    r = rng(ns * 31 + T)
+    S = (r.standard_normal((ns, T, T), np.float32) * 5.0).astype(np.float32)
+    scale = 1.0 / np.sqrt(64.0).astype(np.float32)
+    P1, P2 = ops.causal_softmax_fwd(S, float(scale)), zo.causal_softmax_fwd(S, float(scale))
+    close(P1, P2, what="causal softmax")
+    iu = np.triu_indices(T, 1)
+    assert np.all(P1[:, iu[0], iu[1]] == 0.0)
+    dP = r.standard_normal((ns, T, T), np.float32)
+    d0 = r.standard_normal((ns, T, T), np.float32)
+    d1, d2 = d0.copy(), d0.copy()
+    ops.causal_softmax_bwd(P2, dP, float(scale), d1)
+    zo.causal_softmax_bwd(P2, dP, float(scale), d2)
+    close(d1, d2, what="causal softmax bwd")
+
+
+@pytest.mark.parametrize("rows,D", [(1, 1), (2, 3), (64, 512), (100, 768), (7, 1001)])
+def test_rmsnorm_layernorm(ops, zo, rows, D):
+    r = rng(rows * 3 + D)
+    X = r.standard_normal((rows, D), np.float32)
+    G = (1.0 + 0.1 * r.standard_normal(D)).astype(np.float32)
+    Bt = (0.1 * r.standard_normal(D)).astype(np.float32)
+    dY = r.standard_normal((rows, D), np.float32)
+    close(ops.rmsnorm_fwd(X, G, 1e-5), zo.rmsnorm_fwd(X, G, 1e-5), what="rmsnorm")
+    dx0, dg0 = r.standard_normal((rows, D), np.float32), r.standard_normal(D, np.float32)
+    a, b, c, d = dx0.copy(), dg0.copy(), dx0.copy(), dg0.copy()
+    ops.rmsnorm_bwd(X, G, dY, 1e-5, a, b)
+    zo.rmsnorm_bwd(X, G, dY, 1e-5, c, d)
+    close(a, c, what="rmsnorm dX")
+    close(b, d, rtol=3e-5, what="rmsnorm dG")
+    close(ops.layernorm_fwd(X, G, Bt, 1e-5), zo.layernorm_fwd(X, G, Bt, 1e-5), what="layernorm")
+    a, b, e = dx0.copy(), dg0.copy(), dg0.copy()
+    c, d, f = dx0.copy(), dg0.copy(), dg0.copy()
+    ops.layernorm_bwd(X, G, dY, 1e-5, a, b, e)
+    zo.layernorm_bwd(X, G, dY, 1e-5, c, d, f)
+    close(a, c, rtol=3e-5, what="layernorm dX")
+    close(b, d, rtol=3e-5, what="layernorm dG")
+    close(e, f, rtol=3e-5, what="layernorm dB")
+
+
+CONV_CASES = [
+    # N, Ci, H, W, Co, K, pad
+    (1, 1, 3, 3, 1, 2, 0),
+    (64, 1, 28, 28, 4, 3, 0),     # reference CNN layer 1 (examples/cnn.zig)
+    (64, 4, 13, 13, 8, 3, 0),     # layer 2
+    (64, 8, 5, 5, 16, 3, 0),      # layer 3
+    (16, 1, 28, 28, 32, 3, 1),    # workload-definition shapes (padded), reduced batch
+    (8, 32, 14, 14, 64, 3, 1),
+    (3, 5, 9, 7, 11, 3, 1),       # ragged everything
+    (2, 3, 6, 6, 2, 5, 2),
+]
+
+
+@pytest.mark.parametrize("N,Ci,H,W,Co,K,pad", CONV_CASES)
+def test_conv2d(ops, zo, N, Ci, H, W, Co, K, pad):
+    r = rng(N + Ci * 10 + H * 100 + Co * 1000 + pad)
+    X = r.random((N, Ci, H, W), np.float32)
+    Wt = (r.standard_normal((Co, Ci, K, K)) * 0.3).astype(np.float32)
+    b = (r.standard_normal(Co) * 0.1).astype(np.float32)
+    Y1, Y2 = ops.conv2d_fwd(X, Wt, b, pad), zo.conv2d_fwd(X, Wt, b, pad)
+    np.testing.assert_array_equal(Y1, Y2)   # same order, same rounding: bit-exact
+    np.testing.assert_array_equal(ops.conv2d_fwd(X, Wt, None, pad), zo.conv2d_fwd(X, Wt, None, pad))
+    dY = r.standard_normal(Y2.shape, np.float32)
+    dY[r.random(Y2.shape) < 0.3] = 0.0      # ReLU-like zeros: the reference skips them
+    g = [np.zeros_like(X), np.zeros_like(Wt), np.zeros_like(b)]
+    h = [np.zeros_like(X), np.zeros_like(Wt), np.zeros_like(b)]
+    ops.conv2d_bwd(X, Wt, dY, g[0], g[1], g[2], pad)
+    zo.conv2d_bwd(X, Wt, dY, h[0], h[1], h[2], pad)
+    close(g[0], h[0], what="conv dX")
+    close(g[1], h[1], rtol=3e-5, what="conv dW")
+    close(g[2], h[2], rtol=3e-5, what="conv dbias")
+    # first layer: the input has no gradient
+    g1, h1 = np.zeros_like(Wt), np.zeros_like(Wt)
+    ops.conv2d_bwd(X, Wt, dY, None, g1, None, pad)
+    zo.conv2d_bwd(X, Wt, dY, None, h1, None, pad)
+    close(g1, h1, rtol=3e-5, what="conv dW only")
+
+
+@pytest.mark.parametrize("N,C,H,W,pool,stride", [(1, 1, 4, 4, 2, 2), (64, 4, 26, 26, 2, 2), (64, 8, 11, 11, 2, 2),
+                                                (8, 32, 28, 28, 2, 2), (3, 2, 7, 9, 3, 2), (2, 2, 8, 8, 3, 1)])
+def test_maxpool2d(ops, zo, N, C, H, W, pool, stride):
+    r = rng(N + C + H + W + pool)
+    X = r.standard_normal((N, C, H, W), np.float32)
+    Y1, i1 = ops.maxpool2d_fwd(X, pool, stride, want_idx=True)
+    Y2, i2 = zo.maxpool2d_fwd(X, pool, stride, want_idx=True)
+    np.testing.assert_array_equal(i1, i2)
+    np.testing.assert_array_equal(Y1, Y2)
+    dY = r.standard_normal(Y2.shape, np.float32)
+    dY[r.random(Y2.shape) < 0.2] = 0.0
+    d0 = r.standard_normal(X.shape, np.float32)
+    d1, d2 = d0.copy(), d0.copy()
+    ops.maxpool2d_bwd(X, dY, d1, pool, stride)
+    zo.maxpool2d_bwd(X, dY, d2, pool, stride)
+    if stride >= pool:
+        np.testing.assert_array_equal(d1, d2)
+    else:
+        close(d1, d2, what="overlapping pool bwd")
+
+
+def test_maxpool2d_ties(ops, zo):
+    """Constructed ties: the first maximum in (ph, pw) order must win."""
+    X = np.zeros((2, 3, 6, 6), np.float32)
+    X[0, 0] = 1.0                       # every window all-equal
+    X[0, 1, ::2, 1::2] = 5.0            # ties between (0,1) of neighbouring windows only
+    X[0, 2, 1::2, :] = 2.0              # ties along the bottom row of each window
+    X[1] = np.tile(np.array([[3, 3], [3, 3]], np.float32), (3, 3))
+    Y1, i1 = ops.maxpool2d_fwd(X, 2, 2, want_idx=True)
+    Y2, i2 = zo.maxpool2d_fwd(X, 2, 2, want_idx=True)
+    np.testing.assert_array_equal(i1, i2)
+    assert i2[0, 0, 0, 0] == 0 and i2[0, 2, 0, 0] == 6
+    d1, d2 = np.zeros_like(X), np.zeros_like(X)
+    ops.maxpool2d_bwd(X, np.ones_like(Y2), d1, 2, 2)
+    zo.maxpool2d_bwd(X, np.ones_like(Y2), d2, 2, 2)
+    np.testing.assert_array_equal(d1, d2)
+
+
+@pytest.mark.parametrize("V,D,shape", [(3, 4, (2, 2)), (50, 33, (4, 7)), (1000, 768, (2, 300)), (16, 2500, (3, 9))])
+def test_embedding(ops, zo, V, D, shape):
+    r = rng(V + D)
+    W = r.standard_normal((V, D), np.float32)
+    ids = r.integers(0, V, shape).astype(np.float32)
+    np.testing.assert_array_equal(ops.embedding_fwd(W, ids), zo.embedding_fwd(W, ids))
+    dY = r.standard_normal(shape + (D,), np.float32)
+    g0 = r.standard_normal((V, D), np.float32)
+    g1, g2 = g0.copy(), g0.copy()
+    ops.embedding_bwd(ids, dY, g1)
+    zo.embedding_bwd(ids, dY, g2)
+    close(g1, g2, what="embedding dW")
+
+
+@pytest.mark.parametrize("shape,d0,d1", [((2, 3), 0, 1), ((4, 16, 12, 64), 1, 2), ((2, 3, 5, 7), 2, 3),
+                                          ((2, 12, 100, 64), 2, 3), ((3, 4, 5), 0, 2), ((33, 65), 0, 1)])
+def test_transpose(ops, zo, shape, d0, d1):
+    r = rng(sum(shape))
+    A = r.standard_normal(shape, np.float32)
+    np.testing.assert_array_equal(ops.transpose_fwd(A, d0, d1), zo.transpose_fwd(A, d0, d1))
+    oshape = list(shape)
+    oshape[d0], oshape[d1] = oshape[d1], oshape[d0]
+    dC = r.standard_normal(oshape, np.float32)
+    g0 = r.standard_normal(shape, np.float32)
+    g1, g2 = g0.copy(), g0.copy()
+    ops.transpose_bwd(dC, g1, d0, d1)
+    zo.transpose_bwd(dC, g2, d0, d1)
+    np.testing.assert_array_equal(g1, g2)
+
+
+@pytest.mark.parametrize("n", [1, 7, 4096, 100003])
+def test_add_mul_accumulate(ops, zo, n):
+    r = rng(n)
+    A, B = r.standard_normal(n, np.float32), r.standard_normal(n, np.float32)
+    np.testing.assert_array_equal(ops.add_fwd(A, B), zo.add_fwd(A, B))
+    np.testing.assert_array_equal(ops.mul_scalar_fwd(A, 0.125), zo.mul_scalar_fwd(A, 0.125))
+    np.testing.assert_array_equal(ops.mul_scalar_fwd(A, 0.3), zo.mul_scalar_fwd(A, 0.3))
+    d1, d2 = B.copy(), B.copy()
+    ops.accumulate(A, d1)
+    zo.accumulate(A, d2)
+    np.testing.assert_array_equal(d1, d2)
+    d1, d2 = B.copy(), B.copy()
+    ops.mul_scalar_bwd(A, 0.3, d1)
+    zo.mul_scalar_bwd(A, 0.3, d2)
+    np.testing.assert_array_equal(d1, d2)
+
+
+@pytest.mark.parametrize("M,N", [(2, 3), (64, 10), (100, 1), (1, 100), (64, 8192), (7, 33)])
+def test_argmax_bit_exact(ops, zo, M, N):
+    r = rng(M * 13 + N)
+    A = r.integers(-3, 4, (M, N)).astype(np.float32)   # many exact ties
+    for dim in (0, 1):
+        np.testing.assert_array_equal(ops.argmax(A, dim), zo.argmax(A, dim))
+    A = r.standard_normal((M, N), np.float32)
+    for dim in (0, 1):
+        np.testing.assert_array_equal(ops.argmax(A, dim), zo.argmax(A, dim))
+
+
+@pytest.mark.parametrize("n", [1, 1000, 1 << 18])
+def test_sgd_step(ops, zo, n):
+    r = rng(n)
+    w0, g = r.standard_normal(n, np.float32), r.standard_normal(n, np.float32)
+    w1, w2 = w0.copy(), w0.copy()
+    ops.sgd_step(w1, g, None, 0.05, 0.0)
+    zo.sgd_step(w2, g, None, 0.05, 0.0)
+    np.testing.assert_array_equal(w1, w2)
+    w1, w2, v1, v2 = w0.copy(), w0.copy(), np.zeros(n, np.float32), np.zeros(n, np.float32)
+    for _ in range(3):
+        ops.sgd_step(w1, g, v1, 0.01, 0.9)
+        zo.sgd_step(w2, g, v2, 0.01, 0.9)
+    np.testing.assert_array_equal(w1, w2)
+    np.testing.assert_array_equal(v1, v2)

@@ -1,0 +1,50 @@
+// Shared helpers for the znn CUDA shim (sm_100a only).
+#pragma once
+#include <cuda_runtime.h>
+#include <stdint.h>
+#include <stdio.h>
+
+#include "../../include/znn_cuda.h"
+
+namespace znn {
+
+// Per-host-thread error text, returned by znn_last_error().
+void set_error(const char* fmt, ...);
+int fail(int code, const char* fmt, ...);
+
+// The stream every kernel of the calling host thread is launched on.
+cudaStream_t stream();
+
+// Device status word (one int per device, zero-initialised).  Kernels OR a
+// ZNN_DEV_* bit into it when a bounded wait expires; znn_device_status() reads it.
+int* device_status_word();
+
+// Shim-owned scratch for GEMM operand planes; grows on demand.
+void* workspace(size_t bytes);
+
+int sm_count();
+
+#define ZNN_CUDA_OK(expr)                                                              \
+    do {                                                                               \
+        cudaError_t _e = (expr);                                                       \
+        if (_e != cudaSuccess)                                                         \
+            return ::znn::fail(ZNN_ERR_CUDA, "%s failed: %s (%s:%d)", #expr,           \
+                               cudaGetErrorString(_e), __FILE__, __LINE__);            \
+    } while (0)
+
+#define ZNN_LAUNCH_OK(name)                                                            \
+    do {                                                                               \
+        cudaError_t _e = cudaGetLastError();                                           \
+        if (_e != cudaSuccess)                                                         \
+            return ::znn::fail(ZNN_ERR_CUDA, "launch of %s failed: %s", name,          \
+                               cudaGetErrorString(_e));                                \
+    } while (0)
+
+#define ZNN_REQUIRE(cond, ...)                                                         \
+    do {                                                                               \
+        if (!(cond)) return ::znn::fail(ZNN_ERR_INVALID, __VA_ARGS__);                 \
+    } while (0)
+
+static inline int ceil_div(long a, long b) { return (int)((a + b - 1) / b); }
+
+}  // namespace znn

@@ -1,0 +1,280 @@
+// Conv2D (NCHW, stride 1, optional zero padding) and MaxPool2D.
+//
+// The reference's convolutions have K = Ci*KH*KW between 9 and 288 and at most
+// 64 output channels: far below a tensor-core tile, and a few GFLOP per step at
+// most.  They run as direct CUDA-core kernels that keep the reference's
+// summation order (bias, then ci -> kh -> kw) and, being compiled with
+// -fmad=false, its rounding points: the forward pass is bit-identical to the
+// reference loops, which is what keeps MaxPool argmax indices bit-exact.
+#include "common.cuh"
+
+namespace znn {
+
+constexpr int kCoTile = 8;  // output channels per thread
+
+// One thread: one output pixel (n, h, w) for kCoTile consecutive output channels.
+// The weights of the channel tile sit in shared memory.
+__global__ void conv2d_fwd_kernel(const float* __restrict__ X, const float* __restrict__ W, const float* __restrict__ bias,
+                                  float* __restrict__ Y, int N, int Ci, int H, int Wd, int Co, int KH, int KW, int pad,
+                                  int Ho, int Wo)
+{
+    extern __shared__ float wsh[];  // [kCoTile][Ci*KH*KW]
+    const int kk = Ci * KH * KW;
+    const int co0 = blockIdx.y * kCoTile;
+    for (int i = threadIdx.x; i < kCoTile * kk; i += blockDim.x) {
+        const int c = i / kk;
+        wsh[i] = (co0 + c < Co) ? W[(size_t)(co0 + c) * kk + (i - c * kk)] : 0.0f;
+    }
+    __syncthreads();
+    const size_t pix = blockIdx.x * (size_t)blockDim.x + threadIdx.x;
+    const size_t npix = (size_t)N * Ho * Wo;
+    if (pix >= npix) return;
+    const int w = (int)(pix % Wo);
+    const int h = (int)((pix / Wo) % Ho);
+    const int n = (int)(pix / ((size_t)Wo * Ho));
+    float acc[kCoTile];
+#pragma unroll
+    for (int c = 0; c < kCoTile; c++) acc[c] = (bias && co0 + c < Co) ? bias[co0 + c] : 0.0f;
+    const float* xn = X + (size_t)n * Ci * H * Wd;
+    int widx = 0;
+    for (int ci = 0; ci < Ci; ci++)
+        for (int kh = 0; kh < KH; kh++) {
+            const int ih = h + kh - pad;
+            for (int kw = 0; kw < KW; kw++, widx++) {
+                const int iw = w + kw - pad;
+                if (ih < 0 || ih >= H || iw < 0 || iw >= Wd) continue;
+                const float xv = xn[((size_t)ci * H + ih) * Wd + iw];
+#pragma unroll
+                for (int c = 0; c < kCoTile; c++) acc[c] += xv * wsh[c * kk + widx];
+            }
+        }
+#pragma unroll
+    for (int c = 0; c < kCoTile; c++)
+        if (co0 + c < Co) Y[(((size_t)n * Co + co0 + c) * Ho + h) * Wo + w] = acc[c];
+}
+
+// dX[n,ci,ih,iw] += sum_{co,kh,kw} dY[n,co,ih-kh+pad,iw-kw+pad] * W[co,ci,kh,kw]  (gather form)
+__global__ void conv2d_bwd_data_kernel(const float* __restrict__ dY, const float* __restrict__ W, float* __restrict__ dX,
+                                       int N, int Ci, int H, int Wd, int Co, int KH, int KW, int pad, int Ho, int Wo)
+{
+    extern __shared__ float wsh[];  // all weights [Co][Ci][KH][KW]
+    const int wtotal = Co * Ci * KH * KW;
+    for (int i = threadIdx.x; i < wtotal; i += blockDim.x) wsh[i] = W[i];
+    __syncthreads();
+    const size_t total = (size_t)N * Ci * H * Wd;
+    for (size_t e = blockIdx.x * (size_t)blockDim.x + threadIdx.x; e < total; e += (size_t)gridDim.x * blockDim.x) {
+        const int iw = (int)(e % Wd);
+        const int ih = (int)((e / Wd) % H);
+        const int ci = (int)((e / ((size_t)Wd * H)) % Ci);
+        const int n = (int)(e / ((size_t)Wd * H * Ci));
+        float acc = 0.0f;
+        for (int co = 0; co < Co; co++) {
+            const float* dy = dY + ((size_t)n * Co + co) * Ho * Wo;
+            const float* wk = wsh + ((size_t)co * Ci + ci) * KH * KW;
+            for (int kh = 0; kh < KH; kh++) {
+                const int h = ih - kh + pad;
+                if (h < 0 || h >= Ho) continue;
+                for (int kw = 0; kw < KW; kw++) {
+                    const int w = iw - kw + pad;
+                    if (w < 0 || w >= Wo) continue;
+                    acc += dy[(size_t)h * Wo + w] * wk[kh * KW + kw];
+                }
+            }
+        }
+        dX[e] += acc;
+    }
+}
+
+// One block per (co, ci): the KH*KW weight gradients of that pair, reduced over
+// all (n, h, w) in a fixed order (thread-strided partial sums, then a tree).
+__global__ void conv2d_bwd_weight_kernel(const float* __restrict__ X, const float* __restrict__ dY, float* __restrict__ dW,
+                                         int N, int Ci, int H, int Wd, int Co, int KH, int KW, int pad, int Ho, int Wo)
+{
+    extern __shared__ float red[];  // [blockDim.x]
+    const int co = blockIdx.x / Ci, ci = blockIdx.x % Ci;
+    const size_t npix = (size_t)N * Ho * Wo;
+    for (int kh = 0; kh < KH; kh++)
+        for (int kw = 0; kw < KW; kw++) {
+            float s = 0.0f;
+            for (size_t pix = threadIdx.x; pix < npix; pix += blockDim.x) {
+                const int w = (int)(pix % Wo);
+                const int h = (int)((pix / Wo) % Ho);
+                const int n = (int)(pix / ((size_t)Wo * Ho));
+                const int ih = h + kh - pad, iw = w + kw - pad;
+                if (ih < 0 || ih >= H || iw < 0 || iw >= Wd) continue;
+                const float g = dY[(((size_t)n * Co + co) * Ho + h) * Wo + w];
+                s += g * X[(((size_t)n * Ci + ci) * H + ih) * Wd + iw];
+            }
+            red[threadIdx.x] = s;
+            __syncthreads();
+            for (int o = blockDim.x >> 1; o > 0; o >>= 1) {
+                if ((int)threadIdx.x < o) red[threadIdx.x] += red[threadIdx.x + o];
+                __syncthreads();
+            }
+            if (threadIdx.x == 0) dW[(((size_t)co * Ci + ci) * KH + kh) * KW + kw] += red[0];
+            __syncthreads();
+        }
+}
+
+__global__ void conv2d_bwd_bias_kernel(const float* __restrict__ dY, float* __restrict__ dbias, int N, int Co, int HoWo)
+{
+    extern __shared__ float red[];
+    const int co = blockIdx.x;
+    float s = 0.0f;
+    const size_t total = (size_t)N * HoWo;
+    for (size_t i = threadIdx.x; i < total; i += blockDim.x) {
+        const size_t n = i / HoWo, r = i % HoWo;
+        s += dY[(n * Co + co) * HoWo + r];
+    }
+    red[threadIdx.x] = s;
+    __syncthreads();
+    for (int o = blockDim.x >> 1; o > 0; o >>= 1) {
+        if ((int)threadIdx.x < o) red[threadIdx.x] += red[threadIdx.x + o];
+        __syncthreads();
+    }
+    if (threadIdx.x == 0) dbias[co] += red[0];
+}
+
+// window origin (h*stride, w*stride); first maximum in (ph, pw) order wins (strict >)
+__device__ __forceinline__ int pool_argmax(const float* __restrict__ x, int H, int W, int h, int w, int pool, int stride,
+                                           float& best)
+{
+    int bi = (h * stride) * W + (w * stride);
+    best = x[bi];
+    for (int ph = 0; ph < pool; ph++)
+        for (int pw = 0; pw < pool; pw++) {
+            const int ih = h * stride + ph, iw = w * stride + pw;
+            if (ih < H && iw < W) {
+                const float v = x[ih * W + iw];
+                if (v > best) { best = v; bi = ih * W + iw; }
+            }
+        }
+    return bi;
+}
+
+__global__ void maxpool2d_fwd_kernel(const float* __restrict__ X, float* __restrict__ Y, int32_t* __restrict__ idx,
+                                     size_t planes, int H, int W, int Ho, int Wo, int pool, int stride)
+{
+    const size_t total = planes * Ho * Wo;
+    for (size_t e = blockIdx.x * (size_t)blockDim.x + threadIdx.x; e < total; e += (size_t)gridDim.x * blockDim.x) {
+        const int w = (int)(e % Wo), h = (int)((e / Wo) % Ho);
+        const size_t pl = e / ((size_t)Wo * Ho);
+        float best;
+        const int bi = pool_argmax(X + pl * H * W, H, W, h, w, pool, stride, best);
+        Y[e] = best;
+        if (idx) idx[e] = bi;
+    }
+}
+
+template <bool Overlap>
+__global__ void maxpool2d_bwd_kernel(const float* __restrict__ X, const float* __restrict__ dY, float* __restrict__ dX,
+                                     size_t planes, int H, int W, int Ho, int Wo, int pool, int stride)
+{
+    const size_t total = planes * Ho * Wo;
+    for (size_t e = blockIdx.x * (size_t)blockDim.x + threadIdx.x; e < total; e += (size_t)gridDim.x * blockDim.x) {
+        const float g = dY[e];
+        if (g == 0.0f) continue;
+        const int w = (int)(e % Wo), h = (int)((e / Wo) % Ho);
+        const size_t pl = e / ((size_t)Wo * Ho);
+        float best;
+        const int bi = pool_argmax(X + pl * H * W, H, W, h, w, pool, stride, best);
+        // windows are disjoint when stride >= pool: a plain add is race-free
+        if (Overlap) atomicAdd(dX + pl * H * W + bi, g); else dX[pl * H * W + bi] += g;
+    }
+}
+
+}  // namespace znn
+
+using namespace znn;
+
+extern "C" {
+
+int znn_conv2d_fwd(const float* X, const float* W, const float* bias, float* Y, int N, int Ci, int H, int Wd, int Co,
+                   int KH, int KW, int pad)
+{
+    ZNN_REQUIRE(N >= 0 && Ci > 0 && Co > 0 && KH > 0 && KW > 0 && pad >= 0, "bad conv shape");
+    const int Ho = H + 2 * pad - KH + 1, Wo = Wd + 2 * pad - KW + 1;
+    ZNN_REQUIRE(Ho > 0 && Wo > 0, "kernel larger than padded input");
+    if (N == 0) return ZNN_OK;
+    if (!stream()) return fail(ZNN_ERR_CUDA, "no CUDA device state; call znn_init (no CPU fallback)");
+    ZNN_REQUIRE(X && W && Y, "NULL pointer");
+    const size_t smem = (size_t)kCoTile * Ci * KH * KW * sizeof(float);
+    ZNN_REQUIRE(smem <= 96 * 1024, "Ci*KH*KW = %d is beyond what the direct kernel keeps in shared memory", Ci * KH * KW);
+    if (smem > 48 * 1024)
+        ZNN_CUDA_OK(cudaFuncSetAttribute(conv2d_fwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    const size_t npix = (size_t)N * Ho * Wo;
+    dim3 grid((unsigned)((npix + 127) / 128), ceil_div(Co, kCoTile));
+    conv2d_fwd_kernel<<<grid, 128, smem, stream()>>>(X, W, bias, Y, N, Ci, H, Wd, Co, KH, KW, pad, Ho, Wo);
+    ZNN_LAUNCH_OK("conv2d_fwd_kernel");
+    return ZNN_OK;
+}
+
+int znn_conv2d_bwd(const float* X, const float* W, const float* dY, float* dX, float* dW, float* dbias, int N, int Ci,
+                   int H, int Wd, int Co, int KH, int KW, int pad)
+{
+    ZNN_REQUIRE(N >= 0 && Ci > 0 && Co > 0 && KH > 0 && KW > 0 && pad >= 0, "bad conv shape");
+    const int Ho = H + 2 * pad - KH + 1, Wo = Wd + 2 * pad - KW + 1;
+    ZNN_REQUIRE(Ho > 0 && Wo > 0, "kernel larger than padded input");
+    if (N == 0) return ZNN_OK;
+    if (!stream()) return fail(ZNN_ERR_CUDA, "no CUDA device state; call znn_init (no CPU fallback)");
+    ZNN_REQUIRE(X && W && dY, "NULL pointer");
+    if (dbias) {
+        conv2d_bwd_bias_kernel<<<Co, 256, 256 * sizeof(float), stream()>>>(dY, dbias, N, Co, Ho * Wo);
+        ZNN_LAUNCH_OK("conv2d_bwd_bias_kernel");
+    }
+    if (dW) {
+        conv2d_bwd_weight_kernel<<<Co * Ci, 256, 256 * sizeof(float), stream()>>>(X, dY, dW, N, Ci, H, Wd, Co, KH, KW, pad,
+                                                                                  Ho, Wo);
+        ZNN_LAUNCH_OK("conv2d_bwd_weight_kernel");
+    }
+    if (dX) {
+        const size_t smem = (size_t)Co * Ci * KH * KW * sizeof(float);
+        ZNN_REQUIRE(smem <= 200 * 1024, "weights (%zu bytes) beyond the shared memory of the data-gradient kernel", smem);
+        if (smem > 48 * 1024)
+            ZNN_CUDA_OK(cudaFuncSetAttribute(conv2d_bwd_data_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+        const size_t total = (size_t)N * Ci * H * Wd;
+        size_t blocks = (total + 255) / 256;
+        const size_t cap = (size_t)sm_count() * 8;
+        if (blocks > cap) blocks = cap;
+        conv2d_bwd_data_kernel<<<(unsigned)blocks, 256, smem, stream()>>>(dY, W, dX, N, Ci, H, Wd, Co, KH, KW, pad, Ho, Wo);
+        ZNN_LAUNCH_OK("conv2d_bwd_data_kernel");
+    }
+    return ZNN_OK;
+}
+
+int znn_maxpool2d_fwd(const float* X, float* Y, int32_t* idx, int N, int C, int H, int W, int pool, int stride)
+{
+    ZNN_REQUIRE(pool > 0 && stride > 0, "bad pooling parameters");
+    const int Ho = H / stride, Wo = W / stride;
+    const size_t planes = (size_t)N * C;
+    if (planes == 0 || Ho == 0 || Wo == 0) return ZNN_OK;
+    if (!stream()) return fail(ZNN_ERR_CUDA, "no CUDA device state; call znn_init (no CPU fallback)");
+    const size_t total = planes * Ho * Wo;
+    size_t blocks = (total + 255) / 256;
+    const size_t cap = (size_t)sm_count() * 32;
+    if (blocks > cap) blocks = cap;
+    maxpool2d_fwd_kernel<<<(unsigned)blocks, 256, 0, stream()>>>(X, Y, idx, planes, H, W, Ho, Wo, pool, stride);
+    ZNN_LAUNCH_OK("maxpool2d_fwd_kernel");
+    return ZNN_OK;
+}
+
+int znn_maxpool2d_bwd(const float* X, const float* dY, float* dX, int N, int C, int H, int W, int pool, int stride)
+{
+    ZNN_REQUIRE(pool > 0 && stride > 0, "bad pooling parameters");
+    const int Ho = H / stride, Wo = W / stride;
+    const size_t planes = (size_t)N * C;
+    if (planes == 0 || Ho == 0 || Wo == 0 || !dX) return ZNN_OK;
+    if (!stream()) return fail(ZNN_ERR_CUDA, "no CUDA device state; call znn_init (no CPU fallback)");
+    const size_t total = planes * Ho * Wo;
+    size_t blocks = (total + 255) / 256;
+    const size_t cap = (size_t)sm_count() * 32;
+    if (blocks > cap) blocks = cap;
+    if (stride < pool)
+        maxpool2d_bwd_kernel<true><<<(unsigned)blocks, 256, 0, stream()>>>(X, dY, dX, planes, H, W, Ho, Wo, pool, stride);
+    else
+        maxpool2d_bwd_kernel<false><<<(unsigned)blocks, 256, 0, stream()>>>(X, dY, dX, planes, H, W, Ho, Wo, pool, stride);
+    ZNN_LAUNCH_OK("maxpool2d_bwd_kernel");
+    return ZNN_OK;
+}
+
+}  // extern "C"

@@ -1,0 +1,172 @@
+// znn_sgemm / znn_sgemm_batched_strided: the cblas_sgemm boundary of the
+// reference (src/cblas.zig:17-34) on device pointers.  Large problems go to the
+// tcgen05 3xTF32 kernel (gemm_tc.cu); small or launch-bound ones to the fp32 FMA
+// kernel below, which takes any transposes, leading dimensions and alignment.
+#include "common.cuh"
+
+namespace znn {
+
+int gemm_tc(int ta, int tb, int M, int N, int K, float alpha, const float* A, long long lda, long long stride_a,
+            const float* B, long long ldb, long long stride_b, float beta, float* C, long long ldc,
+            long long stride_c, int batch, int ctas);
+
+// C = alpha * op(A) * op(B) + beta * C with fp32 FMAs, k ascending.
+// 64x64 output tile, 16-deep k slices, 256 threads, 4x4 outputs per thread.
+__global__ void __launch_bounds__(256)
+sgemm_fma_kernel(int M, int N, int K, float alpha, const float* __restrict__ A, long long sa_i, long long sa_p,
+                 long long stride_a, const float* __restrict__ B, long long sb_p, long long sb_j, long long stride_b,
+                 float beta, float* __restrict__ C, long long ldc, long long stride_c)
+{
+    __shared__ float As[16][64 + 4];
+    __shared__ float Bs[16][64 + 4];
+    const int b = blockIdx.z;
+    A += (size_t)b * stride_a;
+    B += (size_t)b * stride_b;
+    C += (size_t)b * stride_c;
+    const int i0 = blockIdx.y * 64, j0 = blockIdx.x * 64;
+    const int tx = threadIdx.x & 15, ty = threadIdx.x >> 4;
+    float acc[4][4];
+#pragma unroll
+    for (int r = 0; r < 4; r++)
+#pragma unroll
+        for (int c = 0; c < 4; c++) acc[r][c] = 0.0f;
+
+    // loader mapping: pick the index that is contiguous in memory as the fast one
+    const bool a_p_fast = (sa_p == 1);
+    const bool b_j_fast = (sb_j == 1);
+    for (int p0 = 0; p0 < K; p0 += 16) {
+#pragma unroll
+        for (int t = 0; t < 4; t++) {
+            const int e = threadIdx.x + t * 256;  // 0..1023
+            int li, lp;
+            if (a_p_fast) { lp = e & 15; li = e >> 4; } else { li = e & 63; lp = e >> 6; }
+            const int gi = i0 + li, gp = p0 + lp;
+            As[lp][li] = (gi < M && gp < K) ? A[(size_t)gi * sa_i + (size_t)gp * sa_p] : 0.0f;
+            int lj, lq;
+            if (b_j_fast) { lj = e & 63; lq = e >> 6; } else { lq = e & 15; lj = e >> 4; }
+            const int gj = j0 + lj, gq = p0 + lq;
+            Bs[lq][lj] = (gj < N && gq < K) ? B[(size_t)gq * sb_p + (size_t)gj * sb_j] : 0.0f;
+        }
+        __syncthreads();
+#pragma unroll
+        for (int p = 0; p < 16; p++) {
+            float a[4], bb[4];
+#pragma unroll
+            for (int r = 0; r < 4; r++) a[r] = As[p][ty * 4 + r];
+#pragma unroll
+            for (int c = 0; c < 4; c++) bb[c] = Bs[p][tx * 4 + c];
+#pragma unroll
+            for (int r = 0; r < 4; r++)
+#pragma unroll
+                for (int c = 0; c < 4; c++) acc[r][c] = fmaf(a[r], bb[c], acc[r][c]);
+        }
+        __syncthreads();
+    }
+#pragma unroll
+    for (int r = 0; r < 4; r++) {
+        const int gi = i0 + ty * 4 + r;
+        if (gi >= M) continue;
+#pragma unroll
+        for (int c = 0; c < 4; c++) {
+            const int gj = j0 + tx * 4 + c;
+            if (gj >= N) continue;
+            float* dst = C + (size_t)gi * ldc + gj;
+            float o = alpha * acc[r][c];
+            if (beta != 0.0f) o += beta * (*dst);
+            *dst = o;
+        }
+    }
+}
+
+// beta pass for the degenerate cases (K == 0 or alpha == 0), cblas.zig:56-70.
+__global__ void scale_c_kernel(float* C, long long ldc, long long stride_c, int M, int N, float beta)
+{
+    float* c = C + (size_t)blockIdx.z * stride_c;
+    for (size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x; i < (size_t)M * N;
+         i += (size_t)gridDim.x * blockDim.x) {
+        const size_t r = i / N, col = i % N;
+        float* d = c + r * ldc + col;
+        *d = (beta == 0.0f) ? 0.0f : beta * (*d);
+    }
+}
+
+static thread_local int t_path = 0;       // requested
+static thread_local int t_last_path = 0;  // taken by the last call
+
+static int gemm_dispatch(int ta, int tb, int M, int N, int K, float alpha, const float* A, long long lda,
+                         long long stride_a, const float* B, long long ldb, long long stride_b, float beta, float* C,
+                         long long ldc, long long stride_c, int batch)
+{
+    ZNN_REQUIRE(ta == ZNN_NO_TRANS || ta == ZNN_TRANS, "trans_a must be 111 or 112");
+    ZNN_REQUIRE(tb == ZNN_NO_TRANS || tb == ZNN_TRANS, "trans_b must be 111 or 112");
+    ZNN_REQUIRE(M >= 0 && N >= 0 && K >= 0 && batch >= 0, "negative dimension");
+    if (M == 0 || N == 0 || batch == 0) return ZNN_OK;
+    ZNN_REQUIRE(C, "C is NULL");
+    ZNN_REQUIRE(ldc >= N, "ldc (%lld) < N (%d)", ldc, N);
+    if (!stream()) return fail(ZNN_ERR_CUDA, "no CUDA device state; call znn_init (this library has no CPU fallback)");
+    if (K == 0 || alpha == 0.0f) {
+        if (beta != 1.0f) {
+            const int blocks = ceil_div((long)M * N, 256) > 4096 ? 4096 : ceil_div((long)M * N, 256);
+            scale_c_kernel<<<dim3(blocks, 1, batch), 256, 0, stream()>>>(C, ldc, stride_c, M, N, beta);
+            ZNN_LAUNCH_OK("scale_c_kernel");
+        }
+        t_last_path = 1;
+        return ZNN_OK;
+    }
+    ZNN_REQUIRE(A && B, "A or B is NULL");
+    ZNN_REQUIRE(lda >= (ta == ZNN_NO_TRANS ? K : M), "lda too small");
+    ZNN_REQUIRE(ldb >= (tb == ZNN_NO_TRANS ? N : K), "ldb too small");
+
+    int path = t_path;
+    if (path == 0) {
+        // The tensor-core path costs a split pre-pass and two extra launches; below
+        // ~0.13 GFLOP per call the FMA kernel finishes sooner.
+        const double flops = 2.0 * M * N * (double)K * batch;
+        path = (flops >= 1.3e8 && M >= 64 && N >= 32 && K >= 32) ? 3 : 1;
+    }
+    t_last_path = path;
+    if (path == 2 || path == 3)
+        return gemm_tc(ta, tb, M, N, K, alpha, A, lda, stride_a, B, ldb, stride_b, beta, C, ldc, stride_c, batch,
+                       path == 2 ? 1 : 2);
+
+    const long long sa_i = (ta == ZNN_NO_TRANS) ? lda : 1, sa_p = (ta == ZNN_NO_TRANS) ? 1 : lda;
+    const long long sb_p = (tb == ZNN_NO_TRANS) ? ldb : 1, sb_j = (tb == ZNN_NO_TRANS) ? 1 : ldb;
+    dim3 grid(ceil_div(N, 64), ceil_div(M, 64), batch);
+    sgemm_fma_kernel<<<grid, 256, 0, stream()>>>(M, N, K, alpha, A, sa_i, sa_p, stride_a, B, sb_p, sb_j, stride_b,
+                                                 beta, C, ldc, stride_c);
+    ZNN_LAUNCH_OK("sgemm_fma_kernel");
+    return ZNN_OK;
+}
+
+}  // namespace znn
+
+using namespace znn;
+
+extern "C" {
+
+int znn_sgemm(int order, int trans_a, int trans_b, int M, int N, int K, float alpha, const float* A, int lda,
+              const float* B, int ldb, float beta, float* C, int ldc)
+{
+    ZNN_REQUIRE(order == ZNN_ROW_MAJOR, "only row-major (101) is supported, as in the reference");
+    return gemm_dispatch(trans_a, trans_b, M, N, K, alpha, A, lda, 0, B, ldb, 0, beta, C, ldc, 0, 1);
+}
+
+int znn_sgemm_batched_strided(int trans_a, int trans_b, int M, int N, int K, float alpha, const float* A, int lda,
+                              long long stride_a, const float* B, int ldb, long long stride_b, float beta, float* C,
+                              int ldc, long long stride_c, int batch)
+{
+    ZNN_REQUIRE(batch <= 65535, "batch %d exceeds 65535", batch);
+    return gemm_dispatch(trans_a, trans_b, M, N, K, alpha, A, lda, stride_a, B, ldb, stride_b, beta, C, ldc, stride_c,
+                         batch);
+}
+
+int znn_gemm_set_path(int path)
+{
+    ZNN_REQUIRE(path >= 0 && path <= 3, "path must be 0..3");
+    t_path = path;
+    return ZNN_OK;
+}
+
+int znn_gemm_last_path(void) { return t_last_path; }
+
+}  // extern "C"

@@ -1,0 +1,637 @@
+// fp32-accurate GEMM on the 5th-generation tensor cores (sm_100a).
+//
+//   C[M,N] = alpha * op(A) * op(B) + beta * C        (row-major, fp32)
+//
+// Two steps per call:
+//  1. split pre-pass (HBM-bound): op(A) and op(B) are rewritten into K-major
+//     planes  X_hi = rn_tf32(X),  X_lo = rn_tf32(X - X_hi), zero padded in K to
+//     a multiple of 32, so that the contraction below only ever sees K-major
+//     TF32-exact operands whatever the caller's transpose flags / strides.
+//  2. tcgen05 kernel: per k-block of 32, TMA brings A_hi, A_lo, B_hi, B_lo tiles
+//     (128-byte swizzle) into a shared-memory ring; one thread issues
+//     tcgen05.mma.kind::tf32 for lo*hi, hi*lo and hi*hi (3xTF32; lo*lo is below
+//     fp32 resolution) accumulating in fp32 in tensor memory; four epilogue
+//     warps read the accumulator with tcgen05.ld and apply alpha/beta.
+//     Variants: one CTA per 128xBN tile, or a CTA pair (cta_group::2) per
+//     256xBN tile in which each CTA loads its own half of A and B (plain TMA
+//     loads, no multicast).
+// Every mbarrier wait is bounded: on expiry the role sets a bit in the device
+// status word and leaves; later CTAs see the word and return at once.
+#include <cuda.h>
+
+#include "common.cuh"
+
+namespace znn {
+
+// ---------------------------------------------------------------------------
+// PTX wrappers
+// ---------------------------------------------------------------------------
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ uint64_t globaltimer_ns()
+{
+    uint64_t t;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+    return t;
+}
+
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count)
+{
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
+}
+
+__device__ __forceinline__ void mbar_arrive_expect_tx(uint32_t bar, uint32_t bytes)
+{
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+
+__device__ __forceinline__ uint32_t mbar_try_wait(uint32_t bar, uint32_t parity)
+{
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok)
+        : "r"(bar), "r"(parity)
+        : "memory");
+    return ok;
+}
+
+// Waits at most ~2 s of wall time; false on expiry.
+__device__ __forceinline__ bool mbar_wait_bounded(uint32_t bar, uint32_t parity)
+{
+    if (mbar_try_wait(bar, parity)) return true;
+    const uint64_t t0 = globaltimer_ns();
+    for (;;) {
+#pragma unroll 1
+        for (int i = 0; i < 128; i++)
+            if (mbar_try_wait(bar, parity)) return true;
+        if (globaltimer_ns() - t0 > 2000000000ull) return false;
+    }
+}
+
+__device__ __forceinline__ void tma_load_3d(uint32_t dst, const CUtensorMap* tm, uint32_t bar, int c0, int c1, int c2)
+{
+    asm volatile(
+        "cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5}], [%2];"
+        ::"r"(dst), "l"(tm), "r"(bar), "r"(c0), "r"(c1), "r"(c2)
+        : "memory");
+}
+
+// CTA-pair form: the mbarrier may live in the peer CTA (the pair's leader).
+__device__ __forceinline__ void tma_load_3d_pair(uint32_t dst, const CUtensorMap* tm, uint32_t bar, int c0, int c1, int c2)
+{
+    asm volatile(
+        "cp.async.bulk.tensor.3d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5}], [%2];"
+        ::"r"(dst), "l"(tm), "r"(bar), "r"(c0), "r"(c1), "r"(c2)
+        : "memory");
+}
+
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+
+template <int CTAS>
+__device__ __forceinline__ void tmem_alloc(uint32_t dst_smem, uint32_t ncols)
+{
+    if (CTAS == 1)
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(dst_smem), "r"(ncols) : "memory");
+    else
+        asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(dst_smem), "r"(ncols) : "memory");
+}
+
+template <int CTAS>
+__device__ __forceinline__ void tmem_relinquish()
+{
+    if (CTAS == 1)
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    else
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+}
+
+template <int CTAS>
+__device__ __forceinline__ void tmem_dealloc(uint32_t taddr, uint32_t ncols)
+{
+    if (CTAS == 1)
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(ncols) : "memory");
+    else
+        asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(ncols) : "memory");
+}
+
+template <int CTAS>
+__device__ __forceinline__ void umma_tf32(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b, uint32_t idesc, uint32_t accumulate)
+{
+    if (CTAS == 1)
+        asm volatile(
+            "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+            "tcgen05.mma.cta_group::1.kind::tf32 [%0], %1, %2, %3, p;\n\t}"
+            ::"r"(tmem_d), "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate)
+            : "memory");
+    else
+        asm volatile(
+            "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+            "tcgen05.mma.cta_group::2.kind::tf32 [%0], %1, %2, %3, p;\n\t}"
+            ::"r"(tmem_d), "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate)
+            : "memory");
+}
+
+// Arrive on an mbarrier once all previously issued MMAs of this thread are done.
+__device__ __forceinline__ void umma_commit_1cta(uint32_t bar)
+{
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+
+// Pair form: arrives on the barrier at the same offset in both CTAs of the pair.
+__device__ __forceinline__ void umma_commit_pair(uint32_t bar)
+{
+    const uint16_t mask = 3;
+    asm volatile(
+        "tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;"
+        ::"r"(bar), "h"(mask)
+        : "memory");
+}
+
+__device__ __forceinline__ void tmem_ld_32x32(uint32_t taddr, float (&v)[32])
+{
+    uint32_t r[32];
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+        "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+          "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]),
+          "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]),
+          "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+        : "r"(taddr)
+        : "memory");
+    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+    for (int i = 0; i < 32; i++) v[i] = __uint_as_float(r[i]);
+}
+
+__device__ __forceinline__ uint32_t cluster_ctarank()
+{
+    uint32_t r;
+    asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+    return r;
+}
+
+__device__ __forceinline__ uint32_t mapa_shared(uint32_t addr, uint32_t rank)
+{
+    uint32_t out;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(out) : "r"(addr), "r"(rank));
+    return out;
+}
+
+__device__ __forceinline__ void cluster_sync_all()
+{
+    asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+    asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+
+// Shared-memory matrix descriptor of a K-major tile whose rows are 128 bytes
+// (32 fp32) with the 128-byte swizzle: 8-row groups are 1024 bytes apart.
+__device__ __forceinline__ uint64_t make_kmajor_sw128_desc(uint32_t smem_addr)
+{
+    uint64_t d = 0;
+    d |= (uint64_t)((smem_addr & 0x3FFFF) >> 4);  // start address, 16-byte units
+    d |= (uint64_t)1 << 16;                       // leading byte offset (unused with swizzle)
+    d |= (uint64_t)(1024 >> 4) << 32;             // stride byte offset between 8-row groups
+    d |= (uint64_t)1 << 46;                       // descriptor version of sm_100
+    d |= (uint64_t)2 << 61;                       // SWIZZLE_128B
+    return d;
+}
+
+// kind::tf32 instruction descriptor: D fp32, A/B tf32, both K-major.
+__host__ __device__ constexpr uint32_t make_tf32_idesc(int mma_m, int mma_n)
+{
+    return (1u << 4) | (2u << 7) | (2u << 10) | ((uint32_t)(mma_n >> 3) << 17) | ((uint32_t)(mma_m >> 4) << 24);
+}
+
+// ---------------------------------------------------------------------------
+// the GEMM kernel
+// ---------------------------------------------------------------------------
+struct GemmTcParams {
+    int M, N;            // output extent
+    int k_blocks;        // padded K / 32
+    int tiles_m, tiles_n;
+    float alpha, beta;
+    float* C;
+    long long ldc, stride_c;
+    int* status;
+};
+
+constexpr int kBK = 32;          // fp32 elements per k-block = one 128-byte swizzle row
+constexpr int kTileM = 128;      // rows of A per CTA
+constexpr int kThreads = 192;    // warp 0 TMA, warp 1 MMA + TMEM, warps 2..5 epilogue
+
+template <int BN, int CTAS>
+struct TcCfg {
+    static constexpr int kBRows = BN / CTAS;                   // rows of B this CTA loads
+    static constexpr int kABytes = kTileM * kBK * 4;           // one A plane tile
+    static constexpr int kBBytes = kBRows * kBK * 4;           // one B plane tile
+    static constexpr int kStageBytes = 2 * kABytes + 2 * kBBytes;
+    static constexpr int kStages = (200 * 1024) / kStageBytes > 6 ? 6 : (200 * 1024) / kStageBytes;
+    static constexpr int kSmemBytes = kStages * kStageBytes + 1024 /*align*/ + 256 /*barriers*/;
+    static constexpr int kTmemCols = BN < 32 ? 32 : BN;
+};
+
+template <int BN, int CTAS>
+__global__ void __launch_bounds__(kThreads, 1)
+gemm3x_tf32_kernel(const __grid_constant__ CUtensorMap tm_a_hi, const __grid_constant__ CUtensorMap tm_a_lo,
+                   const __grid_constant__ CUtensorMap tm_b_hi, const __grid_constant__ CUtensorMap tm_b_lo,
+                   const GemmTcParams p)
+{
+    using Cfg = TcCfg<BN, CTAS>;
+    extern __shared__ uint8_t smem_raw[];
+    // 1024-byte alignment is required by the 128-byte swizzle atoms.
+    const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+    uint8_t* smem_gen = smem_raw + (smem_base - smem_u32(smem_raw));
+    const uint32_t bar_base = smem_base + Cfg::kStages * Cfg::kStageBytes;
+    // barrier block: full[kStages], empty[kStages], accum, then the TMEM address
+    auto full_bar = [&](int s) { return bar_base + 8u * s; };
+    auto empty_bar = [&](int s) { return bar_base + 8u * (Cfg::kStages + s); };
+    const uint32_t accum_bar = bar_base + 8u * (2 * Cfg::kStages);
+    volatile uint32_t* tmem_slot =
+        reinterpret_cast<volatile uint32_t*>(smem_gen + Cfg::kStages * Cfg::kStageBytes + 8 * (2 * Cfg::kStages + 1));
+    const uint32_t tmem_slot_addr = bar_base + 8u * (2 * Cfg::kStages + 1);
+    volatile uint32_t* abort_slot = tmem_slot + 1;
+    const uint32_t abort_slot_addr = tmem_slot_addr + 4;
+
+    const int warp = threadIdx.x >> 5;
+    const int lane = threadIdx.x & 31;
+    const uint32_t cta_rank = (CTAS == 2) ? cluster_ctarank() : 0u;
+    const bool leader = (cta_rank == 0);
+
+    // tile coordinates: groups of 8 tile-rows are walked column by column so
+    // that CTAs running together share A row panels and B column panels in L2
+    const int unit = (CTAS == 2) ? (blockIdx.x >> 1) : blockIdx.x;
+    int tile_m, tile_n;
+    {
+        constexpr int G = 8;
+        const int per_group = G * p.tiles_n;
+        const int g = unit / per_group;
+        const int first_m = g * G;
+        const int rows_in_group = min(G, p.tiles_m - first_m);
+        const int r = unit - g * per_group;
+        tile_m = first_m + r % rows_in_group;
+        tile_n = r / rows_in_group;
+    }
+    const int batch = blockIdx.z;
+    const int row0 = (tile_m * CTAS + (int)cta_rank) * kTileM;  // first C / A row of this CTA
+    const int col0 = tile_n * BN;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < Cfg::kStages; s++) {
+            mbar_init(full_bar(s), 1);
+            mbar_init(empty_bar(s), 1);
+        }
+        mbar_init(accum_bar, 1);
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        // A failure recorded by an earlier CTA or kernel makes this one do nothing.
+        // One thread decides for the whole CTA (pair), so the decision is uniform.
+        if (leader) {
+            const uint32_t prior = (uint32_t)(*reinterpret_cast<volatile int*>(p.status));
+            *abort_slot = prior;
+            if (CTAS == 2)
+                asm volatile("st.shared::cluster.u32 [%0], %1;" ::"r"(mapa_shared(abort_slot_addr, 1)), "r"(prior) : "memory");
+        }
+    }
+    if (warp == 1) {
+        tmem_alloc<CTAS>(tmem_slot_addr, Cfg::kTmemCols);
+        tmem_relinquish<CTAS>();
+    }
+    tc_fence_before();
+    __syncthreads();
+    if (CTAS == 2) cluster_sync_all();  // the peer's barriers must exist before anything signals them
+    tc_fence_after();
+    const uint32_t tmem_base = *tmem_slot;
+    const bool aborted = (*abort_slot != 0);
+
+    bool ok = true;
+    if (aborted) {
+        // nothing to do: fall through to the teardown
+    } else if (warp == 0) {
+        // ---------------- TMA producer ----------------
+        if (lane == 0) {
+            const uint32_t full_leader0 = (CTAS == 2) ? mapa_shared(full_bar(0), 0) : full_bar(0);
+            for (int kb = 0; kb < p.k_blocks; kb++) {
+                const int s = kb % Cfg::kStages;
+                const uint32_t ph = (kb / Cfg::kStages) & 1;
+                if (!mbar_wait_bounded(empty_bar(s), ph ^ 1)) { ok = false; break; }
+                const uint32_t st = smem_base + s * Cfg::kStageBytes;
+                const int k0 = kb * kBK;
+                if (CTAS == 1) {
+                    mbar_arrive_expect_tx(full_bar(s), Cfg::kStageBytes);
+                    tma_load_3d(st, &tm_a_hi, full_bar(s), k0, row0, batch);
+                    tma_load_3d(st + Cfg::kABytes, &tm_a_lo, full_bar(s), k0, row0, batch);
+                    tma_load_3d(st + 2 * Cfg::kABytes, &tm_b_hi, full_bar(s), k0, col0, batch);
+                    tma_load_3d(st + 2 * Cfg::kABytes + Cfg::kBBytes, &tm_b_lo, full_bar(s), k0, col0, batch);
+                } else {
+                    // the leader's barrier collects the bytes of both CTAs
+                    if (leader) mbar_arrive_expect_tx(full_bar(s), 2 * Cfg::kStageBytes);
+                    const uint32_t fb = full_leader0 + 8u * s;
+                    const int brow0 = col0 + (int)cta_rank * Cfg::kBRows;
+                    tma_load_3d_pair(st, &tm_a_hi, fb, k0, row0, batch);
+                    tma_load_3d_pair(st + Cfg::kABytes, &tm_a_lo, fb, k0, row0, batch);
+                    tma_load_3d_pair(st + 2 * Cfg::kABytes, &tm_b_hi, fb, k0, brow0, batch);
+                    tma_load_3d_pair(st + 2 * Cfg::kABytes + Cfg::kBBytes, &tm_b_lo, fb, k0, brow0, batch);
+                }
+            }
+            if (!ok) atomicOr(p.status, ZNN_DEV_TMA_WAIT_EXPIRED);
+        }
+    } else if (warp == 1) {
+        // ---------------- MMA issuer (leader CTA only in pair mode) ----------------
+        if (lane == 0 && leader) {
+            constexpr uint32_t idesc = make_tf32_idesc(kTileM * CTAS, BN);
+            for (int kb = 0; kb < p.k_blocks; kb++) {
+                const int s = kb % Cfg::kStages;
+                const uint32_t ph = (kb / Cfg::kStages) & 1;
+                if (!mbar_wait_bounded(full_bar(s), ph)) { ok = false; break; }
+                tc_fence_after();
+                const uint32_t st = smem_base + s * Cfg::kStageBytes;
+                const uint64_t a_hi = make_kmajor_sw128_desc(st);
+                const uint64_t a_lo = make_kmajor_sw128_desc(st + Cfg::kABytes);
+                const uint64_t b_hi = make_kmajor_sw128_desc(st + 2 * Cfg::kABytes);
+                const uint64_t b_lo = make_kmajor_sw128_desc(st + 2 * Cfg::kABytes + Cfg::kBBytes);
+                // small terms first, then the leading term
+#pragma unroll
+                for (int k = 0; k < kBK / 8; k++)  // 8 tf32 = 32 bytes = 2 x 16-byte units
+                    umma_tf32<CTAS>(tmem_base, a_lo + 2 * k, b_hi + 2 * k, idesc, (kb | k) != 0);
+#pragma unroll
+                for (int k = 0; k < kBK / 8; k++) umma_tf32<CTAS>(tmem_base, a_hi + 2 * k, b_lo + 2 * k, idesc, 1);
+#pragma unroll
+                for (int k = 0; k < kBK / 8; k++) umma_tf32<CTAS>(tmem_base, a_hi + 2 * k, b_hi + 2 * k, idesc, 1);
+                if (CTAS == 1) umma_commit_1cta(empty_bar(s)); else umma_commit_pair(empty_bar(s));
+            }
+            if (ok) {
+                if (CTAS == 1) umma_commit_1cta(accum_bar); else umma_commit_pair(accum_bar);
+            } else {
+                atomicOr(p.status, ZNN_DEV_MMA_WAIT_EXPIRED);
+            }
+        }
+    } else {
+        // ---------------- epilogue: TMEM -> registers -> C ----------------
+        const int q = warp & 3;  // the TMEM lane quarter this warp may read
+        bool got = true;
+        if (lane == 0) got = mbar_wait_bounded(accum_bar, 0);
+        got = __shfl_sync(0xffffffffu, (int)got, 0) != 0;
+        if (!got) {
+            if (lane == 0) atomicOr(p.status, ZNN_DEV_EPI_WAIT_EXPIRED);
+        } else {
+            tc_fence_after();
+            const int row = row0 + q * 32 + lane;
+            float* crow = p.C + (size_t)batch * p.stride_c + (size_t)row * p.ldc + col0;
+            const bool vec_ok = ((p.ldc & 3) == 0) && ((reinterpret_cast<uintptr_t>(p.C) & 15) == 0) &&
+                                ((p.stride_c & 3) == 0);
+            const float alpha = p.alpha, beta = p.beta;
+#pragma unroll 1
+            for (int c = 0; c < BN; c += 32) {
+                float v[32];
+                tmem_ld_32x32(tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)c, v);
+                if (row >= p.M) continue;
+                const int ncols = min(32, p.N - (col0 + c));
+                if (ncols <= 0) continue;
+                if (vec_ok && ncols == 32) {
+                    float4* dst = reinterpret_cast<float4*>(crow + c);
+#pragma unroll
+                    for (int j = 0; j < 8; j++) {
+                        float4 o;
+                        o.x = alpha * v[4 * j + 0]; o.y = alpha * v[4 * j + 1];
+                        o.z = alpha * v[4 * j + 2]; o.w = alpha * v[4 * j + 3];
+                        if (beta != 0.0f) {
+                            const float4 old = dst[j];
+                            o.x += beta * old.x; o.y += beta * old.y; o.z += beta * old.z; o.w += beta * old.w;
+                        }
+                        dst[j] = o;
+                    }
+                } else {
+#pragma unroll
+                    for (int j = 0; j < 32; j++) {
+                        if (j < ncols) {
+                            float o = alpha * v[j];
+                            if (beta != 0.0f) o += beta * crow[c + j];
+                            crow[c + j] = o;
+                        }
+                    }
+                }
+            }
+        }
+    }
+
+    tc_fence_before();
+    __syncthreads();
+    if (CTAS == 2) cluster_sync_all();  // the peer may still signal this CTA's barriers / read its tiles
+    if (warp == 1) {
+        tc_fence_after();
+        tmem_dealloc<CTAS>(tmem_base, Cfg::kTmemCols);
+    }
+}
+
+// ---------------------------------------------------------------------------
+// split pre-pass
+// ---------------------------------------------------------------------------
+__device__ __forceinline__ void split_tf32(float x, float& hi, float& lo)
+{
+    uint32_t h;
+    asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(h) : "f"(x));
+    h &= 0xFFFFE000u;
+    float hf = __uint_as_float(h);
+    if (!isfinite(hf)) hf = __uint_as_float(__float_as_uint(x) & 0xFFFFE000u);  // rounding overflowed (or x is inf/nan)
+    float r = isfinite(x) ? (x - hf) : 0.0f;
+    uint32_t l;
+    asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(l) : "f"(r));
+    l &= 0xFFFFE000u;
+    hi = hf;
+    lo = __uint_as_float(l);
+}
+
+// X is [rows, cols] with leading dimension ld (no transpose needed):
+// plane[b][r][k] = split(X[b*stride + r*ld + k]), zero for k >= cols.
+__global__ void split_rows_kernel(const float* __restrict__ X, long long ld, long long stride_x, int rows, int cols,
+                                  int kpad, float* __restrict__ hi, float* __restrict__ lo)
+{
+    const int b = blockIdx.z;
+    const float* xb = X + (size_t)b * stride_x;
+    const size_t plane_off = (size_t)b * rows * kpad;
+    const int kq = kpad >> 2;  // float4 groups per row
+    const bool vec_in = ((ld & 3) == 0) && ((reinterpret_cast<uintptr_t>(xb) & 15) == 0);
+    for (size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x; i < (size_t)rows * kq;
+         i += (size_t)gridDim.x * blockDim.x) {
+        const int r = (int)(i / kq);
+        const int k = (int)(i % kq) * 4;
+        float x[4];
+        if (vec_in && k + 3 < cols) {
+            const float4 t = *reinterpret_cast<const float4*>(xb + (size_t)r * ld + k);
+            x[0] = t.x; x[1] = t.y; x[2] = t.z; x[3] = t.w;
+        } else {
+#pragma unroll
+            for (int j = 0; j < 4; j++) x[j] = (k + j < cols) ? xb[(size_t)r * ld + k + j] : 0.0f;
+        }
+        float4 h, l;
+        split_tf32(x[0], h.x, l.x); split_tf32(x[1], h.y, l.y);
+        split_tf32(x[2], h.z, l.z); split_tf32(x[3], h.w, l.w);
+        *reinterpret_cast<float4*>(hi + plane_off + (size_t)r * kpad + k) = h;
+        *reinterpret_cast<float4*>(lo + plane_off + (size_t)r * kpad + k) = l;
+    }
+}
+
+// X is stored [cols(k), rows] with leading dimension ld: plane[b][r][k] = split(X[b*stride + k*ld + r]).
+// 32x32 tiles through shared memory so that both the read and the write are coalesced.
+__global__ void split_transpose_kernel(const float* __restrict__ X, long long ld, long long stride_x, int rows,
+                                       int cols, int kpad, float* __restrict__ hi, float* __restrict__ lo)
+{
+    __shared__ float tile[32][33];
+    const int b = blockIdx.z;
+    const float* xb = X + (size_t)b * stride_x;
+    const size_t plane_off = (size_t)b * rows * kpad;
+    const int r0 = blockIdx.x * 32, k0 = blockIdx.y * 32;
+    // threads: (32, 8)
+    for (int j = threadIdx.y; j < 32; j += 8) {
+        const int k = k0 + j, r = r0 + threadIdx.x;
+        tile[j][threadIdx.x] = (k < cols && r < rows) ? xb[(size_t)k * ld + r] : 0.0f;
+    }
+    __syncthreads();
+    for (int j = threadIdx.y; j < 32; j += 8) {
+        const int r = r0 + j, k = k0 + threadIdx.x;
+        if (r < rows && k < kpad) {
+            float h, l;
+            split_tf32(tile[threadIdx.x][j], h, l);
+            hi[plane_off + (size_t)r * kpad + k] = h;
+            lo[plane_off + (size_t)r * kpad + k] = l;
+        }
+    }
+}
+
+// ---------------------------------------------------------------------------
+// host side
+// ---------------------------------------------------------------------------
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static EncodeTiledFn encode_fn()
+{
+    static EncodeTiledFn fn = nullptr;
+    if (!fn) {
+        void* p = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
+            q == cudaDriverEntryPointSuccess)
+            fn = (EncodeTiledFn)p;
+    }
+    return fn;
+}
+
+// plane: [batch][rows][kpad] fp32; box = 32 (k) x box_rows x 1
+static int make_plane_map(CUtensorMap* tm, float* plane, int rows, int kpad, int batch, int box_rows)
+{
+    EncodeTiledFn enc = encode_fn();
+    if (!enc) return fail(ZNN_ERR_CUDA, "cuTensorMapEncodeTiled entry point not available");
+    cuuint64_t dims[3] = {(cuuint64_t)kpad, (cuuint64_t)rows, (cuuint64_t)batch};
+    cuuint64_t strides[2] = {(cuuint64_t)kpad * 4, (cuuint64_t)kpad * 4 * (cuuint64_t)rows};
+    cuuint32_t box[3] = {(cuuint32_t)kBK, (cuuint32_t)box_rows, 1};
+    cuuint32_t estr[3] = {1, 1, 1};
+    CUresult r = enc(tm, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 3, plane, dims, strides, box, estr,
+                     CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                     CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) return fail(ZNN_ERR_CUDA, "cuTensorMapEncodeTiled failed with %d", (int)r);
+    return ZNN_OK;
+}
+
+template <int BN, int CTAS>
+static int launch_tc(const CUtensorMap* maps, const GemmTcParams& p, int batch)
+{
+    using Cfg = TcCfg<BN, CTAS>;
+    static bool attr_set = false;
+    auto kern = gemm3x_tf32_kernel<BN, CTAS>;
+    if (!attr_set) {
+        ZNN_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmemBytes));
+        attr_set = true;
+    }
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3((unsigned)(p.tiles_m * p.tiles_n * CTAS), 1, (unsigned)batch);
+    cfg.blockDim = dim3(kThreads, 1, 1);
+    cfg.dynamicSmemBytes = Cfg::kSmemBytes;
+    cfg.stream = stream();
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = CTAS;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    ZNN_CUDA_OK(cudaLaunchKernelEx(&cfg, kern, maps[0], maps[1], maps[2], maps[3], p));
+    return ZNN_OK;
+}
+
+// op(A) is M x K, op(B) is K x N.  ctas = 1 or 2.
+int gemm_tc(int ta, int tb, int M, int N, int K, float alpha, const float* A, long long lda, long long stride_a,
+            const float* B, long long ldb, long long stride_b, float beta, float* C, long long ldc,
+            long long stride_c, int batch, int ctas)
+{
+    int* status = device_status_word();
+    if (!status) return fail(ZNN_ERR_CUDA, "no device state (call znn_init first)");
+    const int kpad = ((K + kBK - 1) / kBK) * kBK;
+    const size_t a_plane = (size_t)batch * M * kpad, b_plane = (size_t)batch * N * kpad;
+    const size_t need = (2 * a_plane + 2 * b_plane) * sizeof(float);
+    float* ws = (float*)workspace(need);
+    if (!ws) return fail(ZNN_ERR_NOMEM, "GEMM scratch of %zu bytes could not be allocated", need);
+    float* a_hi = ws;
+    float* a_lo = a_hi + a_plane;
+    float* b_hi = a_lo + a_plane;
+    float* b_lo = b_hi + b_plane;
+    cudaStream_t st = stream();
+
+    // ---- split pre-pass: both operands become K-major planes ----
+    auto split = [&](const float* X, long long ld, long long stride_x, int rows, bool k_contiguous, float* hi,
+                     float* lo) -> int {
+        if (k_contiguous) {
+            const size_t work = (size_t)rows * (kpad / 4);
+            int blocks = (int)((work + 255) / 256);
+            const int cap = sm_count() * 16;
+            if (blocks > cap) blocks = cap;
+            if (blocks < 1) blocks = 1;
+            split_rows_kernel<<<dim3(blocks, 1, batch), 256, 0, st>>>(X, ld, stride_x, rows, K, kpad, hi, lo);
+        } else {
+            dim3 grid((rows + 31) / 32, kpad / 32, batch);
+            split_transpose_kernel<<<grid, dim3(32, 8), 0, st>>>(X, ld, stride_x, rows, K, kpad, hi, lo);
+        }
+        ZNN_LAUNCH_OK("split pre-pass");
+        return ZNN_OK;
+    };
+    // op(A)[i,p]: NoTrans -> A[i*lda+p] (k contiguous); Trans -> A[p*lda+i]
+    int rc = split(A, lda, stride_a, M, ta == ZNN_NO_TRANS, a_hi, a_lo);
+    if (rc) return rc;
+    // op(B)[p,j] as plane[j][p]: Trans -> B[j*ldb+p] (k contiguous); NoTrans -> B[p*ldb+j]
+    rc = split(B, ldb, stride_b, N, tb == ZNN_TRANS, b_hi, b_lo);
+    if (rc) return rc;
+
+    // ---- tile shape ----
+    int bn = 256;
+    if (N <= 64) bn = 64;
+    else if (N <= 128) bn = 128;
+    const int tile_rows = kTileM * ctas;
+    GemmTcParams p;
+    p.M = M; p.N = N; p.k_blocks = kpad / kBK;
+    p.tiles_m = (M + tile_rows - 1) / tile_rows;
+    p.tiles_n = (N + bn - 1) / bn;
+    p.alpha = alpha; p.beta = beta; p.C = C; p.ldc = ldc; p.stride_c = stride_c; p.status = status;
+
+    CUtensorMap maps[4];
+    if ((rc = make_plane_map(&maps[0], a_hi, M, kpad, batch, kTileM))) return rc;
+    if ((rc = make_plane_map(&maps[1], a_lo, M, kpad, batch, kTileM))) return rc;
+    if ((rc = make_plane_map(&maps[2], b_hi, N, kpad, batch, bn / ctas))) return rc;
+    if ((rc = make_plane_map(&maps[3], b_lo, N, kpad, batch, bn / ctas))) return rc;
+
+    if (ctas == 1) {
+        if (bn == 256) return launch_tc<256, 1>(maps, p, batch);
+        if (bn == 128) return launch_tc<128, 1>(maps, p, batch);
+        return launch_tc<64, 1>(maps, p, batch);
+    }
+    if (bn == 256) return launch_tc<256, 2>(maps, p, batch);
+    if (bn == 128) return launch_tc<128, 2>(maps, p, batch);
+    return launch_tc<64, 2>(maps, p, batch);
+}
+
+}  // namespace znn

@@ -1,0 +1,1017 @@
+// Row-wise and elementwise operators of the znn hot path (HBM-bound kernels).
+// Compiled with -fmad=false: the reference rounds every product before the add
+// (Zig does not contract), and these kernels are bandwidth-bound, so keeping the
+// same rounding points costs nothing and keeps results close to bit-identical.
+#include <math_constants.h>
+
+#include "common.cuh"
+
+namespace znn {
+
+constexpr int kEwThreads = 256;
+
+static inline int ew_blocks(size_t n, int per_thread = 4)
+{
+    size_t b = (n + (size_t)kEwThreads * per_thread - 1) / ((size_t)kEwThreads * per_thread);
+    const size_t cap = (size_t)sm_count() * 32;
+    if (b > cap) b = cap;
+    if (b < 1) b = 1;
+    return (int)b;
+}
+
+__device__ __forceinline__ float warp_sum(float v)
+{
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+    return v;
+}
+
+__device__ __forceinline__ float warp_max(float v)
+{
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+    return v;
+}
+
+// block-wide reductions for up to 1024 threads; result valid in every thread
+__device__ __forceinline__ float block_sum(float v, float* sh)
+{
+    const int lane = threadIdx.x & 31, w = threadIdx.x >> 5, nw = (blockDim.x + 31) >> 5;
+    v = warp_sum(v);
+    __syncthreads();
+    if (lane == 0) sh[w] = v;
+    __syncthreads();
+    float t = (lane < nw) ? sh[lane] : 0.0f;
+    return warp_sum(t);
+}
+
+__device__ __forceinline__ float block_max(float v, float* sh)
+{
+    const int lane = threadIdx.x & 31, w = threadIdx.x >> 5, nw = (blockDim.x + 31) >> 5;
+    v = warp_max(v);
+    __syncthreads();
+    if (lane == 0) sh[w] = v;
+    __syncthreads();
+    float t = (lane < nw) ? sh[lane] : -CUDART_INF_F;
+    return warp_max(t);
+}
+
+// ---------------------------------------------------------------------------
+// elementwise: 128-bit accesses when both pointers are 16-byte aligned
+// ---------------------------------------------------------------------------
+template <class F>
+__global__ void ew1_kernel(const float* __restrict__ a, float* __restrict__ out, size_t n, F f)
+{
+    const size_t tid = blockIdx.x * (size_t)blockDim.x + threadIdx.x, nth = (size_t)gridDim.x * blockDim.x;
+    const bool vec = (((uintptr_t)a | (uintptr_t)out) & 15) == 0;
+    const size_t n4 = vec ? n / 4 : 0;
+    for (size_t i = tid; i < n4; i += nth) {
+        const float4 x = reinterpret_cast<const float4*>(a)[i];
+        float4 o = reinterpret_cast<float4*>(out)[i];
+        o.x = f(x.x, o.x); o.y = f(x.y, o.y); o.z = f(x.z, o.z); o.w = f(x.w, o.w);
+        reinterpret_cast<float4*>(out)[i] = o;
+    }
+    for (size_t i = n4 * 4 + tid; i < n; i += nth) out[i] = f(a[i], out[i]);
+}
+
+template <class F>
+__global__ void ew2_kernel(const float* __restrict__ a, const float* __restrict__ b, float* __restrict__ out, size_t n, F f)
+{
+    const size_t tid = blockIdx.x * (size_t)blockDim.x + threadIdx.x, nth = (size_t)gridDim.x * blockDim.x;
+    const bool vec = (((uintptr_t)a | (uintptr_t)b | (uintptr_t)out) & 15) == 0;
+    const size_t n4 = vec ? n / 4 : 0;
+    for (size_t i = tid; i < n4; i += nth) {
+        const float4 x = reinterpret_cast<const float4*>(a)[i];
+        const float4 y = reinterpret_cast<const float4*>(b)[i];
+        float4 o = reinterpret_cast<float4*>(out)[i];
+        o.x = f(x.x, y.x, o.x); o.y = f(x.y, y.y, o.y); o.z = f(x.z, y.z, o.z); o.w = f(x.w, y.w, o.w);
+        reinterpret_cast<float4*>(out)[i] = o;
+    }
+    for (size_t i = n4 * 4 + tid; i < n; i += nth) out[i] = f(a[i], b[i], out[i]);
+}
+
+// write-only variants (the old value of out is not read)
+template <class F>
+__global__ void ew1w_kernel(const float* __restrict__ a, float* __restrict__ out, size_t n, F f)
+{
+    const size_t tid = blockIdx.x * (size_t)blockDim.x + threadIdx.x, nth = (size_t)gridDim.x * blockDim.x;
+    const bool vec = (((uintptr_t)a | (uintptr_t)out) & 15) == 0;
+    const size_t n4 = vec ? n / 4 : 0;
+    for (size_t i = tid; i < n4; i += nth) {
+        const float4 x = reinterpret_cast<const float4*>(a)[i];
+        float4 o;
+        o.x = f(x.x); o.y = f(x.y); o.z = f(x.z); o.w = f(x.w);
+        reinterpret_cast<float4*>(out)[i] = o;
+    }
+    for (size_t i = n4 * 4 + tid; i < n; i += nth) out[i] = f(a[i]);
+}
+
+template <class F>
+__global__ void ew2w_kernel(const float* __restrict__ a, const float* __restrict__ b, float* __restrict__ out, size_t n, F f)
+{
+    const size_t tid = blockIdx.x * (size_t)blockDim.x + threadIdx.x, nth = (size_t)gridDim.x * blockDim.x;
+    const bool vec = (((uintptr_t)a | (uintptr_t)b | (uintptr_t)out) & 15) == 0;
+    const size_t n4 = vec ? n / 4 : 0;
+    for (size_t i = tid; i < n4; i += nth) {
+        const float4 x = reinterpret_cast<const float4*>(a)[i];
+        const float4 y = reinterpret_cast<const float4*>(b)[i];
+        float4 o;
+        o.x = f(x.x, y.x); o.y = f(x.y, y.y); o.z = f(x.z, y.z); o.w = f(x.w, y.w);
+        reinterpret_cast<float4*>(out)[i] = o;
+    }
+    for (size_t i = n4 * 4 + tid; i < n; i += nth) out[i] = f(a[i], b[i]);
+}
+
+struct ReluF { __device__ float operator()(float x) const { return x > 0.0f ? x : 0.0f; } };
+struct GeluF {
+    __device__ float operator()(float x) const
+    {
+        const float sqrt_2 = 1.41421356237309504880f;
+        return 0.5f * x * (1.0f + erff(x / sqrt_2));
+    }
+};
+struct ReluBwdF { __device__ float operator()(float a, float dc, float da) const { return da + (a > 0.0f ? dc : 0.0f); } };
+struct GeluBwdF {
+    __device__ float operator()(float x, float dc, float da) const
+    {
+        const float sqrt_2 = 1.41421356237309504880f;
+        const float inv_sqrt_2pi = 0.3989422804014327f;
+        const float cdf = 0.5f * (1.0f + erff(x / sqrt_2));
+        const float pdf = inv_sqrt_2pi * expf(-0.5f * x * x);
+        return da + dc * (cdf + x * pdf);
+    }
+};
+struct AddF { __device__ float operator()(float a, float b) const { return a + b; } };
+struct AccF { __device__ float operator()(float s, float d) const { return d + s; } };
+struct MulF { float v; __device__ float operator()(float a) const { return a * v; } };
+struct MulAccF { float v; __device__ float operator()(float dc, float da) const { return da + dc * v; } };
+
+__global__ void fill_kernel(float* dst, float v, size_t n)
+{
+    for (size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x) dst[i] = v;
+}
+
+// ---------------------------------------------------------------------------
+// AddBias
+// ---------------------------------------------------------------------------
+__global__ void add_bias_fwd_kernel(const float* __restrict__ A, const float* __restrict__ bias, float* __restrict__ C,
+                                    size_t total, int N)
+{
+    const size_t tid = blockIdx.x * (size_t)blockDim.x + threadIdx.x, nth = (size_t)gridDim.x * blockDim.x;
+    const bool vec = ((N & 3) == 0) && ((((uintptr_t)A | (uintptr_t)C | (uintptr_t)bias) & 15) == 0);
+    if (vec) {
+        const size_t t4 = total / 4;
+        const int n4 = N / 4;
+        for (size_t i = tid; i < t4; i += nth) {
+            const float4 a = reinterpret_cast<const float4*>(A)[i];
+            const float4 b = reinterpret_cast<const float4*>(bias)[i % n4];
+            float4 o;
+            o.x = a.x + b.x; o.y = a.y + b.y; o.z = a.z + b.z; o.w = a.w + b.w;
+            reinterpret_cast<float4*>(C)[i] = o;
+        }
+    } else {
+        for (size_t i = tid; i < total; i += nth) C[i] = A[i] + bias[i % N];
+    }
+}
+
+// Column sums in two deterministic stages.  Stage 1: block (32 columns x 8 row
+// lanes) walks a chunk of rows; the 8 row lanes are summed in fixed order and the
+// chunk's partial goes to scratch[chunk][n].  Stage 2 adds the chunk partials in
+// order into out[n].  `PassThrough` also does dA += dC on the way (AddBias backward).
+template <bool PassThrough>
+__global__ void colsum_stage1_kernel(const float* __restrict__ dC, float* __restrict__ dA, float* __restrict__ partial,
+                                     int M, int N, int rows_per_chunk)
+{
+    __shared__ float sh[8][33];
+    const int n = blockIdx.x * 32 + threadIdx.x;
+    const int m0 = blockIdx.y * rows_per_chunk;
+    const int m1 = min(M, m0 + rows_per_chunk);
+    float s = 0.0f;
+    if (n < N) {
+        for (int m = m0 + threadIdx.y; m < m1; m += 8) {
+            const float g = dC[(size_t)m * N + n];
+            if (PassThrough) dA[(size_t)m * N + n] += g;
+            s += g;
+        }
+    }
+    sh[threadIdx.y][threadIdx.x] = s;
+    __syncthreads();
+    if (threadIdx.y == 0 && n < N) {
+        float t = 0.0f;
+#pragma unroll
+        for (int y = 0; y < 8; y++) t += sh[y][threadIdx.x];
+        partial[(size_t)blockIdx.y * N + n] = t;
+    }
+}
+
+__global__ void colsum_stage2_kernel(const float* __restrict__ partial, float* __restrict__ out, int chunks, int N)
+{
+    const int n = blockIdx.x * blockDim.x + threadIdx.x;
+    if (n >= N) return;
+    float t = 0.0f;
+    for (int c = 0; c < chunks; c++) t += partial[(size_t)c * N + n];
+    out[n] += t;
+}
+
+// same, for sum over rows of a[m,n] * b[m,n] * rowscale[m]  (RmsNorm / LayerNorm parameter gradients)
+template <int Mode>  // 0: dy*x*scale (rms dG), 1: dy*(x-mean)*rstd (ln dG), 2: dy (ln dB)
+__global__ void colsum_norm_stage1_kernel(const float* __restrict__ dY, const float* __restrict__ X,
+                                          const float* __restrict__ rowstat, float* __restrict__ partial, int M, int N,
+                                          int rows_per_chunk)
+{
+    __shared__ float sh[8][33];
+    const int n = blockIdx.x * 32 + threadIdx.x;
+    const int m0 = blockIdx.y * rows_per_chunk;
+    const int m1 = min(M, m0 + rows_per_chunk);
+    float s = 0.0f;
+    if (n < N) {
+        for (int m = m0 + threadIdx.y; m < m1; m += 8) {
+            const float dy = dY[(size_t)m * N + n];
+            if (Mode == 0) s += dy * X[(size_t)m * N + n] * rowstat[m];
+            else if (Mode == 1) s += dy * ((X[(size_t)m * N + n] - rowstat[2 * m]) * rowstat[2 * m + 1]);
+            else s += dy;
+        }
+    }
+    sh[threadIdx.y][threadIdx.x] = s;
+    __syncthreads();
+    if (threadIdx.y == 0 && n < N) {
+        float t = 0.0f;
+#pragma unroll
+        for (int y = 0; y < 8; y++) t += sh[y][threadIdx.x];
+        partial[(size_t)blockIdx.y * N + n] = t;
+    }
+}
+
+static void colsum_plan(int M, int& chunks, int& rows_per_chunk)
+{
+    chunks = (M + 63) / 64;
+    if (chunks > 256) chunks = 256;
+    if (chunks < 1) chunks = 1;
+    rows_per_chunk = (M + chunks - 1) / chunks;
+    chunks = (M + rows_per_chunk - 1) / rows_per_chunk;
+    if (chunks < 1) chunks = 1;
+}
+
+// ---------------------------------------------------------------------------
+// SoftmaxCrossEntropy
+// ---------------------------------------------------------------------------
+template <class TargetT>
+__global__ void softmax_xent_fwd_kernel(const float* __restrict__ logits, const TargetT* __restrict__ targets,
+                                        float* __restrict__ probs, float* __restrict__ rowloss, int N)
+{
+    __shared__ float sh[32];
+    const size_t row = blockIdx.x;
+    const float* x = logits + row * N;
+    float* p = probs + row * N;
+    float mx = -CUDART_INF_F;
+    for (int j = threadIdx.x; j < N; j += blockDim.x) mx = fmaxf(mx, x[j]);
+    mx = block_max(mx, sh);
+    float sum = 0.0f;
+    for (int j = threadIdx.x; j < N; j += blockDim.x) sum += expf(x[j] - mx);
+    sum = block_sum(sum, sh);
+    for (int j = threadIdx.x; j < N; j += blockDim.x) p[j] = expf(x[j] - mx) / sum;
+    if (threadIdx.x == 0) {
+        const int t = (int)targets[row];
+        const float pt = expf(x[t] - mx) / sum;
+        rowloss[row] = -logf(fmaxf(pt, 1e-15f));
+    }
+}
+
+// mean of M per-row losses, summed in a fixed order
+__global__ void mean_rows_kernel(const float* __restrict__ rowloss, float* __restrict__ loss, int M)
+{
+    __shared__ float sh[32];
+    float s = 0.0f;
+    for (int i = threadIdx.x; i < M; i += blockDim.x) s += rowloss[i];
+    s = block_sum(s, sh);
+    if (threadIdx.x == 0) loss[0] = s / (float)M;
+}
+
+template <class TargetT>
+__global__ void softmax_xent_bwd_kernel(const float* __restrict__ probs, const TargetT* __restrict__ targets,
+                                        float* __restrict__ dlogits, int M, int N)
+{
+    const float scale = 1.0f / (float)M;
+    const size_t total = (size_t)M * N;
+    for (size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x) {
+        const size_t r = i / N;
+        const int j = (int)(i - r * N);
+        const float ind = (j == (int)targets[r]) ? 1.0f : 0.0f;
+        dlogits[i] += scale * (probs[i] - ind);
+    }
+}
+
+// ---------------------------------------------------------------------------
+// Softmax rows (one warp per row)
+// ---------------------------------------------------------------------------
+// Causal = true: row i of each T x T slice sees columns j <= i of scale*S; the
+// reference adds -1e9 to the others, whose exp underflows to exactly 0.
+template <bool Causal>
+__global__ void softmax_rows_fwd_kernel(const float* __restrict__ S, float scale, float* __restrict__ P, size_t rows, int D)
+{
+    const size_t row = blockIdx.x * (size_t)(blockDim.x >> 5) + (threadIdx.x >> 5);
+    if (row >= rows) return;
+    const int lane = threadIdx.x & 31;
+    const float* x = S + row * D;
+    float* p = P + row * D;
+    const int lim = Causal ? (int)(row % D) + 1 : D;  // number of visible columns
+    float mx = -CUDART_INF_F;
+    for (int j = lane; j < lim; j += 32) mx = fmaxf(mx, Causal ? x[j] * scale : x[j]);
+    mx = warp_max(mx);
+    float sum = 0.0f;
+    for (int j = lane; j < lim; j += 32) sum += expf((Causal ? x[j] * scale : x[j]) - mx);
+    sum = warp_sum(sum);
+    for (int j = lane; j < D; j += 32) p[j] = (j < lim) ? expf((Causal ? x[j] * scale : x[j]) - mx) / sum : 0.0f;
+}
+
+// dA += scale * Y * (dY - sum(dY*Y))   (scale = 1 for the plain Softmax op)
+__global__ void softmax_rows_bwd_kernel(const float* __restrict__ Y, const float* __restrict__ dY, float scale,
+                                        float* __restrict__ dA, size_t rows, int D, int causal)
+{
+    const size_t row = blockIdx.x * (size_t)(blockDim.x >> 5) + (threadIdx.x >> 5);
+    if (row >= rows) return;
+    const int lane = threadIdx.x & 31;
+    const float* y = Y + row * D;
+    const float* dy = dY + row * D;
+    float* da = dA + row * D;
+    const int lim = causal ? (int)(row % D) + 1 : D;  // Y is exactly 0 beyond lim
+    float s = 0.0f;
+    for (int j = lane; j < lim; j += 32) s += dy[j] * y[j];
+    s = warp_sum(s);
+    for (int j = lane; j < lim; j += 32) da[j] += (y[j] * (dy[j] - s)) * scale;
+}
+
+// ---------------------------------------------------------------------------
+// RmsNorm / LayerNorm (one warp per row)
+// ---------------------------------------------------------------------------
+__global__ void rmsnorm_fwd_kernel(const float* __restrict__ X, const float* __restrict__ G, float eps,
+                                   float* __restrict__ Y, size_t rows, int D)
+{
+    const size_t row = blockIdx.x * (size_t)(blockDim.x >> 5) + (threadIdx.x >> 5);
+    if (row >= rows) return;
+    const int lane = threadIdx.x & 31;
+    const float* x = X + row * D;
+    float* y = Y + row * D;
+    float s = 0.0f;
+    for (int j = lane; j < D; j += 32) s += x[j] * x[j];
+    s = warp_sum(s);
+    const float rms = sqrtf(s / (float)D + eps);
+    for (int j = lane; j < D; j += 32) y[j] = x[j] / rms * G[j];
+}
+
+// dX (optional) and the per-row 1/rms needed by the dG column sums
+__global__ void rmsnorm_bwd_rows_kernel(const float* __restrict__ X, const float* __restrict__ G,
+                                        const float* __restrict__ dY, float eps, float* __restrict__ dX,
+                                        float* __restrict__ rowscale, size_t rows, int D)
+{
+    const size_t row = blockIdx.x * (size_t)(blockDim.x >> 5) + (threadIdx.x >> 5);
+    if (row >= rows) return;
+    const int lane = threadIdx.x & 31;
+    const float* x = X + row * D;
+    const float* dy = dY + row * D;
+    float s = 0.0f;
+    for (int j = lane; j < D; j += 32) s += x[j] * x[j];
+    s = warp_sum(s);
+    const float scale = 1.0f / sqrtf(s / (float)D + eps);
+    if (rowscale && lane == 0) rowscale[row] = scale;
+    if (dX) {
+        float t = 0.0f;
+        for (int j = lane; j < D; j += 32) t += dy[j] * G[j] * x[j];
+        t = warp_sum(t);
+        float* dx = dX + row * D;
+        for (int j = lane; j < D; j += 32) {
+            const float term1 = G[j] * dy[j];
+            const float term2 = x[j] * scale * scale * t / (float)D;
+            dx[j] += scale * (term1 - term2);
+        }
+    }
+}
+
+__global__ void layernorm_fwd_kernel(const float* __restrict__ X, const float* __restrict__ G,
+                                     const float* __restrict__ Bt, float eps, float* __restrict__ Y, size_t rows, int D)
+{
+    const size_t row = blockIdx.x * (size_t)(blockDim.x >> 5) + (threadIdx.x >> 5);
+    if (row >= rows) return;
+    const int lane = threadIdx.x & 31;
+    const float* x = X + row * D;
+    float* y = Y + row * D;
+    float s = 0.0f;
+    for (int j = lane; j < D; j += 32) s += x[j];
+    const float mean = warp_sum(s) / (float)D;
+    float v = 0.0f;
+    for (int j = lane; j < D; j += 32) { const float d = x[j] - mean; v += d * d; }
+    const float rstd = 1.0f / sqrtf(warp_sum(v) / (float)D + eps);
+    for (int j = lane; j < D; j += 32) y[j] = (x[j] - mean) * rstd * G[j] + Bt[j];
+}
+
+__global__ void layernorm_bwd_rows_kernel(const float* __restrict__ X, const float* __restrict__ G,
+                                          const float* __restrict__ dY, float eps, float* __restrict__ dX,
+                                          float* __restrict__ rowstat, size_t rows, int D)
+{
+    const size_t row = blockIdx.x * (size_t)(blockDim.x >> 5) + (threadIdx.x >> 5);
+    if (row >= rows) return;
+    const int lane = threadIdx.x & 31;
+    const float* x = X + row * D;
+    const float* dy = dY + row * D;
+    float s = 0.0f;
+    for (int j = lane; j < D; j += 32) s += x[j];
+    const float mean = warp_sum(s) / (float)D;
+    float v = 0.0f;
+    for (int j = lane; j < D; j += 32) { const float d = x[j] - mean; v += d * d; }
+    const float rstd = 1.0f / sqrtf(warp_sum(v) / (float)D + eps);
+    if (rowstat && lane == 0) { rowstat[2 * row] = mean; rowstat[2 * row + 1] = rstd; }
+    if (dX) {
+        float s1 = 0.0f, s2 = 0.0f;
+        for (int j = lane; j < D; j += 32) {
+            const float gdy = G[j] * dy[j];
+            s1 += gdy;
+            s2 += gdy * ((x[j] - mean) * rstd);
+        }
+        s1 = warp_sum(s1);
+        s2 = warp_sum(s2);
+        float* dx = dX + row * D;
+        for (int j = lane; j < D; j += 32) {
+            const float xh = (x[j] - mean) * rstd;
+            dx[j] += rstd * (G[j] * dy[j] - s1 / (float)D - xh * s2 / (float)D);
+        }
+    }
+}
+
+// ---------------------------------------------------------------------------
+// Embedding
+// ---------------------------------------------------------------------------
+__global__ void embedding_fwd_kernel(const float* __restrict__ W, const float* __restrict__ ids, float* __restrict__ Y,
+                                     size_t n, int D)
+{
+    for (size_t i = blockIdx.x; i < n; i += gridDim.x) {
+        const size_t idx = (size_t)ids[i];
+        const float* w = W + idx * D;
+        float* y = Y + i * D;
+        for (int j = threadIdx.x; j < D; j += blockDim.x) y[j] = w[j];
+    }
+}
+
+// One block per vocabulary row: finds the positions that use this row (kept in
+// (b,t) order) and adds their dY rows one after the other, as the reference's
+// sequential scatter-add does for that row.
+__global__ void embedding_bwd_kernel(const float* __restrict__ ids, const float* __restrict__ dY,
+                                     float* __restrict__ dW, int n, int D)
+{
+    __shared__ int matches[256];
+    __shared__ int warp_counts[8];
+    __shared__ int nmatch;
+    const int v = blockIdx.x;
+    const int lane = threadIdx.x & 31, w = threadIdx.x >> 5;
+    // each thread owns columns threadIdx.x, +256, ... (D <= 256*8)
+    float acc[8];
+#pragma unroll
+    for (int c = 0; c < 8; c++) acc[c] = 0.0f;
+    bool any = false;
+    for (int base = 0; base < n; base += 256) {
+        const int i = base + threadIdx.x;
+        const bool hit = (i < n) && ((int)ids[i] == v);
+        const unsigned bal = __ballot_sync(0xffffffffu, hit);
+        if (lane == 0) warp_counts[w] = __popc(bal);
+        __syncthreads();
+        int off = 0;
+        for (int k = 0; k < w; k++) off += warp_counts[k];
+        if (hit) matches[off + __popc(bal & ((1u << lane) - 1))] = i;
+        if (threadIdx.x == 0) {
+            int t = 0;
+            for (int k = 0; k < 8; k++) t += warp_counts[k];
+            nmatch = t;
+        }
+        __syncthreads();
+        const int nm = nmatch;
+        for (int k = 0; k < nm; k++) {
+            const float* g = dY + (size_t)matches[k] * D;
+#pragma unroll
+            for (int c = 0; c < 8; c++) {
+                const int j = threadIdx.x + c * 256;
+                if (j < D) acc[c] += g[j];
+            }
+            any = true;
+        }
+        __syncthreads();
+    }
+    if (any) {
+#pragma unroll
+        for (int c = 0; c < 8; c++) {
+            const int j = threadIdx.x + c * 256;
+            if (j < D) dW[(size_t)v * D + j] += acc[c];
+        }
+    }
+}
+
+// general (D > 2048) fallback: thread per (vocab row, column), scanning ids in order
+__global__ void embedding_bwd_wide_kernel(const float* __restrict__ ids, const float* __restrict__ dY,
+                                          float* __restrict__ dW, int n, int D)
+{
+    const int v = blockIdx.x;
+    for (int j = threadIdx.x; j < D; j += blockDim.x) {
+        float acc = 0.0f;
+        bool any = false;
+        for (int i = 0; i < n; i++)
+            if ((int)ids[i] == v) { acc += dY[(size_t)i * D + j]; any = true; }
+        if (any) dW[(size_t)v * D + j] += acc;
+    }
+}
+
+// ---------------------------------------------------------------------------
+// Transpose of two dims (rank <= 8)
+// ---------------------------------------------------------------------------
+struct TransposeDesc {
+    int rank;
+    long long out_dims[8];
+    long long src_strides[8];
+};
+
+template <bool Backward>
+__global__ void transpose_generic_kernel(const float* __restrict__ in, float* __restrict__ out, TransposeDesc d, size_t total)
+{
+    for (size_t f = blockIdx.x * (size_t)blockDim.x + threadIdx.x; f < total; f += (size_t)gridDim.x * blockDim.x) {
+        size_t rem = f;
+        long long src = 0;
+#pragma unroll 1
+        for (int k = d.rank - 1; k >= 0; k--) {
+            const long long idx = (long long)(rem % (size_t)d.out_dims[k]);
+            rem /= (size_t)d.out_dims[k];
+            src += idx * d.src_strides[k];
+        }
+        if (Backward) out[src] += in[f];   // dA[src] += dC[f]  (a permutation: no two f share a src)
+        else out[f] = in[src];             // C[f] = A[src]
+    }
+}
+
+// last two dims swapped: per-slice R x Cc -> Cc x R through a shared-memory tile
+template <bool Backward>
+__global__ void transpose_last2_kernel(const float* __restrict__ in, float* __restrict__ out, int R, int Cc)
+{
+    __shared__ float tile[32][33];
+    const size_t slice = blockIdx.z;
+    // forward: in is [R, Cc], out is [Cc, R].  backward: in (dC) is [Cc, R], out (dA) is [R, Cc], accumulated.
+    const int in_rows = Backward ? Cc : R, in_cols = Backward ? R : Cc;
+    const float* src = in + slice * (size_t)R * Cc;
+    float* dst = out + slice * (size_t)R * Cc;
+    const int c0 = blockIdx.x * 32, r0 = blockIdx.y * 32;  // tile origin in the input
+    for (int j = threadIdx.y; j < 32; j += 8) {
+        const int r = r0 + j, c = c0 + threadIdx.x;
+        tile[j][threadIdx.x] = (r < in_rows && c < in_cols) ? src[(size_t)r * in_cols + c] : 0.0f;
+    }
+    __syncthreads();
+    for (int j = threadIdx.y; j < 32; j += 8) {
+        const int orow = c0 + j, ocol = r0 + threadIdx.x;  // output is [in_cols, in_rows]
+        if (orow < in_cols && ocol < in_rows) {
+            float* p = dst + (size_t)orow * in_rows + ocol;
+            if (Backward) *p += tile[threadIdx.x][j]; else *p = tile[threadIdx.x][j];
+        }
+    }
+}
+
+// ---------------------------------------------------------------------------
+// argmax, SGD
+// ---------------------------------------------------------------------------
+// first maximum wins: strict > while scanning, lower index on equal values when merging
+__global__ void argmax_rows_kernel(const float* __restrict__ A, float* __restrict__ out, int M, int N)
+{
+    const int row = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    if (row >= M) return;
+    const int lane = threadIdx.x & 31;
+    const float* a = A + (size_t)row * N;
+    float mv = -CUDART_INF_F;
+    int mi = 0x7fffffff;
+    for (int j = lane; j < N; j += 32) {
+        const float v = a[j];
+        if (mi == 0x7fffffff || v > mv) { mv = v; mi = j; }
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+        const float ov = __shfl_xor_sync(0xffffffffu, mv, o);
+        const int oi = __shfl_xor_sync(0xffffffffu, mi, o);
+        if (oi != 0x7fffffff && (mi == 0x7fffffff || ov > mv || (ov == mv && oi < mi))) { mv = ov; mi = oi; }
+    }
+    if (lane == 0) out[row] = (float)mi;
+}
+
+__global__ void argmax_cols_kernel(const float* __restrict__ A, float* __restrict__ out, int M, int N)
+{
+    const int j = blockIdx.x * blockDim.x + threadIdx.x;
+    if (j >= N) return;
+    float mv = A[j];
+    int mi = 0;
+    for (int i = 1; i < M; i++) {
+        const float v = A[(size_t)i * N + j];
+        if (v > mv) { mv = v; mi = i; }
+    }
+    out[j] = (float)mi;
+}
+
+__global__ void sgd_kernel(float* __restrict__ w, const float* __restrict__ g, float* __restrict__ v, float lr,
+                           float momentum, float grad_scale, size_t n)
+{
+    const size_t tid = blockIdx.x * (size_t)blockDim.x + threadIdx.x, nth = (size_t)gridDim.x * blockDim.x;
+    const bool scaled = (grad_scale != 1.0f);
+    for (size_t i = tid; i < n; i += nth) {
+        float gi = g[i];
+        if (scaled) gi *= grad_scale;
+        if (v) {
+            const float vel = momentum * v[i] + lr * gi;
+            v[i] = vel;
+            w[i] -= vel;
+        } else {
+            w[i] -= lr * gi;
+        }
+    }
+}
+
+}  // namespace znn
+
+using namespace znn;
+
+#define ZNN_NEED_DEVICE()                                                                                  \
+    do {                                                                                                   \
+        if (!stream()) return fail(ZNN_ERR_CUDA, "no CUDA device state; call znn_init (no CPU fallback)"); \
+    } while (0)
+
+extern "C" {
+
+int znn_fill(float* dst, float value, size_t n)
+{
+    if (n == 0) return ZNN_OK;
+    ZNN_NEED_DEVICE();
+    ZNN_REQUIRE(dst, "dst is NULL");
+    fill_kernel<<<ew_blocks(n), kEwThreads, 0, stream()>>>(dst, value, n);
+    ZNN_LAUNCH_OK("fill_kernel");
+    return ZNN_OK;
+}
+
+int znn_add_bias_fwd(const float* A, const float* bias, float* C, int M, int N)
+{
+    if (M <= 0 || N <= 0) return ZNN_OK;
+    ZNN_NEED_DEVICE();
+    ZNN_REQUIRE(A && bias && C, "NULL pointer");
+    const size_t total = (size_t)M * N;
+    add_bias_fwd_kernel<<<ew_blocks(total), kEwThreads, 0, stream()>>>(A, bias, C, total, N);
+    ZNN_LAUNCH_OK("add_bias_fwd_kernel");
+    return ZNN_OK;
+}
+
+int znn_add_bias_bwd(const float* dC, float* dA, float* dbias, int M, int N)
+{
+    if (M <= 0 || N <= 0) return ZNN_OK;
+    ZNN_NEED_DEVICE();
+    ZNN_REQUIRE(dC, "dC is NULL");
+    if (!dbias) {
+        if (dA) return znn_accumulate(dC, dA, (size_t)M * N);
+        return ZNN_OK;
+    }
+    int chunks, rpc;
+    colsum_plan(M, chunks, rpc);
+    float* partial = (float*)workspace((size_t)chunks * N * sizeof(float));
+    if (!partial) return fail(ZNN_ERR_NOMEM, "scratch for bias gradient");
+    dim3 grid(ceil_div(N, 32), chunks), block(32, 8);
+    if (dA) colsum_stage1_kernel<true><<<grid, block, 0, stream()>>>(dC, dA, partial, M, N, rpc);
+    else colsum_stage1_kernel<false><<<grid, block, 0, stream()>>>(dC, nullptr, partial, M, N, rpc);
+    ZNN_LAUNCH_OK("colsum_stage1_kernel");
+    colsum_stage2_kernel<<<ceil_div(N, 128), 128, 0, stream()>>>(partial, dbias, chunks, N);
+    ZNN_LAUNCH_OK("colsum_stage2_kernel");
+    return ZNN_OK;
+}
+
+int znn_relu_fwd(const float* A, float* C, size_t n)
+{
+    if (n == 0) return ZNN_OK;
+    ZNN_NEED_DEVICE();
+    ew1w_kernel<<<ew_blocks(n), kEwThreads, 0, stream()>>>(A, C, n, ReluF());
+    ZNN_LAUNCH_OK("relu_fwd");
+    return ZNN_OK;
+}
+
+int znn_relu_bwd(const float* A, const float* dC, float* dA, size_t n)
+{
+    if (n == 0 || !dA) return ZNN_OK;
+    ZNN_NEED_DEVICE();
+    ew2_kernel<<<ew_blocks(n), kEwThreads, 0, stream()>>>(A, dC, dA, n, ReluBwdF());
+    ZNN_LAUNCH_OK("relu_bwd");
+    return ZNN_OK;
+}
+
+int znn_gelu_fwd(const float* A, float* C, size_t n)
+{
+    if (n == 0) return ZNN_OK;
+    ZNN_NEED_DEVICE();
+    ew1w_kernel<<<ew_blocks(n), kEwThreads, 0, stream()>>>(A, C, n, GeluF());
+    ZNN_LAUNCH_OK("gelu_fwd");
+    return ZNN_OK;
+}
+
+int znn_gelu_bwd(const float* A, const float* dC, float* dA, size_t n)
+{
+    if (n == 0 || !dA) return ZNN_OK;
+    ZNN_NEED_DEVICE();
+    ew2_kernel<<<ew_blocks(n), kEwThreads, 0, stream()>>>(A, dC, dA, n, GeluBwdF());
+    ZNN_LAUNCH_OK("gelu_bwd");
+    return ZNN_OK;
+}
+
+}  // extern "C"
+
+template <class T>
+static int xent_fwd(const float* logits, const T* targets, float* probs, float* loss, int M, int N)
+{
+    ZNN_REQUIRE(M > 0 && N > 0, "empty logits");
+    ZNN_NEED_DEVICE();
+    ZNN_REQUIRE(logits && targets && probs && loss, "NULL pointer");
+    float* rowloss = (float*)workspace((size_t)M * sizeof(float));
+    if (!rowloss) return fail(ZNN_ERR_NOMEM, "scratch for per-row losses");
+    const int threads = N >= 1024 ? 256 : (N >= 128 ? 128 : 32);
+    softmax_xent_fwd_kernel<T><<<M, threads, 0, stream()>>>(logits, targets, probs, rowloss, N);
+    ZNN_LAUNCH_OK("softmax_xent_fwd_kernel");
+    mean_rows_kernel<<<1, 1024, 0, stream()>>>(rowloss, loss, M);
+    ZNN_LAUNCH_OK("mean_rows_kernel");
+    return ZNN_OK;
+}
+
+template <class T>
+static int xent_bwd(const float* probs, const T* targets, float* dlogits, int M, int N)
+{
+    if (M <= 0 || N <= 0) return ZNN_OK;
+    ZNN_NEED_DEVICE();
+    ZNN_REQUIRE(probs && targets && dlogits, "NULL pointer");
+    softmax_xent_bwd_kernel<T><<<ew_blocks((size_t)M * N, 2), kEwThreads, 0, stream()>>>(probs, targets, dlogits, M, N);
+    ZNN_LAUNCH_OK("softmax_xent_bwd_kernel");
+    return ZNN_OK;
+}
+
+extern "C" {
+
+int znn_softmax_xent_fwd(const float* logits, const int32_t* targets, float* probs, float* loss, int M, int N)
+{
+    return xent_fwd<int32_t>(logits, targets, probs, loss, M, N);
+}
+
+int znn_softmax_xent_fwd_u8(const float* logits, const uint8_t* targets, float* probs, float* loss, int M, int N)
+{
+    return xent_fwd<uint8_t>(logits, targets, probs, loss, M, N);
+}
+
+int znn_softmax_xent_bwd(const float* probs, const int32_t* targets, float* dlogits, int M, int N)
+{
+    return xent_bwd<int32_t>(probs, targets, dlogits, M, N);
+}
+
+int znn_softmax_xent_bwd_u8(const float* probs, const uint8_t* targets, float* dlogits, int M, int N)
+{
+    return xent_bwd<uint8_t>(probs, targets, dlogits, M, N);
+}
+
+static inline unsigned row_blocks(size_t rows, int warps_per_block) { return (unsigned)((rows + warps_per_block - 1) / warps_per_block); }
+
+int znn_softmax_fwd(const float* A, float* C, size_t rows, int D)
+{
+    if (rows == 0 || D <= 0) return ZNN_OK;
+    ZNN_NEED_DEVICE();
+    softmax_rows_fwd_kernel<false><<<row_blocks(rows, 8), 256, 0, stream()>>>(A, 1.0f, C, rows, D);
+    ZNN_LAUNCH_OK("softmax_rows_fwd_kernel");
+    return ZNN_OK;
+}
+
+int znn_softmax_bwd(const float* Y, const float* dY, float* dA, size_t rows, int D)
+{
+    if (rows == 0 || D <= 0 || !dA) return ZNN_OK;
+    ZNN_NEED_DEVICE();
+    softmax_rows_bwd_kernel<<<row_blocks(rows, 8), 256, 0, stream()>>>(Y, dY, 1.0f, dA, rows, D, 0);
+    ZNN_LAUNCH_OK("softmax_rows_bwd_kernel");
+    return ZNN_OK;
+}
+
+int znn_causal_softmax_fwd(const float* S, float scale, float* P, int nslices, int T)
+{
+    if (nslices <= 0 || T <= 0) return ZNN_OK;
+    ZNN_NEED_DEVICE();
+    const size_t rows = (size_t)nslices * T;
+    softmax_rows_fwd_kernel<true><<<row_blocks(rows, 8), 256, 0, stream()>>>(S, scale, P, rows, T);
+    ZNN_LAUNCH_OK("causal softmax fwd");
+    return ZNN_OK;
+}
+
+int znn_causal_softmax_bwd(const float* P, const float* dP, float scale, float* dS, int nslices, int T)
+{
+    if (nslices <= 0 || T <= 0 || !dS) return ZNN_OK;
+    ZNN_NEED_DEVICE();
+    const size_t rows = (size_t)nslices * T;
+    softmax_rows_bwd_kernel<<<row_blocks(rows, 8), 256, 0, stream()>>>(P, dP, scale, dS, rows, T, 1);
+    ZNN_LAUNCH_OK("causal softmax bwd");
+    return ZNN_OK;
+}
+
+int znn_rmsnorm_fwd(const float* X, const float* G, float eps, float* Y, size_t rows, int D)
+{
+    if (rows == 0 || D <= 0) return ZNN_OK;
+    ZNN_NEED_DEVICE();
+    rmsnorm_fwd_kernel<<<row_blocks(rows, 8), 256, 0, stream()>>>(X, G, eps, Y, rows, D);
+    ZNN_LAUNCH_OK("rmsnorm_fwd_kernel");
+    return ZNN_OK;
+}
+
+int znn_rmsnorm_bwd(const float* X, const float* G, const float* dY, float eps, float* dX, float* dG, size_t rows, int D)
+{
+    if (rows == 0 || D <= 0 || (!dX && !dG)) return ZNN_OK;
+    ZNN_NEED_DEVICE();
+    ZNN_REQUIRE(rows <= 0x7fffffff, "too many rows");
+    int chunks = 0, rpc = 0;
+    float* rowscale = nullptr;
+    float* partial = nullptr;
+    if (dG) {
+        colsum_plan((int)rows, chunks, rpc);
+        float* ws = (float*)workspace((rows + (size_t)chunks * D) * sizeof(float));
+        if (!ws) return fail(ZNN_ERR_NOMEM, "scratch for RmsNorm backward");
+        rowscale = ws;
+        partial = ws + rows;
+    }
+    rmsnorm_bwd_rows_kernel<<<row_blocks(rows, 8), 256, 0, stream()>>>(X, G, dY, eps, dX, rowscale, rows, D);
+    ZNN_LAUNCH_OK("rmsnorm_bwd_rows_kernel");
+    if (dG) {
+        dim3 grid(ceil_div(D, 32), chunks), block(32, 8);
+        colsum_norm_stage1_kernel<0><<<grid, block, 0, stream()>>>(dY, X, rowscale, partial, (int)rows, D, rpc);
+        ZNN_LAUNCH_OK("colsum_norm_stage1_kernel");
+        colsum_stage2_kernel<<<ceil_div(D, 128), 128, 0, stream()>>>(partial, dG, chunks, D);
+        ZNN_LAUNCH_OK("colsum_stage2_kernel");
+    }
+    return ZNN_OK;
+}
+
+int znn_layernorm_fwd(const float* X, const float* G, const float* B, float eps, float* Y, size_t rows, int D)
+{
+    if (rows == 0 || D <= 0) return ZNN_OK;
+    ZNN_NEED_DEVICE();
+    layernorm_fwd_kernel<<<row_blocks(rows, 8), 256, 0, stream()>>>(X, G, B, eps, Y, rows, D);
+    ZNN_LAUNCH_OK("layernorm_fwd_kernel");
+    return ZNN_OK;
+}
+
+int znn_layernorm_bwd(const float* X, const float* G, const float* dY, float eps, float* dX, float* dG, float* dB,
+                      size_t rows, int D)
+{
+    if (rows == 0 || D <= 0 || (!dX && !dG && !dB)) return ZNN_OK;
+    ZNN_NEED_DEVICE();
+    ZNN_REQUIRE(rows <= 0x7fffffff, "too many rows");
+    int chunks = 0, rpc = 0;
+    float* rowstat = nullptr;
+    float* partial = nullptr;
+    if (dG || dB) {
+        colsum_plan((int)rows, chunks, rpc);
+        float* ws = (float*)workspace((2 * rows + (size_t)chunks * D) * sizeof(float));
+        if (!ws) return fail(ZNN_ERR_NOMEM, "scratch for LayerNorm backward");
+        rowstat = ws;
+        partial = ws + 2 * rows;
+    }
+    layernorm_bwd_rows_kernel<<<row_blocks(rows, 8), 256, 0, stream()>>>(X, G, dY, eps, dX, rowstat, rows, D);
+    ZNN_LAUNCH_OK("layernorm_bwd_rows_kernel");
+    dim3 grid(ceil_div(D, 32), chunks), block(32, 8);
+    if (dG) {
+        colsum_norm_stage1_kernel<1><<<grid, block, 0, stream()>>>(dY, X, rowstat, partial, (int)rows, D, rpc);
+        ZNN_LAUNCH_OK("colsum_norm_stage1_kernel");
+        colsum_stage2_kernel<<<ceil_div(D, 128), 128, 0, stream()>>>(partial, dG, chunks, D);
+        ZNN_LAUNCH_OK("colsum_stage2_kernel");
+    }
+    if (dB) {
+        colsum_norm_stage1_kernel<2><<<grid, block, 0, stream()>>>(dY, X, rowstat, partial, (int)rows, D, rpc);
+        ZNN_LAUNCH_OK("colsum_norm_stage1_kernel");
+        colsum_stage2_kernel<<<ceil_div(D, 128), 128, 0, stream()>>>(partial, dB, chunks, D);
+        ZNN_LAUNCH_OK("colsum_stage2_kernel");
+    }
+    return ZNN_OK;
+}
+
+int znn_embedding_fwd(const float* W, const float* ids, float* Y, size_t n, int D, int vocab)
+{
+    (void)vocab;
+    if (n == 0 || D <= 0) return ZNN_OK;
+    ZNN_NEED_DEVICE();
+    const unsigned blocks = (unsigned)(n < 65535u * 16u ? n : 65535u * 16u);
+    embedding_fwd_kernel<<<blocks, D >= 256 ? 256 : 64, 0, stream()>>>(W, ids, Y, n, D);
+    ZNN_LAUNCH_OK("embedding_fwd_kernel");
+    return ZNN_OK;
+}
+
+int znn_embedding_bwd(const float* ids, const float* dY, float* dW, size_t n, int D, int vocab)
+{
+    if (n == 0 || D <= 0 || !dW) return ZNN_OK;
+    ZNN_NEED_DEVICE();
+    ZNN_REQUIRE(vocab > 0, "vocab must be given for the backward pass");
+    ZNN_REQUIRE(n <= 0x7fffffff, "too many ids");
+    if (D <= 2048) embedding_bwd_kernel<<<vocab, 256, 0, stream()>>>(ids, dY, dW, (int)n, D);
+    else embedding_bwd_wide_kernel<<<vocab, 256, 0, stream()>>>(ids, dY, dW, (int)n, D);
+    ZNN_LAUNCH_OK("embedding_bwd_kernel");
+    return ZNN_OK;
+}
+
+static int transpose_impl(const float* in, float* out, const int64_t* dims, int rank, int d0, int d1, bool backward)
+{
+    ZNN_REQUIRE(rank >= 1 && rank <= 8, "rank must be 1..8");
+    ZNN_REQUIRE(d0 >= 0 && d0 < rank && d1 >= 0 && d1 < rank, "dims out of range");
+    ZNN_NEED_DEVICE();
+    size_t total = 1;
+    for (int k = 0; k < rank; k++) total *= (size_t)dims[k];
+    if (total == 0) return ZNN_OK;
+    if (d0 > d1) { int t = d0; d0 = d1; d1 = t; }
+    if (d0 != d1 && d0 == rank - 2 && d1 == rank - 1) {
+        size_t slices = 1;
+        for (int k = 0; k < rank - 2; k++) slices *= (size_t)dims[k];
+        const int R = (int)dims[rank - 2], Cc = (int)dims[rank - 1];
+        if (slices <= 65535) {
+            const int in_rows = backward ? Cc : R, in_cols = backward ? R : Cc;
+            dim3 grid(ceil_div(in_cols, 32), ceil_div(in_rows, 32), (unsigned)slices), block(32, 8);
+            if (backward) transpose_last2_kernel<true><<<grid, block, 0, stream()>>>(in, out, R, Cc);
+            else transpose_last2_kernel<false><<<grid, block, 0, stream()>>>(in, out, R, Cc);
+            ZNN_LAUNCH_OK("transpose_last2_kernel");
+            return ZNN_OK;
+        }
+    }
+    TransposeDesc d;
+    d.rank = rank;
+    long long strides[8];
+    long long s = 1;
+    for (int k = rank - 1; k >= 0; k--) { strides[k] = s; s *= dims[k]; }
+    for (int k = 0; k < rank; k++) { d.out_dims[k] = dims[k]; d.src_strides[k] = strides[k]; }
+    d.out_dims[d0] = dims[d1]; d.out_dims[d1] = dims[d0];
+    d.src_strides[d0] = strides[d1]; d.src_strides[d1] = strides[d0];
+    if (backward) transpose_generic_kernel<true><<<ew_blocks(total, 2), kEwThreads, 0, stream()>>>(in, out, d, total);
+    else transpose_generic_kernel<false><<<ew_blocks(total, 2), kEwThreads, 0, stream()>>>(in, out, d, total);
+    ZNN_LAUNCH_OK("transpose_generic_kernel");
+    return ZNN_OK;
+}
+
+int znn_transpose_fwd(const float* A, float* C, const int64_t* dims, int rank, int d0, int d1)
+{
+    return transpose_impl(A, C, dims, rank, d0, d1, false);
+}
+
+int znn_transpose_bwd(const float* dC, float* dA, const int64_t* dims, int rank, int d0, int d1)
+{
+    if (!dA) return ZNN_OK;
+    return transpose_impl(dC, dA, dims, rank, d0, d1, true);
+}
+
+int znn_add_fwd(const float* A, const float* B, float* C, size_t n)
+{
+    if (n == 0) return ZNN_OK;
+    ZNN_NEED_DEVICE();
+    ew2w_kernel<<<ew_blocks(n), kEwThreads, 0, stream()>>>(A, B, C, n, AddF());
+    ZNN_LAUNCH_OK("add_fwd");
+    return ZNN_OK;
+}
+
+int znn_accumulate(const float* src, float* dst, size_t n)
+{
+    if (n == 0 || !dst) return ZNN_OK;
+    ZNN_NEED_DEVICE();
+    ew1_kernel<<<ew_blocks(n), kEwThreads, 0, stream()>>>(src, dst, n, AccF());
+    ZNN_LAUNCH_OK("accumulate");
+    return ZNN_OK;
+}
+
+int znn_mul_scalar_fwd(const float* A, float v, float* C, size_t n)
+{
+    if (n == 0) return ZNN_OK;
+    ZNN_NEED_DEVICE();
+    MulF f; f.v = v;
+    ew1w_kernel<<<ew_blocks(n), kEwThreads, 0, stream()>>>(A, C, n, f);
+    ZNN_LAUNCH_OK("mul_scalar_fwd");
+    return ZNN_OK;
+}
+
+int znn_mul_scalar_bwd(const float* dC, float v, float* dA, size_t n)
+{
+    if (n == 0 || !dA) return ZNN_OK;
+    ZNN_NEED_DEVICE();
+    MulAccF f; f.v = v;
+    ew1_kernel<<<ew_blocks(n), kEwThreads, 0, stream()>>>(dC, dA, n, f);
+    ZNN_LAUNCH_OK("mul_scalar_bwd");
+    return ZNN_OK;
+}
+
+int znn_argmax(const float* A, float* out, int M, int N, int dim)
+{
+    ZNN_REQUIRE(dim == 0 || dim == 1, "dim must be 0 or 1");
+    if (M <= 0 || N <= 0) return ZNN_OK;
+    ZNN_NEED_DEVICE();
+    if (dim == 1) argmax_rows_kernel<<<ceil_div(M, 8), 256, 0, stream()>>>(A, out, M, N);
+    else argmax_cols_kernel<<<ceil_div(N, 128), 128, 0, stream()>>>(A, out, M, N);
+    ZNN_LAUNCH_OK("argmax kernel");
+    return ZNN_OK;
+}
+
+int znn_sgd_step(float* w, const float* g, float* v, float lr, float momentum, float grad_scale, size_t n)
+{
+    if (n == 0) return ZNN_OK;
+    ZNN_NEED_DEVICE();
+    ZNN_REQUIRE(w && g, "NULL pointer");
+    ZNN_REQUIRE(v || momentum == 0.0f, "momentum needs a velocity buffer");
+    sgd_kernel<<<ew_blocks(n), kEwThreads, 0, stream()>>>(w, g, (momentum > 0.0f) ? v : nullptr, lr, momentum, grad_scale, n);
+    ZNN_LAUNCH_OK("sgd_kernel");
+    return ZNN_OK;
+}
+
+}  // extern "C"

@@ -1,0 +1,239 @@
+// Runtime part of the shim: device selection, stream, allocation, copies,
+// error text, device status word, GEMM scratch.
+#include <stdarg.h>
+#include <string.h>
+
+#include <mutex>
+
+#include "common.cuh"
+
+namespace znn {
+
+static thread_local char t_err[512] = "";
+
+void set_error(const char* fmt, ...)
+{
+    va_list ap;
+    va_start(ap, fmt);
+    vsnprintf(t_err, sizeof(t_err), fmt, ap);
+    va_end(ap);
+}
+
+int fail(int code, const char* fmt, ...)
+{
+    va_list ap;
+    va_start(ap, fmt);
+    vsnprintf(t_err, sizeof(t_err), fmt, ap);
+    va_end(ap);
+    return code;
+}
+
+constexpr int kMaxDev = 16;
+
+struct DeviceState {
+    bool ready = false;
+    cudaStream_t own_stream = nullptr;
+    int* status = nullptr;  // device int
+    void* ws = nullptr;
+    size_t ws_bytes = 0;
+    int sms = 0;
+};
+
+static DeviceState g_dev[kMaxDev];
+static std::mutex g_mu;
+static thread_local cudaStream_t t_user_stream = nullptr;
+static thread_local bool t_has_user_stream = false;
+
+static DeviceState* cur(bool create)
+{
+    int d = -1;
+    if (cudaGetDevice(&d) != cudaSuccess || d < 0 || d >= kMaxDev) return nullptr;
+    DeviceState& s = g_dev[d];
+    if (!s.ready && create) {
+        std::lock_guard<std::mutex> lk(g_mu);
+        if (!s.ready) {
+            if (cudaStreamCreateWithFlags(&s.own_stream, cudaStreamNonBlocking) != cudaSuccess) return nullptr;
+            if (cudaMalloc((void**)&s.status, sizeof(int)) != cudaSuccess) return nullptr;
+            if (cudaMemset(s.status, 0, sizeof(int)) != cudaSuccess) return nullptr;
+            cudaDeviceProp prop;
+            if (cudaGetDeviceProperties(&prop, d) != cudaSuccess) return nullptr;
+            s.sms = prop.multiProcessorCount;
+            s.ready = true;
+        }
+    }
+    return s.ready ? &s : nullptr;
+}
+
+cudaStream_t stream()
+{
+    if (t_has_user_stream) return t_user_stream;
+    DeviceState* s = cur(true);
+    return s ? s->own_stream : nullptr;
+}
+
+int* device_status_word()
+{
+    DeviceState* s = cur(true);
+    return s ? s->status : nullptr;
+}
+
+int sm_count()
+{
+    DeviceState* s = cur(true);
+    return s ? s->sms : 0;
+}
+
+void* workspace(size_t bytes)
+{
+    DeviceState* s = cur(true);
+    if (!s) return nullptr;
+    if (bytes <= s->ws_bytes) return s->ws;
+    // Growing: everything queued so far may still read the old block.
+    cudaStreamSynchronize(stream());
+    if (s->ws) cudaFree(s->ws);
+    s->ws = nullptr;
+    s->ws_bytes = 0;
+    size_t want = bytes + (bytes >> 3);
+    if (cudaMalloc(&s->ws, want) != cudaSuccess) {
+        cudaGetLastError();
+        want = bytes;
+        if (cudaMalloc(&s->ws, want) != cudaSuccess) {
+            cudaGetLastError();
+            return nullptr;
+        }
+    }
+    s->ws_bytes = want;
+    return s->ws;
+}
+
+}  // namespace znn
+
+using namespace znn;
+
+extern "C" {
+
+int znn_device_count(int* count)
+{
+    ZNN_REQUIRE(count, "count is NULL");
+    cudaError_t e = cudaGetDeviceCount(count);
+    if (e != cudaSuccess) {
+        *count = 0;
+        return fail(ZNN_ERR_CUDA, "cudaGetDeviceCount: %s", cudaGetErrorString(e));
+    }
+    return ZNN_OK;
+}
+
+int znn_init(int device)
+{
+    int n = 0;
+    cudaError_t e = cudaGetDeviceCount(&n);
+    if (e != cudaSuccess || n == 0)
+        return fail(ZNN_ERR_CUDA, "no CUDA device: %s (this library has no CPU fallback)",
+                    e != cudaSuccess ? cudaGetErrorString(e) : "device count is 0");
+    ZNN_REQUIRE(device >= 0 && device < n && device < kMaxDev, "device %d out of range (have %d)", device, n);
+    ZNN_CUDA_OK(cudaSetDevice(device));
+    cudaDeviceProp prop;
+    ZNN_CUDA_OK(cudaGetDeviceProperties(&prop, device));
+    if (prop.major != 10)
+        return fail(ZNN_ERR_UNSUPPORTED, "device %d is sm_%d%d; this library is built for sm_100a only", device,
+                    prop.major, prop.minor);
+    if (!cur(true)) return fail(ZNN_ERR_CUDA, "could not create per-device state");
+    return ZNN_OK;
+}
+
+int znn_set_stream(void* cuda_stream)
+{
+    t_user_stream = (cudaStream_t)cuda_stream;
+    t_has_user_stream = (cuda_stream != nullptr);
+    return ZNN_OK;
+}
+
+int znn_get_stream(void** cuda_stream)
+{
+    ZNN_REQUIRE(cuda_stream, "cuda_stream is NULL");
+    *cuda_stream = (void*)stream();
+    return ZNN_OK;
+}
+
+int znn_sync(void)
+{
+    ZNN_CUDA_OK(cudaStreamSynchronize(stream()));
+    return ZNN_OK;
+}
+
+int znn_malloc(void** ptr, size_t bytes)
+{
+    ZNN_REQUIRE(ptr, "ptr is NULL");
+    *ptr = nullptr;
+    if (bytes == 0) return ZNN_OK;
+    cudaError_t e = cudaMalloc(ptr, bytes);
+    if (e != cudaSuccess) {
+        cudaGetLastError();
+        return fail(e == cudaErrorMemoryAllocation ? ZNN_ERR_NOMEM : ZNN_ERR_CUDA, "cudaMalloc(%zu): %s", bytes,
+                    cudaGetErrorString(e));
+    }
+    return ZNN_OK;
+}
+
+int znn_free(void* ptr)
+{
+    if (!ptr) return ZNN_OK;
+    ZNN_CUDA_OK(cudaFree(ptr));
+    return ZNN_OK;
+}
+
+int znn_memset(void* ptr, int value, size_t bytes)
+{
+    if (bytes == 0) return ZNN_OK;
+    ZNN_CUDA_OK(cudaMemsetAsync(ptr, value, bytes, stream()));
+    return ZNN_OK;
+}
+
+int znn_memcpy_h2d(void* dst, const void* src, size_t bytes)
+{
+    if (bytes == 0) return ZNN_OK;
+    ZNN_CUDA_OK(cudaMemcpyAsync(dst, src, bytes, cudaMemcpyHostToDevice, stream()));
+    return ZNN_OK;
+}
+
+int znn_memcpy_d2h(void* dst, const void* src, size_t bytes)
+{
+    if (bytes == 0) return ZNN_OK;
+    ZNN_CUDA_OK(cudaMemcpyAsync(dst, src, bytes, cudaMemcpyDeviceToHost, stream()));
+    ZNN_CUDA_OK(cudaStreamSynchronize(stream()));
+    return ZNN_OK;
+}
+
+int znn_memcpy_d2d(void* dst, const void* src, size_t bytes)
+{
+    if (bytes == 0) return ZNN_OK;
+    ZNN_CUDA_OK(cudaMemcpyAsync(dst, src, bytes, cudaMemcpyDeviceToDevice, stream()));
+    return ZNN_OK;
+}
+
+int znn_last_error(char* buf, size_t buflen)
+{
+    ZNN_REQUIRE(buf && buflen > 0, "buf is NULL");
+    strncpy(buf, t_err, buflen - 1);
+    buf[buflen - 1] = 0;
+    return ZNN_OK;
+}
+
+int znn_device_status(int* status, int clear)
+{
+    ZNN_REQUIRE(status, "status is NULL");
+    int* w = device_status_word();
+    if (!w) return fail(ZNN_ERR_CUDA, "no device state");
+    ZNN_CUDA_OK(cudaStreamSynchronize(stream()));
+    ZNN_CUDA_OK(cudaMemcpy(status, w, sizeof(int), cudaMemcpyDeviceToHost));
+    if (clear && *status) ZNN_CUDA_OK(cudaMemset(w, 0, sizeof(int)));
+    return ZNN_OK;
+}
+
+int znn_gemm_workspace_reserve(size_t bytes)
+{
+    if (!workspace(bytes)) return fail(ZNN_ERR_NOMEM, "could not reserve %zu bytes of GEMM scratch", bytes);
+    return ZNN_OK;
+}
+
+}  // extern "C"

@@ -1,0 +1,427 @@
+"""Host-array front end of the C ABI: every function copies its numpy inputs to
+the device, makes ONE call through libznn_cuda.so, and copies the result back.
+
+The names and argument meaning mirror the reference's operator arms
+(src/autodiff.zig Op.forward / Op.backward), so parity tests read like the
+reference's own tests.  Backward functions accumulate into the gradient arrays
+passed in (a None gradient = requires_grad false), as the reference does.
+"""
+import ctypes as C
+
+import numpy as np
+
+from ._lib import lib
+
+ROW_MAJOR, NO_TRANS, TRANS = 101, 111, 112
+
+_inited = {}
+
+
+def init(device=0):
+    """Select the device for this thread and create the per-device state."""
+    lib().call("znn_init", device)
+    _inited[device] = True
+
+
+def _ensure():
+    if not _inited:
+        init(0)
+
+
+class DevBuf:
+    """A device allocation owned by Python (znn_malloc / znn_free)."""
+
+    def __init__(self, nbytes):
+        self.nbytes = int(nbytes)
+        p = C.c_void_p()
+        lib().call("znn_malloc", C.byref(p), self.nbytes)
+        self.ptr = p.value if self.nbytes else None
+
+    @classmethod
+    def from_host(cls, arr):
+        arr = np.ascontiguousarray(arr)
+        b = cls(arr.nbytes)
+        if arr.nbytes:
+            lib().call("znn_memcpy_h2d", b.ptr, arr.ctypes.data, arr.nbytes)
+            lib().call("znn_sync")  # arr may be a temporary
+        return b
+
+    def to_host(self, shape, dtype=np.float32):
+        out = np.empty(shape, dtype)
+        if out.nbytes:
+            lib().call("znn_memcpy_d2h", out.ctypes.data, self.ptr, out.nbytes)
+        return out
+
+    def into(self, arr):
+        if arr.nbytes:
+            lib().call("znn_memcpy_d2h", arr.ctypes.data, self.ptr, arr.nbytes)
+
+    def free(self):
+        if self.ptr:
+            lib().call("znn_free", self.ptr)
+            self.ptr = None
+
+    def __del__(self):
+        try:
+            self.free()
+        except Exception:
+            pass
+
+
+def _up(a, dtype=np.float32):
+    if a is None:
+        return None
+    return DevBuf.from_host(np.ascontiguousarray(a, dtype=dtype))
+
+
+def _ptr(b):
+    return b.ptr if b is not None else None
+
+
+def _f(a):
+    return np.ascontiguousarray(a, dtype=np.float32)
+
+
+def check_device_status():
+    st = C.c_int(0)
+    lib().call("znn_device_status", C.byref(st), 1)
+    if st.value:
+        raise RuntimeError(f"device status word = {st.value}: a bounded device-side wait expired")
+
+
+def set_gemm_path(path):
+    lib().call("znn_gemm_set_path", int(path))
+
+
+def last_gemm_path():
+    return lib().dll.znn_gemm_last_path()
+
+
+def sgemm(ta, tb, M, N, K, alpha, A, lda, B, ldb, beta, Cm, ldc):
+    """cblas_sgemm on host arrays (row-major). Cm is updated in place and returned."""
+    _ensure()
+    dA, dB, dC = _up(A), _up(B), _up(Cm)
+    lib().call("znn_sgemm", ROW_MAJOR, ta, tb, M, N, K, alpha, dA.ptr, lda, dB.ptr, ldb, beta, dC.ptr, ldc)
+    check_device_status()
+    dC.into(Cm)
+    return Cm
+
+
+def sgemm_batched(ta, tb, M, N, K, alpha, A, lda, sa, B, ldb, sb, beta, Cm, ldc, sc, batch):
+    _ensure()
+    dA, dB, dC = _up(A), _up(B), _up(Cm)
+    lib().call("znn_sgemm_batched_strided", ta, tb, M, N, K, alpha, dA.ptr, lda, sa, dB.ptr, ldb, sb, beta,
+               dC.ptr, ldc, sc, batch)
+    check_device_status()
+    dC.into(Cm)
+    return Cm
+
+
+def matmul_fwd(A, B):
+    A, B = _f(A), _f(B)
+    M, K = A.shape
+    N = B.shape[1]
+    out = np.zeros((M, N), np.float32)
+    return sgemm(NO_TRANS, NO_TRANS, M, N, K, 1.0, A, K, B, N, 0.0, out, N)
+
+
+def matmul_bwd(A, B, dC, dA=None, dB=None):
+    M, K = A.shape
+    N = B.shape[1]
+    if dA is not None:
+        sgemm(NO_TRANS, TRANS, M, K, N, 1.0, dC, N, B, N, 1.0, dA, K)
+    if dB is not None:
+        sgemm(TRANS, NO_TRANS, K, N, M, 1.0, A, K, dC, N, 1.0, dB, N)
+
+
+def batch_matmul_fwd(A, B):
+    A, B = _f(A), _f(B)
+    M, K = A.shape[-2:]
+    N = B.shape[-1]
+    nb = int(np.prod(A.shape[:-2]))
+    out = np.zeros(A.shape[:-2] + (M, N), np.float32)
+    return sgemm_batched(NO_TRANS, NO_TRANS, M, N, K, 1.0, A, K, M * K, B, N, K * N, 0.0, out, N, M * N, nb)
+
+
+def batch_matmul_bwd(A, B, dC, dA=None, dB=None):
+    M, K = A.shape[-2:]
+    N = B.shape[-1]
+    nb = int(np.prod(A.shape[:-2]))
+    if dA is not None:
+        sgemm_batched(NO_TRANS, TRANS, M, K, N, 1.0, dC, N, M * N, B, N, K * N, 1.0, dA, K, M * K, nb)
+    if dB is not None:
+        sgemm_batched(TRANS, NO_TRANS, K, N, M, 1.0, A, K, M * K, dC, N, M * N, 1.0, dB, N, K * N, nb)
+
+
+def add_bias_fwd(A, bias):
+    _ensure()
+    A, bias = _f(A), _f(bias)
+    dA, db = _up(A), _up(bias)
+    dC = DevBuf(A.nbytes)
+    lib().call("znn_add_bias_fwd", dA.ptr, db.ptr, dC.ptr, A.shape[0], A.shape[1])
+    return dC.to_host(A.shape)
+
+
+def add_bias_bwd(dC, dA=None, dbias=None):
+    _ensure()
+    d_dC, d_dA, d_db = _up(dC), _up(dA), _up(dbias)
+    lib().call("znn_add_bias_bwd", d_dC.ptr, _ptr(d_dA), _ptr(d_db), dC.shape[0], dC.shape[1])
+    if dA is not None:
+        d_dA.into(dA)
+    if dbias is not None:
+        d_db.into(dbias)
+
+
+def _unary_fwd(name, A):
+    _ensure()
+    A = _f(A)
+    dA = _up(A)
+    dC = DevBuf(A.nbytes)
+    lib().call(name, dA.ptr, dC.ptr, A.size)
+    return dC.to_host(A.shape)
+
+
+def _unary_bwd(name, A, dC, dA):
+    _ensure()
+    a, g, o = _up(A), _up(dC), _up(dA)
+    lib().call(name, a.ptr, g.ptr, o.ptr, A.size)
+    o.into(dA)
+
+
+def relu_fwd(A):
+    return _unary_fwd("znn_relu_fwd", A)
+
+
+def gelu_fwd(A):
+    return _unary_fwd("znn_gelu_fwd", A)
+
+
+def relu_bwd(A, dC, dA):
+    _unary_bwd("znn_relu_bwd", A, dC, dA)
+
+
+def gelu_bwd(A, dC, dA):
+    _unary_bwd("znn_gelu_bwd", A, dC, dA)
+
+
+def softmax_xent_fwd(logits, targets, u8=False):
+    _ensure()
+    logits = _f(logits)
+    M, N = logits.shape
+    dl = _up(logits)
+    dt = _up(targets, np.uint8 if u8 else np.int32)
+    dp, dloss = DevBuf(logits.nbytes), DevBuf(4)
+    lib().call("znn_softmax_xent_fwd_u8" if u8 else "znn_softmax_xent_fwd", dl.ptr, dt.ptr, dp.ptr, dloss.ptr, M, N)
+    return dloss.to_host((1,)), dp.to_host((M, N))
+
+
+def softmax_xent_bwd(probs, targets, dlogits, u8=False):
+    _ensure()
+    M, N = probs.shape
+    dp, dt, dg = _up(probs), _up(targets, np.uint8 if u8 else np.int32), _up(dlogits)
+    lib().call("znn_softmax_xent_bwd_u8" if u8 else "znn_softmax_xent_bwd", dp.ptr, dt.ptr, dg.ptr, M, N)
+    dg.into(dlogits)
+
+
+def softmax_fwd(A):
+    _ensure()
+    A = _f(A)
+    D = A.shape[-1]
+    dA, dC = _up(A), DevBuf(A.nbytes)
+    lib().call("znn_softmax_fwd", dA.ptr, dC.ptr, A.size // D, D)
+    return dC.to_host(A.shape)
+
+
+def softmax_bwd(Y, dY, dA):
+    _ensure()
+    D = Y.shape[-1]
+    y, g, o = _up(Y), _up(dY), _up(dA)
+    lib().call("znn_softmax_bwd", y.ptr, g.ptr, o.ptr, Y.size // D, D)
+    o.into(dA)
+
+
+def causal_softmax_fwd(S, scale):
+    _ensure()
+    S = _f(S)
+    T = S.shape[-1]
+    dS, dP = _up(S), DevBuf(S.nbytes)
+    lib().call("znn_causal_softmax_fwd", dS.ptr, scale, dP.ptr, S.size // (T * T), T)
+    return dP.to_host(S.shape)
+
+
+def causal_softmax_bwd(P, dP, scale, dS):
+    _ensure()
+    T = P.shape[-1]
+    p, g, o = _up(P), _up(dP), _up(dS)
+    lib().call("znn_causal_softmax_bwd", p.ptr, g.ptr, scale, o.ptr, P.size // (T * T), T)
+    o.into(dS)
+
+
+def rmsnorm_fwd(X, G, eps):
+    _ensure()
+    X, G = _f(X), _f(G)
+    D = X.shape[-1]
+    x, g, y = _up(X), _up(G), DevBuf(X.nbytes)
+    lib().call("znn_rmsnorm_fwd", x.ptr, g.ptr, eps, y.ptr, X.size // D, D)
+    return y.to_host(X.shape)
+
+
+def rmsnorm_bwd(X, G, dY, eps, dX=None, dG=None):
+    _ensure()
+    D = X.shape[-1]
+    x, g, dy, dx, dg = _up(X), _up(G), _up(dY), _up(dX), _up(dG)
+    lib().call("znn_rmsnorm_bwd", x.ptr, g.ptr, dy.ptr, eps, _ptr(dx), _ptr(dg), X.size // D, D)
+    if dX is not None:
+        dx.into(dX)
+    if dG is not None:
+        dg.into(dG)
+
+
+def layernorm_fwd(X, G, Bt, eps):
+    _ensure()
+    X, G, Bt = _f(X), _f(G), _f(Bt)
+    D = X.shape[-1]
+    x, g, b, y = _up(X), _up(G), _up(Bt), DevBuf(X.nbytes)
+    lib().call("znn_layernorm_fwd", x.ptr, g.ptr, b.ptr, eps, y.ptr, X.size // D, D)
+    return y.to_host(X.shape)
+
+
+def layernorm_bwd(X, G, dY, eps, dX=None, dG=None, dB=None):
+    _ensure()
+    D = X.shape[-1]
+    x, g, dy, dx, dg, db = _up(X), _up(G), _up(dY), _up(dX), _up(dG), _up(dB)
+    lib().call("znn_layernorm_bwd", x.ptr, g.ptr, dy.ptr, eps, _ptr(dx), _ptr(dg), _ptr(db), X.size // D, D)
+    for host, dev in ((dX, dx), (dG, dg), (dB, db)):
+        if host is not None:
+            dev.into(host)
+
+
+def conv2d_fwd(X, W, bias=None, pad=0):
+    _ensure()
+    X, W = _f(X), _f(W)
+    N, Ci, H, Wd = X.shape
+    Co, _, KH, KW = W.shape
+    Ho, Wo = H + 2 * pad - KH + 1, Wd + 2 * pad - KW + 1
+    x, w, b = _up(X), _up(W), _up(bias)
+    y = DevBuf(N * Co * Ho * Wo * 4)
+    lib().call("znn_conv2d_fwd", x.ptr, w.ptr, _ptr(b), y.ptr, N, Ci, H, Wd, Co, KH, KW, pad)
+    return y.to_host((N, Co, Ho, Wo))
+
+
+def conv2d_bwd(X, W, dY, dX=None, dW=None, dbias=None, pad=0):
+    _ensure()
+    N, Ci, H, Wd = X.shape
+    Co, _, KH, KW = W.shape
+    x, w, dy, dx, dw, db = _up(X), _up(W), _up(dY), _up(dX), _up(dW), _up(dbias)
+    lib().call("znn_conv2d_bwd", x.ptr, w.ptr, dy.ptr, _ptr(dx), _ptr(dw), _ptr(db), N, Ci, H, Wd, Co, KH, KW, pad)
+    for host, dev in ((dX, dx), (dW, dw), (dbias, db)):
+        if host is not None:
+            dev.into(host)
+
+
+def maxpool2d_fwd(X, pool, stride, want_idx=False):
+    _ensure()
+    X = _f(X)
+    N, Cc, H, W = X.shape
+    Ho, Wo = H // stride, W // stride
+    x = _up(X)
+    y = DevBuf(N * Cc * Ho * Wo * 4)
+    idx = DevBuf(N * Cc * Ho * Wo * 4) if want_idx else None
+    lib().call("znn_maxpool2d_fwd", x.ptr, y.ptr, _ptr(idx), N, Cc, H, W, pool, stride)
+    out = y.to_host((N, Cc, Ho, Wo))
+    return (out, idx.to_host((N, Cc, Ho, Wo), np.int32)) if want_idx else out
+
+
+def maxpool2d_bwd(X, dY, dX, pool, stride):
+    _ensure()
+    N, Cc, H, W = X.shape
+    x, dy, dx = _up(X), _up(dY), _up(dX)
+    lib().call("znn_maxpool2d_bwd", x.ptr, dy.ptr, dx.ptr, N, Cc, H, W, pool, stride)
+    dx.into(dX)
+
+
+def embedding_fwd(W, ids):
+    _ensure()
+    W, ids = _f(W), _f(ids)
+    V, D = W.shape
+    w, i = _up(W), _up(ids)
+    y = DevBuf(ids.size * D * 4)
+    lib().call("znn_embedding_fwd", w.ptr, i.ptr, y.ptr, ids.size, D, V)
+    return y.to_host(ids.shape + (D,))
+
+
+def embedding_bwd(ids, dY, dW):
+    _ensure()
+    ids = _f(ids)
+    V, D = dW.shape
+    i, dy, dw = _up(ids), _up(dY), _up(dW)
+    lib().call("znn_embedding_bwd", i.ptr, dy.ptr, dw.ptr, ids.size, D, V)
+    dw.into(dW)
+
+
+def transpose_fwd(A, d0, d1):
+    _ensure()
+    A = _f(A)
+    dims = np.array(A.shape, dtype=np.int64)
+    oshape = list(A.shape)
+    oshape[d0], oshape[d1] = oshape[d1], oshape[d0]
+    a, c = _up(A), DevBuf(A.nbytes)
+    lib().call("znn_transpose_fwd", a.ptr, c.ptr, dims.ctypes.data, A.ndim, d0, d1)
+    return c.to_host(tuple(oshape))
+
+
+def transpose_bwd(dC, dA, d0, d1):
+    _ensure()
+    dims = np.array(dA.shape, dtype=np.int64)
+    g, o = _up(dC), _up(dA)
+    lib().call("znn_transpose_bwd", g.ptr, o.ptr, dims.ctypes.data, dA.ndim, d0, d1)
+    o.into(dA)
+
+
+def add_fwd(A, B):
+    _ensure()
+    A, B = _f(A), _f(B)
+    a, b, c = _up(A), _up(B), DevBuf(A.nbytes)
+    lib().call("znn_add_fwd", a.ptr, b.ptr, c.ptr, A.size)
+    return c.to_host(A.shape)
+
+
+def accumulate(src, dst):
+    _ensure()
+    s, d = _up(src), _up(dst)
+    lib().call("znn_accumulate", s.ptr, d.ptr, dst.size)
+    d.into(dst)
+
+
+def mul_scalar_fwd(A, v):
+    _ensure()
+    A = _f(A)
+    a, c = _up(A), DevBuf(A.nbytes)
+    lib().call("znn_mul_scalar_fwd", a.ptr, v, c.ptr, A.size)
+    return c.to_host(A.shape)
+
+
+def mul_scalar_bwd(dC, v, dA):
+    _ensure()
+    g, o = _up(dC), _up(dA)
+    lib().call("znn_mul_scalar_bwd", g.ptr, v, o.ptr, dA.size)
+    o.into(dA)
+
+
+def argmax(A, dim):
+    _ensure()
+    A = _f(A)
+    M, N = A.shape
+    n_out = M if dim == 1 else N
+    a, o = _up(A), DevBuf(n_out * 4)
+    lib().call("znn_argmax", a.ptr, o.ptr, M, N, dim)
+    return o.to_host((n_out,))
+
+
+def sgd_step(w, g, v, lr, momentum, grad_scale=1.0):
+    _ensure()
+    dw, dg, dv = _up(w), _up(g), _up(v)
+    lib().call("znn_sgd_step", dw.ptr, dg.ptr, _ptr(dv), lr, momentum, grad_scale, w.size)
+    dw.into(w)
+    if v is not None:
+        dv.into(v)
