@@ -1,0 +1,329 @@
+#!/usr/bin/env python
+"""Benchmark of the znn MatMul hot path on B200.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--n 8192] [--impl reference]
+
+A "step" is one pass of the reference's MatMul operator over one batch of
+synthetic N(0,1) operands: forward C = A.B (src/autodiff.zig:110-133) and the two
+backward products dA += dC.B^T, dB += A^T.dC (:593-641), all through znn_sgemm,
+the cblas_sgemm boundary.  The metric is fp32-accurate GEMM TFLOP/s = 3*2*n^3 / t.
+
+N > 1 (launched by torchrun, one rank per GPU): the sweep has no exchange step,
+so every rank runs an independent replica ("replicas only"); the value is the sum
+over ranks divided by the slowest rank's time.
+
+--impl reference times the reference's CPU path for the same step: the oracle's
+restatement of the MatMul arms with cblas_sgemm bound to the host OpenBLAS (all
+host threads), on a bounded sample size.
+"""
+import argparse
+import ctypes as C
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+METRIC = "fp32_accurate_gemm_tflops"
+UNIT = "TFLOP/s"
+
+
+def read_peaks():
+    p = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(p):
+        with open(p) as fh:
+            d = json.load(fh)
+        return d, "measured"
+    return {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0}, "fallback"
+
+
+class ClockSampler:
+    """Samples nvidia-smi clocks / throttle reasons while the timed region runs."""
+
+    FIELDS = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
+              "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+              "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu_index):
+        self.gpu = gpu_index
+        self.proc = None
+        self.lines = []
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", "-i", str(self.gpu), f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits",
+                 "-lms", "100"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.thread = threading.Thread(target=self._pump, daemon=True)
+            self.thread.start()
+        except OSError:
+            self.proc = None
+
+    def _pump(self):
+        for line in self.proc.stdout:
+            self.lines.append(line.strip())
+
+    def stop(self):
+        if not self.proc:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+        sm, mx, power, reasons = [], [], [], set()
+        for ln in self.lines:
+            f = [x.strip() for x in ln.split(",")]
+            if len(f) < 9:
+                continue
+            try:
+                sm.append(float(f[1]))
+                mx.append(float(f[2]))
+                power.append(float(f[3]))
+            except ValueError:
+                continue
+            for name, val in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"), f[5:9]):
+                if val.lower().startswith("active"):
+                    reasons.add(name)
+        return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": max(mx) if mx else None,
+                "power_w_max": max(power) if power else None, "samples": len(sm), "reasons": sorted(reasons)}
+
+
+# --------------------------------------------------------------------------- CPU side
+def cpu_step(zo, A, B, dC, Cm, dA, dB, n):
+    zo.matmul_fwd_into = None
+    zo.sgemm(111, 111, n, n, n, 1.0, A, n, B, n, 0.0, Cm, n)
+    zo.sgemm(111, 112, n, n, n, 1.0, dC, n, B, n, 1.0, dA, n)
+    zo.sgemm(112, 111, n, n, n, 1.0, A, n, dC, n, 1.0, dB, n)
+
+
+def cpu_measure(steps, warmup, budget_s=25.0, with_naive=True):
+    """Times the oracle's MatMul step on the host cores (bounded sample)."""
+    import numpy as np
+    from oracle import zo
+    zo.build()
+    ptr, info = zo.find_host_cblas()
+    out = {"kind": "port", "unit": UNIT}
+    r = np.random.default_rng(0)
+    naive = None
+    if with_naive:
+        # the reference's Linux code path: the naive loops of src/cblas.zig:37-96, one thread
+        m = 768
+        A, B = r.standard_normal((m, m), np.float32), r.standard_normal((m, m), np.float32)
+        Cm = np.zeros((m, m), np.float32)
+        zo.bind_sgemm(None)
+        t0 = time.perf_counter()
+        zo.sgemm(111, 111, m, m, m, 1.0, A, m, B, m, 0.0, Cm, m)
+        naive = 2.0 * m ** 3 / (time.perf_counter() - t0) / 1e12
+        out["naive_fallback_1thread_tflops"] = naive
+        out["naive_sample"] = f"{m}^3 forward product, 1 thread (src/cblas.zig:37-96 restated)"
+    if ptr is None:
+        out.update({"value": naive, "cores": 1, "sample": out.get("naive_sample", ""), "blas": "none found"})
+        return out
+    zo.bind_sgemm(ptr)
+    cores = info.get("threads") or os.cpu_count()
+    # pick a size whose step fits the budget: probe at 1024
+    m = 1024
+    A, B = r.standard_normal((m, m), np.float32), r.standard_normal((m, m), np.float32)
+    Cm = np.zeros((m, m), np.float32)
+    zo.sgemm(111, 111, m, m, m, 1.0, A, m, B, m, 0.0, Cm, m)
+    t0 = time.perf_counter()
+    zo.sgemm(111, 111, m, m, m, 1.0, A, m, B, m, 0.0, Cm, m)
+    rate = 2.0 * m ** 3 / (time.perf_counter() - t0)
+    n = 8192
+    total_steps = steps + warmup
+    while n > 512 and 6.0 * n ** 3 * total_steps / rate > budget_s:
+        n //= 2
+    A, B, dC = (r.standard_normal((n, n), np.float32) for _ in range(3))
+    Cm, dA, dB = (np.zeros((n, n), np.float32) for _ in range(3))
+    for _ in range(warmup):
+        cpu_step(zo, A, B, dC, Cm, dA, dB, n)
+    t0 = time.perf_counter()
+    for _ in range(steps):
+        cpu_step(zo, A, B, dC, Cm, dA, dB, n)
+    dt = time.perf_counter() - t0
+    zo.bind_sgemm(None)
+    out.update({"value": 6.0 * n ** 3 * steps / dt / 1e12, "cores": int(cores), "ms_per_step": dt / steps * 1e3,
+                "sample": f"{steps} steps of fwd+dA+dB at n={n} (bounded sample of the n=8192 workload), "
+                          f"cblas_sgemm = {os.path.basename(info['path'])} with {cores} threads",
+                "n": n})
+    return out
+
+
+def run_reference(args):
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return 0
+    steps, warmup = max(1, args.steps), max(0, args.warmup)
+    t_wall = time.perf_counter()
+    res = cpu_measure(steps, warmup, budget_s=60.0, with_naive=True)
+    line = {
+        "impl": "reference", "metric": METRIC, "value": res["value"], "unit": UNIT, "n_gpus": args.gpus,
+        "steps": steps, "warmup": warmup, "ms_per_step": res.get("ms_per_step"), "higher_is_better": True,
+        "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": {"workload": f"matmul_sweep_square_{args.n}_fwd_dA_dB", "sample_n": res.get("n"),
+                   "note": "CPU path of the reference restated in C (oracle), cblas_sgemm bound to host OpenBLAS"},
+        "cpu_baseline": {k: res[k] for k in res if k in ("value", "unit", "cores", "kind", "sample",
+                                                         "naive_fallback_1thread_tflops", "naive_sample")},
+        "e2e": {"value": res["value"], "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0, "wall_s": time.perf_counter() - t_wall,
+    }
+    print(json.dumps(line), flush=True)
+    return 0
+
+
+# --------------------------------------------------------------------------- GPU side
+def run_gpu(args):
+    import torch
+    import torch.distributed as dist
+    from znn_b200._lib import lib
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device: the znn_b200 hot path has no CPU fallback")
+    torch.cuda.set_device(local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+    L = lib()
+    L.call("znn_init", local)
+    stream = torch.cuda.current_stream()
+    L.call("znn_set_stream", stream.cuda_stream)
+
+    n = args.n
+    steps, warmup = max(1, args.steps), max(3, args.warmup)
+    g = torch.Generator(device="cuda").manual_seed(1234 + rank)
+    A = torch.randn((n, n), device="cuda", generator=g, dtype=torch.float32)
+    B = torch.randn((n, n), device="cuda", generator=g, dtype=torch.float32)
+    dC = torch.randn((n, n), device="cuda", generator=g, dtype=torch.float32)
+    Cm = torch.empty((n, n), device="cuda", dtype=torch.float32)
+    dA = torch.zeros((n, n), device="cuda", dtype=torch.float32)
+    dB = torch.zeros((n, n), device="cuda", dtype=torch.float32)
+    L.call("znn_gemm_workspace_reserve", 4 * 2 * n * n * 4 + (1 << 20))
+
+    def step():
+        L.call("znn_sgemm", 101, 111, 111, n, n, n, 1.0, A.data_ptr(), n, B.data_ptr(), n, 0.0, Cm.data_ptr(), n)
+        L.call("znn_sgemm", 101, 111, 112, n, n, n, 1.0, dC.data_ptr(), n, B.data_ptr(), n, 1.0, dA.data_ptr(), n)
+        L.call("znn_sgemm", 101, 112, 111, n, n, n, 1.0, A.data_ptr(), n, dC.data_ptr(), n, 1.0, dB.data_ptr(), n)
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    # ---- device-resident timing ----
+    for _ in range(warmup):
+        step()
+    barrier()
+    cnt = C.c_longlong(0)
+    L.call("znn_launch_count", C.byref(cnt), 1)
+    L.call("znn_gemm_profile", 1)
+    sampler = ClockSampler(local)
+    if rank == 0:
+        sampler.start()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record(stream)
+    for _ in range(steps):
+        step()
+    e1.record(stream)
+    barrier()
+    ms = e0.elapsed_time(e1)
+    clocks = sampler.stop() if rank == 0 else None
+    L.call("znn_launch_count", C.byref(cnt), 1)
+    launches = cnt.value
+    kms, kl, kfl = C.c_double(0), C.c_longlong(0), C.c_double(0)
+    L.call("znn_gemm_profile_read", C.byref(kms), C.byref(kl), C.byref(kfl))
+    L.call("znn_gemm_profile", 0)
+    st = C.c_int(0)
+    L.call("znn_device_status", C.byref(st), 1)
+    if st.value:
+        raise SystemExit(f"device status word {st.value}: a bounded device-side wait expired; the run is invalid")
+    t = torch.tensor([ms], device="cuda", dtype=torch.float64)
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    ms_max = float(t.item())
+    flops_step = 6.0 * n ** 3
+    value = world * flops_step * steps / (ms_max * 1e-3) / 1e12
+
+    # ---- end to end: host buffers in, host buffers out, through the same C ABI ----
+    hA, hB, hdC = (torch.empty((n, n), dtype=torch.float32).pin_memory() for _ in range(3))
+    hC, hdA, hdB = (torch.empty((n, n), dtype=torch.float32).pin_memory() for _ in range(3))
+    hA.copy_(A)
+    hB.copy_(B)
+    hdC.copy_(dC)
+    nbytes = n * n * 4
+
+    def e2e_step():
+        L.call("znn_memcpy_h2d", A.data_ptr(), hA.data_ptr(), nbytes)
+        L.call("znn_memcpy_h2d", B.data_ptr(), hB.data_ptr(), nbytes)
+        L.call("znn_memcpy_h2d", dC.data_ptr(), hdC.data_ptr(), nbytes)
+        step()
+        L.call("znn_memcpy_d2h", hC.data_ptr(), Cm.data_ptr(), nbytes)
+        L.call("znn_memcpy_d2h", hdA.data_ptr(), dA.data_ptr(), nbytes)
+        L.call("znn_memcpy_d2h", hdB.data_ptr(), dB.data_ptr(), nbytes)
+
+    e2e_step()
+    barrier()
+    e2e_steps = min(steps, 5)
+    e0.record(stream)
+    for _ in range(e2e_steps):
+        e2e_step()
+    e1.record(stream)
+    barrier()
+    t = torch.tensor([e0.elapsed_time(e1)], device="cuda", dtype=torch.float64)
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    e2e_value = world * flops_step * e2e_steps / (float(t.item()) * 1e-3) / 1e12
+
+    if rank == 0:
+        peaks, peaks_kind = read_peaks()
+        # 3xTF32 ceiling: the TF32 dense rate is half the bf16 rate on this part, and
+        # each algorithmic flop costs three tensor-core passes.
+        peak = peaks["bf16_tflops"] / 2.0 / 3.0
+        achieved = (kfl.value / (kms.value * 1e-3) / 1e12) if kms.value > 0 else None
+        line = {
+            "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": steps, "warmup": warmup,
+            "ms_per_step": ms_max / steps, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+            "dtype": "f32 (3xTF32 split, fp32 accumulate)", "data": "synthetic",
+            "config": {"workload": f"matmul_sweep_square_{n}_fwd_dA_dB", "M": n, "N": n, "K": n,
+                       "flops_per_step": flops_step, "l2": "inputs (3 x %d MB) exceed the 126 MB L2" % (nbytes >> 20),
+                       "parallelism": "replicas only" if world > 1 else "single GPU"},
+            "roofline": {"bound": "tensor", "achieved": achieved, "peak": peak, "unit": UNIT,
+                         "frac": (achieved / peak) if achieved else None, "traffic": None,
+                         "kernel": "gemm3x_tf32_kernel<256,2>", "launches": kl.value,
+                         "avg_launch_ms": (kms.value / kl.value) if kl.value else None,
+                         "peak_source": f"{peaks_kind}: bf16 burst {peaks['bf16_tflops']} TF/s / 2 (tf32) / 3 (passes)"},
+            "e2e": {"value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": 3 * nbytes, "d2h_bytes_per_step": 3 * nbytes,
+                    "steps": e2e_steps},
+            "gpu_launches": launches, "clocks": clocks,
+        }
+        if not args.no_cpu_baseline and world == 1:
+            line["cpu_baseline"] = {k: v for k, v in cpu_measure(2, 1, budget_s=20.0).items() if k != "n"}
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.destroy_process_group()
+    return 0
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=10)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--n", type=int, default=8192)
+    ap.add_argument("--impl", default="znn_b200", choices=["znn_b200", "reference"])
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    args = ap.parse_args()
+    if args.impl == "reference":
+        return run_reference(args)
+    return run_gpu(args)
+
+
+if __name__ == "__main__":
+    sys.exit(main())

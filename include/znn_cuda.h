@@ -59,6 +59,7 @@ int znn_memcpy_d2d(void* dst, const void* src, size_t bytes);
 int znn_last_error(char* buf, size_t buflen);
 int znn_device_status(int* status, int clear); /* syncs, reads (and clears) the device status word */
 int znn_gemm_workspace_reserve(size_t bytes);  /* pre-size the GEMM scratch (avoids cudaMalloc later) */
+int znn_launch_count(long long* count, int reset); /* kernels launched by this host thread so far */
 
 /* ---- GEMM: replaces cblas_sgemm (src/cblas.zig:11-96; prototype :17-34) at its 8 call
  *      sites (src/tensor.zig:181,721; src/autodiff.zig:117,513,604,624,1143,1163).
@@ -75,6 +76,16 @@ int znn_sgemm_batched_strided(int trans_a, int trans_b, int M, int N, int K, flo
 /* path: 0 = automatic, 1 = fp32 FMA kernel, 2 = tcgen05 one CTA per tile, 3 = tcgen05 CTA pairs */
 int znn_gemm_set_path(int path);
 int znn_gemm_last_path(void);
+/* Number of contraction elements the tensor-core paths accumulate inside tensor memory before
+ * the partial sum is promoted to an fp32 register sum (multiple of 32; default 256).  The
+ * tensor core's accumulator truncates, so longer chunks trade accuracy for fewer promotions. */
+int znn_gemm_set_chunk(int k_elements);
+/* Measurement aid: with profiling on, every tensor-core GEMM kernel launch (not its split
+ * pre-pass) is bracketed by CUDA events on the launching stream; znn_gemm_profile_read waits
+ * for them and returns the summed kernel time, the launch count and the algorithmic
+ * floating-point operations (2*M*N*K*batch) of those launches, then clears the record. */
+int znn_gemm_profile(int enable);
+int znn_gemm_profile_read(double* kernel_ms, long long* launches, double* flops);
 
 /* ---- row-wise operators: the arms of Op.forward (src/autodiff.zig:107-575) and
  *      Op.backward (:579-1231) ---- */

@@ -16,7 +16,8 @@ _CTYPES = {
     "void*": C.c_void_p, "const void*": C.c_void_p, "void**": C.POINTER(C.c_void_p),
     "float*": C.c_void_p, "const float*": C.c_void_p, "int*": C.POINTER(C.c_int),
     "int32_t*": C.c_void_p, "const int32_t*": C.c_void_p, "const uint8_t*": C.c_void_p,
-    "const int64_t*": C.c_void_p, "char*": C.c_char_p,
+    "const int64_t*": C.c_void_p, "char*": C.c_char_p, "long long*": C.POINTER(C.c_longlong),
+    "double*": C.POINTER(C.c_double),
 }
 
 

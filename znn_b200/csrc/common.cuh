@@ -24,6 +24,9 @@ void* workspace(size_t bytes);
 
 int sm_count();
 
+// Kernel-launch counter of the calling host thread (read by znn_launch_count).
+void count_launch();
+
 #define ZNN_CUDA_OK(expr)                                                              \
     do {                                                                               \
         cudaError_t _e = (expr);                                                       \
@@ -38,6 +41,7 @@ int sm_count();
         if (_e != cudaSuccess)                                                         \
             return ::znn::fail(ZNN_ERR_CUDA, "launch of %s failed: %s", name,          \
                                cudaGetErrorString(_e));                                \
+        ::znn::count_launch();                                                         \
     } while (0)
 
 #define ZNN_REQUIRE(cond, ...)                                                         \

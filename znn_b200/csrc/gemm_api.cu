@@ -9,6 +9,9 @@ namespace znn {
 int gemm_tc(int ta, int tb, int M, int N, int K, float alpha, const float* A, long long lda, long long stride_a,
             const float* B, long long ldb, long long stride_b, float beta, float* C, long long ldc,
             long long stride_c, int batch, int ctas);
+int tc_profile_enable(int enable);
+void tc_set_chunk_kblocks(int v);
+int tc_profile_read(double* kernel_ms, long long* launches, double* flops);
 
 // C = alpha * op(A) * op(B) + beta * C with fp32 FMAs, k ascending.
 // 64x64 output tile, 16-deep k slices, 256 threads, 4x4 outputs per thread.
@@ -168,5 +171,19 @@ int znn_gemm_set_path(int path)
 }
 
 int znn_gemm_last_path(void) { return t_last_path; }
+
+int znn_gemm_set_chunk(int k_elements)
+{
+    ZNN_REQUIRE(k_elements >= 32 && k_elements % 32 == 0, "chunk must be a positive multiple of 32");
+    tc_set_chunk_kblocks(k_elements / 32);
+    return ZNN_OK;
+}
+
+int znn_gemm_profile(int enable) { return tc_profile_enable(enable); }
+
+int znn_gemm_profile_read(double* kernel_ms, long long* launches, double* flops)
+{
+    return tc_profile_read(kernel_ms, launches, flops);
+}
 
 }  // extern "C"

@@ -214,6 +214,8 @@ __host__ __device__ constexpr uint32_t make_tf32_idesc(int mma_m, int mma_n)
 struct GemmTcParams {
     int M, N;            // output extent
     int k_blocks;        // padded K / 32
+    int k_real;          // the caller's K (for flop accounting only)
+    int chunk_kblocks;   // k-blocks accumulated inside tensor memory before promotion
     int tiles_m, tiles_n;
     float alpha, beta;
     float* C;
@@ -223,7 +225,8 @@ struct GemmTcParams {
 
 constexpr int kBK = 32;          // fp32 elements per k-block = one 128-byte swizzle row
 constexpr int kTileM = 128;      // rows of A per CTA
-constexpr int kThreads = 192;    // warp 0 TMA, warp 1 MMA + TMEM, warps 2..5 epilogue
+constexpr int kEpiWarps = 8;
+constexpr int kThreads = 64 + 32 * kEpiWarps;  // warp 0 TMA, warp 1 MMA + TMEM, warps 2..9 epilogue
 
 template <int BN, int CTAS>
 struct TcCfg {
@@ -233,9 +236,21 @@ struct TcCfg {
     static constexpr int kStageBytes = 2 * kABytes + 2 * kBBytes;
     static constexpr int kStages = (200 * 1024) / kStageBytes > 6 ? 6 : (200 * 1024) / kStageBytes;
     static constexpr int kSmemBytes = kStages * kStageBytes + 1024 /*align*/ + 256 /*barriers*/;
-    static constexpr int kTmemCols = BN < 32 ? 32 : BN;
+    static constexpr int kTmemCols = 2 * BN < 32 ? 32 : 2 * BN;  // two accumulator buffers
+    static constexpr int kColsPerThread = BN / 2;                // each epilogue warp owns a lane quarter x column half
 };
 
+__device__ __forceinline__ void mbar_arrive_remote(uint32_t cluster_addr)
+{
+    asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
+}
+
+// The tensor core adds into its fp32 accumulator with truncation, so the error of
+// a long accumulation grows linearly with K (measured: 7e-6 relative at K = 1024,
+// 5.7e-5 at K = 8192).  The k-loop is therefore cut into chunks of
+// `chunk_kblocks` k-blocks: each chunk accumulates in one of two tensor-memory
+// buffers, and the epilogue warps add finished chunks into fp32 registers with
+// round-to-nearest while the next chunk is being multiplied.
 template <int BN, int CTAS>
 __global__ void __launch_bounds__(kThreads, 1)
 gemm3x_tf32_kernel(const __grid_constant__ CUtensorMap tm_a_hi, const __grid_constant__ CUtensorMap tm_a_lo,
@@ -248,13 +263,15 @@ gemm3x_tf32_kernel(const __grid_constant__ CUtensorMap tm_a_hi, const __grid_con
     const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
     uint8_t* smem_gen = smem_raw + (smem_base - smem_u32(smem_raw));
     const uint32_t bar_base = smem_base + Cfg::kStages * Cfg::kStageBytes;
-    // barrier block: full[kStages], empty[kStages], accum, then the TMEM address
+    // barrier block: full[kStages], empty[kStages], acc_full[2], acc_empty[2], then two words
     auto full_bar = [&](int s) { return bar_base + 8u * s; };
     auto empty_bar = [&](int s) { return bar_base + 8u * (Cfg::kStages + s); };
-    const uint32_t accum_bar = bar_base + 8u * (2 * Cfg::kStages);
+    auto acc_full_bar = [&](int b) { return bar_base + 8u * (2 * Cfg::kStages + b); };
+    auto acc_empty_bar = [&](int b) { return bar_base + 8u * (2 * Cfg::kStages + 2 + b); };
+    constexpr int kWordOff = 8 * (2 * Cfg::kStages + 4);
     volatile uint32_t* tmem_slot =
-        reinterpret_cast<volatile uint32_t*>(smem_gen + Cfg::kStages * Cfg::kStageBytes + 8 * (2 * Cfg::kStages + 1));
-    const uint32_t tmem_slot_addr = bar_base + 8u * (2 * Cfg::kStages + 1);
+        reinterpret_cast<volatile uint32_t*>(smem_gen + Cfg::kStages * Cfg::kStageBytes + kWordOff);
+    const uint32_t tmem_slot_addr = bar_base + kWordOff;
     volatile uint32_t* abort_slot = tmem_slot + 1;
     const uint32_t abort_slot_addr = tmem_slot_addr + 4;
 
@@ -280,13 +297,18 @@ gemm3x_tf32_kernel(const __grid_constant__ CUtensorMap tm_a_hi, const __grid_con
     const int batch = blockIdx.z;
     const int row0 = (tile_m * CTAS + (int)cta_rank) * kTileM;  // first C / A row of this CTA
     const int col0 = tile_n * BN;
+    const int chunk = p.chunk_kblocks;
+    const int nchunks = (p.k_blocks + chunk - 1) / chunk;
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < Cfg::kStages; s++) {
             mbar_init(full_bar(s), 1);
             mbar_init(empty_bar(s), 1);
         }
-        mbar_init(accum_bar, 1);
+        for (int b = 0; b < 2; b++) {
+            mbar_init(acc_full_bar(b), 1);
+            mbar_init(acc_empty_bar(b), kEpiWarps * CTAS);  // every epilogue warp of the tile's CTAs
+        }
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
         // A failure recorded by an earlier CTA or kernel makes this one do nothing.
         // One thread decides for the whole CTA (pair), so the decision is uniform.
@@ -344,74 +366,108 @@ gemm3x_tf32_kernel(const __grid_constant__ CUtensorMap tm_a_hi, const __grid_con
         // ---------------- MMA issuer (leader CTA only in pair mode) ----------------
         if (lane == 0 && leader) {
             constexpr uint32_t idesc = make_tf32_idesc(kTileM * CTAS, BN);
-            for (int kb = 0; kb < p.k_blocks; kb++) {
-                const int s = kb % Cfg::kStages;
-                const uint32_t ph = (kb / Cfg::kStages) & 1;
-                if (!mbar_wait_bounded(full_bar(s), ph)) { ok = false; break; }
+            int kb = 0;
+            for (int c = 0; c < nchunks && ok; c++) {
+                const int buf = c & 1;
+                // the epilogue warps must have drained this buffer (two chunks ago)
+                if (!mbar_wait_bounded(acc_empty_bar(buf), ((c >> 1) & 1) ^ 1)) { ok = false; break; }
                 tc_fence_after();
-                const uint32_t st = smem_base + s * Cfg::kStageBytes;
-                const uint64_t a_hi = make_kmajor_sw128_desc(st);
-                const uint64_t a_lo = make_kmajor_sw128_desc(st + Cfg::kABytes);
-                const uint64_t b_hi = make_kmajor_sw128_desc(st + 2 * Cfg::kABytes);
-                const uint64_t b_lo = make_kmajor_sw128_desc(st + 2 * Cfg::kABytes + Cfg::kBBytes);
-                // small terms first, then the leading term
+                const uint32_t d_tmem = tmem_base + (uint32_t)(buf * BN);
+                const int kb_end = min(p.k_blocks, kb + chunk);
+                for (bool first = true; kb < kb_end; kb++) {
+                    const int s = kb % Cfg::kStages;
+                    const uint32_t ph = (kb / Cfg::kStages) & 1;
+                    if (!mbar_wait_bounded(full_bar(s), ph)) { ok = false; break; }
+                    tc_fence_after();
+                    const uint32_t st = smem_base + s * Cfg::kStageBytes;
+                    const uint64_t a_hi = make_kmajor_sw128_desc(st);
+                    const uint64_t a_lo = make_kmajor_sw128_desc(st + Cfg::kABytes);
+                    const uint64_t b_hi = make_kmajor_sw128_desc(st + 2 * Cfg::kABytes);
+                    const uint64_t b_lo = make_kmajor_sw128_desc(st + 2 * Cfg::kABytes + Cfg::kBBytes);
+                    // small terms first, then the leading term; 8 tf32 = 32 bytes = 2 sixteen-byte units per k step
 #pragma unroll
-                for (int k = 0; k < kBK / 8; k++)  // 8 tf32 = 32 bytes = 2 x 16-byte units
-                    umma_tf32<CTAS>(tmem_base, a_lo + 2 * k, b_hi + 2 * k, idesc, (kb | k) != 0);
+                    for (int k = 0; k < kBK / 8; k++)
+                        umma_tf32<CTAS>(d_tmem, a_lo + 2 * k, b_hi + 2 * k, idesc, (first && k == 0) ? 0u : 1u);
 #pragma unroll
-                for (int k = 0; k < kBK / 8; k++) umma_tf32<CTAS>(tmem_base, a_hi + 2 * k, b_lo + 2 * k, idesc, 1);
+                    for (int k = 0; k < kBK / 8; k++) umma_tf32<CTAS>(d_tmem, a_hi + 2 * k, b_lo + 2 * k, idesc, 1);
 #pragma unroll
-                for (int k = 0; k < kBK / 8; k++) umma_tf32<CTAS>(tmem_base, a_hi + 2 * k, b_hi + 2 * k, idesc, 1);
-                if (CTAS == 1) umma_commit_1cta(empty_bar(s)); else umma_commit_pair(empty_bar(s));
+                    for (int k = 0; k < kBK / 8; k++) umma_tf32<CTAS>(d_tmem, a_hi + 2 * k, b_hi + 2 * k, idesc, 1);
+                    if (CTAS == 1) umma_commit_1cta(empty_bar(s)); else umma_commit_pair(empty_bar(s));
+                    first = false;
+                }
+                if (ok) {
+                    if (CTAS == 1) umma_commit_1cta(acc_full_bar(buf)); else umma_commit_pair(acc_full_bar(buf));
+                }
             }
-            if (ok) {
-                if (CTAS == 1) umma_commit_1cta(accum_bar); else umma_commit_pair(accum_bar);
-            } else {
-                atomicOr(p.status, ZNN_DEV_MMA_WAIT_EXPIRED);
-            }
+            if (!ok) atomicOr(p.status, ZNN_DEV_MMA_WAIT_EXPIRED);
         }
     } else {
-        // ---------------- epilogue: TMEM -> registers -> C ----------------
-        const int q = warp & 3;  // the TMEM lane quarter this warp may read
+        // ---------------- epilogue: tensor memory -> fp32 registers (per chunk) -> C ----------------
+        const int q = warp & 3;              // the TMEM lane quarter this warp may read
+        const int half = (warp - 2) >> 2;    // which half of the tile's columns
+        constexpr int CPT = Cfg::kColsPerThread;
+        float acc[CPT];
+#pragma unroll
+        for (int i = 0; i < CPT; i++) acc[i] = 0.0f;
+        const uint32_t acc_empty_leader0 = (CTAS == 2) ? mapa_shared(acc_empty_bar(0), 0) : acc_empty_bar(0);
         bool got = true;
-        if (lane == 0) got = mbar_wait_bounded(accum_bar, 0);
-        got = __shfl_sync(0xffffffffu, (int)got, 0) != 0;
+        for (int c = 0; c < nchunks; c++) {
+            const int buf = c & 1;
+            if (lane == 0) got = mbar_wait_bounded(acc_full_bar(buf), (c >> 1) & 1);
+            got = __shfl_sync(0xffffffffu, (int)got, 0) != 0;
+            if (!got) break;
+            tc_fence_after();
+            const uint32_t t0 = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(buf * BN + half * CPT);
+#pragma unroll
+            for (int j = 0; j < CPT / 32; j++) {
+                float v[32];
+                tmem_ld_32x32(t0 + 32u * j, v);
+#pragma unroll
+                for (int i = 0; i < 32; i++) acc[32 * j + i] += v[i];
+            }
+            // hand the buffer back to the MMA issuer
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) {
+                if (CTAS == 1) asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(acc_empty_bar(buf)) : "memory");
+                else mbar_arrive_remote(acc_empty_leader0 + 8u * buf);
+            }
+        }
         if (!got) {
             if (lane == 0) atomicOr(p.status, ZNN_DEV_EPI_WAIT_EXPIRED);
         } else {
-            tc_fence_after();
             const int row = row0 + q * 32 + lane;
-            float* crow = p.C + (size_t)batch * p.stride_c + (size_t)row * p.ldc + col0;
+            const int cbase = col0 + half * CPT;
             const bool vec_ok = ((p.ldc & 3) == 0) && ((reinterpret_cast<uintptr_t>(p.C) & 15) == 0) &&
                                 ((p.stride_c & 3) == 0);
             const float alpha = p.alpha, beta = p.beta;
-#pragma unroll 1
-            for (int c = 0; c < BN; c += 32) {
-                float v[32];
-                tmem_ld_32x32(tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)c, v);
-                if (row >= p.M) continue;
-                const int ncols = min(32, p.N - (col0 + c));
-                if (ncols <= 0) continue;
-                if (vec_ok && ncols == 32) {
-                    float4* dst = reinterpret_cast<float4*>(crow + c);
+            if (row < p.M) {
+                float* crow = p.C + (size_t)batch * p.stride_c + (size_t)row * p.ldc + cbase;
 #pragma unroll
-                    for (int j = 0; j < 8; j++) {
-                        float4 o;
-                        o.x = alpha * v[4 * j + 0]; o.y = alpha * v[4 * j + 1];
-                        o.z = alpha * v[4 * j + 2]; o.w = alpha * v[4 * j + 3];
-                        if (beta != 0.0f) {
-                            const float4 old = dst[j];
-                            o.x += beta * old.x; o.y += beta * old.y; o.z += beta * old.z; o.w += beta * old.w;
+                for (int c = 0; c < CPT; c += 32) {
+                    const int ncols = min(32, p.N - (cbase + c));
+                    if (ncols <= 0) continue;
+                    if (vec_ok && ncols == 32) {
+                        float4* dst = reinterpret_cast<float4*>(crow + c);
+#pragma unroll
+                        for (int j = 0; j < 8; j++) {
+                            float4 o;
+                            o.x = alpha * acc[c + 4 * j + 0]; o.y = alpha * acc[c + 4 * j + 1];
+                            o.z = alpha * acc[c + 4 * j + 2]; o.w = alpha * acc[c + 4 * j + 3];
+                            if (beta != 0.0f) {
+                                const float4 old = dst[j];
+                                o.x += beta * old.x; o.y += beta * old.y; o.z += beta * old.z; o.w += beta * old.w;
+                            }
+                            dst[j] = o;
                         }
-                        dst[j] = o;
-                    }
-                } else {
+                    } else {
 #pragma unroll
-                    for (int j = 0; j < 32; j++) {
-                        if (j < ncols) {
-                            float o = alpha * v[j];
-                            if (beta != 0.0f) o += beta * crow[c + j];
-                            crow[c + j] = o;
+                        for (int j = 0; j < 32; j++) {
+                            if (j < ncols) {
+                                float o = alpha * acc[c + j];
+                                if (beta != 0.0f) o += beta * crow[c + j];
+                                crow[c + j] = o;
+                            }
                         }
                     }
                 }
@@ -539,6 +595,63 @@ static int make_plane_map(CUtensorMap* tm, float* plane, int rows, int kpad, int
     return ZNN_OK;
 }
 
+// ---- optional event bracketing of the tensor-core kernel (measurement aid) ----
+struct TcProfile {
+    bool on = false;
+    static constexpr int kMaxEvents = 4096;
+    cudaEvent_t ev[kMaxEvents][2];
+    int created = 0;
+    int used = 0;
+    double flops = 0.0;
+};
+static thread_local TcProfile t_prof;
+
+static cudaEvent_t* prof_begin(double flops)
+{
+    TcProfile& pr = t_prof;
+    if (!pr.on || pr.used >= TcProfile::kMaxEvents) return nullptr;
+    if (pr.used >= pr.created) {
+        if (cudaEventCreate(&pr.ev[pr.created][0]) != cudaSuccess) return nullptr;
+        if (cudaEventCreate(&pr.ev[pr.created][1]) != cudaSuccess) return nullptr;
+        pr.created++;
+    }
+    cudaEvent_t* e = pr.ev[pr.used++];
+    pr.flops += flops;
+    cudaEventRecord(e[0], stream());
+    return e;
+}
+
+static void prof_end(cudaEvent_t* e)
+{
+    if (e) cudaEventRecord(e[1], stream());
+}
+
+int tc_profile_enable(int enable)
+{
+    t_prof.on = (enable != 0);
+    t_prof.used = 0;
+    t_prof.flops = 0.0;
+    return ZNN_OK;
+}
+
+int tc_profile_read(double* kernel_ms, long long* launches, double* flops)
+{
+    TcProfile& pr = t_prof;
+    double total = 0.0;
+    for (int i = 0; i < pr.used; i++) {
+        ZNN_CUDA_OK(cudaEventSynchronize(pr.ev[i][1]));
+        float ms = 0.0f;
+        ZNN_CUDA_OK(cudaEventElapsedTime(&ms, pr.ev[i][0], pr.ev[i][1]));
+        total += ms;
+    }
+    if (kernel_ms) *kernel_ms = total;
+    if (launches) *launches = pr.used;
+    if (flops) *flops = pr.flops;
+    pr.used = 0;
+    pr.flops = 0.0;
+    return ZNN_OK;
+}
+
 template <int BN, int CTAS>
 static int launch_tc(const CUtensorMap* maps, const GemmTcParams& p, int batch)
 {
@@ -561,9 +674,16 @@ static int launch_tc(const CUtensorMap* maps, const GemmTcParams& p, int batch)
     attr[0].val.clusterDim.z = 1;
     cfg.attrs = attr;
     cfg.numAttrs = 1;
+    cudaEvent_t* ev = prof_begin(2.0 * p.M * (double)p.N * p.k_real * batch);
     ZNN_CUDA_OK(cudaLaunchKernelEx(&cfg, kern, maps[0], maps[1], maps[2], maps[3], p));
+    prof_end(ev);
+    count_launch();
     return ZNN_OK;
 }
+
+static thread_local int t_chunk_kblocks = 8;  // 256 contraction elements per tensor-memory accumulation
+int tc_chunk_kblocks() { return t_chunk_kblocks; }
+void tc_set_chunk_kblocks(int v) { t_chunk_kblocks = v < 1 ? 1 : v; }
 
 // op(A) is M x K, op(B) is K x N.  ctas = 1 or 2.
 int gemm_tc(int ta, int tb, int M, int N, int K, float alpha, const float* A, long long lda, long long stride_a,
@@ -613,7 +733,7 @@ int gemm_tc(int ta, int tb, int M, int N, int K, float alpha, const float* A, lo
     else if (N <= 128) bn = 128;
     const int tile_rows = kTileM * ctas;
     GemmTcParams p;
-    p.M = M; p.N = N; p.k_blocks = kpad / kBK;
+    p.M = M; p.N = N; p.k_blocks = kpad / kBK; p.k_real = K; p.chunk_kblocks = tc_chunk_kblocks();
     p.tiles_m = (M + tile_rows - 1) / tile_rows;
     p.tiles_n = (N + bn - 1) / bn;
     p.alpha = alpha; p.beta = beta; p.C = C; p.ldc = ldc; p.stride_c = stride_c; p.status = status;

@@ -40,6 +40,15 @@ struct DeviceState {
 };
 
 static DeviceState g_dev[kMaxDev];
+static thread_local long long t_launches = 0;
+
+void count_launch() { t_launches++; }
+long long launches_and_reset(int reset)
+{
+    const long long v = t_launches;
+    if (reset) t_launches = 0;
+    return v;
+}
 static std::mutex g_mu;
 static thread_local cudaStream_t t_user_stream = nullptr;
 static thread_local bool t_has_user_stream = false;
@@ -105,6 +114,8 @@ void* workspace(size_t bytes)
     s->ws_bytes = want;
     return s->ws;
 }
+
+long long launches_and_reset(int reset);
 
 }  // namespace znn
 
@@ -227,6 +238,13 @@ int znn_device_status(int* status, int clear)
     ZNN_CUDA_OK(cudaStreamSynchronize(stream()));
     ZNN_CUDA_OK(cudaMemcpy(status, w, sizeof(int), cudaMemcpyDeviceToHost));
     if (clear && *status) ZNN_CUDA_OK(cudaMemset(w, 0, sizeof(int)));
+    return ZNN_OK;
+}
+
+int znn_launch_count(long long* count, int reset)
+{
+    ZNN_REQUIRE(count, "count is NULL");
+    *count = launches_and_reset(reset);
     return ZNN_OK;
 }
 
