@@ -58,7 +58,7 @@ class ClockSampler:
         try:
             self.proc = subprocess.Popen(
                 ["nvidia-smi", "-i", str(self.gpu), f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits",
-                 "-lms", "100"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+                 "-lms", "20"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
             self.thread = threading.Thread(target=self._pump, daemon=True)
             self.thread.start()
         except OSError:
@@ -96,7 +96,6 @@ class ClockSampler:
 
 # --------------------------------------------------------------------------- CPU side
 def cpu_step(zo, A, B, dC, Cm, dA, dB, n):
-    zo.matmul_fwd_into = None
     zo.sgemm(111, 111, n, n, n, 1.0, A, n, B, n, 0.0, Cm, n)
     zo.sgemm(111, 112, n, n, n, 1.0, dC, n, B, n, 1.0, dA, n)
     zo.sgemm(112, 111, n, n, n, 1.0, A, n, dC, n, 1.0, dB, n)
@@ -193,7 +192,9 @@ def run_gpu(args):
         dist.init_process_group("nccl", device_id=torch.device("cuda", local))
     L = lib()
     L.call("znn_init", local)
-    stream = torch.cuda.current_stream()
+    # a non-default stream, so that torch's events and the shim's kernels share it
+    stream = torch.cuda.Stream()
+    torch.cuda.set_stream(stream)
     L.call("znn_set_stream", stream.cuda_stream)
 
     n = args.n
@@ -281,6 +282,23 @@ def run_gpu(args):
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
     e2e_value = world * flops_step * e2e_steps / (float(t.item()) * 1e-3) / 1e12
 
+    tf32_live = None
+    if rank == 0 and world == 1:
+        # context only: the library TF32 GEMM rate on this GPU right now (one pass, not 3xTF32)
+        torch.backends.cuda.matmul.allow_tf32 = True
+        for _ in range(3):
+            torch.matmul(A, B, out=Cm)
+        torch.cuda.synchronize()
+        best = 1e9
+        for _ in range(5):
+            e0.record(stream)
+            torch.matmul(A, B, out=Cm)
+            e1.record(stream)
+            torch.cuda.synchronize()
+            best = min(best, e0.elapsed_time(e1))
+        tf32_live = 2.0 * n ** 3 / (best * 1e-3) / 1e12
+        torch.backends.cuda.matmul.allow_tf32 = False
+
     if rank == 0:
         peaks, peaks_kind = read_peaks()
         # 3xTF32 ceiling: the TF32 dense rate is half the bf16 rate on this part, and
@@ -298,7 +316,9 @@ def run_gpu(args):
                          "frac": (achieved / peak) if achieved else None, "traffic": None,
                          "kernel": "gemm3x_tf32_kernel<256,2>", "launches": kl.value,
                          "avg_launch_ms": (kms.value / kl.value) if kl.value else None,
-                         "peak_source": f"{peaks_kind}: bf16 burst {peaks['bf16_tflops']} TF/s / 2 (tf32) / 3 (passes)"},
+                         "peak_source": f"{peaks_kind}: bf16 burst {peaks['bf16_tflops']} TF/s / 2 (tf32) / 3 (passes)",
+                         "cublas_tf32_live_tflops": tf32_live,
+                         "frac_of_live_cublas_tf32_third": (achieved / (tf32_live / 3.0)) if (achieved and tf32_live) else None},
             "e2e": {"value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": 3 * nbytes, "d2h_bytes_per_step": 3 * nbytes,
                     "steps": e2e_steps},
             "gpu_launches": launches, "clocks": clocks,
@@ -314,8 +334,8 @@ def run_gpu(args):
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=10)
-    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--steps", type=int, default=40)
+    ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--n", type=int, default=8192)
     ap.add_argument("--impl", default="znn_b200", choices=["znn_b200", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
