@@ -105,6 +105,22 @@ int znn_softmax_xent_fwd(const float* logits, const int32_t* targets, float* pro
 int znn_softmax_xent_fwd_u8(const float* logits, const uint8_t* targets, float* probs, float* loss, int M, int N);
 int znn_softmax_xent_bwd(const float* probs, const int32_t* targets, float* dlogits, int M, int N);
 int znn_softmax_xent_bwd_u8(const float* probs, const uint8_t* targets, float* dlogits, int M, int N);
+/* No counterpart in the reference.  Same result as znn_softmax_xent_fwd for callers that must
+ * not allocate (a service whose memory budget was fixed at start-up, or a latency-critical
+ * thread that cannot afford cudaMalloc, which synchronises the whole device): the per-row losses go to a fixed 256 KiB device array inside
+ * the library instead of the growable scratch block, so this call never reaches cudaMalloc,
+ * cudaFree or any allocating routine.  Limits and rules:
+ *   - M <= 65536 rows; larger M is rejected with ZNN_ERR_INVALID (N is not limited);
+ *   - work is enqueued on cuda_stream (a cudaStream_t; NULL = the legacy default stream), the
+ *     shim's own stream and state are not touched, znn_init is not required;
+ *   - the first call on each device looks up the array's device address
+ *     (cudaGetSymbolAddress, which may load the module): make that first call before any
+ *     stream capture starts;
+ *   - all calls on a device share the one array and it keeps the last call's contents
+ *     (rows < M are rewritten before use, nothing needs clearing): two calls whose kernels can
+ *     overlap on the GPU (different streams, no dependency) race on it; serialise them. */
+int znn_softmax_xent_fwd_static(const float* logits, const int32_t* targets, float* probs, float* loss,
+                                int M, int N, void* cuda_stream);
 /* Softmax over the last dimension: :435-461 / :1054-1076 */
 int znn_softmax_fwd(const float* A, float* C, size_t rows, int D);
 int znn_softmax_bwd(const float* Y, const float* dY, float* dA, size_t rows, int D);

@@ -4,6 +4,8 @@
 // same rounding points costs nothing and keeps results close to bit-identical.
 #include <math_constants.h>
 
+#include <mutex>
+
 #include "common.cuh"
 
 namespace znn {
@@ -1015,3 +1017,60 @@ int znn_sgd_step(float* w, const float* g, float* v, float lr, float momentum, f
 }
 
 }  // extern "C"
+
+// ---------------------------------------------------------------------------
+// SoftmaxCrossEntropy forward for callers that may not allocate
+// ---------------------------------------------------------------------------
+// znn_softmax_xent_fwd keeps its per-row losses in the shim's scratch block,
+// which is grown with cudaMalloc when a call needs more than it holds.  Some
+// callers cannot tolerate that: a serving loop whose memory budget was fixed at
+// start-up and must not grow, or a latency-critical host thread that must never
+// block on the allocator (cudaMalloc synchronises the whole device).  For them the per-row losses live in the fixed array below, which
+// is part of the library image: every GPU that loads libznn_cuda.so holds these
+// 256 KiB until the process exits, whether or not the entry point is used.
+constexpr int kStaticXentMaxRows = 65536;
+static __device__ __align__(256) float g_static_xent_rowloss[kStaticXentMaxRows];
+
+// In host code the array's name is only a handle for the runtime, not an address
+// a kernel can use; the device address is looked up once per device, with that
+// device current, and cached here.
+static float* g_static_xent_ptr[16] = {nullptr};
+static std::mutex g_static_xent_mu;
+
+static int static_xent_scratch(float** out)
+{
+    int dev = -1;
+    ZNN_CUDA_OK(cudaGetDevice(&dev));
+    ZNN_REQUIRE(dev >= 0 && dev < 16, "device index %d is outside the supported range", dev);
+    std::lock_guard<std::mutex> lk(g_static_xent_mu);
+    if (!g_static_xent_ptr[dev]) {
+        float* p = nullptr;
+        ZNN_CUDA_OK(cudaGetSymbolAddress((void**)&p, g_static_xent_rowloss));
+        ZNN_REQUIRE(p != nullptr, "cudaGetSymbolAddress returned a null device address");
+        g_static_xent_ptr[dev] = p;
+    }
+    *out = g_static_xent_ptr[dev];
+    return ZNN_OK;
+}
+
+extern "C" int znn_softmax_xent_fwd_static(const float* logits, const int32_t* targets, float* probs, float* loss,
+                                           int M, int N, void* cuda_stream)
+{
+    ZNN_REQUIRE(M > 0 && N > 0, "empty logits");
+    ZNN_REQUIRE(M <= kStaticXentMaxRows,
+                "M = %d rows exceeds the %d rows the fixed scratch array holds; use znn_softmax_xent_fwd", M,
+                kStaticXentMaxRows);
+    ZNN_REQUIRE(logits && targets && probs && loss, "NULL pointer");
+    float* rowloss = nullptr;
+    const int rc = static_xent_scratch(&rowloss);
+    if (rc != ZNN_OK) return rc;
+    cudaStream_t st = (cudaStream_t)cuda_stream;
+    const int threads = N >= 1024 ? 256 : (N >= 128 ? 128 : 32);
+    // Rows 0..M-1 of the array are overwritten before they are read, so nothing has
+    // to be cleared; rows beyond M keep whatever an earlier call left there.
+    softmax_xent_fwd_kernel<int32_t><<<M, threads, 0, st>>>(logits, targets, probs, rowloss, N);
+    ZNN_LAUNCH_OK("softmax_xent_fwd_kernel (fixed scratch)");
+    mean_rows_kernel<<<1, 1024, 0, st>>>(rowloss, loss, M);
+    ZNN_LAUNCH_OK("mean_rows_kernel (fixed scratch)");
+    return ZNN_OK;
+}
