@@ -169,6 +169,21 @@ int znn_sgd_step(float* w, const float* g, float* v, float lr, float momentum, f
 /* fill helpers (src/tensor.zig:354-379 fills; used for dC = 1 seeds and zeroGrad) */
 int znn_fill(float* dst, float value, size_t n);
 
+/* ---- data parallelism (new: the reference is single-process).  One process per GPU; the
+ *      training step's only exchange is the sum of parameter gradients over ranks.
+ *      znn_dp_unique_id is called on rank 0 and its 128 bytes are handed to every rank out of
+ *      band (torch.distributed, a file, MPI ...).  All-reduces run on a communication stream
+ *      ordered after the work already queued on the compute stream; znn_dp_join makes the
+ *      compute stream wait for them. ---- */
+int znn_dp_unique_id(char* out128);
+int znn_dp_init(int world, int rank, const char* id128);
+int znn_dp_world(int* world, int* rank);
+int znn_dp_allreduce_async(float* buf, size_t count);   /* in-place fp32 sum */
+int znn_dp_join(void);
+int znn_dp_allreduce(float* buf, size_t count);
+int znn_dp_broadcast(float* buf, size_t count, int root);
+int znn_dp_finalize(void);
+
 #ifdef __cplusplus
 }
 #endif

@@ -1,0 +1,81 @@
+/*
+ * znn_host.h -- C entry points of the host-side mirror of the reference's
+ * Tensor / Graph / Op / nn / optim layer (znn_b200/csrc/host/), for callers that
+ * cannot use the C++ classes directly (the Python tests and benchmarks).
+ *
+ * Two levels:
+ *  - znn_graph_*: a Graph (src/autodiff.zig:1237-2264) with integer tensor
+ *    handles; `znn_graph_op` appends one op by its reference builder name
+ *    ("matmul", "addBias", "relu", "gelu", "softmaxCrossEntropy", "reshape",
+ *    "transposeND", "mulScalar", "add", "conv2d", "maxpool2d", "softmax",
+ *    "rmsNorm", "batchMatMul", "embedding", plus "causalSoftmax", "layerNorm").
+ *  - znn_model_*: the example programs' models (examples/fashion_mnist.zig,
+ *    examples/cnn.zig, examples/transformer_block.zig, examples/transformer_gpt.zig)
+ *    with their training step: new graph -> forward -> SoftmaxCrossEntropy ->
+ *    zeroGrad -> backward -> [gradient all-reduce] -> SGD step.
+ * All functions return 0 or a negative ZNN_ERR_* code (text: znn_last_error).
+ */
+#ifndef ZNN_HOST_H
+#define ZNN_HOST_H
+#include <stddef.h>
+#include <stdint.h>
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef struct znn_graph znn_graph;
+typedef struct znn_model znn_model;
+
+int znn_graph_create(size_t arena_bytes, znn_graph** out);
+int znn_graph_destroy(znn_graph* g);
+/* Graph.array / Graph.tensorND (host_data may be NULL = zeros) */
+int znn_graph_array(znn_graph* g, const long long* dims, int rank, const float* host_data, int requires_grad, int* id);
+/* args: reshape -> new dims; transposeND -> dim0, dim1; mulScalar -> value; maxpool2d -> pool, stride;
+ * rmsNorm/layerNorm -> eps; conv2d -> pad (optional); causalSoftmax -> scale;
+ * softmaxCrossEntropy -> the M integer class labels */
+int znn_graph_op(znn_graph* g, const char* name, const int* inputs, int n_inputs, const double* args, int n_args, int* id);
+int znn_graph_backward(znn_graph* g, int id, int seed_one);  /* seed_one=1: Graph.backward, 0: backwardWithGrad */
+int znn_graph_forward(znn_graph* g);                         /* Graph.forward: re-execute the tape */
+int znn_graph_zero_grad(znn_graph* g);
+int znn_graph_shape(znn_graph* g, int id, long long* dims8, int* rank, int* requires_grad);
+int znn_graph_read(znn_graph* g, int id, int which, float* host, size_t count);        /* which: 0 data, 1 grad */
+int znn_graph_write(znn_graph* g, int id, int which, const float* host, size_t count);
+int znn_graph_num_ops(znn_graph* g, int* n);
+
+#define ZNN_MODEL_MLP 1         /* dims: in, h1, h2, out            (examples/fashion_mnist.zig:25-27) */
+#define ZNN_MODEL_CNN_REF 2     /* no dims                          (examples/cnn.zig:24-27)           */
+#define ZNN_MODEL_CNN_PADDED 3  /* no dims: 1->32->64 pad 1, 3136->128->10 (workload definition)      */
+#define ZNN_MODEL_BLOCK 4       /* dims: n_embd, n_head             (src/nn.zig:950-1022)              */
+#define ZNN_MODEL_GPT 5         /* dims: vocab, block_size, n_embd, n_head, n_layer (src/nn.zig:1125) */
+
+int znn_model_create(int kind, const long long* dims, int ndims, size_t arena_bytes, znn_model** out);
+int znn_model_destroy(znn_model* m);
+int znn_model_param_count(znn_model* m, int* n);
+int znn_model_param_info(znn_model* m, int i, char* name, size_t name_len, long long* dims8, int* rank,
+                         long long* offset, long long* fan_in);
+int znn_model_total_floats(znn_model* m, long long* total);   /* slab length incl. alignment padding */
+int znn_model_set_params(znn_model* m, const float* host_slab);
+int znn_model_get_params(znn_model* m, float* host_slab);
+int znn_model_get_grads(znn_model* m, float* host_slab);
+int znn_model_get_velocities(znn_model* m, float* host_slab);
+/* keys: "lr", "momentum", "fused_softmax" (1/0), "dp_bucket_floats", "dp_overlap" (1/0) */
+int znn_model_set_option(znn_model* m, const char* key, double value);
+/* One training step.  x: [batch, features] pixels (MLP/CNN) or [batch, seq] fp32 token ids (GPT); targets: batch
+ * (or batch*seq) int32 labels.  on_device = 1: both pointers are device memory and are used in place.
+ * loss_host may be NULL (no read-back, no synchronisation). */
+int znn_model_train_step(znn_model* m, const float* x, const int32_t* targets, int batch, int seq, int on_device,
+                         float* loss_host);
+/* forward only; logits_host receives batch x classes (MLP/CNN) or batch*seq x vocab (GPT); may be NULL */
+int znn_model_forward(znn_model* m, const float* x, int batch, int seq, int on_device, float* logits_host);
+/* transformer block: y = block(x); backward from dy; x,dy,y host arrays of B*T*n_embd; dx may be NULL */
+int znn_model_block_fwd_bwd(znn_model* m, const float* x, const float* dy, int B, int T, float* y, float* dx);
+/* greedy decode as examples/transformer_gpt.zig:116-146 (full re-forward per token over the last block_size ids,
+ * first-maximum argmax), for `batch` prompts of prompt_len ids at once; out_ids: batch x n_new */
+int znn_model_greedy_decode(znn_model* m, const float* prompt_ids, int batch, int prompt_len, int n_new, float* out_ids);
+int znn_model_arena_high_water(znn_model* m, long long* bytes);
+int znn_model_last_step_ops(znn_model* m, int* n_ops);
+
+#ifdef __cplusplus
+}
+#endif
+#endif

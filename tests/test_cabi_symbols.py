@@ -25,13 +25,16 @@ def test_header_declares_the_hot_path():
 
 
 def test_every_declared_symbol_is_exported(dll):
-    missing = [n for n, _ in _lib.declared_functions() if not hasattr(dll, n)]
-    assert not missing, f"declared in include/znn_cuda.h but not exported: {missing}"
+    for header in (_lib.HEADER, _lib.HOST_HEADER):
+        decl = _lib.declared_functions(header)
+        assert decl, header
+        missing = [n for n, _ in decl if not hasattr(dll, n)]
+        assert not missing, f"declared in {header} but not exported: {missing}"
 
 
 def test_ctypes_signatures_resolve():
     L = _lib.lib()
-    for name, types in _lib.declared_functions():
+    for name, types in _lib.declared_functions() + _lib.declared_functions(_lib.HOST_HEADER):
         assert len(getattr(L.dll, name).argtypes) == len(types)
 
 

@@ -1,0 +1,163 @@
+"""The example programs' models run by the C++ host mirror (znn_model_*) against the CPU oracle's
+composition of the same ops, on seeded synthetic inputs with the datasets' shapes and value ranges.
+
+Bars: loss trajectory within 1e-4 relative at every step; argmax predictions bit-exact;
+parameters after training within 1e-4 of their scale."""
+import numpy as np
+import pytest
+
+from oracle import models
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(scope="module")
+def Model():
+    from znn_b200 import ops
+    from znn_b200.models import Model as M
+    ops.init(0)
+    return M
+
+
+def pixels(r, n):
+    return (r.integers(0, 256, (n, 784)).astype(np.float32) / np.float32(255.0)).astype(np.float32)
+
+
+def relclose(a, b, tol, what):
+    a, b = np.asarray(a, np.float64), np.asarray(b, np.float64)
+    scale = max(1e-30, float(np.abs(b).max()))
+    err = float(np.abs(a - b).max())
+    assert err <= tol * scale, f"{what}: {err:.3e} vs scale {scale:.3e}"
+
+
+def run_training(Model, kind, dims, cfg, steps, batch, lr, momentum, seed, scheme="he", seq=0, vocab=10):
+    r = np.random.default_rng(seed)
+    P0 = models.init_params(kind, cfg, seed=seed + 1, scheme=scheme)
+    m = Model(kind, dims, arena_bytes=512 << 20)
+    m.set_params(P0)
+    m.set_option("lr", lr)
+    m.set_option("momentum", momentum)
+    tr = models.OracleTrainer(kind, P0, cfg, lr=lr, momentum=momentum)
+    worst = 0.0
+    for s in range(steps):
+        if kind == "gpt":
+            x = r.integers(0, vocab, (batch, seq)).astype(np.float32)
+            t = np.concatenate([x[:, 1:], r.integers(0, vocab, (batch, 1))], axis=1).astype(np.int32)
+        else:
+            x, t = pixels(r, batch), r.integers(0, 10, batch).astype(np.int32)
+        lo, logits_o = tr.step(x, t)
+        lg = m.train_step(x, t, seq=seq)
+        rel = abs(lg - lo) / abs(lo)
+        worst = max(worst, rel)
+        assert rel <= 1e-4, f"{kind} step {s}: loss {lg} vs oracle {lo} (rel {rel:.2e})"
+    Pg = m.get_params()
+    for k in tr.P:
+        relclose(Pg[k], tr.P[k], 1e-4, f"{kind} {k} after {steps} steps")
+    return m, tr, worst
+
+
+def test_mlp_100_steps_loss_trajectory(Model):
+    """Config 1: 784->128->64->10 (examples/fashion_mnist.zig:25-27), batch 64, SGD momentum 0.9 lr 0.01."""
+    m, tr, worst = run_training(Model, "mlp", (784, 128, 64, 10), (784, 128, 64, 10), 100, 64, 0.01, 0.9, seed=1234,
+                                scheme="uniform")
+    r = np.random.default_rng(99)
+    x = pixels(r, 100)                                         # evaluation batch of 100 (fashion_mnist.zig:222-255)
+    from oracle import ograph, zo
+    g = ograph.OGraph()
+    P = {k: g.array(v, False) for k, v in tr.P.items()}
+    lo = models.mlp_net(g, P, g.array(x, False)).data
+    lg = m.forward(x, classes=10)
+    relclose(lg, lo, 1e-4, "eval logits")
+    np.testing.assert_array_equal(np.argmax(lg, 1), zo.argmax(lo, 1).astype(np.int64))
+
+
+def test_mlp_he_init_reference_schedule(Model):
+    """The reference's own hyper-parameters: He-normal init, lr 0.05 (fashion_mnist.zig:98-101)."""
+    run_training(Model, "mlp", (784, 128, 64, 10), (784, 128, 64, 10), 30, 64, 0.05, 0.9, seed=7, scheme="he")
+
+
+def test_cnn_reference_shape(Model):
+    """examples/cnn.zig: 1->4->8->16 valid convs, fc 144->10, batch 64."""
+    run_training(Model, "cnn_ref", (), None, 12, 64, 0.05, 0.9, seed=11)
+
+
+def test_cnn_padded_shape(Model):
+    """Workload-definition CNN: 1->32->64 3x3 pad 1, 3136->128->10 (reduced batch for the CPU oracle)."""
+    run_training(Model, "cnn_padded", (), None, 4, 16, 0.01, 0.9, seed=13, scheme="uniform")
+
+
+def test_gpt_small_training(Model):
+    """examples/transformer_gpt.zig architecture at a size the CPU oracle finishes: fused causal softmax in
+    the C++ mirror against the reference's literal mulScalar/mask/add/softmax sequence in the oracle."""
+    cfg = {"vocab_size": 61, "block_size": 24, "n_embd": 32, "n_head": 4, "n_layer": 2}
+    dims = (61, 24, 32, 4, 2)
+    m, tr, _ = run_training(Model, "gpt", dims, cfg, 15, 3, 0.05, 0.9, seed=21, seq=24, vocab=61)
+    assert m.last_step_ops() > 50
+
+
+def test_gpt_literal_attention_path(Model):
+    """fused_softmax = 0 runs the reference's op sequence literally (materialised -1e9 mask)."""
+    cfg = {"vocab_size": 29, "block_size": 8, "n_embd": 16, "n_head": 2, "n_layer": 1}
+    r = np.random.default_rng(3)
+    P0 = models.init_params("gpt", cfg, seed=4)
+    x = r.integers(0, 29, (2, 8)).astype(np.float32)
+    t = r.integers(0, 29, (2, 8)).astype(np.int32)
+    losses = []
+    for fused in (1, 0):
+        m = Model("gpt", (29, 8, 16, 2, 1), arena_bytes=64 << 20)
+        m.set_params(P0)
+        m.set_option("fused_softmax", fused)
+        m.set_option("lr", 0.0)
+        losses.append((m.train_step(x, t, seq=8), m.get_grads(), m.last_step_ops()))
+    assert losses[1][2] == losses[0][2] + 3          # mulScalar + add + softmax instead of one op
+    assert abs(losses[0][0] - losses[1][0]) <= 1e-6 * abs(losses[1][0])
+    for k in losses[0][1]:
+        relclose(losses[0][1][k], losses[1][1][k], 1e-5, k)
+
+
+def test_transformer_block_config_shape_small(Model):
+    """Pre-norm block forward+backward (examples/transformer_block.zig), d_model 64, 4 heads, batch 2 x seq 16."""
+    from oracle import ograph
+    r = np.random.default_rng(8)
+    cfg = {"n_embd": 64}
+    P0 = models.init_params("block", cfg, seed=9, scheme="n002")
+    x = r.standard_normal((2, 16, 64), np.float32)
+    dy = r.standard_normal((2, 16, 64), np.float32)
+    m = Model("block", (64, 4), arena_bytes=64 << 20)
+    m.set_params(P0)
+    y, dx = m.block_fwd_bwd(x, dy)
+    g = ograph.OGraph()
+    P = {k: g.array(v, True) for k, v in P0.items()}
+    xt = g.array(x, True)
+    yo = models.transformer_block(g, P, "block", xt, n_head=4)
+    yo.grad[...] = dy
+    g.backwardWithGrad(yo)
+    relclose(y, yo.data, 1e-5, "y")
+    relclose(dx, xt.grad, 3e-5, "dx")
+    G = m.get_grads()
+    for k, tns in P.items():
+        relclose(G[k], tns.grad.reshape(P0[k].shape), 3e-5, k)
+
+
+def test_greedy_decode_matches_oracle(Model):
+    """examples/transformer_gpt.zig:116-146: full re-forward per token, first-maximum argmax; tokens bit-exact."""
+    from oracle import ograph, zo
+    cfg = {"vocab_size": 37, "block_size": 12, "n_embd": 16, "n_head": 2, "n_layer": 2}
+    P0 = models.init_params("gpt", cfg, seed=31)
+    r = np.random.default_rng(32)
+    prompts = r.integers(0, 37, (3, 4)).astype(np.float32)
+    m = Model("gpt", (37, 12, 16, 2, 2), arena_bytes=64 << 20)
+    m.set_params(P0)
+    got = m.greedy_decode(prompts, 14)                         # runs past block_size: the window slides
+    seqs = [list(p) for p in prompts]
+    for _ in range(14):
+        T = min(len(seqs[0]), 12)
+        win = np.array([s[-T:] for s in seqs], np.float32)
+        g = ograph.OGraph()
+        P = {k: g.array(v, False) for k, v in P0.items()}
+        logits = models.gpt(g, P, g.array(win, False), cfg).data
+        nxt = zo.argmax(np.ascontiguousarray(logits[:, -1, :]), 1)
+        for s, n in zip(seqs, nxt):
+            s.append(float(n))
+    want = np.array([s[4:] for s in seqs], np.float32)
+    np.testing.assert_array_equal(got, want)

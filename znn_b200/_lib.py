@@ -10,14 +10,17 @@ import re
 HERE = os.path.dirname(os.path.abspath(__file__))
 LIB_PATH = os.path.join(HERE, "libznn_cuda.so")
 HEADER = os.path.join(os.path.dirname(HERE), "include", "znn_cuda.h")
+HOST_HEADER = os.path.join(os.path.dirname(HERE), "include", "znn_host.h")
 
 _CTYPES = {
-    "int": C.c_int, "float": C.c_float, "size_t": C.c_size_t, "long long": C.c_longlong,
+    "int": C.c_int, "float": C.c_float, "double": C.c_double, "size_t": C.c_size_t, "long long": C.c_longlong,
     "void*": C.c_void_p, "const void*": C.c_void_p, "void**": C.POINTER(C.c_void_p),
     "float*": C.c_void_p, "const float*": C.c_void_p, "int*": C.POINTER(C.c_int),
     "int32_t*": C.c_void_p, "const int32_t*": C.c_void_p, "const uint8_t*": C.c_void_p,
-    "const int64_t*": C.c_void_p, "char*": C.c_char_p, "long long*": C.POINTER(C.c_longlong),
-    "double*": C.POINTER(C.c_double),
+    "const int64_t*": C.c_void_p, "char*": C.c_char_p, "const char*": C.c_char_p, "long long*": C.POINTER(C.c_longlong),
+    "double*": C.POINTER(C.c_double), "const double*": C.c_void_p, "const long long*": C.c_void_p,
+    "const int*": C.c_void_p, "znn_graph*": C.c_void_p, "znn_model*": C.c_void_p,
+    "znn_graph**": C.POINTER(C.c_void_p), "znn_model**": C.POINTER(C.c_void_p),
 }
 
 
@@ -52,7 +55,7 @@ class _Lib:
                 f"{LIB_PATH} is missing: build it with `python -m znn_b200.build` (nvcc, sm_100a). "
                 "There is no CPU or PyTorch fallback.")
         self.dll = C.CDLL(LIB_PATH)
-        for name, types in declared_functions():
+        for name, types in declared_functions() + declared_functions(HOST_HEADER):
             fn = getattr(self.dll, name)
             fn.restype = C.c_int
             fn.argtypes = [_CTYPES[t] for t in types]

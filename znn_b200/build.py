@@ -26,6 +26,9 @@ SOURCES = [
     ("rowops.cu", ["-fmad=false"]),
     ("conv.cu", ["-fmad=false"]),
     ("dp.cu", []),
+    ("host/graph.cpp", []),
+    ("host/nn.cpp", []),
+    ("host/capi.cpp", []),
 ]
 
 
@@ -38,7 +41,9 @@ def nvcc():
 
 def _deps_mtime():
     hdrs = [os.path.join(CSRC, f) for f in os.listdir(CSRC) if f.endswith((".cuh", ".h", ".hpp"))]
+    hdrs += [os.path.join(CSRC, "host", f) for f in os.listdir(os.path.join(CSRC, "host")) if f.endswith(".hpp")]
     hdrs.append(os.path.join(os.path.dirname(HERE), "include", "znn_cuda.h"))
+    hdrs.append(os.path.join(os.path.dirname(HERE), "include", "znn_host.h"))
     return max(os.path.getmtime(h) for h in hdrs)
 
 
@@ -52,7 +57,7 @@ def build(force=False, verbose=False):
         path = os.path.join(CSRC, src)
         if not os.path.exists(path):
             continue
-        obj = os.path.join(OBJ, src.replace(".cu", ".o"))
+        obj = os.path.join(OBJ, os.path.basename(src).rsplit(".", 1)[0] + ".o")
         objs.append(obj)
         if force or not os.path.exists(obj) or os.path.getmtime(obj) < max(os.path.getmtime(path), hdr_m):
             cmd = [nvcc()] + ARCH + COMMON + extra + ["-c", path, "-o", obj]
@@ -72,9 +77,8 @@ def build(force=False, verbose=False):
     if failed:
         raise RuntimeError("nvcc failed:\n" + "\n".join(f"--- {s} ---\n{o}" for s, o in failed))
     if rebuilt or not os.path.exists(LIB):
-        cmd = [nvcc(), "-shared", "-o", LIB] + objs + ARCH + ["-lnccl"] if any(o.endswith("dp.o") for o in objs) else \
-              [nvcc(), "-shared", "-o", LIB] + objs + ARCH
-        subprocess.check_call(cmd)
+        # NCCL is loaded with dlopen at run time (dp.cu), so only libdl is linked
+        subprocess.check_call([nvcc(), "-shared", "-o", LIB] + objs + ARCH + ["-ldl"])
     return LIB
 
 

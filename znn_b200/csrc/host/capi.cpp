@@ -1,0 +1,567 @@
+// C entry points of the host mirror (include/znn_host.h).
+#include <math.h>
+#include <string.h>
+
+#include <memory>
+#include <unordered_map>
+
+#include "../../../include/znn_cuda.h"
+#include "../../../include/znn_host.h"
+#include "nn.hpp"
+
+namespace znn {
+int fail(int code, const char* fmt, ...);  // runtime.cu: sets the thread's error text
+}
+
+using namespace znn::host;
+
+#define ZNN_HOST_TRY try {
+#define ZNN_HOST_CATCH                                              \
+    }                                                               \
+    catch (const Error& e) { return znn::fail(e.code, "%s", e.what()); } \
+    catch (const std::exception& e) { return znn::fail(ZNN_ERR_INVALID, "%s", e.what()); } \
+    return ZNN_OK;
+
+struct znn_graph {
+    std::unique_ptr<Arena> arena;
+    std::unique_ptr<Graph> g;
+    std::vector<Tensor*> handles;
+};
+
+static Tensor* handle(znn_graph* g, int id)
+{
+    if (id < 0 || (size_t)id >= g->handles.size()) throw Error(ZNN_ERR_INVALID, "unknown tensor handle " + std::to_string(id));
+    return g->handles[id];
+}
+
+static Shape shape_from(const long long* dims, int rank)
+{
+    if (rank < 0 || rank > 8) throw Error(ZNN_ERR_INVALID, "rank must be 0..8");
+    size_t d[8];
+    for (int i = 0; i < rank; i++) {
+        if (dims[i] < 0) throw Error(ZNN_ERR_INVALID, "negative dimension");
+        d[i] = (size_t)dims[i];
+    }
+    return Shape(d, (size_t)rank);
+}
+
+extern "C" {
+
+int znn_graph_create(size_t arena_bytes, znn_graph** out)
+{
+    ZNN_HOST_TRY
+    if (!out) throw Error(ZNN_ERR_INVALID, "out is NULL");
+    std::unique_ptr<znn_graph> zg(new znn_graph());
+    zg->arena.reset(new Arena(arena_bytes));
+    zg->g.reset(new Graph(zg->arena.get()));
+    *out = zg.release();
+    ZNN_HOST_CATCH
+}
+
+int znn_graph_destroy(znn_graph* g)
+{
+    ZNN_HOST_TRY
+    if (g) {
+        znn_sync();
+        delete g;
+    }
+    ZNN_HOST_CATCH
+}
+
+int znn_graph_array(znn_graph* g, const long long* dims, int rank, const float* host_data, int requires_grad, int* id)
+{
+    ZNN_HOST_TRY
+    const Shape s = shape_from(dims, rank);
+    Tensor* t = host_data ? g->g->array(s, host_data, requires_grad != 0) : g->g->tensorND(s, requires_grad != 0);
+    g->handles.push_back(t);
+    if (id) *id = (int)g->handles.size() - 1;
+    ZNN_HOST_CATCH
+}
+
+int znn_graph_op(znn_graph* zg, const char* name, const int* inputs, int n_inputs, const double* args, int n_args, int* id)
+{
+    ZNN_HOST_TRY
+    Graph& g = *zg->g;
+    const std::string op(name ? name : "");
+    auto in = [&](int i) -> Tensor* {
+        if (i >= n_inputs) throw Error(ZNN_ERR_INVALID, op + ": too few inputs");
+        return handle(zg, inputs[i]);
+    };
+    auto arg = [&](int i) -> double {
+        if (i >= n_args) throw Error(ZNN_ERR_INVALID, op + ": too few arguments");
+        return args[i];
+    };
+    Tensor* out = nullptr;
+    if (op == "matmul") out = g.matmul(in(0), in(1));
+    else if (op == "addBias") out = g.addBias(in(0), in(1));
+    else if (op == "relu") out = g.relu(in(0));
+    else if (op == "gelu") out = g.gelu(in(0));
+    else if (op == "softmaxCrossEntropy") {
+        Tensor* logits = in(0);
+        const size_t M = logits->shape.dims[0];
+        if ((size_t)n_args != M) throw Error(ZNN_ERR_INVALID, "softmaxCrossEntropy: one label per row expected");
+        std::vector<int32_t> t(M);
+        for (size_t i = 0; i < M; i++) t[i] = (int32_t)args[i];
+        int32_t* dev = (int32_t*)zg->arena->alloc(M * sizeof(int32_t));
+        check(znn_memcpy_h2d(dev, t.data(), M * sizeof(int32_t)), "upload labels");
+        check(znn_sync(), "znn_sync");
+        out = g.softmaxCrossEntropy(logits, dev);
+    } else if (op == "reshape") {
+        size_t d[8];
+        if (n_args > 8) throw Error(ZNN_ERR_INVALID, "reshape: rank above 8");
+        for (int i = 0; i < n_args; i++) d[i] = (size_t)args[i];
+        out = g.reshape(in(0), Shape(d, (size_t)n_args));
+    } else if (op == "transposeND" || op == "transpose") out = g.transposeND(in(0), (int)arg(0), (int)arg(1));
+    else if (op == "mulScalar") out = g.mulScalar(in(0), (float)arg(0));
+    else if (op == "add") out = g.add(in(0), in(1));
+    else if (op == "conv2d") out = g.conv2d(in(0), in(1), n_inputs > 2 ? in(2) : nullptr, n_args > 0 ? (int)args[0] : 0);
+    else if (op == "maxpool2d") out = g.maxpool2d(in(0), (int)arg(0), (int)arg(1));
+    else if (op == "softmax") out = g.softmax(in(0));
+    else if (op == "causalSoftmax") out = g.causalSoftmax(in(0), (float)arg(0));
+    else if (op == "rmsNorm") out = g.rmsNorm(in(0), in(1), (float)arg(0));
+    else if (op == "layerNorm") out = g.layerNorm(in(0), in(1), in(2), (float)arg(0));
+    else if (op == "batchMatMul") out = g.batchMatMul(in(0), in(1));
+    else if (op == "embedding") out = g.embedding(in(0), in(1));
+    else throw Error(ZNN_ERR_INVALID, "unknown op '" + op + "'");
+    zg->handles.push_back(out);
+    if (id) *id = (int)zg->handles.size() - 1;
+    ZNN_HOST_CATCH
+}
+
+int znn_graph_backward(znn_graph* g, int id, int seed_one)
+{
+    ZNN_HOST_TRY
+    if (seed_one) g->g->backward(handle(g, id));
+    else g->g->backwardWithGrad(handle(g, id));
+    ZNN_HOST_CATCH
+}
+
+int znn_graph_forward(znn_graph* g)
+{
+    ZNN_HOST_TRY
+    g->g->forward();
+    ZNN_HOST_CATCH
+}
+
+int znn_graph_zero_grad(znn_graph* g)
+{
+    ZNN_HOST_TRY
+    g->g->zeroGrad();
+    ZNN_HOST_CATCH
+}
+
+int znn_graph_shape(znn_graph* g, int id, long long* dims8, int* rank, int* requires_grad)
+{
+    ZNN_HOST_TRY
+    Tensor* t = handle(g, id);
+    if (dims8)
+        for (size_t i = 0; i < t->shape.len; i++) dims8[i] = (long long)t->shape.dims[i];
+    if (rank) *rank = (int)t->shape.len;
+    if (requires_grad) *requires_grad = t->requires_grad ? 1 : 0;
+    ZNN_HOST_CATCH
+}
+
+int znn_graph_read(znn_graph* g, int id, int which, float* host, size_t count)
+{
+    ZNN_HOST_TRY
+    Tensor* t = handle(g, id);
+    const float* src = which ? t->grad : t->data;
+    if (!src) throw Error(ZNN_ERR_INVALID, "tensor has no gradient buffer (requires_grad is false)");
+    if (count > t->numel()) throw Error(ZNN_ERR_INVALID, "read beyond the tensor");
+    check(znn_memcpy_d2h(host, src, count * sizeof(float)), "znn_memcpy_d2h");
+    ZNN_HOST_CATCH
+}
+
+int znn_graph_write(znn_graph* g, int id, int which, const float* host, size_t count)
+{
+    ZNN_HOST_TRY
+    Tensor* t = handle(g, id);
+    float* dst = which ? t->grad : t->data;
+    if (!dst) throw Error(ZNN_ERR_INVALID, "tensor has no gradient buffer (requires_grad is false)");
+    if (count > t->numel()) throw Error(ZNN_ERR_INVALID, "write beyond the tensor");
+    check(znn_memcpy_h2d(dst, host, count * sizeof(float)), "znn_memcpy_h2d");
+    check(znn_sync(), "znn_sync");
+    ZNN_HOST_CATCH
+}
+
+int znn_graph_num_ops(znn_graph* g, int* n)
+{
+    ZNN_HOST_TRY
+    if (n) *n = (int)g->g->ops().size();
+    ZNN_HOST_CATCH
+}
+
+}  // extern "C"
+
+// ------------------------------------------------------------------ models
+struct znn_model {
+    int kind = 0;
+    ParamStore ps;
+    std::unique_ptr<Arena> arena;
+    MlpNet mlp;
+    CnnNet cnn;
+    TransformerBlock block;
+    GPT gpt;
+    SGDOptimizer opt;
+    size_t in_features = 0, classes = 0;
+    size_t dp_bucket_floats = 8u << 20;  // 32 MB buckets
+    bool dp_overlap = true;
+    int last_ops = 0;
+    std::unordered_map<const Tensor*, int> param_index;
+};
+
+namespace {
+
+struct Bucket {
+    size_t begin, end;  // float range of the gradient slab
+    int pending;        // parameters whose gradient is not complete yet
+    bool fired;
+};
+
+// Starts the all-reduce of a gradient bucket as soon as the backward sweep has run
+// every op that writes into it.
+class DpSchedule {
+public:
+    DpSchedule(znn_model& m, const Graph& g) : m_(m)
+    {
+        const auto& ps = m.ps.params();
+        remaining_.assign(ps.size(), 0);
+        for (const Op* op : g.ops())
+            for (const Tensor* in : op->inputs) {
+                auto it = m.param_index.find(in);
+                if (it != m.param_index.end()) remaining_[it->second]++;
+            }
+        bucket_of_.assign(ps.size(), 0);
+        size_t begin = 0;
+        for (size_t i = 0; i < ps.size(); i++) {
+            const size_t end = (i + 1 < ps.size()) ? ps[i + 1].offset : m.ps.total();
+            bucket_of_[i] = (int)buckets_.size();
+            if (end - begin >= m.dp_bucket_floats || i + 1 == ps.size()) {
+                buckets_.push_back(Bucket{begin, end, 0, false});
+                begin = end;
+            }
+        }
+        for (size_t i = 0; i < ps.size(); i++)
+            if (remaining_[i] > 0) buckets_[bucket_of_[i]].pending++;
+    }
+
+    void after(Op* op)
+    {
+        for (const Tensor* in : op->inputs) {
+            auto it = m_.param_index.find(in);
+            if (it == m_.param_index.end()) continue;
+            if (--remaining_[it->second] == 0) {
+                Bucket& b = buckets_[bucket_of_[it->second]];
+                if (--b.pending == 0) fire(b);
+            }
+        }
+    }
+
+    void finish()
+    {
+        for (Bucket& b : buckets_)
+            if (!b.fired) fire(b);
+        check(znn_dp_join(), "znn_dp_join");
+    }
+
+    size_t buckets() const { return buckets_.size(); }
+
+private:
+    void fire(Bucket& b)
+    {
+        b.fired = true;
+        check(znn_dp_allreduce_async(m_.ps.grads() + b.begin, b.end - b.begin), "gradient all-reduce");
+    }
+    znn_model& m_;
+    std::vector<int> remaining_, bucket_of_;
+    std::vector<Bucket> buckets_;
+};
+
+Tensor* wrap_device(Graph& g, const Shape& s, const float* dev)
+{
+    // a graph input that lives in caller-owned device memory: no copy, no gradient
+    Tensor* t = g.tensorND(Shape{1}, false);
+    t->shape = s;
+    t->strides = contiguous_strides(s);
+    t->data = const_cast<float*>(dev);
+    return t;
+}
+
+Tensor* model_forward(znn_model& m, Graph& g, const float* x, int batch, int seq, bool on_device)
+{
+    Tensor* xt = nullptr;
+    switch (m.kind) {
+    case ZNN_MODEL_MLP:
+    case ZNN_MODEL_CNN_REF:
+    case ZNN_MODEL_CNN_PADDED: {
+        const Shape s{(size_t)batch, m.in_features};
+        xt = on_device ? wrap_device(g, s, x) : g.array(s, x, false);
+        return m.kind == ZNN_MODEL_MLP ? m.mlp.forward(g, xt) : m.cnn.forward(g, xt);
+    }
+    case ZNN_MODEL_GPT: {
+        const Shape s{(size_t)batch, (size_t)seq};
+        xt = on_device ? wrap_device(g, s, x) : g.array(s, x, false);
+        Tensor* logits = m.gpt.forward(g, xt);
+        return g.reshape(logits, Shape{(size_t)batch * seq, m.gpt.cfg.vocab_size});  // transformer_gpt.zig:90-92
+    }
+    default: throw Error(ZNN_ERR_INVALID, "this model kind has no classification forward");
+    }
+}
+
+}  // namespace
+
+extern "C" {
+
+int znn_model_create(int kind, const long long* dims, int ndims, size_t arena_bytes, znn_model** out)
+{
+    ZNN_HOST_TRY
+    if (!out) throw Error(ZNN_ERR_INVALID, "out is NULL");
+    auto need = [&](int n) {
+        if (ndims < n) throw Error(ZNN_ERR_INVALID, "too few dims for this model kind");
+    };
+    std::unique_ptr<znn_model> m(new znn_model());
+    m->kind = kind;
+    switch (kind) {
+    case ZNN_MODEL_MLP:
+        need(4);
+        m->mlp = MlpNet(m->ps, (size_t)dims[0], (size_t)dims[1], (size_t)dims[2], (size_t)dims[3]);
+        m->in_features = (size_t)dims[0];
+        m->classes = (size_t)dims[3];
+        break;
+    case ZNN_MODEL_CNN_REF:
+    case ZNN_MODEL_CNN_PADDED:
+        m->cnn = CnnNet(m->ps, kind == ZNN_MODEL_CNN_REF);
+        m->in_features = 784;
+        m->classes = 10;
+        break;
+    case ZNN_MODEL_BLOCK:
+        need(2);
+        m->block = TransformerBlock(m->ps, "block", (size_t)dims[0], (size_t)dims[1]);
+        m->in_features = (size_t)dims[0];
+        break;
+    case ZNN_MODEL_GPT: {
+        need(5);
+        GPTConfig c;
+        c.vocab_size = (size_t)dims[0];
+        c.block_size = (size_t)dims[1];
+        c.n_embd = (size_t)dims[2];
+        c.n_head = (size_t)dims[3];
+        c.n_layer = (size_t)dims[4];
+        if (c.n_head == 0 || c.n_embd % c.n_head != 0) throw Error(ZNN_ERR_INVALID, "n_embd must be a multiple of n_head");
+        m->gpt = GPT(m->ps, c);
+        m->classes = c.vocab_size;
+        break;
+    }
+    default: throw Error(ZNN_ERR_INVALID, "unknown model kind");
+    }
+    m->ps.finalize();
+    for (size_t i = 0; i < m->ps.params().size(); i++) m->param_index[m->ps.params()[i].tensor] = (int)i;
+    m->arena.reset(new Arena(arena_bytes));
+    m->opt.ps = &m->ps;
+    *out = m.release();
+    ZNN_HOST_CATCH
+}
+
+int znn_model_destroy(znn_model* m)
+{
+    ZNN_HOST_TRY
+    if (m) {
+        znn_sync();
+        delete m;
+    }
+    ZNN_HOST_CATCH
+}
+
+int znn_model_param_count(znn_model* m, int* n)
+{
+    ZNN_HOST_TRY
+    if (n) *n = (int)m->ps.params().size();
+    ZNN_HOST_CATCH
+}
+
+int znn_model_param_info(znn_model* m, int i, char* name, size_t name_len, long long* dims8, int* rank, long long* offset,
+                         long long* fan_in)
+{
+    ZNN_HOST_TRY
+    if (i < 0 || (size_t)i >= m->ps.params().size()) throw Error(ZNN_ERR_INVALID, "parameter index out of range");
+    const ParamInfo& p = m->ps.params()[i];
+    if (name && name_len) {
+        strncpy(name, p.name.c_str(), name_len - 1);
+        name[name_len - 1] = 0;
+    }
+    if (dims8)
+        for (size_t k = 0; k < p.tensor->shape.len; k++) dims8[k] = (long long)p.tensor->shape.dims[k];
+    if (rank) *rank = (int)p.tensor->shape.len;
+    if (offset) *offset = (long long)p.offset;
+    if (fan_in) *fan_in = (long long)p.fan_in;
+    ZNN_HOST_CATCH
+}
+
+int znn_model_total_floats(znn_model* m, long long* total)
+{
+    ZNN_HOST_TRY
+    if (total) *total = (long long)m->ps.total();
+    ZNN_HOST_CATCH
+}
+
+int znn_model_set_params(znn_model* m, const float* host_slab)
+{
+    ZNN_HOST_TRY
+    check(znn_memcpy_h2d(m->ps.values(), host_slab, m->ps.total() * sizeof(float)), "upload parameters");
+    check(znn_sync(), "znn_sync");
+    ZNN_HOST_CATCH
+}
+
+int znn_model_get_params(znn_model* m, float* host_slab)
+{
+    ZNN_HOST_TRY
+    check(znn_memcpy_d2h(host_slab, m->ps.values(), m->ps.total() * sizeof(float)), "download parameters");
+    ZNN_HOST_CATCH
+}
+
+int znn_model_get_grads(znn_model* m, float* host_slab)
+{
+    ZNN_HOST_TRY
+    check(znn_memcpy_d2h(host_slab, m->ps.grads(), m->ps.total() * sizeof(float)), "download gradients");
+    ZNN_HOST_CATCH
+}
+
+int znn_model_get_velocities(znn_model* m, float* host_slab)
+{
+    ZNN_HOST_TRY
+    check(znn_memcpy_d2h(host_slab, m->ps.velocities(), m->ps.total() * sizeof(float)), "download velocities");
+    ZNN_HOST_CATCH
+}
+
+int znn_model_set_option(znn_model* m, const char* key, double value)
+{
+    ZNN_HOST_TRY
+    const std::string k(key ? key : "");
+    if (k == "lr") m->opt.lr = (float)value;
+    else if (k == "momentum") m->opt.momentum = (float)value;
+    else if (k == "fused_softmax") {
+        m->gpt.set_fused_softmax(value != 0.0);
+        m->block.attn.fused_softmax = (value != 0.0);
+    } else if (k == "dp_bucket_floats") m->dp_bucket_floats = (size_t)value;
+    else if (k == "dp_overlap") m->dp_overlap = (value != 0.0);
+    else throw Error(ZNN_ERR_INVALID, "unknown option '" + k + "'");
+    ZNN_HOST_CATCH
+}
+
+int znn_model_train_step(znn_model* m, const float* x, const int32_t* targets, int batch, int seq, int on_device,
+                         float* loss_host)
+{
+    ZNN_HOST_TRY
+    if (batch <= 0) throw Error(ZNN_ERR_INVALID, "batch must be positive");
+    if (m->kind == ZNN_MODEL_GPT && seq <= 0) throw Error(ZNN_ERR_INVALID, "seq must be positive");
+    m->arena->reset();                       // Graph.init / graph.deinit of the previous batch
+    Graph g(m->arena.get());
+    const size_t rows = (m->kind == ZNN_MODEL_GPT) ? (size_t)batch * seq : (size_t)batch;
+    const int32_t* dev_targets = targets;
+    if (!on_device) {
+        int32_t* t = (int32_t*)m->arena->alloc(rows * sizeof(int32_t));
+        check(znn_memcpy_h2d(t, targets, rows * sizeof(int32_t)), "upload targets");
+        dev_targets = t;  // the stream synchronisation of the input upload below covers this copy
+    }
+    Tensor* logits = model_forward(*m, g, x, batch, seq, on_device != 0);
+    Tensor* loss = g.softmaxCrossEntropy(logits, dev_targets);
+    m->ps.zeroGrad();                        // model.zeroGrad() (fashion_mnist.zig:155)
+    int world = 1;
+    znn_dp_world(&world, nullptr);
+    if (world > 1) {
+        DpSchedule sched(*m, g);
+        if (m->dp_overlap) {
+            std::function<void(Op*)> hook = [&](Op* op) { sched.after(op); };
+            g.backward(loss, &hook);
+        } else {
+            g.backward(loss);
+        }
+        sched.finish();
+    } else {
+        g.backward(loss);
+    }
+    m->opt.step(1.0f / (float)world);        // optimizer.step(); 1/world turns the rank sum into the global mean
+    m->last_ops = (int)g.ops().size();
+    if (loss_host) check(znn_memcpy_d2h(loss_host, loss->data, sizeof(float)), "read loss");
+    ZNN_HOST_CATCH
+}
+
+int znn_model_forward(znn_model* m, const float* x, int batch, int seq, int on_device, float* logits_host)
+{
+    ZNN_HOST_TRY
+    m->arena->reset();
+    Graph g(m->arena.get());
+    Tensor* logits = model_forward(*m, g, x, batch, seq, on_device != 0);
+    if (logits_host) check(znn_memcpy_d2h(logits_host, logits->data, logits->numel() * sizeof(float)), "read logits");
+    ZNN_HOST_CATCH
+}
+
+int znn_model_block_fwd_bwd(znn_model* m, const float* x, const float* dy, int B, int T, float* y, float* dx)
+{
+    ZNN_HOST_TRY
+    if (m->kind != ZNN_MODEL_BLOCK) throw Error(ZNN_ERR_INVALID, "not a transformer block model");
+    m->arena->reset();
+    Graph g(m->arena.get());
+    const Shape s{(size_t)B, (size_t)T, m->in_features};
+    Tensor* xt = g.array(s, x, dx != nullptr);
+    Tensor* out = m->block.forward(g, xt);
+    if (y) check(znn_memcpy_d2h(y, out->data, out->numel() * sizeof(float)), "read y");
+    if (dy) {
+        m->ps.zeroGrad();
+        check(znn_memcpy_h2d(out->grad, dy, out->numel() * sizeof(float)), "upload dy");
+        check(znn_sync(), "znn_sync");
+        g.backwardWithGrad(out);
+        if (dx) check(znn_memcpy_d2h(dx, xt->grad, xt->numel() * sizeof(float)), "read dx");
+    }
+    m->last_ops = (int)g.ops().size();
+    ZNN_HOST_CATCH
+}
+
+int znn_model_greedy_decode(znn_model* m, const float* prompt_ids, int batch, int prompt_len, int n_new, float* out_ids)
+{
+    ZNN_HOST_TRY
+    if (m->kind != ZNN_MODEL_GPT) throw Error(ZNN_ERR_INVALID, "not a GPT model");
+    const size_t block = m->gpt.cfg.block_size, V = m->gpt.cfg.vocab_size;
+    std::vector<std::vector<float>> seqs(batch);
+    for (int b = 0; b < batch; b++) seqs[b].assign(prompt_ids + (size_t)b * prompt_len, prompt_ids + (size_t)(b + 1) * prompt_len);
+    void* p = nullptr;
+    check(znn_malloc(&p, (size_t)batch * sizeof(float)), "decode scratch");
+    float* next_dev = (float*)p;
+    std::vector<float> next(batch), window;
+    for (int step = 0; step < n_new; step++) {
+        const size_t len = seqs[0].size();
+        const size_t T = len < block ? len : block;  // last min(len, block_size) ids (transformer_gpt.zig:121-128)
+        window.resize((size_t)batch * T);
+        for (int b = 0; b < batch; b++)
+            memcpy(&window[(size_t)b * T], &seqs[b][len - T], T * sizeof(float));
+        m->arena->reset();
+        Graph g(m->arena.get());
+        Tensor* ids = g.array(Shape{(size_t)batch, T}, window.data(), false);
+        Tensor* logits = m->gpt.forward(g, ids);  // [batch, T, V]
+        for (int b = 0; b < batch; b++)           // first-maximum pick over the last position (:135-142)
+            check(znn_argmax(logits->data + ((size_t)b * T + (T - 1)) * V, next_dev + b, 1, (int)V, 1), "argmax");
+        check(znn_memcpy_d2h(next.data(), next_dev, (size_t)batch * sizeof(float)), "read tokens");
+        for (int b = 0; b < batch; b++) {
+            seqs[b].push_back(next[b]);
+            out_ids[(size_t)b * n_new + step] = next[b];
+        }
+    }
+    znn_free(next_dev);
+    ZNN_HOST_CATCH
+}
+
+int znn_model_arena_high_water(znn_model* m, long long* bytes)
+{
+    ZNN_HOST_TRY
+    if (bytes) *bytes = (long long)m->arena->high_water();
+    ZNN_HOST_CATCH
+}
+
+int znn_model_last_step_ops(znn_model* m, int* n_ops)
+{
+    ZNN_HOST_TRY
+    if (n_ops) *n_ops = m->last_ops;
+    ZNN_HOST_CATCH
+}
+
+}  // extern "C"

@@ -1,0 +1,589 @@
+// Host-side Tensor / Op / Graph mirror: see graph.hpp.  Bookkeeping only; every
+// arm forwards to the C ABI.
+#include "graph.hpp"
+
+#include <algorithm>
+#include <unordered_set>
+
+#include "../../../include/znn_cuda.h"
+
+namespace znn {
+namespace host {
+
+void check(int rc, const char* what)
+{
+    if (rc == 0) return;
+    char buf[512];
+    znn_last_error(buf, sizeof(buf));
+    throw Error(rc, std::string(what) + ": " + buf);
+}
+
+Shape::Shape(std::initializer_list<size_t> d)
+{
+    if (d.size() > 8) throw Error(ZNN_ERR_INVALID, "rank above 8");
+    for (size_t v : d) dims[len++] = v;
+}
+
+Shape::Shape(const size_t* d, size_t n)
+{
+    if (n > 8) throw Error(ZNN_ERR_INVALID, "rank above 8");
+    for (size_t i = 0; i < n; i++) dims[i] = d[i];
+    len = n;
+}
+
+size_t Shape::numel() const
+{
+    size_t t = 1;
+    for (size_t i = 0; i < len; i++) t *= dims[i];
+    return t;
+}
+
+bool Shape::operator==(const Shape& o) const
+{
+    if (len != o.len) return false;
+    for (size_t i = 0; i < len; i++)
+        if (dims[i] != o.dims[i]) return false;
+    return true;
+}
+
+Shape contiguous_strides(const Shape& s)
+{
+    Shape st;
+    st.len = s.len;
+    size_t acc = 1;
+    for (size_t i = s.len; i > 0;) {
+        i--;
+        st.dims[i] = acc;
+        acc *= s.dims[i];
+    }
+    return st;
+}
+
+// ---------------------------------------------------------------- Arena
+Arena::Arena(size_t bytes) : cap_(bytes)
+{
+    void* p = nullptr;
+    check(znn_malloc(&p, bytes), "Arena: znn_malloc");
+    base_ = (char*)p;
+}
+
+Arena::~Arena()
+{
+    if (base_) znn_free(base_);
+}
+
+void* Arena::alloc(size_t bytes)
+{
+    const size_t need = (bytes + 255) & ~(size_t)255;
+    if (used_ + need > cap_)
+        throw Error(ZNN_ERR_NOMEM, "graph arena exhausted: need " + std::to_string(used_ + need) + " of " +
+                                       std::to_string(cap_) + " bytes");
+    void* p = base_ + used_;
+    used_ += need;
+    if (used_ > high_) high_ = used_;
+    return p;
+}
+
+// ---------------------------------------------------------------- Graph
+Graph::~Graph()
+{
+    for (Tensor* t : tensors_) delete t;
+    for (Op* o : ops_) delete o;
+}
+
+Tensor* Graph::new_tensor(const Shape& shape, bool requires_grad, bool zero_data)
+{
+    Tensor* t = new Tensor();
+    t->shape = shape;
+    t->strides = contiguous_strides(shape);
+    t->requires_grad = requires_grad;
+    const size_t bytes = shape.numel() * sizeof(float);
+    t->data = (float*)arena_->alloc(bytes);
+    if (zero_data) check(znn_memset(t->data, 0, bytes), "znn_memset");
+    if (requires_grad) {
+        t->grad = (float*)arena_->alloc(bytes);
+        check(znn_memset(t->grad, 0, bytes), "znn_memset");
+    }
+    tensors_.push_back(t);
+    return t;
+}
+
+Op* Graph::new_op(OpType type, std::initializer_list<Tensor*> inputs, Tensor* out)
+{
+    Op* o = new Op();
+    o->type = type;
+    o->inputs.assign(inputs.begin(), inputs.end());
+    o->outputs.push_back(out);
+    out->creator = o;
+    ops_.push_back(o);
+    return o;
+}
+
+Tensor* Graph::tensorND(const Shape& shape, bool requires_grad) { return new_tensor(shape, requires_grad, true); }
+
+Tensor* Graph::array(const Shape& shape, const float* host_data, bool requires_grad)
+{
+    Tensor* t = new_tensor(shape, requires_grad, false);
+    check(znn_memcpy_h2d(t->data, host_data, shape.numel() * sizeof(float)), "znn_memcpy_h2d");
+    check(znn_sync(), "znn_sync");  // the host buffer may be a temporary
+    return t;
+}
+
+Tensor* Graph::arrayFromDevice(const Shape& shape, const float* dev_data, bool requires_grad)
+{
+    Tensor* t = new_tensor(shape, requires_grad, false);
+    check(znn_memcpy_d2d(t->data, dev_data, shape.numel() * sizeof(float)), "znn_memcpy_d2d");
+    return t;
+}
+
+static bool any_grad(std::initializer_list<Tensor*> ts)
+{
+    for (Tensor* t : ts)
+        if (t && t->requires_grad) return true;
+    return false;
+}
+
+Tensor* Graph::matmul(Tensor* A, Tensor* B)
+{
+    if (A->shape.len < 2 || B->shape.len < 2 || A->shape.dims[1] != B->shape.dims[0])
+        throw Error(ZNN_ERR_INVALID, "matmul: inner dimensions differ");
+    Tensor* C = new_tensor(Shape{A->shape.dims[0], B->shape.dims[1]}, any_grad({A, B}), false);
+    Op* o = new_op(OpType::MatMul, {A, B}, C);
+    o->forward();
+    return C;
+}
+
+Tensor* Graph::addBias(Tensor* A, Tensor* bias)
+{
+    Tensor* C = new_tensor(A->shape, any_grad({A, bias}), false);
+    new_op(OpType::AddBias, {A, bias}, C)->forward();
+    return C;
+}
+
+Tensor* Graph::relu(Tensor* A)
+{
+    Tensor* C = new_tensor(A->shape, A->requires_grad, false);
+    new_op(OpType::Relu, {A}, C)->forward();
+    return C;
+}
+
+Tensor* Graph::gelu(Tensor* A)
+{
+    Tensor* C = new_tensor(A->shape, A->requires_grad, false);
+    new_op(OpType::Gelu, {A}, C)->forward();
+    return C;
+}
+
+Tensor* Graph::softmaxCrossEntropy(Tensor* logits, const int32_t* dev_targets)
+{
+    if (logits->shape.len != 2) throw Error(ZNN_ERR_INVALID, "softmaxCrossEntropy needs 2-D logits");
+    Tensor* loss = new_tensor(Shape{1, 1}, logits->requires_grad, false);
+    Op* o = new_op(OpType::SoftmaxCrossEntropy, {logits}, loss);
+    o->probs = (float*)arena_->alloc(logits->numel() * sizeof(float));
+    o->targets = const_cast<int32_t*>(dev_targets);
+    o->forward();
+    return loss;
+}
+
+Tensor* Graph::reshape(Tensor* A, const Shape& new_shape)
+{
+    if (new_shape.numel() != A->numel()) throw Error(ZNN_ERR_INVALID, "reshape: element counts differ");
+    Tensor* C = new Tensor();
+    C->shape = new_shape;
+    C->strides = contiguous_strides(new_shape);
+    C->requires_grad = A->requires_grad;
+    C->data = A->data;  // shares the forward data (autodiff.zig:1346)
+    if (A->requires_grad) {
+        C->grad = (float*)arena_->alloc(A->numel() * sizeof(float));
+        check(znn_memset(C->grad, 0, A->numel() * sizeof(float)), "znn_memset");
+    }
+    tensors_.push_back(C);
+    new_op(OpType::Reshape, {A}, C);
+    return C;
+}
+
+Tensor* Graph::transposeND(Tensor* A, int dim0, int dim1)
+{
+    if (dim0 < 0 || dim1 < 0 || (size_t)dim0 >= A->shape.len || (size_t)dim1 >= A->shape.len)
+        throw Error(ZNN_ERR_INVALID, "transposeND: dimension out of range");
+    Shape s = A->shape;
+    std::swap(s.dims[dim0], s.dims[dim1]);
+    Tensor* C = new_tensor(s, A->requires_grad, false);
+    Op* o = new_op(OpType::Transpose, {A}, C);
+    o->dim0 = dim0;
+    o->dim1 = dim1;
+    o->forward();
+    return C;
+}
+
+Tensor* Graph::mulScalar(Tensor* A, float v)
+{
+    Tensor* C = new_tensor(A->shape, A->requires_grad, false);
+    Op* o = new_op(OpType::MulScalar, {A}, C);
+    o->scalar = v;
+    o->forward();
+    return C;
+}
+
+Tensor* Graph::add(Tensor* A, Tensor* B)
+{
+    if (A->numel() != B->numel()) throw Error(ZNN_ERR_INVALID, "add: sizes differ");
+    Tensor* C = new_tensor(A->shape, any_grad({A, B}), false);
+    new_op(OpType::Add, {A, B}, C)->forward();
+    return C;
+}
+
+Tensor* Graph::conv2d(Tensor* A, Tensor* W, Tensor* bias, int pad)
+{
+    if (A->shape.len != 4 || W->shape.len != 4 || A->shape.dims[1] != W->shape.dims[1])
+        throw Error(ZNN_ERR_INVALID, "conv2d: need NCHW input and [Co,Ci,KH,KW] weights with matching Ci");
+    const size_t Ho = A->shape.dims[2] + 2 * pad - W->shape.dims[2] + 1;
+    const size_t Wo = A->shape.dims[3] + 2 * pad - W->shape.dims[3] + 1;
+    Tensor* C = new_tensor(Shape{A->shape.dims[0], W->shape.dims[0], Ho, Wo}, any_grad({A, W, bias}), false);
+    Op* o = bias ? new_op(OpType::Conv2D, {A, W, bias}, C) : new_op(OpType::Conv2D, {A, W}, C);
+    o->pad = pad;
+    o->forward();
+    return C;
+}
+
+Tensor* Graph::maxpool2d(Tensor* A, int pool, int stride)
+{
+    if (A->shape.len != 4 || pool <= 0 || stride <= 0) throw Error(ZNN_ERR_INVALID, "maxpool2d: bad arguments");
+    Tensor* C = new_tensor(Shape{A->shape.dims[0], A->shape.dims[1], A->shape.dims[2] / stride, A->shape.dims[3] / stride},
+                           A->requires_grad, false);
+    Op* o = new_op(OpType::MaxPool2D, {A}, C);
+    o->pool = pool;
+    o->stride = stride;
+    o->forward();
+    return C;
+}
+
+Tensor* Graph::softmax(Tensor* A)
+{
+    Tensor* C = new_tensor(A->shape, A->requires_grad, false);
+    new_op(OpType::Softmax, {A}, C)->forward();
+    return C;
+}
+
+Tensor* Graph::causalSoftmax(Tensor* S, float scale)
+{
+    if (S->shape.len < 2 || S->shape.dims[S->shape.len - 1] != S->shape.dims[S->shape.len - 2])
+        throw Error(ZNN_ERR_INVALID, "causalSoftmax: the last two dimensions must be equal");
+    Tensor* C = new_tensor(S->shape, S->requires_grad, false);
+    Op* o = new_op(OpType::CausalSoftmax, {S}, C);
+    o->scalar = scale;
+    o->forward();
+    return C;
+}
+
+Tensor* Graph::rmsNorm(Tensor* X, Tensor* G, float eps)
+{
+    Tensor* Y = new_tensor(X->shape, any_grad({X, G}), false);
+    Op* o = new_op(OpType::RmsNorm, {X, G}, Y);
+    o->scalar = eps;
+    o->forward();
+    return Y;
+}
+
+Tensor* Graph::layerNorm(Tensor* X, Tensor* G, Tensor* B, float eps)
+{
+    Tensor* Y = new_tensor(X->shape, any_grad({X, G, B}), false);
+    Op* o = new_op(OpType::LayerNorm, {X, G, B}, Y);
+    o->scalar = eps;
+    o->forward();
+    return Y;
+}
+
+Tensor* Graph::batchMatMul(Tensor* A, Tensor* B)
+{
+    if (A->shape.len != 4 || B->shape.len != 4 || A->shape.dims[3] != B->shape.dims[2] ||
+        A->shape.dims[0] != B->shape.dims[0] || A->shape.dims[1] != B->shape.dims[1])
+        throw Error(ZNN_ERR_INVALID, "batchMatMul: need [b,h,M,K] x [b,h,K,N]");
+    Tensor* C = new_tensor(Shape{A->shape.dims[0], A->shape.dims[1], A->shape.dims[2], B->shape.dims[3]},
+                           any_grad({A, B}), false);
+    new_op(OpType::BatchMatMul, {A, B}, C)->forward();
+    return C;
+}
+
+Tensor* Graph::embedding(Tensor* W, Tensor* X)
+{
+    if (W->shape.len != 2 || X->shape.len != 2) throw Error(ZNN_ERR_INVALID, "embedding: W [V,D], ids [B,T]");
+    Tensor* Y = new_tensor(Shape{X->shape.dims[0], X->shape.dims[1], W->shape.dims[1]}, W->requires_grad, false);
+    new_op(OpType::Embedding, {W, X}, Y)->forward();
+    return Y;
+}
+
+// ---------------------------------------------------------------- Op arms
+static int64_t* dims64(const Shape& s, int64_t* buf)
+{
+    for (size_t i = 0; i < s.len; i++) buf[i] = (int64_t)s.dims[i];
+    return buf;
+}
+
+void Op::forward()
+{
+    Tensor* A = inputs[0];
+    Tensor* C = outputs[0];
+    switch (type) {
+    case OpType::MatMul: {
+        Tensor* B = inputs[1];
+        const int M = (int)A->shape.dims[0], K = (int)A->shape.dims[1], N = (int)B->shape.dims[1];
+        check(znn_sgemm(ZNN_ROW_MAJOR, ZNN_NO_TRANS, ZNN_NO_TRANS, M, N, K, 1.0f, A->data, K, B->data, N, 0.0f, C->data, N),
+              "MatMul forward");
+        break;
+    }
+    case OpType::AddBias:
+        check(znn_add_bias_fwd(A->data, inputs[1]->data, C->data, (int)A->shape.dims[0], (int)A->shape.dims[1]), "AddBias forward");
+        break;
+    case OpType::Relu: check(znn_relu_fwd(A->data, C->data, A->numel()), "Relu forward"); break;
+    case OpType::Gelu: check(znn_gelu_fwd(A->data, C->data, A->numel()), "Gelu forward"); break;
+    case OpType::SoftmaxCrossEntropy:
+        check(znn_softmax_xent_fwd(A->data, targets, probs, C->data, (int)A->shape.dims[0], (int)A->shape.dims[1]),
+              "SoftmaxCrossEntropy forward");
+        break;
+    case OpType::Reshape: break;  // aliased data (autodiff.zig:272-275)
+    case OpType::Transpose: {
+        int64_t d[8];
+        check(znn_transpose_fwd(A->data, C->data, dims64(A->shape, d), (int)A->shape.len, dim0, dim1), "Transpose forward");
+        break;
+    }
+    case OpType::MulScalar: check(znn_mul_scalar_fwd(A->data, scalar, C->data, A->numel()), "MulScalar forward"); break;
+    case OpType::Add: check(znn_add_fwd(A->data, inputs[1]->data, C->data, A->numel()), "Add forward"); break;
+    case OpType::Conv2D: {
+        Tensor* W = inputs[1];
+        const float* b = inputs.size() > 2 ? inputs[2]->data : nullptr;
+        check(znn_conv2d_fwd(A->data, W->data, b, C->data, (int)A->shape.dims[0], (int)A->shape.dims[1], (int)A->shape.dims[2],
+                             (int)A->shape.dims[3], (int)W->shape.dims[0], (int)W->shape.dims[2], (int)W->shape.dims[3], pad),
+              "Conv2D forward");
+        break;
+    }
+    case OpType::MaxPool2D:
+        check(znn_maxpool2d_fwd(A->data, C->data, nullptr, (int)A->shape.dims[0], (int)A->shape.dims[1], (int)A->shape.dims[2],
+                                (int)A->shape.dims[3], pool, stride),
+              "MaxPool2D forward");
+        break;
+    case OpType::Softmax: {
+        const int D = (int)A->shape.dims[A->shape.len - 1];
+        check(znn_softmax_fwd(A->data, C->data, A->numel() / D, D), "Softmax forward");
+        break;
+    }
+    case OpType::CausalSoftmax: {
+        const int T = (int)A->shape.dims[A->shape.len - 1];
+        check(znn_causal_softmax_fwd(A->data, scalar, C->data, (int)(A->numel() / ((size_t)T * T)), T), "CausalSoftmax forward");
+        break;
+    }
+    case OpType::RmsNorm: {
+        const int D = (int)A->shape.dims[A->shape.len - 1];
+        check(znn_rmsnorm_fwd(A->data, inputs[1]->data, scalar, C->data, A->numel() / D, D), "RmsNorm forward");
+        break;
+    }
+    case OpType::LayerNorm: {
+        const int D = (int)A->shape.dims[A->shape.len - 1];
+        check(znn_layernorm_fwd(A->data, inputs[1]->data, inputs[2]->data, scalar, C->data, A->numel() / D, D), "LayerNorm forward");
+        break;
+    }
+    case OpType::BatchMatMul: {
+        Tensor* B = inputs[1];
+        const int nb = (int)(A->shape.dims[0] * A->shape.dims[1]);
+        const int M = (int)A->shape.dims[2], K = (int)A->shape.dims[3], N = (int)B->shape.dims[3];
+        check(znn_sgemm_batched_strided(ZNN_NO_TRANS, ZNN_NO_TRANS, M, N, K, 1.0f, A->data, K, (long long)M * K, B->data, N,
+                                        (long long)K * N, 0.0f, C->data, N, (long long)M * N, nb),
+              "BatchMatMul forward");
+        break;
+    }
+    case OpType::Embedding: {
+        Tensor* W = inputs[0];
+        Tensor* X = inputs[1];
+        check(znn_embedding_fwd(W->data, X->data, C->data, X->numel(), (int)W->shape.dims[1], (int)W->shape.dims[0]),
+              "Embedding forward");
+        break;
+    }
+    }
+}
+
+void Op::backward()
+{
+    Tensor* A = inputs[0];
+    Tensor* C = outputs[0];
+    switch (type) {
+    case OpType::MatMul: {
+        Tensor* B = inputs[1];
+        const int M = (int)A->shape.dims[0], K = (int)A->shape.dims[1], N = (int)B->shape.dims[1];
+        if (A->requires_grad)  // dA += dC . B^T (autodiff.zig:602-620)
+            check(znn_sgemm(ZNN_ROW_MAJOR, ZNN_NO_TRANS, ZNN_TRANS, M, K, N, 1.0f, C->grad, N, B->data, N, 1.0f, A->grad, K),
+                  "MatMul backward dA");
+        if (B->requires_grad)  // dB += A^T . dC (:623-640)
+            check(znn_sgemm(ZNN_ROW_MAJOR, ZNN_TRANS, ZNN_NO_TRANS, K, N, M, 1.0f, A->data, K, C->grad, N, 1.0f, B->grad, N),
+                  "MatMul backward dB");
+        break;
+    }
+    case OpType::AddBias:
+        check(znn_add_bias_bwd(C->grad, A->requires_grad ? A->grad : nullptr, inputs[1]->requires_grad ? inputs[1]->grad : nullptr,
+                               (int)A->shape.dims[0], (int)A->shape.dims[1]),
+              "AddBias backward");
+        break;
+    case OpType::Relu:
+        if (A->requires_grad) check(znn_relu_bwd(A->data, C->grad, A->grad, A->numel()), "Relu backward");
+        break;
+    case OpType::Gelu:
+        if (A->requires_grad) check(znn_gelu_bwd(A->data, C->grad, A->grad, A->numel()), "Gelu backward");
+        break;
+    case OpType::SoftmaxCrossEntropy:
+        // ignores loss.grad and has no requires_grad gate, as the reference (:758-774); a logits
+        // tensor without a grad buffer simply has nothing to receive it
+        if (A->grad)
+            check(znn_softmax_xent_bwd(probs, targets, A->grad, (int)A->shape.dims[0], (int)A->shape.dims[1]),
+                  "SoftmaxCrossEntropy backward");
+        break;
+    case OpType::Reshape:
+        if (A->requires_grad) check(znn_accumulate(C->grad, A->grad, A->numel()), "Reshape backward");
+        break;
+    case OpType::Transpose:
+        if (A->requires_grad) {
+            int64_t d[8];
+            check(znn_transpose_bwd(C->grad, A->grad, dims64(A->shape, d), (int)A->shape.len, dim0, dim1), "Transpose backward");
+        }
+        break;
+    case OpType::MulScalar:
+        if (A->requires_grad) check(znn_mul_scalar_bwd(C->grad, scalar, A->grad, A->numel()), "MulScalar backward");
+        break;
+    case OpType::Add:
+        if (A->requires_grad) check(znn_accumulate(C->grad, A->grad, A->numel()), "Add backward");
+        if (inputs[1]->requires_grad) check(znn_accumulate(C->grad, inputs[1]->grad, A->numel()), "Add backward");
+        break;
+    case OpType::Conv2D: {
+        Tensor* W = inputs[1];
+        Tensor* b = inputs.size() > 2 ? inputs[2] : nullptr;
+        check(znn_conv2d_bwd(A->data, W->data, C->grad, A->requires_grad ? A->grad : nullptr, W->requires_grad ? W->grad : nullptr,
+                             (b && b->requires_grad) ? b->grad : nullptr, (int)A->shape.dims[0], (int)A->shape.dims[1],
+                             (int)A->shape.dims[2], (int)A->shape.dims[3], (int)W->shape.dims[0], (int)W->shape.dims[2],
+                             (int)W->shape.dims[3], pad),
+              "Conv2D backward");
+        break;
+    }
+    case OpType::MaxPool2D:
+        if (A->requires_grad)
+            check(znn_maxpool2d_bwd(A->data, C->grad, A->grad, (int)A->shape.dims[0], (int)A->shape.dims[1], (int)A->shape.dims[2],
+                                    (int)A->shape.dims[3], pool, stride),
+                  "MaxPool2D backward");
+        break;
+    case OpType::Softmax:
+        if (A->requires_grad) {
+            const int D = (int)A->shape.dims[A->shape.len - 1];
+            check(znn_softmax_bwd(C->data, C->grad, A->grad, A->numel() / D, D), "Softmax backward");
+        }
+        break;
+    case OpType::CausalSoftmax:
+        if (A->requires_grad) {
+            const int T = (int)A->shape.dims[A->shape.len - 1];
+            check(znn_causal_softmax_bwd(C->data, C->grad, scalar, A->grad, (int)(A->numel() / ((size_t)T * T)), T),
+                  "CausalSoftmax backward");
+        }
+        break;
+    case OpType::RmsNorm: {
+        Tensor* G = inputs[1];
+        const int D = (int)A->shape.dims[A->shape.len - 1];
+        check(znn_rmsnorm_bwd(A->data, G->data, C->grad, scalar, A->requires_grad ? A->grad : nullptr,
+                              G->requires_grad ? G->grad : nullptr, A->numel() / D, D),
+              "RmsNorm backward");
+        break;
+    }
+    case OpType::LayerNorm: {
+        Tensor* G = inputs[1];
+        Tensor* B = inputs[2];
+        const int D = (int)A->shape.dims[A->shape.len - 1];
+        check(znn_layernorm_bwd(A->data, G->data, C->grad, scalar, A->requires_grad ? A->grad : nullptr,
+                                G->requires_grad ? G->grad : nullptr, B->requires_grad ? B->grad : nullptr, A->numel() / D, D),
+              "LayerNorm backward");
+        break;
+    }
+    case OpType::BatchMatMul: {
+        Tensor* B = inputs[1];
+        const int nb = (int)(A->shape.dims[0] * A->shape.dims[1]);
+        const int M = (int)A->shape.dims[2], K = (int)A->shape.dims[3], N = (int)B->shape.dims[3];
+        if (A->requires_grad)
+            check(znn_sgemm_batched_strided(ZNN_NO_TRANS, ZNN_TRANS, M, K, N, 1.0f, C->grad, N, (long long)M * N, B->data, N,
+                                            (long long)K * N, 1.0f, A->grad, K, (long long)M * K, nb),
+                  "BatchMatMul backward dA");
+        if (B->requires_grad)
+            check(znn_sgemm_batched_strided(ZNN_TRANS, ZNN_NO_TRANS, K, N, M, 1.0f, A->data, K, (long long)M * K, C->grad, N,
+                                            (long long)M * N, 1.0f, B->grad, N, (long long)K * N, nb),
+                  "BatchMatMul backward dB");
+        break;
+    }
+    case OpType::Embedding: {
+        Tensor* W = inputs[0];
+        Tensor* X = inputs[1];
+        if (W->requires_grad)
+            check(znn_embedding_bwd(X->data, C->grad, W->grad, X->numel(), (int)W->shape.dims[1], (int)W->shape.dims[0]),
+                  "Embedding backward");
+        break;
+    }
+    }
+}
+
+// ---------------------------------------------------------------- sweeps
+static void topo(Tensor* node, std::unordered_set<Tensor*>& seen, std::vector<Tensor*>& out)
+{
+    // iterative DFS post-order, inputs visited in order (autodiff.zig:2239-2249)
+    struct Frame { Tensor* t; size_t next; };
+    std::vector<Frame> stack;
+    if (!seen.insert(node).second) return;
+    stack.push_back({node, 0});
+    while (!stack.empty()) {
+        Frame& f = stack.back();
+        Op* op = f.t->creator;
+        if (op && f.next < op->inputs.size()) {
+            Tensor* in = op->inputs[f.next++];
+            if (seen.insert(in).second) stack.push_back({in, 0});
+        } else {
+            out.push_back(f.t);
+            stack.pop_back();
+        }
+    }
+}
+
+void Graph::sweep(Tensor* root, const std::function<void(Op*)>* after_op)
+{
+    std::unordered_set<Tensor*> seen;
+    std::vector<Tensor*> order;
+    topo(root, seen, order);
+    for (size_t i = order.size(); i > 0;) {
+        i--;
+        Op* op = order[i]->creator;
+        if (op) {
+            op->backward();
+            if (after_op) (*after_op)(op);
+        }
+    }
+}
+
+void Graph::backward(Tensor* loss, const std::function<void(Op*)>* after_op)
+{
+    if (!loss->grad) throw Error(ZNN_ERR_INVALID, "backward: the loss tensor has no gradient buffer");
+    check(znn_fill(loss->grad, 1.0f, 1), "seed loss gradient");  // loss.grad[0] = 1 (autodiff.zig:2203)
+    sweep(loss, after_op);
+}
+
+void Graph::backwardWithGrad(Tensor* out, const std::function<void(Op*)>* after_op) { sweep(out, after_op); }
+
+void Graph::forward()
+{
+    for (Op* o : ops_) o->forward();
+}
+
+void Graph::zeroGrad()
+{
+    for (Tensor* t : tensors_)
+        if (t->grad) check(znn_memset(t->grad, 0, t->numel() * sizeof(float)), "znn_memset");
+}
+
+size_t Graph::op_index(const Op* op) const
+{
+    for (size_t i = 0; i < ops_.size(); i++)
+        if (ops_[i] == op) return i;
+    return (size_t)-1;
+}
+
+}  // namespace host
+}  // namespace znn

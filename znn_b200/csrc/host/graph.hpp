@@ -1,0 +1,151 @@
+// Host-side mirror of the reference's Tensor / Op / Graph (src/tensor.zig:14-88,
+// src/autodiff.zig:14-105, :1237-2264) over device memory.
+//
+// Same names and semantics as the reference: every Graph builder runs the eager
+// forward, sets requires_grad to the OR of its inputs, allocates a zeroed grad,
+// and appends an Op to the tape; backward() sorts topologically from the loss
+// (DFS post-order over creator.inputs), seeds loss.grad[0] = 1 and sweeps in
+// reverse calling each creator's backward arm, which ACCUMULATES into its
+// inputs' grads.  All arithmetic is done by the C ABI of include/znn_cuda.h;
+// this layer is bookkeeping only.
+#pragma once
+#include <stddef.h>
+#include <stdint.h>
+
+#include <functional>
+#include <initializer_list>
+#include <stdexcept>
+#include <string>
+#include <vector>
+
+namespace znn {
+namespace host {
+
+struct Error : std::runtime_error {
+    int code;
+    Error(int c, const std::string& what) : std::runtime_error(what), code(c) {}
+};
+// throws Error when rc != 0 (text from znn_last_error)
+void check(int rc, const char* what);
+
+// src/tensor.zig:14-39
+struct Shape {
+    size_t dims[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+    size_t len = 0;
+    Shape() = default;
+    Shape(std::initializer_list<size_t> d);
+    Shape(const size_t* d, size_t n);
+    size_t numel() const;
+    bool operator==(const Shape& o) const;
+};
+Shape contiguous_strides(const Shape& s);  // src/tensor.zig:49-65
+
+struct Op;
+
+// src/tensor.zig:81-88: data / grad are DEVICE pointers here
+struct Tensor {
+    float* data = nullptr;
+    float* grad = nullptr;  // nullptr when !requires_grad (the reference's empty slice)
+    Shape shape, strides;
+    bool requires_grad = false;
+    Op* creator = nullptr;
+    size_t numel() const { return shape.numel(); }
+};
+
+// hot-path subset of src/autodiff.zig:14-40, plus two additions
+enum class OpType {
+    MatMul, AddBias, Relu, Gelu, SoftmaxCrossEntropy, Reshape, Transpose, MulScalar, Add, Conv2D, MaxPool2D,
+    Softmax, RmsNorm, BatchMatMul, Embedding,
+    CausalSoftmax,  // fused mulScalar + mask add + softmax of src/nn.zig:835-886 (an addition)
+    LayerNorm       // extension, no reference counterpart
+};
+
+// src/autodiff.zig:100-105 (OpContext flattened)
+struct Op {
+    OpType type;
+    std::vector<Tensor*> inputs, outputs;
+    float scalar = 0.0f;        // MulScalar value / RmsNorm eps / CausalSoftmax scale
+    int dim0 = 0, dim1 = 0;     // Transpose
+    int pool = 0, stride = 0;   // MaxPool2D
+    int pad = 0;                // Conv2D (0 = reference)
+    float* probs = nullptr;     // SoftmaxCrossEntropy: device M x N
+    int32_t* targets = nullptr; // SoftmaxCrossEntropy: device int32 labels
+    void forward();             // src/autodiff.zig:107-575
+    void backward();            // src/autodiff.zig:579-1231
+};
+
+// Device bump allocator: the analogue of Graph.arena (std.heap.ArenaAllocator).
+// reset() makes every allocation of the previous step reusable at once.
+class Arena {
+public:
+    explicit Arena(size_t bytes);
+    ~Arena();
+    Arena(const Arena&) = delete;
+    Arena& operator=(const Arena&) = delete;
+    void* alloc(size_t bytes);  // 256-byte aligned; throws Error(ZNN_ERR_NOMEM) when exhausted
+    void reset() { used_ = 0; }
+    size_t used() const { return used_; }
+    size_t high_water() const { return high_; }
+    size_t capacity() const { return cap_; }
+
+private:
+    char* base_ = nullptr;
+    size_t cap_ = 0, used_ = 0, high_ = 0;
+};
+
+// src/autodiff.zig:1237-2264
+class Graph {
+public:
+    explicit Graph(Arena* arena) : arena_(arena) {}
+    ~Graph();
+    Graph(const Graph&) = delete;
+    Graph& operator=(const Graph&) = delete;
+
+    // creators (:1260-1326)
+    Tensor* tensorND(const Shape& shape, bool requires_grad);
+    Tensor* array(const Shape& shape, const float* host_data, bool requires_grad);      // uploads
+    Tensor* arrayFromDevice(const Shape& shape, const float* dev_data, bool requires_grad);
+
+    // builders
+    Tensor* matmul(Tensor* A, Tensor* B);                                   // :1414
+    Tensor* addBias(Tensor* A, Tensor* bias);                               // :1446
+    Tensor* relu(Tensor* A);                                                // :1478
+    Tensor* gelu(Tensor* A);                                                // :1508
+    Tensor* softmaxCrossEntropy(Tensor* logits, const int32_t* dev_targets); // :1630 (int32 labels on device)
+    Tensor* reshape(Tensor* A, const Shape& new_shape);                     // :1329 (aliases data, own grad)
+    Tensor* transposeND(Tensor* A, int dim0, int dim1);                     // :1378
+    Tensor* mulScalar(Tensor* A, float v);                                  // :1910
+    Tensor* add(Tensor* A, Tensor* B);                                      // :1972
+    Tensor* conv2d(Tensor* A, Tensor* W, Tensor* bias, int pad = 0);        // :2003
+    Tensor* maxpool2d(Tensor* A, int pool, int stride);                     // :2038
+    Tensor* softmax(Tensor* A);                                             // :2068
+    Tensor* rmsNorm(Tensor* X, Tensor* G, float eps);                       // :2098
+    Tensor* batchMatMul(Tensor* A, Tensor* B);                              // :2129
+    Tensor* embedding(Tensor* W, Tensor* X);                                // :2160
+    Tensor* causalSoftmax(Tensor* S, float scale);                          // fused addition
+    Tensor* layerNorm(Tensor* X, Tensor* G, Tensor* B, float eps);          // extension
+
+    // `after_op(op)` is called after a tape op has run its
+    // backward arm; data-parallel training uses it to start gradient all-reduces.
+    void backward(Tensor* loss, const std::function<void(Op*)>* after_op = nullptr);   // :2192
+    void backwardWithGrad(Tensor* out, const std::function<void(Op*)>* after_op = nullptr); // :2217
+    void forward();    // :2252 re-executes the tape in creation order
+    void zeroGrad();   // :2259
+
+    const std::vector<Op*>& ops() const { return ops_; }
+    const std::vector<Tensor*>& tensors() const { return tensors_; }
+    Arena* arena() { return arena_; }
+    // index of `op` in the tape (creation order)
+    size_t op_index(const Op* op) const;
+
+private:
+    Tensor* new_tensor(const Shape& shape, bool requires_grad, bool zero_data);
+    Op* new_op(OpType type, std::initializer_list<Tensor*> inputs, Tensor* out);
+    void sweep(Tensor* root, const std::function<void(Op*)>* after_op);
+    Arena* arena_;
+    std::vector<Tensor*> tensors_;
+    std::vector<Op*> ops_;
+};
+
+}  // namespace host
+}  // namespace znn

@@ -1,0 +1,114 @@
+"""Python view of the host mirror's models (include/znn_host.h, znn_model_*): the
+reference's example programs (MLP, CNN, transformer block, GPT) with their
+training step, run entirely by the C++ host mirror over the CUDA kernels."""
+import ctypes as C
+
+import numpy as np
+
+from ._lib import lib
+
+KINDS = {"mlp": 1, "cnn_ref": 2, "cnn_padded": 3, "block": 4, "gpt": 5}
+
+
+class Model:
+    def __init__(self, kind, dims=(), arena_bytes=1 << 30):
+        self.kind = kind
+        d = (C.c_longlong * max(1, len(dims)))(*dims)
+        h = C.c_void_p()
+        lib().call("znn_model_create", KINDS[kind], d, len(dims), arena_bytes, C.byref(h))
+        self.h = h
+        n = C.c_int()
+        lib().call("znn_model_param_count", self.h, C.byref(n))
+        self.params = []   # (name, shape, offset, fan_in)
+        for i in range(n.value):
+            name = C.create_string_buffer(128)
+            dims8 = (C.c_longlong * 8)()
+            rank, off, fan = C.c_int(), C.c_longlong(), C.c_longlong()
+            lib().call("znn_model_param_info", self.h, i, name, 128, dims8, C.byref(rank), C.byref(off), C.byref(fan))
+            self.params.append((name.value.decode(), tuple(int(dims8[k]) for k in range(rank.value)), off.value, fan.value))
+        t = C.c_longlong()
+        lib().call("znn_model_total_floats", self.h, C.byref(t))
+        self.total = t.value
+
+    def close(self):
+        if self.h:
+            lib().call("znn_model_destroy", self.h)
+            self.h = None
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+    # ---- parameters as dicts name -> array
+    def _pack(self, P):
+        slab = np.zeros(self.total, np.float32)
+        for name, shape, off, _ in self.params:
+            a = np.asarray(P[name], np.float32)
+            assert a.size == int(np.prod(shape)), (name, a.shape, shape)
+            slab[off:off + a.size] = a.reshape(-1)
+        return slab
+
+    def _unpack(self, slab):
+        return {name: slab[off:off + int(np.prod(shape))].reshape(shape).copy() for name, shape, off, _ in self.params}
+
+    def set_params(self, P):
+        slab = self._pack(P)
+        lib().call("znn_model_set_params", self.h, slab.ctypes.data)
+
+    def _get(self, fn):
+        slab = np.empty(self.total, np.float32)
+        lib().call(fn, self.h, slab.ctypes.data)
+        return self._unpack(slab)
+
+    def get_params(self): return self._get("znn_model_get_params")
+    def get_grads(self): return self._get("znn_model_get_grads")
+    def get_velocities(self): return self._get("znn_model_get_velocities")
+
+    def set_option(self, key, value):
+        lib().call("znn_model_set_option", self.h, key.encode(), float(value))
+
+    def train_step(self, x, targets, seq=0, read_loss=True):
+        x = np.ascontiguousarray(x, np.float32)
+        t = np.ascontiguousarray(targets, np.int32)
+        batch = x.shape[0]
+        loss = C.c_float()
+        lib().call("znn_model_train_step", self.h, x.ctypes.data, t.ctypes.data, batch, seq, 0,
+                   C.byref(loss) if read_loss else None)
+        return loss.value if read_loss else None
+
+    def train_step_device(self, x_ptr, t_ptr, batch, seq=0, loss_ptr=None):
+        lib().call("znn_model_train_step", self.h, x_ptr, t_ptr, batch, seq, 1, loss_ptr)
+
+    def forward(self, x, seq=0, classes=None):
+        x = np.ascontiguousarray(x, np.float32)
+        batch = x.shape[0]
+        rows = batch * (seq if seq else 1)
+        out = np.empty((rows, classes), np.float32)
+        lib().call("znn_model_forward", self.h, x.ctypes.data, batch, seq, 0, out.ctypes.data)
+        return out
+
+    def block_fwd_bwd(self, x, dy):
+        x = np.ascontiguousarray(x, np.float32)
+        dy = np.ascontiguousarray(dy, np.float32)
+        B, T, _ = x.shape
+        y, dx = np.empty_like(x), np.empty_like(x)
+        lib().call("znn_model_block_fwd_bwd", self.h, x.ctypes.data, dy.ctypes.data, B, T, y.ctypes.data, dx.ctypes.data)
+        return y, dx
+
+    def greedy_decode(self, prompts, n_new):
+        p = np.ascontiguousarray(prompts, np.float32)
+        out = np.empty((p.shape[0], n_new), np.float32)
+        lib().call("znn_model_greedy_decode", self.h, p.ctypes.data, p.shape[0], p.shape[1], n_new, out.ctypes.data)
+        return out
+
+    def last_step_ops(self):
+        n = C.c_int()
+        lib().call("znn_model_last_step_ops", self.h, C.byref(n))
+        return n.value
+
+    def arena_high_water(self):
+        b = C.c_longlong()
+        lib().call("znn_model_arena_high_water", self.h, C.byref(b))
+        return b.value
