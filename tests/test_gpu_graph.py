@@ -17,9 +17,9 @@ def G():
     return Graph
 
 
-def close(a, b, rtol=1e-5, what=""):
+def close(a, b, rtol=1e-5, what="", floor=0.0):
     a, b = np.asarray(a, np.float64), np.asarray(b, np.float64)
-    scale = max(1e-30, float(np.abs(b).max()))
+    scale = max(1e-30, float(np.abs(b).max()), floor)
     err = float(np.abs(a - b).max())
     assert err <= rtol * scale + 1e-12, f"{what}: {err:.3e} vs scale {scale:.3e}"
 
@@ -135,5 +135,8 @@ def test_transformer_block_matches_cpu_graph(G):
     (y0, dx0, g0), (y1, dx1, g1) = outs
     close(y1, y0, what="block output")
     close(dx1, dx0, rtol=3e-5, what="block dx")
+    # the key-bias gradient is zero in exact arithmetic (softmax cancels a per-row shift): compare
+    # such tensors on the scale of their neighbours
+    floor = 1e-2 * max(float(np.abs(v).max()) for v in g0.values())
     for k in g0:
-        close(g1[k], g0[k], rtol=3e-5, what=k)
+        close(g1[k], g0[k], rtol=3e-5, what=k, floor=floor)

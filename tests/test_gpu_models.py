@@ -23,11 +23,18 @@ def pixels(r, n):
     return (r.integers(0, 256, (n, 784)).astype(np.float32) / np.float32(255.0)).astype(np.float32)
 
 
-def relclose(a, b, tol, what):
+def relclose(a, b, tol, what, floor=0.0):
+    """max |a-b| <= tol * max(|b|max, floor).  `floor` is the scale of the neighbouring tensors: some
+    gradients are zero in exact arithmetic (a key bias shifts every score of a row alike, so softmax
+    cancels it) and both sides then hold rounding noise only."""
     a, b = np.asarray(a, np.float64), np.asarray(b, np.float64)
-    scale = max(1e-30, float(np.abs(b).max()))
+    scale = max(1e-30, float(np.abs(b).max()), floor)
     err = float(np.abs(a - b).max())
     assert err <= tol * scale, f"{what}: {err:.3e} vs scale {scale:.3e}"
+
+
+def grad_floor(grads):
+    return max(float(np.abs(v).max()) for v in grads.values())
 
 
 def run_training(Model, kind, dims, cfg, steps, batch, lr, momentum, seed, scheme="he", seq=0, vocab=10):
@@ -51,8 +58,9 @@ def run_training(Model, kind, dims, cfg, steps, batch, lr, momentum, seed, schem
         worst = max(worst, rel)
         assert rel <= 1e-4, f"{kind} step {s}: loss {lg} vs oracle {lo} (rel {rel:.2e})"
     Pg = m.get_params()
+    floor = 1e-2 * grad_floor(tr.P)
     for k in tr.P:
-        relclose(Pg[k], tr.P[k], 1e-4, f"{kind} {k} after {steps} steps")
+        relclose(Pg[k], tr.P[k], 1e-4, f"{kind} {k} after {steps} steps", floor)
     return m, tr, worst
 
 
@@ -109,10 +117,11 @@ def test_gpt_literal_attention_path(Model):
         m.set_option("fused_softmax", fused)
         m.set_option("lr", 0.0)
         losses.append((m.train_step(x, t, seq=8), m.get_grads(), m.last_step_ops()))
-    assert losses[1][2] == losses[0][2] + 3          # mulScalar + add + softmax instead of one op
+    assert losses[1][2] == losses[0][2] + 2          # mulScalar, add, softmax instead of the one fused op
     assert abs(losses[0][0] - losses[1][0]) <= 1e-6 * abs(losses[1][0])
+    floor = 1e-2 * grad_floor(losses[1][1])
     for k in losses[0][1]:
-        relclose(losses[0][1][k], losses[1][1][k], 1e-5, k)
+        relclose(losses[0][1][k], losses[1][1][k], 1e-5, k, floor)
 
 
 def test_transformer_block_config_shape_small(Model):
@@ -135,8 +144,9 @@ def test_transformer_block_config_shape_small(Model):
     relclose(y, yo.data, 1e-5, "y")
     relclose(dx, xt.grad, 3e-5, "dx")
     G = m.get_grads()
+    floor = 1e-2 * max(float(np.abs(t.grad).max()) for t in P.values())
     for k, tns in P.items():
-        relclose(G[k], tns.grad.reshape(P0[k].shape), 3e-5, k)
+        relclose(G[k], tns.grad.reshape(P0[k].shape), 3e-5, k, floor)
 
 
 def test_greedy_decode_matches_oracle(Model):
