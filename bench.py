@@ -299,6 +299,10 @@ def run_gpu(args):
         tf32_live = 2.0 * n ** 3 / (best * 1e-3) / 1e12
         torch.backends.cuda.matmul.allow_tf32 = False
 
+    gpt = None
+    if args.workload in ("all", "gpt"):
+        gpt = gpt_part(args, L, torch, dist, stream, world, rank, local)
+
     if rank == 0:
         peaks, peaks_kind = read_peaks()
         # 3xTF32 ceiling: the TF32 dense rate is half the bf16 rate on this part, and
@@ -323,12 +327,115 @@ def run_gpu(args):
                     "steps": e2e_steps},
             "gpu_launches": launches, "clocks": clocks,
         }
+        if gpt is not None:
+            line["gpt"] = gpt
         if not args.no_cpu_baseline and world == 1:
             line["cpu_baseline"] = {k: v for k, v in cpu_measure(2, 1, budget_s=20.0).items() if k != "n"}
         print(json.dumps(line), flush=True)
     if world > 1:
         dist.destroy_process_group()
     return 0
+
+
+def gpt_part(args, L, torch, dist, stream, world, rank, local):
+    """GPT training step of examples/transformer_gpt.zig at the workload definition's size (vocab 8192, 6 layers,
+    d_model 768, 12 heads, FFN 3072, context 1024, per-GPU batch 8), data parallel over the ranks: every rank
+    trains on its own 8 x 1024 tokens, gradients are summed by NCCL (overlapped with backward) and applied with
+    1/world.  Returns tokens/s over all ranks (weak scaling)."""
+    import numpy as np
+    from znn_b200.models import Model
+
+    V, T, D, H, NL, B = 8192, 1024, 768, 12, 6, 8
+    if world > 1:
+        uid = torch.zeros(128, dtype=torch.uint8, device="cuda")
+        if rank == 0:
+            buf = C.create_string_buffer(128)
+            L.call("znn_dp_unique_id", buf)
+            uid.copy_(torch.frombuffer(bytearray(buf.raw), dtype=torch.uint8))
+        dist.broadcast(uid, src=0)
+        torch.cuda.synchronize()
+        L.call("znn_dp_init", world, rank, bytes(uid.cpu().numpy().tobytes()))
+    m = Model("gpt", (V, T, D, H, NL), arena_bytes=30 << 30)
+    r = np.random.default_rng(42)                       # the same seed on every rank: identical replicas
+    P = {}
+    for name, shape, _, fan_in in m.params:
+        if fan_in:
+            P[name] = (r.standard_normal(shape, np.float32) * np.float32(0.02))
+        else:
+            P[name] = np.ones(shape, np.float32) if "ln_" in name else np.zeros(shape, np.float32)
+    m.set_params(P)
+    del P
+    m.set_option("lr", 0.01)
+    m.set_option("momentum", 0.9)
+    rr = np.random.default_rng(1000 + rank)             # each rank its own shard of the global batch
+    ids = rr.integers(0, V, (B, T)).astype(np.float32)
+    tgt = np.concatenate([ids[:, 1:], rr.integers(0, V, (B, 1))], axis=1).astype(np.int32)
+    d_ids = torch.from_numpy(ids).cuda()
+    d_tgt = torch.from_numpy(tgt).cuda()
+    steps, warmup = max(1, min(args.steps, 20)), 3
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    for _ in range(warmup):
+        m.train_step_device(d_ids.data_ptr(), d_tgt.data_ptr(), B, T)
+    barrier()
+    cnt = C.c_longlong(0)
+    L.call("znn_launch_count", C.byref(cnt), 1)
+    L.call("znn_gemm_profile", 1)
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record(stream)
+    for _ in range(steps):
+        m.train_step_device(d_ids.data_ptr(), d_tgt.data_ptr(), B, T)
+    e1.record(stream)
+    barrier()
+    t = torch.tensor([e0.elapsed_time(e1)], device="cuda", dtype=torch.float64)
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    ms = float(t.item())
+    L.call("znn_launch_count", C.byref(cnt), 1)
+    kms, kl, kfl = C.c_double(0), C.c_longlong(0), C.c_double(0)
+    L.call("znn_gemm_profile_read", C.byref(kms), C.byref(kl), C.byref(kfl))
+    L.call("znn_gemm_profile", 0)
+    # end to end: token ids and targets from host memory every step, loss read back every step
+    loss = m.train_step(ids, tgt, seq=T)
+    barrier()
+    e2e_steps = min(steps, 5)
+    e0.record(stream)
+    for _ in range(e2e_steps):
+        loss = m.train_step(ids, tgt, seq=T)
+    e1.record(stream)
+    barrier()
+    t = torch.tensor([e0.elapsed_time(e1)], device="cuda", dtype=torch.float64)
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    e2e_ms = float(t.item())
+    st = C.c_int(0)
+    L.call("znn_device_status", C.byref(st), 1)
+    if st.value:
+        raise SystemExit(f"device status word {st.value} during the GPT step; the run is invalid")
+    out = {
+        "metric": "gpt_train_tokens_per_s", "value": world * B * T * steps / (ms * 1e-3), "unit": "tokens/s",
+        "n_gpus": world, "steps": steps, "warmup": warmup, "ms_per_step": ms / steps, "scaling": "weak",
+        "config": {"workload": "gpt_train_step", "vocab": V, "n_layer": NL, "d_model": D, "n_head": H, "ffn": 4 * D,
+                   "context": T, "per_gpu_batch": B, "global_batch": B * world, "head": "untied Linear with bias",
+                   "norm": "RMSNorm", "optimizer": "SGD momentum 0.9", "parallelism": f"dp{world}",
+                   "params": sum(int(np.prod(sh)) for _, sh, _, _ in m.params)},
+        "e2e": {"value": world * B * T * e2e_steps / (e2e_ms * 1e-3), "unit": "tokens/s",
+                "h2d_bytes_per_step": ids.nbytes + tgt.nbytes, "d2h_bytes_per_step": 4, "steps": e2e_steps},
+        "gpu_launches": cnt.value, "tape_ops": m.last_step_ops(), "last_loss": loss,
+        "arena_high_water_gb": m.arena_high_water() / 2 ** 30,
+        "tensor_core_gemm": {"launches": kl.value, "kernel_ms_per_step": kms.value / steps,
+                             "tflops": (kfl.value / (kms.value * 1e-3) / 1e12) if kms.value > 0 else None,
+                             "share_of_step": (kms.value / ms) if ms > 0 else None},
+        "model_flops_per_token": 349e6,
+    }
+    m.close()
+    if world > 1:
+        L.call("znn_dp_finalize")
+    return out
 
 
 def main():
@@ -339,6 +446,8 @@ def main():
     ap.add_argument("--n", type=int, default=8192)
     ap.add_argument("--impl", default="znn_b200", choices=["znn_b200", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--workload", default="all", choices=["all", "matmul", "gpt"],
+                    help="matmul: the headline MatMul sweep step only; all: also the GPT training step")
     args = ap.parse_args()
     if args.impl == "reference":
         return run_reference(args)
