@@ -80,6 +80,10 @@ int znn_gemm_last_path(void);
  * the partial sum is promoted to an fp32 register sum (multiple of 32; default 256).  The
  * tensor core's accumulator truncates, so longer chunks trade accuracy for fewer promotions. */
 int znn_gemm_set_chunk(int k_elements);
+/* Split-K (default on): when a product has too few output tiles to fill the GPU and a long
+ * contraction (parameter gradients dW = X^T dY), K is cut into slices run by different CTAs and
+ * the partial sums are added in a fixed order by a second kernel.  0 switches it off. */
+int znn_gemm_set_splitk(int enable);
 /* Measurement aid: with profiling on, every tensor-core GEMM kernel launch (not its split
  * pre-pass) is bracketed by CUDA events on the launching stream; znn_gemm_profile_read waits
  * for them and returns the summed kernel time, the launch count and the algorithmic

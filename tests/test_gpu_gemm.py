@@ -149,3 +149,28 @@ def test_full_size_rows_vs_fp64(ops):
     assert e <= TOL, f"8192^3 sampled rows: rel err {e:.3e} vs fp64"
     got2 = ops.matmul_fwd(A * np.float32(2.0), B)   # scaling by a power of two is exact
     np.testing.assert_array_equal(got2, got * np.float32(2.0))
+
+
+@pytest.mark.parametrize("path", [2, 3])
+@pytest.mark.parametrize("ta,tb,M,N,K", [(T, NT, 768, 768, 8192), (T, NT, 300, 200, 4100), (NT, NT, 256, 512, 2048),
+                                          (NT, T, 128, 64, 4096)])
+def test_split_k_parameter_gradient_shapes(ops, path, ta, tb, M, N, K):
+    """Few output tiles, long contraction (dW = X^T dY): K is split over CTAs and reduced in a fixed
+    order; accumulate semantics (beta = 1) and bit-reproducibility must hold."""
+    from znn_b200._lib import lib
+    A, B = make(ta, tb, M, N, K, seed=K + M)
+    C0 = np.random.default_rng(4).standard_normal((M, N), np.float32)
+    a64 = A.astype(np.float64) if ta == NT else A.astype(np.float64).T
+    b64 = B.astype(np.float64) if tb == NT else B.astype(np.float64).T
+    exact = a64 @ b64 + C0
+    ops.set_gemm_path(path)
+    outs = []
+    for splitk in (1, 1, 0):
+        lib().call("znn_gemm_set_splitk", splitk)
+        got = C0.copy()
+        ops.sgemm(ta, tb, M, N, K, 1.0, A, A.shape[1], B, B.shape[1], 1.0, got, N)
+        outs.append(got)
+        e = rel_err(got, exact)
+        assert e <= TOL, f"split-K={splitk} {M}x{N}x{K}: rel err {e:.3e} vs fp64"
+    lib().call("znn_gemm_set_splitk", 1)
+    np.testing.assert_array_equal(outs[0], outs[1])          # deterministic reduction order

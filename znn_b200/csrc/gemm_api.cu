@@ -11,6 +11,7 @@ int gemm_tc(int ta, int tb, int M, int N, int K, float alpha, const float* A, lo
             long long stride_c, int batch, int ctas);
 int tc_profile_enable(int enable);
 void tc_set_chunk_kblocks(int v);
+void tc_set_splitk(int on);
 int tc_profile_read(double* kernel_ms, long long* launches, double* flops);
 
 // C = alpha * op(A) * op(B) + beta * C with fp32 FMAs, k ascending.
@@ -176,6 +177,12 @@ int znn_gemm_set_chunk(int k_elements)
 {
     ZNN_REQUIRE(k_elements >= 32 && k_elements % 32 == 0, "chunk must be a positive multiple of 32");
     tc_set_chunk_kblocks(k_elements / 32);
+    return ZNN_OK;
+}
+
+int znn_gemm_set_splitk(int enable)
+{
+    tc_set_splitk(enable);
     return ZNN_OK;
 }
 

@@ -216,6 +216,8 @@ struct GemmTcParams {
     int k_blocks;        // padded K / 32
     int k_real;          // the caller's K (for flop accounting only)
     int chunk_kblocks;   // k-blocks accumulated inside tensor memory before promotion
+    int kblocks_per_split;  // split-K: k-blocks handled by one blockIdx.y slice (== k_blocks when not split)
+    float* partial;      // split-K: [splits][batch][M][N] partial sums, nullptr when not split
     int tiles_m, tiles_n;
     float alpha, beta;
     float* C;
@@ -298,7 +300,10 @@ gemm3x_tf32_kernel(const __grid_constant__ CUtensorMap tm_a_hi, const __grid_con
     const int row0 = (tile_m * CTAS + (int)cta_rank) * kTileM;  // first C / A row of this CTA
     const int col0 = tile_n * BN;
     const int chunk = p.chunk_kblocks;
-    const int nchunks = (p.k_blocks + chunk - 1) / chunk;
+    // split-K: this CTA (pair) contracts k-blocks [kb_first, kb_first + kb_count)
+    const int kb_first = (int)blockIdx.y * p.kblocks_per_split;
+    const int kb_count = min(p.k_blocks - kb_first, p.kblocks_per_split);
+    const int nchunks = (kb_count + chunk - 1) / chunk;
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < Cfg::kStages; s++) {
@@ -337,12 +342,12 @@ gemm3x_tf32_kernel(const __grid_constant__ CUtensorMap tm_a_hi, const __grid_con
         // ---------------- TMA producer ----------------
         if (lane == 0) {
             const uint32_t full_leader0 = (CTAS == 2) ? mapa_shared(full_bar(0), 0) : full_bar(0);
-            for (int kb = 0; kb < p.k_blocks; kb++) {
+            for (int kb = 0; kb < kb_count; kb++) {
                 const int s = kb % Cfg::kStages;
                 const uint32_t ph = (kb / Cfg::kStages) & 1;
                 if (!mbar_wait_bounded(empty_bar(s), ph ^ 1)) { ok = false; break; }
                 const uint32_t st = smem_base + s * Cfg::kStageBytes;
-                const int k0 = kb * kBK;
+                const int k0 = (kb_first + kb) * kBK;
                 if (CTAS == 1) {
                     mbar_arrive_expect_tx(full_bar(s), Cfg::kStageBytes);
                     tma_load_3d(st, &tm_a_hi, full_bar(s), k0, row0, batch);
@@ -373,7 +378,7 @@ gemm3x_tf32_kernel(const __grid_constant__ CUtensorMap tm_a_hi, const __grid_con
                 if (!mbar_wait_bounded(acc_empty_bar(buf), ((c >> 1) & 1) ^ 1)) { ok = false; break; }
                 tc_fence_after();
                 const uint32_t d_tmem = tmem_base + (uint32_t)(buf * BN);
-                const int kb_end = min(p.k_blocks, kb + chunk);
+                const int kb_end = min(kb_count, kb + chunk);
                 for (bool first = true; kb < kb_end; kb++) {
                     const int s = kb % Cfg::kStages;
                     const uint32_t ph = (kb / Cfg::kStages) & 1;
@@ -438,11 +443,16 @@ gemm3x_tf32_kernel(const __grid_constant__ CUtensorMap tm_a_hi, const __grid_con
         } else {
             const int row = row0 + q * 32 + lane;
             const int cbase = col0 + half * CPT;
-            const bool vec_ok = ((p.ldc & 3) == 0) && ((reinterpret_cast<uintptr_t>(p.C) & 15) == 0) &&
-                                ((p.stride_c & 3) == 0);
-            const float alpha = p.alpha, beta = p.beta;
+            // split-K slices store their raw partial sums; a reduce kernel applies alpha/beta afterwards
+            const bool to_partial = (p.partial != nullptr);
+            float* const out = to_partial ? p.partial + ((size_t)blockIdx.y * gridDim.z + batch) * (size_t)p.M * p.N : p.C;
+            const long long out_ld = to_partial ? (long long)p.N : p.ldc;
+            const long long out_stride = to_partial ? 0 : p.stride_c;
+            const bool vec_ok = ((out_ld & 3) == 0) && ((reinterpret_cast<uintptr_t>(out) & 15) == 0) &&
+                                ((out_stride & 3) == 0);
+            const float alpha = to_partial ? 1.0f : p.alpha, beta = to_partial ? 0.0f : p.beta;
             if (row < p.M) {
-                float* crow = p.C + (size_t)batch * p.stride_c + (size_t)row * p.ldc + cbase;
+                float* crow = out + (size_t)batch * out_stride + (size_t)row * out_ld + cbase;
 #pragma unroll
                 for (int c = 0; c < CPT; c += 32) {
                     const int ncols = min(32, p.N - (cbase + c));
@@ -559,6 +569,23 @@ __global__ void split_transpose_kernel(const float* __restrict__ X, long long ld
     }
 }
 
+// C = alpha * sum_s partial[s] + beta * C, slices added in order (deterministic)
+__global__ void splitk_reduce_kernel(const float* __restrict__ partial, int splits, int M, int N, int batch, float alpha,
+                                     float beta, float* __restrict__ C, long long ldc, long long stride_c)
+{
+    const size_t per = (size_t)M * N;
+    const size_t total = per * batch;
+    for (size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x) {
+        float s = 0.0f;
+        for (int k = 0; k < splits; k++) s += partial[(size_t)k * total + i];
+        const size_t b = i / per, r = (i % per) / N, c = i % N;
+        float* dst = C + b * stride_c + r * ldc + c;
+        float o = alpha * s;
+        if (beta != 0.0f) o += beta * (*dst);
+        *dst = o;
+    }
+}
+
 // ---------------------------------------------------------------------------
 // host side
 // ---------------------------------------------------------------------------
@@ -663,7 +690,8 @@ static int launch_tc(const CUtensorMap* maps, const GemmTcParams& p, int batch)
         attr_set = true;
     }
     cudaLaunchConfig_t cfg = {};
-    cfg.gridDim = dim3((unsigned)(p.tiles_m * p.tiles_n * CTAS), 1, (unsigned)batch);
+    const int splits = (p.k_blocks + p.kblocks_per_split - 1) / p.kblocks_per_split;
+    cfg.gridDim = dim3((unsigned)(p.tiles_m * p.tiles_n * CTAS), (unsigned)splits, (unsigned)batch);
     cfg.blockDim = dim3(kThreads, 1, 1);
     cfg.dynamicSmemBytes = Cfg::kSmemBytes;
     cfg.stream = stream();
@@ -681,6 +709,8 @@ static int launch_tc(const CUtensorMap* maps, const GemmTcParams& p, int batch)
     return ZNN_OK;
 }
 
+static thread_local bool t_splitk_enabled = true;
+void tc_set_splitk(int on) { t_splitk_enabled = (on != 0); }
 static thread_local int t_chunk_kblocks = 8;  // 256 contraction elements per tensor-memory accumulation
 int tc_chunk_kblocks() { return t_chunk_kblocks; }
 void tc_set_chunk_kblocks(int v) { t_chunk_kblocks = v < 1 ? 1 : v; }
@@ -694,7 +724,33 @@ int gemm_tc(int ta, int tb, int M, int N, int K, float alpha, const float* A, lo
     if (!status) return fail(ZNN_ERR_CUDA, "no device state (call znn_init first)");
     const int kpad = ((K + kBK - 1) / kBK) * kBK;
     const size_t a_plane = (size_t)batch * M * kpad, b_plane = (size_t)batch * N * kpad;
-    const size_t need = (2 * a_plane + 2 * b_plane) * sizeof(float);
+    // ---- tile shape and split-K plan ----
+    int bn = 256;
+    if (N <= 64) bn = 64;
+    else if (N <= 128) bn = 128;
+    const int tile_rows = kTileM * ctas;
+    const int tiles_m = (M + tile_rows - 1) / tile_rows, tiles_n = (N + bn - 1) / bn;
+    const int k_blocks = kpad / kBK;
+    const int chunk = tc_chunk_kblocks();
+    // Few output tiles and a long contraction (parameter gradients: dW = X^T dY): cut K over
+    // blockIdx.y so that every CTA pair slot of the GPU has work; slices are whole chunks.
+    int splits = 1;
+    {
+        const long units = (long)tiles_m * tiles_n * batch;
+        const int slots = sm_count() / ctas;
+        const int max_by_k = k_blocks / (chunk > 8 ? chunk : 8);
+        if (t_splitk_enabled && units * 2 <= slots && max_by_k >= 2) {
+            splits = (int)(slots / units);
+            if (splits > max_by_k) splits = max_by_k;
+            if (splits > 32) splits = 32;
+            if (splits < 1) splits = 1;
+        }
+    }
+    int kbps = (k_blocks + splits - 1) / splits;
+    kbps = ((kbps + chunk - 1) / chunk) * chunk;          // whole chunks per slice
+    splits = (k_blocks + kbps - 1) / kbps;
+    const size_t partial_floats = splits > 1 ? (size_t)splits * batch * M * N : 0;
+    const size_t need = (2 * a_plane + 2 * b_plane + partial_floats) * sizeof(float);
     float* ws = (float*)workspace(need);
     if (!ws) return fail(ZNN_ERR_NOMEM, "GEMM scratch of %zu bytes could not be allocated", need);
     float* a_hi = ws;
@@ -727,15 +783,12 @@ int gemm_tc(int ta, int tb, int M, int N, int K, float alpha, const float* A, lo
     rc = split(B, ldb, stride_b, N, tb == ZNN_TRANS, b_hi, b_lo);
     if (rc) return rc;
 
-    // ---- tile shape ----
-    int bn = 256;
-    if (N <= 64) bn = 64;
-    else if (N <= 128) bn = 128;
-    const int tile_rows = kTileM * ctas;
     GemmTcParams p;
-    p.M = M; p.N = N; p.k_blocks = kpad / kBK; p.k_real = K; p.chunk_kblocks = tc_chunk_kblocks();
-    p.tiles_m = (M + tile_rows - 1) / tile_rows;
-    p.tiles_n = (N + bn - 1) / bn;
+    p.M = M; p.N = N; p.k_blocks = k_blocks; p.k_real = K; p.chunk_kblocks = chunk;
+    p.kblocks_per_split = kbps;
+    p.partial = splits > 1 ? (b_lo + b_plane) : nullptr;
+    p.tiles_m = tiles_m;
+    p.tiles_n = tiles_n;
     p.alpha = alpha; p.beta = beta; p.C = C; p.ldc = ldc; p.stride_c = stride_c; p.status = status;
 
     CUtensorMap maps[4];
@@ -745,13 +798,24 @@ int gemm_tc(int ta, int tb, int M, int N, int K, float alpha, const float* A, lo
     if ((rc = make_plane_map(&maps[3], b_lo, N, kpad, batch, bn / ctas))) return rc;
 
     if (ctas == 1) {
-        if (bn == 256) return launch_tc<256, 1>(maps, p, batch);
-        if (bn == 128) return launch_tc<128, 1>(maps, p, batch);
-        return launch_tc<64, 1>(maps, p, batch);
+        if (bn == 256) rc = launch_tc<256, 1>(maps, p, batch);
+        else if (bn == 128) rc = launch_tc<128, 1>(maps, p, batch);
+        else rc = launch_tc<64, 1>(maps, p, batch);
+    } else {
+        if (bn == 256) rc = launch_tc<256, 2>(maps, p, batch);
+        else if (bn == 128) rc = launch_tc<128, 2>(maps, p, batch);
+        else rc = launch_tc<64, 2>(maps, p, batch);
     }
-    if (bn == 256) return launch_tc<256, 2>(maps, p, batch);
-    if (bn == 128) return launch_tc<128, 2>(maps, p, batch);
-    return launch_tc<64, 2>(maps, p, batch);
+    if (rc) return rc;
+    if (splits > 1) {
+        const size_t total = (size_t)batch * M * N;
+        int blocks = (int)((total + 255) / 256);
+        const int cap = sm_count() * 16;
+        if (blocks > cap) blocks = cap;
+        splitk_reduce_kernel<<<blocks, 256, 0, st>>>(p.partial, splits, M, N, batch, alpha, beta, C, ldc, stride_c);
+        ZNN_LAUNCH_OK("splitk_reduce_kernel");
+    }
+    return ZNN_OK;
 }
 
 }  // namespace znn
