@@ -73,7 +73,10 @@ int znn_sgemm_batched_strided(int trans_a, int trans_b, int M, int N, int K, flo
                               const float* A, int lda, long long stride_a,
                               const float* B, int ldb, long long stride_b, float beta,
                               float* C, int ldc, long long stride_c, int batch);
-/* path: 0 = automatic, 1 = fp32 FMA kernel, 2 = tcgen05 one CTA per tile, 3 = tcgen05 CTA pairs */
+/* path: 0 = automatic, 1 = fp32 FMA kernel, 2 = tcgen05 one CTA per tile over pre-split operand
+ * planes, 3 = tcgen05 CTA pairs over pre-split planes, 4 = tcgen05 CTA pairs reading the operands
+ * in place (hi/lo split in shared memory; needs 16-byte aligned bases and leading dimensions that
+ * are multiples of 4, otherwise path 3 is taken) */
 int znn_gemm_set_path(int path);
 int znn_gemm_last_path(void);
 /* Number of contraction elements the tensor-core paths accumulate inside tensor memory before
@@ -84,6 +87,10 @@ int znn_gemm_set_chunk(int k_elements);
  * contraction (parameter gradients dW = X^T dY), K is cut into slices run by different CTAs and
  * the partial sums are added in a fixed order by a second kernel.  0 switches it off. */
 int znn_gemm_set_splitk(int enable);
+/* In-place path only: 1 (default) = the converter warps leave the raw fp32 tile as the hi operand:
+ * the tensor core ignores the 13 low mantissa bits of a kind::tf32 operand (measured on B200: results
+ * are bit-identical to mode 0); 0 = they also store hi = x with those bits cleared. */
+int znn_gemm_set_conv_mode(int mode);
 /* Measurement aid: with profiling on, every tensor-core GEMM kernel launch (not its split
  * pre-pass) is bracketed by CUDA events on the launching stream; znn_gemm_profile_read waits
  * for them and returns the summed kernel time, the launch count and the algorithmic

@@ -2,8 +2,9 @@
 
 Bar (from the workload definition): normwise relative error <= 1e-5 against the
 reference sgemm on N(0,1) inputs, for the forward product and both backward
-products, on every code path: fp32-FMA kernel (1), tcgen05 one-CTA tiles (2),
-tcgen05 CTA-pair tiles (3) and the automatic choice (0).
+products, on every code path: fp32-FMA kernel (1), tcgen05 one-CTA tiles (2) and
+CTA-pair tiles (3) over pre-split operand planes, CTA-pair tiles reading the
+operands in place (4), and the automatic choice (0).
 """
 import numpy as np
 import pytest
@@ -44,7 +45,10 @@ def run_case(ops, zo, path, ta, tb, M, N, K, alpha=1.0, beta=0.0, lda_pad=0, ldb
     got = C0.copy()
     ops.set_gemm_path(path)
     ops.sgemm(ta, tb, M, N, K, alpha, A, lda, B, ldb, beta, got, ldc)
-    if path != 0:
+    if path == 4:
+        # in-place operand reads need 16-byte aligned leading dimensions; otherwise the planes path runs
+        assert ops.last_gemm_path() == (4 if (lda % 4 == 0 and ldb % 4 == 0) else 3)
+    elif path != 0:
         assert ops.last_gemm_path() == path
     if ldc_pad:  # columns beyond N are not touched
         np.testing.assert_array_equal(got[:, N:], C0[:, N:])
@@ -57,30 +61,33 @@ SMALL = [(2, 2, 3), (1, 1, 1), (64, 10, 784), (64, 128, 784), (33, 65, 17), (128
          (256, 256, 256), (200, 64, 96), (300, 72, 1000)]
 
 
-@pytest.mark.parametrize("path", [1, 2, 3])
+@pytest.mark.parametrize("path", [1, 2, 3, 4])
 @pytest.mark.parametrize("M,N,K", SMALL)
 def test_forward_nn(ops, zo, path, M, N, K):
     run_case(ops, zo, path, NT, NT, M, N, K, seed=M + N + K)
 
 
-@pytest.mark.parametrize("path", [1, 2, 3])
+@pytest.mark.parametrize("path", [1, 2, 3, 4])
 @pytest.mark.parametrize("ta,tb", [(NT, T), (T, NT), (T, T)])
-@pytest.mark.parametrize("M,N,K", [(64, 10, 784), (130, 258, 70), (256, 128, 512)])
+@pytest.mark.parametrize("M,N,K", [(64, 10, 784), (130, 258, 70), (256, 128, 512), (132, 260, 72), (384, 320, 96)])
 def test_transposed_accumulate(ops, zo, path, ta, tb, M, N, K):
     """The backward calls: dA += dC.B^T (NoTrans,Trans) and dB += A^T.dC (Trans,NoTrans), beta = 1."""
     run_case(ops, zo, path, ta, tb, M, N, K, beta=1.0, seed=7 * M + N)
 
 
-@pytest.mark.parametrize("path", [1, 2, 3])
+@pytest.mark.parametrize("path", [1, 2, 3, 4])
 def test_alpha_beta_and_leading_dimensions(ops, zo, path):
     run_case(ops, zo, path, NT, NT, 150, 90, 200, alpha=0.5, beta=-2.0, lda_pad=3, ldb_pad=5, ldc_pad=7, seed=3)
     run_case(ops, zo, path, T, T, 129, 257, 65, alpha=2.0, beta=0.0, lda_pad=1, ldb_pad=2, ldc_pad=1, seed=4)
+    # padded but TMA-readable leading dimensions: the in-place path must honour them
+    run_case(ops, zo, path, NT, NT, 152, 92, 200, alpha=0.5, beta=-2.0, lda_pad=4, ldb_pad=8, ldc_pad=4, seed=5)
+    run_case(ops, zo, path, T, NT, 136, 264, 68, alpha=1.5, beta=1.0, lda_pad=8, ldb_pad=4, ldc_pad=0, seed=6)
 
 
 def test_beta_zero_ignores_old_c(ops):
     """beta == 0 must overwrite C even when it holds NaN (the reference memsets, cblas.zig:56-60)."""
     r = np.random.default_rng(5)
-    for path in (1, 2, 3):
+    for path in (1, 2, 3, 4):
         A, B = r.standard_normal((128, 64), np.float32), r.standard_normal((64, 256), np.float32)
         Cm = np.full((128, 256), np.nan, np.float32)
         ops.set_gemm_path(path)
@@ -100,7 +107,7 @@ def test_degenerate(ops, zo):
     ops.sgemm(NT, NT, 0, 5, 1, 1.0, A, 1, B, 5, 0.0, Cm, 5)      # empty M: no-op
 
 
-@pytest.mark.parametrize("path", [1, 2, 3])
+@pytest.mark.parametrize("path", [1, 2, 3, 4])
 def test_batched(ops, zo, path):
     """BatchMatMul forward/backward shapes of attention (per (b,h) slices)."""
     r = np.random.default_rng(11)
@@ -119,7 +126,7 @@ def test_batched(ops, zo, path):
     assert rel_err(g[0], h[0]) <= TOL and rel_err(g[1], h[1]) <= TOL
 
 
-@pytest.mark.parametrize("path", [2, 3, 0])
+@pytest.mark.parametrize("path", [2, 3, 4, 0])
 @pytest.mark.parametrize("M,N,K", [(512, 512, 512), (1024, 1024, 1024), (64, 4096, 4096), (4096, 64, 4096)])
 def test_sweep_shapes_vs_fp64(ops, zo, path, M, N, K):
     """Workload-definition sweep shapes that the fp64 arbiter finishes quickly on the CPU."""
@@ -151,7 +158,7 @@ def test_full_size_rows_vs_fp64(ops):
     np.testing.assert_array_equal(got2, got * np.float32(2.0))
 
 
-@pytest.mark.parametrize("path", [2, 3])
+@pytest.mark.parametrize("path", [2, 3, 4])
 @pytest.mark.parametrize("ta,tb,M,N,K", [(T, NT, 768, 768, 8192), (T, NT, 300, 200, 4100), (NT, NT, 256, 512, 2048),
                                           (NT, T, 128, 64, 4096)])
 def test_split_k_parameter_gradient_shapes(ops, path, ta, tb, M, N, K):
@@ -174,3 +181,23 @@ def test_split_k_parameter_gradient_shapes(ops, path, ta, tb, M, N, K):
         assert e <= TOL, f"split-K={splitk} {M}x{N}x{K}: rel err {e:.3e} vs fp64"
     lib().call("znn_gemm_set_splitk", 1)
     np.testing.assert_array_equal(outs[0], outs[1])          # deterministic reduction order
+
+
+def test_tensor_core_ignores_low_mantissa_bits(ops):
+    """The in-place path feeds raw fp32 tiles as the hi operand (conv mode 1) on the strength of the tensor
+    core dropping the 13 low mantissa bits of a tf32 operand.  Mode 0 clears them explicitly: both must give
+    bit-identical results, for K-major and MN-major operands."""
+    from znn_b200._lib import lib
+    r = np.random.default_rng(123)
+    ops.set_gemm_path(4)
+    for ta, tb in ((NT, NT), (T, NT), (NT, T)):
+        A, B = make(ta, tb, 512, 384, 1024, seed=9)
+        outs = []
+        for mode in (0, 1):
+            lib().call("znn_gemm_set_conv_mode", mode)
+            got = np.zeros((512, 384), np.float32)
+            ops.sgemm(ta, tb, 512, 384, 1024, 1.0, A, A.shape[1], B, B.shape[1], 0.0, got, 384)
+            assert ops.last_gemm_path() == 4
+            outs.append(got)
+        np.testing.assert_array_equal(outs[0], outs[1])
+    lib().call("znn_gemm_set_conv_mode", 1)

@@ -9,9 +9,15 @@ namespace znn {
 int gemm_tc(int ta, int tb, int M, int N, int K, float alpha, const float* A, long long lda, long long stride_a,
             const float* B, long long ldb, long long stride_b, float beta, float* C, long long ldc,
             long long stride_c, int batch, int ctas);
+bool gemm_tc_direct_eligible(const float* A, long long lda, long long stride_a, const float* B, long long ldb,
+                             long long stride_b, int batch);
+int gemm_tc_direct(int ta, int tb, int M, int N, int K, float alpha, const float* A, long long lda, long long stride_a,
+                   const float* B, long long ldb, long long stride_b, float beta, float* C, long long ldc,
+                   long long stride_c, int batch);
 int tc_profile_enable(int enable);
 void tc_set_chunk_kblocks(int v);
 void tc_set_splitk(int on);
+void tc_set_conv_mode(int m);
 int tc_profile_read(double* kernel_ms, long long* launches, double* flops);
 
 // C = alpha * op(A) * op(B) + beta * C with fp32 FMAs, k ascending.
@@ -122,13 +128,31 @@ static int gemm_dispatch(int ta, int tb, int M, int N, int K, float alpha, const
     ZNN_REQUIRE(ldb >= (tb == ZNN_NO_TRANS ? N : K), "ldb too small");
 
     int path = t_path;
+    const bool direct_ok = gemm_tc_direct_eligible(A, lda, stride_a, B, ldb, stride_b, batch);
     if (path == 0) {
-        // The tensor-core path costs a split pre-pass and two extra launches; below
-        // ~0.13 GFLOP per call the FMA kernel finishes sooner.
+        // The tensor-core paths cost extra launches; below ~0.13 GFLOP per call the FMA kernel finishes sooner.
         const double flops = 2.0 * M * N * (double)K * batch;
-        path = (flops >= 1.3e8 && M >= 64 && N >= 32 && K >= 32) ? 3 : 1;
+        if (!(flops >= 1.3e8 && M >= 64 && N >= 32 && K >= 32)) {
+            path = 1;
+        } else if (!direct_ok) {
+            path = 3;
+        } else {
+            // Planes path: one split pre-pass over both operands (12 bytes per element, about twice that
+            // when the operand has to be transposed on the way), then the fastest kernel.  In-place path:
+            // no pre-pass, but the in-kernel split shares shared-memory bandwidth with the tensor core
+            // and costs ~18 % of kernel time (both measured on B200).  Take the cheaper one.
+            const double a_bytes = 12.0 * M * (double)K * batch * (ta == ZNN_NO_TRANS ? 1.0 : 2.0);
+            const double b_bytes = 12.0 * N * (double)K * batch * (tb == ZNN_TRANS ? 1.0 : 2.0);
+            const double prepass_us = (a_bytes + b_bytes) / 5.0e6 + 6.0;  // ~5 TB/s effective + two launches
+            const double kernel_us = flops / 2.0e8;                       // ~200 TFLOP/s
+            path = (prepass_us < 0.18 * kernel_us) ? 3 : 4;
+        }
     }
+    // the in-place path needs TMA-readable operands; otherwise the pre-split planes path takes any layout
+    if (path == 4 && !direct_ok) path = 3;
     t_last_path = path;
+    if (path == 4)
+        return gemm_tc_direct(ta, tb, M, N, K, alpha, A, lda, stride_a, B, ldb, stride_b, beta, C, ldc, stride_c, batch);
     if (path == 2 || path == 3)
         return gemm_tc(ta, tb, M, N, K, alpha, A, lda, stride_a, B, ldb, stride_b, beta, C, ldc, stride_c, batch,
                        path == 2 ? 1 : 2);
@@ -166,7 +190,7 @@ int znn_sgemm_batched_strided(int trans_a, int trans_b, int M, int N, int K, flo
 
 int znn_gemm_set_path(int path)
 {
-    ZNN_REQUIRE(path >= 0 && path <= 3, "path must be 0..3");
+    ZNN_REQUIRE(path >= 0 && path <= 4, "path must be 0..4");
     t_path = path;
     return ZNN_OK;
 }
@@ -183,6 +207,13 @@ int znn_gemm_set_chunk(int k_elements)
 int znn_gemm_set_splitk(int enable)
 {
     tc_set_splitk(enable);
+    return ZNN_OK;
+}
+
+int znn_gemm_set_conv_mode(int mode)
+{
+    ZNN_REQUIRE(mode == 0 || mode == 1, "mode must be 0 or 1");
+    tc_set_conv_mode(mode);
     return ZNN_OK;
 }
 

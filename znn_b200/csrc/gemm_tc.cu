@@ -218,6 +218,7 @@ struct GemmTcParams {
     int chunk_kblocks;   // k-blocks accumulated inside tensor memory before promotion
     int kblocks_per_split;  // split-K: k-blocks handled by one blockIdx.y slice (== k_blocks when not split)
     float* partial;      // split-K: [splits][batch][M][N] partial sums, nullptr when not split
+    int conv_mode;       // direct kernel: 0 = store the masked hi tile, 1 = leave the raw tile as hi
     int tiles_m, tiles_n;
     float alpha, beta;
     float* C;
@@ -569,6 +570,365 @@ __global__ void split_transpose_kernel(const float* __restrict__ X, long long ld
     }
 }
 
+// ---------------------------------------------------------------------------
+// the direct GEMM kernel: no pre-pass, the hi/lo split happens in shared memory
+// ---------------------------------------------------------------------------
+// Operands are read by TMA straight from the caller's fp32 matrices, K-major
+// (the contraction index contiguous) or MN-major (the row/column index
+// contiguous), whatever the transpose flags give, so nothing is transposed or
+// copied in HBM.  Two converter warps rewrite each landed tile in place as
+// hi = rn_tf32(x) and store lo = rn_tf32(x - hi) next to it; the conversion is
+// elementwise, so it is blind to the 128-byte swizzle.  CTA pairs only.
+//   16 warps: 0 TMA, 1 MMA + TMEM, 2-3 idle, 4-7 converters, 8-15 epilogue.  The epilogue warps
+//   hold 128 accumulators per thread, so registers are moved to them with setmaxnreg
+//   (warpgroups 0-1 shrink to 56, warpgroups 2-3 grow to 200).
+constexpr int kDirectThreads = 512;
+constexpr int kConvWarps = 4;
+constexpr int kConvWarp0 = 4, kEpiWarp0 = 8;
+
+__device__ __forceinline__ uint32_t mbar_try_wait_cluster(uint32_t bar, uint32_t parity)
+{
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.acquire.cluster.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok)
+        : "r"(bar), "r"(parity)
+        : "memory");
+    return ok;
+}
+
+__device__ __forceinline__ bool mbar_wait_bounded_cluster(uint32_t bar, uint32_t parity)
+{
+    if (mbar_try_wait_cluster(bar, parity)) return true;
+    const uint64_t t0 = globaltimer_ns();
+    for (;;) {
+#pragma unroll 1
+        for (int i = 0; i < 128; i++)
+            if (mbar_try_wait_cluster(bar, parity)) return true;
+        if (globaltimer_ns() - t0 > 2000000000ull) return false;
+    }
+}
+
+// MN-major tile (32-bit elements): the only shared-memory layout the tensor core takes is the
+// 128-byte swizzle with 32-byte atoms (TMA: SWIZZLE_128B_ATOM_32B).  Each TMA box is 32 M/N
+// elements (one 128-byte row) x 32 k-rows = 4096 bytes; swizzle atoms are 4 k-rows (512 bytes),
+// so one K = 8 instruction spans two atoms.
+__device__ __forceinline__ uint64_t make_mnmajor_sw128_desc(uint32_t smem_addr)
+{
+    uint64_t d = 0;
+    d |= (uint64_t)((smem_addr & 0x3FFFF) >> 4);
+    d |= (uint64_t)(4096 >> 4) << 16;  // leading byte offset: next 32-wide M/N group (next box)
+    d |= (uint64_t)(512 >> 4) << 32;   // stride byte offset: next atom of 4 k-rows
+    d |= (uint64_t)1 << 46;
+    d |= (uint64_t)1 << 61;            // SWIZZLE_128B_BASE32B
+    return d;
+}
+
+__host__ __device__ constexpr uint32_t make_tf32_idesc_major(int mma_m, int mma_n, bool a_mn, bool b_mn)
+{
+    return make_tf32_idesc(mma_m, mma_n) | ((a_mn ? 1u : 0u) << 15) | ((b_mn ? 1u : 0u) << 16);
+}
+
+template <int BN>
+struct DirectCfg {
+    static constexpr int kBRows = BN / 2;
+    static constexpr int kABytes = kTileM * kBK * 4;
+    static constexpr int kBBytes = kBRows * kBK * 4;
+    static constexpr int kStageBytes = 2 * kABytes + 2 * kBBytes;  // A raw/hi, A lo, B raw/hi, B lo
+    static constexpr int kStages = (200 * 1024) / kStageBytes > 6 ? 6 : (200 * 1024) / kStageBytes;
+    static constexpr int kSmemBytes = kStages * kStageBytes + 1024 + 512;
+    static constexpr int kTmemCols = 2 * BN < 32 ? 32 : 2 * BN;
+    static constexpr int kColsPerThread = BN / 2;
+};
+
+template <int BN, bool A_MN, bool B_MN>
+__global__ void __launch_bounds__(kDirectThreads, 1)
+gemm3x_direct_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CUtensorMap tm_b,
+                     const GemmTcParams p)
+{
+    using Cfg = DirectCfg<BN>;
+    constexpr int CTAS = 2;
+    extern __shared__ uint8_t smem_raw[];
+    const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+    uint8_t* smem_gen = smem_raw + (smem_base - smem_u32(smem_raw));
+    const uint32_t bar_base = smem_base + Cfg::kStages * Cfg::kStageBytes;
+    // barriers: full[S] (TMA -> converters, per CTA), conv[S] (converters of both CTAs -> MMA, in the leader),
+    // empty[S] (MMA -> TMA, both CTAs), acc_full[2], acc_empty[2]
+    auto full_bar = [&](int s) { return bar_base + 8u * s; };
+    auto conv_bar = [&](int s) { return bar_base + 8u * (Cfg::kStages + s); };
+    auto empty_bar = [&](int s) { return bar_base + 8u * (2 * Cfg::kStages + s); };
+    auto acc_full_bar = [&](int b) { return bar_base + 8u * (3 * Cfg::kStages + b); };
+    auto acc_empty_bar = [&](int b) { return bar_base + 8u * (3 * Cfg::kStages + 2 + b); };
+    constexpr int kWordOff = 8 * (3 * Cfg::kStages + 4);
+    volatile uint32_t* tmem_slot =
+        reinterpret_cast<volatile uint32_t*>(smem_gen + Cfg::kStages * Cfg::kStageBytes + kWordOff);
+    const uint32_t tmem_slot_addr = bar_base + kWordOff;
+    volatile uint32_t* abort_slot = tmem_slot + 1;
+    const uint32_t abort_slot_addr = tmem_slot_addr + 4;
+
+    const int warp = threadIdx.x >> 5;
+    const int lane = threadIdx.x & 31;
+    const uint32_t cta_rank = cluster_ctarank();
+    const bool leader = (cta_rank == 0);
+
+    const int unit = blockIdx.x >> 1;
+    int tile_m, tile_n;
+    {
+        constexpr int G = 8;
+        const int per_group = G * p.tiles_n;
+        const int g = unit / per_group;
+        const int first_m = g * G;
+        const int rows_in_group = min(G, p.tiles_m - first_m);
+        const int r = unit - g * per_group;
+        tile_m = first_m + r % rows_in_group;
+        tile_n = r / rows_in_group;
+    }
+    const int batch = blockIdx.z;
+    const int row0 = (tile_m * CTAS + (int)cta_rank) * kTileM;
+    const int col0 = tile_n * BN;
+    const int chunk = p.chunk_kblocks;
+    const int kb_first = (int)blockIdx.y * p.kblocks_per_split;
+    const int kb_count = min(p.k_blocks - kb_first, p.kblocks_per_split);
+    const int nchunks = (kb_count + chunk - 1) / chunk;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < Cfg::kStages; s++) {
+            mbar_init(full_bar(s), 1);
+            mbar_init(conv_bar(s), kConvWarps * CTAS);
+            mbar_init(empty_bar(s), 1);
+        }
+        for (int b = 0; b < 2; b++) {
+            mbar_init(acc_full_bar(b), 1);
+            mbar_init(acc_empty_bar(b), kEpiWarps * CTAS);
+        }
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        if (leader) {
+            const uint32_t prior = (uint32_t)(*reinterpret_cast<volatile int*>(p.status));
+            *abort_slot = prior;
+            asm volatile("st.shared::cluster.u32 [%0], %1;" ::"r"(mapa_shared(abort_slot_addr, 1)), "r"(prior) : "memory");
+        }
+    }
+    if (warp == 1) {
+        tmem_alloc<CTAS>(tmem_slot_addr, Cfg::kTmemCols);
+        tmem_relinquish<CTAS>();
+    }
+    tc_fence_before();
+    __syncthreads();
+    cluster_sync_all();
+    tc_fence_after();
+    const uint32_t tmem_base = *tmem_slot;
+    const bool aborted = (*abort_slot != 0);
+
+    bool ok = true;
+    if (warp < kEpiWarp0) {
+    asm volatile("setmaxnreg.dec.sync.aligned.u32 56;");
+    if (aborted || warp == 2 || warp == 3) {
+    } else if (warp == 0) {
+        // ---------------- TMA producer: raw fp32 tiles of this CTA's rows of A and of B ----------------
+        if (lane == 0) {
+            for (int kb = 0; kb < kb_count; kb++) {
+                const int s = kb % Cfg::kStages;
+                const uint32_t ph = (kb / Cfg::kStages) & 1;
+                if (!mbar_wait_bounded(empty_bar(s), ph ^ 1)) { ok = false; break; }
+                const uint32_t st = smem_base + s * Cfg::kStageBytes;
+                const int k0 = (kb_first + kb) * kBK;
+                mbar_arrive_expect_tx(full_bar(s), Cfg::kABytes + Cfg::kBBytes);
+                if (A_MN) {
+#pragma unroll
+                    for (int j = 0; j < kTileM / 32; j++)
+                        tma_load_3d(st + j * 4096, &tm_a, full_bar(s), row0 + 32 * j, k0, batch);
+                } else {
+                    tma_load_3d(st, &tm_a, full_bar(s), k0, row0, batch);
+                }
+                const uint32_t sb = st + 2 * Cfg::kABytes;
+                const int brow0 = col0 + (int)cta_rank * Cfg::kBRows;
+                if (B_MN) {
+#pragma unroll
+                    for (int j = 0; j < Cfg::kBRows / 32; j++)
+                        tma_load_3d(sb + j * 4096, &tm_b, full_bar(s), brow0 + 32 * j, k0, batch);
+                } else {
+                    tma_load_3d(sb, &tm_b, full_bar(s), k0, brow0, batch);
+                }
+            }
+            if (!ok) atomicOr(p.status, ZNN_DEV_TMA_WAIT_EXPIRED);
+        }
+    } else if (warp == 1) {
+        // ---------------- MMA issuer (leader CTA only) ----------------
+        if (lane == 0 && leader) {
+            constexpr uint32_t idesc = make_tf32_idesc_major(kTileM * CTAS, BN, A_MN, B_MN);
+            // descriptor start-address step per K=8 MMA, in 16-byte units
+            constexpr uint32_t a_step = A_MN ? (1024 >> 4) : (32 >> 4);
+            constexpr uint32_t b_step = B_MN ? (1024 >> 4) : (32 >> 4);
+            int kb = 0;
+            for (int c = 0; c < nchunks && ok; c++) {
+                const int buf = c & 1;
+                if (!mbar_wait_bounded_cluster(acc_empty_bar(buf), ((c >> 1) & 1) ^ 1)) { ok = false; break; }
+                tc_fence_after();
+                const uint32_t d_tmem = tmem_base + (uint32_t)(buf * BN);
+                const int kb_end = min(kb_count, kb + chunk);
+                for (bool first = true; kb < kb_end; kb++) {
+                    const int s = kb % Cfg::kStages;
+                    const uint32_t ph = (kb / Cfg::kStages) & 1;
+                    if (!mbar_wait_bounded_cluster(conv_bar(s), ph)) { ok = false; break; }
+                    tc_fence_after();
+                    const uint32_t st = smem_base + s * Cfg::kStageBytes;
+                    const uint64_t a_hi = A_MN ? make_mnmajor_sw128_desc(st) : make_kmajor_sw128_desc(st);
+                    const uint64_t a_lo = A_MN ? make_mnmajor_sw128_desc(st + Cfg::kABytes) : make_kmajor_sw128_desc(st + Cfg::kABytes);
+                    const uint32_t sb = st + 2 * Cfg::kABytes;
+                    const uint64_t b_hi = B_MN ? make_mnmajor_sw128_desc(sb) : make_kmajor_sw128_desc(sb);
+                    const uint64_t b_lo = B_MN ? make_mnmajor_sw128_desc(sb + Cfg::kBBytes) : make_kmajor_sw128_desc(sb + Cfg::kBBytes);
+#pragma unroll
+                    for (int k = 0; k < kBK / 8; k++)
+                        umma_tf32<CTAS>(d_tmem, a_lo + a_step * k, b_hi + b_step * k, idesc, (first && k == 0) ? 0u : 1u);
+#pragma unroll
+                    for (int k = 0; k < kBK / 8; k++) umma_tf32<CTAS>(d_tmem, a_hi + a_step * k, b_lo + b_step * k, idesc, 1);
+#pragma unroll
+                    for (int k = 0; k < kBK / 8; k++) umma_tf32<CTAS>(d_tmem, a_hi + a_step * k, b_hi + b_step * k, idesc, 1);
+                    umma_commit_pair(empty_bar(s));
+                    first = false;
+                }
+                if (ok) umma_commit_pair(acc_full_bar(buf));
+            }
+            if (!ok) atomicOr(p.status, ZNN_DEV_MMA_WAIT_EXPIRED);
+        }
+    } else if (warp < kEpiWarp0) {
+        // ---------------- converters: raw tile -> hi (in place) and lo ----------------
+        const int ct = threadIdx.x - 32 * kConvWarp0;  // 0..127
+        const uint32_t conv_leader0 = mapa_shared(conv_bar(0), 0);
+        constexpr int kAVec = Cfg::kABytes / 16, kBVec = Cfg::kBBytes / 16;
+        const bool store_hi = (p.conv_mode == 0);
+        bool got = true;
+        for (int kb = 0; kb < kb_count; kb++) {
+            const int s = kb % Cfg::kStages;
+            const uint32_t ph = (kb / Cfg::kStages) & 1;
+            if (lane == 0) got = mbar_wait_bounded(full_bar(s), ph);
+            got = __shfl_sync(0xffffffffu, (int)got, 0) != 0;
+            if (!got) break;
+            uint8_t* st = smem_gen + s * Cfg::kStageBytes;
+            // hi = x with the 13 low mantissa bits cleared (exactly a TF32 value); lo = x - hi is exact in
+            // fp32 and at most 2^-10 |x|; the tensor core drops lo's own low bits, a 2^-21 relative effect
+            auto convert = [&](uint8_t* base, int nvec, int lo_off) {
+                constexpr int kT = 32 * kConvWarps;
+#pragma unroll 1
+                for (int i0 = ct; i0 < nvec; i0 += 4 * kT) {
+                    uint4 x[4];
+#pragma unroll
+                    for (int u = 0; u < 4; u++)
+                        if (i0 + u * kT < nvec) x[u] = *reinterpret_cast<const uint4*>(base + 16 * (i0 + u * kT));
+#pragma unroll
+                    for (int u = 0; u < 4; u++) {
+                        if (i0 + u * kT >= nvec) continue;
+                        uint4 h;
+                        h.x = x[u].x & 0xFFFFE000u; h.y = x[u].y & 0xFFFFE000u;
+                        h.z = x[u].z & 0xFFFFE000u; h.w = x[u].w & 0xFFFFE000u;
+                        float4 l;
+                        l.x = __uint_as_float(x[u].x) - __uint_as_float(h.x);
+                        l.y = __uint_as_float(x[u].y) - __uint_as_float(h.y);
+                        l.z = __uint_as_float(x[u].z) - __uint_as_float(h.z);
+                        l.w = __uint_as_float(x[u].w) - __uint_as_float(h.w);
+                        uint8_t* src = base + 16 * (i0 + u * kT);
+                        if (store_hi) *reinterpret_cast<uint4*>(src) = h;
+                        *reinterpret_cast<float4*>(src + lo_off) = l;
+                    }
+                }
+            };
+            convert(st, kAVec, Cfg::kABytes);
+            convert(st + 2 * Cfg::kABytes, kBVec, Cfg::kBBytes);
+            // make the generic-proxy writes visible to the tensor core (async proxy), then signal the leader
+            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+            __syncwarp();
+            if (lane == 0) mbar_arrive_remote(conv_leader0 + 8u * s);
+        }
+        if (!got && lane == 0) atomicOr(p.status, ZNN_DEV_TMA_WAIT_EXPIRED);
+    }
+    } else {
+        asm volatile("setmaxnreg.inc.sync.aligned.u32 200;");
+        if (!aborted) {
+        // ---------------- epilogue (as in the pre-split kernel) ----------------
+        const int q = warp & 3;
+        const int half = (warp - kEpiWarp0) >> 2;
+        constexpr int CPT = Cfg::kColsPerThread;
+        float acc[CPT];
+#pragma unroll
+        for (int i = 0; i < CPT; i++) acc[i] = 0.0f;
+        const uint32_t acc_empty_leader0 = mapa_shared(acc_empty_bar(0), 0);
+        bool got = true;
+        for (int c = 0; c < nchunks; c++) {
+            const int buf = c & 1;
+            if (lane == 0) got = mbar_wait_bounded(acc_full_bar(buf), (c >> 1) & 1);
+            got = __shfl_sync(0xffffffffu, (int)got, 0) != 0;
+            if (!got) break;
+            tc_fence_after();
+            const uint32_t t0 = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(buf * BN + half * CPT);
+#pragma unroll
+            for (int j = 0; j < CPT / 32; j++) {
+                float v[32];
+                tmem_ld_32x32(t0 + 32u * j, v);
+#pragma unroll
+                for (int i = 0; i < 32; i++) acc[32 * j + i] += v[i];
+            }
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive_remote(acc_empty_leader0 + 8u * buf);
+        }
+        if (!got) {
+            if (lane == 0) atomicOr(p.status, ZNN_DEV_EPI_WAIT_EXPIRED);
+        } else {
+            const int row = row0 + q * 32 + lane;
+            const int cbase = col0 + half * CPT;
+            const bool to_partial = (p.partial != nullptr);
+            float* const out = to_partial ? p.partial + ((size_t)blockIdx.y * gridDim.z + batch) * (size_t)p.M * p.N : p.C;
+            const long long out_ld = to_partial ? (long long)p.N : p.ldc;
+            const long long out_stride = to_partial ? 0 : p.stride_c;
+            const bool vec_ok = ((out_ld & 3) == 0) && ((reinterpret_cast<uintptr_t>(out) & 15) == 0) &&
+                                ((out_stride & 3) == 0);
+            const float alpha = to_partial ? 1.0f : p.alpha, beta = to_partial ? 0.0f : p.beta;
+            if (row < p.M) {
+                float* crow = out + (size_t)batch * out_stride + (size_t)row * out_ld + cbase;
+#pragma unroll
+                for (int c = 0; c < CPT; c += 32) {
+                    const int ncols = min(32, p.N - (cbase + c));
+                    if (ncols <= 0) continue;
+                    if (vec_ok && ncols == 32) {
+                        float4* dst = reinterpret_cast<float4*>(crow + c);
+#pragma unroll
+                        for (int j = 0; j < 8; j++) {
+                            float4 o;
+                            o.x = alpha * acc[c + 4 * j + 0]; o.y = alpha * acc[c + 4 * j + 1];
+                            o.z = alpha * acc[c + 4 * j + 2]; o.w = alpha * acc[c + 4 * j + 3];
+                            if (beta != 0.0f) {
+                                const float4 old = dst[j];
+                                o.x += beta * old.x; o.y += beta * old.y; o.z += beta * old.z; o.w += beta * old.w;
+                            }
+                            dst[j] = o;
+                        }
+                    } else {
+#pragma unroll
+                        for (int j = 0; j < 32; j++) {
+                            if (j < ncols) {
+                                float o = alpha * acc[c + j];
+                                if (beta != 0.0f) o += beta * crow[c + j];
+                                crow[c + j] = o;
+                            }
+                        }
+                    }
+                }
+            }
+        }
+        }
+    }
+
+    tc_fence_before();
+    __syncthreads();
+    cluster_sync_all();
+    if (warp == 1) {
+        tc_fence_after();
+        tmem_dealloc<CTAS>(tmem_base, Cfg::kTmemCols);
+    }
+}
+
 // C = alpha * sum_s partial[s] + beta * C, slices added in order (deterministic)
 __global__ void splitk_reduce_kernel(const float* __restrict__ partial, int splits, int M, int N, int batch, float alpha,
                                      float beta, float* __restrict__ C, long long ldc, long long stride_c)
@@ -709,11 +1069,47 @@ static int launch_tc(const CUtensorMap* maps, const GemmTcParams& p, int batch)
     return ZNN_OK;
 }
 
+static thread_local int t_conv_mode = 1;
+void tc_set_conv_mode(int m) { t_conv_mode = m; }
 static thread_local bool t_splitk_enabled = true;
 void tc_set_splitk(int on) { t_splitk_enabled = (on != 0); }
 static thread_local int t_chunk_kblocks = 8;  // 256 contraction elements per tensor-memory accumulation
 int tc_chunk_kblocks() { return t_chunk_kblocks; }
 void tc_set_chunk_kblocks(int v) { t_chunk_kblocks = v < 1 ? 1 : v; }
+
+struct TcPlan {
+    int bn, tiles_m, tiles_n, k_blocks, chunk, splits, kbps;
+};
+
+static TcPlan make_plan(int M, int N, int K, int batch, int ctas)
+{
+    TcPlan pl;
+    pl.bn = 256;
+    if (N <= 64) pl.bn = 64;
+    else if (N <= 128) pl.bn = 128;
+    const int tile_rows = kTileM * ctas;
+    pl.tiles_m = (M + tile_rows - 1) / tile_rows;
+    pl.tiles_n = (N + pl.bn - 1) / pl.bn;
+    pl.k_blocks = (K + kBK - 1) / kBK;
+    pl.chunk = tc_chunk_kblocks();
+    // Few output tiles and a long contraction (parameter gradients: dW = X^T dY): cut K over
+    // blockIdx.y so that every CTA pair slot of the GPU has work; slices are whole chunks.
+    int splits = 1;
+    const long units = (long)pl.tiles_m * pl.tiles_n * batch;
+    const int slots = sm_count() / ctas;
+    const int max_by_k = pl.k_blocks / (pl.chunk > 8 ? pl.chunk : 8);
+    if (t_splitk_enabled && units * 2 <= slots && max_by_k >= 2) {
+        splits = (int)(slots / units);
+        if (splits > max_by_k) splits = max_by_k;
+        if (splits > 32) splits = 32;
+        if (splits < 1) splits = 1;
+    }
+    int kbps = (pl.k_blocks + splits - 1) / splits;
+    kbps = ((kbps + pl.chunk - 1) / pl.chunk) * pl.chunk;  // whole chunks per slice
+    pl.kbps = kbps;
+    pl.splits = (pl.k_blocks + kbps - 1) / kbps;
+    return pl;
+}
 
 // op(A) is M x K, op(B) is K x N.  ctas = 1 or 2.
 int gemm_tc(int ta, int tb, int M, int N, int K, float alpha, const float* A, long long lda, long long stride_a,
@@ -724,31 +1120,9 @@ int gemm_tc(int ta, int tb, int M, int N, int K, float alpha, const float* A, lo
     if (!status) return fail(ZNN_ERR_CUDA, "no device state (call znn_init first)");
     const int kpad = ((K + kBK - 1) / kBK) * kBK;
     const size_t a_plane = (size_t)batch * M * kpad, b_plane = (size_t)batch * N * kpad;
-    // ---- tile shape and split-K plan ----
-    int bn = 256;
-    if (N <= 64) bn = 64;
-    else if (N <= 128) bn = 128;
-    const int tile_rows = kTileM * ctas;
-    const int tiles_m = (M + tile_rows - 1) / tile_rows, tiles_n = (N + bn - 1) / bn;
-    const int k_blocks = kpad / kBK;
-    const int chunk = tc_chunk_kblocks();
-    // Few output tiles and a long contraction (parameter gradients: dW = X^T dY): cut K over
-    // blockIdx.y so that every CTA pair slot of the GPU has work; slices are whole chunks.
-    int splits = 1;
-    {
-        const long units = (long)tiles_m * tiles_n * batch;
-        const int slots = sm_count() / ctas;
-        const int max_by_k = k_blocks / (chunk > 8 ? chunk : 8);
-        if (t_splitk_enabled && units * 2 <= slots && max_by_k >= 2) {
-            splits = (int)(slots / units);
-            if (splits > max_by_k) splits = max_by_k;
-            if (splits > 32) splits = 32;
-            if (splits < 1) splits = 1;
-        }
-    }
-    int kbps = (k_blocks + splits - 1) / splits;
-    kbps = ((kbps + chunk - 1) / chunk) * chunk;          // whole chunks per slice
-    splits = (k_blocks + kbps - 1) / kbps;
+    const TcPlan pl = make_plan(M, N, K, batch, ctas);
+    const int bn = pl.bn, tiles_m = pl.tiles_m, tiles_n = pl.tiles_n, k_blocks = pl.k_blocks, chunk = pl.chunk;
+    const int splits = pl.splits, kbps = pl.kbps;
     const size_t partial_floats = splits > 1 ? (size_t)splits * batch * M * N : 0;
     const size_t need = (2 * a_plane + 2 * b_plane + partial_floats) * sizeof(float);
     float* ws = (float*)workspace(need);
@@ -787,6 +1161,7 @@ int gemm_tc(int ta, int tb, int M, int N, int K, float alpha, const float* A, lo
     p.M = M; p.N = N; p.k_blocks = k_blocks; p.k_real = K; p.chunk_kblocks = chunk;
     p.kblocks_per_split = kbps;
     p.partial = splits > 1 ? (b_lo + b_plane) : nullptr;
+    p.conv_mode = 0;
     p.tiles_m = tiles_m;
     p.tiles_n = tiles_n;
     p.alpha = alpha; p.beta = beta; p.C = C; p.ldc = ldc; p.stride_c = stride_c; p.status = status;
@@ -813,6 +1188,117 @@ int gemm_tc(int ta, int tb, int M, int N, int K, float alpha, const float* A, lo
         const int cap = sm_count() * 16;
         if (blocks > cap) blocks = cap;
         splitk_reduce_kernel<<<blocks, 256, 0, st>>>(p.partial, splits, M, N, batch, alpha, beta, C, ldc, stride_c);
+        ZNN_LAUNCH_OK("splitk_reduce_kernel");
+    }
+    return ZNN_OK;
+}
+
+
+// ---- direct path host side ----
+// X is the caller's matrix.  K-major: X[row*ld + k]; MN-major: X[k*ld + row].
+static int make_operand_map(CUtensorMap* tm, const float* X, bool mn_major, int rows, int K, long long ld,
+                            long long stride, int batch, int box_rows)
+{
+    EncodeTiledFn enc = encode_fn();
+    if (!enc) return fail(ZNN_ERR_CUDA, "cuTensorMapEncodeTiled entry point not available");
+    const cuuint64_t inner = mn_major ? (cuuint64_t)rows : (cuuint64_t)K;
+    const cuuint64_t outer = mn_major ? (cuuint64_t)K : (cuuint64_t)rows;
+    cuuint64_t dims[3] = {inner, outer, (cuuint64_t)batch};
+    const cuuint64_t bstride = (batch > 1) ? (cuuint64_t)stride * 4 : (cuuint64_t)ld * 4 * outer;
+    cuuint64_t strides[2] = {(cuuint64_t)ld * 4, bstride};
+    cuuint32_t box[3] = {(cuuint32_t)kBK, (cuuint32_t)(mn_major ? kBK : box_rows), 1};
+    cuuint32_t estr[3] = {1, 1, 1};
+    CUresult r = enc(tm, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 3, const_cast<float*>(X), dims, strides, box, estr,
+                     CU_TENSOR_MAP_INTERLEAVE_NONE,
+                     mn_major ? CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B : CU_TENSOR_MAP_SWIZZLE_128B,
+                     CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) return fail(ZNN_ERR_CUDA, "cuTensorMapEncodeTiled (operand) failed with %d", (int)r);
+    return ZNN_OK;
+}
+
+template <int BN, bool A_MN, bool B_MN>
+static int launch_direct(const CUtensorMap& ma, const CUtensorMap& mb, const GemmTcParams& p, int batch)
+{
+    using Cfg = DirectCfg<BN>;
+    static bool attr_set = false;
+    auto kern = gemm3x_direct_kernel<BN, A_MN, B_MN>;
+    if (!attr_set) {
+        ZNN_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmemBytes));
+        attr_set = true;
+    }
+    const int splits = (p.k_blocks + p.kblocks_per_split - 1) / p.kblocks_per_split;
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3((unsigned)(p.tiles_m * p.tiles_n * 2), (unsigned)splits, (unsigned)batch);
+    cfg.blockDim = dim3(kDirectThreads, 1, 1);
+    cfg.dynamicSmemBytes = Cfg::kSmemBytes;
+    cfg.stream = stream();
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = 2;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    cudaEvent_t* ev = prof_begin(2.0 * p.M * (double)p.N * p.k_real * batch);
+    ZNN_CUDA_OK(cudaLaunchKernelEx(&cfg, kern, ma, mb, p));
+    prof_end(ev);
+    count_launch();
+    return ZNN_OK;
+}
+
+template <int BN>
+static int launch_direct_major(bool a_mn, bool b_mn, const CUtensorMap& ma, const CUtensorMap& mb, const GemmTcParams& p,
+                               int batch)
+{
+    if (a_mn) return b_mn ? launch_direct<BN, true, true>(ma, mb, p, batch) : launch_direct<BN, true, false>(ma, mb, p, batch);
+    return b_mn ? launch_direct<BN, false, true>(ma, mb, p, batch) : launch_direct<BN, false, false>(ma, mb, p, batch);
+}
+
+// True when TMA can read both operands where they lie: 16-byte aligned bases, leading dimensions and batch strides.
+bool gemm_tc_direct_eligible(const float* A, long long lda, long long stride_a, const float* B, long long ldb,
+                             long long stride_b, int batch)
+{
+    auto ok = [&](const float* X, long long ld, long long stride) {
+        return (reinterpret_cast<uintptr_t>(X) & 15) == 0 && (ld & 3) == 0 && (batch == 1 || (stride & 3) == 0);
+    };
+    return ok(A, lda, stride_a) && ok(B, ldb, stride_b);
+}
+
+int gemm_tc_direct(int ta, int tb, int M, int N, int K, float alpha, const float* A, long long lda, long long stride_a,
+                   const float* B, long long ldb, long long stride_b, float beta, float* C, long long ldc,
+                   long long stride_c, int batch)
+{
+    int* status = device_status_word();
+    if (!status) return fail(ZNN_ERR_CUDA, "no device state (call znn_init first)");
+    const TcPlan pl = make_plan(M, N, K, batch, 2);
+    float* partial = nullptr;
+    if (pl.splits > 1) {
+        partial = (float*)workspace((size_t)pl.splits * batch * M * N * sizeof(float));
+        if (!partial) return fail(ZNN_ERR_NOMEM, "split-K scratch could not be allocated");
+    }
+    const bool a_mn = (ta == ZNN_TRANS), b_mn = (tb == ZNN_NO_TRANS);
+    CUtensorMap ma, mb;
+    int rc;
+    if ((rc = make_operand_map(&ma, A, a_mn, M, K, lda, stride_a, batch, kTileM))) return rc;
+    if ((rc = make_operand_map(&mb, B, b_mn, N, K, ldb, stride_b, batch, pl.bn / 2))) return rc;
+    GemmTcParams p;
+    p.M = M; p.N = N; p.k_blocks = pl.k_blocks; p.k_real = K; p.chunk_kblocks = pl.chunk;
+    p.kblocks_per_split = pl.kbps;
+    p.partial = partial;
+    p.conv_mode = t_conv_mode;
+    p.tiles_m = pl.tiles_m;
+    p.tiles_n = pl.tiles_n;
+    p.alpha = alpha; p.beta = beta; p.C = C; p.ldc = ldc; p.stride_c = stride_c; p.status = status;
+    if (pl.bn == 256) rc = launch_direct_major<256>(a_mn, b_mn, ma, mb, p, batch);
+    else if (pl.bn == 128) rc = launch_direct_major<128>(a_mn, b_mn, ma, mb, p, batch);
+    else rc = launch_direct_major<64>(a_mn, b_mn, ma, mb, p, batch);
+    if (rc) return rc;
+    if (pl.splits > 1) {
+        const size_t total = (size_t)batch * M * N;
+        int blocks = (int)((total + 255) / 256);
+        const int cap = sm_count() * 16;
+        if (blocks > cap) blocks = cap;
+        splitk_reduce_kernel<<<blocks, 256, 0, stream()>>>(partial, pl.splits, M, N, batch, alpha, beta, C, ldc, stride_c);
         ZNN_LAUNCH_OK("splitk_reduce_kernel");
     }
     return ZNN_OK;
