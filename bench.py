@@ -197,6 +197,13 @@ def run_gpu(args):
     torch.cuda.set_stream(stream)
     L.call("znn_set_stream", stream.cuda_stream)
 
+    if args.workload == "configs":
+        if rank == 0:
+            print(json.dumps({"metric": "config_timings", "n_gpus": 1, "data": "synthetic",
+                              "configs": configs_part(args, L, torch, stream)}), flush=True)
+        if world > 1:
+            dist.destroy_process_group()
+        return 0
     if args.workload == "gpt":          # the GPT training step alone (used for profiling captures)
         gpt = gpt_part(args, L, torch, dist, stream, world, rank, local)
         if rank == 0:
@@ -447,6 +454,82 @@ def gpt_part(args, L, torch, dist, stream, world, rank, local):
     return out
 
 
+def configs_part(args, L, torch, stream):
+    """The remaining workload-definition configs on one GPU, device timed (CUDA events on the launching stream):
+    C1 MLP step, C3 CNN step (reference shape and padded shape), C4 transformer block forward+backward,
+    C5 greedy decode.  Reported next to the headline numbers; each also runs against the CPU oracle in tests/."""
+    import numpy as np
+    from znn_b200.models import Model
+
+    out = {}
+    r = np.random.default_rng(7)
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+
+    def he(m, scheme="he"):
+        P = {}
+        for name, shape, _, fan_in in m.params:
+            if fan_in:
+                std = (2.0 / fan_in) ** 0.5 if scheme == "he" else 0.02
+                P[name] = (r.standard_normal(shape, np.float32) * np.float32(std))
+            else:
+                P[name] = np.ones(shape, np.float32) if "ln_" in name else np.zeros(shape, np.float32)
+        m.set_params(P)
+
+    def time_steps(fn, steps, warmup=5):
+        for _ in range(warmup):
+            fn()
+        torch.cuda.synchronize()
+        e0.record(stream)
+        for _ in range(steps):
+            fn()
+        e1.record(stream)
+        torch.cuda.synchronize()
+        return e0.elapsed_time(e1) / steps
+
+    for key, kind, dims, batch in (("mlp_784_128_64_10_b64", "mlp", (784, 128, 64, 10), 64),
+                                   ("cnn_reference_shape_b64", "cnn_ref", (), 64),
+                                   ("cnn_padded_shape_b256", "cnn_padded", (), 256)):
+        m = Model(kind, dims, arena_bytes=2 << 30)
+        he(m)
+        m.set_option("lr", 0.01)
+        m.set_option("momentum", 0.9)
+        x = (r.integers(0, 256, (batch, 784)).astype(np.float32) / np.float32(255.0))
+        t = r.integers(0, 10, batch).astype(np.int32)
+        dx, dt = torch.from_numpy(x).cuda(), torch.from_numpy(t).cuda()
+        ms = time_steps(lambda: m.train_step_device(dx.data_ptr(), dt.data_ptr(), batch), 200)
+        ms_e2e = time_steps(lambda: m.train_step(x, t), 50)
+        out[key] = {"us_per_step": ms * 1e3, "steps_per_s": 1e3 / ms, "images_per_s": batch * 1e3 / ms,
+                    "e2e_us_per_step": ms_e2e * 1e3, "tape_ops": m.last_step_ops(), "bound": "launch latency"}
+        m.close()
+
+    # C4: pre-norm block, d_model 512, 8 heads, FFN 2048, batch 32 x seq 256 (168 GFLOP per forward+backward)
+    m = Model("block", (512, 8), arena_bytes=8 << 30)
+    he(m, "n002")
+    x = r.standard_normal((32, 256, 512), np.float32)
+    dy = r.standard_normal((32, 256, 512), np.float32)
+    ms = time_steps(lambda: m.block_fwd_bwd(x, dy), 10, warmup=3)
+    out["transformer_block_b32_t256_d512"] = {"ms_fwd_bwd_incl_host_copies": ms, "tflops": 168e9 / (ms * 1e-3) / 1e12,
+                                              "note": "x and dy uploaded, y and dx read back inside the timed region"}
+    m.close()
+
+    # C5 decode: 64 prompts of 16 ids, 256 new tokens, greedy, full re-forward per token as the reference does
+    m = Model("gpt", (8192, 1024, 768, 12, 6), arena_bytes=40 << 30)
+    he(m, "n002")
+    prompts = r.integers(0, 8192, (64, 16)).astype(np.float32)
+    n_new = 256 if args.steps >= 10 else 32
+    m.greedy_decode(prompts, 2)
+    torch.cuda.synchronize()
+    e0.record(stream)
+    m.greedy_decode(prompts, n_new)
+    e1.record(stream)
+    torch.cuda.synchronize()
+    ms = e0.elapsed_time(e1)
+    out["gpt_greedy_decode_b64"] = {"new_tokens": n_new, "tokens_per_s": 64 * n_new / (ms * 1e-3), "ms_total": ms,
+                                    "note": "no KV cache: the reference re-runs the whole window per token"}
+    m.close()
+    return out
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -455,8 +538,9 @@ def main():
     ap.add_argument("--n", type=int, default=8192)
     ap.add_argument("--impl", default="znn_b200", choices=["znn_b200", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
-    ap.add_argument("--workload", default="all", choices=["all", "matmul", "gpt"],
-                    help="matmul: the headline MatMul sweep step only; all: also the GPT training step")
+    ap.add_argument("--workload", default="all", choices=["all", "matmul", "gpt", "configs"],
+                    help="matmul: the headline MatMul sweep step only; all: also the GPT training step; "
+                         "configs: the MLP / CNN / block / decode configs on one GPU")
     args = ap.parse_args()
     if args.impl == "reference":
         return run_reference(args)

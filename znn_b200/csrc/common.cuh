@@ -21,6 +21,8 @@ int* device_status_word();
 
 // Shim-owned scratch for GEMM operand planes; grows on demand.
 void* workspace(size_t bytes);
+// slot 1 is a second, independent block for callers that hold scratch across a GEMM call (conv im2col)
+void* workspace_slot(int slot, size_t bytes);
 
 int sm_count();
 

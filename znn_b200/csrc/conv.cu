@@ -1,5 +1,9 @@
 // Conv2D (NCHW, stride 1, optional zero padding) and MaxPool2D.
 //
+// Backward of all but tiny layers is lowered to GEMMs over an explicit im2col matrix:
+//   dW[Co,K] += dYt^T . col,  dcol = dYt . W  followed by a col2im gather,  dbias = column sums of dYt,
+// with col[p][k] the input taps under output pixel p and dYt the gradient in pixel-major order.
+//
 // The reference's convolutions have K = Ci*KH*KW between 9 and 288 and at most
 // 64 output channels: far below a tensor-core tile, and a few GFLOP per step at
 // most.  They run as direct CUDA-core kernels that keep the reference's
@@ -183,6 +187,67 @@ __global__ void maxpool2d_bwd_kernel(const float* __restrict__ X, const float* _
     }
 }
 
+
+// ---- backward through GEMMs: im2col, pixel-major gradient, col2im ----
+// col[p][k], p = (n, h, w) output pixel, k = (ci, kh, kw): the row of input taps under output pixel p
+// (zero where the tap falls into the padding).  K contiguous.
+__global__ void im2col_kernel(const float* __restrict__ X, float* __restrict__ col, int N, int Ci, int H, int Wd, int KH,
+                              int KW, int pad, int Ho, int Wo)
+{
+    const int K = Ci * KH * KW;
+    const size_t total = (size_t)N * Ho * Wo * K;
+    for (size_t e = blockIdx.x * (size_t)blockDim.x + threadIdx.x; e < total; e += (size_t)gridDim.x * blockDim.x) {
+        const int k = (int)(e % K);
+        const size_t p = e / K;
+        const int w = (int)(p % Wo), h = (int)((p / Wo) % Ho), n = (int)(p / ((size_t)Wo * Ho));
+        const int kw = k % KW, kh = (k / KW) % KH, ci = k / (KW * KH);
+        const int ih = h + kh - pad, iw = w + kw - pad;
+        col[e] = (ih >= 0 && ih < H && iw >= 0 && iw < Wd) ? X[(((size_t)n * Ci + ci) * H + ih) * Wd + iw] : 0.0f;
+    }
+}
+
+// dY [N][Co][HW] -> dYt [N*HW][Co] (per-sample transpose through a shared tile)
+__global__ void nchw_to_pixel_major_kernel(const float* __restrict__ dY, float* __restrict__ dYt, int Co, int HW)
+{
+    __shared__ float tile[32][33];
+    const size_t n = blockIdx.z;
+    const float* src = dY + n * (size_t)Co * HW;
+    float* dst = dYt + n * (size_t)HW * Co;
+    const int p0 = blockIdx.x * 32, c0 = blockIdx.y * 32;
+    for (int j = threadIdx.y; j < 32; j += 8) {
+        const int c = c0 + j, p = p0 + threadIdx.x;
+        tile[j][threadIdx.x] = (c < Co && p < HW) ? src[(size_t)c * HW + p] : 0.0f;
+    }
+    __syncthreads();
+    for (int j = threadIdx.y; j < 32; j += 8) {
+        const int p = p0 + j, c = c0 + threadIdx.x;
+        if (p < HW && c < Co) dst[(size_t)p * Co + c] = tile[threadIdx.x][j];
+    }
+}
+
+// dX[n,ci,ih,iw] += sum_{kh,kw} dcol[p(n, ih-kh+pad, iw-kw+pad)][ci,kh,kw]   (gather: no atomics)
+__global__ void col2im_add_kernel(const float* __restrict__ dcol, float* __restrict__ dX, int N, int Ci, int H, int Wd,
+                                  int KH, int KW, int pad, int Ho, int Wo)
+{
+    const int K = Ci * KH * KW;
+    const size_t total = (size_t)N * Ci * H * Wd;
+    for (size_t e = blockIdx.x * (size_t)blockDim.x + threadIdx.x; e < total; e += (size_t)gridDim.x * blockDim.x) {
+        const int iw = (int)(e % Wd), ih = (int)((e / Wd) % H);
+        const int ci = (int)((e / ((size_t)Wd * H)) % Ci), n = (int)(e / ((size_t)Wd * H * Ci));
+        float acc = 0.0f;
+        for (int kh = 0; kh < KH; kh++) {
+            const int h = ih - kh + pad;
+            if (h < 0 || h >= Ho) continue;
+            for (int kw = 0; kw < KW; kw++) {
+                const int w = iw - kw + pad;
+                if (w < 0 || w >= Wo) continue;
+                acc += dcol[(((size_t)n * Ho + h) * Wo + w) * K + (ci * KH + kh) * KW + kw];
+            }
+        }
+        dX[e] += acc;
+    }
+}
+
 }  // namespace znn
 
 using namespace znn;
@@ -218,6 +283,46 @@ int znn_conv2d_bwd(const float* X, const float* W, const float* dY, float* dX, f
     if (N == 0) return ZNN_OK;
     if (!stream()) return fail(ZNN_ERR_CUDA, "no CUDA device state; call znn_init (no CPU fallback)");
     ZNN_REQUIRE(X && W && dY, "NULL pointer");
+    const size_t P = (size_t)N * Ho * Wo;   // output pixels
+    const int K = Ci * KH * KW;
+    // Large layers: lower the backward pass to GEMMs over an explicit im2col matrix (the contraction runs
+    // on the tensor cores / the split-K FMA kernel).  Tiny layers keep the direct kernels below.
+    if (P >= 4096 && P * (size_t)K <= ((size_t)1 << 31) && P <= 0x7fffffff / 2) {
+        const size_t col_f = (dW || dX) ? P * K : 0;
+        const size_t dyt_f = P * (size_t)Co;
+        float* ws = (float*)workspace_slot(1, (col_f + dyt_f) * sizeof(float));
+        if (!ws) return fail(ZNN_ERR_NOMEM, "conv backward scratch (%zu bytes)", (col_f + dyt_f) * sizeof(float));
+        float* col = ws;              // im2col(X) for dW, then reused as dcol for dX
+        float* dyt = ws + col_f;
+        const int cap = sm_count() * 16;
+        {
+            dim3 grid(ceil_div(Ho * Wo, 32), ceil_div(Co, 32), N), block(32, 8);
+            nchw_to_pixel_major_kernel<<<grid, block, 0, stream()>>>(dY, dyt, Co, Ho * Wo);
+            ZNN_LAUNCH_OK("nchw_to_pixel_major_kernel");
+        }
+        int rc;
+        if (dbias && (rc = znn_add_bias_bwd(dyt, nullptr, dbias, (int)P, Co))) return rc;   // column sums over pixels
+        if (dW) {
+            size_t blocks = (P * K + 255) / 256;
+            if (blocks > (size_t)cap) blocks = cap;
+            im2col_kernel<<<(unsigned)blocks, 256, 0, stream()>>>(X, col, N, Ci, H, Wd, KH, KW, pad, Ho, Wo);
+            ZNN_LAUNCH_OK("im2col_kernel");
+            // dW[Co,K] += dYt^T[Co,P] . col[P,K]
+            if ((rc = znn_sgemm(ZNN_ROW_MAJOR, ZNN_TRANS, ZNN_NO_TRANS, Co, K, (int)P, 1.0f, dyt, Co, col, K, 1.0f, dW, K)))
+                return rc;
+        }
+        if (dX) {
+            // dcol[P,K] = dYt[P,Co] . W[Co,K], then gather back onto the input
+            if ((rc = znn_sgemm(ZNN_ROW_MAJOR, ZNN_NO_TRANS, ZNN_NO_TRANS, (int)P, K, Co, 1.0f, dyt, Co, W, K, 0.0f, col, K)))
+                return rc;
+            const size_t total = (size_t)N * Ci * H * Wd;
+            size_t blocks = (total + 255) / 256;
+            if (blocks > (size_t)cap) blocks = cap;
+            col2im_add_kernel<<<(unsigned)blocks, 256, 0, stream()>>>(col, dX, N, Ci, H, Wd, KH, KW, pad, Ho, Wo);
+            ZNN_LAUNCH_OK("col2im_add_kernel");
+        }
+        return ZNN_OK;
+    }
     if (dbias) {
         conv2d_bwd_bias_kernel<<<Co, 256, 256 * sizeof(float), stream()>>>(dY, dbias, N, Co, Ho * Wo);
         ZNN_LAUNCH_OK("conv2d_bwd_bias_kernel");

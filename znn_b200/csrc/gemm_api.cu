@@ -14,6 +14,8 @@ bool gemm_tc_direct_eligible(const float* A, long long lda, long long stride_a, 
 int gemm_tc_direct(int ta, int tb, int M, int N, int K, float alpha, const float* A, long long lda, long long stride_a,
                    const float* B, long long ldb, long long stride_b, float beta, float* C, long long ldc,
                    long long stride_c, int batch);
+int launch_splitk_reduce(const float* partial, int splits, int M, int N, int batch, float alpha, float beta, float* C,
+                         long long ldc, long long stride_c);
 int tc_profile_enable(int enable);
 void tc_set_chunk_kblocks(int v);
 void tc_set_splitk(int on);
@@ -25,14 +27,18 @@ int tc_profile_read(double* kernel_ms, long long* launches, double* flops);
 __global__ void __launch_bounds__(256)
 sgemm_fma_kernel(int M, int N, int K, float alpha, const float* __restrict__ A, long long sa_i, long long sa_p,
                  long long stride_a, const float* __restrict__ B, long long sb_p, long long sb_j, long long stride_b,
-                 float beta, float* __restrict__ C, long long ldc, long long stride_c)
+                 float beta, float* __restrict__ C, long long ldc, long long stride_c, int splits, int k_per_split)
 {
     __shared__ float As[16][64 + 4];
     __shared__ float Bs[16][64 + 4];
-    const int b = blockIdx.z;
+    // blockIdx.z = slice * batch + b; with split-K (splits > 1) C is the [splits][batch][M][N] partial buffer
+    const int nbatch = gridDim.z / splits;
+    const int b = blockIdx.z % nbatch, slice = blockIdx.z / nbatch;
+    const int k_begin = slice * k_per_split;
+    const int k_end = min(K, k_begin + k_per_split);
     A += (size_t)b * stride_a;
     B += (size_t)b * stride_b;
-    C += (size_t)b * stride_c;
+    C += (size_t)b * stride_c + (size_t)slice * nbatch * stride_c;
     const int i0 = blockIdx.y * 64, j0 = blockIdx.x * 64;
     const int tx = threadIdx.x & 15, ty = threadIdx.x >> 4;
     float acc[4][4];
@@ -44,18 +50,18 @@ sgemm_fma_kernel(int M, int N, int K, float alpha, const float* __restrict__ A, 
     // loader mapping: pick the index that is contiguous in memory as the fast one
     const bool a_p_fast = (sa_p == 1);
     const bool b_j_fast = (sb_j == 1);
-    for (int p0 = 0; p0 < K; p0 += 16) {
+    for (int p0 = k_begin; p0 < k_end; p0 += 16) {
 #pragma unroll
         for (int t = 0; t < 4; t++) {
             const int e = threadIdx.x + t * 256;  // 0..1023
             int li, lp;
             if (a_p_fast) { lp = e & 15; li = e >> 4; } else { li = e & 63; lp = e >> 6; }
             const int gi = i0 + li, gp = p0 + lp;
-            As[lp][li] = (gi < M && gp < K) ? A[(size_t)gi * sa_i + (size_t)gp * sa_p] : 0.0f;
+            As[lp][li] = (gi < M && gp < k_end) ? A[(size_t)gi * sa_i + (size_t)gp * sa_p] : 0.0f;
             int lj, lq;
             if (b_j_fast) { lj = e & 63; lq = e >> 6; } else { lq = e & 15; lj = e >> 4; }
             const int gj = j0 + lj, gq = p0 + lq;
-            Bs[lq][lj] = (gj < N && gq < K) ? B[(size_t)gq * sb_p + (size_t)gj * sb_j] : 0.0f;
+            Bs[lq][lj] = (gj < N && gq < k_end) ? B[(size_t)gq * sb_p + (size_t)gj * sb_j] : 0.0f;
         }
         __syncthreads();
 #pragma unroll
@@ -159,9 +165,32 @@ static int gemm_dispatch(int ta, int tb, int M, int N, int K, float alpha, const
 
     const long long sa_i = (ta == ZNN_NO_TRANS) ? lda : 1, sa_p = (ta == ZNN_NO_TRANS) ? 1 : lda;
     const long long sb_p = (tb == ZNN_NO_TRANS) ? ldb : 1, sb_j = (tb == ZNN_NO_TRANS) ? 1 : ldb;
+    // few output tiles and a long contraction (small-channel conv weight gradients): split K over blocks,
+    // partial tiles to scratch, fixed-order reduction
+    const long tiles = (long)ceil_div(N, 64) * ceil_div(M, 64) * batch;
+    int splits = 1;
+    if (tiles * 2 <= sm_count() && K >= 2048) {
+        splits = (int)((2L * sm_count()) / tiles);
+        if (splits > K / 512) splits = K / 512;
+        if (splits > 128) splits = 128;
+        if ((long)splits * batch > 65535) splits = 65535 / batch;
+        if (splits < 1) splits = 1;
+    }
+    if (splits > 1) {
+        int kps = (K + splits - 1) / splits;
+        kps = ((kps + 15) / 16) * 16;
+        splits = (K + kps - 1) / kps;
+        float* partial = (float*)workspace((size_t)splits * batch * M * N * sizeof(float));
+        if (!partial) return fail(ZNN_ERR_NOMEM, "split-K scratch could not be allocated");
+        dim3 grid(ceil_div(N, 64), ceil_div(M, 64), batch * splits);
+        sgemm_fma_kernel<<<grid, 256, 0, stream()>>>(M, N, K, 1.0f, A, sa_i, sa_p, stride_a, B, sb_p, sb_j, stride_b, 0.0f,
+                                                     partial, N, (long long)M * N, splits, kps);
+        ZNN_LAUNCH_OK("sgemm_fma_kernel (split-K)");
+        return launch_splitk_reduce(partial, splits, M, N, batch, alpha, beta, C, ldc, stride_c);
+    }
     dim3 grid(ceil_div(N, 64), ceil_div(M, 64), batch);
     sgemm_fma_kernel<<<grid, 256, 0, stream()>>>(M, N, K, alpha, A, sa_i, sa_p, stride_a, B, sb_p, sb_j, stride_b,
-                                                 beta, C, ldc, stride_c);
+                                                 beta, C, ldc, stride_c, 1, K);
     ZNN_LAUNCH_OK("sgemm_fma_kernel");
     return ZNN_OK;
 }

@@ -949,6 +949,19 @@ __global__ void splitk_reduce_kernel(const float* __restrict__ partial, int spli
 // ---------------------------------------------------------------------------
 // host side
 // ---------------------------------------------------------------------------
+int launch_splitk_reduce(const float* partial, int splits, int M, int N, int batch, float alpha, float beta, float* C,
+                         long long ldc, long long stride_c)
+{
+    const size_t total = (size_t)batch * M * N;
+    int blocks = (int)((total + 255) / 256);
+    const int cap = sm_count() * 16;
+    if (blocks > cap) blocks = cap;
+    if (blocks < 1) blocks = 1;
+    splitk_reduce_kernel<<<blocks, 256, 0, stream()>>>(partial, splits, M, N, batch, alpha, beta, C, ldc, stride_c);
+    ZNN_LAUNCH_OK("splitk_reduce_kernel");
+    return ZNN_OK;
+}
+
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
                                   const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
                                   CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);

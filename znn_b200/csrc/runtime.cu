@@ -34,8 +34,8 @@ struct DeviceState {
     bool ready = false;
     cudaStream_t own_stream = nullptr;
     int* status = nullptr;  // device int
-    void* ws = nullptr;
-    size_t ws_bytes = 0;
+    void* ws[2] = {nullptr, nullptr};   // slot 0: GEMM planes / partials / row-op partials; slot 1: conv im2col
+    size_t ws_bytes[2] = {0, 0};
     int sms = 0;
 };
 
@@ -92,28 +92,30 @@ int sm_count()
     return s ? s->sms : 0;
 }
 
-void* workspace(size_t bytes)
+void* workspace_slot(int slot, size_t bytes)
 {
     DeviceState* s = cur(true);
-    if (!s) return nullptr;
-    if (bytes <= s->ws_bytes) return s->ws;
+    if (!s || slot < 0 || slot > 1) return nullptr;
+    if (bytes <= s->ws_bytes[slot]) return s->ws[slot];
     // Growing: everything queued so far may still read the old block.
     cudaStreamSynchronize(stream());
-    if (s->ws) cudaFree(s->ws);
-    s->ws = nullptr;
-    s->ws_bytes = 0;
+    if (s->ws[slot]) cudaFree(s->ws[slot]);
+    s->ws[slot] = nullptr;
+    s->ws_bytes[slot] = 0;
     size_t want = bytes + (bytes >> 3);
-    if (cudaMalloc(&s->ws, want) != cudaSuccess) {
+    if (cudaMalloc(&s->ws[slot], want) != cudaSuccess) {
         cudaGetLastError();
         want = bytes;
-        if (cudaMalloc(&s->ws, want) != cudaSuccess) {
+        if (cudaMalloc(&s->ws[slot], want) != cudaSuccess) {
             cudaGetLastError();
             return nullptr;
         }
     }
-    s->ws_bytes = want;
-    return s->ws;
+    s->ws_bytes[slot] = want;
+    return s->ws[slot];
 }
+
+void* workspace(size_t bytes) { return workspace_slot(0, bytes); }
 
 long long launches_and_reset(int reset);
 
