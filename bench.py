@@ -197,6 +197,13 @@ def run_gpu(args):
     torch.cuda.set_stream(stream)
     L.call("znn_set_stream", stream.cuda_stream)
 
+    if args.workload == "rowops":
+        if rank == 0:
+            print(json.dumps({"metric": "rowop_hbm_bandwidth", "n_gpus": 1, "data": "synthetic",
+                              "rowops": rowops_part(args, L, torch, stream)}), flush=True)
+        if world > 1:
+            dist.destroy_process_group()
+        return 0
     if args.workload == "configs":
         if rank == 0:
             print(json.dumps({"metric": "config_timings", "n_gpus": 1, "data": "synthetic",
@@ -530,6 +537,77 @@ def configs_part(args, L, torch, stream):
     return out
 
 
+def rowops_part(args, L, torch, stream):
+    """Row-wise / elementwise kernels at transformer sizes, each timed alone with CUDA events on the launching
+    stream; working sets exceed the 126 MB L2.  GB/s = algorithmic bytes per launch / time, compared with the
+    measured HBM copy bandwidth."""
+    peaks, kind = read_peaks()
+    hbm = peaks["hbm_gbs"]
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    f32 = torch.float32
+
+    def rnd(*shape):
+        return torch.randn(shape, device="cuda", dtype=f32)
+
+    def timeit(fn, iters=20):
+        for _ in range(3):
+            fn()
+        torch.cuda.synchronize()
+        e0.record(stream)
+        for _ in range(iters):
+            fn()
+        e1.record(stream)
+        torch.cuda.synchronize()
+        return e0.elapsed_time(e1) / iters
+
+    res = {}
+
+    def rec(name, nbytes, fn):
+        ms = timeit(fn)
+        gbs = nbytes / (ms * 1e-3) / 1e9
+        res[name] = {"us": ms * 1e3, "algorithmic_MB": nbytes / 1e6, "GBps": gbs, "frac_of_hbm_" + kind: gbs / hbm}
+
+    M, N = 8192, 3072 * 4                       # 403 MB per tensor
+    n = M * N
+    A, B, Cc = rnd(M, N), rnd(M, N), rnd(M, N)
+    bias = rnd(N)
+    p = lambda t: t.data_ptr()
+    rec("add_bias_fwd", 8 * n, lambda: L.call("znn_add_bias_fwd", p(A), p(bias), p(Cc), M, N))
+    rec("add_bias_bwd(dA+=dC, dbias)", 12 * n, lambda: L.call("znn_add_bias_bwd", p(A), p(B), p(bias), M, N))
+    rec("relu_fwd", 8 * n, lambda: L.call("znn_relu_fwd", p(A), p(Cc), n))
+    rec("gelu_fwd", 8 * n, lambda: L.call("znn_gelu_fwd", p(A), p(Cc), n))
+    rec("gelu_bwd", 16 * n, lambda: L.call("znn_gelu_bwd", p(A), p(B), p(Cc), n))
+    rec("add_fwd", 12 * n, lambda: L.call("znn_add_fwd", p(A), p(B), p(Cc), n))
+    rec("accumulate", 12 * n, lambda: L.call("znn_accumulate", p(A), p(Cc), n))
+    rec("sgd_momentum_step", 20 * n, lambda: L.call("znn_sgd_step", p(A), p(B), p(Cc), 1e-9, 0.9, 1.0, n))
+    T = 1024
+    ns = n // (T * T)
+    rec("causal_softmax_fwd", 8 * n, lambda: L.call("znn_causal_softmax_fwd", p(A), 0.125, p(Cc), ns, T))
+    rec("causal_softmax_bwd", 16 * n, lambda: L.call("znn_causal_softmax_bwd", p(Cc), p(B), 0.125, p(A), ns, T))
+    rec("softmax_fwd_rows1024", 8 * n, lambda: L.call("znn_softmax_fwd", p(A), p(Cc), n // T, T))
+    D = 768
+    rows = n // D
+    G = rnd(D)
+    dG = torch.zeros(D, device="cuda", dtype=f32)
+    rec("rmsnorm_fwd_768", 8 * n, lambda: L.call("znn_rmsnorm_fwd", p(A), p(G), 1e-5, p(Cc), rows, D))
+    rec("rmsnorm_bwd_768(dX,dG)", 16 * n, lambda: L.call("znn_rmsnorm_bwd", p(A), p(G), p(B), 1e-5, p(Cc), p(dG), rows, D))
+    V = 8192
+    Mx = n // V
+    tg = torch.randint(0, V, (Mx,), device="cuda", dtype=torch.int32)
+    loss = torch.zeros(1, device="cuda", dtype=f32)
+    rec("softmax_xent_fwd_vocab8192", 8 * n, lambda: L.call("znn_softmax_xent_fwd", p(A), p(tg), p(Cc), p(loss), Mx, V))
+    rec("softmax_xent_bwd_vocab8192", 12 * n, lambda: L.call("znn_softmax_xent_bwd", p(Cc), p(tg), p(B), Mx, V))
+    ids = torch.randint(0, V, (n // D,), device="cuda").to(f32)
+    W = rnd(V, D)
+    rec("embedding_fwd", 8 * n, lambda: L.call("znn_embedding_fwd", p(W), p(ids), p(Cc), n // D, D, V))
+    dims = torch.tensor([n // (T * 12 * 64), T, 12, 64], dtype=torch.int64)
+    rec("transpose_head_split(1,2)", 8 * n, lambda: L.call("znn_transpose_fwd", p(A), p(Cc), dims.data_ptr(), 4, 1, 2))
+    dims2 = torch.tensor([n // (T * 64), T, 64], dtype=torch.int64)
+    rec("transpose_last2(K->K^T)", 8 * n, lambda: L.call("znn_transpose_fwd", p(A), p(Cc), dims2.data_ptr(), 3, 1, 2))
+    rec("argmax_rows_vocab8192", 4 * n, lambda: L.call("znn_argmax", p(A), p(bias), Mx, V, 1))
+    return {"hbm_peak_GBps": hbm, "peak_source": kind, "tensor_MB": 4 * n / 1e6, "ops": res}
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -538,7 +616,7 @@ def main():
     ap.add_argument("--n", type=int, default=8192)
     ap.add_argument("--impl", default="znn_b200", choices=["znn_b200", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
-    ap.add_argument("--workload", default="all", choices=["all", "matmul", "gpt", "configs"],
+    ap.add_argument("--workload", default="all", choices=["all", "matmul", "gpt", "configs", "rowops"],
                     help="matmul: the headline MatMul sweep step only; all: also the GPT training step; "
                          "configs: the MLP / CNN / block / decode configs on one GPU")
     args = ap.parse_args()

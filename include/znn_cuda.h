@@ -73,6 +73,12 @@ int znn_sgemm_batched_strided(int trans_a, int trans_b, int M, int N, int K, flo
                               const float* A, int lda, long long stride_a,
                               const float* B, int ldb, long long stride_b, float beta,
                               float* C, int ldc, long long stride_c, int batch);
+/* Fused form of Linear.forward = addBias(matmul(x, W), b) (src/nn.zig:44-51): Y[M,N] = X[M,K].W[K,N] + bias[N]
+ * in one pass (the bias is added in the GEMM epilogue); an addition, the two separate ops remain.
+ * Backward of the pair (src/autodiff.zig:593-641 and :652-672 chained): dX += dY.W^T, dW += X^T.dY,
+ * dbias += column sums of dY; NULL gradient pointers are skipped. */
+int znn_linear_fwd(const float* X, const float* W, const float* bias, float* Y, int M, int K, int N);
+int znn_linear_bwd(const float* X, const float* W, const float* dY, float* dX, float* dW, float* dbias, int M, int K, int N);
 /* path: 0 = automatic, 1 = fp32 FMA kernel, 2 = tcgen05 one CTA per tile over pre-split operand
  * planes, 3 = tcgen05 CTA pairs over pre-split planes, 4 = tcgen05 CTA pairs reading the operands
  * in place (hi/lo split in shared memory; needs 16-byte aligned bases and leading dimensions that

@@ -8,7 +8,7 @@
  *    handles; `znn_graph_op` appends one op by its reference builder name
  *    ("matmul", "addBias", "relu", "gelu", "softmaxCrossEntropy", "reshape",
  *    "transposeND", "mulScalar", "add", "conv2d", "maxpool2d", "softmax",
- *    "rmsNorm", "batchMatMul", "embedding", plus "causalSoftmax", "layerNorm").
+ *    "rmsNorm", "batchMatMul", "embedding", plus the additions "causalSoftmax", "layerNorm", "linear").
  *  - znn_model_*: the example programs' models (examples/fashion_mnist.zig,
  *    examples/cnn.zig, examples/transformer_block.zig, examples/transformer_gpt.zig)
  *    with their training step: new graph -> forward -> SoftmaxCrossEntropy ->
@@ -58,7 +58,8 @@ int znn_model_set_params(znn_model* m, const float* host_slab);
 int znn_model_get_params(znn_model* m, float* host_slab);
 int znn_model_get_grads(znn_model* m, float* host_slab);
 int znn_model_get_velocities(znn_model* m, float* host_slab);
-/* keys: "lr", "momentum", "fused_softmax" (1/0), "dp_bucket_floats", "dp_overlap" (1/0) */
+/* keys: "lr", "momentum", "fused_softmax" (1/0), "fused_linear" (1/0, process-wide), "dp_bucket_floats",
+ * "dp_overlap" (1/0) */
 int znn_model_set_option(znn_model* m, const char* key, double value);
 /* One training step.  x: [batch, features] pixels (MLP/CNN) or [batch, seq] fp32 token ids (GPT); targets: batch
  * (or batch*seq) int32 labels.  on_device = 1: both pointers are device memory and are used in place.

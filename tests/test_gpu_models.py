@@ -115,6 +115,7 @@ def test_gpt_literal_attention_path(Model):
         m = Model("gpt", (29, 8, 16, 2, 1), arena_bytes=64 << 20)
         m.set_params(P0)
         m.set_option("fused_softmax", fused)
+        m.set_option("fused_linear", 0)
         m.set_option("lr", 0.0)
         losses.append((m.train_step(x, t, seq=8), m.get_grads(), m.last_step_ops()))
     assert losses[1][2] == losses[0][2] + 2          # mulScalar, add, softmax instead of the one fused op
@@ -122,6 +123,17 @@ def test_gpt_literal_attention_path(Model):
     floor = 1e-2 * grad_floor(losses[1][1])
     for k in losses[0][1]:
         relclose(losses[0][1][k], losses[1][1][k], 1e-5, k, floor)
+    # the fused Linear op (matmul + addBias in one GEMM epilogue) against the two separate ops
+    m = Model("gpt", (29, 8, 16, 2, 1), arena_bytes=64 << 20)
+    m.set_params(P0)
+    m.set_option("fused_linear", 1)
+    m.set_option("lr", 0.0)
+    lf = m.train_step(x, t, seq=8)
+    Gf = m.get_grads()
+    assert m.last_step_ops() < losses[0][2]
+    assert abs(lf - losses[0][0]) <= 1e-6 * abs(lf)
+    for k in Gf:
+        relclose(Gf[k], losses[0][1][k], 1e-5, k, floor)
 
 
 def test_transformer_block_config_shape_small(Model):

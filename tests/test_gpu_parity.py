@@ -302,3 +302,30 @@ def test_sgd_step(ops, zo, n):
         zo.sgd_step(w2, g, v2, 0.01, 0.9)
     np.testing.assert_array_equal(w1, w2)
     np.testing.assert_array_equal(v1, v2)
+
+
+@pytest.mark.parametrize("M,K,N", [(64, 784, 128), (5, 7, 3), (512, 768, 3072), (300, 100, 10)])
+def test_fused_linear(ops, zo, M, K, N):
+    """znn_linear_fwd / znn_linear_bwd (one GEMM with the bias in its epilogue) against the reference's
+    two ops, matmul then addBias (src/nn.zig:44-51), and their backward arms chained."""
+    import ctypes as C
+    from znn_b200._lib import lib
+    r = rng(M + K + N)
+    X, W, b = r.standard_normal((M, K), np.float32), r.standard_normal((K, N), np.float32), r.standard_normal(N, np.float32)
+    dY = r.standard_normal((M, N), np.float32)
+    L = lib()
+    dX_, dW_, db_ = (ops.DevBuf.from_host(np.zeros(s, np.float32)) for s in ((M, K), (K, N), (N,)))
+    x_, w_, b_, dy_ = (ops.DevBuf.from_host(a) for a in (X, W, b, dY))
+    y_ = ops.DevBuf(M * N * 4)
+    L.call("znn_linear_fwd", x_.ptr, w_.ptr, b_.ptr, y_.ptr, M, K, N)
+    L.call("znn_linear_bwd", x_.ptr, w_.ptr, dy_.ptr, dX_.ptr, dW_.ptr, db_.ptr, M, K, N)
+    ops.check_device_status()
+    want_y = zo.add_bias_fwd(zo.matmul_fwd(X, W), b)
+    dC, dbr = np.zeros((M, N), np.float32), np.zeros(N, np.float32)
+    zo.add_bias_bwd(dY, dC, dbr)
+    dXr, dWr = np.zeros_like(X), np.zeros_like(W)
+    zo.matmul_bwd(X, W, dC, dXr, dWr)
+    close(y_.to_host((M, N)), want_y, what="linear fwd")
+    close(dX_.to_host((M, K)), dXr, what="linear dX")
+    close(dW_.to_host((K, N)), dWr, what="linear dW")
+    close(db_.to_host((N,)), dbr, what="linear dbias")

@@ -8,14 +8,14 @@ namespace znn {
 
 int gemm_tc(int ta, int tb, int M, int N, int K, float alpha, const float* A, long long lda, long long stride_a,
             const float* B, long long ldb, long long stride_b, float beta, float* C, long long ldc,
-            long long stride_c, int batch, int ctas);
+            long long stride_c, int batch, int ctas, const float* bias);
 bool gemm_tc_direct_eligible(const float* A, long long lda, long long stride_a, const float* B, long long ldb,
                              long long stride_b, int batch);
 int gemm_tc_direct(int ta, int tb, int M, int N, int K, float alpha, const float* A, long long lda, long long stride_a,
                    const float* B, long long ldb, long long stride_b, float beta, float* C, long long ldc,
-                   long long stride_c, int batch);
+                   long long stride_c, int batch, const float* bias);
 int launch_splitk_reduce(const float* partial, int splits, int M, int N, int batch, float alpha, float beta, float* C,
-                         long long ldc, long long stride_c);
+                         long long ldc, long long stride_c, const float* bias);
 int tc_profile_enable(int enable);
 void tc_set_chunk_kblocks(int v);
 void tc_set_splitk(int on);
@@ -27,7 +27,8 @@ int tc_profile_read(double* kernel_ms, long long* launches, double* flops);
 __global__ void __launch_bounds__(256)
 sgemm_fma_kernel(int M, int N, int K, float alpha, const float* __restrict__ A, long long sa_i, long long sa_p,
                  long long stride_a, const float* __restrict__ B, long long sb_p, long long sb_j, long long stride_b,
-                 float beta, float* __restrict__ C, long long ldc, long long stride_c, int splits, int k_per_split)
+                 float beta, float* __restrict__ C, long long ldc, long long stride_c, int splits, int k_per_split,
+                 const float* __restrict__ bias)
 {
     __shared__ float As[16][64 + 4];
     __shared__ float Bs[16][64 + 4];
@@ -88,6 +89,7 @@ sgemm_fma_kernel(int M, int N, int K, float alpha, const float* __restrict__ A, 
             if (gj >= N) continue;
             float* dst = C + (size_t)gi * ldc + gj;
             float o = alpha * acc[r][c];
+            if (bias) o += bias[gj];
             if (beta != 0.0f) o += beta * (*dst);
             *dst = o;
         }
@@ -109,9 +111,10 @@ __global__ void scale_c_kernel(float* C, long long ldc, long long stride_c, int 
 static thread_local int t_path = 0;       // requested
 static thread_local int t_last_path = 0;  // taken by the last call
 
+// bias (optional, [N]) is added to every row of the result: the fused form of MatMul + AddBias
 static int gemm_dispatch(int ta, int tb, int M, int N, int K, float alpha, const float* A, long long lda,
                          long long stride_a, const float* B, long long ldb, long long stride_b, float beta, float* C,
-                         long long ldc, long long stride_c, int batch)
+                         long long ldc, long long stride_c, int batch, const float* bias = nullptr)
 {
     ZNN_REQUIRE(ta == ZNN_NO_TRANS || ta == ZNN_TRANS, "trans_a must be 111 or 112");
     ZNN_REQUIRE(tb == ZNN_NO_TRANS || tb == ZNN_TRANS, "trans_b must be 111 or 112");
@@ -121,6 +124,7 @@ static int gemm_dispatch(int ta, int tb, int M, int N, int K, float alpha, const
     ZNN_REQUIRE(ldc >= N, "ldc (%lld) < N (%d)", ldc, N);
     if (!stream()) return fail(ZNN_ERR_CUDA, "no CUDA device state; call znn_init (this library has no CPU fallback)");
     if (K == 0 || alpha == 0.0f) {
+        ZNN_REQUIRE(!bias, "bias with an empty contraction is not supported");
         if (beta != 1.0f) {
             const int blocks = ceil_div((long)M * N, 256) > 4096 ? 4096 : ceil_div((long)M * N, 256);
             scale_c_kernel<<<dim3(blocks, 1, batch), 256, 0, stream()>>>(C, ldc, stride_c, M, N, beta);
@@ -158,10 +162,10 @@ static int gemm_dispatch(int ta, int tb, int M, int N, int K, float alpha, const
     if (path == 4 && !direct_ok) path = 3;
     t_last_path = path;
     if (path == 4)
-        return gemm_tc_direct(ta, tb, M, N, K, alpha, A, lda, stride_a, B, ldb, stride_b, beta, C, ldc, stride_c, batch);
+        return gemm_tc_direct(ta, tb, M, N, K, alpha, A, lda, stride_a, B, ldb, stride_b, beta, C, ldc, stride_c, batch, bias);
     if (path == 2 || path == 3)
         return gemm_tc(ta, tb, M, N, K, alpha, A, lda, stride_a, B, ldb, stride_b, beta, C, ldc, stride_c, batch,
-                       path == 2 ? 1 : 2);
+                       path == 2 ? 1 : 2, bias);
 
     const long long sa_i = (ta == ZNN_NO_TRANS) ? lda : 1, sa_p = (ta == ZNN_NO_TRANS) ? 1 : lda;
     const long long sb_p = (tb == ZNN_NO_TRANS) ? ldb : 1, sb_j = (tb == ZNN_NO_TRANS) ? 1 : ldb;
@@ -184,13 +188,13 @@ static int gemm_dispatch(int ta, int tb, int M, int N, int K, float alpha, const
         if (!partial) return fail(ZNN_ERR_NOMEM, "split-K scratch could not be allocated");
         dim3 grid(ceil_div(N, 64), ceil_div(M, 64), batch * splits);
         sgemm_fma_kernel<<<grid, 256, 0, stream()>>>(M, N, K, 1.0f, A, sa_i, sa_p, stride_a, B, sb_p, sb_j, stride_b, 0.0f,
-                                                     partial, N, (long long)M * N, splits, kps);
+                                                     partial, N, (long long)M * N, splits, kps, nullptr);
         ZNN_LAUNCH_OK("sgemm_fma_kernel (split-K)");
-        return launch_splitk_reduce(partial, splits, M, N, batch, alpha, beta, C, ldc, stride_c);
+        return launch_splitk_reduce(partial, splits, M, N, batch, alpha, beta, C, ldc, stride_c, bias);
     }
     dim3 grid(ceil_div(N, 64), ceil_div(M, 64), batch);
     sgemm_fma_kernel<<<grid, 256, 0, stream()>>>(M, N, K, alpha, A, sa_i, sa_p, stride_a, B, sb_p, sb_j, stride_b,
-                                                 beta, C, ldc, stride_c, 1, K);
+                                                 beta, C, ldc, stride_c, 1, K, bias);
     ZNN_LAUNCH_OK("sgemm_fma_kernel");
     return ZNN_OK;
 }
@@ -215,6 +219,21 @@ int znn_sgemm_batched_strided(int trans_a, int trans_b, int M, int N, int K, flo
     ZNN_REQUIRE(batch <= 65535, "batch %d exceeds 65535", batch);
     return gemm_dispatch(trans_a, trans_b, M, N, K, alpha, A, lda, stride_a, B, ldb, stride_b, beta, C, ldc, stride_c,
                          batch);
+}
+
+int znn_linear_fwd(const float* X, const float* W, const float* bias, float* Y, int M, int K, int N)
+{
+    ZNN_REQUIRE(bias, "bias is NULL");
+    return gemm_dispatch(ZNN_NO_TRANS, ZNN_NO_TRANS, M, N, K, 1.0f, X, K, 0, W, N, 0, 0.0f, Y, N, 0, 1, bias);
+}
+
+int znn_linear_bwd(const float* X, const float* W, const float* dY, float* dX, float* dW, float* dbias, int M, int K, int N)
+{
+    int rc;
+    if (dbias && (rc = znn_add_bias_bwd(dY, nullptr, dbias, M, N))) return rc;
+    if (dX && (rc = gemm_dispatch(ZNN_NO_TRANS, ZNN_TRANS, M, K, N, 1.0f, dY, N, 0, W, N, 0, 1.0f, dX, K, 0, 1))) return rc;
+    if (dW && (rc = gemm_dispatch(ZNN_TRANS, ZNN_NO_TRANS, K, N, M, 1.0f, X, K, 0, dY, N, 0, 1.0f, dW, N, 0, 1))) return rc;
+    return ZNN_OK;
 }
 
 int znn_gemm_set_path(int path)

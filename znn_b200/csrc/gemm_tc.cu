@@ -219,6 +219,7 @@ struct GemmTcParams {
     int kblocks_per_split;  // split-K: k-blocks handled by one blockIdx.y slice (== k_blocks when not split)
     float* partial;      // split-K: [splits][batch][M][N] partial sums, nullptr when not split
     int conv_mode;       // direct kernel: 0 = store the masked hi tile, 1 = leave the raw tile as hi
+    const float* bias;   // optional [N] vector added to every output row (fused AddBias), may be nullptr
     int tiles_m, tiles_n;
     float alpha, beta;
     float* C;
@@ -246,6 +247,63 @@ struct TcCfg {
 __device__ __forceinline__ void mbar_arrive_remote(uint32_t cluster_addr)
 {
     asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
+}
+
+
+// Final store of one epilogue warp's 32 x CPT sub-tile.  Each thread holds one row in registers; a store straight
+// from there would write 16 bytes per row per instruction.  The sub-tile is turned through shared memory (the
+// operand ring is idle by now) so that every instruction moves one contiguous run of a row: 512 bytes for CPT = 128.
+template <int CPT>
+__device__ __forceinline__ void epilogue_store_warp(const float (&acc)[CPT], float* stage, int lane, int row_base, int cbase,
+                                                    int M, int N, float* out, long long out_ld, float alpha, float beta,
+                                                    const float* bias, bool vec_ok)
+{
+    constexpr int PITCH = CPT + 4;  // floats; keeps the 16-byte row writes of a quarter warp in distinct banks
+#pragma unroll
+    for (int c = 0; c < CPT; c += 4)
+        *reinterpret_cast<float4*>(stage + lane * PITCH + c) = make_float4(acc[c], acc[c + 1], acc[c + 2], acc[c + 3]);
+    __syncwarp();
+    const int rows = min(32, M - row_base);
+    constexpr int RB = 8;  // rows in flight: the loads of old C (beta != 0) are issued together
+    for (int r0 = 0; r0 < rows; r0 += RB) {
+        for (int c4 = lane; c4 < CPT / 4; c4 += 32) {
+            const int col = cbase + 4 * c4;
+            if (col >= N) continue;
+            const bool full = vec_ok && (col + 3 < N);
+            float4 old[RB];
+            if (beta != 0.0f && full) {
+#pragma unroll
+                for (int u = 0; u < RB; u++)
+                    if (r0 + u < rows) old[u] = *reinterpret_cast<const float4*>(out + (size_t)(row_base + r0 + u) * out_ld + col);
+            }
+            float4 b4 = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+            if (bias && full) b4 = *reinterpret_cast<const float4*>(bias + col);
+#pragma unroll
+            for (int u = 0; u < RB; u++) {
+                if (r0 + u >= rows) continue;
+                float* crow = out + (size_t)(row_base + r0 + u) * out_ld;
+                const float4 v = *reinterpret_cast<const float4*>(stage + (r0 + u) * PITCH + 4 * c4);
+                float o[4] = {alpha * v.x, alpha * v.y, alpha * v.z, alpha * v.w};
+                if (full) {
+                    o[0] += b4.x; o[1] += b4.y; o[2] += b4.z; o[3] += b4.w;
+                    if (beta != 0.0f) {
+                        o[0] += beta * old[u].x; o[1] += beta * old[u].y; o[2] += beta * old[u].z; o[3] += beta * old[u].w;
+                    }
+                    *reinterpret_cast<float4*>(crow + col) = make_float4(o[0], o[1], o[2], o[3]);
+                } else {
+#pragma unroll
+                    for (int e = 0; e < 4; e++) {
+                        if (col + e < N) {
+                            float t = o[e];
+                            if (bias) t += bias[col + e];
+                            if (beta != 0.0f) t += beta * crow[col + e];
+                            crow[col + e] = t;
+                        }
+                    }
+                }
+            }
+        }
+    }
 }
 
 // The tensor core adds into its fp32 accumulator with truncation, so the error of
@@ -442,47 +500,18 @@ gemm3x_tf32_kernel(const __grid_constant__ CUtensorMap tm_a_hi, const __grid_con
         if (!got) {
             if (lane == 0) atomicOr(p.status, ZNN_DEV_EPI_WAIT_EXPIRED);
         } else {
-            const int row = row0 + q * 32 + lane;
             const int cbase = col0 + half * CPT;
             // split-K slices store their raw partial sums; a reduce kernel applies alpha/beta afterwards
             const bool to_partial = (p.partial != nullptr);
-            float* const out = to_partial ? p.partial + ((size_t)blockIdx.y * gridDim.z + batch) * (size_t)p.M * p.N : p.C;
+            float* const out = to_partial ? p.partial + ((size_t)blockIdx.y * gridDim.z + batch) * (size_t)p.M * p.N
+                                          : p.C + (size_t)batch * p.stride_c;
             const long long out_ld = to_partial ? (long long)p.N : p.ldc;
-            const long long out_stride = to_partial ? 0 : p.stride_c;
+            const float* const bias = to_partial ? nullptr : p.bias;
             const bool vec_ok = ((out_ld & 3) == 0) && ((reinterpret_cast<uintptr_t>(out) & 15) == 0) &&
-                                ((out_stride & 3) == 0);
+                                ((reinterpret_cast<uintptr_t>(p.bias) & 15) == 0);
             const float alpha = to_partial ? 1.0f : p.alpha, beta = to_partial ? 0.0f : p.beta;
-            if (row < p.M) {
-                float* crow = out + (size_t)batch * out_stride + (size_t)row * out_ld + cbase;
-#pragma unroll
-                for (int c = 0; c < CPT; c += 32) {
-                    const int ncols = min(32, p.N - (cbase + c));
-                    if (ncols <= 0) continue;
-                    if (vec_ok && ncols == 32) {
-                        float4* dst = reinterpret_cast<float4*>(crow + c);
-#pragma unroll
-                        for (int j = 0; j < 8; j++) {
-                            float4 o;
-                            o.x = alpha * acc[c + 4 * j + 0]; o.y = alpha * acc[c + 4 * j + 1];
-                            o.z = alpha * acc[c + 4 * j + 2]; o.w = alpha * acc[c + 4 * j + 3];
-                            if (beta != 0.0f) {
-                                const float4 old = dst[j];
-                                o.x += beta * old.x; o.y += beta * old.y; o.z += beta * old.z; o.w += beta * old.w;
-                            }
-                            dst[j] = o;
-                        }
-                    } else {
-#pragma unroll
-                        for (int j = 0; j < 32; j++) {
-                            if (j < ncols) {
-                                float o = alpha * acc[c + j];
-                                if (beta != 0.0f) o += beta * crow[c + j];
-                                crow[c + j] = o;
-                            }
-                        }
-                    }
-                }
-            }
+            float* stage = reinterpret_cast<float*>(smem_gen) + (size_t)(warp - 2) * 32 * (CPT + 4);
+            epilogue_store_warp<CPT>(acc, stage, lane, row0 + q * 32, cbase, p.M, p.N, out, out_ld, alpha, beta, bias, vec_ok);
         }
     }
 
@@ -876,46 +905,18 @@ gemm3x_direct_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_cons
         if (!got) {
             if (lane == 0) atomicOr(p.status, ZNN_DEV_EPI_WAIT_EXPIRED);
         } else {
-            const int row = row0 + q * 32 + lane;
             const int cbase = col0 + half * CPT;
+            // split-K slices store their raw partial sums; a reduce kernel applies alpha/beta afterwards
             const bool to_partial = (p.partial != nullptr);
-            float* const out = to_partial ? p.partial + ((size_t)blockIdx.y * gridDim.z + batch) * (size_t)p.M * p.N : p.C;
+            float* const out = to_partial ? p.partial + ((size_t)blockIdx.y * gridDim.z + batch) * (size_t)p.M * p.N
+                                          : p.C + (size_t)batch * p.stride_c;
             const long long out_ld = to_partial ? (long long)p.N : p.ldc;
-            const long long out_stride = to_partial ? 0 : p.stride_c;
+            const float* const bias = to_partial ? nullptr : p.bias;
             const bool vec_ok = ((out_ld & 3) == 0) && ((reinterpret_cast<uintptr_t>(out) & 15) == 0) &&
-                                ((out_stride & 3) == 0);
+                                ((reinterpret_cast<uintptr_t>(p.bias) & 15) == 0);
             const float alpha = to_partial ? 1.0f : p.alpha, beta = to_partial ? 0.0f : p.beta;
-            if (row < p.M) {
-                float* crow = out + (size_t)batch * out_stride + (size_t)row * out_ld + cbase;
-#pragma unroll
-                for (int c = 0; c < CPT; c += 32) {
-                    const int ncols = min(32, p.N - (cbase + c));
-                    if (ncols <= 0) continue;
-                    if (vec_ok && ncols == 32) {
-                        float4* dst = reinterpret_cast<float4*>(crow + c);
-#pragma unroll
-                        for (int j = 0; j < 8; j++) {
-                            float4 o;
-                            o.x = alpha * acc[c + 4 * j + 0]; o.y = alpha * acc[c + 4 * j + 1];
-                            o.z = alpha * acc[c + 4 * j + 2]; o.w = alpha * acc[c + 4 * j + 3];
-                            if (beta != 0.0f) {
-                                const float4 old = dst[j];
-                                o.x += beta * old.x; o.y += beta * old.y; o.z += beta * old.z; o.w += beta * old.w;
-                            }
-                            dst[j] = o;
-                        }
-                    } else {
-#pragma unroll
-                        for (int j = 0; j < 32; j++) {
-                            if (j < ncols) {
-                                float o = alpha * acc[c + j];
-                                if (beta != 0.0f) o += beta * crow[c + j];
-                                crow[c + j] = o;
-                            }
-                        }
-                    }
-                }
-            }
+            float* stage = reinterpret_cast<float*>(smem_gen) + (size_t)(warp - kEpiWarp0) * 32 * (CPT + 4);
+            epilogue_store_warp<CPT>(acc, stage, lane, row0 + q * 32, cbase, p.M, p.N, out, out_ld, alpha, beta, bias, vec_ok);
         }
         }
     }
@@ -931,7 +932,8 @@ gemm3x_direct_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_cons
 
 // C = alpha * sum_s partial[s] + beta * C, slices added in order (deterministic)
 __global__ void splitk_reduce_kernel(const float* __restrict__ partial, int splits, int M, int N, int batch, float alpha,
-                                     float beta, float* __restrict__ C, long long ldc, long long stride_c)
+                                     float beta, float* __restrict__ C, long long ldc, long long stride_c,
+                                     const float* __restrict__ bias)
 {
     const size_t per = (size_t)M * N;
     const size_t total = per * batch;
@@ -941,6 +943,7 @@ __global__ void splitk_reduce_kernel(const float* __restrict__ partial, int spli
         const size_t b = i / per, r = (i % per) / N, c = i % N;
         float* dst = C + b * stride_c + r * ldc + c;
         float o = alpha * s;
+        if (bias) o += bias[c];
         if (beta != 0.0f) o += beta * (*dst);
         *dst = o;
     }
@@ -950,14 +953,14 @@ __global__ void splitk_reduce_kernel(const float* __restrict__ partial, int spli
 // host side
 // ---------------------------------------------------------------------------
 int launch_splitk_reduce(const float* partial, int splits, int M, int N, int batch, float alpha, float beta, float* C,
-                         long long ldc, long long stride_c)
+                         long long ldc, long long stride_c, const float* bias)
 {
     const size_t total = (size_t)batch * M * N;
     int blocks = (int)((total + 255) / 256);
     const int cap = sm_count() * 16;
     if (blocks > cap) blocks = cap;
     if (blocks < 1) blocks = 1;
-    splitk_reduce_kernel<<<blocks, 256, 0, stream()>>>(partial, splits, M, N, batch, alpha, beta, C, ldc, stride_c);
+    splitk_reduce_kernel<<<blocks, 256, 0, stream()>>>(partial, splits, M, N, batch, alpha, beta, C, ldc, stride_c, bias);
     ZNN_LAUNCH_OK("splitk_reduce_kernel");
     return ZNN_OK;
 }
@@ -1127,7 +1130,7 @@ static TcPlan make_plan(int M, int N, int K, int batch, int ctas)
 // op(A) is M x K, op(B) is K x N.  ctas = 1 or 2.
 int gemm_tc(int ta, int tb, int M, int N, int K, float alpha, const float* A, long long lda, long long stride_a,
             const float* B, long long ldb, long long stride_b, float beta, float* C, long long ldc,
-            long long stride_c, int batch, int ctas)
+            long long stride_c, int batch, int ctas, const float* bias)
 {
     int* status = device_status_word();
     if (!status) return fail(ZNN_ERR_CUDA, "no device state (call znn_init first)");
@@ -1175,6 +1178,7 @@ int gemm_tc(int ta, int tb, int M, int N, int K, float alpha, const float* A, lo
     p.kblocks_per_split = kbps;
     p.partial = splits > 1 ? (b_lo + b_plane) : nullptr;
     p.conv_mode = 0;
+    p.bias = bias;
     p.tiles_m = tiles_m;
     p.tiles_n = tiles_n;
     p.alpha = alpha; p.beta = beta; p.C = C; p.ldc = ldc; p.stride_c = stride_c; p.status = status;
@@ -1195,14 +1199,7 @@ int gemm_tc(int ta, int tb, int M, int N, int K, float alpha, const float* A, lo
         else rc = launch_tc<64, 2>(maps, p, batch);
     }
     if (rc) return rc;
-    if (splits > 1) {
-        const size_t total = (size_t)batch * M * N;
-        int blocks = (int)((total + 255) / 256);
-        const int cap = sm_count() * 16;
-        if (blocks > cap) blocks = cap;
-        splitk_reduce_kernel<<<blocks, 256, 0, st>>>(p.partial, splits, M, N, batch, alpha, beta, C, ldc, stride_c);
-        ZNN_LAUNCH_OK("splitk_reduce_kernel");
-    }
+    if (splits > 1) return launch_splitk_reduce(p.partial, splits, M, N, batch, alpha, beta, C, ldc, stride_c, bias);
     return ZNN_OK;
 }
 
@@ -1279,7 +1276,7 @@ bool gemm_tc_direct_eligible(const float* A, long long lda, long long stride_a, 
 
 int gemm_tc_direct(int ta, int tb, int M, int N, int K, float alpha, const float* A, long long lda, long long stride_a,
                    const float* B, long long ldb, long long stride_b, float beta, float* C, long long ldc,
-                   long long stride_c, int batch)
+                   long long stride_c, int batch, const float* bias)
 {
     int* status = device_status_word();
     if (!status) return fail(ZNN_ERR_CUDA, "no device state (call znn_init first)");
@@ -1299,6 +1296,7 @@ int gemm_tc_direct(int ta, int tb, int M, int N, int K, float alpha, const float
     p.kblocks_per_split = pl.kbps;
     p.partial = partial;
     p.conv_mode = t_conv_mode;
+    p.bias = bias;
     p.tiles_m = pl.tiles_m;
     p.tiles_n = pl.tiles_n;
     p.alpha = alpha; p.beta = beta; p.C = C; p.ldc = ldc; p.stride_c = stride_c; p.status = status;
@@ -1306,14 +1304,7 @@ int gemm_tc_direct(int ta, int tb, int M, int N, int K, float alpha, const float
     else if (pl.bn == 128) rc = launch_direct_major<128>(a_mn, b_mn, ma, mb, p, batch);
     else rc = launch_direct_major<64>(a_mn, b_mn, ma, mb, p, batch);
     if (rc) return rc;
-    if (pl.splits > 1) {
-        const size_t total = (size_t)batch * M * N;
-        int blocks = (int)((total + 255) / 256);
-        const int cap = sm_count() * 16;
-        if (blocks > cap) blocks = cap;
-        splitk_reduce_kernel<<<blocks, 256, 0, stream()>>>(partial, pl.splits, M, N, batch, alpha, beta, C, ldc, stride_c);
-        ZNN_LAUNCH_OK("splitk_reduce_kernel");
-    }
+    if (pl.splits > 1) return launch_splitk_reduce(partial, pl.splits, M, N, batch, alpha, beta, C, ldc, stride_c, bias);
     return ZNN_OK;
 }
 

@@ -121,6 +121,7 @@ int znn_graph_op(znn_graph* zg, const char* name, const int* inputs, int n_input
     else if (op == "rmsNorm") out = g.rmsNorm(in(0), in(1), (float)arg(0));
     else if (op == "layerNorm") out = g.layerNorm(in(0), in(1), in(2), (float)arg(0));
     else if (op == "batchMatMul") out = g.batchMatMul(in(0), in(1));
+    else if (op == "linear") out = g.linear(in(0), in(1), in(2));
     else if (op == "embedding") out = g.embedding(in(0), in(1));
     else throw Error(ZNN_ERR_INVALID, "unknown op '" + op + "'");
     zg->handles.push_back(out);
@@ -442,7 +443,8 @@ int znn_model_set_option(znn_model* m, const char* key, double value)
     else if (k == "fused_softmax") {
         m->gpt.set_fused_softmax(value != 0.0);
         m->block.attn.fused_softmax = (value != 0.0);
-    } else if (k == "dp_bucket_floats") m->dp_bucket_floats = (size_t)value;
+    } else if (k == "fused_linear") set_fused_linear(value != 0.0);
+    else if (k == "dp_bucket_floats") m->dp_bucket_floats = (size_t)value;
     else if (k == "dp_overlap") m->dp_overlap = (value != 0.0);
     else throw Error(ZNN_ERR_INVALID, "unknown option '" + k + "'");
     ZNN_HOST_CATCH

@@ -294,6 +294,15 @@ Tensor* Graph::layerNorm(Tensor* X, Tensor* G, Tensor* B, float eps)
     return Y;
 }
 
+Tensor* Graph::linear(Tensor* X, Tensor* W, Tensor* bias)
+{
+    if (X->shape.len < 2 || W->shape.len < 2 || X->shape.dims[1] != W->shape.dims[0] || bias->numel() != W->shape.dims[1])
+        throw Error(ZNN_ERR_INVALID, "linear: need X [M,K], W [K,N], bias [N]");
+    Tensor* Y = new_tensor(Shape{X->shape.dims[0], W->shape.dims[1]}, any_grad({X, W, bias}), false);
+    new_op(OpType::LinearBias, {X, W, bias}, Y)->forward();
+    return Y;
+}
+
 Tensor* Graph::batchMatMul(Tensor* A, Tensor* B)
 {
     if (A->shape.len != 4 || B->shape.len != 4 || A->shape.dims[3] != B->shape.dims[2] ||
@@ -380,6 +389,13 @@ void Op::forward()
     case OpType::LayerNorm: {
         const int D = (int)A->shape.dims[A->shape.len - 1];
         check(znn_layernorm_fwd(A->data, inputs[1]->data, inputs[2]->data, scalar, C->data, A->numel() / D, D), "LayerNorm forward");
+        break;
+    }
+    case OpType::LinearBias: {
+        Tensor* W = inputs[1];
+        check(znn_linear_fwd(A->data, W->data, inputs[2]->data, C->data, (int)A->shape.dims[0], (int)A->shape.dims[1],
+                             (int)W->shape.dims[1]),
+              "Linear forward");
         break;
     }
     case OpType::BatchMatMul: {
@@ -495,6 +511,15 @@ void Op::backward()
         check(znn_layernorm_bwd(A->data, G->data, C->grad, scalar, A->requires_grad ? A->grad : nullptr,
                                 G->requires_grad ? G->grad : nullptr, B->requires_grad ? B->grad : nullptr, A->numel() / D, D),
               "LayerNorm backward");
+        break;
+    }
+    case OpType::LinearBias: {
+        Tensor* W = inputs[1];
+        Tensor* b = inputs[2];
+        check(znn_linear_bwd(A->data, W->data, C->grad, A->requires_grad ? A->grad : nullptr,
+                             W->requires_grad ? W->grad : nullptr, b->requires_grad ? b->grad : nullptr,
+                             (int)A->shape.dims[0], (int)A->shape.dims[1], (int)W->shape.dims[1]),
+              "Linear backward");
         break;
     }
     case OpType::BatchMatMul: {

@@ -57,7 +57,8 @@ enum class OpType {
     MatMul, AddBias, Relu, Gelu, SoftmaxCrossEntropy, Reshape, Transpose, MulScalar, Add, Conv2D, MaxPool2D,
     Softmax, RmsNorm, BatchMatMul, Embedding,
     CausalSoftmax,  // fused mulScalar + mask add + softmax of src/nn.zig:835-886 (an addition)
-    LayerNorm       // extension, no reference counterpart
+    LayerNorm,      // extension, no reference counterpart
+    LinearBias      // fused matmul + addBias of Linear.forward (src/nn.zig:44-51), an addition
 };
 
 // src/autodiff.zig:100-105 (OpContext flattened)
@@ -124,6 +125,7 @@ public:
     Tensor* embedding(Tensor* W, Tensor* X);                                // :2160
     Tensor* causalSoftmax(Tensor* S, float scale);                          // fused addition
     Tensor* layerNorm(Tensor* X, Tensor* G, Tensor* B, float eps);          // extension
+    Tensor* linear(Tensor* X, Tensor* W, Tensor* bias);                     // fused addBias(matmul(X, W), bias)
 
     // `after_op(op)` is called after a tape op has run its
     // backward arm; data-parallel training uses it to start gradient all-reduces.

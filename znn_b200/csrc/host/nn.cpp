@@ -62,7 +62,15 @@ Linear::Linear(ParamStore& ps, const std::string& name, size_t in_features, size
     bias = ps.add(name + ".bias", Shape{1, out_features}, 0);
 }
 
-Tensor* Linear::forward(Graph& g, Tensor* x) const { return g.addBias(g.matmul(x, weight), bias); }
+static bool g_fused_linear = true;
+void set_fused_linear(bool on) { g_fused_linear = on; }
+bool fused_linear() { return g_fused_linear; }
+
+Tensor* Linear::forward(Graph& g, Tensor* x) const
+{
+    if (g_fused_linear) return g.linear(x, weight, bias);
+    return g.addBias(g.matmul(x, weight), bias);
+}
 
 Conv2D::Conv2D(ParamStore& ps, const std::string& name, size_t in_ch, size_t out_ch, size_t k, int pad_) : pad(pad_)
 {

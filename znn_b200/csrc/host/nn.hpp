@@ -44,6 +44,10 @@ private:
     float *w_ = nullptr, *g_ = nullptr, *v_ = nullptr;
 };
 
+// Linear.forward runs the fused matmul+addBias op by default; false = the reference's two ops.
+void set_fused_linear(bool on);
+bool fused_linear();
+
 // src/nn.zig:10-52.  W is [in, out], b is [1, out]; forward = addBias(matmul(x, W), b)
 struct Linear {
     Tensor* weight = nullptr;

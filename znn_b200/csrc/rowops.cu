@@ -279,6 +279,56 @@ __global__ void softmax_xent_fwd_kernel(const float* __restrict__ logits, const 
     }
 }
 
+// Rows of at most 1024*V4 logits with N % 4 == 0: one 128-bit read of the row into registers, one write of
+// the probabilities.
+template <class TargetT, int V4>
+__global__ void __launch_bounds__(256)
+softmax_xent_fwd_reg_kernel(const float* __restrict__ logits, const TargetT* __restrict__ targets,
+                            float* __restrict__ probs, float* __restrict__ rowloss, int N)
+{
+    __shared__ float sh[32];
+    const size_t row = blockIdx.x;
+    const float4* x = reinterpret_cast<const float4*>(logits + row * N);
+    float4* p = reinterpret_cast<float4*>(probs + row * N);
+    const int n4 = N >> 2;
+    float4 v[V4];
+    float mx = -CUDART_INF_F;
+#pragma unroll
+    for (int k = 0; k < V4; k++) {
+        const int j4 = threadIdx.x + 256 * k;
+        if (j4 < n4) {
+            v[k] = x[j4];
+            mx = fmaxf(mx, fmaxf(fmaxf(v[k].x, v[k].y), fmaxf(v[k].z, v[k].w)));
+        }
+    }
+    mx = block_max(mx, sh);
+    float sum = 0.0f;
+#pragma unroll
+    for (int k = 0; k < V4; k++) {
+        const int j4 = threadIdx.x + 256 * k;
+        if (j4 < n4) {
+            v[k].x = expf(v[k].x - mx); v[k].y = expf(v[k].y - mx);
+            v[k].z = expf(v[k].z - mx); v[k].w = expf(v[k].w - mx);
+            sum += (v[k].x + v[k].y) + (v[k].z + v[k].w);
+        }
+    }
+    sum = block_sum(sum, sh);
+    const int t = (int)targets[row];
+#pragma unroll
+    for (int k = 0; k < V4; k++) {
+        const int j4 = threadIdx.x + 256 * k;
+        if (j4 < n4) {
+            float4 o;
+            o.x = v[k].x / sum; o.y = v[k].y / sum; o.z = v[k].z / sum; o.w = v[k].w / sum;
+            p[j4] = o;
+            if ((t >> 2) == j4) {
+                const float pt = (t & 3) == 0 ? o.x : (t & 3) == 1 ? o.y : (t & 3) == 2 ? o.z : o.w;
+                rowloss[row] = -logf(fmaxf(pt, 1e-15f));
+            }
+        }
+    }
+}
+
 // mean of M per-row losses, summed in a fixed order
 __global__ void mean_rows_kernel(const float* __restrict__ rowloss, float* __restrict__ loss, int M)
 {
@@ -295,7 +345,24 @@ __global__ void softmax_xent_bwd_kernel(const float* __restrict__ probs, const T
 {
     const float scale = 1.0f / (float)M;
     const size_t total = (size_t)M * N;
-    for (size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x) {
+    const size_t tid = blockIdx.x * (size_t)blockDim.x + threadIdx.x, nth = (size_t)gridDim.x * blockDim.x;
+    if ((N & 3) == 0 && ((((uintptr_t)probs | (uintptr_t)dlogits) & 15) == 0)) {
+        const size_t n4 = (size_t)(N >> 2);
+        for (size_t i = tid; i < total / 4; i += nth) {
+            const size_t r = i / n4;
+            const int j = (int)(i - r * n4) * 4;
+            const int t = (int)targets[r];
+            const float4 p = reinterpret_cast<const float4*>(probs)[i];
+            float4 d = reinterpret_cast<float4*>(dlogits)[i];
+            d.x += scale * (p.x - (j == t ? 1.0f : 0.0f));
+            d.y += scale * (p.y - (j + 1 == t ? 1.0f : 0.0f));
+            d.z += scale * (p.z - (j + 2 == t ? 1.0f : 0.0f));
+            d.w += scale * (p.w - (j + 3 == t ? 1.0f : 0.0f));
+            reinterpret_cast<float4*>(dlogits)[i] = d;
+        }
+        return;
+    }
+    for (size_t i = tid; i < total; i += nth) {
         const size_t r = i / N;
         const int j = (int)(i - r * N);
         const float ind = (j == (int)targets[r]) ? 1.0f : 0.0f;
@@ -324,6 +391,61 @@ __global__ void softmax_rows_fwd_kernel(const float* __restrict__ S, float scale
     for (int j = lane; j < lim; j += 32) sum += expf((Causal ? x[j] * scale : x[j]) - mx);
     sum = warp_sum(sum);
     for (int j = lane; j < D; j += 32) p[j] = (j < lim) ? expf((Causal ? x[j] * scale : x[j]) - mx) / sum : 0.0f;
+}
+
+// Same, for rows of at most 128*V4 elements with D % 4 == 0: the row is read once with 128-bit loads,
+// kept in registers, and written once.
+template <bool Causal, int V4>
+__global__ void softmax_rows_reg_kernel(const float* __restrict__ S, float scale, float* __restrict__ P, size_t rows, int D)
+{
+    const size_t row = blockIdx.x * (size_t)(blockDim.x >> 5) + (threadIdx.x >> 5);
+    if (row >= rows) return;
+    const int lane = threadIdx.x & 31;
+    const float4* x = reinterpret_cast<const float4*>(S + row * D);
+    float4* p = reinterpret_cast<float4*>(P + row * D);
+    const int lim = Causal ? (int)(row % D) + 1 : D;
+    float4 v[V4];
+    float mx = -CUDART_INF_F;
+#pragma unroll
+    for (int k = 0; k < V4; k++) {
+        const int j = 4 * (lane + 32 * k);
+        if (j < lim) {
+            float4 t = x[lane + 32 * k];
+            if (Causal) { t.x *= scale; t.y *= scale; t.z *= scale; t.w *= scale; }
+            if (j + 1 >= lim) t.y = -CUDART_INF_F;
+            if (j + 2 >= lim) t.z = -CUDART_INF_F;
+            if (j + 3 >= lim) t.w = -CUDART_INF_F;
+            v[k] = t;
+            mx = fmaxf(mx, fmaxf(fmaxf(t.x, t.y), fmaxf(t.z, t.w)));
+        } else {
+            v[k] = make_float4(-CUDART_INF_F, -CUDART_INF_F, -CUDART_INF_F, -CUDART_INF_F);
+        }
+    }
+    mx = warp_max(mx);
+    float sum = 0.0f;
+#pragma unroll
+    for (int k = 0; k < V4; k++) {
+        const int j = 4 * (lane + 32 * k);
+        if (j < lim) {
+            float4 e;
+            e.x = expf(v[k].x - mx);
+            e.y = (j + 1 < lim) ? expf(v[k].y - mx) : 0.0f;
+            e.z = (j + 2 < lim) ? expf(v[k].z - mx) : 0.0f;
+            e.w = (j + 3 < lim) ? expf(v[k].w - mx) : 0.0f;
+            v[k] = e;
+            sum += (e.x + e.y) + (e.z + e.w);
+        }
+    }
+    sum = warp_sum(sum);
+#pragma unroll
+    for (int k = 0; k < V4; k++) {
+        const int j = 4 * (lane + 32 * k);
+        if (j < D) {
+            float4 o = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+            if (j < lim) { o.x = v[k].x / sum; o.y = v[k].y / sum; o.z = v[k].z / sum; o.w = v[k].w / sum; }
+            p[lane + 32 * k] = o;
+        }
+    }
 }
 
 // dA += scale * Y * (dY - sum(dY*Y))   (scale = 1 for the plain Softmax op)
@@ -545,6 +667,31 @@ __global__ void transpose_generic_kernel(const float* __restrict__ in, float* __
     }
 }
 
+// Swapped dims both before the last one: the tensor is [o][a][m][b][inner] -> [o][b][m][a][inner] with runs of
+// `inner` contiguous floats moved as float4 (head split / merge of attention: inner = head size).
+template <bool Backward>
+__global__ void transpose_runs_kernel(const float4* __restrict__ in, float4* __restrict__ out, unsigned O, unsigned Ad,
+                                      unsigned Mm, unsigned Bd, unsigned I4, unsigned total4)
+{
+    for (unsigned f = blockIdx.x * blockDim.x + threadIdx.x; f < total4; f += gridDim.x * blockDim.x) {
+        unsigned t = f;
+        const unsigned i4 = t % I4; t /= I4;
+        const unsigned a = t % Ad; t /= Ad;
+        const unsigned mm = t % Mm; t /= Mm;
+        const unsigned b = t % Bd;
+        const unsigned o = t / Bd;
+        const unsigned src = (((o * Ad + a) * Mm + mm) * Bd + b) * I4 + i4;
+        if (Backward) {
+            float4 d = out[src];
+            const float4 g = in[f];
+            d.x += g.x; d.y += g.y; d.z += g.z; d.w += g.w;
+            out[src] = d;
+        } else {
+            out[f] = in[src];
+        }
+    }
+}
+
 // last two dims swapped: per-slice R x Cc -> Cc x R through a shared-memory tile
 template <bool Backward>
 __global__ void transpose_last2_kernel(const float* __restrict__ in, float* __restrict__ out, int R, int Cc)
@@ -613,17 +760,31 @@ __global__ void sgd_kernel(float* __restrict__ w, const float* __restrict__ g, f
 {
     const size_t tid = blockIdx.x * (size_t)blockDim.x + threadIdx.x, nth = (size_t)gridDim.x * blockDim.x;
     const bool scaled = (grad_scale != 1.0f);
-    for (size_t i = tid; i < n; i += nth) {
-        float gi = g[i];
+    const bool vec = ((((uintptr_t)w | (uintptr_t)g | (uintptr_t)v) & 15) == 0);
+    const size_t n4 = vec ? n / 4 : 0;
+    auto upd = [&](float& wi, float gi, float* vi) {
         if (scaled) gi *= grad_scale;
-        if (v) {
-            const float vel = momentum * v[i] + lr * gi;
-            v[i] = vel;
-            w[i] -= vel;
+        if (vi) {
+            const float vel = momentum * (*vi) + lr * gi;
+            *vi = vel;
+            wi -= vel;
         } else {
-            w[i] -= lr * gi;
+            wi -= lr * gi;
         }
+    };
+    for (size_t i = tid; i < n4; i += nth) {
+        float4 wv = reinterpret_cast<float4*>(w)[i];
+        const float4 gv = reinterpret_cast<const float4*>(g)[i];
+        if (v) {
+            float4 vv = reinterpret_cast<float4*>(v)[i];
+            upd(wv.x, gv.x, &vv.x); upd(wv.y, gv.y, &vv.y); upd(wv.z, gv.z, &vv.z); upd(wv.w, gv.w, &vv.w);
+            reinterpret_cast<float4*>(v)[i] = vv;
+        } else {
+            upd(wv.x, gv.x, nullptr); upd(wv.y, gv.y, nullptr); upd(wv.z, gv.z, nullptr); upd(wv.w, gv.w, nullptr);
+        }
+        reinterpret_cast<float4*>(w)[i] = wv;
     }
+    for (size_t i = n4 * 4 + tid; i < n; i += nth) upd(w[i], g[i], v ? v + i : nullptr);
 }
 
 }  // namespace znn
@@ -726,8 +887,14 @@ static int xent_fwd(const float* logits, const T* targets, float* probs, float* 
     ZNN_REQUIRE(logits && targets && probs && loss, "NULL pointer");
     float* rowloss = (float*)workspace((size_t)M * sizeof(float));
     if (!rowloss) return fail(ZNN_ERR_NOMEM, "scratch for per-row losses");
-    const int threads = N >= 1024 ? 256 : (N >= 128 ? 128 : 32);
-    softmax_xent_fwd_kernel<T><<<M, threads, 0, stream()>>>(logits, targets, probs, rowloss, N);
+    const bool v4 = (N % 4 == 0) && ((((uintptr_t)logits | (uintptr_t)probs) & 15) == 0);
+    if (v4 && N > 2048 && N <= 1024 * 8) {
+        if (N <= 1024 * 4) softmax_xent_fwd_reg_kernel<T, 4><<<M, 256, 0, stream()>>>(logits, targets, probs, rowloss, N);
+        else softmax_xent_fwd_reg_kernel<T, 8><<<M, 256, 0, stream()>>>(logits, targets, probs, rowloss, N);
+    } else {
+        const int threads = N >= 1024 ? 256 : (N >= 128 ? 128 : 32);
+        softmax_xent_fwd_kernel<T><<<M, threads, 0, stream()>>>(logits, targets, probs, rowloss, N);
+    }
     ZNN_LAUNCH_OK("softmax_xent_fwd_kernel");
     mean_rows_kernel<<<1, 1024, 0, stream()>>>(rowloss, loss, M);
     ZNN_LAUNCH_OK("mean_rows_kernel");
@@ -773,7 +940,10 @@ int znn_softmax_fwd(const float* A, float* C, size_t rows, int D)
 {
     if (rows == 0 || D <= 0) return ZNN_OK;
     ZNN_NEED_DEVICE();
-    softmax_rows_fwd_kernel<false><<<row_blocks(rows, 8), 256, 0, stream()>>>(A, 1.0f, C, rows, D);
+    const bool v4 = (D % 4 == 0) && ((((uintptr_t)A | (uintptr_t)C) & 15) == 0);
+    if (v4 && D <= 256) softmax_rows_reg_kernel<false, 2><<<row_blocks(rows, 8), 256, 0, stream()>>>(A, 1.0f, C, rows, D);
+    else if (v4 && D <= 1024) softmax_rows_reg_kernel<false, 8><<<row_blocks(rows, 8), 256, 0, stream()>>>(A, 1.0f, C, rows, D);
+    else softmax_rows_fwd_kernel<false><<<row_blocks(rows, 8), 256, 0, stream()>>>(A, 1.0f, C, rows, D);
     ZNN_LAUNCH_OK("softmax_rows_fwd_kernel");
     return ZNN_OK;
 }
@@ -792,7 +962,10 @@ int znn_causal_softmax_fwd(const float* S, float scale, float* P, int nslices, i
     if (nslices <= 0 || T <= 0) return ZNN_OK;
     ZNN_NEED_DEVICE();
     const size_t rows = (size_t)nslices * T;
-    softmax_rows_fwd_kernel<true><<<row_blocks(rows, 8), 256, 0, stream()>>>(S, scale, P, rows, T);
+    const bool v4 = (T % 4 == 0) && ((((uintptr_t)S | (uintptr_t)P) & 15) == 0);
+    if (v4 && T <= 256) softmax_rows_reg_kernel<true, 2><<<row_blocks(rows, 8), 256, 0, stream()>>>(S, scale, P, rows, T);
+    else if (v4 && T <= 1024) softmax_rows_reg_kernel<true, 8><<<row_blocks(rows, 8), 256, 0, stream()>>>(S, scale, P, rows, T);
+    else softmax_rows_fwd_kernel<true><<<row_blocks(rows, 8), 256, 0, stream()>>>(S, scale, P, rows, T);
     ZNN_LAUNCH_OK("causal softmax fwd");
     return ZNN_OK;
 }
@@ -928,6 +1101,26 @@ static int transpose_impl(const float* in, float* out, const int64_t* dims, int 
             if (backward) transpose_last2_kernel<true><<<grid, block, 0, stream()>>>(in, out, R, Cc);
             else transpose_last2_kernel<false><<<grid, block, 0, stream()>>>(in, out, R, Cc);
             ZNN_LAUNCH_OK("transpose_last2_kernel");
+            return ZNN_OK;
+        }
+    }
+    if (d0 != d1 && d1 < rank - 1) {
+        size_t inner = 1, mid = 1, outer = 1;
+        for (int k = d1 + 1; k < rank; k++) inner *= (size_t)dims[k];
+        for (int k = d0 + 1; k < d1; k++) mid *= (size_t)dims[k];
+        for (int k = 0; k < d0; k++) outer *= (size_t)dims[k];
+        if ((inner & 3) == 0 && total / 4 < 0x7fffffffu && (((uintptr_t)in | (uintptr_t)out) & 15) == 0) {
+            const unsigned total4 = (unsigned)(total / 4);
+            const unsigned blocks = (unsigned)ew_blocks(total4, 2);
+            if (backward)
+                transpose_runs_kernel<true><<<blocks, kEwThreads, 0, stream()>>>(
+                    (const float4*)in, (float4*)out, (unsigned)outer, (unsigned)dims[d0], (unsigned)mid, (unsigned)dims[d1],
+                    (unsigned)(inner / 4), total4);
+            else
+                transpose_runs_kernel<false><<<blocks, kEwThreads, 0, stream()>>>(
+                    (const float4*)in, (float4*)out, (unsigned)outer, (unsigned)dims[d0], (unsigned)mid, (unsigned)dims[d1],
+                    (unsigned)(inner / 4), total4);
+            ZNN_LAUNCH_OK("transpose_runs_kernel");
             return ZNN_OK;
         }
     }

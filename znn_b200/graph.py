@@ -89,6 +89,7 @@ class Graph:
     def layerNorm(self, X, G, B, eps): return self._op("layerNorm", [X, G, B], [eps])
     def batchMatMul(self, A, B): return self._op("batchMatMul", [A, B])
     def embedding(self, W, X): return self._op("embedding", [W, X])
+    def linear(self, X, W, b): return self._op("linear", [X, W, b])
 
     def backward(self, t): lib().call("znn_graph_backward", self.h, t.id, 1)
     def backwardWithGrad(self, t): lib().call("znn_graph_backward", self.h, t.id, 0)
