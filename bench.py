@@ -505,7 +505,10 @@ def configs_part(args, L, torch, stream):
         dx, dt = torch.from_numpy(x).cuda(), torch.from_numpy(t).cuda()
         ms = time_steps(lambda: m.train_step_device(dx.data_ptr(), dt.data_ptr(), batch), 200)
         ms_e2e = time_steps(lambda: m.train_step(x, t), 50)
+        m.set_option("cuda_graph", 1)       # capture the step once, then replay it
+        ms_graph = time_steps(lambda: m.train_step_device(dx.data_ptr(), dt.data_ptr(), batch), 200)
         out[key] = {"us_per_step": ms * 1e3, "steps_per_s": 1e3 / ms, "images_per_s": batch * 1e3 / ms,
+                    "cuda_graph_us_per_step": ms_graph * 1e3, "cuda_graph_images_per_s": batch * 1e3 / ms_graph,
                     "e2e_us_per_step": ms_e2e * 1e3, "tape_ops": m.last_step_ops(), "bound": "launch latency"}
         m.close()
 

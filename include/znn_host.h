@@ -59,7 +59,8 @@ int znn_model_get_params(znn_model* m, float* host_slab);
 int znn_model_get_grads(znn_model* m, float* host_slab);
 int znn_model_get_velocities(znn_model* m, float* host_slab);
 /* keys: "lr", "momentum", "fused_softmax" (1/0), "fused_linear" (1/0, process-wide), "dp_bucket_floats",
- * "dp_overlap" (1/0) */
+ * "dp_overlap" (1/0), "cuda_graph" (1/0: capture the training step once per (input buffers, batch) and replay it;
+ * MLP / CNN models with device-resident inputs on one GPU; lr and momentum are baked in at capture) */
 int znn_model_set_option(znn_model* m, const char* key, double value);
 /* One training step.  x: [batch, features] pixels (MLP/CNN) or [batch, seq] fp32 token ids (GPT); targets: batch
  * (or batch*seq) int32 labels.  on_device = 1: both pointers are device memory and are used in place.
@@ -75,6 +76,7 @@ int znn_model_block_fwd_bwd(znn_model* m, const float* x, const float* dy, int B
 int znn_model_greedy_decode(znn_model* m, const float* prompt_ids, int batch, int prompt_len, int n_new, float* out_ids);
 int znn_model_arena_high_water(znn_model* m, long long* bytes);
 int znn_model_last_step_ops(znn_model* m, int* n_ops);
+int znn_model_graph_replays(znn_model* m, long long* n);
 
 #ifdef __cplusplus
 }

@@ -183,3 +183,39 @@ def test_greedy_decode_matches_oracle(Model):
             s.append(float(n))
     want = np.array([s[4:] for s in seqs], np.float32)
     np.testing.assert_array_equal(got, want)
+
+
+@pytest.mark.parametrize("kind,dims", [("mlp", (784, 128, 64, 10)), ("cnn_ref", ())])
+def test_cuda_graph_replay_matches_eager(Model, kind, dims):
+    """The captured-and-replayed training step must leave exactly the parameters the eager step leaves
+    (same kernels, same order), step after step, with new data copied into the same device buffers."""
+    from znn_b200 import ops
+    r = np.random.default_rng(5)
+    P0 = models.init_params(kind, dims if dims else None, seed=6)
+    batches = [(pixels(r, 64), r.integers(0, 10, 64).astype(np.int32)) for _ in range(6)]
+    finals, losses = [], []
+    for use_graph in (0, 1):
+        m = Model(kind, dims, arena_bytes=256 << 20)
+        m.set_params(P0)
+        m.set_option("lr", 0.05)
+        m.set_option("momentum", 0.9)
+        m.set_option("cuda_graph", use_graph)
+        dx, dt = ops.DevBuf(64 * 784 * 4), ops.DevBuf(64 * 4)
+        ls = []
+        for x, t in batches:
+            lib_ = ops.lib()
+            lib_.call("znn_memcpy_h2d", dx.ptr, x.ctypes.data, x.nbytes)
+            lib_.call("znn_memcpy_h2d", dt.ptr, t.ctypes.data, t.nbytes)
+            lib_.call("znn_sync")
+            import ctypes as C
+            loss = C.c_float()
+            lib_.call("znn_model_train_step", m.h, dx.ptr, dt.ptr, 64, 0, 1, C.byref(loss))
+            ls.append(loss.value)
+        if use_graph:
+            assert m.graph_replays() == len(batches) - 1      # the first step runs eagerly, the rest replay
+        finals.append(m.get_params())
+        losses.append(ls)
+        m.close()
+    assert losses[0] == losses[1]
+    for k in finals[0]:
+        np.testing.assert_array_equal(finals[0][k], finals[1][k])

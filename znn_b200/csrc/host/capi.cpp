@@ -1,4 +1,5 @@
 // C entry points of the host mirror (include/znn_host.h).
+#include <cuda_runtime.h>
 #include <math.h>
 #include <string.h>
 
@@ -209,7 +210,24 @@ struct znn_model {
     bool dp_overlap = true;
     int last_ops = 0;
     std::unordered_map<const Tensor*, int> param_index;
+    // CUDA-graph replay of the training step (option "cuda_graph"): the step's launch sequence is captured once
+    // per (input pointers, batch) and replayed; the per-step arena hands out the same addresses every step, so the
+    // captured kernels stay valid.
+    bool use_graph = false;
+    cudaGraphExec_t graph_exec = nullptr;
+    const void* graph_x = nullptr;
+    const void* graph_t = nullptr;
+    int graph_batch = 0, graph_seen = 0;
+    float* graph_loss = nullptr;
+    long long graph_replays = 0;
 };
+
+static void drop_graph(znn_model* m)
+{
+    if (m->graph_exec) cudaGraphExecDestroy(m->graph_exec);
+    m->graph_exec = nullptr;
+    m->graph_seen = 0;
+}
 
 namespace {
 
@@ -368,6 +386,7 @@ int znn_model_destroy(znn_model* m)
     ZNN_HOST_TRY
     if (m) {
         znn_sync();
+        drop_graph(m);
         delete m;
     }
     ZNN_HOST_CATCH
@@ -444,18 +463,20 @@ int znn_model_set_option(znn_model* m, const char* key, double value)
         m->gpt.set_fused_softmax(value != 0.0);
         m->block.attn.fused_softmax = (value != 0.0);
     } else if (k == "fused_linear") set_fused_linear(value != 0.0);
+    else if (k == "cuda_graph") {
+        m->use_graph = (value != 0.0);
+        if (!m->use_graph) drop_graph(m);
+    }
     else if (k == "dp_bucket_floats") m->dp_bucket_floats = (size_t)value;
     else if (k == "dp_overlap") m->dp_overlap = (value != 0.0);
     else throw Error(ZNN_ERR_INVALID, "unknown option '" + k + "'");
     ZNN_HOST_CATCH
 }
 
-int znn_model_train_step(znn_model* m, const float* x, const int32_t* targets, int batch, int seq, int on_device,
-                         float* loss_host)
+// One training step as the example programs run it (examples/fashion_mnist.zig:131-167); returns the device
+// address of the loss scalar.
+static float* run_train_step(znn_model* m, const float* x, const int32_t* targets, int batch, int seq, bool on_device)
 {
-    ZNN_HOST_TRY
-    if (batch <= 0) throw Error(ZNN_ERR_INVALID, "batch must be positive");
-    if (m->kind == ZNN_MODEL_GPT && seq <= 0) throw Error(ZNN_ERR_INVALID, "seq must be positive");
     m->arena->reset();                       // Graph.init / graph.deinit of the previous batch
     Graph g(m->arena.get());
     const size_t rows = (m->kind == ZNN_MODEL_GPT) ? (size_t)batch * seq : (size_t)batch;
@@ -465,7 +486,7 @@ int znn_model_train_step(znn_model* m, const float* x, const int32_t* targets, i
         check(znn_memcpy_h2d(t, targets, rows * sizeof(int32_t)), "upload targets");
         dev_targets = t;  // the stream synchronisation of the input upload below covers this copy
     }
-    Tensor* logits = model_forward(*m, g, x, batch, seq, on_device != 0);
+    Tensor* logits = model_forward(*m, g, x, batch, seq, on_device);
     Tensor* loss = g.softmaxCrossEntropy(logits, dev_targets);
     m->ps.zeroGrad();                        // model.zeroGrad() (fashion_mnist.zig:155)
     int world = 1;
@@ -484,7 +505,72 @@ int znn_model_train_step(znn_model* m, const float* x, const int32_t* targets, i
     }
     m->opt.step(1.0f / (float)world);        // optimizer.step(); 1/world turns the rank sum into the global mean
     m->last_ops = (int)g.ops().size();
-    if (loss_host) check(znn_memcpy_d2h(loss_host, loss->data, sizeof(float)), "read loss");
+    return loss->data;
+}
+
+int znn_model_train_step(znn_model* m, const float* x, const int32_t* targets, int batch, int seq, int on_device,
+                         float* loss_host)
+{
+    ZNN_HOST_TRY
+    if (batch <= 0) throw Error(ZNN_ERR_INVALID, "batch must be positive");
+    if (m->kind == ZNN_MODEL_GPT && seq <= 0) throw Error(ZNN_ERR_INVALID, "seq must be positive");
+    int world = 1;
+    znn_dp_world(&world, nullptr);
+    // Replay is possible when nothing in the step touches the host: device-resident inputs, one GPU, and a model
+    // whose forward uploads nothing (the GPT forward uploads its position ids, so it always runs eagerly).
+    const bool can_replay = m->use_graph && on_device && world == 1 && m->kind != ZNN_MODEL_GPT && m->kind != ZNN_MODEL_BLOCK;
+    float* loss_dev = nullptr;
+    if (!can_replay) {
+        loss_dev = run_train_step(m, x, targets, batch, seq, on_device != 0);
+    } else {
+        if (m->graph_x != x || m->graph_t != targets || m->graph_batch != batch) {
+            drop_graph(m);
+            m->graph_x = x;
+            m->graph_t = targets;
+            m->graph_batch = batch;
+        }
+        if (m->graph_exec) {
+            void* st = nullptr;
+            check(znn_get_stream(&st), "znn_get_stream");
+            if (cudaGraphLaunch(m->graph_exec, (cudaStream_t)st) != cudaSuccess)
+                throw Error(ZNN_ERR_CUDA, std::string("cudaGraphLaunch: ") + cudaGetErrorString(cudaGetLastError()));
+            m->graph_replays++;
+            loss_dev = m->graph_loss;
+        } else if (m->graph_seen == 0) {
+            // first step with these buffers: run eagerly so that scratch blocks reach their final size
+            loss_dev = run_train_step(m, x, targets, batch, seq, true);
+            m->graph_seen = 1;
+        } else {
+            void* stv = nullptr;
+            check(znn_get_stream(&stv), "znn_get_stream");
+            cudaStream_t st = (cudaStream_t)stv;
+            if (cudaStreamBeginCapture(st, cudaStreamCaptureModeThreadLocal) != cudaSuccess)
+                throw Error(ZNN_ERR_CUDA, std::string("cudaStreamBeginCapture: ") + cudaGetErrorString(cudaGetLastError()));
+            cudaGraph_t graph = nullptr;
+            try {
+                m->graph_loss = run_train_step(m, x, targets, batch, seq, true);
+            } catch (...) {
+                cudaStreamEndCapture(st, &graph);
+                if (graph) cudaGraphDestroy(graph);
+                cudaGetLastError();
+                m->use_graph = false;
+                throw;
+            }
+            if (cudaStreamEndCapture(st, &graph) != cudaSuccess || !graph)
+                throw Error(ZNN_ERR_CUDA, std::string("cudaStreamEndCapture: ") + cudaGetErrorString(cudaGetLastError()));
+            const cudaError_t e = cudaGraphInstantiate(&m->graph_exec, graph, 0);
+            cudaGraphDestroy(graph);
+            if (e != cudaSuccess) {
+                m->graph_exec = nullptr;
+                throw Error(ZNN_ERR_CUDA, std::string("cudaGraphInstantiate: ") + cudaGetErrorString(e));
+            }
+            if (cudaGraphLaunch(m->graph_exec, st) != cudaSuccess)
+                throw Error(ZNN_ERR_CUDA, std::string("cudaGraphLaunch: ") + cudaGetErrorString(cudaGetLastError()));
+            m->graph_replays++;
+            loss_dev = m->graph_loss;
+        }
+    }
+    if (loss_host) check(znn_memcpy_d2h(loss_host, loss_dev, sizeof(float)), "read loss");
     ZNN_HOST_CATCH
 }
 
@@ -556,6 +642,13 @@ int znn_model_arena_high_water(znn_model* m, long long* bytes)
 {
     ZNN_HOST_TRY
     if (bytes) *bytes = (long long)m->arena->high_water();
+    ZNN_HOST_CATCH
+}
+
+int znn_model_graph_replays(znn_model* m, long long* n)
+{
+    ZNN_HOST_TRY
+    if (n) *n = m->graph_replays;
     ZNN_HOST_CATCH
 }
 

@@ -103,6 +103,11 @@ class Model:
         lib().call("znn_model_greedy_decode", self.h, p.ctypes.data, p.shape[0], p.shape[1], n_new, out.ctypes.data)
         return out
 
+    def graph_replays(self):
+        n = C.c_longlong()
+        lib().call("znn_model_graph_replays", self.h, C.byref(n))
+        return n.value
+
     def last_step_ops(self):
         n = C.c_int()
         lib().call("znn_model_last_step_ops", self.h, C.byref(n))
