@@ -608,12 +608,14 @@ __global__ void split_transpose_kernel(const float* __restrict__ X, long long ld
 // copied in HBM.  Two converter warps rewrite each landed tile in place as
 // hi = rn_tf32(x) and store lo = rn_tf32(x - hi) next to it; the conversion is
 // elementwise, so it is blind to the 128-byte swizzle.  CTA pairs only.
-//   16 warps: 0 TMA, 1 MMA + TMEM, 2-3 idle, 4-7 converters, 8-15 epilogue.  The epilogue warps
-//   hold 128 accumulators per thread, so registers are moved to them with setmaxnreg
-//   (warpgroups 0-1 shrink to 56, warpgroups 2-3 grow to 200).
+//   16 warps: 0 TMA, 1 MMA + TMEM, 2-7 converters, 8-15 epilogue.  The converters work as two groups of
+//   three warps that take alternate pipeline stages, so that one group's proxy fence and barrier arrival
+//   overlap the other group's conversion.  The epilogue warps hold 128 accumulators per thread, so registers
+//   are moved to them with setmaxnreg (warpgroups 0-1 shrink to 56, warpgroups 2-3 grow to 200).
 constexpr int kDirectThreads = 512;
-constexpr int kConvWarps = 4;
-constexpr int kConvWarp0 = 4, kEpiWarp0 = 8;
+constexpr int kConvWarps = 3;     // warps per converter group
+constexpr int kConvGroups = 2;
+constexpr int kConvWarp0 = 2, kEpiWarp0 = 8;
 
 __device__ __forceinline__ uint32_t mbar_try_wait_cluster(uint32_t bar, uint32_t parity)
 {
@@ -753,7 +755,7 @@ gemm3x_direct_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_cons
     bool ok = true;
     if (warp < kEpiWarp0) {
     asm volatile("setmaxnreg.dec.sync.aligned.u32 56;");
-    if (aborted || warp == 2 || warp == 3) {
+    if (aborted) {
     } else if (warp == 0) {
         // ---------------- TMA producer: raw fp32 tiles of this CTA's rows of A and of B ----------------
         if (lane == 0) {
@@ -824,12 +826,13 @@ gemm3x_direct_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_cons
         }
     } else if (warp < kEpiWarp0) {
         // ---------------- converters: raw tile -> hi (in place) and lo ----------------
-        const int ct = threadIdx.x - 32 * kConvWarp0;  // 0..127
+        const int group = (warp - kConvWarp0) / kConvWarps;                      // which alternate stages
+        const int ct = threadIdx.x - 32 * (kConvWarp0 + group * kConvWarps);    // 0..95 inside the group
         const uint32_t conv_leader0 = mapa_shared(conv_bar(0), 0);
         constexpr int kAVec = Cfg::kABytes / 16, kBVec = Cfg::kBBytes / 16;
         const bool store_hi = (p.conv_mode == 0);
         bool got = true;
-        for (int kb = 0; kb < kb_count; kb++) {
+        for (int kb = group; kb < kb_count; kb += kConvGroups) {
             const int s = kb % Cfg::kStages;
             const uint32_t ph = (kb / Cfg::kStages) & 1;
             if (lane == 0) got = mbar_wait_bounded(full_bar(s), ph);
