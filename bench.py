@@ -275,7 +275,8 @@ def run_gpu(args):
     flops_step = 6.0 * n ** 3
     value = world * flops_step * steps / (ms_max * 1e-3) / 1e12
 
-    # ---- end to end: host buffers in, host buffers out, through the same C ABI ----
+    # ---- end to end: host tensors in, host tensors out, ONE call of the host-operand entry point.
+    # The shim pipelines the three uploads, the three products and the three downloads by panels.
     hA, hB, hdC = (torch.empty((n, n), dtype=torch.float32).pin_memory() for _ in range(3))
     hC, hdA, hdB = (torch.empty((n, n), dtype=torch.float32).pin_memory() for _ in range(3))
     hA.copy_(A)
@@ -284,26 +285,31 @@ def run_gpu(args):
     nbytes = n * n * 4
 
     def e2e_step():
-        L.call("znn_memcpy_h2d", A.data_ptr(), hA.data_ptr(), nbytes)
-        L.call("znn_memcpy_h2d", B.data_ptr(), hB.data_ptr(), nbytes)
-        L.call("znn_memcpy_h2d", dC.data_ptr(), hdC.data_ptr(), nbytes)
-        step()
-        L.call("znn_memcpy_d2h", hC.data_ptr(), Cm.data_ptr(), nbytes)
-        L.call("znn_memcpy_d2h", hdA.data_ptr(), dA.data_ptr(), nbytes)
-        L.call("znn_memcpy_d2h", hdB.data_ptr(), dB.data_ptr(), nbytes)
+        # gradients start from zero (after zeroGrad), so accumulate = 0 writes them without uploading zeros
+        L.call("znn_matmul_host_fwd_bwd", hA.data_ptr(), hB.data_ptr(), hdC.data_ptr(), hC.data_ptr(),
+               hdA.data_ptr(), hdB.data_ptr(), n, n, n, 0, 0)
 
-    e2e_step()
+    for _ in range(2):
+        e2e_step()
     barrier()
     e2e_steps = min(steps, 5)
     e0.record(stream)
     for _ in range(e2e_steps):
-        e2e_step()
+        e2e_step()       # returns when its results are in host memory
     e1.record(stream)
     barrier()
     t = torch.tensor([e0.elapsed_time(e1)], device="cuda", dtype=torch.float64)
     if world > 1:
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
     e2e_value = world * flops_step * e2e_steps / (float(t.item()) * 1e-3) / 1e12
+    # spot check of the pipelined results against the device-resident products of the same inputs
+    L.call("znn_sgemm", 101, 111, 111, n, n, n, 1.0, A.data_ptr(), n, B.data_ptr(), n, 0.0, Cm.data_ptr(), n)
+    torch.cuda.synchronize()
+    sl = slice(n - 256, n)
+    ref_rows = Cm[sl].cpu()
+    e2e_check = float((hC[sl] - ref_rows).norm() / ref_rows.norm())
+    if not e2e_check <= 1e-5:
+        raise SystemExit(f"end-to-end result differs from the device-resident product: {e2e_check}")
 
     tf32_live = None
     if rank == 0 and world == 1:
@@ -347,7 +353,7 @@ def run_gpu(args):
                          "cublas_tf32_live_tflops": tf32_live,
                          "frac_of_live_cublas_tf32_third": (achieved / (tf32_live / 3.0)) if (achieved and tf32_live) else None},
             "e2e": {"value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": 3 * nbytes, "d2h_bytes_per_step": 3 * nbytes,
-                    "steps": e2e_steps},
+                    "steps": e2e_steps, "call": "znn_matmul_host_fwd_bwd (pinned host tensors; copies and panels pipelined)"},
             "gpu_launches": launches, "clocks": clocks,
         }
         if gpt is not None:

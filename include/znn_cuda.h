@@ -73,6 +73,23 @@ int znn_sgemm_batched_strided(int trans_a, int trans_b, int M, int N, int K, flo
                               const float* A, int lda, long long stride_a,
                               const float* B, int ldb, long long stride_b, float beta,
                               float* C, int ldc, long long stride_c, int batch);
+/* cblas_sgemm with HOST operands, the exact shape of the reference's binding (src/cblas.zig:17-34 is
+ * called with host slices at all 8 call sites): A, B and C are host pointers; C is final in host memory
+ * when the call returns.  The product is pipelined by row panels of C: panel i's rows of op(A) (and of C
+ * when beta != 0) travel host->device while panel i-1 is multiplied and panel i-2's result travels
+ * device->host.  Pinned (page-locked) host memory makes the copies asynchronous; pageable memory works
+ * but serialises them.  panels: number of row panels, 0 = automatic (one per ~1024 rows, at most 16). */
+int znn_sgemm_host(int order, int trans_a, int trans_b, int M, int N, int K, float alpha,
+                   const float* A, int lda, const float* B, int ldb, float beta, float* C, int ldc, int panels);
+/* The MatMul operator's forward and backward arms (src/autodiff.zig:107-133 and :593-641) over HOST
+ * tensors in one pipelined call: C = A.B, dA (+)= dC.B^T, dB (+)= A^T.dC with A[M,K], B[K,N], dC[M,N],
+ * all compact row-major host arrays.  Each operand crosses the link once; C and dA leave by row panels
+ * while later operand rows still arrive, dB by column panels once dC is complete.  NULL outputs are
+ * skipped (dC may be NULL when both gradients are).  accumulate = 1 adds to the gradients already in
+ * dA/dB (the reference's +=, which costs their upload); 0 overwrites them (the same result after
+ * zeroGrad).  panels as for znn_sgemm_host. */
+int znn_matmul_host_fwd_bwd(const float* A, const float* B, const float* dC, float* C, float* dA, float* dB,
+                            int M, int K, int N, int accumulate, int panels);
 /* Fused form of Linear.forward = addBias(matmul(x, W), b) (src/nn.zig:44-51): Y[M,N] = X[M,K].W[K,N] + bias[N]
  * in one pass (the bias is added in the GEMM epilogue); an addition, the two separate ops remain.
  * Backward of the pair (src/autodiff.zig:593-641 and :652-672 chained): dX += dY.W^T, dW += X^T.dY,

@@ -23,6 +23,7 @@ SOURCES = [
     ("runtime.cu", []),
     ("gemm_tc.cu", []),
     ("gemm_api.cu", []),
+    ("hostop.cu", []),
     ("rowops.cu", ["-fmad=false"]),
     ("conv.cu", ["-fmad=false"]),
     ("dp.cu", []),

@@ -245,6 +245,13 @@ int znn_gemm_set_path(int path)
 
 int znn_gemm_last_path(void) { return t_last_path; }
 
+}  // extern "C"
+namespace znn {
+int gemm_requested_path() { return t_path; }
+}
+extern "C" {
+
+
 int znn_gemm_set_chunk(int k_elements)
 {
     ZNN_REQUIRE(k_elements >= 32 && k_elements % 32 == 0, "chunk must be a positive multiple of 32");

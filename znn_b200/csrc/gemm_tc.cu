@@ -1092,6 +1092,7 @@ static thread_local int t_conv_mode = 1;
 void tc_set_conv_mode(int m) { t_conv_mode = m; }
 static thread_local bool t_splitk_enabled = true;
 void tc_set_splitk(int on) { t_splitk_enabled = (on != 0); }
+int tc_get_splitk() { return t_splitk_enabled ? 1 : 0; }
 static thread_local int t_chunk_kblocks = 8;  // 256 contraction elements per tensor-memory accumulation
 int tc_chunk_kblocks() { return t_chunk_kblocks; }
 void tc_set_chunk_kblocks(int v) { t_chunk_kblocks = v < 1 ? 1 : v; }

@@ -34,8 +34,8 @@ struct DeviceState {
     bool ready = false;
     cudaStream_t own_stream = nullptr;
     int* status = nullptr;  // device int
-    void* ws[2] = {nullptr, nullptr};   // slot 0: GEMM planes / partials / row-op partials; slot 1: conv im2col
-    size_t ws_bytes[2] = {0, 0};
+    void* ws[3] = {nullptr, nullptr, nullptr};   // slot 0: GEMM planes / partials / row-op partials; slot 1: conv im2col; slot 2: device copies of host operands
+    size_t ws_bytes[3] = {0, 0, 0};
     int sms = 0;
 };
 
@@ -92,10 +92,18 @@ int sm_count()
     return s ? s->sms : 0;
 }
 
+void stream_override(cudaStream_t s, bool has, cudaStream_t* old_s, bool* old_has)
+{
+    if (old_s) *old_s = t_user_stream;
+    if (old_has) *old_has = t_has_user_stream;
+    t_user_stream = s;
+    t_has_user_stream = has;
+}
+
 void* workspace_slot(int slot, size_t bytes)
 {
     DeviceState* s = cur(true);
-    if (!s || slot < 0 || slot > 1) return nullptr;
+    if (!s || slot < 0 || slot > 2) return nullptr;
     if (bytes <= s->ws_bytes[slot]) return s->ws[slot];
     // Growing: everything queued so far may still read the old block.
     cudaStreamSynchronize(stream());

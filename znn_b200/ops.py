@@ -107,6 +107,37 @@ def sgemm(ta, tb, M, N, K, alpha, A, lda, B, ldb, beta, Cm, ldc):
     return Cm
 
 
+def sgemm_host(ta, tb, M, N, K, alpha, A, lda, B, ldb, beta, Cm, ldc, panels=0):
+    """cblas_sgemm straight on host arrays: ONE call, the shim pipelines copies and panels itself."""
+    _ensure()
+    for a in (A, B, Cm):
+        assert a.dtype == np.float32 and a.flags["C_CONTIGUOUS"]
+    lib().call("znn_sgemm_host", ROW_MAJOR, ta, tb, M, N, K, alpha, A.ctypes.data, lda, B.ctypes.data, ldb, beta,
+               Cm.ctypes.data, ldc, panels)
+    check_device_status()
+    return Cm
+
+
+def matmul_host_fwd_bwd(A, B, dC=None, want_dA=True, want_dB=True, dA=None, dB=None, panels=0):
+    """MatMul forward + backward on host arrays in one pipelined call.  With dA/dB given the
+    gradients are accumulated into them (the reference's +=); otherwise fresh arrays are returned."""
+    _ensure()
+    A, B = _f(A), _f(B)
+    M, K = A.shape
+    N = B.shape[1]
+    Cm = np.empty((M, N), np.float32)
+    acc = int(dA is not None or dB is not None)
+    if dC is not None:
+        dC = _f(dC)
+        if not acc:
+            dA = np.empty((M, K), np.float32) if want_dA else None
+            dB = np.empty((K, N), np.float32) if want_dB else None
+    p = lambda a: a.ctypes.data if a is not None else None
+    lib().call("znn_matmul_host_fwd_bwd", p(A), p(B), p(dC), p(Cm), p(dA), p(dB), M, K, N, acc, panels)
+    check_device_status()
+    return Cm, dA, dB
+
+
 def sgemm_batched(ta, tb, M, N, K, alpha, A, lda, sa, B, ldb, sb, beta, Cm, ldc, sc, batch):
     _ensure()
     dA, dB, dC = _up(A), _up(B), _up(Cm)
