@@ -15,9 +15,6 @@ int fail(int code, const char* fmt, ...);
 // The stream every kernel of the calling host thread is launched on.
 cudaStream_t stream();
 
-// Replaces the calling thread's launch stream (has = false: the shim-owned one) and returns the previous setting.
-void stream_override(cudaStream_t s, bool has, cudaStream_t* old_s, bool* old_has);
-
 // Device status word (one int per device, zero-initialised).  Kernels OR a
 // ZNN_DEV_* bit into it when a bounded wait expires; znn_device_status() reads it.
 int* device_status_word();
@@ -29,10 +26,6 @@ void* workspace(size_t bytes);
 void* workspace_slot(int slot, size_t bytes);
 
 int sm_count();
-
-// GEMM knobs of the calling host thread, for callers that override them for a while (hostop.cu)
-int gemm_requested_path();
-int tc_get_splitk();
 
 // Kernel-launch counter of the calling host thread (read by znn_launch_count).
 void count_launch();

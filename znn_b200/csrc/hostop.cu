@@ -15,7 +15,7 @@ namespace znn {
 namespace {
 
 struct Pipe {
-    cudaStream_t up = nullptr, down = nullptr, lane2 = nullptr;
+    cudaStream_t up = nullptr, down = nullptr;
     std::vector<cudaEvent_t> events;
     size_t used = 0;
 };
@@ -30,7 +30,6 @@ Pipe* pipe()
     if (!p.up) {
         if (cudaStreamCreateWithFlags(&p.up, cudaStreamNonBlocking) != cudaSuccess) return nullptr;
         if (cudaStreamCreateWithFlags(&p.down, cudaStreamNonBlocking) != cudaSuccess) return nullptr;
-        if (cudaStreamCreateWithFlags(&p.lane2, cudaStreamNonBlocking) != cudaSuccess) return nullptr;
     }
     p.used = 0;
     return &p;
@@ -73,73 +72,13 @@ int panel_rows(int rows, int panels)
     return pr < 128 ? 128 : pr;
 }
 
-// The compute side of the pipeline.  A panel product rarely fills a whole number of waves of CTAs, so
-// with one compute stream the GPU idles at every panel's tail.  When the in-place tensor-core path can
-// take every panel (it needs no scratch, so two products may be in flight at once), consecutive panels
-// alternate between the caller's stream and a second one and the next panel's CTAs fill the tail.
-// The thread's stream and GEMM knobs are put back when the object goes out of scope.
-struct Lanes {
-    Pipe* p;
-    cudaStream_t lane[2];
-    int n = 1;
-    cudaStream_t saved_stream = nullptr;
-    bool saved_has = false;
-    int saved_path = 0, saved_splitk = 1;
-    bool overridden = false;
-
-    Lanes(Pipe* pipe_, bool two) : p(pipe_)
-    {
-        lane[0] = stream();
-        lane[1] = p->lane2;
-        if (!two) return;
-        n = 2;
-        overridden = true;
-        saved_path = gemm_requested_path();
-        saved_splitk = tc_get_splitk();
-        stream_override(lane[0], true, &saved_stream, &saved_has);
-        znn_gemm_set_path(4);
-        znn_gemm_set_splitk(0);
-    }
-    ~Lanes()
-    {
-        if (!overridden) return;
-        stream_override(saved_stream, saved_has, nullptr, nullptr);
-        znn_gemm_set_path(saved_path);
-        znn_gemm_set_splitk(saved_splitk);
-    }
-    int open()   // the second lane starts after whatever the caller queued
-    {
-        return n == 2 ? chain(p, lane[0], lane[1]) : ZNN_OK;
-    }
-    cudaStream_t use(int i)
-    {
-        cudaStream_t s = lane[i % n];
-        if (n == 2) stream_override(s, true, nullptr, nullptr);
-        return s;
-    }
-    // Waits for everything the call queued; an error from the device surfaces here.
-    int drain()
-    {
-        if (n == 2) {
-            stream_override(lane[0], true, nullptr, nullptr);
-            int rc = chain(p, lane[1], lane[0]);   // the caller's stream stays ordered after the whole call
-            if (rc != ZNN_OK) return rc;
-        }
-        ZNN_CUDA_OK(cudaStreamSynchronize(p->up));
-        ZNN_CUDA_OK(cudaStreamSynchronize(lane[0]));
-        ZNN_CUDA_OK(cudaStreamSynchronize(p->down));
-        return ZNN_OK;
-    }
-};
-
-// Two lanes need every panel on the in-place tensor-core path: dimensions that keep each operand's
-// rows 16-byte aligned, and panels large enough for that path to be the right one anyway.
-bool two_lanes_ok(int M, int N, int K, int pr)
+// Waits for everything the call queued; an error from the device surfaces here.
+int drain(Pipe* p)
 {
-    if (pr >= M) return false;   // one panel
-    if ((M % 4) || (N % 4) || (K % 4)) return false;
-    const int small = M < N ? (M < K ? M : K) : (N < K ? N : K);
-    return small >= 256 && 2.0 * pr * (double)N * K >= 1.0e9;
+    ZNN_CUDA_OK(cudaStreamSynchronize(p->up));
+    ZNN_CUDA_OK(cudaStreamSynchronize(stream()));
+    ZNN_CUDA_OK(cudaStreamSynchronize(p->down));
+    return ZNN_OK;
 }
 
 }  // namespace
@@ -186,15 +125,12 @@ int znn_sgemm_host(int order, int trans_a, int trans_b, int M, int N, int K, flo
     const int lda_d = an ? K : M, ldb_d = bn ? N : K;
 
     const int pr = panel_rows(M, panels);
-    Lanes lanes(p, mult && two_lanes_ok(M, N, K, pr));
     // whatever ran before on the compute stream may still use the device copies
     ZNN_TRY(chain(p, stream(), p->up));
     ZNN_TRY(chain(p, stream(), p->down));
-    ZNN_TRY(lanes.open());
     if (mult)
         ZNN_CUDA_OK(copy_block(dB, ldb_d, B, ldb, bn ? K : N, bn ? N : K, cudaMemcpyHostToDevice, p->up));
 
-    int panel = 0;
     for (int m0 = 0; m0 < M; m0 += pr) {
         const int mp = (M - m0 < pr) ? M - m0 : pr;
         if (mult) {
@@ -205,14 +141,14 @@ int znn_sgemm_host(int order, int trans_a, int trans_b, int M, int N, int K, flo
         }
         if (beta != 0.0f)
             ZNN_CUDA_OK(copy_block(dC + (size_t)m0 * N, N, C + (size_t)m0 * ldc, ldc, mp, N, cudaMemcpyHostToDevice, p->up));
-        cudaStream_t cs = lanes.use(panel++);
+        cudaStream_t cs = stream();
         ZNN_TRY(chain(p, p->up, cs));
         const float* a_panel = an ? dA + (size_t)m0 * K : dA + m0;
         ZNN_TRY(znn_sgemm(order, trans_a, trans_b, mp, N, K, alpha, a_panel, lda_d, dB, ldb_d, beta, dC + (size_t)m0 * N, N));
         ZNN_TRY(chain(p, cs, p->down));
         ZNN_CUDA_OK(copy_block(C + (size_t)m0 * ldc, ldc, dC + (size_t)m0 * N, N, mp, N, cudaMemcpyDeviceToHost, p->down));
     }
-    return lanes.drain();
+    return drain(p);
 }
 
 int znn_matmul_host_fwd_bwd(const float* A, const float* B, const float* dC, float* Cout, float* dA, float* dB,
@@ -240,11 +176,8 @@ int znn_matmul_host_fwd_bwd(const float* A, const float* B, const float* dC, flo
 
     const int pr = panel_rows(M, panels);
     const int pc = panel_rows(N, panels);
-    Lanes lanes(p, two_lanes_ok(M, N, K, pr) && two_lanes_ok(N, M, K, pc));
     ZNN_TRY(chain(p, stream(), p->up));
     ZNN_TRY(chain(p, stream(), p->down));
-    ZNN_TRY(lanes.open());
-    int panel = 0;
 
     // B first: every panel of C and of dA needs all of it.
     ZNN_CUDA_OK(cudaMemcpyAsync(d_b, B, nb * sizeof(float), cudaMemcpyHostToDevice, p->up));
@@ -255,7 +188,7 @@ int znn_matmul_host_fwd_bwd(const float* A, const float* B, const float* dC, flo
         ZNN_CUDA_OK(cudaMemcpyAsync(d_a + (size_t)m0 * K, A + (size_t)m0 * K, (size_t)mp * K * sizeof(float),
                                     cudaMemcpyHostToDevice, p->up));
         if (!Cout) continue;
-        cudaStream_t cs = lanes.use(panel++);
+        cudaStream_t cs = stream();
         ZNN_TRY(chain(p, p->up, cs));
         ZNN_TRY(znn_sgemm(ZNN_ROW_MAJOR, ZNN_NO_TRANS, ZNN_NO_TRANS, mp, N, K, 1.0f, d_a + (size_t)m0 * K, K, d_b, N, 0.0f,
                           d_c + (size_t)m0 * N, N));
@@ -263,7 +196,7 @@ int znn_matmul_host_fwd_bwd(const float* A, const float* B, const float* dC, flo
         ZNN_CUDA_OK(cudaMemcpyAsync(Cout + (size_t)m0 * N, d_c + (size_t)m0 * N, (size_t)mp * N * sizeof(float),
                                     cudaMemcpyDeviceToHost, p->down));
     }
-    if (!dA && !dB) return lanes.drain();
+    if (!dA && !dB) return drain(p);
 
     // dA (+)= dC.B^T by row panels as dC arrives (MatMul backward, src/autodiff.zig:593-641)
     for (int m0 = 0; m0 < M; m0 += pr) {
@@ -274,7 +207,7 @@ int znn_matmul_host_fwd_bwd(const float* A, const float* B, const float* dC, flo
         if (accumulate)
             ZNN_CUDA_OK(cudaMemcpyAsync(d_da + (size_t)m0 * K, dA + (size_t)m0 * K, (size_t)mp * K * sizeof(float),
                                         cudaMemcpyHostToDevice, p->up));
-        cudaStream_t cs = lanes.use(panel++);
+        cudaStream_t cs = stream();
         ZNN_TRY(chain(p, p->up, cs));
         ZNN_TRY(znn_sgemm(ZNN_ROW_MAJOR, ZNN_NO_TRANS, ZNN_TRANS, mp, K, N, 1.0f, d_dc + (size_t)m0 * N, N, d_b, N, gbeta,
                           d_da + (size_t)m0 * K, K));
@@ -282,20 +215,20 @@ int znn_matmul_host_fwd_bwd(const float* A, const float* B, const float* dC, flo
         ZNN_CUDA_OK(cudaMemcpyAsync(dA + (size_t)m0 * K, d_da + (size_t)m0 * K, (size_t)mp * K * sizeof(float),
                                     cudaMemcpyDeviceToHost, p->down));
     }
-    if (!dB) return lanes.drain();
+    if (!dB) return drain(p);
 
     // dB (+)= A^T.dC needs every row of dC, so it is cut into column panels once dC is complete;
     // each finished panel leaves while the next one is multiplied.
     for (int n0 = 0; n0 < N; n0 += pc) {
         const int np = (N - n0 < pc) ? N - n0 : pc;
         if (accumulate) ZNN_CUDA_OK(copy_block(d_db + n0, N, dB + n0, N, K, np, cudaMemcpyHostToDevice, p->up));
-        cudaStream_t cs = lanes.use(panel++);
+        cudaStream_t cs = stream();
         ZNN_TRY(chain(p, p->up, cs));   // all of dC (queued above) has arrived
         ZNN_TRY(znn_sgemm(ZNN_ROW_MAJOR, ZNN_TRANS, ZNN_NO_TRANS, K, np, M, 1.0f, d_a, K, d_dc + n0, N, gbeta, d_db + n0, N));
         ZNN_TRY(chain(p, cs, p->down));
         ZNN_CUDA_OK(copy_block(dB + n0, N, d_db + n0, N, K, np, cudaMemcpyDeviceToHost, p->down));
     }
-    return lanes.drain();
+    return drain(p);
 }
 
 }  // extern "C"

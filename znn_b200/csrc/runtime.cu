@@ -92,14 +92,6 @@ int sm_count()
     return s ? s->sms : 0;
 }
 
-void stream_override(cudaStream_t s, bool has, cudaStream_t* old_s, bool* old_has)
-{
-    if (old_s) *old_s = t_user_stream;
-    if (old_has) *old_has = t_has_user_stream;
-    t_user_stream = s;
-    t_has_user_stream = has;
-}
-
 void* workspace_slot(int slot, size_t bytes)
 {
     DeviceState* s = cur(true);
