@@ -197,6 +197,13 @@ def run_gpu(args):
     torch.cuda.set_stream(stream)
     L.call("znn_set_stream", stream.cuda_stream)
 
+    if args.workload == "shape":
+        if rank == 0:
+            print(json.dumps({"metric": "gemm_shape_tflops", "n_gpus": 1, "data": "synthetic",
+                              "product": shape_part(args, L, torch, stream)}), flush=True)
+        if world > 1:
+            dist.destroy_process_group()
+        return 0
     if args.workload == "rowops":
         if rank == 0:
             print(json.dumps({"metric": "rowop_hbm_bandwidth", "n_gpus": 1, "data": "synthetic",
@@ -450,7 +457,9 @@ def gpt_part(args, L, torch, dist, stream, world, rank, local):
     st = C.c_int(0)
     L.call("znn_device_status", C.byref(st), 1)
     if st.value:
-        raise SystemExit(f"device status word {st.value} during the GPT step; the run is invalid")
+        rec = (C.c_int * 16)()
+        L.call("znn_gemm_wait_record", rec)
+        raise SystemExit(f"device status word {st.value} during the GPT step; the run is invalid; first expired wait: {list(rec)}")
     out = {
         "metric": "gpt_train_tokens_per_s", "value": world * B * T * steps / (ms * 1e-3), "unit": "tokens/s",
         "n_gpus": world, "steps": steps, "warmup": warmup, "ms_per_step": ms / steps, "scaling": "weak",
@@ -552,6 +561,43 @@ def configs_part(args, L, torch, stream):
     return out
 
 
+def shape_part(args, L, torch, stream):
+    """One (batched) product at a given shape, timed alone with CUDA events: the small case for profiler captures."""
+    M, N, K, ta, tb, batch = [int(v) for v in args.shape.split(",")]
+    g = torch.Generator(device="cuda").manual_seed(7)
+    A = torch.randn((batch, M, K) if ta == 111 else (batch, K, M), device="cuda", generator=g)
+    B = torch.randn((batch, K, N) if tb == 111 else (batch, N, K), device="cuda", generator=g)
+    Cm = torch.zeros((batch, M, N), device="cuda")
+    L.call("znn_gemm_set_path", args.path)
+    lda, ldb = (K if ta == 111 else M), (N if tb == 111 else K)
+
+    def run():
+        L.call("znn_sgemm_batched_strided", ta, tb, M, N, K, 1.0, A.data_ptr(), lda, M * K, B.data_ptr(), ldb, K * N,
+               0.0, Cm.data_ptr(), N, M * N, batch)
+
+    steps, warmup = max(1, args.steps), max(1, args.warmup)
+    for _ in range(warmup):
+        run()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record(stream)
+    for _ in range(steps):
+        run()
+    e1.record(stream)
+    torch.cuda.synchronize()
+    us = e0.elapsed_time(e1) * 1e3 / steps
+    st = C.c_int(0)
+    L.call("znn_device_status", C.byref(st), 1)
+    if st.value:
+        rec = (C.c_int * 16)()
+        L.call("znn_gemm_wait_record", rec)
+        raise SystemExit(f"device status word {st.value}: a bounded device-side wait expired; first: {list(rec)}")
+    want = torch.matmul(A[0].double() if ta == 111 else A[0].double().t(), B[0].double() if tb == 111 else B[0].double().t())
+    err = float((Cm[0].double() - want).norm() / want.norm())
+    return {"shape": [M, N, K], "trans": [ta, tb], "batch": batch, "path": L.dll.znn_gemm_last_path(), "us": us,
+            "tflops": 2.0 * M * N * K * batch / us / 1e6, "rel_err_slice0_vs_fp64": err}
+
+
 def rowops_part(args, L, torch, stream):
     """Row-wise / elementwise kernels at transformer sizes, each timed alone with CUDA events on the launching
     stream; working sets exceed the 126 MB L2.  GB/s = algorithmic bytes per launch / time, compared with the
@@ -631,7 +677,10 @@ def main():
     ap.add_argument("--n", type=int, default=8192)
     ap.add_argument("--impl", default="znn_b200", choices=["znn_b200", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
-    ap.add_argument("--workload", default="all", choices=["all", "matmul", "gpt", "configs", "rowops"],
+    ap.add_argument("--shape", default="1024,64,1024,111,111,96",
+                    help="--workload shape: M,N,K,trans_a,trans_b,batch of one (batched) product")
+    ap.add_argument("--path", type=int, default=0, help="--workload shape: GEMM path (0 = automatic)")
+    ap.add_argument("--workload", default="all", choices=["all", "matmul", "gpt", "configs", "rowops", "shape"],
                     help="matmul: the headline MatMul sweep step only; all: also the GPT training step; "
                          "configs: the MLP / CNN / block / decode configs on one GPU")
     args = ap.parse_args()

@@ -114,6 +114,13 @@ int znn_gemm_set_splitk(int enable);
  * the tensor core ignores the 13 low mantissa bits of a kind::tf32 operand (measured on B200: results
  * are bit-identical to mode 0); 0 = they also store hi = x with those bits cleared. */
 int znn_gemm_set_conv_mode(int mode);
+/* In-place path only: 1 (default) = persistent launch (one CTA pair per SM pair walks the output tiles, so the
+ * next tile's main loop overlaps the previous tile's epilogue); 0 = one CTA pair per output tile. */
+int znn_gemm_set_persistent(int enable);
+/* Diagnostic: where the first bounded device-side wait of a tensor-core GEMM expired since the last call (16 ints:
+ * claimed flag, role, barrier, work unit, counter, M, N, K, split-K slices, tile width, CTA rank, CTA pair, units,
+ * pairs, beta*1000, batch); all zero when none did.  Reading clears the record. */
+int znn_gemm_wait_record(int* out16);
 /* Measurement aid: with profiling on, every tensor-core GEMM kernel launch (not its split
  * pre-pass) is bracketed by CUDA events on the launching stream; znn_gemm_profile_read waits
  * for them and returns the summed kernel time, the launch count and the algorithmic

@@ -201,3 +201,28 @@ def test_tensor_core_ignores_low_mantissa_bits(ops):
             outs.append(got)
         np.testing.assert_array_equal(outs[0], outs[1])
     lib().call("znn_gemm_set_conv_mode", 1)
+
+
+@pytest.mark.parametrize("ta,tb,M,N,K,batch", [(NT, NT, 2048, 2048, 96, 4), (NT, T, 1024, 64, 512, 20), (T, NT, 768, 384, 800, 9),
+                                               (T, NT, 64, 1024, 256, 24), (NT, NT, 520, 1000, 72, 11)])
+@pytest.mark.parametrize("beta", [0.0, 1.0])
+def test_in_place_kernel_many_work_units_per_cta_pair(ops, ta, tb, M, N, K, batch, beta):
+    """The in-place kernel is persistent: each CTA pair walks several output tiles, with pipeline stages and
+    accumulator buffers carried across tiles (odd chunk counts shift the buffer parity from tile to tile).
+    More tiles than the GPU has CTA pairs, ragged edges, beta on and off, against fp64."""
+    r = np.random.default_rng(M + N + K + batch)
+    A = r.standard_normal((batch, M, K) if ta == NT else (batch, K, M), np.float32)
+    B = r.standard_normal((batch, K, N) if tb == NT else (batch, N, K), np.float32)
+    C0 = r.standard_normal((batch, M, N), np.float32)
+    got = C0.copy()
+    ops.set_gemm_path(4)
+    try:
+        ops.sgemm_batched(ta, tb, M, N, K, 0.75, A, A.shape[2], A[0].size, B, B.shape[2], B[0].size, beta, got, N, M * N, batch)
+        assert ops.last_gemm_path() == 4
+    finally:
+        ops.set_gemm_path(0)
+    a64 = A.astype(np.float64) if ta == NT else A.astype(np.float64).transpose(0, 2, 1)
+    b64 = B.astype(np.float64) if tb == NT else B.astype(np.float64).transpose(0, 2, 1)
+    want = 0.75 * (a64 @ b64) + beta * C0
+    for b in range(batch):
+        assert rel_err(got[b], want[b]) <= TOL, f"slice {b}"

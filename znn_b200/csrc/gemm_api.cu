@@ -2,6 +2,8 @@
 // reference (src/cblas.zig:17-34) on device pointers.  Large problems go to the
 // tcgen05 3xTF32 kernel (gemm_tc.cu); small or launch-bound ones to the fp32 FMA
 // kernel below, which takes any transposes, leading dimensions and alignment.
+#include <stdlib.h>
+
 #include "common.cuh"
 
 namespace znn {
@@ -19,6 +21,8 @@ int launch_splitk_reduce(const float* partial, int splits, int M, int N, int bat
 int tc_profile_enable(int enable);
 void tc_set_chunk_kblocks(int v);
 void tc_set_splitk(int on);
+void tc_set_persistent(int on);
+int tc_wait_record(int* out16);
 void tc_set_conv_mode(int m);
 int tc_profile_read(double* kernel_ms, long long* launches, double* flops);
 
@@ -153,11 +157,27 @@ static int gemm_dispatch(int ta, int tb, int M, int N, int K, float alpha, const
     // the in-place path needs TMA-readable operands; otherwise the pre-split planes path takes any layout
     if (path == 4 && !direct_ok) path = 3;
     t_last_path = path;
-    if (path == 4)
-        return gemm_tc_direct(ta, tb, M, N, K, alpha, A, lda, stride_a, B, ldb, stride_b, beta, C, ldc, stride_c, batch, bias);
-    if (path == 2 || path == 3)
-        return gemm_tc(ta, tb, M, N, K, alpha, A, lda, stride_a, B, ldb, stride_b, beta, C, ldc, stride_c, batch,
-                       path == 2 ? 1 : 2, bias);
+    if (path >= 2) {
+        int rc = (path == 4) ? gemm_tc_direct(ta, tb, M, N, K, alpha, A, lda, stride_a, B, ldb, stride_b, beta, C, ldc,
+                                              stride_c, batch, bias)
+                             : gemm_tc(ta, tb, M, N, K, alpha, A, lda, stride_a, B, ldb, stride_b, beta, C, ldc, stride_c,
+                                       batch, path == 2 ? 1 : 2, bias);
+        // Debug aid (environment ZNN_GEMM_CHECK=1): wait for every tensor-core product and name the first one
+        // whose kernel reported an expired device-side wait.
+        static const bool check = [] { const char* e = getenv("ZNN_GEMM_CHECK"); return e && e[0] == '1'; }();
+        if (rc == ZNN_OK && check) {
+            int st = 0;
+            ZNN_CUDA_OK(cudaStreamSynchronize(stream()));
+            ZNN_CUDA_OK(cudaMemcpy(&st, device_status_word(), sizeof(int), cudaMemcpyDeviceToHost));
+            if (st != 0)
+                return fail(ZNN_ERR_CUDA,
+                            "device status %d after GEMM path %d ta %d tb %d M %d N %d K %d batch %d lda %lld ldb %lld ldc %lld "
+                            "beta %g bias %d A %p B %p C %p",
+                            st, path, ta, tb, M, N, K, batch, lda, ldb, ldc, (double)beta, bias != nullptr, (const void*)A,
+                            (const void*)B, (void*)C);
+        }
+        return rc;
+    }
 
     const long long sa_i = (ta == ZNN_NO_TRANS) ? lda : 1, sa_p = (ta == ZNN_NO_TRANS) ? 1 : lda;
     const long long sb_p = (tb == ZNN_NO_TRANS) ? ldb : 1, sb_j = (tb == ZNN_NO_TRANS) ? 1 : ldb;
@@ -247,6 +267,18 @@ int znn_gemm_set_chunk(int k_elements)
 int znn_gemm_set_splitk(int enable)
 {
     tc_set_splitk(enable);
+    return ZNN_OK;
+}
+
+int znn_gemm_wait_record(int* out16)
+{
+    ZNN_REQUIRE(out16, "out16 is NULL");
+    return tc_wait_record(out16);
+}
+
+int znn_gemm_set_persistent(int enable)
+{
+    tc_set_persistent(enable);
     return ZNN_OK;
 }
 

@@ -19,6 +19,8 @@
 // status word and leaves; later CTAs see the word and return at once.
 #include <cuda.h>
 
+#include <stdlib.h>
+
 #include "common.cuh"
 
 namespace znn {
@@ -28,12 +30,11 @@ namespace znn {
 // ---------------------------------------------------------------------------
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
 
-__device__ __forceinline__ uint64_t globaltimer_ns()
-{
-    uint64_t t;
-    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
-    return t;
-}
+// Time base of the bounded waits: the SM's own 64-bit cycle counter.  (%globaltimer is not used: its 64-bit read
+// is not guaranteed to be consistent when the low word wraps, every 4.29 s, and a torn read makes an elapsed time of
+// seconds out of nothing.)  4e9 cycles are 2.0 s at the 1.965 GHz maximum clock, 2.7 s at 1.5 GHz.
+__device__ __forceinline__ uint64_t wait_clock() { return (uint64_t)clock64(); }
+constexpr uint64_t kWaitLimitCycles = 4000000000ull;
 
 __device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count)
 {
@@ -58,16 +59,16 @@ __device__ __forceinline__ uint32_t mbar_try_wait(uint32_t bar, uint32_t parity)
     return ok;
 }
 
-// Waits at most ~2 s of wall time; false on expiry.
+// Waits at most ~2 s (4e9 SM cycles); false on expiry.
 __device__ __forceinline__ bool mbar_wait_bounded(uint32_t bar, uint32_t parity)
 {
     if (mbar_try_wait(bar, parity)) return true;
-    const uint64_t t0 = globaltimer_ns();
+    const uint64_t t0 = wait_clock();
     for (;;) {
 #pragma unroll 1
         for (int i = 0; i < 128; i++)
             if (mbar_try_wait(bar, parity)) return true;
-        if (globaltimer_ns() - t0 > 2000000000ull) return false;
+        if (wait_clock() - t0 > kWaitLimitCycles) return false;
     }
 }
 
@@ -221,6 +222,7 @@ struct GemmTcParams {
     int conv_mode;       // direct kernel: 0 = store the masked hi tile, 1 = leave the raw tile as hi
     const float* bias;   // optional [N] vector added to every output row (fused AddBias), may be nullptr
     int tiles_m, tiles_n;
+    int splits, batch;   // in-place kernel: work units = tiles_m * tiles_n * splits * batch
     float alpha, beta;
     float* C;
     long long ldc, stride_c;
@@ -637,12 +639,12 @@ __device__ __forceinline__ uint32_t mbar_try_wait_cluster(uint32_t bar, uint32_t
 __device__ __forceinline__ bool mbar_wait_bounded_cluster(uint32_t bar, uint32_t parity)
 {
     if (mbar_try_wait_cluster(bar, parity)) return true;
-    const uint64_t t0 = globaltimer_ns();
+    const uint64_t t0 = wait_clock();
     for (;;) {
 #pragma unroll 1
         for (int i = 0; i < 128; i++)
             if (mbar_try_wait_cluster(bar, parity)) return true;
-        if (globaltimer_ns() - t0 > 2000000000ull) return false;
+        if (wait_clock() - t0 > kWaitLimitCycles) return false;
     }
 }
 
@@ -666,18 +668,201 @@ __host__ __device__ constexpr uint32_t make_tf32_idesc_major(int mma_m, int mma_
     return make_tf32_idesc(mma_m, mma_n) | ((a_mn ? 1u : 0u) << 15) | ((b_mn ? 1u : 0u) << 16);
 }
 
+// Epilogue staging: each epilogue warp turns 32 rows x 32 columns at a time through its own block of shared
+// memory (pitch 33 floats: conflict-free both ways), so that every store instruction writes one contiguous
+// 128-byte run of a row of C.  The blocks are separate from the operand ring, which is busy with the next tile.
+constexpr int kEpiStagePitch = 33;
+constexpr int kEpiStageBytes = kEpiWarps * 32 * kEpiStagePitch * 4;   // 33792
+
+// Where the first bounded wait of the in-place kernel expired (diagnostic; read and cleared by znn_gemm_wait_record):
+// [0] claimed, [1] role (0 TMA, 1 MMA, 2 converter, 3 epilogue), [2] barrier (0 empty, 1 full, 2 conv, 3 acc_empty,
+// 4 acc_full), [3] work unit, [4] stage counter or chunk counter, [5..7] M N K, [8] split-K slices, [9] BN, [10] CTA rank,
+// [11] CTA pair, [12] units in the launch, [13] pairs in the launch.
+__device__ int g_wait_record[16];
+
+__device__ __forceinline__ void record_expiry(int role, int barrier, int unit, unsigned counter, int cta_rank, int pair)
+{
+    if (atomicCAS(&g_wait_record[0], 0, 1) != 0) return;
+    g_wait_record[1] = role; g_wait_record[2] = barrier; g_wait_record[3] = unit; g_wait_record[4] = (int)counter;
+    g_wait_record[10] = cta_rank; g_wait_record[11] = pair;
+}
+
+// filled by thread 0 of the CTA that recorded the expiry, at the end of the kernel (keeps the hot loops lean)
+__device__ __forceinline__ void record_shape(const GemmTcParams& p, int bn, int npairs)
+{
+    g_wait_record[5] = p.M; g_wait_record[6] = p.N; g_wait_record[7] = p.k_real; g_wait_record[8] = p.splits;
+    g_wait_record[9] = bn; g_wait_record[12] = p.tiles_m * p.tiles_n * p.splits * p.batch; g_wait_record[13] = npairs;
+    g_wait_record[14] = (int)(p.beta * 1000.0f); g_wait_record[15] = p.batch;
+}
+
 template <int BN>
 struct DirectCfg {
     static constexpr int kBRows = BN / 2;
     static constexpr int kABytes = kTileM * kBK * 4;
     static constexpr int kBBytes = kBRows * kBK * 4;
     static constexpr int kStageBytes = 2 * kABytes + 2 * kBBytes;  // A raw/hi, A lo, B raw/hi, B lo
-    static constexpr int kStages = (200 * 1024) / kStageBytes > 6 ? 6 : (200 * 1024) / kStageBytes;
-    static constexpr int kSmemBytes = kStages * kStageBytes + 1024 + 512;
+    static constexpr int kRingBudget = 232448 - 1024 - 512 - kEpiStageBytes;
+    static constexpr int kStages = kRingBudget / kStageBytes > 6 ? 6 : kRingBudget / kStageBytes;
+    static constexpr int kSmemBytes = kStages * kStageBytes + 1024 + 512 + kEpiStageBytes;
     static constexpr int kTmemCols = 2 * BN < 32 ? 32 : 2 * BN;
     static constexpr int kColsPerThread = BN / 2;
+    static_assert(kStageBytes % 1024 == 0, "stages must keep the 1 KB alignment of what follows");
 };
 
+// One work unit = one 256 x BN output tile of one batch slice and one split-K slice.
+struct DirectUnit {
+    int row0, col0, batch, split, kb_first, kb_count, nchunks;
+};
+
+__device__ __forceinline__ DirectUnit direct_unit(const GemmTcParams& p, int u, int cta_rank, int bn)
+{
+    const int units_per = p.tiles_m * p.tiles_n;
+    const int t = u % units_per;
+    const int sb = u / units_per;
+    DirectUnit d;
+    d.split = sb % p.splits;
+    d.batch = sb / p.splits;
+    // groups of 8 tile-rows are walked column by column so that CTA pairs running together share
+    // A row panels and B column panels in L2
+    constexpr int G = 8;
+    const int per_group = G * p.tiles_n;
+    const int g = t / per_group;
+    const int first_m = g * G;
+    const int rows_in_group = min(G, p.tiles_m - first_m);
+    const int r = t - g * per_group;
+    const int tile_m = first_m + r % rows_in_group;
+    const int tile_n = r / rows_in_group;
+    d.row0 = (tile_m * 2 + cta_rank) * kTileM;
+    d.col0 = tile_n * bn;
+    d.kb_first = d.split * p.kblocks_per_split;
+    d.kb_count = min(p.k_blocks - d.kb_first, p.kblocks_per_split);
+    d.nchunks = (d.kb_count + p.chunk_kblocks - 1) / p.chunk_kblocks;
+    return d;
+}
+
+// k-blocks of work unit u (all the converter warps need to know about it)
+__device__ __forceinline__ int direct_unit_kb_count(const GemmTcParams& p, int u)
+{
+    if (p.splits == 1) return p.k_blocks;
+    const int split = (u / (p.tiles_m * p.tiles_n)) % p.splits;
+    return min(p.k_blocks - split * p.kblocks_per_split, p.kblocks_per_split);
+}
+
+// Final store of one epilogue warp's 32 x CPT sub-tile (each thread holds one row in registers).
+template <int CPT>
+__device__ __forceinline__ void epilogue_store_rows(const float (&acc)[CPT], float* stage, int lane, int row_base, int cbase,
+                                                    int M, int N, float* out, long long out_ld, float alpha, float beta,
+                                                    const float* bias)
+{
+    const int rows = min(32, M - row_base);
+    constexpr int RB = 8;  // rows in flight: the loads of old C (beta != 0) are issued together
+#pragma unroll
+    for (int j = 0; j < CPT / 32; j++) {
+#pragma unroll
+        for (int c = 0; c < 32; c++) stage[lane * kEpiStagePitch + c] = acc[32 * j + c];
+        __syncwarp();
+        const int col = cbase + 32 * j + lane;
+        if (col < N) {
+            const float bv = bias ? bias[col] : 0.0f;
+            for (int r0 = 0; r0 < rows; r0 += RB) {
+                float old[RB];
+                if (beta != 0.0f) {
+#pragma unroll
+                    for (int u = 0; u < RB; u++)
+                        if (r0 + u < rows) old[u] = out[(size_t)(row_base + r0 + u) * out_ld + col];
+                }
+#pragma unroll
+                for (int u = 0; u < RB; u++) {
+                    if (r0 + u >= rows) continue;
+                    float o = alpha * stage[(r0 + u) * kEpiStagePitch + lane];
+                    if (bias) o += bv;
+                    if (beta != 0.0f) o += beta * old[u];
+                    out[(size_t)(row_base + r0 + u) * out_ld + col] = o;
+                }
+            }
+        }
+        __syncwarp();
+    }
+}
+
+// The same store with 16-byte accesses, for a 16-byte aligned C whose leading dimension is a multiple of 4: the warp's
+// 4 KB block holds 1024 / CPT whole rows of the sub-tile at a time (8 rows of 128 columns), written by the lanes that
+// own those rows and read back row by row, so that one instruction stores up to 512 contiguous bytes of C.  The float4
+// index is XOR-ed with the row so that neither direction has bank conflicts.  A third of the instructions of the
+// scalar form, which matters because the epilogue warps share the SM with the next tile's main loop.
+template <int CPT>
+__device__ __forceinline__ void epilogue_store_vec(const float (&acc)[CPT], float* stage, int lane, int row_base, int cbase,
+                                                   int M, int N, float* out, long long out_ld, float alpha, float beta,
+                                                   const float* bias)
+{
+    constexpr int LPR = CPT / 4;          // lanes (float4) per row
+    constexpr int RPP = 1024 / CPT;       // rows per pass (block = 1024 floats)
+    constexpr int RPI = 32 / LPR;         // rows per read instruction
+    constexpr int NI = RPP / RPI;         // read instructions per pass
+    const int rows = min(32, M - row_base);
+    if (rows <= 0) return;
+    float4* const st4 = reinterpret_cast<float4*>(stage);
+    const int my_f = lane % LPR;           // float4 index inside the row this lane reads
+    const int col = cbase + 4 * my_f;
+    const bool col_full = col + 3 < N;
+    float4 b4 = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+    if (bias && col_full) b4 = *reinterpret_cast<const float4*>(bias + col);
+#pragma unroll
+    for (int g = 0; g < 32 / RPP; g++) {
+        if (g * RPP >= rows) break;
+        // lanes g*RPP .. g*RPP+RPP-1 own the rows of this pass
+        if (lane / RPP == g) {
+            const int rl = lane % RPP;
+#pragma unroll
+            for (int f = 0; f < LPR; f++)
+                st4[rl * LPR + (f ^ (rl & 7) & (LPR - 1))] = make_float4(acc[4 * f], acc[4 * f + 1], acc[4 * f + 2], acc[4 * f + 3]);
+        }
+        __syncwarp();
+        constexpr int IB = NI < 4 ? NI : 4;   // old-C loads in flight per lane
+#pragma unroll
+        for (int i0 = 0; i0 < NI; i0 += IB) {
+            float4 old[IB];
+            if (beta != 0.0f && col_full) {
+#pragma unroll
+                for (int i = 0; i < IB; i++) {
+                    const int r = g * RPP + (i0 + i) * RPI + lane / LPR;
+                    if (r < rows) old[i] = *reinterpret_cast<const float4*>(out + (size_t)(row_base + r) * out_ld + col);
+                }
+            }
+#pragma unroll
+            for (int i = 0; i < IB; i++) {
+                const int rl = (i0 + i) * RPI + lane / LPR;
+                const int r = g * RPP + rl;
+                if (r >= rows || col >= N) continue;
+                const float4 v = st4[rl * LPR + (my_f ^ (rl & 7) & (LPR - 1))];
+                float o[4] = {alpha * v.x, alpha * v.y, alpha * v.z, alpha * v.w};
+                float* crow = out + (size_t)(row_base + r) * out_ld;
+                if (col_full) {
+                    o[0] += b4.x; o[1] += b4.y; o[2] += b4.z; o[3] += b4.w;
+                    if (beta != 0.0f) {
+                        o[0] += beta * old[i].x; o[1] += beta * old[i].y; o[2] += beta * old[i].z; o[3] += beta * old[i].w;
+                    }
+                    *reinterpret_cast<float4*>(crow + col) = make_float4(o[0], o[1], o[2], o[3]);
+                } else {
+#pragma unroll
+                    for (int e = 0; e < 4; e++) {
+                        if (col + e < N) {
+                            float t = o[e];
+                            if (bias) t += bias[col + e];
+                            if (beta != 0.0f) t += beta * crow[col + e];
+                            crow[col + e] = t;
+                        }
+                    }
+                }
+            }
+        }
+        __syncwarp();
+    }
+}
+
+// Persistent: each CTA pair walks the work units pair, pair + npairs, ...  Pipeline-stage and accumulator-buffer
+// counters run on across units, so the TMA/convert/MMA side starts the next unit while the epilogue warps still
+// store the previous one (the two tensor-memory buffers that serve chunked promotion also decouple the units).
 template <int BN, bool A_MN, bool B_MN>
 __global__ void __launch_bounds__(kDirectThreads, 1)
 gemm3x_direct_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CUtensorMap tm_b,
@@ -685,51 +870,39 @@ gemm3x_direct_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_cons
 {
     using Cfg = DirectCfg<BN>;
     constexpr int CTAS = 2;
+    constexpr int S = Cfg::kStages;
     extern __shared__ uint8_t smem_raw[];
     const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
     uint8_t* smem_gen = smem_raw + (smem_base - smem_u32(smem_raw));
-    const uint32_t bar_base = smem_base + Cfg::kStages * Cfg::kStageBytes;
+    // layout: operand ring | epilogue staging | barrier block
+    const uint32_t epi_stage_addr = smem_base + S * Cfg::kStageBytes;
+    const uint32_t bar_base = epi_stage_addr + kEpiStageBytes;
     // barriers: full[S] (TMA -> converters, per CTA), conv[S] (converters of both CTAs -> MMA, in the leader),
     // empty[S] (MMA -> TMA, both CTAs), acc_full[2], acc_empty[2]
     auto full_bar = [&](int s) { return bar_base + 8u * s; };
-    auto conv_bar = [&](int s) { return bar_base + 8u * (Cfg::kStages + s); };
-    auto empty_bar = [&](int s) { return bar_base + 8u * (2 * Cfg::kStages + s); };
-    auto acc_full_bar = [&](int b) { return bar_base + 8u * (3 * Cfg::kStages + b); };
-    auto acc_empty_bar = [&](int b) { return bar_base + 8u * (3 * Cfg::kStages + 2 + b); };
-    constexpr int kWordOff = 8 * (3 * Cfg::kStages + 4);
+    auto conv_bar = [&](int s) { return bar_base + 8u * (S + s); };
+    auto empty_bar = [&](int s) { return bar_base + 8u * (2 * S + s); };
+    auto acc_full_bar = [&](int b) { return bar_base + 8u * (3 * S + b); };
+    auto acc_empty_bar = [&](int b) { return bar_base + 8u * (3 * S + 2 + b); };
+    constexpr int kWordOff = 8 * (3 * S + 4);
+    static_assert(kWordOff + 8 <= 512, "barrier block overflows");
     volatile uint32_t* tmem_slot =
-        reinterpret_cast<volatile uint32_t*>(smem_gen + Cfg::kStages * Cfg::kStageBytes + kWordOff);
+        reinterpret_cast<volatile uint32_t*>(smem_gen + S * Cfg::kStageBytes + kEpiStageBytes + kWordOff);
     const uint32_t tmem_slot_addr = bar_base + kWordOff;
     volatile uint32_t* abort_slot = tmem_slot + 1;
     const uint32_t abort_slot_addr = tmem_slot_addr + 4;
+    float* const epi_stage_all = reinterpret_cast<float*>(smem_gen + S * Cfg::kStageBytes);
 
     const int warp = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
-    const uint32_t cta_rank = cluster_ctarank();
+    const int cta_rank = (int)cluster_ctarank();
     const bool leader = (cta_rank == 0);
-
-    const int unit = blockIdx.x >> 1;
-    int tile_m, tile_n;
-    {
-        constexpr int G = 8;
-        const int per_group = G * p.tiles_n;
-        const int g = unit / per_group;
-        const int first_m = g * G;
-        const int rows_in_group = min(G, p.tiles_m - first_m);
-        const int r = unit - g * per_group;
-        tile_m = first_m + r % rows_in_group;
-        tile_n = r / rows_in_group;
-    }
-    const int batch = blockIdx.z;
-    const int row0 = (tile_m * CTAS + (int)cta_rank) * kTileM;
-    const int col0 = tile_n * BN;
+    const int pair = blockIdx.x >> 1, npairs = gridDim.x >> 1;
+    const int total_units = p.tiles_m * p.tiles_n * p.splits * p.batch;
     const int chunk = p.chunk_kblocks;
-    const int kb_first = (int)blockIdx.y * p.kblocks_per_split;
-    const int kb_count = min(p.k_blocks - kb_first, p.kblocks_per_split);
-    const int nchunks = (kb_count + chunk - 1) / chunk;
 
     if (threadIdx.x == 0) {
-        for (int s = 0; s < Cfg::kStages; s++) {
+        for (int s = 0; s < S; s++) {
             mbar_init(full_bar(s), 1);
             mbar_init(conv_bar(s), kConvWarps * CTAS);
             mbar_init(empty_bar(s), 1);
@@ -763,28 +936,32 @@ gemm3x_direct_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_cons
     } else if (warp == 0) {
         // ---------------- TMA producer: raw fp32 tiles of this CTA's rows of A and of B ----------------
         if (lane == 0) {
-            for (int kb = 0; kb < kb_count; kb++) {
-                const int s = kb % Cfg::kStages;
-                const uint32_t ph = (kb / Cfg::kStages) & 1;
-                if (!mbar_wait_bounded(empty_bar(s), ph ^ 1)) { ok = false; break; }
-                const uint32_t st = smem_base + s * Cfg::kStageBytes;
-                const int k0 = (kb_first + kb) * kBK;
-                mbar_arrive_expect_tx(full_bar(s), Cfg::kABytes + Cfg::kBBytes);
-                if (A_MN) {
+            uint32_t it = 0;
+            for (int u = pair; u < total_units && ok; u += npairs) {
+                const DirectUnit d = direct_unit(p, u, cta_rank, BN);
+                for (int kb = 0; kb < d.kb_count; kb++, it++) {
+                    const int s = it % S;
+                    const uint32_t ph = (it / S) & 1;
+                    if (!mbar_wait_bounded(empty_bar(s), ph ^ 1)) { record_expiry(0, 0, u, it, cta_rank, pair); ok = false; break; }
+                    const uint32_t st = smem_base + s * Cfg::kStageBytes;
+                    const int k0 = (d.kb_first + kb) * kBK;
+                    mbar_arrive_expect_tx(full_bar(s), Cfg::kABytes + Cfg::kBBytes);
+                    if (A_MN) {
 #pragma unroll
-                    for (int j = 0; j < kTileM / 32; j++)
-                        tma_load_3d(st + j * 4096, &tm_a, full_bar(s), row0 + 32 * j, k0, batch);
-                } else {
-                    tma_load_3d(st, &tm_a, full_bar(s), k0, row0, batch);
-                }
-                const uint32_t sb = st + 2 * Cfg::kABytes;
-                const int brow0 = col0 + (int)cta_rank * Cfg::kBRows;
-                if (B_MN) {
+                        for (int j = 0; j < kTileM / 32; j++)
+                            tma_load_3d(st + j * 4096, &tm_a, full_bar(s), d.row0 + 32 * j, k0, d.batch);
+                    } else {
+                        tma_load_3d(st, &tm_a, full_bar(s), k0, d.row0, d.batch);
+                    }
+                    const uint32_t sb = st + 2 * Cfg::kABytes;
+                    const int brow0 = d.col0 + cta_rank * Cfg::kBRows;
+                    if (B_MN) {
 #pragma unroll
-                    for (int j = 0; j < Cfg::kBRows / 32; j++)
-                        tma_load_3d(sb + j * 4096, &tm_b, full_bar(s), brow0 + 32 * j, k0, batch);
-                } else {
-                    tma_load_3d(sb, &tm_b, full_bar(s), k0, brow0, batch);
+                        for (int j = 0; j < Cfg::kBRows / 32; j++)
+                            tma_load_3d(sb + j * 4096, &tm_b, full_bar(s), brow0 + 32 * j, k0, d.batch);
+                    } else {
+                        tma_load_3d(sb, &tm_b, full_bar(s), k0, brow0, d.batch);
+                    }
                 }
             }
             if (!ok) atomicOr(p.status, ZNN_DEV_TMA_WAIT_EXPIRED);
@@ -796,39 +973,44 @@ gemm3x_direct_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_cons
             // descriptor start-address step per K=8 MMA, in 16-byte units
             constexpr uint32_t a_step = A_MN ? (1024 >> 4) : (32 >> 4);
             constexpr uint32_t b_step = B_MN ? (1024 >> 4) : (32 >> 4);
-            int kb = 0;
-            for (int c = 0; c < nchunks && ok; c++) {
-                const int buf = c & 1;
-                if (!mbar_wait_bounded_cluster(acc_empty_bar(buf), ((c >> 1) & 1) ^ 1)) { ok = false; break; }
-                tc_fence_after();
-                const uint32_t d_tmem = tmem_base + (uint32_t)(buf * BN);
-                const int kb_end = min(kb_count, kb + chunk);
-                for (bool first = true; kb < kb_end; kb++) {
-                    const int s = kb % Cfg::kStages;
-                    const uint32_t ph = (kb / Cfg::kStages) & 1;
-                    if (!mbar_wait_bounded_cluster(conv_bar(s), ph)) { ok = false; break; }
+            uint32_t it = 0, cc = 0;
+            for (int u = pair; u < total_units && ok; u += npairs) {
+                const DirectUnit d = direct_unit(p, u, cta_rank, BN);
+                int kb = 0;
+                for (int c = 0; c < d.nchunks && ok; c++, cc++) {
+                    const int buf = cc & 1;
+                    // the epilogue warps must have drained this buffer (two chunks ago, possibly of the previous unit)
+                    if (!mbar_wait_bounded_cluster(acc_empty_bar(buf), ((cc >> 1) & 1) ^ 1)) { record_expiry(1, 3, u, cc, cta_rank, pair); ok = false; break; }
                     tc_fence_after();
-                    const uint32_t st = smem_base + s * Cfg::kStageBytes;
-                    const uint64_t a_hi = A_MN ? make_mnmajor_sw128_desc(st) : make_kmajor_sw128_desc(st);
-                    const uint64_t a_lo = A_MN ? make_mnmajor_sw128_desc(st + Cfg::kABytes) : make_kmajor_sw128_desc(st + Cfg::kABytes);
-                    const uint32_t sb = st + 2 * Cfg::kABytes;
-                    const uint64_t b_hi = B_MN ? make_mnmajor_sw128_desc(sb) : make_kmajor_sw128_desc(sb);
-                    const uint64_t b_lo = B_MN ? make_mnmajor_sw128_desc(sb + Cfg::kBBytes) : make_kmajor_sw128_desc(sb + Cfg::kBBytes);
+                    const uint32_t d_tmem = tmem_base + (uint32_t)(buf * BN);
+                    const int kb_end = min(d.kb_count, kb + chunk);
+                    for (bool first = true; kb < kb_end; kb++, it++) {
+                        const int s = it % S;
+                        const uint32_t ph = (it / S) & 1;
+                        if (!mbar_wait_bounded_cluster(conv_bar(s), ph)) { record_expiry(1, 2, u, it, cta_rank, pair); ok = false; break; }
+                        tc_fence_after();
+                        const uint32_t st = smem_base + s * Cfg::kStageBytes;
+                        const uint64_t a_hi = A_MN ? make_mnmajor_sw128_desc(st) : make_kmajor_sw128_desc(st);
+                        const uint64_t a_lo = A_MN ? make_mnmajor_sw128_desc(st + Cfg::kABytes) : make_kmajor_sw128_desc(st + Cfg::kABytes);
+                        const uint32_t sb = st + 2 * Cfg::kABytes;
+                        const uint64_t b_hi = B_MN ? make_mnmajor_sw128_desc(sb) : make_kmajor_sw128_desc(sb);
+                        const uint64_t b_lo = B_MN ? make_mnmajor_sw128_desc(sb + Cfg::kBBytes) : make_kmajor_sw128_desc(sb + Cfg::kBBytes);
 #pragma unroll
-                    for (int k = 0; k < kBK / 8; k++)
-                        umma_tf32<CTAS>(d_tmem, a_lo + a_step * k, b_hi + b_step * k, idesc, (first && k == 0) ? 0u : 1u);
+                        for (int k = 0; k < kBK / 8; k++)
+                            umma_tf32<CTAS>(d_tmem, a_lo + a_step * k, b_hi + b_step * k, idesc, (first && k == 0) ? 0u : 1u);
 #pragma unroll
-                    for (int k = 0; k < kBK / 8; k++) umma_tf32<CTAS>(d_tmem, a_hi + a_step * k, b_lo + b_step * k, idesc, 1);
+                        for (int k = 0; k < kBK / 8; k++) umma_tf32<CTAS>(d_tmem, a_hi + a_step * k, b_lo + b_step * k, idesc, 1);
 #pragma unroll
-                    for (int k = 0; k < kBK / 8; k++) umma_tf32<CTAS>(d_tmem, a_hi + a_step * k, b_hi + b_step * k, idesc, 1);
-                    umma_commit_pair(empty_bar(s));
-                    first = false;
+                        for (int k = 0; k < kBK / 8; k++) umma_tf32<CTAS>(d_tmem, a_hi + a_step * k, b_hi + b_step * k, idesc, 1);
+                        umma_commit_pair(empty_bar(s));
+                        first = false;
+                    }
+                    if (ok) umma_commit_pair(acc_full_bar(buf));
                 }
-                if (ok) umma_commit_pair(acc_full_bar(buf));
             }
             if (!ok) atomicOr(p.status, ZNN_DEV_MMA_WAIT_EXPIRED);
         }
-    } else if (warp < kEpiWarp0) {
+    } else {
         // ---------------- converters: raw tile -> hi (in place) and lo ----------------
         const int group = (warp - kConvWarp0) / kConvWarps;                      // which alternate stages
         const int ct = threadIdx.x - 32 * (kConvWarp0 + group * kConvWarps);    // 0..95 inside the group
@@ -836,95 +1018,110 @@ gemm3x_direct_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_cons
         constexpr int kAVec = Cfg::kABytes / 16, kBVec = Cfg::kBBytes / 16;
         const bool store_hi = (p.conv_mode == 0);
         bool got = true;
-        for (int kb = group; kb < kb_count; kb += kConvGroups) {
-            const int s = kb % Cfg::kStages;
-            const uint32_t ph = (kb / Cfg::kStages) & 1;
-            if (lane == 0) got = mbar_wait_bounded(full_bar(s), ph);
-            got = __shfl_sync(0xffffffffu, (int)got, 0) != 0;
-            if (!got) break;
-            uint8_t* st = smem_gen + s * Cfg::kStageBytes;
-            // hi = x with the 13 low mantissa bits cleared (exactly a TF32 value); lo = x - hi is exact in
-            // fp32 and at most 2^-10 |x|; the tensor core drops lo's own low bits, a 2^-21 relative effect
-            auto convert = [&](uint8_t* base, int nvec, int lo_off) {
-                constexpr int kT = 32 * kConvWarps;
-#pragma unroll 1
-                for (int i0 = ct; i0 < nvec; i0 += 4 * kT) {
-                    uint4 x[4];
-#pragma unroll
-                    for (int u = 0; u < 4; u++)
-                        if (i0 + u * kT < nvec) x[u] = *reinterpret_cast<const uint4*>(base + 16 * (i0 + u * kT));
-#pragma unroll
-                    for (int u = 0; u < 4; u++) {
-                        if (i0 + u * kT >= nvec) continue;
-                        uint4 h;
-                        h.x = x[u].x & 0xFFFFE000u; h.y = x[u].y & 0xFFFFE000u;
-                        h.z = x[u].z & 0xFFFFE000u; h.w = x[u].w & 0xFFFFE000u;
-                        float4 l;
-                        l.x = __uint_as_float(x[u].x) - __uint_as_float(h.x);
-                        l.y = __uint_as_float(x[u].y) - __uint_as_float(h.y);
-                        l.z = __uint_as_float(x[u].z) - __uint_as_float(h.z);
-                        l.w = __uint_as_float(x[u].w) - __uint_as_float(h.w);
-                        uint8_t* src = base + 16 * (i0 + u * kT);
-                        if (store_hi) *reinterpret_cast<uint4*>(src) = h;
-                        *reinterpret_cast<float4*>(src + lo_off) = l;
-                    }
+        uint32_t it = 0;
+        for (int u = pair; u < total_units && got; u += npairs) {
+            const int kb_count = direct_unit_kb_count(p, u);
+            for (int kb = 0; kb < kb_count; kb++, it++) {
+                if ((int)(it % kConvGroups) != group) continue;
+                const int s = it % S;
+                const uint32_t ph = (it / S) & 1;
+                if (lane == 0) {
+                    got = mbar_wait_bounded(full_bar(s), ph);
+                    if (!got) record_expiry(2, 1, u, it, cta_rank, pair);
                 }
-            };
-            convert(st, kAVec, Cfg::kABytes);
-            convert(st + 2 * Cfg::kABytes, kBVec, Cfg::kBBytes);
-            // make the generic-proxy writes visible to the tensor core (async proxy), then signal the leader
-            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-            __syncwarp();
-            if (lane == 0) mbar_arrive_remote(conv_leader0 + 8u * s);
+                got = __shfl_sync(0xffffffffu, (int)got, 0) != 0;
+                if (!got) break;
+                uint8_t* st = smem_gen + s * Cfg::kStageBytes;
+                // hi = x with the 13 low mantissa bits cleared (exactly a TF32 value); lo = x - hi is exact in
+                // fp32 and at most 2^-10 |x|; the tensor core drops lo's own low bits, a 2^-21 relative effect
+                auto convert = [&](uint8_t* base, int nvec, int lo_off) {
+                    constexpr int kT = 32 * kConvWarps;
+#pragma unroll 1
+                    for (int i0 = ct; i0 < nvec; i0 += 4 * kT) {
+                        uint4 x[4];
+#pragma unroll
+                        for (int v = 0; v < 4; v++)
+                            if (i0 + v * kT < nvec) x[v] = *reinterpret_cast<const uint4*>(base + 16 * (i0 + v * kT));
+#pragma unroll
+                        for (int v = 0; v < 4; v++) {
+                            if (i0 + v * kT >= nvec) continue;
+                            uint4 h;
+                            h.x = x[v].x & 0xFFFFE000u; h.y = x[v].y & 0xFFFFE000u;
+                            h.z = x[v].z & 0xFFFFE000u; h.w = x[v].w & 0xFFFFE000u;
+                            float4 l;
+                            l.x = __uint_as_float(x[v].x) - __uint_as_float(h.x);
+                            l.y = __uint_as_float(x[v].y) - __uint_as_float(h.y);
+                            l.z = __uint_as_float(x[v].z) - __uint_as_float(h.z);
+                            l.w = __uint_as_float(x[v].w) - __uint_as_float(h.w);
+                            uint8_t* src = base + 16 * (i0 + v * kT);
+                            if (store_hi) *reinterpret_cast<uint4*>(src) = h;
+                            *reinterpret_cast<float4*>(src + lo_off) = l;
+                        }
+                    }
+                };
+                convert(st, kAVec, Cfg::kABytes);
+                convert(st + 2 * Cfg::kABytes, kBVec, Cfg::kBBytes);
+                // make the generic-proxy writes visible to the tensor core (async proxy), then signal the leader
+                asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+                __syncwarp();
+                if (lane == 0) mbar_arrive_remote(conv_leader0 + 8u * s);
+            }
         }
         if (!got && lane == 0) atomicOr(p.status, ZNN_DEV_TMA_WAIT_EXPIRED);
     }
     } else {
         asm volatile("setmaxnreg.inc.sync.aligned.u32 200;");
         if (!aborted) {
-        // ---------------- epilogue (as in the pre-split kernel) ----------------
+        // ---------------- epilogue: tensor memory -> fp32 registers (per chunk) -> C ----------------
         const int q = warp & 3;
         const int half = (warp - kEpiWarp0) >> 2;
         constexpr int CPT = Cfg::kColsPerThread;
-        float acc[CPT];
-#pragma unroll
-        for (int i = 0; i < CPT; i++) acc[i] = 0.0f;
         const uint32_t acc_empty_leader0 = mapa_shared(acc_empty_bar(0), 0);
+        float* const stage = epi_stage_all + (size_t)(warp - kEpiWarp0) * 32 * kEpiStagePitch;
+        const bool to_partial = (p.partial != nullptr);
+        const long long out_ld = to_partial ? (long long)p.N : p.ldc;
+        const float* const bias = to_partial ? nullptr : p.bias;
+        const float alpha = to_partial ? 1.0f : p.alpha, beta = to_partial ? 0.0f : p.beta;
         bool got = true;
-        for (int c = 0; c < nchunks; c++) {
-            const int buf = c & 1;
-            if (lane == 0) got = mbar_wait_bounded(acc_full_bar(buf), (c >> 1) & 1);
-            got = __shfl_sync(0xffffffffu, (int)got, 0) != 0;
-            if (!got) break;
-            tc_fence_after();
-            const uint32_t t0 = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(buf * BN + half * CPT);
+        uint32_t cc = 0;
+        for (int u = pair; u < total_units && got; u += npairs) {
+            const DirectUnit d = direct_unit(p, u, cta_rank, BN);
+            float acc[CPT];
 #pragma unroll
-            for (int j = 0; j < CPT / 32; j++) {
-                float v[32];
-                tmem_ld_32x32(t0 + 32u * j, v);
+            for (int i = 0; i < CPT; i++) acc[i] = 0.0f;
+            for (int c = 0; c < d.nchunks; c++, cc++) {
+                const int buf = cc & 1;
+                if (lane == 0) {
+                    got = mbar_wait_bounded(acc_full_bar(buf), (cc >> 1) & 1);
+                    if (!got) record_expiry(3, 4, u, cc, cta_rank, pair);
+                }
+                got = __shfl_sync(0xffffffffu, (int)got, 0) != 0;
+                if (!got) break;
+                tc_fence_after();
+                const uint32_t t0 = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(buf * BN + half * CPT);
 #pragma unroll
-                for (int i = 0; i < 32; i++) acc[32 * j + i] += v[i];
+                for (int j = 0; j < CPT / 32; j++) {
+                    float v[32];
+                    tmem_ld_32x32(t0 + 32u * j, v);
+#pragma unroll
+                    for (int i = 0; i < 32; i++) acc[32 * j + i] += v[i];
+                }
+                tc_fence_before();
+                __syncwarp();
+                if (lane == 0) mbar_arrive_remote(acc_empty_leader0 + 8u * buf);
             }
-            tc_fence_before();
-            __syncwarp();
-            if (lane == 0) mbar_arrive_remote(acc_empty_leader0 + 8u * buf);
-        }
-        if (!got) {
-            if (lane == 0) atomicOr(p.status, ZNN_DEV_EPI_WAIT_EXPIRED);
-        } else {
-            const int cbase = col0 + half * CPT;
+            if (!got) break;
             // split-K slices store their raw partial sums; a reduce kernel applies alpha/beta afterwards
-            const bool to_partial = (p.partial != nullptr);
-            float* const out = to_partial ? p.partial + ((size_t)blockIdx.y * gridDim.z + batch) * (size_t)p.M * p.N
-                                          : p.C + (size_t)batch * p.stride_c;
-            const long long out_ld = to_partial ? (long long)p.N : p.ldc;
-            const float* const bias = to_partial ? nullptr : p.bias;
+            float* const out = to_partial ? p.partial + ((size_t)d.split * p.batch + d.batch) * (size_t)p.M * p.N
+                                          : p.C + (size_t)d.batch * p.stride_c;
             const bool vec_ok = ((out_ld & 3) == 0) && ((reinterpret_cast<uintptr_t>(out) & 15) == 0) &&
-                                ((reinterpret_cast<uintptr_t>(p.bias) & 15) == 0);
-            const float alpha = to_partial ? 1.0f : p.alpha, beta = to_partial ? 0.0f : p.beta;
-            float* stage = reinterpret_cast<float*>(smem_gen) + (size_t)(warp - kEpiWarp0) * 32 * (CPT + 4);
-            epilogue_store_warp<CPT>(acc, stage, lane, row0 + q * 32, cbase, p.M, p.N, out, out_ld, alpha, beta, bias, vec_ok);
+                                ((reinterpret_cast<uintptr_t>(bias) & 15) == 0);
+            if (vec_ok)
+                epilogue_store_vec<CPT>(acc, stage, lane, d.row0 + q * 32, d.col0 + half * CPT, p.M, p.N, out, out_ld, alpha, beta, bias);
+            else
+                epilogue_store_rows<CPT>(acc, stage, lane, d.row0 + q * 32, d.col0 + half * CPT, p.M, p.N, out, out_ld, alpha, beta, bias);
         }
+        if (!got && lane == 0) atomicOr(p.status, ZNN_DEV_EPI_WAIT_EXPIRED);
         }
     }
 
@@ -935,6 +1132,8 @@ gemm3x_direct_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_cons
         tc_fence_after();
         tmem_dealloc<CTAS>(tmem_base, Cfg::kTmemCols);
     }
+    if (threadIdx.x == 0 && !aborted && g_wait_record[0] == 1 && g_wait_record[11] == pair && g_wait_record[5] == 0)
+        record_shape(p, BN, npairs);
 }
 
 // C = alpha * sum_s partial[s] + beta * C, slices added in order (deterministic)
@@ -1036,6 +1235,14 @@ static void prof_end(cudaEvent_t* e)
     if (e) cudaEventRecord(e[1], stream());
 }
 
+int tc_wait_record(int* out16)
+{
+    ZNN_CUDA_OK(cudaMemcpyFromSymbol(out16, g_wait_record, 16 * sizeof(int)));
+    int zero[16] = {0};
+    ZNN_CUDA_OK(cudaMemcpyToSymbol(g_wait_record, zero, sizeof(zero)));
+    return ZNN_OK;
+}
+
 int tc_profile_enable(int enable)
 {
     t_prof.on = (enable != 0);
@@ -1094,6 +1301,8 @@ static int launch_tc(const CUtensorMap* maps, const GemmTcParams& p, int batch)
 
 static thread_local int t_conv_mode = 1;
 void tc_set_conv_mode(int m) { t_conv_mode = m; }
+static thread_local bool t_persistent = true;
+void tc_set_persistent(int on) { t_persistent = (on != 0); }
 static thread_local bool t_splitk_enabled = true;
 void tc_set_splitk(int on) { t_splitk_enabled = (on != 0); }
 static thread_local int t_chunk_kblocks = 8;  // 256 contraction elements per tensor-memory accumulation
@@ -1234,7 +1443,7 @@ static int make_operand_map(CUtensorMap* tm, const float* X, bool mn_major, int 
 }
 
 template <int BN, bool A_MN, bool B_MN>
-static int launch_direct(const CUtensorMap& ma, const CUtensorMap& mb, const GemmTcParams& p, int batch)
+static int launch_direct(const CUtensorMap& ma, const CUtensorMap& mb, const GemmTcParams& p_in, int batch)
 {
     using Cfg = DirectCfg<BN>;
     static bool attr_set = false;
@@ -1243,9 +1452,12 @@ static int launch_direct(const CUtensorMap& ma, const CUtensorMap& mb, const Gem
         ZNN_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmemBytes));
         attr_set = true;
     }
-    const int splits = (p.k_blocks + p.kblocks_per_split - 1) / p.kblocks_per_split;
+    GemmTcParams p = p_in;
+    p.splits = (p.k_blocks + p.kblocks_per_split - 1) / p.kblocks_per_split;
+    p.batch = batch;
+    const long total_units = (long)p.tiles_m * p.tiles_n * p.splits * batch;
+    if (total_units > 0x3fffffffL) return fail(ZNN_ERR_INVALID, "too many output tiles (%ld)", total_units);
     cudaLaunchConfig_t cfg = {};
-    cfg.gridDim = dim3((unsigned)(p.tiles_m * p.tiles_n * 2), (unsigned)splits, (unsigned)batch);
     cfg.blockDim = dim3(kDirectThreads, 1, 1);
     cfg.dynamicSmemBytes = Cfg::kSmemBytes;
     cfg.stream = stream();
@@ -1256,6 +1468,22 @@ static int launch_direct(const CUtensorMap& ma, const CUtensorMap& mb, const Gem
     attr[0].val.clusterDim.z = 1;
     cfg.attrs = attr;
     cfg.numAttrs = 1;
+    // persistent: one CTA pair per pair of SMs that can hold one (asked of the driver once per device)
+    static int pairs_by_device[64] = {0};
+    int dev = 0;
+    ZNN_CUDA_OK(cudaGetDevice(&dev));
+    if (dev < 0 || dev >= 64) return fail(ZNN_ERR_INVALID, "device index %d out of range", dev);
+    if (pairs_by_device[dev] == 0) {
+        cfg.gridDim = dim3((unsigned)sm_count(), 1, 1);
+        int clusters = 0;
+        if (cudaOccupancyMaxActiveClusters(&clusters, kern, &cfg) != cudaSuccess || clusters < 1) {
+            cudaGetLastError();
+            clusters = sm_count() / 2;
+        }
+        pairs_by_device[dev] = clusters;
+    }
+    const long pairs = (!t_persistent || total_units < pairs_by_device[dev]) ? total_units : pairs_by_device[dev];
+    cfg.gridDim = dim3((unsigned)(2 * pairs), 1, 1);
     cudaEvent_t* ev = prof_begin(2.0 * p.M * (double)p.N * p.k_real * batch);
     ZNN_CUDA_OK(cudaLaunchKernelEx(&cfg, kern, ma, mb, p));
     prof_end(ev);
