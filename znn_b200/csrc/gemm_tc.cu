@@ -46,15 +46,18 @@ __device__ __forceinline__ void mbar_arrive_expect_tx(uint32_t bar, uint32_t byt
     asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
 }
 
+// The suspend-time hint lets the hardware park the thread until the phase completes (or the hint runs out) instead
+// of returning at once: waiting roles then leave the issue slots and the shared-memory port to the working warps.
+constexpr uint32_t kWaitSuspendNs = 20000;
 __device__ __forceinline__ uint32_t mbar_try_wait(uint32_t bar, uint32_t parity)
 {
     uint32_t ok;
     asm volatile(
         "{\n\t.reg .pred p;\n\t"
-        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
         "selp.u32 %0, 1, 0, p;\n\t}"
         : "=r"(ok)
-        : "r"(bar), "r"(parity)
+        : "r"(bar), "r"(parity), "r"(kWaitSuspendNs)
         : "memory");
     return ok;
 }
@@ -63,11 +66,17 @@ __device__ __forceinline__ uint32_t mbar_try_wait(uint32_t bar, uint32_t parity)
 __device__ __forceinline__ bool mbar_wait_bounded(uint32_t bar, uint32_t parity)
 {
     if (mbar_try_wait(bar, parity)) return true;
+#pragma unroll 1
+    for (int i = 0; i < 8; i++)
+        if (mbar_try_wait(bar, parity)) return true;
+    // a long wait: poll less often, so that waiting roles leave issue slots and the shared-memory port alone
     const uint64_t t0 = wait_clock();
     for (;;) {
 #pragma unroll 1
-        for (int i = 0; i < 128; i++)
+        for (int i = 0; i < 128; i++) {
             if (mbar_try_wait(bar, parity)) return true;
+            __nanosleep(128);
+        }
         if (wait_clock() - t0 > kWaitLimitCycles) return false;
     }
 }
@@ -628,10 +637,10 @@ __device__ __forceinline__ uint32_t mbar_try_wait_cluster(uint32_t bar, uint32_t
     uint32_t ok;
     asm volatile(
         "{\n\t.reg .pred p;\n\t"
-        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
         "selp.u32 %0, 1, 0, p;\n\t}"
         : "=r"(ok)
-        : "r"(bar), "r"(parity)
+        : "r"(bar), "r"(parity), "r"(kWaitSuspendNs)
         : "memory");
     return ok;
 }
@@ -639,11 +648,17 @@ __device__ __forceinline__ uint32_t mbar_try_wait_cluster(uint32_t bar, uint32_t
 __device__ __forceinline__ bool mbar_wait_bounded_cluster(uint32_t bar, uint32_t parity)
 {
     if (mbar_try_wait_cluster(bar, parity)) return true;
+#pragma unroll 1
+    for (int i = 0; i < 8; i++)
+        if (mbar_try_wait_cluster(bar, parity)) return true;
+    // a long wait: poll less often, so that waiting roles leave issue slots and the shared-memory port alone
     const uint64_t t0 = wait_clock();
     for (;;) {
 #pragma unroll 1
-        for (int i = 0; i < 128; i++)
+        for (int i = 0; i < 128; i++) {
             if (mbar_try_wait_cluster(bar, parity)) return true;
+            __nanosleep(128);
+        }
         if (wait_clock() - t0 > kWaitLimitCycles) return false;
     }
 }
