@@ -359,7 +359,7 @@ def run_gpu(args):
                          "frac": (achieved / peak) if achieved else None,
                          # bytes per launch from the ncu capture of this workload (profiles/gemm3x_direct_kernel_n8192_dram_traffic.md)
                          "traffic": 2.714e9 if (n == 8192 and last_path == 4) else None,
-                         "algorithmic_bytes_per_launch": (3 * nbytes + 4 * nbytes) / 3.0,
+                         "algorithmic_bytes_per_launch": (3 + 4 + 4) * nbytes / 3.0,
                          "kernel": ("gemm3x_direct_kernel<256,*,*> (operands read in place)" if last_path == 4
                                     else "gemm3x_tf32_kernel<256,2> (pre-split operand planes)"),
                          "launches": kl.value,
