@@ -204,6 +204,13 @@ def run_gpu(args):
         if world > 1:
             dist.destroy_process_group()
         return 0
+    if args.workload == "sweep":
+        if rank == 0:
+            print(json.dumps({"metric": "fp32_accurate_gemm_tflops_per_shape", "unit": "TFLOP/s", "n_gpus": 1,
+                              "data": "synthetic", "sweep": sweep_part(args, L, torch, stream)}), flush=True)
+        if world > 1:
+            dist.destroy_process_group()
+        return 0
     if args.workload == "rowops":
         if rank == 0:
             print(json.dumps({"metric": "rowop_hbm_bandwidth", "n_gpus": 1, "data": "synthetic",
@@ -564,6 +571,49 @@ def configs_part(args, L, torch, stream):
     return out
 
 
+def sweep_part(args, L, torch, stream):
+    """The MatMul operator sweep of the workload definition: square M=N=K in {512..8192} plus the two skinny shapes;
+    per shape the forward product (NN, beta 0) and both backward products (dA = dC.B^T, dB = A^T.dC, beta 1), each
+    timed alone with CUDA events after warm-up; operands are N(0,1).  Shapes of 2048 and below fit the 126 MB L2, so
+    their numbers are L2-resident rates (said in the output)."""
+    shapes = [(n, n, n) for n in (512, 1024, 2048, 4096, 8192)] + [(64, 4096, 4096), (4096, 64, 4096)]
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    g = torch.Generator(device="cuda").manual_seed(99)
+    out = []
+    for (M, N, K) in shapes:
+        A = torch.randn((M, K), device="cuda", generator=g)
+        B = torch.randn((K, N), device="cuda", generator=g)
+        dC = torch.randn((M, N), device="cuda", generator=g)
+        Cm = torch.empty((M, N), device="cuda")
+        dA, dB = torch.zeros((M, K), device="cuda"), torch.zeros((K, N), device="cuda")
+        calls = {
+            "fwd_NN": lambda: L.call("znn_sgemm", 101, 111, 111, M, N, K, 1.0, A.data_ptr(), K, B.data_ptr(), N, 0.0, Cm.data_ptr(), N),
+            "dA_NT": lambda: L.call("znn_sgemm", 101, 111, 112, M, K, N, 1.0, dC.data_ptr(), N, B.data_ptr(), N, 1.0, dA.data_ptr(), K),
+            "dB_TN": lambda: L.call("znn_sgemm", 101, 112, 111, K, N, M, 1.0, A.data_ptr(), K, dC.data_ptr(), N, 1.0, dB.data_ptr(), N),
+        }
+        flops = 2.0 * M * N * K
+        reps = max(5, min(200, int(2e12 / flops)))
+        row = {"M": M, "N": N, "K": K, "operand_MB": (M * K + K * N + M * N) * 4 / 1e6,
+               "l2_resident": (M * K + K * N + M * N) * 4 < 126e6}
+        for name, fn in calls.items():
+            for _ in range(3):
+                fn()
+            torch.cuda.synchronize()
+            e0.record(stream)
+            for _ in range(reps):
+                fn()
+            e1.record(stream)
+            torch.cuda.synchronize()
+            us = e0.elapsed_time(e1) * 1e3 / reps
+            row[name] = {"us": us, "tflops": flops / us / 1e6, "path": L.dll.znn_gemm_last_path()}
+        out.append(row)
+    st = C.c_int(0)
+    L.call("znn_device_status", C.byref(st), 1)
+    if st.value:
+        raise SystemExit(f"device status word {st.value}: a bounded device-side wait expired")
+    return out
+
+
 def shape_part(args, L, torch, stream):
     """One (batched) product at a given shape, timed alone with CUDA events: the small case for profiler captures."""
     M, N, K, ta, tb, batch = [int(v) for v in args.shape.split(",")]
@@ -683,7 +733,7 @@ def main():
     ap.add_argument("--shape", default="1024,64,1024,111,111,96",
                     help="--workload shape: M,N,K,trans_a,trans_b,batch of one (batched) product")
     ap.add_argument("--path", type=int, default=0, help="--workload shape: GEMM path (0 = automatic)")
-    ap.add_argument("--workload", default="all", choices=["all", "matmul", "gpt", "configs", "rowops", "shape"],
+    ap.add_argument("--workload", default="all", choices=["all", "matmul", "gpt", "configs", "rowops", "shape", "sweep"],
                     help="matmul: the headline MatMul sweep step only; all: also the GPT training step; "
                          "configs: the MLP / CNN / block / decode configs on one GPU")
     args = ap.parse_args()

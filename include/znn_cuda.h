@@ -90,6 +90,24 @@ int znn_sgemm_host(int order, int trans_a, int trans_b, int M, int N, int K, flo
  * zeroGrad).  panels as for znn_sgemm_host. */
 int znn_matmul_host_fwd_bwd(const float* A, const float* B, const float* dC, float* C, float* dA, float* dB,
                             int M, int K, int N, int accumulate, int panels);
+/* The same call with a hint about triangular structure, for the products around a causal softmax
+ * (src/nn.zig:835-906: S = Q.K^T -> mask -> softmax -> P.V).  The hint never changes a value the caller may read:
+ *   ZNN_TRI_C_LOWER  only the lower triangle of C (col <= row) will be read (S and dP feed the causal softmax, which
+ *                    never reads above the diagonal): output tiles entirely above it are neither computed nor written;
+ *   ZNN_TRI_A_LOWER  op(A)[m,k] is exactly 0 for k > m (P, dS as left operand): the contraction stops at the tile's last row;
+ *   ZNN_TRI_A_UPPER  op(A)[m,k] is exactly 0 for k < m (P^T, dS^T as left operand): it starts at the tile's first row;
+ *   ZNN_TRI_B_LOWER  op(B)[k,n] is exactly 0 for n > k (dS as right operand): it starts at the tile's first column.
+ * Skipped terms are products with exact zeros, so results equal the unhinted call (for finite operands).  Only the
+ * in-place tensor-core path uses the hint (whole 256-row / BN-column tiles); the other paths compute everything. */
+#define ZNN_TRI_NONE 0
+#define ZNN_TRI_C_LOWER 1
+#define ZNN_TRI_A_LOWER 2
+#define ZNN_TRI_A_UPPER 3
+#define ZNN_TRI_B_LOWER 4
+int znn_sgemm_batched_strided_tri(int trans_a, int trans_b, int M, int N, int K, float alpha,
+                                  const float* A, int lda, long long stride_a,
+                                  const float* B, int ldb, long long stride_b, float beta,
+                                  float* C, int ldc, long long stride_c, int batch, int tri);
 /* Fused form of Linear.forward = addBias(matmul(x, W), b) (src/nn.zig:44-51): Y[M,N] = X[M,K].W[K,N] + bias[N]
  * in one pass (the bias is added in the GEMM epilogue); an addition, the two separate ops remain.
  * Backward of the pair (src/autodiff.zig:593-641 and :652-672 chained): dX += dY.W^T, dW += X^T.dY,

@@ -226,3 +226,45 @@ def test_in_place_kernel_many_work_units_per_cta_pair(ops, ta, tb, M, N, K, batc
     want = 0.75 * (a64 @ b64) + beta * C0
     for b in range(batch):
         assert rel_err(got[b], want[b]) <= TOL, f"slice {b}"
+
+
+@pytest.mark.parametrize("T_,hd,batch", [(1024, 64, 3), (768, 64, 2), (520, 32, 2)])
+def test_triangular_hints_of_the_causal_attention_products(ops, T_, hd, batch):
+    """znn_sgemm_batched_strided_tri: the six products around a causal softmax with their structure hints give
+    what the unhinted products give wherever the result may be read (everything, except above the diagonal
+    for ZNN_TRI_C_LOWER)."""
+    r = np.random.default_rng(T_ + hd)
+    f32 = np.float32
+    Q, Kt = r.standard_normal((batch, T_, hd), f32), r.standard_normal((batch, hd, T_), f32)
+    V, dO = r.standard_normal((batch, T_, hd), f32), r.standard_normal((batch, T_, hd), f32)
+    low = np.tril(np.ones((T_, T_), f32))
+    P = (r.standard_normal((batch, T_, T_), f32) * low).astype(f32)      # lower-triangular, exact zeros above
+    dS = (r.standard_normal((batch, T_, T_), f32) * low).astype(f32)
+    ops.set_gemm_path(4)
+    try:
+        def both(ta, tb, M, N, K, A, B, beta, tri):
+            C0 = r.standard_normal((batch, M, N), f32)
+            lda, ldb = A.shape[2], B.shape[2]
+            full = ops.sgemm_batched(ta, tb, M, N, K, 1.0, A, lda, A[0].size, B, ldb, B[0].size, beta, C0.copy(), N, M * N, batch)
+            hint = ops.sgemm_batched_tri(ta, tb, M, N, K, 1.0, A, lda, A[0].size, B, ldb, B[0].size, beta, C0.copy(), N, M * N,
+                                         batch, tri)
+            assert ops.last_gemm_path() == 4
+            return full, hint
+        # S = Q.Kt: only the lower triangle is read
+        full, hint = both(NT, NT, T_, T_, hd, Q, Kt, 0.0, ops.TRI_C_LOWER)
+        assert rel_err(np.tril(hint), np.tril(full)) <= 1e-6
+        # O = P.V, dQ = dS.Kt^T: left operand lower-triangular
+        for (A, B, tb, N, beta) in ((P, V, NT, hd, 0.0), (dS, Kt, T, hd, 1.0)):
+            full, hint = both(NT, tb, T_, N, T_, A, B, beta, ops.TRI_A_LOWER)
+            assert rel_err(hint, full) <= 1e-6
+        # dP = dO.V^T accumulated: only the lower triangle is read
+        full, hint = both(NT, T, T_, T_, hd, dO, V, 1.0, ops.TRI_C_LOWER)
+        assert rel_err(np.tril(hint), np.tril(full)) <= 1e-6
+        # dV = P^T.dO: left operand upper-triangular after the transpose
+        full, hint = both(T, NT, T_, hd, T_, P, dO, 1.0, ops.TRI_A_UPPER)
+        assert rel_err(hint, full) <= 1e-6
+        # dKt = Q^T.dS: right operand lower-triangular
+        full, hint = both(T, NT, hd, T_, T_, Q, dS, 1.0, ops.TRI_B_LOWER)
+        assert rel_err(hint, full) <= 1e-6
+    finally:
+        ops.set_gemm_path(0)

@@ -219,3 +219,30 @@ def test_cuda_graph_replay_matches_eager(Model, kind, dims):
     assert losses[0] == losses[1]
     for k in finals[0]:
         np.testing.assert_array_equal(finals[0][k], finals[1][k])
+
+
+def test_gpt_causal_tile_skipping(Model):
+    """At a context long enough for several 256-wide tiles the six attention products run on the tensor cores with
+    triangular-structure hints (option causal_skip, default on): tiles above the causal diagonal are neither
+    computed nor stored, contractions stop where the probabilities are exact zeros.  Loss and every gradient
+    must equal the run without hints."""
+    cfg = {"vocab_size": 128, "block_size": 768, "n_embd": 128, "n_head": 2, "n_layer": 1}
+    dims = (128, 768, 128, 2, 1)
+    r = np.random.default_rng(8)
+    P0 = models.init_params("gpt", cfg, seed=9)
+    x = r.integers(0, 128, (2, 768)).astype(np.float32)
+    t = r.integers(0, 128, (2, 768)).astype(np.int32)
+    res = []
+    try:
+        for skip in (1, 0):
+            m = Model("gpt", dims, arena_bytes=1 << 30)
+            m.set_params(P0)
+            m.set_option("causal_skip", skip)
+            m.set_option("lr", 0.0)
+            res.append((m.train_step(x, t, seq=768), m.get_grads()))
+    finally:
+        m.set_option("causal_skip", 1)
+    assert abs(res[0][0] - res[1][0]) <= 1e-6 * abs(res[1][0])
+    floor = 1e-2 * grad_floor(res[1][1])
+    for k in res[0][1]:
+        relclose(res[0][1][k], res[1][1][k], 1e-5, k, floor)

@@ -15,7 +15,7 @@ bool gemm_tc_direct_eligible(const float* A, long long lda, long long stride_a, 
                              long long stride_b, int batch);
 int gemm_tc_direct(int ta, int tb, int M, int N, int K, float alpha, const float* A, long long lda, long long stride_a,
                    const float* B, long long ldb, long long stride_b, float beta, float* C, long long ldc,
-                   long long stride_c, int batch, const float* bias);
+                   long long stride_c, int batch, const float* bias, int tri);
 int launch_splitk_reduce(const float* partial, int splits, int M, int N, int batch, float alpha, float beta, float* C,
                          long long ldc, long long stride_c, const float* bias);
 int tc_profile_enable(int enable);
@@ -118,7 +118,7 @@ static thread_local int t_last_path = 0;  // taken by the last call
 // bias (optional, [N]) is added to every row of the result: the fused form of MatMul + AddBias
 static int gemm_dispatch(int ta, int tb, int M, int N, int K, float alpha, const float* A, long long lda,
                          long long stride_a, const float* B, long long ldb, long long stride_b, float beta, float* C,
-                         long long ldc, long long stride_c, int batch, const float* bias = nullptr)
+                         long long ldc, long long stride_c, int batch, const float* bias = nullptr, int tri = 0)
 {
     ZNN_REQUIRE(ta == ZNN_NO_TRANS || ta == ZNN_TRANS, "trans_a must be 111 or 112");
     ZNN_REQUIRE(tb == ZNN_NO_TRANS || tb == ZNN_TRANS, "trans_b must be 111 or 112");
@@ -159,7 +159,7 @@ static int gemm_dispatch(int ta, int tb, int M, int N, int K, float alpha, const
     t_last_path = path;
     if (path >= 2) {
         int rc = (path == 4) ? gemm_tc_direct(ta, tb, M, N, K, alpha, A, lda, stride_a, B, ldb, stride_b, beta, C, ldc,
-                                              stride_c, batch, bias)
+                                              stride_c, batch, bias, tri)
                              : gemm_tc(ta, tb, M, N, K, alpha, A, lda, stride_a, B, ldb, stride_b, beta, C, ldc, stride_c,
                                        batch, path == 2 ? 1 : 2, bias);
         // Debug aid (environment ZNN_GEMM_CHECK=1): wait for every tensor-core product and name the first one
@@ -231,6 +231,16 @@ int znn_sgemm_batched_strided(int trans_a, int trans_b, int M, int N, int K, flo
     ZNN_REQUIRE(batch <= 65535, "batch %d exceeds 65535", batch);
     return gemm_dispatch(trans_a, trans_b, M, N, K, alpha, A, lda, stride_a, B, ldb, stride_b, beta, C, ldc, stride_c,
                          batch);
+}
+
+int znn_sgemm_batched_strided_tri(int trans_a, int trans_b, int M, int N, int K, float alpha, const float* A, int lda,
+                                  long long stride_a, const float* B, int ldb, long long stride_b, float beta, float* C,
+                                  int ldc, long long stride_c, int batch, int tri)
+{
+    ZNN_REQUIRE(batch <= 65535, "batch %d exceeds 65535", batch);
+    ZNN_REQUIRE(tri >= ZNN_TRI_NONE && tri <= ZNN_TRI_B_LOWER, "tri must be one of ZNN_TRI_*");
+    return gemm_dispatch(trans_a, trans_b, M, N, K, alpha, A, lda, stride_a, B, ldb, stride_b, beta, C, ldc, stride_c,
+                         batch, nullptr, tri);
 }
 
 int znn_linear_fwd(const float* X, const float* W, const float* bias, float* Y, int M, int K, int N)

@@ -232,6 +232,7 @@ struct GemmTcParams {
     const float* bias;   // optional [N] vector added to every output row (fused AddBias), may be nullptr
     int tiles_m, tiles_n;
     int splits, batch;   // in-place kernel: work units = tiles_m * tiles_n * splits * batch
+    int tri;             // in-place kernel: triangular structure hint (ZNN_TRI_*), 0 = none; never combined with split-K
     float alpha, beta;
     float* C;
     long long ldc, stride_c;
@@ -724,6 +725,27 @@ struct DirectCfg {
     static_assert(kStageBytes % 1024 == 0, "stages must keep the 1 KB alignment of what follows");
 };
 
+// Triangular structure of a square (causal-attention) product, in whole tiles: which k-blocks the 256 x BN output
+// tile at (row0, col0) needs.  ZNN_TRI_C_LOWER: only tiles that touch the lower triangle (col <= row) are computed,
+// the others get no k-blocks and are not stored.  ZNN_TRI_A_LOWER: op(A)[m,k] = 0 for k > m, so k stops at the tile's
+// last row.  ZNN_TRI_A_UPPER: op(A)[m,k] = 0 for k < m, so k starts at the tile's first row.  ZNN_TRI_B_LOWER:
+// op(B)[k,n] = 0 for n > k, so k starts at the tile's first column.
+__device__ __forceinline__ void tri_k_range(const GemmTcParams& p, int row0, int col0, int& kb_first, int& kb_count)
+{
+    int lo = 0, hi = p.k_blocks;
+    if (p.tri == ZNN_TRI_C_LOWER) {
+        if (col0 > row0 + 2 * kTileM - 1) hi = 0;
+    } else if (p.tri == ZNN_TRI_A_LOWER) {
+        hi = min(hi, (row0 + 2 * kTileM + kBK - 1) / kBK);
+    } else if (p.tri == ZNN_TRI_A_UPPER) {
+        lo = min(hi, row0 / kBK);
+    } else if (p.tri == ZNN_TRI_B_LOWER) {
+        lo = min(hi, col0 / kBK);
+    }
+    kb_first = lo;
+    kb_count = hi - lo;
+}
+
 // One work unit = one 256 x BN output tile of one batch slice and one split-K slice.
 struct DirectUnit {
     int row0, col0, batch, split, kb_first, kb_count, nchunks;
@@ -751,13 +773,15 @@ __device__ __forceinline__ DirectUnit direct_unit(const GemmTcParams& p, int u, 
     d.col0 = tile_n * bn;
     d.kb_first = d.split * p.kblocks_per_split;
     d.kb_count = min(p.k_blocks - d.kb_first, p.kblocks_per_split);
+    if (p.tri) tri_k_range(p, tile_m * 2 * kTileM, d.col0, d.kb_first, d.kb_count);
     d.nchunks = (d.kb_count + p.chunk_kblocks - 1) / p.chunk_kblocks;
     return d;
 }
 
 // k-blocks of work unit u (all the converter warps need to know about it)
-__device__ __forceinline__ int direct_unit_kb_count(const GemmTcParams& p, int u)
+__device__ __forceinline__ int direct_unit_kb_count(const GemmTcParams& p, int u, int bn)
 {
+    if (p.tri) return direct_unit(p, u, 0, bn).kb_count;
     if (p.splits == 1) return p.k_blocks;
     const int split = (u / (p.tiles_m * p.tiles_n)) % p.splits;
     return min(p.k_blocks - split * p.kblocks_per_split, p.kblocks_per_split);
@@ -1035,7 +1059,7 @@ gemm3x_direct_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_cons
         bool got = true;
         uint32_t it = 0;
         for (int u = pair; u < total_units && got; u += npairs) {
-            const int kb_count = direct_unit_kb_count(p, u);
+            const int kb_count = direct_unit_kb_count(p, u, BN);
             for (int kb = 0; kb < kb_count; kb++, it++) {
                 if ((int)(it % kConvGroups) != group) continue;
                 const int s = it % S;
@@ -1126,6 +1150,7 @@ gemm3x_direct_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_cons
                 if (lane == 0) mbar_arrive_remote(acc_empty_leader0 + 8u * buf);
             }
             if (!got) break;
+            if (p.tri == ZNN_TRI_C_LOWER && d.kb_count == 0) continue;   // a tile above the diagonal: nobody reads it
             // split-K slices store their raw partial sums; a reduce kernel applies alpha/beta afterwards
             float* const out = to_partial ? p.partial + ((size_t)d.split * p.batch + d.batch) * (size_t)p.M * p.N
                                           : p.C + (size_t)d.batch * p.stride_c;
@@ -1526,11 +1551,15 @@ bool gemm_tc_direct_eligible(const float* A, long long lda, long long stride_a, 
 
 int gemm_tc_direct(int ta, int tb, int M, int N, int K, float alpha, const float* A, long long lda, long long stride_a,
                    const float* B, long long ldb, long long stride_b, float beta, float* C, long long ldc,
-                   long long stride_c, int batch, const float* bias)
+                   long long stride_c, int batch, const float* bias, int tri)
 {
     int* status = device_status_word();
     if (!status) return fail(ZNN_ERR_CUDA, "no device state (call znn_init first)");
-    const TcPlan pl = make_plan(M, N, K, batch, 2);
+    TcPlan pl = make_plan(M, N, K, batch, 2);
+    if (tri != 0 && pl.splits > 1) {   // the triangular k-ranges are per tile; no split-K on top of them
+        pl.splits = 1;
+        pl.kbps = ((pl.k_blocks + pl.chunk - 1) / pl.chunk) * pl.chunk;
+    }
     float* partial = nullptr;
     if (pl.splits > 1) {
         partial = (float*)workspace((size_t)pl.splits * batch * M * N * sizeof(float));
@@ -1549,6 +1578,7 @@ int gemm_tc_direct(int ta, int tb, int M, int N, int K, float alpha, const float
     p.bias = bias;
     p.tiles_m = pl.tiles_m;
     p.tiles_n = pl.tiles_n;
+    p.tri = tri;
     p.alpha = alpha; p.beta = beta; p.C = C; p.ldc = ldc; p.stride_c = stride_c; p.status = status;
     if (pl.bn == 256) rc = launch_direct_major<256>(a_mn, b_mn, ma, mb, p, batch);
     else if (pl.bn == 128) rc = launch_direct_major<128>(a_mn, b_mn, ma, mb, p, batch);

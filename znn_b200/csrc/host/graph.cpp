@@ -303,14 +303,18 @@ Tensor* Graph::linear(Tensor* X, Tensor* W, Tensor* bias)
     return Y;
 }
 
-Tensor* Graph::batchMatMul(Tensor* A, Tensor* B)
+Tensor* Graph::batchMatMul(Tensor* A, Tensor* B, int tri_role)
 {
     if (A->shape.len != 4 || B->shape.len != 4 || A->shape.dims[3] != B->shape.dims[2] ||
         A->shape.dims[0] != B->shape.dims[0] || A->shape.dims[1] != B->shape.dims[1])
         throw Error(ZNN_ERR_INVALID, "batchMatMul: need [b,h,M,K] x [b,h,K,N]");
     Tensor* C = new_tensor(Shape{A->shape.dims[0], A->shape.dims[1], A->shape.dims[2], B->shape.dims[3]},
                            any_grad({A, B}), false);
-    new_op(OpType::BatchMatMul, {A, B}, C)->forward();
+    if (tri_role != 0 && (tri_role < 0 || tri_role > 2 || A->shape.dims[2] != (tri_role == 1 ? B->shape.dims[3] : A->shape.dims[3])))
+        throw Error(ZNN_ERR_INVALID, "batchMatMul: a causal role needs square scores");
+    Op* op = new_op(OpType::BatchMatMul, {A, B}, C);
+    op->tri_role = tri_role;
+    op->forward();
     return C;
 }
 
@@ -402,8 +406,9 @@ void Op::forward()
         Tensor* B = inputs[1];
         const int nb = (int)(A->shape.dims[0] * A->shape.dims[1]);
         const int M = (int)A->shape.dims[2], K = (int)A->shape.dims[3], N = (int)B->shape.dims[3];
-        check(znn_sgemm_batched_strided(ZNN_NO_TRANS, ZNN_NO_TRANS, M, N, K, 1.0f, A->data, K, (long long)M * K, B->data, N,
-                                        (long long)K * N, 0.0f, C->data, N, (long long)M * N, nb),
+        const int tri = tri_role == 1 ? ZNN_TRI_C_LOWER : tri_role == 2 ? ZNN_TRI_A_LOWER : ZNN_TRI_NONE;
+        check(znn_sgemm_batched_strided_tri(ZNN_NO_TRANS, ZNN_NO_TRANS, M, N, K, 1.0f, A->data, K, (long long)M * K, B->data,
+                                            N, (long long)K * N, 0.0f, C->data, N, (long long)M * N, nb, tri),
               "BatchMatMul forward");
         break;
     }
@@ -526,13 +531,17 @@ void Op::backward()
         Tensor* B = inputs[1];
         const int nb = (int)(A->shape.dims[0] * A->shape.dims[1]);
         const int M = (int)A->shape.dims[2], K = (int)A->shape.dims[3], N = (int)B->shape.dims[3];
+        // role 1: C->grad = dS is lower-triangular (left operand of dA, right operand of dB);
+        // role 2: A->grad = dP is read below the diagonal only, and A^T = P^T is upper-triangular
+        const int tri_da = tri_role == 1 ? ZNN_TRI_A_LOWER : tri_role == 2 ? ZNN_TRI_C_LOWER : ZNN_TRI_NONE;
+        const int tri_db = tri_role == 1 ? ZNN_TRI_B_LOWER : tri_role == 2 ? ZNN_TRI_A_UPPER : ZNN_TRI_NONE;
         if (A->requires_grad)
-            check(znn_sgemm_batched_strided(ZNN_NO_TRANS, ZNN_TRANS, M, K, N, 1.0f, C->grad, N, (long long)M * N, B->data, N,
-                                            (long long)K * N, 1.0f, A->grad, K, (long long)M * K, nb),
+            check(znn_sgemm_batched_strided_tri(ZNN_NO_TRANS, ZNN_TRANS, M, K, N, 1.0f, C->grad, N, (long long)M * N, B->data,
+                                                N, (long long)K * N, 1.0f, A->grad, K, (long long)M * K, nb, tri_da),
                   "BatchMatMul backward dA");
         if (B->requires_grad)
-            check(znn_sgemm_batched_strided(ZNN_TRANS, ZNN_NO_TRANS, K, N, M, 1.0f, A->data, K, (long long)M * K, C->grad, N,
-                                            (long long)M * N, 1.0f, B->grad, N, (long long)K * N, nb),
+            check(znn_sgemm_batched_strided_tri(ZNN_TRANS, ZNN_NO_TRANS, K, N, M, 1.0f, A->data, K, (long long)M * K, C->grad,
+                                                N, (long long)M * N, 1.0f, B->grad, N, (long long)K * N, nb, tri_db),
                   "BatchMatMul backward dB");
         break;
     }

@@ -69,6 +69,7 @@ struct Op {
     int dim0 = 0, dim1 = 0;     // Transpose
     int pool = 0, stride = 0;   // MaxPool2D
     int pad = 0;                // Conv2D (0 = reference)
+    int tri_role = 0;           // BatchMatMul next to a causal softmax: 1 = C are the scores, 2 = A are the probabilities
     float* probs = nullptr;     // SoftmaxCrossEntropy: device M x N
     int32_t* targets = nullptr; // SoftmaxCrossEntropy: device int32 labels
     void forward();             // src/autodiff.zig:107-575
@@ -121,7 +122,10 @@ public:
     Tensor* maxpool2d(Tensor* A, int pool, int stride);                     // :2038
     Tensor* softmax(Tensor* A);                                             // :2068
     Tensor* rmsNorm(Tensor* X, Tensor* G, float eps);                       // :2098
-    Tensor* batchMatMul(Tensor* A, Tensor* B);                              // :2129
+    // tri_role (an addition): 1 = C = Q.K^T feeds a causal softmax (only its lower triangle is ever read, and its
+    // gradient is lower-triangular), 2 = A holds causal-softmax probabilities (lower-triangular); the products then
+    // skip the tiles the mask makes irrelevant (znn_sgemm_batched_strided_tri).  0 = the reference's full products.
+    Tensor* batchMatMul(Tensor* A, Tensor* B, int tri_role = 0);            // :2129
     Tensor* embedding(Tensor* W, Tensor* X);                                // :2160
     Tensor* causalSoftmax(Tensor* S, float scale);                          // fused addition
     Tensor* layerNorm(Tensor* X, Tensor* G, Tensor* B, float eps);          // extension

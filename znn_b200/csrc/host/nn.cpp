@@ -62,6 +62,10 @@ Linear::Linear(ParamStore& ps, const std::string& name, size_t in_features, size
     bias = ps.add(name + ".bias", Shape{1, out_features}, 0);
 }
 
+static bool g_causal_skip = true;
+void set_causal_skip(bool on) { g_causal_skip = on; }
+bool causal_skip() { return g_causal_skip; }
+
 static bool g_fused_linear = true;
 void set_fused_linear(bool on) { g_fused_linear = on; }
 bool fused_linear() { return g_fused_linear; }
@@ -135,7 +139,10 @@ Tensor* CausalSelfAttention::forward(Graph& g, Tensor* x) const
     Tensor* k = g.transposeND(k_4d, 1, 2);
     Tensor* v = g.transposeND(v_4d, 1, 2);
     Tensor* k_t = g.transposeND(k, 2, 3);
-    Tensor* att = g.batchMatMul(q, k_t);
+    // with the fused causal softmax nobody reads the scores above the diagonal, and the probabilities there are
+    // exact zeros: the two products and their four gradient products skip those tiles
+    const bool skip = fused_softmax && g_causal_skip;
+    Tensor* att = g.batchMatMul(q, k_t, skip ? 1 : 0);
     const float scale = 1.0f / sqrtf((float)hs);
     Tensor* att_sm;
     if (fused_softmax) {
@@ -150,7 +157,7 @@ Tensor* CausalSelfAttention::forward(Graph& g, Tensor* x) const
         Tensor* att_masked = g.add(att_scaled, mask_node);
         att_sm = g.softmax(att_masked);
     }
-    Tensor* y_4d = g.batchMatMul(att_sm, v);
+    Tensor* y_4d = g.batchMatMul(att_sm, v, skip ? 2 : 0);
     Tensor* y_trans = g.transposeND(y_4d, 1, 2);
     Tensor* y_3d = g.reshape(y_trans, Shape{B, T, C});
     Tensor* y_2d = g.reshape(y_3d, Shape{B * T, C});

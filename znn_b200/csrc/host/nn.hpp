@@ -45,6 +45,9 @@ private:
 };
 
 // Linear.forward runs the fused matmul+addBias op by default; false = the reference's two ops.
+// The attention products skip the tiles the causal mask makes irrelevant (only with fused_softmax); default on.
+void set_causal_skip(bool on);
+bool causal_skip();
 void set_fused_linear(bool on);
 bool fused_linear();
 

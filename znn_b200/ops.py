@@ -148,6 +148,20 @@ def sgemm_batched(ta, tb, M, N, K, alpha, A, lda, sa, B, ldb, sb, beta, Cm, ldc,
     return Cm
 
 
+TRI_NONE, TRI_C_LOWER, TRI_A_LOWER, TRI_A_UPPER, TRI_B_LOWER = 0, 1, 2, 3, 4
+
+
+def sgemm_batched_tri(ta, tb, M, N, K, alpha, A, lda, sa, B, ldb, sb, beta, Cm, ldc, sc, batch, tri):
+    """znn_sgemm_batched_strided_tri on host arrays (triangular-structure hint, see include/znn_cuda.h)."""
+    _ensure()
+    dA, dB, dC = _up(A), _up(B), _up(Cm)
+    lib().call("znn_sgemm_batched_strided_tri", ta, tb, M, N, K, alpha, dA.ptr, lda, sa, dB.ptr, ldb, sb, beta,
+               dC.ptr, ldc, sc, batch, tri)
+    check_device_status()
+    dC.into(Cm)
+    return Cm
+
+
 def matmul_fwd(A, B):
     A, B = _f(A), _f(B)
     M, K = A.shape
