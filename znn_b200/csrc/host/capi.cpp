@@ -464,6 +464,7 @@ int znn_model_set_option(znn_model* m, const char* key, double value)
         m->block.attn.fused_softmax = (value != 0.0);
     } else if (k == "fused_linear") set_fused_linear(value != 0.0);
     else if (k == "causal_skip") set_causal_skip(value != 0.0);
+    else if (k == "alias_reshape_grad") set_alias_reshape_grad(value != 0.0);
     else if (k == "cuda_graph") {
         m->use_graph = (value != 0.0);
         if (!m->use_graph) drop_graph(m);

@@ -185,6 +185,10 @@ Tensor* Graph::softmaxCrossEntropy(Tensor* logits, const int32_t* dev_targets)
     return loss;
 }
 
+static bool g_alias_reshape_grad = true;
+void set_alias_reshape_grad(bool on) { g_alias_reshape_grad = on; }
+bool alias_reshape_grad() { return g_alias_reshape_grad; }
+
 Tensor* Graph::reshape(Tensor* A, const Shape& new_shape)
 {
     if (new_shape.numel() != A->numel()) throw Error(ZNN_ERR_INVALID, "reshape: element counts differ");
@@ -194,8 +198,14 @@ Tensor* Graph::reshape(Tensor* A, const Shape& new_shape)
     C->requires_grad = A->requires_grad;
     C->data = A->data;  // shares the forward data (autodiff.zig:1346)
     if (A->requires_grad) {
-        C->grad = (float*)arena_->alloc(A->numel() * sizeof(float));
-        check(znn_memset(C->grad, 0, A->numel() * sizeof(float)), "znn_memset");
+        if (alias_reshape_grad()) {
+            // The view shares the gradient buffer too: every backward arm accumulates (+=), so consumers of the
+            // view add straight into the input's gradient and Reshape.backward has nothing left to add.
+            C->grad = A->grad;
+        } else {
+            C->grad = (float*)arena_->alloc(A->numel() * sizeof(float));   // own grad, as autodiff.zig:1347
+            check(znn_memset(C->grad, 0, A->numel() * sizeof(float)), "znn_memset");
+        }
     }
     tensors_.push_back(C);
     new_op(OpType::Reshape, {A}, C);
@@ -457,7 +467,7 @@ void Op::backward()
                   "SoftmaxCrossEntropy backward");
         break;
     case OpType::Reshape:
-        if (A->requires_grad) check(znn_accumulate(C->grad, A->grad, A->numel()), "Reshape backward");
+        if (A->requires_grad && C->grad != A->grad) check(znn_accumulate(C->grad, A->grad, A->numel()), "Reshape backward");
         break;
     case OpType::Transpose:
         if (A->requires_grad) {

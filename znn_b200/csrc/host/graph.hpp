@@ -76,6 +76,11 @@ struct Op {
     void backward();            // src/autodiff.zig:579-1231
 };
 
+// Reshape views share their input's gradient buffer (default on; off = a separate, zeroed gradient and an adding
+// backward arm as in src/autodiff.zig:1346-1347, :831-839).  The sums are the same; only their order differs.
+void set_alias_reshape_grad(bool on);
+bool alias_reshape_grad();
+
 // Device bump allocator: the analogue of Graph.arena (std.heap.ArenaAllocator).
 // reset() makes every allocation of the previous step reusable at once.
 class Arena {
