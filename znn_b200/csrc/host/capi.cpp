@@ -170,6 +170,7 @@ int znn_graph_read(znn_graph* g, int id, int which, float* host, size_t count)
     const float* src = which ? t->grad : t->data;
     if (!src) throw Error(ZNN_ERR_INVALID, "tensor has no gradient buffer (requires_grad is false)");
     if (count > t->numel()) throw Error(ZNN_ERR_INVALID, "read beyond the tensor");
+    if (which) ensure_grad(t);
     check(znn_memcpy_d2h(host, src, count * sizeof(float)), "znn_memcpy_d2h");
     ZNN_HOST_CATCH
 }
@@ -181,6 +182,7 @@ int znn_graph_write(znn_graph* g, int id, int which, const float* host, size_t c
     float* dst = which ? t->grad : t->data;
     if (!dst) throw Error(ZNN_ERR_INVALID, "tensor has no gradient buffer (requires_grad is false)");
     if (count > t->numel()) throw Error(ZNN_ERR_INVALID, "write beyond the tensor");
+    if (which) ensure_grad(t);
     check(znn_memcpy_h2d(dst, host, count * sizeof(float)), "znn_memcpy_h2d");
     check(znn_sync(), "znn_sync");
     ZNN_HOST_CATCH
@@ -465,6 +467,7 @@ int znn_model_set_option(znn_model* m, const char* key, double value)
     } else if (k == "fused_linear") set_fused_linear(value != 0.0);
     else if (k == "causal_skip") set_causal_skip(value != 0.0);
     else if (k == "alias_reshape_grad") set_alias_reshape_grad(value != 0.0);
+    else if (k == "lazy_zero_grad") set_lazy_zero_grad(value != 0.0);
     else if (k == "cuda_graph") {
         m->use_graph = (value != 0.0);
         if (!m->use_graph) drop_graph(m);
@@ -599,9 +602,13 @@ int znn_model_block_fwd_bwd(znn_model* m, const float* x, const float* dy, int B
     if (dy) {
         m->ps.zeroGrad();
         check(znn_memcpy_h2d(out->grad, dy, out->numel() * sizeof(float)), "upload dy");
+        mark_grad_written(out);
         check(znn_sync(), "znn_sync");
         g.backwardWithGrad(out);
-        if (dx) check(znn_memcpy_d2h(dx, xt->grad, xt->numel() * sizeof(float)), "read dx");
+        if (dx) {
+            ensure_grad(xt);
+            check(znn_memcpy_d2h(dx, xt->grad, xt->numel() * sizeof(float)), "read dx");
+        }
     }
     m->last_ops = (int)g.ops().size();
     ZNN_HOST_CATCH

@@ -91,6 +91,35 @@ Graph::~Graph()
     for (Op* o : ops_) delete o;
 }
 
+static bool g_lazy_zero_grad = true;
+void set_lazy_zero_grad(bool on) { g_lazy_zero_grad = on; }
+bool lazy_zero_grad() { return g_lazy_zero_grad; }
+
+static Tensor* grad_root(Tensor* t)
+{
+    while (t->grad_owner) t = t->grad_owner;
+    return t;
+}
+
+void ensure_grad(Tensor* t)
+{
+    if (!t->grad) return;
+    Tensor* r = grad_root(t);
+    if (r->grad_valid) return;
+    check(znn_memset(r->grad, 0, r->numel() * sizeof(float)), "znn_memset");
+    r->grad_valid = true;
+}
+
+bool claim_grad_overwrite(Tensor* t)
+{
+    Tensor* r = grad_root(t);
+    if (r->grad_valid) return false;
+    r->grad_valid = true;
+    return true;
+}
+
+void mark_grad_written(Tensor* t) { grad_root(t)->grad_valid = true; }
+
 Tensor* Graph::new_tensor(const Shape& shape, bool requires_grad, bool zero_data)
 {
     Tensor* t = new Tensor();
@@ -102,7 +131,8 @@ Tensor* Graph::new_tensor(const Shape& shape, bool requires_grad, bool zero_data
     if (zero_data) check(znn_memset(t->data, 0, bytes), "znn_memset");
     if (requires_grad) {
         t->grad = (float*)arena_->alloc(bytes);
-        check(znn_memset(t->grad, 0, bytes), "znn_memset");
+        if (g_lazy_zero_grad) t->grad_valid = false;
+        else check(znn_memset(t->grad, 0, bytes), "znn_memset");
     }
     tensors_.push_back(t);
     return t;
@@ -202,9 +232,11 @@ Tensor* Graph::reshape(Tensor* A, const Shape& new_shape)
             // The view shares the gradient buffer too: every backward arm accumulates (+=), so consumers of the
             // view add straight into the input's gradient and Reshape.backward has nothing left to add.
             C->grad = A->grad;
+            C->grad_owner = A;
         } else {
             C->grad = (float*)arena_->alloc(A->numel() * sizeof(float));   // own grad, as autodiff.zig:1347
-            check(znn_memset(C->grad, 0, A->numel() * sizeof(float)), "znn_memset");
+            if (g_lazy_zero_grad) C->grad_valid = false;
+            else check(znn_memset(C->grad, 0, A->numel() * sizeof(float)), "znn_memset");
         }
     }
     tensors_.push_back(C);
@@ -436,16 +468,26 @@ void Op::backward()
 {
     Tensor* A = inputs[0];
     Tensor* C = outputs[0];
+    // the upstream gradient is read: zero if no consumer wrote it
+    ensure_grad(C);
+    // arms that only add need a defined buffer; the GEMM arms below overwrite a fresh one instead (beta = 0)
+    const bool gemm_arm = type == OpType::MatMul || type == OpType::BatchMatMul || type == OpType::LinearBias;
+    if (!gemm_arm)
+        for (Tensor* in : inputs) ensure_grad(in);
     switch (type) {
     case OpType::MatMul: {
         Tensor* B = inputs[1];
         const int M = (int)A->shape.dims[0], K = (int)A->shape.dims[1], N = (int)B->shape.dims[1];
-        if (A->requires_grad)  // dA += dC . B^T (autodiff.zig:602-620)
-            check(znn_sgemm(ZNN_ROW_MAJOR, ZNN_NO_TRANS, ZNN_TRANS, M, K, N, 1.0f, C->grad, N, B->data, N, 1.0f, A->grad, K),
+        if (A->requires_grad) {  // dA += dC . B^T (autodiff.zig:602-620)
+            const float beta = claim_grad_overwrite(A) ? 0.0f : 1.0f;
+            check(znn_sgemm(ZNN_ROW_MAJOR, ZNN_NO_TRANS, ZNN_TRANS, M, K, N, 1.0f, C->grad, N, B->data, N, beta, A->grad, K),
                   "MatMul backward dA");
-        if (B->requires_grad)  // dB += A^T . dC (:623-640)
-            check(znn_sgemm(ZNN_ROW_MAJOR, ZNN_TRANS, ZNN_NO_TRANS, K, N, M, 1.0f, A->data, K, C->grad, N, 1.0f, B->grad, N),
+        }
+        if (B->requires_grad) {  // dB += A^T . dC (:623-640)
+            const float beta = claim_grad_overwrite(B) ? 0.0f : 1.0f;
+            check(znn_sgemm(ZNN_ROW_MAJOR, ZNN_TRANS, ZNN_NO_TRANS, K, N, M, 1.0f, A->data, K, C->grad, N, beta, B->grad, N),
                   "MatMul backward dB");
+        }
         break;
     }
     case OpType::AddBias:
@@ -531,10 +573,22 @@ void Op::backward()
     case OpType::LinearBias: {
         Tensor* W = inputs[1];
         Tensor* b = inputs[2];
-        check(znn_linear_bwd(A->data, W->data, C->grad, A->requires_grad ? A->grad : nullptr,
-                             W->requires_grad ? W->grad : nullptr, b->requires_grad ? b->grad : nullptr,
-                             (int)A->shape.dims[0], (int)A->shape.dims[1], (int)W->shape.dims[1]),
-              "Linear backward");
+        const int M = (int)A->shape.dims[0], K = (int)A->shape.dims[1], N = (int)W->shape.dims[1];
+        // znn_linear_bwd in pieces, so that a fresh dX is overwritten (beta = 0) instead of zero-filled and added to
+        if (b->requires_grad) {
+            ensure_grad(b);
+            check(znn_add_bias_bwd(C->grad, nullptr, b->grad, M, N), "Linear backward dbias");
+        }
+        if (A->requires_grad) {
+            const float beta = claim_grad_overwrite(A) ? 0.0f : 1.0f;
+            check(znn_sgemm(ZNN_ROW_MAJOR, ZNN_NO_TRANS, ZNN_TRANS, M, K, N, 1.0f, C->grad, N, W->data, N, beta, A->grad, K),
+                  "Linear backward dX");
+        }
+        if (W->requires_grad) {
+            const float beta = claim_grad_overwrite(W) ? 0.0f : 1.0f;
+            check(znn_sgemm(ZNN_ROW_MAJOR, ZNN_TRANS, ZNN_NO_TRANS, K, N, M, 1.0f, A->data, K, C->grad, N, beta, W->grad, N),
+                  "Linear backward dW");
+        }
         break;
     }
     case OpType::BatchMatMul: {
@@ -545,14 +599,19 @@ void Op::backward()
         // role 2: A->grad = dP is read below the diagonal only, and A^T = P^T is upper-triangular
         const int tri_da = tri_role == 1 ? ZNN_TRI_A_LOWER : tri_role == 2 ? ZNN_TRI_C_LOWER : ZNN_TRI_NONE;
         const int tri_db = tri_role == 1 ? ZNN_TRI_B_LOWER : tri_role == 2 ? ZNN_TRI_A_UPPER : ZNN_TRI_NONE;
-        if (A->requires_grad)
+        if (A->requires_grad) {
+            // (with ZNN_TRI_C_LOWER a fresh dP keeps undefined values above the diagonal, where nobody reads)
+            const float beta = claim_grad_overwrite(A) ? 0.0f : 1.0f;
             check(znn_sgemm_batched_strided_tri(ZNN_NO_TRANS, ZNN_TRANS, M, K, N, 1.0f, C->grad, N, (long long)M * N, B->data,
-                                                N, (long long)K * N, 1.0f, A->grad, K, (long long)M * K, nb, tri_da),
+                                                N, (long long)K * N, beta, A->grad, K, (long long)M * K, nb, tri_da),
                   "BatchMatMul backward dA");
-        if (B->requires_grad)
+        }
+        if (B->requires_grad) {
+            const float beta = claim_grad_overwrite(B) ? 0.0f : 1.0f;
             check(znn_sgemm_batched_strided_tri(ZNN_TRANS, ZNN_NO_TRANS, K, N, M, 1.0f, A->data, K, (long long)M * K, C->grad,
-                                                N, (long long)M * N, 1.0f, B->grad, N, (long long)K * N, nb, tri_db),
+                                                N, (long long)M * N, beta, B->grad, N, (long long)K * N, nb, tri_db),
                   "BatchMatMul backward dB");
+        }
         break;
     }
     case OpType::Embedding: {
@@ -605,6 +664,7 @@ void Graph::sweep(Tensor* root, const std::function<void(Op*)>* after_op)
 void Graph::backward(Tensor* loss, const std::function<void(Op*)>* after_op)
 {
     if (!loss->grad) throw Error(ZNN_ERR_INVALID, "backward: the loss tensor has no gradient buffer");
+    ensure_grad(loss);
     check(znn_fill(loss->grad, 1.0f, 1), "seed loss gradient");  // loss.grad[0] = 1 (autodiff.zig:2203)
     sweep(loss, after_op);
 }
@@ -619,7 +679,10 @@ void Graph::forward()
 void Graph::zeroGrad()
 {
     for (Tensor* t : tensors_)
-        if (t->grad) check(znn_memset(t->grad, 0, t->numel() * sizeof(float)), "znn_memset");
+        if (t->grad) {
+            check(znn_memset(t->grad, 0, t->numel() * sizeof(float)), "znn_memset");
+            mark_grad_written(t);
+        }
 }
 
 size_t Graph::op_index(const Op* op) const

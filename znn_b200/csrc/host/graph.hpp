@@ -49,8 +49,23 @@ struct Tensor {
     Shape shape, strides;
     bool requires_grad = false;
     Op* creator = nullptr;
+    // Gradient buffers of graph intermediates are zero-filled lazily: grad_valid is false until the first backward
+    // arm touches the buffer; an arm that overwrites the whole buffer (a GEMM with beta = 0) then needs no fill at all.
+    // A Reshape view that shares its input's buffer points at the owner, whose flag counts.
+    bool grad_valid = true;
+    Tensor* grad_owner = nullptr;
     size_t numel() const { return shape.numel(); }
 };
+
+// Zero-fills t's gradient buffer if nothing has written it yet (call before reading it or adding into it).
+void ensure_grad(Tensor* t);
+// For an arm that can overwrite the whole buffer: true = do so (the buffer then counts as written), false = add.
+bool claim_grad_overwrite(Tensor* t);
+// After the caller stored a complete gradient into the buffer.
+void mark_grad_written(Tensor* t);
+// Lazy zero-fill of intermediate gradients (default on; off = every gradient buffer is zero-filled when created).
+void set_lazy_zero_grad(bool on);
+bool lazy_zero_grad();
 
 // hot-path subset of src/autodiff.zig:14-40, plus two additions
 enum class OpType {
