@@ -157,6 +157,9 @@ int znn_relu_bwd(const float* A, const float* dC, float* dA, size_t n);
 /* Gelu (exact erf form): :156-165 / :699-716 */
 int znn_gelu_fwd(const float* A, float* C, size_t n);
 int znn_gelu_bwd(const float* A, const float* dC, float* dA, size_t n);
+/* the same gradient STORED into dA (an addition: for a gradient buffer nothing has been added to yet, it saves the
+ * zero fill and the read of the zeros) */
+int znn_gelu_bwd_set(const float* A, const float* dC, float* dA, size_t n);
 /* SoftmaxCrossEntropy: :196-238 / :758-774; probs is the M x N buffer the reference keeps in
  * OpContext; loss is one device float.  Targets are int32 (the reference's []const u8 cannot
  * hold a vocabulary above 255); the _u8 form takes the reference's type. */
@@ -189,6 +192,8 @@ int znn_softmax_bwd(const float* Y, const float* dY, float* dA, size_t rows, int
  * (src/autodiff.zig:1054-1076, :914-928, :895-904): dS += scale * P * (dP - sum(dP*P)). */
 int znn_causal_softmax_fwd(const float* S, float scale, float* P, int nslices, int T);
 int znn_causal_softmax_bwd(const float* P, const float* dP, float scale, float* dS, int nslices, int T);
+/* the same gradient STORED into dS, with zeros above the diagonal (an addition, as znn_gelu_bwd_set) */
+int znn_causal_softmax_bwd_set(const float* P, const float* dP, float scale, float* dS, int nslices, int T);
 /* RmsNorm: :462-484 / :1077-1116 */
 int znn_rmsnorm_fwd(const float* X, const float* G, float eps, float* Y, size_t rows, int D);
 int znn_rmsnorm_bwd(const float* X, const float* G, const float* dY, float eps, float* dX, float* dG, size_t rows, int D);

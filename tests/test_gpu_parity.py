@@ -67,6 +67,10 @@ def test_relu_gelu(ops, zo, n):
     ops.gelu_bwd(A, dC, g1)
     zo.gelu_bwd(A, dC, g2)
     close(g1, g2, what="gelu bwd")
+    g3, g4 = np.full(n, np.nan, np.float32), np.zeros(n, np.float32)   # the storing form ignores what the buffer held
+    ops.gelu_bwd_set(A, dC, g3)
+    zo.gelu_bwd(A, dC, g4)
+    close(g3, g4, what="gelu bwd (set)")
 
 
 @pytest.mark.parametrize("M,N", [(1, 2), (64, 10), (256, 10), (33, 255), (16, 8192), (5, 1000)])
@@ -128,6 +132,13 @@ def test_causal_softmax(ops, zo, ns, T):
     ops.causal_softmax_bwd(P2, dP, float(scale), d1)
     zo.causal_softmax_bwd(P2, dP, float(scale), d2)
     close(d1, d2, what="causal softmax bwd")
+    # the storing form: same gradient as adding into zeros, whatever the buffer held, zeros above the diagonal
+    d3 = np.full((ns, T, T), np.nan, np.float32)
+    ops.causal_softmax_bwd_set(P2, dP, float(scale), d3)
+    d4 = np.zeros((ns, T, T), np.float32)
+    zo.causal_softmax_bwd(P2, dP, float(scale), d4)
+    close(d3, d4, what="causal softmax bwd (set)")
+    assert np.all(d3[:, iu[0], iu[1]] == 0.0)
 
 
 @pytest.mark.parametrize("rows,D", [(1, 1), (2, 3), (64, 512), (100, 768), (7, 1001)])

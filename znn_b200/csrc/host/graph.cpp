@@ -471,8 +471,11 @@ void Op::backward()
     // the upstream gradient is read: zero if no consumer wrote it
     ensure_grad(C);
     // arms that only add need a defined buffer; the GEMM arms below overwrite a fresh one instead (beta = 0)
-    const bool gemm_arm = type == OpType::MatMul || type == OpType::BatchMatMul || type == OpType::LinearBias;
-    if (!gemm_arm)
+    // (so do Gelu, CausalSoftmax, Add, MulScalar, Reshape and Transpose, with a storing kernel or a plain copy)
+    const bool can_store = type == OpType::MatMul || type == OpType::BatchMatMul || type == OpType::LinearBias ||
+                           type == OpType::Gelu || type == OpType::CausalSoftmax || type == OpType::Add ||
+                           type == OpType::MulScalar || type == OpType::Reshape || type == OpType::Transpose;
+    if (!can_store)
         for (Tensor* in : inputs) ensure_grad(in);
     switch (type) {
     case OpType::MatMul: {
@@ -499,7 +502,10 @@ void Op::backward()
         if (A->requires_grad) check(znn_relu_bwd(A->data, C->grad, A->grad, A->numel()), "Relu backward");
         break;
     case OpType::Gelu:
-        if (A->requires_grad) check(znn_gelu_bwd(A->data, C->grad, A->grad, A->numel()), "Gelu backward");
+        if (A->requires_grad) {
+            if (claim_grad_overwrite(A)) check(znn_gelu_bwd_set(A->data, C->grad, A->grad, A->numel()), "Gelu backward");
+            else check(znn_gelu_bwd(A->data, C->grad, A->grad, A->numel()), "Gelu backward");
+        }
         break;
     case OpType::SoftmaxCrossEntropy:
         // ignores loss.grad and has no requires_grad gate, as the reference (:758-774); a logits
@@ -509,20 +515,32 @@ void Op::backward()
                   "SoftmaxCrossEntropy backward");
         break;
     case OpType::Reshape:
-        if (A->requires_grad && C->grad != A->grad) check(znn_accumulate(C->grad, A->grad, A->numel()), "Reshape backward");
+        if (A->requires_grad && C->grad != A->grad) {
+            if (claim_grad_overwrite(A)) check(znn_memcpy_d2d(A->grad, C->grad, A->numel() * sizeof(float)), "Reshape backward");
+            else check(znn_accumulate(C->grad, A->grad, A->numel()), "Reshape backward");
+        }
         break;
     case OpType::Transpose:
         if (A->requires_grad) {
             int64_t d[8];
-            check(znn_transpose_bwd(C->grad, A->grad, dims64(A->shape, d), (int)A->shape.len, dim0, dim1), "Transpose backward");
+            if (claim_grad_overwrite(A))   // a fresh gradient: the transpose of dC back, stored
+                check(znn_transpose_fwd(C->grad, A->grad, dims64(C->shape, d), (int)C->shape.len, dim0, dim1), "Transpose backward");
+            else
+                check(znn_transpose_bwd(C->grad, A->grad, dims64(A->shape, d), (int)A->shape.len, dim0, dim1), "Transpose backward");
         }
         break;
     case OpType::MulScalar:
-        if (A->requires_grad) check(znn_mul_scalar_bwd(C->grad, scalar, A->grad, A->numel()), "MulScalar backward");
+        if (A->requires_grad) {
+            if (claim_grad_overwrite(A)) check(znn_mul_scalar_fwd(C->grad, scalar, A->grad, A->numel()), "MulScalar backward");
+            else check(znn_mul_scalar_bwd(C->grad, scalar, A->grad, A->numel()), "MulScalar backward");
+        }
         break;
     case OpType::Add:
-        if (A->requires_grad) check(znn_accumulate(C->grad, A->grad, A->numel()), "Add backward");
-        if (inputs[1]->requires_grad) check(znn_accumulate(C->grad, inputs[1]->grad, A->numel()), "Add backward");
+        for (Tensor* in : {A, inputs[1]}) {
+            if (!in->requires_grad) continue;
+            if (claim_grad_overwrite(in)) check(znn_memcpy_d2d(in->grad, C->grad, A->numel() * sizeof(float)), "Add backward");
+            else check(znn_accumulate(C->grad, in->grad, A->numel()), "Add backward");
+        }
         break;
     case OpType::Conv2D: {
         Tensor* W = inputs[1];
@@ -549,8 +567,12 @@ void Op::backward()
     case OpType::CausalSoftmax:
         if (A->requires_grad) {
             const int T = (int)A->shape.dims[A->shape.len - 1];
-            check(znn_causal_softmax_bwd(C->data, C->grad, scalar, A->grad, (int)(A->numel() / ((size_t)T * T)), T),
-                  "CausalSoftmax backward");
+            if (claim_grad_overwrite(A))
+                check(znn_causal_softmax_bwd_set(C->data, C->grad, scalar, A->grad, (int)(A->numel() / ((size_t)T * T)), T),
+                      "CausalSoftmax backward");
+            else
+                check(znn_causal_softmax_bwd(C->data, C->grad, scalar, A->grad, (int)(A->numel() / ((size_t)T * T)), T),
+                      "CausalSoftmax backward");
         }
         break;
     case OpType::RmsNorm: {

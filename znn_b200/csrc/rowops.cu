@@ -143,6 +143,16 @@ struct GeluBwdF {
         return da + dc * (cdf + x * pdf);
     }
 };
+struct GeluBwdSetF {   // the same derivative, stored instead of added
+    __device__ float operator()(float x, float dc) const
+    {
+        const float sqrt_2 = 1.41421356237309504880f;
+        const float inv_sqrt_2pi = 0.3989422804014327f;
+        const float cdf = 0.5f * (1.0f + erff(x / sqrt_2));
+        const float pdf = inv_sqrt_2pi * expf(-0.5f * x * x);
+        return dc * (cdf + x * pdf);
+    }
+};
 struct AddF { __device__ float operator()(float a, float b) const { return a + b; } };
 struct AccF { __device__ float operator()(float s, float d) const { return d + s; } };
 struct MulF { float v; __device__ float operator()(float a) const { return a * v; } };
@@ -449,8 +459,9 @@ __global__ void softmax_rows_reg_kernel(const float* __restrict__ S, float scale
 }
 
 // dA += scale * Y * (dY - sum(dY*Y))   (scale = 1 for the plain Softmax op)
+// set = 1 stores the gradient (zeros beyond the causal limit) instead of adding it
 __global__ void softmax_rows_bwd_kernel(const float* __restrict__ Y, const float* __restrict__ dY, float scale,
-                                        float* __restrict__ dA, size_t rows, int D, int causal)
+                                        float* __restrict__ dA, size_t rows, int D, int causal, int set = 0)
 {
     const size_t row = blockIdx.x * (size_t)(blockDim.x >> 5) + (threadIdx.x >> 5);
     if (row >= rows) return;
@@ -462,7 +473,11 @@ __global__ void softmax_rows_bwd_kernel(const float* __restrict__ Y, const float
     float s = 0.0f;
     for (int j = lane; j < lim; j += 32) s += dy[j] * y[j];
     s = warp_sum(s);
-    for (int j = lane; j < lim; j += 32) da[j] += (y[j] * (dy[j] - s)) * scale;
+    if (!set) {
+        for (int j = lane; j < lim; j += 32) da[j] += (y[j] * (dy[j] - s)) * scale;
+    } else {
+        for (int j = lane; j < D; j += 32) da[j] = (j < lim) ? (y[j] * (dy[j] - s)) * scale : 0.0f;
+    }
 }
 
 // ---------------------------------------------------------------------------
@@ -877,6 +892,15 @@ int znn_gelu_bwd(const float* A, const float* dC, float* dA, size_t n)
     return ZNN_OK;
 }
 
+int znn_gelu_bwd_set(const float* A, const float* dC, float* dA, size_t n)
+{
+    if (n == 0 || !dA) return ZNN_OK;
+    ZNN_NEED_DEVICE();
+    ew2w_kernel<<<ew_blocks(n), kEwThreads, 0, stream()>>>(A, dC, dA, n, GeluBwdSetF());
+    ZNN_LAUNCH_OK("gelu_bwd_set");
+    return ZNN_OK;
+}
+
 }  // extern "C"
 
 template <class T>
@@ -977,6 +1001,16 @@ int znn_causal_softmax_bwd(const float* P, const float* dP, float scale, float* 
     const size_t rows = (size_t)nslices * T;
     softmax_rows_bwd_kernel<<<row_blocks(rows, 8), 256, 0, stream()>>>(P, dP, scale, dS, rows, T, 1);
     ZNN_LAUNCH_OK("causal softmax bwd");
+    return ZNN_OK;
+}
+
+int znn_causal_softmax_bwd_set(const float* P, const float* dP, float scale, float* dS, int nslices, int T)
+{
+    if (nslices <= 0 || T <= 0 || !dS) return ZNN_OK;
+    ZNN_NEED_DEVICE();
+    const size_t rows = (size_t)nslices * T;
+    softmax_rows_bwd_kernel<<<row_blocks(rows, 8), 256, 0, stream()>>>(P, dP, scale, dS, rows, T, 1, 1);
+    ZNN_LAUNCH_OK("causal softmax bwd (set)");
     return ZNN_OK;
 }
 

@@ -249,6 +249,11 @@ def gelu_bwd(A, dC, dA):
     _unary_bwd("znn_gelu_bwd", A, dC, dA)
 
 
+def gelu_bwd_set(A, dC, dA):
+    """Stores the gradient into dA (whatever it held) instead of adding it."""
+    _unary_bwd("znn_gelu_bwd_set", A, dC, dA)
+
+
 def softmax_xent_fwd(logits, targets, u8=False):
     _ensure()
     logits = _f(logits)
@@ -299,6 +304,15 @@ def causal_softmax_bwd(P, dP, scale, dS):
     T = P.shape[-1]
     p, g, o = _up(P), _up(dP), _up(dS)
     lib().call("znn_causal_softmax_bwd", p.ptr, g.ptr, scale, o.ptr, P.size // (T * T), T)
+    o.into(dS)
+
+
+def causal_softmax_bwd_set(P, dP, scale, dS):
+    """Stores the gradient into dS (zeros above the diagonal) instead of adding it."""
+    _ensure()
+    T = P.shape[-1]
+    p, g, o = _up(P), _up(dP), _up(dS)
+    lib().call("znn_causal_softmax_bwd_set", p.ptr, g.ptr, scale, o.ptr, P.size // (T * T), T)
     o.into(dS)
 
 
