@@ -1195,6 +1195,42 @@ __global__ void splitk_reduce_kernel(const float* __restrict__ partial, int spli
     }
 }
 
+// The same with 16-byte accesses (N, ldc, stride_c multiples of 4; C, bias 16-byte aligned); the slices are still
+// added in index order, eight loads in flight per thread.
+__global__ void splitk_reduce_vec_kernel(const float4* __restrict__ partial, int splits, int M, int N4, int batch, float alpha,
+                                         float beta, float* __restrict__ C, long long ldc, long long stride_c,
+                                         const float* __restrict__ bias)
+{
+    const size_t per4 = (size_t)M * N4;
+    const size_t total4 = per4 * batch;
+    for (size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x; i < total4; i += (size_t)gridDim.x * blockDim.x) {
+        float4 s = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+        for (int k0 = 0; k0 < splits; k0 += 8) {
+            float4 v[8];
+#pragma unroll
+            for (int k = 0; k < 8; k++)
+                if (k0 + k < splits) v[k] = partial[(size_t)(k0 + k) * total4 + i];
+#pragma unroll
+            for (int k = 0; k < 8; k++)
+                if (k0 + k < splits) { s.x += v[k].x; s.y += v[k].y; s.z += v[k].z; s.w += v[k].w; }
+        }
+        const size_t b = i / per4;
+        const unsigned rem = (unsigned)(i - b * per4);
+        const unsigned r = rem / (unsigned)N4, c = (rem - r * (unsigned)N4) * 4u;
+        float4* dst = reinterpret_cast<float4*>(C + b * stride_c + (size_t)r * ldc + c);
+        float4 o = make_float4(alpha * s.x, alpha * s.y, alpha * s.z, alpha * s.w);
+        if (bias) {
+            const float4 b4 = *reinterpret_cast<const float4*>(bias + c);
+            o.x += b4.x; o.y += b4.y; o.z += b4.z; o.w += b4.w;
+        }
+        if (beta != 0.0f) {
+            const float4 old = *dst;
+            o.x += beta * old.x; o.y += beta * old.y; o.z += beta * old.z; o.w += beta * old.w;
+        }
+        *dst = o;
+    }
+}
+
 // ---------------------------------------------------------------------------
 // host side
 // ---------------------------------------------------------------------------
@@ -1202,11 +1238,19 @@ int launch_splitk_reduce(const float* partial, int splits, int M, int N, int bat
                          long long ldc, long long stride_c, const float* bias)
 {
     const size_t total = (size_t)batch * M * N;
-    int blocks = (int)((total + 255) / 256);
+    const bool vec = (N & 3) == 0 && (ldc & 3) == 0 && (batch == 1 || (stride_c & 3) == 0) &&
+                     (reinterpret_cast<uintptr_t>(C) & 15) == 0 && (reinterpret_cast<uintptr_t>(bias) & 15) == 0 &&
+                     (reinterpret_cast<uintptr_t>(partial) & 15) == 0 && (size_t)M * (N / 4) < 0xffffffffull;
+    const size_t items = vec ? total / 4 : total;
+    int blocks = (int)((items + 255) / 256);
     const int cap = sm_count() * 16;
     if (blocks > cap) blocks = cap;
     if (blocks < 1) blocks = 1;
-    splitk_reduce_kernel<<<blocks, 256, 0, stream()>>>(partial, splits, M, N, batch, alpha, beta, C, ldc, stride_c, bias);
+    if (vec)
+        splitk_reduce_vec_kernel<<<blocks, 256, 0, stream()>>>(reinterpret_cast<const float4*>(partial), splits, M, N / 4, batch,
+                                                               alpha, beta, C, ldc, stride_c, bias);
+    else
+        splitk_reduce_kernel<<<blocks, 256, 0, stream()>>>(partial, splits, M, N, batch, alpha, beta, C, ldc, stride_c, bias);
     ZNN_LAUNCH_OK("splitk_reduce_kernel");
     return ZNN_OK;
 }
@@ -1359,6 +1403,16 @@ static TcPlan make_plan(int M, int N, int K, int batch, int ctas)
     pl.bn = 256;
     if (N <= 64) pl.bn = 64;
     else if (N <= 128) pl.bn = 128;
+    else if (ctas == 2) {
+        // Few tiles: with 256-wide tiles the last round of the persistent walk may be mostly empty (96 tiles on 74
+        // CTA pairs take two rounds).  128-wide tiles cost ~0.6 of a 256-wide one each (measured; shared-memory
+        // bound) and fill the rounds better; take them when rounds x cost comes out lower.
+        const long slots = sm_count() / 2;
+        const long tm = (M + 2 * kTileM - 1) / (2 * kTileM);
+        const long u256 = tm * ((N + 255) / 256) * batch, u128 = tm * ((N + 127) / 128) * batch;
+        const double c256 = (double)((u256 + slots - 1) / slots), c128 = 0.6 * (double)((u128 + slots - 1) / slots);
+        if (u256 >= slots && u256 < 4 * slots && c128 < c256) pl.bn = 128;
+    }
     const int tile_rows = kTileM * ctas;
     pl.tiles_m = (M + tile_rows - 1) / tile_rows;
     pl.tiles_n = (N + pl.bn - 1) / pl.bn;

@@ -216,13 +216,22 @@ __global__ void colsum_stage1_kernel(const float* __restrict__ dC, float* __rest
     }
 }
 
+// block = 32 columns x 8 lanes; lane y adds chunks y, y+8, ... in order, then the 8 lane sums are added in order
 __global__ void colsum_stage2_kernel(const float* __restrict__ partial, float* __restrict__ out, int chunks, int N)
 {
-    const int n = blockIdx.x * blockDim.x + threadIdx.x;
-    if (n >= N) return;
+    __shared__ float sh[8][33];
+    const int n = blockIdx.x * 32 + threadIdx.x;
     float t = 0.0f;
-    for (int c = 0; c < chunks; c++) t += partial[(size_t)c * N + n];
-    out[n] += t;
+    if (n < N)
+        for (int c = threadIdx.y; c < chunks; c += 8) t += partial[(size_t)c * N + n];
+    sh[threadIdx.y][threadIdx.x] = t;
+    __syncthreads();
+    if (threadIdx.y == 0 && n < N) {
+        float u = 0.0f;
+#pragma unroll
+        for (int y = 0; y < 8; y++) u += sh[y][threadIdx.x];
+        out[n] += u;
+    }
 }
 
 // same, for sum over rows of a[m,n] * b[m,n] * rowscale[m]  (RmsNorm / LayerNorm parameter gradients)
@@ -851,7 +860,7 @@ int znn_add_bias_bwd(const float* dC, float* dA, float* dbias, int M, int N)
     if (dA) colsum_stage1_kernel<true><<<grid, block, 0, stream()>>>(dC, dA, partial, M, N, rpc);
     else colsum_stage1_kernel<false><<<grid, block, 0, stream()>>>(dC, nullptr, partial, M, N, rpc);
     ZNN_LAUNCH_OK("colsum_stage1_kernel");
-    colsum_stage2_kernel<<<ceil_div(N, 128), 128, 0, stream()>>>(partial, dbias, chunks, N);
+    colsum_stage2_kernel<<<ceil_div(N, 32), dim3(32, 8), 0, stream()>>>(partial, dbias, chunks, N);
     ZNN_LAUNCH_OK("colsum_stage2_kernel");
     return ZNN_OK;
 }
@@ -1044,7 +1053,7 @@ int znn_rmsnorm_bwd(const float* X, const float* G, const float* dY, float eps, 
         dim3 grid(ceil_div(D, 32), chunks), block(32, 8);
         colsum_norm_stage1_kernel<0><<<grid, block, 0, stream()>>>(dY, X, rowscale, partial, (int)rows, D, rpc);
         ZNN_LAUNCH_OK("colsum_norm_stage1_kernel");
-        colsum_stage2_kernel<<<ceil_div(D, 128), 128, 0, stream()>>>(partial, dG, chunks, D);
+        colsum_stage2_kernel<<<ceil_div(D, 32), dim3(32, 8), 0, stream()>>>(partial, dG, chunks, D);
         ZNN_LAUNCH_OK("colsum_stage2_kernel");
     }
     return ZNN_OK;
@@ -1081,13 +1090,13 @@ int znn_layernorm_bwd(const float* X, const float* G, const float* dY, float eps
     if (dG) {
         colsum_norm_stage1_kernel<1><<<grid, block, 0, stream()>>>(dY, X, rowstat, partial, (int)rows, D, rpc);
         ZNN_LAUNCH_OK("colsum_norm_stage1_kernel");
-        colsum_stage2_kernel<<<ceil_div(D, 128), 128, 0, stream()>>>(partial, dG, chunks, D);
+        colsum_stage2_kernel<<<ceil_div(D, 32), dim3(32, 8), 0, stream()>>>(partial, dG, chunks, D);
         ZNN_LAUNCH_OK("colsum_stage2_kernel");
     }
     if (dB) {
         colsum_norm_stage1_kernel<2><<<grid, block, 0, stream()>>>(dY, X, rowstat, partial, (int)rows, D, rpc);
         ZNN_LAUNCH_OK("colsum_norm_stage1_kernel");
-        colsum_stage2_kernel<<<ceil_div(D, 128), 128, 0, stream()>>>(partial, dB, chunks, D);
+        colsum_stage2_kernel<<<ceil_div(D, 32), dim3(32, 8), 0, stream()>>>(partial, dB, chunks, D);
         ZNN_LAUNCH_OK("colsum_stage2_kernel");
     }
     return ZNN_OK;
