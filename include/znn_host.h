@@ -74,6 +74,8 @@ int znn_model_train_step(znn_model* m, const float* x, const int32_t* targets, i
 int znn_model_forward(znn_model* m, const float* x, int batch, int seq, int on_device, float* logits_host);
 /* transformer block: y = block(x); backward from dy; x,dy,y host arrays of B*T*n_embd; dx may be NULL */
 int znn_model_block_fwd_bwd(znn_model* m, const float* x, const float* dy, int B, int T, float* y, float* dx);
+/* the same with DEVICE arrays; asynchronous on the thread's stream */
+int znn_model_block_fwd_bwd_device(znn_model* m, const float* x, const float* dy, int B, int T, float* y, float* dx);
 /* greedy decode as examples/transformer_gpt.zig:116-146 (full re-forward per token over the last block_size ids,
  * first-maximum argmax), for `batch` prompts of prompt_len ids at once; out_ids: batch x n_new */
 int znn_model_greedy_decode(znn_model* m, const float* prompt_ids, int batch, int prompt_len, int n_new, float* out_ids);

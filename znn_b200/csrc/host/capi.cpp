@@ -614,6 +614,30 @@ int znn_model_block_fwd_bwd(znn_model* m, const float* x, const float* dy, int B
     ZNN_HOST_CATCH
 }
 
+int znn_model_block_fwd_bwd_device(znn_model* m, const float* x, const float* dy, int B, int T, float* y, float* dx)
+{
+    ZNN_HOST_TRY
+    if (m->kind != ZNN_MODEL_BLOCK) throw Error(ZNN_ERR_INVALID, "not a transformer block model");
+    m->arena->reset();
+    Graph g(m->arena.get());
+    const Shape s{(size_t)B, (size_t)T, m->in_features};
+    Tensor* xt = g.arrayFromDevice(s, x, dx != nullptr);
+    Tensor* out = m->block.forward(g, xt);
+    if (y) check(znn_memcpy_d2d(y, out->data, out->numel() * sizeof(float)), "copy y");
+    if (dy) {
+        m->ps.zeroGrad();
+        check(znn_memcpy_d2d(out->grad, dy, out->numel() * sizeof(float)), "copy dy");
+        mark_grad_written(out);
+        g.backwardWithGrad(out);
+        if (dx) {
+            ensure_grad(xt);
+            check(znn_memcpy_d2d(dx, xt->grad, xt->numel() * sizeof(float)), "copy dx");
+        }
+    }
+    m->last_ops = (int)g.ops().size();
+    ZNN_HOST_CATCH
+}
+
 int znn_model_greedy_decode(znn_model* m, const float* prompt_ids, int batch, int prompt_len, int n_new, float* out_ids)
 {
     ZNN_HOST_TRY

@@ -97,6 +97,10 @@ class Model:
         lib().call("znn_model_block_fwd_bwd", self.h, x.ctypes.data, dy.ctypes.data, B, T, y.ctypes.data, dx.ctypes.data)
         return y, dx
 
+    def block_fwd_bwd_device(self, x_ptr, dy_ptr, B, T, y_ptr, dx_ptr):
+        """Device pointers in and out; returns at once (work is queued on the thread's stream)."""
+        lib().call("znn_model_block_fwd_bwd_device", self.h, x_ptr, dy_ptr, B, T, y_ptr, dx_ptr)
+
     def greedy_decode(self, prompts, n_new):
         p = np.ascontiguousarray(prompts, np.float32)
         out = np.empty((p.shape[0], n_new), np.float32)
