@@ -567,12 +567,26 @@ def configs_part(args, L, torch, stream):
     m.greedy_decode(prompts, 2)
     torch.cuda.synchronize()
     e0.record(stream)
-    m.greedy_decode(prompts, n_new)
+    toks = m.greedy_decode(prompts, n_new)
     e1.record(stream)
     torch.cuda.synchronize()
     ms = e0.elapsed_time(e1)
     out["gpt_greedy_decode_b64"] = {"new_tokens": n_new, "tokens_per_s": 64 * n_new / (ms * 1e-3), "ms_total": ms,
                                     "note": "no KV cache: the reference re-runs the whole window per token"}
+    m.greedy_decode_kv(prompts, 2)
+    torch.cuda.synchronize()
+    e0.record(stream)
+    toks_kv = m.greedy_decode_kv(prompts, n_new)
+    e1.record(stream)
+    torch.cuda.synchronize()
+    ms = e0.elapsed_time(e1)
+    same = toks_kv == toks
+    # a sequence follows the reference's tokens up to its first differing pick (a near-tie of two logits)
+    first_diff = [int(np.argmin(row)) if not row.all() else n_new for row in same]
+    out["gpt_greedy_decode_b64_kv_cache"] = {"new_tokens": n_new, "tokens_per_s": 64 * n_new / (ms * 1e-3), "ms_total": ms,
+                                             "sequences_identical_to_full_reforward": int(sum(f == n_new for f in first_diff)),
+                                             "sequences": 64, "shortest_identical_prefix": int(min(first_diff)),
+                                             "note": "key/value cache: one pass per position; same operators"}
     m.close()
     return out
 

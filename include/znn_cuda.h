@@ -56,6 +56,8 @@ int znn_memset(void* ptr, int value, size_t bytes);
 int znn_memcpy_h2d(void* dst, const void* src, size_t bytes);   /* async on the stream */
 int znn_memcpy_d2h(void* dst, const void* src, size_t bytes);   /* waits for completion */
 int znn_memcpy_d2d(void* dst, const void* src, size_t bytes);
+/* rows x width_bytes between pitched device arrays (async on the stream); used to append K/V rows to a decode cache */
+int znn_memcpy2d_d2d(void* dst, size_t dst_pitch, const void* src, size_t src_pitch, size_t width_bytes, size_t rows);
 int znn_last_error(char* buf, size_t buflen);
 int znn_device_status(int* status, int clear); /* syncs, reads (and clears) the device status word */
 int znn_gemm_workspace_reserve(size_t bytes);  /* pre-size the GEMM scratch (avoids cudaMalloc later) */

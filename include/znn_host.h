@@ -79,6 +79,10 @@ int znn_model_block_fwd_bwd_device(znn_model* m, const float* x, const float* dy
 /* greedy decode as examples/transformer_gpt.zig:116-146 (full re-forward per token over the last block_size ids,
  * first-maximum argmax), for `batch` prompts of prompt_len ids at once; out_ids: batch x n_new */
 int znn_model_greedy_decode(znn_model* m, const float* prompt_ids, int batch, int prompt_len, int n_new, float* out_ids);
+/* The same tokens with a key/value cache (an addition: the reference re-runs the whole window per token): every position
+ * passes through the layers once.  Needs prompt_len + n_new - 1 <= block_size (no sliding window).  Logits agree with the
+ * full re-forward to GEMM rounding, so the greedy tokens are the same unless two logits tie within that rounding. */
+int znn_model_greedy_decode_kv(znn_model* m, const float* prompt_ids, int batch, int prompt_len, int n_new, float* out_ids);
 int znn_model_arena_high_water(znn_model* m, long long* bytes);
 int znn_model_last_step_ops(znn_model* m, int* n_ops);
 int znn_model_graph_replays(znn_model* m, long long* n);

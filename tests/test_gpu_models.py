@@ -246,3 +246,26 @@ def test_gpt_causal_tile_skipping(Model):
     floor = 1e-2 * grad_floor(res[1][1])
     for k in res[0][1]:
         relclose(res[0][1][k], res[1][1][k], 1e-5, k, floor)
+
+
+def test_kv_cache_decode_gives_the_same_tokens(Model):
+    """The key/value-cache decode (one pass per position) against the reference's full re-forward per token, both
+    on the GPU and against the oracle's tokens; window not sliding (prompt + new - 1 <= block_size)."""
+    cfg = {"vocab_size": 37, "block_size": 12, "n_embd": 16, "n_head": 2, "n_layer": 2}
+    P0 = models.init_params("gpt", cfg, seed=31)
+    r = np.random.default_rng(33)
+    prompts = r.integers(0, 37, (5, 4)).astype(np.float32)
+    m = Model("gpt", (37, 12, 16, 2, 2), arena_bytes=64 << 20)
+    m.set_params(P0)
+    full = m.greedy_decode(prompts, 9)
+    kv = m.greedy_decode_kv(prompts, 9)
+    np.testing.assert_array_equal(kv, full)
+    with pytest.raises(RuntimeError):
+        m.greedy_decode_kv(prompts, 10)           # would need the sliding window
+    # a longer context on the tensor-core paths: d_model 128, 2 heads of 64, 40 positions
+    cfg2 = {"vocab_size": 96, "block_size": 48, "n_embd": 128, "n_head": 2, "n_layer": 2}
+    P1 = models.init_params("gpt", cfg2, seed=5)
+    prompts2 = r.integers(0, 96, (8, 6)).astype(np.float32)
+    m2 = Model("gpt", (96, 48, 128, 2, 2), arena_bytes=256 << 20)
+    m2.set_params(P1)
+    np.testing.assert_array_equal(m2.greedy_decode_kv(prompts2, 40), m2.greedy_decode(prompts2, 40))

@@ -185,9 +185,12 @@ static int gemm_dispatch(int ta, int tb, int M, int N, int K, float alpha, const
     // partial tiles to scratch, fixed-order reduction
     const long tiles = (long)ceil_div(N, 64) * ceil_div(M, 64) * batch;
     int splits = 1;
-    if (tiles * 2 <= sm_count() && K >= 2048) {
+    if (tiles * 2 <= sm_count() && K >= 256) {
+        // slices of at least 64 contraction elements (128 once K is long): a 64-row product against a wide weight matrix
+        // (decode, the MLP layers) is a stream over the weights and needs every SM on it
+        const int min_slice = K >= 2048 ? 128 : 64;
         splits = (int)((2L * sm_count()) / tiles);
-        if (splits > K / 512) splits = K / 512;
+        if (splits > K / min_slice) splits = K / min_slice;
         if (splits > 128) splits = 128;
         if ((long)splits * batch > 65535) splits = 65535 / batch;
         if (splits < 1) splits = 1;

@@ -671,6 +671,93 @@ int znn_model_greedy_decode(znn_model* m, const float* prompt_ids, int batch, in
     ZNN_HOST_CATCH
 }
 
+// Greedy decode with a key/value cache: position p of every sequence goes through the layers once; its key and value
+// rows are appended to per-layer caches [batch, head, Tmax, hs] and its query attends to rows 0..p.  The arithmetic per
+// element is that of the full re-forward (same operators: Embedding, Add, RmsNorm, Linear, scaled dot products, row
+// softmax over the visible positions, GELU), so the logits agree to GEMM rounding and the greedy tokens are the same
+// unless two logits tie within that rounding.  No host synchronisation inside the loop: the picked ids stay on the device.
+int znn_model_greedy_decode_kv(znn_model* m, const float* prompt_ids, int batch, int prompt_len, int n_new, float* out_ids)
+{
+    ZNN_HOST_TRY
+    if (m->kind != ZNN_MODEL_GPT) throw Error(ZNN_ERR_INVALID, "not a GPT model");
+    const GPTConfig& cfg = m->gpt.cfg;
+    const size_t C = cfg.n_embd, nh = cfg.n_head, hs = C / nh, V = cfg.vocab_size, L = cfg.n_layer;
+    const size_t Tmax = (size_t)prompt_len + (size_t)n_new;
+    if (prompt_len < 1 || n_new < 1 || batch < 1) throw Error(ZNN_ERR_INVALID, "empty prompt, batch or request");
+    if (Tmax - 1 > cfg.block_size)
+        throw Error(ZNN_ERR_INVALID, "the key/value cache decode needs prompt_len + n_new - 1 <= block_size (the window must not slide)");
+    const size_t B = (size_t)batch;
+    m->arena->reset();
+    auto dev = [&](size_t n) { return (float*)m->arena->alloc(n * sizeof(float)); };
+    float* ids_all = dev(B * Tmax);           // [Tmax][B]: prompt ids, then the picked ids
+    float* posv = dev(B);
+    float *x = dev(B * C), *x1 = dev(B * C), *tmp = dev(B * C), *xn = dev(B * C);
+    float *q = dev(B * C), *k = dev(B * C), *v = dev(B * C), *y = dev(B * C);
+    float *att = dev(B * nh * Tmax), *prob = dev(B * nh * Tmax);
+    float *hid = dev(B * 4 * C), *act = dev(B * 4 * C), *logits = dev(B * V);
+    std::vector<float*> Kc(L), Vc(L);
+    for (size_t l = 0; l < L; l++) {
+        Kc[l] = dev(B * nh * Tmax * hs);
+        Vc[l] = dev(B * nh * Tmax * hs);
+    }
+    {   // prompt, transposed to [position][sequence]
+        std::vector<float> pt((size_t)prompt_len * B);
+        for (size_t b = 0; b < B; b++)
+            for (int t = 0; t < prompt_len; t++) pt[(size_t)t * B + b] = prompt_ids[b * prompt_len + t];
+        check(znn_memcpy_h2d(ids_all, pt.data(), pt.size() * sizeof(float)), "upload prompt");
+        check(znn_sync(), "znn_sync");
+    }
+    const float scale = 1.0f / sqrtf((float)hs);
+    auto linear = [&](const Linear& lin, const float* in, float* out, size_t K, size_t N) {
+        check(znn_linear_fwd(in, lin.weight->data, lin.bias->data, out, (int)B, (int)K, (int)N), "Linear");
+    };
+    for (size_t pos = 0; pos + 1 < Tmax; pos++) {
+        const float* ids = ids_all + pos * B;
+        check(znn_fill(posv, (float)pos, B), "positions");
+        check(znn_embedding_fwd(m->gpt.token_embedding.weight->data, ids, x, B, (int)C, (int)V), "token embedding");
+        check(znn_embedding_fwd(m->gpt.position_embedding.weight->data, posv, tmp, B, (int)C, (int)cfg.block_size), "position embedding");
+        check(znn_add_fwd(x, tmp, x1, B * C), "embedding sum");
+        std::swap(x, x1);
+        const int len = (int)pos + 1;
+        for (size_t l = 0; l < L; l++) {
+            const TransformerBlock& blk = m->gpt.h[l];
+            check(znn_rmsnorm_fwd(x, blk.ln_1.weight->data, blk.ln_1.eps, xn, B, (int)C), "ln_1");
+            linear(blk.attn.q_attn, xn, q, C, C);
+            linear(blk.attn.k_attn, xn, k, C, C);
+            linear(blk.attn.v_attn, xn, v, C, C);
+            // rows [b, h, pos, :] of the caches
+            check(znn_memcpy2d_d2d(Kc[l] + pos * hs, Tmax * hs * sizeof(float), k, hs * sizeof(float), hs * sizeof(float), B * nh), "K cache");
+            check(znn_memcpy2d_d2d(Vc[l] + pos * hs, Tmax * hs * sizeof(float), v, hs * sizeof(float), hs * sizeof(float), B * nh), "V cache");
+            // scores[b,h,0:len] = scale * q[b,h,:] . K[b,h,0:len,:]^T   (rows of `len` floats, packed)
+            check(znn_sgemm_batched_strided(ZNN_NO_TRANS, ZNN_TRANS, 1, len, (int)hs, scale, q, (int)hs, (long long)hs, Kc[l], (int)hs,
+                                            (long long)(Tmax * hs), 0.0f, att, len, (long long)len, (int)(B * nh)),
+                  "scores");
+            // softmax over the visible positions (the causal mask of the full forward leaves exactly these)
+            check(znn_softmax_fwd(att, prob, B * nh, len), "softmax");
+            check(znn_sgemm_batched_strided(ZNN_NO_TRANS, ZNN_NO_TRANS, 1, (int)hs, len, 1.0f, prob, len, (long long)len, Vc[l], (int)hs,
+                                            (long long)(Tmax * hs), 0.0f, y, (int)hs, (long long)hs, (int)(B * nh)),
+                  "P.V");
+            linear(blk.attn.c_proj, y, tmp, C, C);
+            check(znn_add_fwd(x, tmp, x1, B * C), "residual 1");
+            check(znn_rmsnorm_fwd(x1, blk.ln_2.weight->data, blk.ln_2.eps, xn, B, (int)C), "ln_2");
+            linear(blk.mlp.c_fc, xn, hid, C, 4 * C);
+            check(znn_gelu_fwd(hid, act, B * 4 * C), "gelu");
+            linear(blk.mlp.c_proj, act, tmp, 4 * C, C);
+            check(znn_add_fwd(x1, tmp, x, B * C), "residual 2");
+        }
+        if (pos + 1 >= (size_t)prompt_len) {   // the next position is a new token: pick it
+            check(znn_rmsnorm_fwd(x, m->gpt.ln_f.weight->data, m->gpt.ln_f.eps, xn, B, (int)C), "ln_f");
+            linear(m->gpt.lm_head, xn, logits, C, V);
+            check(znn_argmax(logits, ids_all + (pos + 1) * B, (int)B, (int)V, 1), "argmax");   // first maximum per row
+        }
+    }
+    std::vector<float> picked((size_t)n_new * B);
+    check(znn_memcpy_d2h(picked.data(), ids_all + (size_t)prompt_len * B, picked.size() * sizeof(float)), "read tokens");
+    for (size_t b = 0; b < B; b++)
+        for (int t = 0; t < n_new; t++) out_ids[b * n_new + t] = picked[(size_t)t * B + b];
+    ZNN_HOST_CATCH
+}
+
 int znn_model_arena_high_water(znn_model* m, long long* bytes)
 {
     ZNN_HOST_TRY

@@ -224,6 +224,13 @@ int znn_memcpy_d2d(void* dst, const void* src, size_t bytes)
     return ZNN_OK;
 }
 
+int znn_memcpy2d_d2d(void* dst, size_t dst_pitch, const void* src, size_t src_pitch, size_t width_bytes, size_t rows)
+{
+    if (width_bytes == 0 || rows == 0) return ZNN_OK;
+    ZNN_CUDA_OK(cudaMemcpy2DAsync(dst, dst_pitch, src, src_pitch, width_bytes, rows, cudaMemcpyDeviceToDevice, stream()));
+    return ZNN_OK;
+}
+
 int znn_last_error(char* buf, size_t buflen)
 {
     ZNN_REQUIRE(buf && buflen > 0, "buf is NULL");

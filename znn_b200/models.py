@@ -107,6 +107,13 @@ class Model:
         lib().call("znn_model_greedy_decode", self.h, p.ctypes.data, p.shape[0], p.shape[1], n_new, out.ctypes.data)
         return out
 
+    def greedy_decode_kv(self, prompts, n_new):
+        """Greedy decode with a key/value cache (same tokens as greedy_decode while the window does not slide)."""
+        p = np.ascontiguousarray(prompts, np.float32)
+        out = np.empty((p.shape[0], n_new), np.float32)
+        lib().call("znn_model_greedy_decode_kv", self.h, p.ctypes.data, p.shape[0], p.shape[1], n_new, out.ctypes.data)
+        return out
+
     def graph_replays(self):
         n = C.c_longlong()
         lib().call("znn_model_graph_replays", self.h, C.byref(n))
