@@ -137,6 +137,10 @@ int znn_gemm_set_conv_mode(int mode);
 /* In-place path only: 1 (default) = persistent launch (one CTA pair per SM pair walks the output tiles, so the
  * next tile's main loop overlaps the previous tile's epilogue); 0 = one CTA pair per output tile. */
 int znn_gemm_set_persistent(int enable);
+/* In-place path only: 1 (default) = when the last round of the persistent walk would be less than 70 % full, its tiles
+ * are cut into K-slices (whole accumulation chunks) run by otherwise idle CTA pairs; the slices' partial tiles are added
+ * in slice order by a small second kernel (deterministic).  0 = every tile is one unit. */
+int znn_gemm_set_tail_split(int enable);
 /* Diagnostic: where the first bounded device-side wait of a tensor-core GEMM expired since the last call (16 ints:
  * claimed flag, role, barrier, work unit, counter, M, N, K, split-K slices, tile width, CTA rank, CTA pair, units,
  * pairs, beta*1000, batch); all zero when none did.  Reading clears the record. */

@@ -268,3 +268,30 @@ def test_triangular_hints_of_the_causal_attention_products(ops, T_, hd, batch):
         assert rel_err(hint, full) <= 1e-6
     finally:
         ops.set_gemm_path(0)
+
+
+def test_persistent_and_per_tile_launch_give_the_same_bits(ops):
+    """znn_gemm_set_persistent: the persistent walk and one CTA pair per tile run the same arithmetic per element;
+    and no bounded device-side wait expired anywhere in this module (znn_gemm_wait_record stays all zero)."""
+    import ctypes as C
+    from znn_b200._lib import lib
+    r = np.random.default_rng(77)
+    M, N, K = 1536, 1280, 640
+    A, B = r.standard_normal((M, K), np.float32), r.standard_normal((K, N), np.float32)
+    C0 = r.standard_normal((M, N), np.float32)
+    res = []
+    ops.set_gemm_path(4)
+    try:
+        for pers in (1, 0):
+            lib().call("znn_gemm_set_persistent", pers)
+            got = C0.copy()
+            ops.sgemm(NT, NT, M, N, K, 1.0, A, K, B, N, 1.0, got, N)
+            assert ops.last_gemm_path() == 4
+            res.append(got)
+    finally:
+        lib().call("znn_gemm_set_persistent", 1)
+        ops.set_gemm_path(0)
+    np.testing.assert_array_equal(res[0], res[1])
+    rec = (C.c_int * 16)()
+    lib().call("znn_gemm_wait_record", rec)
+    assert list(rec) == [0] * 16

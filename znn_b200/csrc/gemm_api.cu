@@ -22,6 +22,7 @@ int tc_profile_enable(int enable);
 void tc_set_chunk_kblocks(int v);
 void tc_set_splitk(int on);
 void tc_set_persistent(int on);
+void tc_set_tail_split(int on);
 int tc_wait_record(int* out16);
 void tc_set_conv_mode(int m);
 int tc_profile_read(double* kernel_ms, long long* launches, double* flops);
@@ -292,6 +293,12 @@ int znn_gemm_wait_record(int* out16)
 int znn_gemm_set_persistent(int enable)
 {
     tc_set_persistent(enable);
+    return ZNN_OK;
+}
+
+int znn_gemm_set_tail_split(int enable)
+{
+    tc_set_tail_split(enable);
     return ZNN_OK;
 }
 

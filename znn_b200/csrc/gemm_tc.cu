@@ -233,6 +233,11 @@ struct GemmTcParams {
     int tiles_m, tiles_n;
     int splits, batch;   // in-place kernel: work units = tiles_m * tiles_n * splits * batch
     int tri;             // in-place kernel: triangular structure hint (ZNN_TRI_*), 0 = none; never combined with split-K
+    // in-place kernel, tail split: work units from tail_first on are the tiles of the last, partly filled round of the
+    // persistent walk, each cut into tail_slices K-slices of tail_kbps k-blocks whose raw 256 x BN partial tiles go to
+    // tail_partial[unit - tail_first]; a small kernel adds the slices in order.  tail_first = number of units when off.
+    int tail_first, tail_slices, tail_kbps;
+    float* tail_partial;
     float alpha, beta;
     float* C;
     long long ldc, stride_c;
@@ -753,9 +758,16 @@ struct DirectUnit {
 
 __device__ __forceinline__ DirectUnit direct_unit(const GemmTcParams& p, int u, int cta_rank, int bn)
 {
+    int slice = -1;
+    int uu = u;
+    if (u >= p.tail_first) {   // a K-slice of one of the last round's tiles
+        const int sub = u - p.tail_first;
+        uu = p.tail_first + sub / p.tail_slices;
+        slice = sub - (uu - p.tail_first) * p.tail_slices;
+    }
     const int units_per = p.tiles_m * p.tiles_n;
-    const int t = u % units_per;
-    const int sb = u / units_per;
+    const int t = uu % units_per;
+    const int sb = uu / units_per;
     DirectUnit d;
     d.split = sb % p.splits;
     d.batch = sb / p.splits;
@@ -774,6 +786,10 @@ __device__ __forceinline__ DirectUnit direct_unit(const GemmTcParams& p, int u, 
     d.kb_first = d.split * p.kblocks_per_split;
     d.kb_count = min(p.k_blocks - d.kb_first, p.kblocks_per_split);
     if (p.tri) tri_k_range(p, tile_m * 2 * kTileM, d.col0, d.kb_first, d.kb_count);
+    if (slice >= 0) {
+        d.kb_first = slice * p.tail_kbps;
+        d.kb_count = min(p.k_blocks - d.kb_first, p.tail_kbps);
+    }
     d.nchunks = (d.kb_count + p.chunk_kblocks - 1) / p.chunk_kblocks;
     return d;
 }
@@ -782,6 +798,10 @@ __device__ __forceinline__ DirectUnit direct_unit(const GemmTcParams& p, int u, 
 __device__ __forceinline__ int direct_unit_kb_count(const GemmTcParams& p, int u, int bn)
 {
     if (p.tri) return direct_unit(p, u, 0, bn).kb_count;
+    if (u >= p.tail_first) {
+        const int slice = (u - p.tail_first) % p.tail_slices;
+        return min(p.k_blocks - slice * p.tail_kbps, p.tail_kbps);
+    }
     if (p.splits == 1) return p.k_blocks;
     const int split = (u / (p.tiles_m * p.tiles_n)) % p.splits;
     return min(p.k_blocks - split * p.kblocks_per_split, p.kblocks_per_split);
@@ -937,7 +957,8 @@ gemm3x_direct_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_cons
     const int cta_rank = (int)cluster_ctarank();
     const bool leader = (cta_rank == 0);
     const int pair = blockIdx.x >> 1, npairs = gridDim.x >> 1;
-    const int total_units = p.tiles_m * p.tiles_n * p.splits * p.batch;
+    const int base_units = p.tiles_m * p.tiles_n * p.splits * p.batch;
+    const int total_units = p.tail_first + (base_units - p.tail_first) * p.tail_slices;
     const int chunk = p.chunk_kblocks;
 
     if (threadIdx.x == 0) {
@@ -1152,6 +1173,13 @@ gemm3x_direct_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_cons
             if (!got) break;
             if (p.tri == ZNN_TRI_C_LOWER && d.kb_count == 0) continue;   // a tile above the diagonal: nobody reads it
             // split-K slices store their raw partial sums; a reduce kernel applies alpha/beta afterwards
+            if (u >= p.tail_first) {
+                // a K-slice of a last-round tile: the raw 256 x BN partial tile, packed, to its own slot
+                float* const slot = p.tail_partial + (size_t)(u - p.tail_first) * (size_t)(2 * kTileM * BN);
+                epilogue_store_vec<CPT>(acc, stage, lane, cta_rank * kTileM + q * 32, half * CPT, 2 * kTileM, BN, slot, BN, 1.0f,
+                                        0.0f, nullptr);
+                continue;
+            }
             float* const out = to_partial ? p.partial + ((size_t)d.split * p.batch + d.batch) * (size_t)p.M * p.N
                                           : p.C + (size_t)d.batch * p.stride_c;
             const bool vec_ok = ((out_ld & 3) == 0) && ((reinterpret_cast<uintptr_t>(out) & 15) == 0) &&
@@ -1228,6 +1256,58 @@ __global__ void splitk_reduce_vec_kernel(const float4* __restrict__ partial, int
             o.x += beta * old.x; o.y += beta * old.y; o.z += beta * old.z; o.w += beta * old.w;
         }
         *dst = o;
+    }
+}
+
+// Adds the K-slices of the last-round tiles (tail split of the in-place kernel) in slice order and applies
+// alpha / beta / bias: C[tile] = alpha * sum_s partial[tile][s] + bias + beta * C[tile].  One block row per tile.
+template <int BN>
+__global__ void tail_reduce_kernel(const GemmTcParams p)
+{
+    const int j = blockIdx.y;                      // which tail tile
+    __shared__ DirectUnit sd;
+    if (threadIdx.x == 0) sd = direct_unit(p, p.tail_first + j * p.tail_slices, 0, BN);   // slice 0: the tile's coordinates
+    __syncthreads();
+    const DirectUnit d = sd;
+    constexpr int kElems = 2 * kTileM * BN;
+    const float4* base = reinterpret_cast<const float4*>(p.tail_partial + (size_t)j * p.tail_slices * (size_t)kElems);
+    float* const Cb = p.C + (size_t)d.batch * p.stride_c;
+    const bool vec = ((p.ldc & 3) == 0) && ((reinterpret_cast<uintptr_t>(Cb) & 15) == 0) &&
+                     ((reinterpret_cast<uintptr_t>(p.bias) & 15) == 0);
+    const int e4 = blockIdx.x * blockDim.x + threadIdx.x;     // one float4 of the tile per thread
+    if (e4 >= kElems / 4) return;
+    const int r = e4 / (BN / 4), c = (e4 - r * (BN / 4)) * 4;
+    const int row = d.row0 + r, col = d.col0 + c;
+    if (row >= p.M || col >= p.N) return;
+    float4 sum = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+    float4 v[8];
+#pragma unroll
+    for (int sl = 0; sl < 8; sl++)
+        if (sl < p.tail_slices) v[sl] = base[(size_t)sl * (kElems / 4) + e4];
+#pragma unroll
+    for (int sl = 0; sl < 8; sl++)
+        if (sl < p.tail_slices) { sum.x += v[sl].x; sum.y += v[sl].y; sum.z += v[sl].z; sum.w += v[sl].w; }
+    float o[4] = {p.alpha * sum.x, p.alpha * sum.y, p.alpha * sum.z, p.alpha * sum.w};
+    float* dst = Cb + (size_t)row * p.ldc + col;
+    if (vec && col + 3 < p.N) {
+        if (p.bias) {
+            const float4 b4 = *reinterpret_cast<const float4*>(p.bias + col);
+            o[0] += b4.x; o[1] += b4.y; o[2] += b4.z; o[3] += b4.w;
+        }
+        if (p.beta != 0.0f) {
+            const float4 old = *reinterpret_cast<const float4*>(dst);
+            o[0] += p.beta * old.x; o[1] += p.beta * old.y; o[2] += p.beta * old.z; o[3] += p.beta * old.w;
+        }
+        *reinterpret_cast<float4*>(dst) = make_float4(o[0], o[1], o[2], o[3]);
+    } else {
+#pragma unroll
+        for (int e = 0; e < 4; e++) {
+            if (col + e >= p.N) break;
+            float t = o[e];
+            if (p.bias) t += p.bias[col + e];
+            if (p.beta != 0.0f) t += p.beta * dst[e];
+            dst[e] = t;
+        }
     }
 }
 
@@ -1385,6 +1465,8 @@ static int launch_tc(const CUtensorMap* maps, const GemmTcParams& p, int batch)
 
 static thread_local int t_conv_mode = 1;
 void tc_set_conv_mode(int m) { t_conv_mode = m; }
+static thread_local bool t_tail_split = true;
+void tc_set_tail_split(int on) { t_tail_split = (on != 0); }
 static thread_local bool t_persistent = true;
 void tc_set_persistent(int on) { t_persistent = (on != 0); }
 static thread_local bool t_splitk_enabled = true;
@@ -1397,7 +1479,39 @@ struct TcPlan {
     int bn, tiles_m, tiles_n, k_blocks, chunk, splits, kbps;
 };
 
-static TcPlan make_plan(int M, int N, int K, int batch, int ctas)
+// Tail split of the persistent walk: `units` tiles on `slots` CTA pairs; when the last round would be less than 70 %
+// full its tiles are cut into K-slices (whole chunks, at most 8) so that the round costs 1/slices.  Returns the number
+// of slices (1 = no split) and the k-blocks per slice.
+static int tail_slices_for(long units, long slots, int k_blocks, int chunk, int* kbps_out)
+{
+    *kbps_out = k_blocks;
+    const long rounds = units / slots, tail = units % slots;
+    if (rounds < 1 || tail == 0 || tail * 10 >= slots * 7) return 1;
+    long s = slots / tail;
+    const long by_k = k_blocks / chunk;
+    if (s > by_k) s = by_k;
+    if (s > 8) s = 8;
+    if (s < 2) return 1;
+    int kbps = (int)((k_blocks + s - 1) / s);
+    kbps = ((kbps + chunk - 1) / chunk) * chunk;
+    const int eff = (k_blocks + kbps - 1) / kbps;
+    if (eff < 2) return 1;
+    *kbps_out = kbps;
+    return eff;
+}
+
+// rounds of the walk in units of one tile's time (the tail round costs 1/slices plus the small reduce pass)
+static double plan_rounds(long units, long slots, int k_blocks, int chunk, bool tail_ok)
+{
+    const long rounds = units / slots, tail = units % slots;
+    if (tail == 0) return (double)rounds;
+    int kbps;
+    const int s = tail_ok ? tail_slices_for(units, slots, k_blocks, chunk, &kbps) : 1;
+    // a slice pays the pipeline fill again (~6 k-blocks' worth) and the reduce pass another ~4
+    return (double)rounds + (s > 1 ? ((double)kbps + 10.0) / ((double)k_blocks + 6.0) : 1.0);
+}
+
+static TcPlan make_plan(int M, int N, int K, int batch, int ctas, bool tail_ok = false)
 {
     TcPlan pl;
     pl.bn = 256;
@@ -1406,11 +1520,13 @@ static TcPlan make_plan(int M, int N, int K, int batch, int ctas)
     else if (ctas == 2) {
         // Few tiles: with 256-wide tiles the last round of the persistent walk may be mostly empty (96 tiles on 74
         // CTA pairs take two rounds).  128-wide tiles cost ~0.6 of a 256-wide one each (measured; shared-memory
-        // bound) and fill the rounds better; take them when rounds x cost comes out lower.
+        // bound) and fill the rounds better; the in-place kernel can also cut the tiles of a thin last round into
+        // K-slices (tail split).  Take the width whose rounds x cost comes out lower.
         const long slots = sm_count() / 2;
         const long tm = (M + 2 * kTileM - 1) / (2 * kTileM);
         const long u256 = tm * ((N + 255) / 256) * batch, u128 = tm * ((N + 127) / 128) * batch;
-        const double c256 = (double)((u256 + slots - 1) / slots), c128 = 0.6 * (double)((u128 + slots - 1) / slots);
+        const int kb = (K + kBK - 1) / kBK, ch = tc_chunk_kblocks();
+        const double c256 = plan_rounds(u256, slots, kb, ch, tail_ok), c128 = 0.6 * plan_rounds(u128, slots, kb, ch, tail_ok);
         if (u256 >= slots && u256 < 4 * slots && c128 < c256) pl.bn = 128;
     }
     const int tile_rows = kTileM * ctas;
@@ -1549,8 +1665,13 @@ static int launch_direct(const CUtensorMap& ma, const CUtensorMap& mb, const Gem
     GemmTcParams p = p_in;
     p.splits = (p.k_blocks + p.kblocks_per_split - 1) / p.kblocks_per_split;
     p.batch = batch;
-    const long total_units = (long)p.tiles_m * p.tiles_n * p.splits * batch;
-    if (total_units > 0x3fffffffL) return fail(ZNN_ERR_INVALID, "too many output tiles (%ld)", total_units);
+    const long base_units = (long)p.tiles_m * p.tiles_n * p.splits * batch;
+    if (base_units > 0x3fffffffL) return fail(ZNN_ERR_INVALID, "too many output tiles (%ld)", base_units);
+    if (p.tail_slices < 1) {   // no tail split
+        p.tail_first = (int)base_units;
+        p.tail_slices = 1;
+    }
+    const long total_units = p.tail_first + (base_units - p.tail_first) * p.tail_slices;
     cudaLaunchConfig_t cfg = {};
     cfg.blockDim = dim3(kDirectThreads, 1, 1);
     cfg.dynamicSmemBytes = Cfg::kSmemBytes;
@@ -1609,15 +1730,29 @@ int gemm_tc_direct(int ta, int tb, int M, int N, int K, float alpha, const float
 {
     int* status = device_status_word();
     if (!status) return fail(ZNN_ERR_CUDA, "no device state (call znn_init first)");
-    TcPlan pl = make_plan(M, N, K, batch, 2);
+    const bool tail_ok = t_tail_split && t_persistent && tri == 0;
+    TcPlan pl = make_plan(M, N, K, batch, 2, tail_ok);
     if (tri != 0 && pl.splits > 1) {   // the triangular k-ranges are per tile; no split-K on top of them
         pl.splits = 1;
         pl.kbps = ((pl.k_blocks + pl.chunk - 1) / pl.chunk) * pl.chunk;
+    }
+    // tail split (only without split-K): the tiles of a thin last round are cut into K-slices
+    int tail_slices = 1, tail_kbps = pl.k_blocks;
+    long tail_tiles = 0;
+    const long units = (long)pl.tiles_m * pl.tiles_n * batch, slots = sm_count() / 2;
+    if (tail_ok && pl.splits == 1) {
+        tail_slices = tail_slices_for(units, slots, pl.k_blocks, pl.chunk, &tail_kbps);
+        if (tail_slices > 1) tail_tiles = units % slots;
     }
     float* partial = nullptr;
     if (pl.splits > 1) {
         partial = (float*)workspace((size_t)pl.splits * batch * M * N * sizeof(float));
         if (!partial) return fail(ZNN_ERR_NOMEM, "split-K scratch could not be allocated");
+    }
+    float* tail_partial = nullptr;
+    if (tail_tiles > 0) {
+        tail_partial = (float*)workspace((size_t)tail_tiles * tail_slices * 2 * kTileM * pl.bn * sizeof(float));
+        if (!tail_partial) return fail(ZNN_ERR_NOMEM, "tail-split scratch could not be allocated");
     }
     const bool a_mn = (ta == ZNN_TRANS), b_mn = (tb == ZNN_NO_TRANS);
     CUtensorMap ma, mb;
@@ -1633,11 +1768,25 @@ int gemm_tc_direct(int ta, int tb, int M, int N, int K, float alpha, const float
     p.tiles_m = pl.tiles_m;
     p.tiles_n = pl.tiles_n;
     p.tri = tri;
+    p.splits = pl.splits;
+    p.batch = batch;
+    p.tail_first = (int)(units * pl.splits - tail_tiles);
+    p.tail_slices = tail_tiles > 0 ? tail_slices : 0;   // 0 = off (launch_direct normalises it)
+    p.tail_kbps = tail_kbps;
+    p.tail_partial = tail_partial;
     p.alpha = alpha; p.beta = beta; p.C = C; p.ldc = ldc; p.stride_c = stride_c; p.status = status;
     if (pl.bn == 256) rc = launch_direct_major<256>(a_mn, b_mn, ma, mb, p, batch);
     else if (pl.bn == 128) rc = launch_direct_major<128>(a_mn, b_mn, ma, mb, p, batch);
     else rc = launch_direct_major<64>(a_mn, b_mn, ma, mb, p, batch);
     if (rc) return rc;
+    if (tail_tiles > 0) {
+        p.tail_slices = tail_slices;
+        const dim3 grid((unsigned)(2 * kTileM * pl.bn / 4 / 256), (unsigned)tail_tiles, 1);   // one float4 per thread
+        if (pl.bn == 256) tail_reduce_kernel<256><<<grid, 256, 0, stream()>>>(p);
+        else if (pl.bn == 128) tail_reduce_kernel<128><<<grid, 256, 0, stream()>>>(p);
+        else tail_reduce_kernel<64><<<grid, 256, 0, stream()>>>(p);
+        ZNN_LAUNCH_OK("tail_reduce_kernel");
+    }
     if (pl.splits > 1) return launch_splitk_reduce(partial, pl.splits, M, N, batch, alpha, beta, C, ldc, stride_c, bias);
     return ZNN_OK;
 }
