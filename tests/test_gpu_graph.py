@@ -140,3 +140,21 @@ def test_transformer_block_matches_cpu_graph(G):
     floor = 1e-2 * max(float(np.abs(v).max()) for v in g0.values())
     for k in g0:
         close(g1[k], g0[k], rtol=3e-5, what=k, floor=floor)
+
+
+def test_batch_matmul_nt_equals_transpose_then_batch_matmul(G):
+    """batchMatMulNT(A, B) = batchMatMul(A, transposeND(B, 2, 3)) in values and in both gradients."""
+    r = np.random.default_rng(12)
+    a = r.standard_normal((2, 3, 20, 8), np.float32)
+    b = r.standard_normal((2, 3, 12, 8), np.float32)
+    dc = r.standard_normal((2, 3, 20, 12), np.float32)
+    outs = []
+    for fused in (True, False):
+        g = G()
+        A, B = g.array(a, True), g.array(b, True)
+        Cn = g.batchMatMulNT(A, B) if fused else g.batchMatMul(A, g.transposeND(B, 2, 3))
+        Cn.set_grad(dc)
+        g.backwardWithGrad(Cn)
+        outs.append((np.array(Cn.data), np.array(A.grad), np.array(B.grad)))
+    for x, y in zip(outs[0], outs[1]):
+        np.testing.assert_allclose(x, y, rtol=1e-5, atol=1e-6)

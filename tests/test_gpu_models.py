@@ -234,18 +234,22 @@ def test_gpt_causal_tile_skipping(Model):
     t = r.integers(0, 128, (2, 768)).astype(np.int32)
     res = []
     try:
-        for skip in (1, 0):
+        # hints on; hints off; and the reference's literal transposeND(K) + batchMatMul instead of the one Q.K^T op
+        for skip, qkt in ((1, 1), (0, 1), (0, 0), (1, 0)):
             m = Model("gpt", dims, arena_bytes=1 << 30)
             m.set_params(P0)
             m.set_option("causal_skip", skip)
+            m.set_option("fused_qkt", qkt)
             m.set_option("lr", 0.0)
             res.append((m.train_step(x, t, seq=768), m.get_grads()))
     finally:
         m.set_option("causal_skip", 1)
-    assert abs(res[0][0] - res[1][0]) <= 1e-6 * abs(res[1][0])
-    floor = 1e-2 * grad_floor(res[1][1])
-    for k in res[0][1]:
-        relclose(res[0][1][k], res[1][1][k], 1e-5, k, floor)
+        m.set_option("fused_qkt", 1)
+    floor = 1e-2 * grad_floor(res[2][1])
+    for i in (0, 1, 3):
+        assert abs(res[i][0] - res[2][0]) <= 1e-6 * abs(res[2][0])
+        for k in res[i][1]:
+            relclose(res[i][1][k], res[2][1][k], 1e-5, k, floor)
 
 
 def test_kv_cache_decode_gives_the_same_tokens(Model):

@@ -122,6 +122,7 @@ int znn_graph_op(znn_graph* zg, const char* name, const int* inputs, int n_input
     else if (op == "rmsNorm") out = g.rmsNorm(in(0), in(1), (float)arg(0));
     else if (op == "layerNorm") out = g.layerNorm(in(0), in(1), in(2), (float)arg(0));
     else if (op == "batchMatMul") out = g.batchMatMul(in(0), in(1));
+    else if (op == "batchMatMulNT") out = g.batchMatMulNT(in(0), in(1));
     else if (op == "linear") out = g.linear(in(0), in(1), in(2));
     else if (op == "embedding") out = g.embedding(in(0), in(1));
     else throw Error(ZNN_ERR_INVALID, "unknown op '" + op + "'");
@@ -466,6 +467,7 @@ int znn_model_set_option(znn_model* m, const char* key, double value)
         m->block.attn.fused_softmax = (value != 0.0);
     } else if (k == "fused_linear") set_fused_linear(value != 0.0);
     else if (k == "causal_skip") set_causal_skip(value != 0.0);
+    else if (k == "fused_qkt") set_fused_qkt(value != 0.0);
     else if (k == "alias_reshape_grad") set_alias_reshape_grad(value != 0.0);
     else if (k == "lazy_zero_grad") set_lazy_zero_grad(value != 0.0);
     else if (k == "cuda_graph") {

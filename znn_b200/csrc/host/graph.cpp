@@ -360,6 +360,21 @@ Tensor* Graph::batchMatMul(Tensor* A, Tensor* B, int tri_role)
     return C;
 }
 
+Tensor* Graph::batchMatMulNT(Tensor* A, Tensor* B, int tri_role)
+{
+    if (A->shape.len != 4 || B->shape.len != 4 || A->shape.dims[3] != B->shape.dims[3] ||
+        A->shape.dims[0] != B->shape.dims[0] || A->shape.dims[1] != B->shape.dims[1])
+        throw Error(ZNN_ERR_INVALID, "batchMatMulNT: need [b,h,M,K] x [b,h,N,K]");
+    if (tri_role != 0 && (tri_role != 1 || A->shape.dims[2] != B->shape.dims[2]))
+        throw Error(ZNN_ERR_INVALID, "batchMatMulNT: the causal role needs square scores");
+    Tensor* C = new_tensor(Shape{A->shape.dims[0], A->shape.dims[1], A->shape.dims[2], B->shape.dims[2]},
+                           any_grad({A, B}), false);
+    Op* op = new_op(OpType::BatchMatMulNT, {A, B}, C);
+    op->tri_role = tri_role;
+    op->forward();
+    return C;
+}
+
 Tensor* Graph::embedding(Tensor* W, Tensor* X)
 {
     if (W->shape.len != 2 || X->shape.len != 2) throw Error(ZNN_ERR_INVALID, "embedding: W [V,D], ids [B,T]");
@@ -454,6 +469,16 @@ void Op::forward()
               "BatchMatMul forward");
         break;
     }
+    case OpType::BatchMatMulNT: {
+        Tensor* B = inputs[1];
+        const int nb = (int)(A->shape.dims[0] * A->shape.dims[1]);
+        const int M = (int)A->shape.dims[2], K = (int)A->shape.dims[3], N = (int)B->shape.dims[2];
+        check(znn_sgemm_batched_strided_tri(ZNN_NO_TRANS, ZNN_TRANS, M, N, K, 1.0f, A->data, K, (long long)M * K, B->data, K,
+                                            (long long)N * K, 0.0f, C->data, N, (long long)M * N, nb,
+                                            tri_role == 1 ? ZNN_TRI_C_LOWER : ZNN_TRI_NONE),
+              "BatchMatMulNT forward");
+        break;
+    }
     case OpType::Embedding: {
         Tensor* W = inputs[0];
         Tensor* X = inputs[1];
@@ -472,7 +497,8 @@ void Op::backward()
     ensure_grad(C);
     // arms that only add need a defined buffer; the GEMM arms below overwrite a fresh one instead (beta = 0)
     // (so do Gelu, CausalSoftmax, Add, MulScalar, Reshape and Transpose, with a storing kernel or a plain copy)
-    const bool can_store = type == OpType::MatMul || type == OpType::BatchMatMul || type == OpType::LinearBias ||
+    const bool can_store = type == OpType::MatMul || type == OpType::BatchMatMul || type == OpType::BatchMatMulNT ||
+                           type == OpType::LinearBias ||
                            type == OpType::Gelu || type == OpType::CausalSoftmax || type == OpType::Add ||
                            type == OpType::MulScalar || type == OpType::Reshape || type == OpType::Transpose;
     if (!can_store)
@@ -633,6 +659,28 @@ void Op::backward()
             check(znn_sgemm_batched_strided_tri(ZNN_TRANS, ZNN_NO_TRANS, K, N, M, 1.0f, A->data, K, (long long)M * K, C->grad,
                                                 N, (long long)M * N, beta, B->grad, N, (long long)K * N, nb, tri_db),
                   "BatchMatMul backward dB");
+        }
+        break;
+    }
+    case OpType::BatchMatMulNT: {
+        // C = A.B^T  =>  dA += dC.B (left operand dC lower-triangular when C are causal scores),
+        //                dB += dC^T.A (left operand dC^T upper-triangular)
+        Tensor* B = inputs[1];
+        const int nb = (int)(A->shape.dims[0] * A->shape.dims[1]);
+        const int M = (int)A->shape.dims[2], K = (int)A->shape.dims[3], N = (int)B->shape.dims[2];
+        if (A->requires_grad) {
+            const float beta = claim_grad_overwrite(A) ? 0.0f : 1.0f;
+            check(znn_sgemm_batched_strided_tri(ZNN_NO_TRANS, ZNN_NO_TRANS, M, K, N, 1.0f, C->grad, N, (long long)M * N, B->data,
+                                                K, (long long)N * K, beta, A->grad, K, (long long)M * K, nb,
+                                                tri_role == 1 ? ZNN_TRI_A_LOWER : ZNN_TRI_NONE),
+                  "BatchMatMulNT backward dA");
+        }
+        if (B->requires_grad) {
+            const float beta = claim_grad_overwrite(B) ? 0.0f : 1.0f;
+            check(znn_sgemm_batched_strided_tri(ZNN_TRANS, ZNN_NO_TRANS, N, K, M, 1.0f, C->grad, N, (long long)M * N, A->data,
+                                                K, (long long)M * K, beta, B->grad, K, (long long)N * K, nb,
+                                                tri_role == 1 ? ZNN_TRI_A_UPPER : ZNN_TRI_NONE),
+                  "BatchMatMulNT backward dB");
         }
         break;
     }

@@ -73,7 +73,8 @@ enum class OpType {
     Softmax, RmsNorm, BatchMatMul, Embedding,
     CausalSoftmax,  // fused mulScalar + mask add + softmax of src/nn.zig:835-886 (an addition)
     LayerNorm,      // extension, no reference counterpart
-    LinearBias      // fused matmul + addBias of Linear.forward (src/nn.zig:44-51), an addition
+    LinearBias,     // fused matmul + addBias of Linear.forward (src/nn.zig:44-51), an addition
+    BatchMatMulNT   // C = A.B^T per (batch, head) slice: transposeND(K) + batchMatMul of src/nn.zig:796-835 in one op, an addition
 };
 
 // src/autodiff.zig:100-105 (OpContext flattened)
@@ -146,6 +147,9 @@ public:
     // gradient is lower-triangular), 2 = A holds causal-softmax probabilities (lower-triangular); the products then
     // skip the tiles the mask makes irrelevant (znn_sgemm_batched_strided_tri).  0 = the reference's full products.
     Tensor* batchMatMul(Tensor* A, Tensor* B, int tri_role = 0);            // :2129
+    // C[b,h] = A[b,h] . B[b,h]^T for A [b,h,M,K], B [b,h,N,K] (an addition: no transposed copy of B is made and the
+    // gradient of B comes out as dC^T.A, a product with a tall output instead of a 64-row one); tri_role as above
+    Tensor* batchMatMulNT(Tensor* A, Tensor* B, int tri_role = 0);
     Tensor* embedding(Tensor* W, Tensor* X);                                // :2160
     Tensor* causalSoftmax(Tensor* S, float scale);                          // fused addition
     Tensor* layerNorm(Tensor* X, Tensor* G, Tensor* B, float eps);          // extension

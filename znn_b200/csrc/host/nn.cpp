@@ -62,6 +62,10 @@ Linear::Linear(ParamStore& ps, const std::string& name, size_t in_features, size
     bias = ps.add(name + ".bias", Shape{1, out_features}, 0);
 }
 
+static bool g_fused_qkt = true;
+void set_fused_qkt(bool on) { g_fused_qkt = on; }
+bool fused_qkt() { return g_fused_qkt; }
+
 static bool g_causal_skip = true;
 void set_causal_skip(bool on) { g_causal_skip = on; }
 bool causal_skip() { return g_causal_skip; }
@@ -138,11 +142,16 @@ Tensor* CausalSelfAttention::forward(Graph& g, Tensor* x) const
     Tensor* q = g.transposeND(q_4d, 1, 2);
     Tensor* k = g.transposeND(k_4d, 1, 2);
     Tensor* v = g.transposeND(v_4d, 1, 2);
-    Tensor* k_t = g.transposeND(k, 2, 3);
     // with the fused causal softmax nobody reads the scores above the diagonal, and the probabilities there are
     // exact zeros: the two products and their four gradient products skip those tiles
     const bool skip = fused_softmax && g_causal_skip;
-    Tensor* att = g.batchMatMul(q, k_t, skip ? 1 : 0);
+    Tensor* att;
+    if (g_fused_qkt) {
+        att = g.batchMatMulNT(q, k, skip ? 1 : 0);          // Q.K^T without the transposed copy of K
+    } else {
+        Tensor* k_t = g.transposeND(k, 2, 3);               // nn.zig:796-835 literally
+        att = g.batchMatMul(q, k_t, skip ? 1 : 0);
+    }
     const float scale = 1.0f / sqrtf((float)hs);
     Tensor* att_sm;
     if (fused_softmax) {

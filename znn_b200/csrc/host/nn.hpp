@@ -48,6 +48,9 @@ private:
 // The attention products skip the tiles the causal mask makes irrelevant (only with fused_softmax); default on.
 void set_causal_skip(bool on);
 bool causal_skip();
+// Attention scores as one Q.K^T op instead of transposeND(K) + batchMatMul; default on.
+void set_fused_qkt(bool on);
+bool fused_qkt();
 void set_fused_linear(bool on);
 bool fused_linear();
 

@@ -88,6 +88,7 @@ class Graph:
     def rmsNorm(self, X, G, eps): return self._op("rmsNorm", [X, G], [eps])
     def layerNorm(self, X, G, B, eps): return self._op("layerNorm", [X, G, B], [eps])
     def batchMatMul(self, A, B): return self._op("batchMatMul", [A, B])
+    def batchMatMulNT(self, A, B): return self._op("batchMatMulNT", [A, B])
     def embedding(self, W, X): return self._op("embedding", [W, X])
     def linear(self, X, W, b): return self._op("linear", [X, W, b])
 
