@@ -110,6 +110,17 @@ int znn_sgemm_batched_strided_tri(int trans_a, int trans_b, int M, int N, int K,
                                   const float* A, int lda, long long stride_a,
                                   const float* B, int ldb, long long stride_b, float beta,
                                   float* C, int ldc, long long stride_c, int batch, int tri);
+/* Backward of the attention probabilities fused into the product that feeds it (an addition; src/autodiff.zig:1117-1182
+ * BatchMatMul backward dA followed by :1054-1076 Softmax backward and the mulScalar backward of src/nn.zig:836):
+ *   dS[s] = scale * P[s] o (dO[s].V[s]^T - D[s][:, None]),   D[s][i] = sum_j dP[s][i,j] P[s][i,j] = dO[s][i,:].O[s][i,:]
+ * for nslices slices of T x T scores, dO, V of T x hs; dP is never written.  Only tiles that touch the lower triangle
+ * are computed and stored (P is zero above the diagonal, so dS is zero there inside those tiles; tiles entirely above
+ * it are left untouched).  dS is overwritten.  Needs the in-place tensor-core path (16-byte aligned pointers, T and hs
+ * multiples of 4); returns ZNN_ERR_UNSUPPORTED otherwise and the caller uses the separate ops. */
+int znn_attn_dscores(const float* dO, const float* V, const float* P, const float* D, float scale, float* dS, int T, int hs,
+                     int nslices);
+/* out[r] = sum_j A[r,j] * B[r,j] for `rows` rows of D floats (the D vector above from dO and O) */
+int znn_rowdot(const float* A, const float* B, float* out, size_t rows, int D);
 /* Fused form of Linear.forward = addBias(matmul(x, W), b) (src/nn.zig:44-51): Y[M,N] = X[M,K].W[K,N] + bias[N]
  * in one pass (the bias is added in the GEMM epilogue); an addition, the two separate ops remain.
  * Backward of the pair (src/autodiff.zig:593-641 and :652-672 chained): dX += dY.W^T, dW += X^T.dY,

@@ -59,7 +59,8 @@ int znn_model_get_params(znn_model* m, float* host_slab);
 int znn_model_get_grads(znn_model* m, float* host_slab);
 int znn_model_get_velocities(znn_model* m, float* host_slab);
 /* keys: "lr", "momentum", "fused_softmax" (1/0), "fused_linear" (1/0, process-wide), "causal_skip" (1/0, process-wide: attention products
- * skip the tiles above the causal diagonal; needs fused_softmax), "fused_qkt" (1/0, process-wide: attention scores as one
+ * skip the tiles above the causal diagonal; needs fused_softmax), "fused_softmax_bwd" (1/0, process-wide: the gradient of the attention scores comes out of
+ * the dO.V^T product's epilogue, no dP buffer and no separate softmax backward), "fused_qkt" (1/0, process-wide: attention scores as one
  * Q.K^T op instead of a transposed copy of K and a product), "alias_reshape_grad" (1/0, process-wide: Reshape views
  * share the gradient buffer of their input instead of adding into it in backward), "lazy_zero_grad" (1/0, process-wide:
  * gradient buffers of intermediates are zero-filled only when first added to; GEMM arms overwrite them with beta = 0), "dp_bucket_floats",

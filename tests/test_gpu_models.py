@@ -120,7 +120,10 @@ def test_gpt_literal_attention_path(Model):
         losses.append((m.train_step(x, t, seq=8), m.get_grads(), m.last_step_ops()))
     assert losses[1][2] == losses[0][2] + 2          # mulScalar, add, softmax instead of the one fused op
     assert abs(losses[0][0] - losses[1][0]) <= 1e-6 * abs(losses[1][0])
-    floor = 1e-2 * grad_floor(losses[1][1])
+    # gradients that are zero in exact arithmetic (k_attn.bias) hold cancellation noise of ~1e-7 of the largest
+    # gradient on both sides; the fused score gradient takes its row sums from dO.O instead of sum(dP o P), so the two
+    # noises differ: 3 % of the largest gradient as the scale keeps the bar at 3e-7 of it
+    floor = 3e-2 * grad_floor(losses[1][1])
     for k in losses[0][1]:
         relclose(losses[0][1][k], losses[1][1][k], 1e-5, k, floor)
     # the fused Linear op (matmul + addBias in one GEMM epilogue) against the two separate ops
@@ -235,18 +238,20 @@ def test_gpt_causal_tile_skipping(Model):
     res = []
     try:
         # hints on; hints off; and the reference's literal transposeND(K) + batchMatMul instead of the one Q.K^T op
-        for skip, qkt in ((1, 1), (0, 1), (0, 0), (1, 0)):
+        for skip, qkt, fsb in ((1, 1, 1), (0, 1, 1), (0, 0, 0), (1, 0, 0), (1, 1, 0)):
             m = Model("gpt", dims, arena_bytes=1 << 30)
             m.set_params(P0)
             m.set_option("causal_skip", skip)
             m.set_option("fused_qkt", qkt)
+            m.set_option("fused_softmax_bwd", fsb)
             m.set_option("lr", 0.0)
             res.append((m.train_step(x, t, seq=768), m.get_grads()))
     finally:
         m.set_option("causal_skip", 1)
         m.set_option("fused_qkt", 1)
-    floor = 1e-2 * grad_floor(res[2][1])
-    for i in (0, 1, 3):
+        m.set_option("fused_softmax_bwd", 1)
+    floor = 3e-2 * grad_floor(res[2][1])   # see test_gpt_literal_attention_path: noise of exactly-zero gradients
+    for i in (0, 1, 3, 4):
         assert abs(res[i][0] - res[2][0]) <= 1e-6 * abs(res[2][0])
         for k in res[i][1]:
             relclose(res[i][1][k], res[2][1][k], 1e-5, k, floor)
@@ -273,3 +278,11 @@ def test_kv_cache_decode_gives_the_same_tokens(Model):
     m2 = Model("gpt", (96, 48, 128, 2, 2), arena_bytes=256 << 20)
     m2.set_params(P1)
     np.testing.assert_array_equal(m2.greedy_decode_kv(prompts2, 40), m2.greedy_decode(prompts2, 40))
+
+
+def test_gpt_long_context_against_the_oracle(Model):
+    """Context 512 with 64-wide heads: the attention products run on the tensor cores with the triangular hints, the
+    one Q.K^T op, aliased reshape gradients and lazily zeroed gradients, all at their defaults, against the oracle's
+    literal reference sequence (full products, materialised -1e9 mask, transposed copy of K, separate gradients)."""
+    cfg = {"vocab_size": 96, "block_size": 512, "n_embd": 128, "n_head": 2, "n_layer": 1}
+    run_training(Model, "gpt", (96, 512, 128, 2, 1), cfg, 3, 2, 0.05, 0.9, seed=41, seq=512, vocab=96)

@@ -340,3 +340,24 @@ def test_fused_linear(ops, zo, M, K, N):
     close(dX_.to_host((M, K)), dXr, what="linear dX")
     close(dW_.to_host((K, N)), dWr, what="linear dW")
     close(db_.to_host((N,)), dbr, what="linear dbias")
+
+
+@pytest.mark.parametrize("ns,T,hs", [(3, 520, 64), (2, 1024, 64), (4, 96, 32)])
+def test_fused_attention_score_gradient(ops, zo, ns, T, hs):
+    """znn_attn_dscores = BatchMatMul backward dA (dP = dO.V^T), Softmax backward and the scale of the reference's
+    attention, in one product: against the oracle's separate steps on the lower triangle (what is ever read)."""
+    r = rng(ns * 7 + T)
+    S = (r.standard_normal((ns, T, T), np.float32) * 3.0).astype(np.float32)
+    scale = float(1.0 / np.sqrt(np.float32(hs)))
+    P = zo.causal_softmax_fwd(S, scale)
+    dO = r.standard_normal((ns, T, hs), np.float32)
+    V = r.standard_normal((ns, T, hs), np.float32)
+    dP = np.zeros((ns, T, T), np.float32)
+    for s in range(ns):
+        zo.sgemm(111, 112, T, T, hs, 1.0, dO[s], hs, V[s], hs, 0.0, dP[s], T, naive=True)
+    want = np.zeros((ns, T, T), np.float32)
+    zo.causal_softmax_bwd(P, dP, scale, want)
+    got = ops.attn_dscores(dO, V, P, scale)
+    close(np.tril(got), np.tril(want), what="fused attention score gradient")
+    a, b = r.standard_normal((50, 64), np.float32), r.standard_normal((50, 64), np.float32)
+    close(ops.rowdot(a, b), (a.astype(np.float64) * b).sum(1).astype(np.float32), what="rowdot")

@@ -15,7 +15,7 @@ bool gemm_tc_direct_eligible(const float* A, long long lda, long long stride_a, 
                              long long stride_b, int batch);
 int gemm_tc_direct(int ta, int tb, int M, int N, int K, float alpha, const float* A, long long lda, long long stride_a,
                    const float* B, long long ldb, long long stride_b, float beta, float* C, long long ldc,
-                   long long stride_c, int batch, const float* bias, int tri);
+                   long long stride_c, int batch, const float* bias, int tri, const float* ep_p, const float* ep_d);
 int launch_splitk_reduce(const float* partial, int splits, int M, int N, int batch, float alpha, float beta, float* C,
                          long long ldc, long long stride_c, const float* bias);
 int tc_profile_enable(int enable);
@@ -119,7 +119,8 @@ static thread_local int t_last_path = 0;  // taken by the last call
 // bias (optional, [N]) is added to every row of the result: the fused form of MatMul + AddBias
 static int gemm_dispatch(int ta, int tb, int M, int N, int K, float alpha, const float* A, long long lda,
                          long long stride_a, const float* B, long long ldb, long long stride_b, float beta, float* C,
-                         long long ldc, long long stride_c, int batch, const float* bias = nullptr, int tri = 0)
+                         long long ldc, long long stride_c, int batch, const float* bias = nullptr, int tri = 0,
+                         const float* ep_p = nullptr, const float* ep_d = nullptr)
 {
     ZNN_REQUIRE(ta == ZNN_NO_TRANS || ta == ZNN_TRANS, "trans_a must be 111 or 112");
     ZNN_REQUIRE(tb == ZNN_NO_TRANS || tb == ZNN_TRANS, "trans_b must be 111 or 112");
@@ -144,6 +145,10 @@ static int gemm_dispatch(int ta, int tb, int M, int N, int K, float alpha, const
 
     int path = t_path;
     const bool direct_ok = gemm_tc_direct_eligible(A, lda, stride_a, B, ldb, stride_b, batch);
+    if (ep_p) {   // the fused epilogue exists on the in-place tensor-core path only
+        if (!direct_ok) return fail(ZNN_ERR_UNSUPPORTED, "fused epilogue: operands not readable in place");
+        path = 4;
+    }
     if (path == 0) {
         // The tensor-core paths cost extra launches; below ~0.13 GFLOP per call the FMA kernel finishes sooner.
         const double flops = 2.0 * M * N * (double)K * batch;
@@ -160,7 +165,7 @@ static int gemm_dispatch(int ta, int tb, int M, int N, int K, float alpha, const
     t_last_path = path;
     if (path >= 2) {
         int rc = (path == 4) ? gemm_tc_direct(ta, tb, M, N, K, alpha, A, lda, stride_a, B, ldb, stride_b, beta, C, ldc,
-                                              stride_c, batch, bias, tri)
+                                              stride_c, batch, bias, tri, ep_p, ep_d)
                              : gemm_tc(ta, tb, M, N, K, alpha, A, lda, stride_a, B, ldb, stride_b, beta, C, ldc, stride_c,
                                        batch, path == 2 ? 1 : 2, bias);
         // Debug aid (environment ZNN_GEMM_CHECK=1): wait for every tensor-core product and name the first one
@@ -245,6 +250,15 @@ int znn_sgemm_batched_strided_tri(int trans_a, int trans_b, int M, int N, int K,
     ZNN_REQUIRE(tri >= ZNN_TRI_NONE && tri <= ZNN_TRI_B_LOWER, "tri must be one of ZNN_TRI_*");
     return gemm_dispatch(trans_a, trans_b, M, N, K, alpha, A, lda, stride_a, B, ldb, stride_b, beta, C, ldc, stride_c,
                          batch, nullptr, tri);
+}
+
+int znn_attn_dscores(const float* dO, const float* V, const float* P, const float* D, float scale, float* dS, int T, int hs,
+                     int nslices)
+{
+    ZNN_REQUIRE(dO && V && P && D && dS, "NULL pointer");
+    ZNN_REQUIRE(T > 0 && hs > 0 && nslices > 0 && nslices <= 65535, "bad dimensions");
+    return gemm_dispatch(ZNN_NO_TRANS, ZNN_TRANS, T, T, hs, scale, dO, hs, (long long)T * hs, V, hs, (long long)T * hs, 0.0f, dS, T,
+                         (long long)T * T, nslices, nullptr, ZNN_TRI_C_LOWER, P, D);
 }
 
 int znn_linear_fwd(const float* X, const float* W, const float* bias, float* Y, int M, int K, int N)

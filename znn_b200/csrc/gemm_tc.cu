@@ -238,6 +238,15 @@ struct GemmTcParams {
     // tail_partial[unit - tail_first]; a small kernel adds the slices in order.  tail_first = number of units when off.
     int tail_first, tail_slices, tail_kbps;
     float* tail_partial;
+    // in-place kernel, softmax-backward epilogue: C = alpha * P o (A.B - d[row]) with P laid out like C (ldc, stride_c)
+    // and d one float per row and batch slice; nullptr = the ordinary epilogue
+    const float* ep_p;
+    const float* ep_d;
+    // in-place kernel, triangular hint: the tiles of one slice that have work, dearest first (tile_m << 8 | tile_n);
+    // units are then (table entry, slice) with the slice running fastest, so that the walk deals every CTA pair the
+    // same mix of dear and cheap tiles.  tri_n = 0: no table (more than 64 tiles per slice), plain order.
+    int tri_n;
+    unsigned short tri_tab[64], tri_kf[64], tri_kc[64];   // tile code, first k-block, k-block count per entry
     float alpha, beta;
     float* C;
     long long ldc, stride_c;
@@ -730,27 +739,6 @@ struct DirectCfg {
     static_assert(kStageBytes % 1024 == 0, "stages must keep the 1 KB alignment of what follows");
 };
 
-// Triangular structure of a square (causal-attention) product, in whole tiles: which k-blocks the 256 x BN output
-// tile at (row0, col0) needs.  ZNN_TRI_C_LOWER: only tiles that touch the lower triangle (col <= row) are computed,
-// the others get no k-blocks and are not stored.  ZNN_TRI_A_LOWER: op(A)[m,k] = 0 for k > m, so k stops at the tile's
-// last row.  ZNN_TRI_A_UPPER: op(A)[m,k] = 0 for k < m, so k starts at the tile's first row.  ZNN_TRI_B_LOWER:
-// op(B)[k,n] = 0 for n > k, so k starts at the tile's first column.
-__device__ __forceinline__ void tri_k_range(const GemmTcParams& p, int row0, int col0, int& kb_first, int& kb_count)
-{
-    int lo = 0, hi = p.k_blocks;
-    if (p.tri == ZNN_TRI_C_LOWER) {
-        if (col0 > row0 + 2 * kTileM - 1) hi = 0;
-    } else if (p.tri == ZNN_TRI_A_LOWER) {
-        hi = min(hi, (row0 + 2 * kTileM + kBK - 1) / kBK);
-    } else if (p.tri == ZNN_TRI_A_UPPER) {
-        lo = min(hi, row0 / kBK);
-    } else if (p.tri == ZNN_TRI_B_LOWER) {
-        lo = min(hi, col0 / kBK);
-    }
-    kb_first = lo;
-    kb_count = hi - lo;
-}
-
 // One work unit = one 256 x BN output tile of one batch slice and one split-K slice.
 struct DirectUnit {
     int row0, col0, batch, split, kb_first, kb_count, nchunks;
@@ -758,6 +746,20 @@ struct DirectUnit {
 
 __device__ __forceinline__ DirectUnit direct_unit(const GemmTcParams& p, int u, int cta_rank, int bn)
 {
+    DirectUnit d;
+    if (p.tri_n > 0) {
+        // triangular hint with a tile table: unit = (table entry, slice), slices fastest (no split-K, no tail split)
+        const int e = u / p.batch;
+        const unsigned tt = p.tri_tab[e];
+        d.split = 0;
+        d.batch = u - e * p.batch;
+        d.row0 = ((int)(tt >> 8) * 2 + cta_rank) * kTileM;
+        d.col0 = (int)(tt & 255u) * bn;
+        d.kb_first = p.tri_kf[e];
+        d.kb_count = p.tri_kc[e];
+        d.nchunks = (d.kb_count + p.chunk_kblocks - 1) / p.chunk_kblocks;
+        return d;
+    }
     int slice = -1;
     int uu = u;
     if (u >= p.tail_first) {   // a K-slice of one of the last round's tiles
@@ -768,7 +770,6 @@ __device__ __forceinline__ DirectUnit direct_unit(const GemmTcParams& p, int u, 
     const int units_per = p.tiles_m * p.tiles_n;
     const int t = uu % units_per;
     const int sb = uu / units_per;
-    DirectUnit d;
     d.split = sb % p.splits;
     d.batch = sb / p.splits;
     // groups of 8 tile-rows are walked column by column so that CTA pairs running together share
@@ -785,7 +786,6 @@ __device__ __forceinline__ DirectUnit direct_unit(const GemmTcParams& p, int u, 
     d.col0 = tile_n * bn;
     d.kb_first = d.split * p.kblocks_per_split;
     d.kb_count = min(p.k_blocks - d.kb_first, p.kblocks_per_split);
-    if (p.tri) tri_k_range(p, tile_m * 2 * kTileM, d.col0, d.kb_first, d.kb_count);
     if (slice >= 0) {
         d.kb_first = slice * p.tail_kbps;
         d.kb_count = min(p.k_blocks - d.kb_first, p.tail_kbps);
@@ -797,7 +797,7 @@ __device__ __forceinline__ DirectUnit direct_unit(const GemmTcParams& p, int u, 
 // k-blocks of work unit u (all the converter warps need to know about it)
 __device__ __forceinline__ int direct_unit_kb_count(const GemmTcParams& p, int u, int bn)
 {
-    if (p.tri) return direct_unit(p, u, 0, bn).kb_count;
+    if (p.tri_n > 0) return p.tri_kc[u / p.batch];
     if (u >= p.tail_first) {
         const int slice = (u - p.tail_first) % p.tail_slices;
         return min(p.k_blocks - slice * p.tail_kbps, p.tail_kbps);
@@ -852,8 +852,11 @@ __device__ __forceinline__ void epilogue_store_rows(const float (&acc)[CPT], flo
 template <int CPT>
 __device__ __forceinline__ void epilogue_store_vec(const float (&acc)[CPT], float* stage, int lane, int row_base, int cbase,
                                                    int M, int N, float* out, long long out_ld, float alpha, float beta,
-                                                   const float* bias, int rot)
+                                                   const float* bias, int rot, const float* ep_p = nullptr,
+                                                   const float* ep_d = nullptr)
 {
+    // ep_p != nullptr: softmax-backward form, out = alpha * P o (acc - d[row]) with P laid out like out and d one
+    // value per row of this slice (beta and bias unused, N a multiple of 4)
     constexpr int LPR = CPT / 4;          // lanes (float4) per row
     constexpr int RPP = 1024 / CPT;       // rows per pass (block = 1024 floats)
     constexpr int RPI = 32 / LPR;         // rows per read instruction
@@ -884,11 +887,14 @@ __device__ __forceinline__ void epilogue_store_vec(const float (&acc)[CPT], floa
 #pragma unroll
         for (int i0 = 0; i0 < NI; i0 += IB) {
             float4 old[IB];
-            if (beta != 0.0f && col_full) {
+            if ((beta != 0.0f || ep_p) && col_full) {
+                const float* src = ep_p ? ep_p : out;
 #pragma unroll
                 for (int i = 0; i < IB; i++) {
                     const int r = g * RPP + ((i0 + i + rot) % NI) * RPI + lane / LPR;
-                    if (r < rows) old[i] = *reinterpret_cast<const float4*>(out + (size_t)(row_base + r) * out_ld + col);
+                    if (r < rows) {
+                        old[i] = *reinterpret_cast<const float4*>(src + (size_t)(row_base + r) * out_ld + col);
+                    }
                 }
             }
 #pragma unroll
@@ -897,8 +903,17 @@ __device__ __forceinline__ void epilogue_store_vec(const float (&acc)[CPT], floa
                 const int r = g * RPP + rl;
                 if (r >= rows || col >= N) continue;
                 const float4 v = st4[rl * LPR + (my_f ^ (rl & 7) & (LPR - 1))];
-                float o[4] = {alpha * v.x, alpha * v.y, alpha * v.z, alpha * v.w};
                 float* crow = out + (size_t)(row_base + r) * out_ld;
+                if (ep_p) {
+                    if (col_full) {
+                        const float dr = ep_d[row_base + r];
+                        *reinterpret_cast<float4*>(crow + col) =
+                            make_float4((old[i].x * (v.x - dr)) * alpha, (old[i].y * (v.y - dr)) * alpha,
+                                        (old[i].z * (v.z - dr)) * alpha, (old[i].w * (v.w - dr)) * alpha);
+                    }
+                    continue;
+                }
+                float o[4] = {alpha * v.x, alpha * v.y, alpha * v.z, alpha * v.w};
                 if (col_full) {
                     o[0] += b4.x; o[1] += b4.y; o[2] += b4.z; o[3] += b4.w;
                     if (beta != 0.0f) {
@@ -960,7 +975,7 @@ gemm3x_direct_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_cons
     const int cta_rank = (int)cluster_ctarank();
     const bool leader = (cta_rank == 0);
     const int pair = blockIdx.x >> 1, npairs = gridDim.x >> 1;
-    const int base_units = p.tiles_m * p.tiles_n * p.splits * p.batch;
+    const int base_units = (p.tri_n > 0 ? p.tri_n : p.tiles_m * p.tiles_n * p.splits) * p.batch;
     const int total_units = p.tail_first + (base_units - p.tail_first) * p.tail_slices;
     const int chunk = p.chunk_kblocks;
 
@@ -1174,7 +1189,6 @@ gemm3x_direct_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_cons
                 if (lane == 0) mbar_arrive_remote(acc_empty_leader0 + 8u * buf);
             }
             if (!got) break;
-            if (p.tri == ZNN_TRI_C_LOWER && d.kb_count == 0) continue;   // a tile above the diagonal: nobody reads it
             // split-K slices store their raw partial sums; a reduce kernel applies alpha/beta afterwards
             if (u >= p.tail_first) {
                 // a K-slice of a last-round tile: the raw 256 x BN partial tile, packed, to its own slot
@@ -1189,7 +1203,8 @@ gemm3x_direct_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_cons
                                 ((reinterpret_cast<uintptr_t>(bias) & 15) == 0);
             if (vec_ok)
                 epilogue_store_vec<CPT>(acc, stage, lane, d.row0 + q * 32, d.col0 + half * CPT, p.M, p.N, out, out_ld, alpha, beta, bias,
-                                        warp + pair);
+                                        warp + pair, p.ep_p ? p.ep_p + (size_t)d.batch * p.stride_c : nullptr,
+                                        p.ep_d ? p.ep_d + (size_t)d.batch * p.M : nullptr);
             else
                 epilogue_store_rows<CPT>(acc, stage, lane, d.row0 + q * 32, d.col0 + half * CPT, p.M, p.N, out, out_ld, alpha, beta, bias);
         }
@@ -1607,6 +1622,8 @@ int gemm_tc(int ta, int tb, int M, int N, int K, float alpha, const float* A, lo
     p.M = M; p.N = N; p.k_blocks = k_blocks; p.k_real = K; p.chunk_kblocks = chunk;
     p.kblocks_per_split = kbps;
     p.partial = splits > 1 ? (b_lo + b_plane) : nullptr;
+    p.ep_p = nullptr;
+    p.ep_d = nullptr;
     p.conv_mode = 0;
     p.bias = bias;
     p.tiles_m = tiles_m;
@@ -1669,7 +1686,7 @@ static int launch_direct(const CUtensorMap& ma, const CUtensorMap& mb, const Gem
     GemmTcParams p = p_in;
     p.splits = (p.k_blocks + p.kblocks_per_split - 1) / p.kblocks_per_split;
     p.batch = batch;
-    const long base_units = (long)p.tiles_m * p.tiles_n * p.splits * batch;
+    const long base_units = (p.tri_n > 0 ? (long)p.tri_n : (long)p.tiles_m * p.tiles_n * p.splits) * batch;
     if (base_units > 0x3fffffffL) return fail(ZNN_ERR_INVALID, "too many output tiles (%ld)", base_units);
     if (p.tail_slices < 1) {   // no tail split
         p.tail_first = (int)base_units;
@@ -1730,13 +1747,19 @@ bool gemm_tc_direct_eligible(const float* A, long long lda, long long stride_a, 
 
 int gemm_tc_direct(int ta, int tb, int M, int N, int K, float alpha, const float* A, long long lda, long long stride_a,
                    const float* B, long long ldb, long long stride_b, float beta, float* C, long long ldc,
-                   long long stride_c, int batch, const float* bias, int tri)
+                   long long stride_c, int batch, const float* bias, int tri, const float* ep_p, const float* ep_d)
 {
     int* status = device_status_word();
     if (!status) return fail(ZNN_ERR_CUDA, "no device state (call znn_init first)");
-    const bool tail_ok = t_tail_split && t_persistent && tri == 0;
+    if (ep_p) {
+        // the softmax-backward epilogue exists in the 16-byte form only, and never meets partial tiles
+        if ((N & 3) || (ldc & 3) || (reinterpret_cast<uintptr_t>(C) & 15) || (reinterpret_cast<uintptr_t>(ep_p) & 15) ||
+            (batch > 1 && (stride_c & 3)) || !ep_d || bias || beta != 0.0f)
+            return fail(ZNN_ERR_UNSUPPORTED, "softmax-backward epilogue: unaligned output or unsupported arguments");
+    }
+    const bool tail_ok = t_tail_split && t_persistent && tri == 0 && !ep_p;
     TcPlan pl = make_plan(M, N, K, batch, 2, tail_ok);
-    if (tri != 0 && pl.splits > 1) {   // the triangular k-ranges are per tile; no split-K on top of them
+    if ((tri != 0 || ep_p) && pl.splits > 1) {   // the triangular k-ranges are per tile; no split-K on top of them
         pl.splits = 1;
         pl.kbps = ((pl.k_blocks + pl.chunk - 1) / pl.chunk) * pl.chunk;
     }
@@ -1771,13 +1794,52 @@ int gemm_tc_direct(int ta, int tb, int M, int N, int K, float alpha, const float
     p.bias = bias;
     p.tiles_m = pl.tiles_m;
     p.tiles_n = pl.tiles_n;
-    p.tri = tri;
     p.splits = pl.splits;
     p.batch = batch;
     p.tail_first = (int)(units * pl.splits - tail_tiles);
     p.tail_slices = tail_tiles > 0 ? tail_slices : 0;   // 0 = off (launch_direct normalises it)
     p.tail_kbps = tail_kbps;
     p.tail_partial = tail_partial;
+    p.ep_p = ep_p;
+    p.ep_d = ep_d;
+    // The hint works through a table of the slice's tiles (which have work, and which k-blocks); a slice of more than
+    // 64 tiles is computed in full instead (the hint never changes values that may be read).
+    p.tri_n = 0;
+    p.tri = 0;
+    if (tri != 0 && pl.splits == 1 && pl.tiles_m * pl.tiles_n <= 64 && pl.k_blocks < 65536) {
+        p.tri = tri;
+        // k-blocks every tile of a slice needs under the hint; the table lists the tiles with work, dearest first
+        struct Ent { int cost; unsigned short code, kf; };
+        Ent ent[64];
+        int n = 0;
+        for (int tm = 0; tm < pl.tiles_m; tm++)
+            for (int tn = 0; tn < pl.tiles_n; tn++) {
+                const int row0 = tm * 2 * kTileM, col0 = tn * pl.bn;
+                int lo = 0, hi = pl.k_blocks;
+                if (tri == ZNN_TRI_C_LOWER) { if (col0 > row0 + 2 * kTileM - 1) hi = 0; }
+                else if (tri == ZNN_TRI_A_LOWER) { const int h2 = (row0 + 2 * kTileM + kBK - 1) / kBK; if (h2 < hi) hi = h2; }
+                else if (tri == ZNN_TRI_A_UPPER) { lo = row0 / kBK < hi ? row0 / kBK : hi; }
+                else if (tri == ZNN_TRI_B_LOWER) { lo = col0 / kBK < hi ? col0 / kBK : hi; }
+                // a tile without k-blocks still has to be stored (zeros, or beta * C) unless it lies above the diagonal
+                if (hi - lo <= 0 && tri == ZNN_TRI_C_LOWER) continue;
+                ent[n].cost = hi - lo > 0 ? hi - lo : 0;
+                ent[n].kf = (unsigned short)lo;
+                ent[n].code = (unsigned short)((tm << 8) | tn);
+                n++;
+            }
+        for (int i = 1; i < n; i++) {   // insertion sort, dearest first (stable)
+            const Ent x = ent[i];
+            int j = i - 1;
+            while (j >= 0 && ent[j].cost < x.cost) { ent[j + 1] = ent[j]; j--; }
+            ent[j + 1] = x;
+        }
+        for (int i = 0; i < n; i++) {
+            p.tri_tab[i] = ent[i].code;
+            p.tri_kf[i] = ent[i].kf;
+            p.tri_kc[i] = (unsigned short)ent[i].cost;
+        }
+        p.tri_n = n;
+    }
     p.alpha = alpha; p.beta = beta; p.C = C; p.ldc = ldc; p.stride_c = stride_c; p.status = status;
     if (pl.bn == 256) rc = launch_direct_major<256>(a_mn, b_mn, ma, mb, p, batch);
     else if (pl.bn == 128) rc = launch_direct_major<128>(a_mn, b_mn, ma, mb, p, batch);

@@ -120,6 +120,12 @@ bool claim_grad_overwrite(Tensor* t)
 
 void mark_grad_written(Tensor* t) { grad_root(t)->grad_valid = true; }
 
+bool grad_is_fresh(Tensor* t) { return t->grad && !grad_root(t)->grad_valid; }
+
+static bool g_fused_softmax_bwd = true;
+void set_fused_softmax_bwd(bool on) { g_fused_softmax_bwd = on; }
+bool fused_softmax_bwd() { return g_fused_softmax_bwd; }
+
 Tensor* Graph::new_tensor(const Shape& shape, bool requires_grad, bool zero_data)
 {
     Tensor* t = new Tensor();
@@ -356,6 +362,8 @@ Tensor* Graph::batchMatMul(Tensor* A, Tensor* B, int tri_role)
         throw Error(ZNN_ERR_INVALID, "batchMatMul: a causal role needs square scores");
     Op* op = new_op(OpType::BatchMatMul, {A, B}, C);
     op->tri_role = tri_role;
+    if (tri_role == 2 && A->requires_grad)
+        op->scratch = (float*)arena_->alloc(A->shape.dims[0] * A->shape.dims[1] * A->shape.dims[2] * sizeof(float));
     op->forward();
     return C;
 }
@@ -493,6 +501,10 @@ void Op::backward()
 {
     Tensor* A = inputs[0];
     Tensor* C = outputs[0];
+    if (skip_backward) {   // the consumer's fused backward already produced this op's input gradient
+        skip_backward = false;
+        return;
+    }
     // the upstream gradient is read: zero if no consumer wrote it
     ensure_grad(C);
     // arms that only add need a defined buffer; the GEMM arms below overwrite a fresh one instead (beta = 0)
@@ -647,7 +659,27 @@ void Op::backward()
         // role 2: A->grad = dP is read below the diagonal only, and A^T = P^T is upper-triangular
         const int tri_da = tri_role == 1 ? ZNN_TRI_A_LOWER : tri_role == 2 ? ZNN_TRI_C_LOWER : ZNN_TRI_NONE;
         const int tri_db = tri_role == 1 ? ZNN_TRI_B_LOWER : tri_role == 2 ? ZNN_TRI_A_UPPER : ZNN_TRI_NONE;
-        if (A->requires_grad) {
+        // Role 2 with the probabilities coming straight from a CausalSoftmax whose input gradient is still fresh: produce
+        // the gradient of the scores in the epilogue of dO.V^T (znn_attn_dscores); dP is never written and the softmax's
+        // own backward is skipped.  (Role 2 asserts that the probabilities have no other consumer.)
+        bool fused_done = false;
+        if (tri_role == 2 && g_fused_softmax_bwd && scratch && A->requires_grad && A->creator &&
+            A->creator->type == OpType::CausalSoftmax && grad_is_fresh(A)) {
+            Op* sm = A->creator;
+            Tensor* S = sm->inputs[0];
+            if (S->requires_grad && grad_is_fresh(S)) {
+                check(znn_rowdot(C->grad, C->data, scratch, (size_t)nb * M, N), "attention D vector");
+                const int rc = znn_attn_dscores(C->grad, B->data, A->data, scratch, sm->scalar, S->grad, M, N, nb);
+                if (rc == ZNN_OK) {
+                    claim_grad_overwrite(S);
+                    sm->skip_backward = true;
+                    fused_done = true;
+                } else if (rc != ZNN_ERR_UNSUPPORTED) {
+                    check(rc, "fused attention score gradient");
+                }
+            }
+        }
+        if (A->requires_grad && !fused_done) {
             // (with ZNN_TRI_C_LOWER a fresh dP keeps undefined values above the diagonal, where nobody reads)
             const float beta = claim_grad_overwrite(A) ? 0.0f : 1.0f;
             check(znn_sgemm_batched_strided_tri(ZNN_NO_TRANS, ZNN_TRANS, M, K, N, 1.0f, C->grad, N, (long long)M * N, B->data,

@@ -61,9 +61,15 @@ struct Tensor {
 void ensure_grad(Tensor* t);
 // For an arm that can overwrite the whole buffer: true = do so (the buffer then counts as written), false = add.
 bool claim_grad_overwrite(Tensor* t);
+// True when nothing has been written or added to t's gradient buffer yet.
+bool grad_is_fresh(Tensor* t);
 // After the caller stored a complete gradient into the buffer.
 void mark_grad_written(Tensor* t);
 // Lazy zero-fill of intermediate gradients (default on; off = every gradient buffer is zero-filled when created).
+// BatchMatMul role 2 backward produces the gradient of the SCORES directly (znn_attn_dscores), skipping dP and the
+// separate softmax backward; default on.
+void set_fused_softmax_bwd(bool on);
+bool fused_softmax_bwd();
 void set_lazy_zero_grad(bool on);
 bool lazy_zero_grad();
 
@@ -86,6 +92,8 @@ struct Op {
     int pool = 0, stride = 0;   // MaxPool2D
     int pad = 0;                // Conv2D (0 = reference)
     int tri_role = 0;           // BatchMatMul next to a causal softmax: 1 = C are the scores, 2 = A are the probabilities
+    float* scratch = nullptr;   // BatchMatMul role 2: one float per probability row (the D vector of the fused backward)
+    bool skip_backward = false; // CausalSoftmax: its input gradient was already produced by the consumer's fused backward
     float* probs = nullptr;     // SoftmaxCrossEntropy: device M x N
     int32_t* targets = nullptr; // SoftmaxCrossEntropy: device int32 labels
     void forward();             // src/autodiff.zig:107-575

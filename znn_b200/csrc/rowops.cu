@@ -489,6 +489,21 @@ __global__ void softmax_rows_bwd_kernel(const float* __restrict__ Y, const float
     }
 }
 
+// out[row] = sum_j a[row,j] * b[row,j], one warp per row
+__global__ void rowdot_kernel(const float* __restrict__ A, const float* __restrict__ B, float* __restrict__ out, size_t rows,
+                              int D)
+{
+    const size_t row = blockIdx.x * (size_t)(blockDim.x >> 5) + (threadIdx.x >> 5);
+    if (row >= rows) return;
+    const int lane = threadIdx.x & 31;
+    const float* a = A + row * D;
+    const float* b = B + row * D;
+    float s = 0.0f;
+    for (int j = lane; j < D; j += 32) s += a[j] * b[j];
+    s = warp_sum(s);
+    if (lane == 0) out[row] = s;
+}
+
 // ---------------------------------------------------------------------------
 // RmsNorm / LayerNorm (one warp per row)
 // ---------------------------------------------------------------------------
@@ -1020,6 +1035,16 @@ int znn_causal_softmax_bwd_set(const float* P, const float* dP, float scale, flo
     const size_t rows = (size_t)nslices * T;
     softmax_rows_bwd_kernel<<<row_blocks(rows, 8), 256, 0, stream()>>>(P, dP, scale, dS, rows, T, 1, 1);
     ZNN_LAUNCH_OK("causal softmax bwd (set)");
+    return ZNN_OK;
+}
+
+int znn_rowdot(const float* A, const float* B, float* out, size_t rows, int D)
+{
+    if (rows == 0 || D <= 0) return ZNN_OK;
+    ZNN_NEED_DEVICE();
+    ZNN_REQUIRE(A && B && out, "NULL pointer");
+    rowdot_kernel<<<row_blocks(rows, 8), 256, 0, stream()>>>(A, B, out, rows, D);
+    ZNN_LAUNCH_OK("rowdot_kernel");
     return ZNN_OK;
 }
 

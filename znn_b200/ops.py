@@ -316,6 +316,32 @@ def causal_softmax_bwd_set(P, dP, scale, dS):
     o.into(dS)
 
 
+def attn_dscores(dO, V, P, scale):
+    """dS = scale * P o (dO.V^T - D), D = rowsum(dO o O) with O = P.V (computed here on the host in fp64 -> fp32);
+    returns dS (tiles entirely above the diagonal keep the zeros they are given here)."""
+    _ensure()
+    dO, V, P = _f(dO), _f(V), _f(P)
+    ns, T, hs = dO.shape
+    O = (P.astype(np.float64) @ V.astype(np.float64))
+    D = np.ascontiguousarray((dO.astype(np.float64) * O).sum(-1).astype(np.float32))
+    d_do, d_v, d_p, d_d = _up(dO), _up(V), _up(P), _up(D)
+    out = np.zeros((ns, T, T), np.float32)
+    d_out = _up(out)
+    lib().call("znn_attn_dscores", d_do.ptr, d_v.ptr, d_p.ptr, d_d.ptr, scale, d_out.ptr, T, hs, ns)
+    check_device_status()
+    d_out.into(out)
+    return out
+
+
+def rowdot(A, B):
+    _ensure()
+    A, B = _f(A), _f(B)
+    rows, D = A.shape
+    a, b, o = _up(A), _up(B), DevBuf(rows * 4)
+    lib().call("znn_rowdot", a.ptr, b.ptr, o.ptr, rows, D)
+    return o.to_host((rows,))
+
+
 def rmsnorm_fwd(X, G, eps):
     _ensure()
     X, G = _f(X), _f(G)
