@@ -2,21 +2,19 @@
 //
 //   C[M,N] = alpha * op(A) * op(B) + beta * C        (row-major, fp32)
 //
-// Two steps per call:
-//  1. split pre-pass (HBM-bound): op(A) and op(B) are rewritten into K-major
-//     planes  X_hi = rn_tf32(X),  X_lo = rn_tf32(X - X_hi), zero padded in K to
-//     a multiple of 32, so that the contraction below only ever sees K-major
-//     TF32-exact operands whatever the caller's transpose flags / strides.
-//  2. tcgen05 kernel: per k-block of 32, TMA brings A_hi, A_lo, B_hi, B_lo tiles
-//     (128-byte swizzle) into a shared-memory ring; one thread issues
-//     tcgen05.mma.kind::tf32 for lo*hi, hi*lo and hi*hi (3xTF32; lo*lo is below
-//     fp32 resolution) accumulating in fp32 in tensor memory; four epilogue
-//     warps read the accumulator with tcgen05.ld and apply alpha/beta.
-//     Variants: one CTA per 128xBN tile, or a CTA pair (cta_group::2) per
-//     256xBN tile in which each CTA loads its own half of A and B (plain TMA
-//     loads, no multicast).
-// Every mbarrier wait is bounded: on expiry the role sets a bit in the device
-// status word and leaves; later CTAs see the word and return at once.
+// Each product is three tcgen05.mma.kind::tf32 passes over a hi/lo split of the operands (lo*hi, hi*lo, hi*hi;
+// lo*lo is below fp32 resolution), accumulated in fp32 in tensor memory in chunks of 256 contraction elements that
+// the epilogue warps add up in registers (the tensor core's accumulator truncates).  Two kernels:
+//
+//  * gemm3x_direct_kernel (the default): TMA reads the caller's matrices in place, K-major or MN-major; converter
+//    warps write the lo plane next to each landed tile; CTA pairs (cta_group::2) on 256 x BN tiles; persistent (one
+//    pair per SM pair walks the tiles, the epilogue of one tile overlaps the main loop of the next); optional
+//    split-K, tail split of a thin last round, triangular-structure hints, fused bias and softmax-backward epilogues.
+//  * gemm3x_tf32_kernel (operands the TMA cannot read in place: unaligned bases or leading dimensions): a split
+//    pre-pass rewrites op(A) and op(B) as K-major hi/lo planes in scratch, then one CTA or a CTA pair per tile.
+//
+// No TMA multicast anywhere (each CTA loads its own half of A and B).  Every mbarrier wait is bounded: on expiry the
+// role sets a bit in the device status word and leaves; later CTAs and kernels see the word and return at once.
 #include <cuda.h>
 
 #include <stdlib.h>
@@ -632,16 +630,17 @@ __global__ void split_transpose_kernel(const float* __restrict__ X, long long ld
 // ---------------------------------------------------------------------------
 // the direct GEMM kernel: no pre-pass, the hi/lo split happens in shared memory
 // ---------------------------------------------------------------------------
-// Operands are read by TMA straight from the caller's fp32 matrices, K-major
-// (the contraction index contiguous) or MN-major (the row/column index
-// contiguous), whatever the transpose flags give, so nothing is transposed or
-// copied in HBM.  Two converter warps rewrite each landed tile in place as
-// hi = rn_tf32(x) and store lo = rn_tf32(x - hi) next to it; the conversion is
-// elementwise, so it is blind to the 128-byte swizzle.  CTA pairs only.
+// Operands are read by TMA straight from the caller's fp32 matrices, K-major (the contraction index contiguous) or
+// MN-major (the row/column index contiguous), whatever the transpose flags give, so nothing is transposed or copied
+// in HBM.  Converter warps store lo = x - (x with the 13 low mantissa bits cleared) next to each landed tile; the raw
+// tile itself serves as hi (the tensor core ignores those 13 bits); the conversion is elementwise, so it is blind to
+// the 128-byte swizzle.  CTA pairs only.
 //   16 warps: 0 TMA, 1 MMA + TMEM, 2-7 converters, 8-15 epilogue.  The converters work as two groups of
 //   three warps that take alternate pipeline stages, so that one group's proxy fence and barrier arrival
 //   overlap the other group's conversion.  The epilogue warps hold 128 accumulators per thread, so registers
-//   are moved to them with setmaxnreg (warpgroups 0-1 shrink to 56, warpgroups 2-3 grow to 200).
+//   are moved to them with setmaxnreg (warpgroups 0-1 shrink to 56, warpgroups 2-3 grow to 200); the code of the
+//   56-register roles has to stay lean: spills there cost 6 % of the 8192^3 product when they crept in once (`-Xptxas -v`
+//   shows them; the few bytes the 200-register epilogue role spills today cost nothing measurable).
 constexpr int kDirectThreads = 512;
 constexpr int kConvWarps = 3;     // warps per converter group
 constexpr int kConvGroups = 2;
