@@ -15,6 +15,15 @@ over ranks divided by the slowest rank's time.
 --impl reference times the reference's CPU path for the same step: the oracle's
 restatement of the MatMul arms with cblas_sgemm bound to the host OpenBLAS (all
 host threads), on a bounded sample size.
+
+The default run (--workload all) prints ONE JSON line: the MatMul step (value, roofline of the tensor-core kernel,
+e2e through znn_matmul_host_fwd_bwd with pinned host tensors, cpu_baseline, clocks) with a "gpt" object inside
+(GPT training step of the workload definition, tokens/s).  Other workloads, one JSON line each:
+  --workload matmul | gpt   one of the two parts alone (used for profiler captures)
+  --workload sweep          every shape of the MatMul sweep, forward and both backward products
+  --workload configs        MLP / CNN / transformer-block / greedy-decode configurations
+  --workload rowops         HBM bandwidth of the row-wise kernels
+  --workload shape --shape M,N,K,ta,tb,batch [--path P]   one (batched) product, for small-case captures
 """
 import argparse
 import ctypes as C
