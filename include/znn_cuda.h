@@ -247,6 +247,10 @@ int znn_argmax(const float* A, float* out, int M, int N, int dim);
 /* SGD with optional momentum: src/optim.zig:50-66. v may be NULL when momentum == 0.
  * grad_scale multiplies the gradient first (1.0 = reference; 1/world for data parallel). */
 int znn_sgd_step(float* w, const float* g, float* v, float lr, float momentum, float grad_scale, size_t n);
+/* Adam: src/optim.zig:133-151.  t = step count after the increment (1 for the first step); the bias-corrected step size
+ * lr*sqrt(1-beta2^t)/(1-beta1^t) is computed on the host in fp32 as the reference does; m, v are the moment buffers. */
+int znn_adam_step(float* w, const float* g, float* m, float* v, float lr, float beta1, float beta2, float eps, float t,
+                  float grad_scale, size_t n);
 /* fill helpers (src/tensor.zig:354-379 fills; used for dC = 1 seeds and zeroGrad) */
 int znn_fill(float* dst, float value, size_t n);
 

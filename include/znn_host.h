@@ -54,6 +54,12 @@ int znn_model_param_count(znn_model* m, int* n);
 int znn_model_param_info(znn_model* m, int i, char* name, size_t name_len, long long* dims8, int* rank,
                          long long* offset, long long* fan_in);
 int znn_model_total_floats(znn_model* m, long long* total);   /* slab length incl. alignment padding */
+/* Checkpoint files byte-compatible with the reference's saveModel / loadModel (src/nn.zig:268-382): 8-byte little-endian
+ * header length, a safetensors-style JSON header (entries in parameter order, no spaces, padded with spaces to a multiple
+ * of 8), then the fp32 data in the same order.  Loading checks names, dtype, shapes, sizes and that offsets do not go
+ * backwards, as the reference does. */
+int znn_model_save(znn_model* m, const char* path);
+int znn_model_load(znn_model* m, const char* path);
 int znn_model_set_params(znn_model* m, const float* host_slab);
 int znn_model_get_params(znn_model* m, float* host_slab);
 int znn_model_get_grads(znn_model* m, float* host_slab);

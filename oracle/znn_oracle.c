@@ -567,6 +567,20 @@ void zo_argmax(const float *A, float *out, int M, int N, int dim)
     }
 }
 
+/* src/optim.zig:133-151 (AdamOptimizer.step): t is the step count AFTER the increment; lr_t as the reference computes it */
+void zo_adam_step(float *w, const float *g, float *m, float *v, float lr, float beta1, float beta2, float eps, float t,
+                  size_t n)
+{
+    const float correction1 = 1.0f - powf(beta1, t);
+    const float correction2 = 1.0f - powf(beta2, t);
+    const float lr_t = lr * sqrtf(correction2) / correction1;
+    for (size_t i = 0; i < n; i++) {
+        m[i] = beta1 * m[i] + (1.0f - beta1) * g[i];
+        v[i] = beta2 * v[i] + (1.0f - beta2) * g[i] * g[i];
+        w[i] -= lr_t * m[i] / (sqrtf(v[i]) + eps);
+    }
+}
+
 /* src/optim.zig:50-66 */
 void zo_sgd_step(float *w, const float *g, float *v, float lr, float momentum, size_t n)
 {

@@ -125,6 +125,8 @@ void zo_mul_scalar_bwd(const float *dC, float v, float *dA, size_t n);
 void zo_argmax(const float *A, float *out, int M, int N, int dim);
 /* SGD: src/optim.zig:50-66 (v may be NULL when momentum == 0) */
 void zo_sgd_step(float *w, const float *g, float *v, float lr, float momentum, size_t n);
+void zo_adam_step(float *w, const float *g, float *m, float *v, float lr, float beta1, float beta2, float eps, float t,
+                  size_t n);
 
 #ifdef __cplusplus
 }

@@ -327,5 +327,11 @@ def argmax(A, dim):
     return out
 
 
+def adam_step(w, g, m, v, lr, beta1, beta2, eps, t):
+    """AdamOptimizer.step (src/optim.zig:133-151) in place; t = step count after the increment."""
+    lib().zo_adam_step(_p(w), _p(g), _p(m), _p(v), C.c_float(lr), C.c_float(beta1), C.c_float(beta2), C.c_float(eps),
+                       C.c_float(t), C.c_size_t(w.size))
+
+
 def sgd_step(w, g, v, lr, momentum):
     lib().zo_sgd_step(_p(w), _p(g), _p(v), C.c_float(lr), C.c_float(momentum), C.c_size_t(w.size))

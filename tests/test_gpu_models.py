@@ -286,3 +286,33 @@ def test_gpt_long_context_against_the_oracle(Model):
     literal reference sequence (full products, materialised -1e9 mask, transposed copy of K, separate gradients)."""
     cfg = {"vocab_size": 96, "block_size": 512, "n_embd": 128, "n_head": 2, "n_layer": 1}
     run_training(Model, "gpt", (96, 512, 128, 2, 1), cfg, 3, 2, 0.05, 0.9, seed=41, seq=512, vocab=96)
+
+
+def test_checkpoint_files_interchange_with_the_reference_layout(Model, tmp_path):
+    """znn_model_save writes byte for byte what the reference's saveModel writes (src/nn.zig:268-303, restated in
+    oracle/checkpoint.py) and znn_model_load reads such a file back, with the reference's checks."""
+    from oracle import checkpoint
+    cfg = {"vocab_size": 29, "block_size": 8, "n_embd": 16, "n_head": 2, "n_layer": 2}
+    P0 = models.init_params("gpt", cfg, seed=2)
+    m = Model("gpt", (29, 8, 16, 2, 2), arena_bytes=64 << 20)
+    m.set_params(P0)
+    ours, ref = tmp_path / "ours.safetensors", tmp_path / "ref.safetensors"
+    m.save(ours)
+    order = [(name, shape) for name, shape, _, _ in m.params]
+    checkpoint.save(ref, [(name, np.asarray(P0[name], np.float32).reshape(shape)) for name, shape in order])
+    assert ours.read_bytes() == ref.read_bytes()
+    # a second model loads the reference-layout file
+    P1 = models.init_params("gpt", cfg, seed=3)
+    m2 = Model("gpt", (29, 8, 16, 2, 2), arena_bytes=64 << 20)
+    m2.set_params(P1)
+    m2.load(ref)
+    got = m2.get_params()
+    for name, shape in order:
+        np.testing.assert_array_equal(got[name], np.asarray(P0[name], np.float32).reshape(shape))
+    # wrong architecture: a shape check fails, as ShapeMismatch / TensorNotFound in the reference
+    m3 = Model("gpt", (29, 8, 32, 2, 2), arena_bytes=64 << 20)
+    with pytest.raises(RuntimeError):
+        m3.load(ref)
+    m4 = Model("gpt", (29, 8, 16, 2, 3), arena_bytes=64 << 20)
+    with pytest.raises(RuntimeError):
+        m4.load(ref)

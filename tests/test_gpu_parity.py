@@ -361,3 +361,20 @@ def test_fused_attention_score_gradient(ops, zo, ns, T, hs):
     close(np.tril(got), np.tril(want), what="fused attention score gradient")
     a, b = r.standard_normal((50, 64), np.float32), r.standard_normal((50, 64), np.float32)
     close(ops.rowdot(a, b), (a.astype(np.float64) * b).sum(1).astype(np.float32), what="rowdot")
+
+
+@pytest.mark.parametrize("n", [1, 7, 1000, 65537])
+def test_adam_step(ops, zo, n):
+    """AdamOptimizer.step (src/optim.zig:133-151): three consecutive steps, bit for bit (no fused multiply-adds)."""
+    r = rng(n)
+    w1 = r.standard_normal(n, np.float32)
+    w2 = w1.copy()
+    m1, v1 = np.zeros(n, np.float32), np.zeros(n, np.float32)
+    m2, v2 = m1.copy(), v1.copy()
+    for t in (1.0, 2.0, 3.0):
+        g = r.standard_normal(n, np.float32)
+        ops.adam_step(w1, g, m1, v1, 1e-3, 0.9, 0.999, 1e-8, t)
+        zo.adam_step(w2, g, m2, v2, 1e-3, 0.9, 0.999, 1e-8, t)
+        np.testing.assert_array_equal(m1, m2)
+        np.testing.assert_array_equal(v1, v2)
+        close(w1, w2, rtol=1e-6, what="adam weights")

@@ -761,6 +761,130 @@ int znn_model_greedy_decode_kv(znn_model* m, const float* prompt_ids, int batch,
     ZNN_HOST_CATCH
 }
 
+// ---- checkpoint files in the reference's layout (src/nn.zig:173-455): 8-byte little-endian header length, a JSON
+// header {"name":{"dtype":"F32","shape":[..],"data_offsets":[start,end]},...} without spaces, entries in parameter
+// (struct-field) order, padded with spaces to a multiple of 8, then the fp32 data back to back in the same order ----
+static std::string checkpoint_header(const ParamStore& ps)
+{
+    std::string h = "{";
+    size_t off = 0;
+    bool first = true;
+    for (const ParamInfo& pi : ps.params()) {
+        if (!first) h += ",";
+        first = false;
+        h += "\"" + pi.name + "\":{\"dtype\":\"F32\",\"shape\":[";
+        for (size_t i = 0; i < pi.tensor->shape.len; i++) {
+            if (i) h += ",";
+            h += std::to_string(pi.tensor->shape.dims[i]);
+        }
+        const size_t bytes = pi.tensor->numel() * 4;
+        h += "],\"data_offsets\":[" + std::to_string(off) + "," + std::to_string(off + bytes) + "]}";
+        off += bytes;
+    }
+    h += "}";
+    h.append((8 - h.size() % 8) % 8, ' ');
+    return h;
+}
+
+int znn_model_save(znn_model* m, const char* path)
+{
+    ZNN_HOST_TRY
+    if (!path) throw Error(ZNN_ERR_INVALID, "path is NULL");
+    const std::string header = checkpoint_header(m->ps);
+    FILE* f = fopen(path, "wb");
+    if (!f) throw Error(ZNN_ERR_INVALID, std::string("cannot create ") + path);
+    const uint64_t hl = header.size();
+    unsigned char le[8];
+    for (int i = 0; i < 8; i++) le[i] = (unsigned char)(hl >> (8 * i));
+    bool ok = fwrite(le, 1, 8, f) == 8 && fwrite(header.data(), 1, header.size(), f) == header.size();
+    std::vector<float> host;
+    for (const ParamInfo& pi : m->ps.params()) {
+        if (!ok) break;
+        host.resize(pi.tensor->numel());
+        check(znn_memcpy_d2h(host.data(), pi.tensor->data, host.size() * sizeof(float)), "read parameter");
+        ok = fwrite(host.data(), sizeof(float), host.size(), f) == host.size();
+    }
+    ok = (fclose(f) == 0) && ok;
+    if (!ok) throw Error(ZNN_ERR_INVALID, std::string("write to ") + path + " failed");
+    ZNN_HOST_CATCH
+}
+
+// value of `"key":` inside the JSON object that starts at obj (a '{'); returns the position after the colon or npos
+static size_t json_member(const std::string& h, size_t obj, size_t obj_end, const char* key)
+{
+    const std::string pat = std::string("\"") + key + "\"";
+    size_t p = h.find(pat, obj);
+    if (p == std::string::npos || p >= obj_end) return std::string::npos;
+    p = h.find(':', p + pat.size());
+    return (p == std::string::npos || p >= obj_end) ? std::string::npos : p + 1;
+}
+
+static std::vector<long long> json_int_array(const std::string& h, size_t p, size_t obj_end)
+{
+    std::vector<long long> v;
+    p = h.find('[', p);
+    if (p == std::string::npos || p >= obj_end) throw Error(ZNN_ERR_INVALID, "checkpoint header: array expected");
+    const size_t e = h.find(']', p);
+    if (e == std::string::npos || e > obj_end) throw Error(ZNN_ERR_INVALID, "checkpoint header: unterminated array");
+    size_t i = p + 1;
+    while (i < e) {
+        while (i < e && (h[i] == ' ' || h[i] == ',')) i++;
+        if (i >= e) break;
+        size_t used = 0;
+        v.push_back(std::stoll(h.substr(i, e - i), &used));
+        i += used;
+    }
+    return v;
+}
+
+int znn_model_load(znn_model* m, const char* path)
+{
+    ZNN_HOST_TRY
+    if (!path) throw Error(ZNN_ERR_INVALID, "path is NULL");
+    FILE* f = fopen(path, "rb");
+    if (!f) throw Error(ZNN_ERR_INVALID, std::string("cannot open ") + path);
+    struct Closer { FILE* f; ~Closer() { if (f) fclose(f); } } closer{f};
+    unsigned char le[8];
+    if (fread(le, 1, 8, f) != 8) throw Error(ZNN_ERR_INVALID, "checkpoint: no header length");
+    uint64_t hl = 0;
+    for (int i = 0; i < 8; i++) hl |= (uint64_t)le[i] << (8 * i);
+    if (hl == 0 || hl > (1ull << 30)) throw Error(ZNN_ERR_INVALID, "checkpoint: implausible header length");
+    std::string h(hl, ' ');
+    if (fread(&h[0], 1, hl, f) != hl) throw Error(ZNN_ERR_INVALID, "checkpoint: truncated header");
+    size_t current = 0;   // the reference reads sequentially and refuses offsets that go backwards (nn.zig:431-434)
+    std::vector<float> host;
+    for (const ParamInfo& pi : m->ps.params()) {
+        const std::string key = "\"" + pi.name + "\"";
+        size_t k = h.find(key + ":");
+        if (k == std::string::npos) k = h.find(key + " :");
+        if (k == std::string::npos) throw Error(ZNN_ERR_INVALID, "checkpoint: tensor '" + pi.name + "' not found in the header");
+        const size_t obj = h.find('{', k + key.size());
+        const size_t obj_end = obj == std::string::npos ? obj : h.find('}', obj);
+        if (obj_end == std::string::npos) throw Error(ZNN_ERR_INVALID, "checkpoint header: malformed entry for " + pi.name);
+        const size_t dt = json_member(h, obj, obj_end, "dtype");
+        if (dt == std::string::npos || h.find("\"F32\"", dt) == std::string::npos || h.find("\"F32\"", dt) > obj_end)
+            throw Error(ZNN_ERR_INVALID, "checkpoint: '" + pi.name + "' is not F32");
+        const size_t sh = json_member(h, obj, obj_end, "shape");
+        const size_t of = json_member(h, obj, obj_end, "data_offsets");
+        if (sh == std::string::npos || of == std::string::npos)
+            throw Error(ZNN_ERR_INVALID, "checkpoint header: shape or data_offsets missing for " + pi.name);
+        const std::vector<long long> shape = json_int_array(h, sh, obj_end), offs = json_int_array(h, of, obj_end);
+        if (shape.size() != pi.tensor->shape.len) throw Error(ZNN_ERR_INVALID, "checkpoint: rank mismatch for " + pi.name);
+        for (size_t i = 0; i < shape.size(); i++)
+            if ((size_t)shape[i] != pi.tensor->shape.dims[i]) throw Error(ZNN_ERR_INVALID, "checkpoint: shape mismatch for " + pi.name);
+        const size_t bytes = pi.tensor->numel() * 4;
+        if (offs.size() != 2 || (size_t)(offs[1] - offs[0]) != bytes) throw Error(ZNN_ERR_INVALID, "checkpoint: size mismatch for " + pi.name);
+        if ((size_t)offs[0] < current) throw Error(ZNN_ERR_INVALID, "checkpoint: offsets of '" + pi.name + "' go backwards");
+        if (fseek(f, (long)(8 + hl + (uint64_t)offs[0]), SEEK_SET) != 0) throw Error(ZNN_ERR_INVALID, "checkpoint: seek failed");
+        host.resize(pi.tensor->numel());
+        if (fread(host.data(), 1, bytes, f) != bytes) throw Error(ZNN_ERR_INVALID, "checkpoint: truncated data for " + pi.name);
+        check(znn_memcpy_h2d(pi.tensor->data, host.data(), bytes), "write parameter");
+        check(znn_sync(), "znn_sync");
+        current = (size_t)offs[1];
+    }
+    ZNN_HOST_CATCH
+}
+
 int znn_model_arena_high_water(znn_model* m, long long* bytes)
 {
     ZNN_HOST_TRY

@@ -794,6 +794,23 @@ __global__ void argmax_cols_kernel(const float* __restrict__ A, float* __restric
     out[j] = (float)mi;
 }
 
+// src/optim.zig:141-149 per element; lr_t is computed once on the host as the reference does
+__global__ void adam_kernel(float* __restrict__ w, const float* __restrict__ g, float* __restrict__ m, float* __restrict__ v,
+                            float lr_t, float beta1, float beta2, float eps, float grad_scale, size_t n)
+{
+    const size_t tid = blockIdx.x * (size_t)blockDim.x + threadIdx.x, nth = (size_t)gridDim.x * blockDim.x;
+    const float ob1 = 1.0f - beta1, ob2 = 1.0f - beta2;
+    for (size_t i = tid; i < n; i += nth) {
+        float gi = g[i];
+        if (grad_scale != 1.0f) gi *= grad_scale;
+        const float mi = beta1 * m[i] + ob1 * gi;
+        const float vi = beta2 * v[i] + ob2 * gi * gi;
+        m[i] = mi;
+        v[i] = vi;
+        w[i] -= lr_t * mi / (sqrtf(vi) + eps);
+    }
+}
+
 __global__ void sgd_kernel(float* __restrict__ w, const float* __restrict__ g, float* __restrict__ v, float lr,
                            float momentum, float grad_scale, size_t n)
 {
@@ -1263,6 +1280,21 @@ int znn_argmax(const float* A, float* out, int M, int N, int dim)
     if (dim == 1) argmax_rows_kernel<<<ceil_div(M, 8), 256, 0, stream()>>>(A, out, M, N);
     else argmax_cols_kernel<<<ceil_div(N, 128), 128, 0, stream()>>>(A, out, M, N);
     ZNN_LAUNCH_OK("argmax kernel");
+    return ZNN_OK;
+}
+
+int znn_adam_step(float* w, const float* g, float* m, float* v, float lr, float beta1, float beta2, float eps, float t,
+                  float grad_scale, size_t n)
+{
+    if (n == 0) return ZNN_OK;
+    ZNN_NEED_DEVICE();
+    ZNN_REQUIRE(w && g && m && v, "NULL pointer");
+    ZNN_REQUIRE(t >= 1.0f, "t is the step count after the increment (>= 1)");
+    const float correction1 = 1.0f - powf(beta1, t);
+    const float correction2 = 1.0f - powf(beta2, t);
+    const float lr_t = lr * sqrtf(correction2) / correction1;
+    adam_kernel<<<ew_blocks(n), kEwThreads, 0, stream()>>>(w, g, m, v, lr_t, beta1, beta2, eps, grad_scale, n);
+    ZNN_LAUNCH_OK("adam_kernel");
     return ZNN_OK;
 }
 

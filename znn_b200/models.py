@@ -62,6 +62,13 @@ class Model:
         lib().call(fn, self.h, slab.ctypes.data)
         return self._unpack(slab)
 
+    def save(self, path):
+        """Checkpoint in the reference's safetensors-style layout (src/nn.zig:268-303)."""
+        lib().call("znn_model_save", self.h, str(path).encode())
+
+    def load(self, path):
+        lib().call("znn_model_load", self.h, str(path).encode())
+
     def get_params(self): return self._get("znn_model_get_params")
     def get_grads(self): return self._get("znn_model_get_grads")
     def get_velocities(self): return self._get("znn_model_get_velocities")

@@ -316,6 +316,16 @@ def causal_softmax_bwd_set(P, dP, scale, dS):
     o.into(dS)
 
 
+def adam_step(w, g, m, v, lr, beta1, beta2, eps, t, grad_scale=1.0):
+    """In place on the host arrays w, m, v."""
+    _ensure()
+    dw, dg, dm, dv = _up(w), _up(g), _up(m), _up(v)
+    lib().call("znn_adam_step", dw.ptr, dg.ptr, dm.ptr, dv.ptr, lr, beta1, beta2, eps, t, grad_scale, w.size)
+    dw.into(w)
+    dm.into(m)
+    dv.into(v)
+
+
 def attn_dscores(dO, V, P, scale):
     """dS = scale * P o (dO.V^T - D), D = rowsum(dO o O) with O = P.V (computed here on the host in fp64 -> fp32);
     returns dS (tiles entirely above the diagonal keep the zeros they are given here)."""
