@@ -251,6 +251,14 @@ int znn_sgd_step(float* w, const float* g, float* v, float lr, float momentum, f
  * lr*sqrt(1-beta2^t)/(1-beta1^t) is computed on the host in fp32 as the reference does; m, v are the moment buffers. */
 int znn_adam_step(float* w, const float* g, float* m, float* v, float lr, float beta1, float beta2, float eps, float t,
                   float grad_scale, size_t n);
+/* Input pipeline on the device.
+ * znn_pixels_to_unit: IDX pixel bytes -> fp32 pixel / 255.0, the conversion of loadImages (src/dataset.zig:53-63).
+ * znn_batch_gather: the copy loop of DataLoader.nextInto (src/dataset.zig:211-220): for j < batch,
+ *   x_dest[j, :] = images[indices[j], :] (input_dim floats) and y_dest[j] = labels[indices[j]].
+ *   images, labels, indices and both destinations are device memory; labels and y_dest may both be NULL. */
+int znn_pixels_to_unit(const uint8_t* pixels, float* out, size_t n);
+int znn_batch_gather(const float* images, const uint8_t* labels, const int32_t* indices, float* x_dest, uint8_t* y_dest,
+                     int batch, int input_dim);
 /* fill helpers (src/tensor.zig:354-379 fills; used for dC = 1 seeds and zeroGrad) */
 int znn_fill(float* dst, float value, size_t n);
 

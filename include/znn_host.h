@@ -95,6 +95,27 @@ int znn_model_arena_high_water(znn_model* m, long long* bytes);
 int znn_model_last_step_ops(znn_model* m, int* n_ops);
 int znn_model_graph_replays(znn_model* m, long long* n);
 
+/* ---- input pipeline: src/dataset.zig ------------------------------------------------------------------------------
+ * The dataset stays resident in device memory; a batch is produced by one gather launch, no host data moves.
+ * znn_dataset_load_idx: loadDataset's two readers (src/dataset.zig:23-106): big-endian IDX headers, magic 0x803 /
+ *   0x801 (else an error naming InvalidMagicNumber), pixels as fp32 pixel/255.  Returns device pointers the caller
+ *   frees with znn_free.  The counts are returned as read; the reference does not compare them either.
+ * znn_loader_*: DataLoader (src/dataset.zig:132-223).  seed < 0 = the reference's default 1337.  shuffle permutes
+ *   the order at create and at every reset with the reference's generator and draw (std.Random.DefaultPrng,
+ *   intRangeLessThan).  next_into writes x_dest (n x input_dim fp32) and y_dest (n bytes), both device memory, and
+ *   sets *n = 0 where the reference returns null (epoch finished, or a short tail with drop_last). */
+typedef struct znn_loader znn_loader;
+int znn_dataset_load_idx(const char* images_path, const char* labels_path, float** images, uint8_t** labels,
+                         unsigned* num_images, unsigned* rows, unsigned* cols, unsigned* num_labels);
+int znn_loader_create(const float* images, const uint8_t* labels, size_t num_samples, int input_dim, size_t batch_size,
+                      int shuffle, int drop_last, long long seed, znn_loader** out);
+int znn_loader_destroy(znn_loader* l);
+int znn_loader_reset(znn_loader* l);
+int znn_loader_set_drop_last(znn_loader* l, int drop_last);
+int znn_loader_peek_next_batch_size(znn_loader* l, size_t* n);
+int znn_loader_next_into(znn_loader* l, float* x_dest, uint8_t* y_dest, size_t* n);
+int znn_loader_indices(znn_loader* l, int32_t* host_out, size_t count);   /* the current sample order */
+
 #ifdef __cplusplus
 }
 #endif

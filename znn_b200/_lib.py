@@ -21,6 +21,9 @@ _CTYPES = {
     "double*": C.POINTER(C.c_double), "const double*": C.c_void_p, "const long long*": C.c_void_p,
     "const int*": C.c_void_p, "znn_graph*": C.c_void_p, "znn_model*": C.c_void_p,
     "znn_graph**": C.POINTER(C.c_void_p), "znn_model**": C.POINTER(C.c_void_p),
+    "uint8_t*": C.c_void_p, "float**": C.POINTER(C.c_void_p), "uint8_t**": C.POINTER(C.c_void_p),
+    "unsigned*": C.POINTER(C.c_uint), "size_t*": C.POINTER(C.c_size_t),
+    "znn_loader*": C.c_void_p, "znn_loader**": C.POINTER(C.c_void_p),
 }
 
 

@@ -30,6 +30,7 @@ SOURCES = [
     ("host/graph.cpp", []),
     ("host/nn.cpp", []),
     ("host/capi.cpp", []),
+    ("host/dataset.cpp", []),
 ]
 
 

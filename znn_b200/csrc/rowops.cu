@@ -4,6 +4,7 @@
 // same rounding points costs nothing and keeps results close to bit-identical.
 #include <math_constants.h>
 
+#include <algorithm>
 #include <mutex>
 
 #include "common.cuh"
@@ -843,6 +844,38 @@ __global__ void sgd_kernel(float* __restrict__ w, const float* __restrict__ g, f
     for (size_t i = n4 * 4 + tid; i < n; i += nth) upd(w[i], g[i], v ? v + i : nullptr);
 }
 
+// pixel bytes -> fp32 in [0, 1]: IEEE division by 255 as the reference's loader does per pixel
+__global__ void pixels_to_unit_kernel(const uint8_t* __restrict__ px, float* __restrict__ out, size_t n)
+{
+    const size_t tid = (size_t)blockIdx.x * blockDim.x + threadIdx.x, nth = (size_t)gridDim.x * blockDim.x;
+    const size_t n4 = ((reinterpret_cast<uintptr_t>(px) & 3) == 0 && (reinterpret_cast<uintptr_t>(out) & 15) == 0) ? n / 4 : 0;
+    for (size_t i = tid; i < n4; i += nth) {
+        const uchar4 b = reinterpret_cast<const uchar4*>(px)[i];
+        reinterpret_cast<float4*>(out)[i] =
+            make_float4(__fdiv_rn((float)b.x, 255.0f), __fdiv_rn((float)b.y, 255.0f), __fdiv_rn((float)b.z, 255.0f),
+                        __fdiv_rn((float)b.w, 255.0f));
+    }
+    for (size_t i = n4 * 4 + tid; i < n; i += nth) out[i] = __fdiv_rn((float)px[i], 255.0f);
+}
+
+// one batch of sample rows and labels picked by index; blockIdx.y = slot in the batch
+__global__ void batch_gather_kernel(const float* __restrict__ images, const uint8_t* __restrict__ labels,
+                                    const int32_t* __restrict__ indices, float* __restrict__ x_dest,
+                                    uint8_t* __restrict__ y_dest, int input_dim, int vec_ok)
+{
+    const int j = blockIdx.y;
+    const size_t idx = (size_t)indices[j];
+    const float* src = images + idx * (size_t)input_dim;
+    float* dst = x_dest + (size_t)j * input_dim;
+    const int tid = blockIdx.x * blockDim.x + threadIdx.x, nth = gridDim.x * blockDim.x;
+    if (vec_ok) {
+        for (int i = tid; i < input_dim / 4; i += nth) reinterpret_cast<float4*>(dst)[i] = reinterpret_cast<const float4*>(src)[i];
+    } else {
+        for (int i = tid; i < input_dim; i += nth) dst[i] = src[i];
+    }
+    if (tid == 0 && labels && y_dest) y_dest[j] = labels[idx];
+}
+
 }  // namespace znn
 
 using namespace znn;
@@ -853,6 +886,33 @@ using namespace znn;
     } while (0)
 
 extern "C" {
+
+int znn_pixels_to_unit(const uint8_t* pixels, float* out, size_t n)
+{
+    if (n == 0) return ZNN_OK;
+    ZNN_NEED_DEVICE();
+    ZNN_REQUIRE(pixels && out, "pixels/out is NULL");
+    pixels_to_unit_kernel<<<ew_blocks(n), kEwThreads, 0, stream()>>>(pixels, out, n);
+    ZNN_LAUNCH_OK("pixels_to_unit_kernel");
+    return ZNN_OK;
+}
+
+int znn_batch_gather(const float* images, const uint8_t* labels, const int32_t* indices, float* x_dest, uint8_t* y_dest,
+                     int batch, int input_dim)
+{
+    if (batch <= 0 || input_dim <= 0) return ZNN_OK;
+    ZNN_NEED_DEVICE();
+    ZNN_REQUIRE(images && indices && x_dest, "images/indices/x_dest is NULL");
+    ZNN_REQUIRE((labels == nullptr) == (y_dest == nullptr), "labels and y_dest go together");
+    ZNN_REQUIRE(batch <= 65535, "batch exceeds 65535 rows per call");
+    const int vec_ok = input_dim % 4 == 0 && (reinterpret_cast<uintptr_t>(images) & 15) == 0 &&
+                       (reinterpret_cast<uintptr_t>(x_dest) & 15) == 0;
+    const int per_row = vec_ok ? input_dim / 4 : input_dim;
+    const dim3 grid((unsigned)std::min(64, (per_row + kEwThreads - 1) / kEwThreads), (unsigned)batch);
+    batch_gather_kernel<<<grid, kEwThreads, 0, stream()>>>(images, labels, indices, x_dest, y_dest, input_dim, vec_ok);
+    ZNN_LAUNCH_OK("batch_gather_kernel");
+    return ZNN_OK;
+}
 
 int znn_fill(float* dst, float value, size_t n)
 {
