@@ -75,9 +75,17 @@ class ClockSampler:
 
     def _pump(self):
         for line in self.proc.stdout:
-            self.lines.append(line.strip())
+            self.lines.append((time.time(), line.strip()))
 
-    def stop(self):
+    def wait_first_sample(self, limit_s=5.0):
+        """nvidia-smi needs a moment to start; a short timed region would otherwise end before its first line."""
+        t_end = time.time() + limit_s
+        while self.proc and not self.lines and time.time() < t_end:
+            time.sleep(0.01)
+
+    def stop(self, window=None):
+        """window = (t0, t1) host times of the timed region: only samples inside it count; where the region was
+        shorter than two sampling periods, the samples of the warm-up (the same work) are used and the result says so."""
         if not self.proc:
             return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
         self.proc.terminate()
@@ -85,8 +93,12 @@ class ClockSampler:
             self.proc.wait(timeout=5)
         except subprocess.TimeoutExpired:
             self.proc.kill()
+        scope, lines = "whole run", [ln for _, ln in self.lines]
+        if window:
+            inside = [ln for t, ln in self.lines if window[0] <= t <= window[1]]
+            scope, lines = ("timed region", inside) if len(inside) >= 2 else ("warm-up and timed region", lines)
         sm, mx, power, reasons = [], [], [], set()
-        for ln in self.lines:
+        for ln in lines:
             f = [x.strip() for x in ln.split(",")]
             if len(f) < 9:
                 continue
@@ -100,7 +112,8 @@ class ClockSampler:
                 if val.lower().startswith("active"):
                     reasons.add(name)
         return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": max(mx) if mx else None,
-                "power_w_max": max(power) if power else None, "samples": len(sm), "reasons": sorted(reasons)}
+                "power_w_max": max(power) if power else None, "samples": len(sm), "sampled_over": scope,
+                "reasons": sorted(reasons)}
 
 
 # --------------------------------------------------------------------------- CPU side
@@ -265,15 +278,17 @@ def run_gpu(args):
         torch.cuda.synchronize()
 
     # ---- device-resident timing ----
+    sampler = ClockSampler(local)
+    if rank == 0:
+        sampler.start()
+        sampler.wait_first_sample()
     for _ in range(warmup):
         step()
     barrier()
     cnt = C.c_longlong(0)
     L.call("znn_launch_count", C.byref(cnt), 1)
     L.call("znn_gemm_profile", 1)
-    sampler = ClockSampler(local)
-    if rank == 0:
-        sampler.start()
+    t_host0 = time.time()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     e0.record(stream)
     for _ in range(steps):
@@ -281,7 +296,7 @@ def run_gpu(args):
     e1.record(stream)
     barrier()
     ms = e0.elapsed_time(e1)
-    clocks = sampler.stop() if rank == 0 else None
+    clocks = sampler.stop((t_host0, time.time())) if rank == 0 else None
     L.call("znn_launch_count", C.byref(cnt), 1)
     launches = cnt.value
     kms, kl, kfl = C.c_double(0), C.c_longlong(0), C.c_double(0)
