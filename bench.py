@@ -567,6 +567,59 @@ def configs_part(args, L, torch, stream):
                     "e2e_us_per_step": ms_e2e * 1e3, "tape_ops": m.last_step_ops(), "bound": "launch latency"}
         m.close()
 
+    # C1 fed by the device-resident loader: synthetic pixel bytes of the dataset's shape, converted on the device,
+    # shuffled batches gathered on the device; against the same loop fed from host arrays batch by batch
+    from znn_b200 import dataset as zds
+    from znn_b200.ops import DevBuf
+    n_img, batch = 12800, 64
+    px = r.integers(0, 256, (n_img, 784)).astype(np.uint8)
+    lab = r.integers(0, 10, n_img).astype(np.uint8)
+    d_px, d_img, d_lab = DevBuf.from_host(px), DevBuf(n_img * 784 * 4), DevBuf.from_host(lab)
+    L.call("znn_pixels_to_unit", d_px.ptr, d_img.ptr, n_img * 784)
+    data = zds.Dataset(d_img, d_lab, n_img, 28, 28, n_img)
+    loader = zds.DataLoader(data, batch, shuffle=True, drop_last=True)
+    m = Model("mlp", (784, 128, 64, 10), arena_bytes=1 << 30)
+    he(m)
+    m.set_option("lr", 0.01)
+    m.set_option("momentum", 0.9)
+    m.set_option("targets_u8", 1)
+    x_dev, y_dev = DevBuf(batch * 784 * 4), DevBuf(batch)
+
+    def epoch_device():
+        loader.reset()
+        n = 0
+        while loader.next_into(x_dev, y_dev):
+            m.train_step_device(x_dev.ptr, y_dev.ptr, batch)
+            n += 1
+        return n
+
+    images_host = px.astype(np.float32) / np.float32(255.0)
+    order = loader.indices()
+
+    def epoch_host():
+        n = 0
+        for i in range(0, n_img - batch + 1, batch):
+            idx = order[i:i + batch]
+            m.train_step(images_host[idx], lab[idx], read_loss=False)
+            n += 1
+        return n
+
+    res = {}
+    for name, fn in (("device_loader", epoch_device), ("host_batches", epoch_host)):
+        fn()
+        torch.cuda.synchronize()
+        e0.record(stream)
+        steps_run = fn()
+        e1.record(stream)
+        torch.cuda.synchronize()
+        res[name] = e0.elapsed_time(e1) * 1e3 / steps_run
+    out["mlp_epoch_b64_input_pipeline"] = {
+        "us_per_step_device_loader": res["device_loader"], "us_per_step_host_batches": res["host_batches"],
+        "samples": n_img, "note": "device loader: one gather launch per batch, byte labels used in place; host batches: "
+                                  "numpy gather + one upload of pixels and labels per step"}
+    m.close()
+    loader.close()
+
     # C4: pre-norm block, d_model 512, 8 heads, FFN 2048, batch 32 x seq 256 (168 GFLOP per forward+backward)
     m = Model("block", (512, 8), arena_bytes=8 << 30)
     he(m, "n002")

@@ -60,6 +60,11 @@ int znn_model_total_floats(znn_model* m, long long* total);   /* slab length inc
  * backwards, as the reference does. */
 int znn_model_save(znn_model* m, const char* path);
 int znn_model_load(znn_model* m, const char* path);
+/* Optimizer state for resuming (an extension: the reference's file holds parameters only): the SGD velocities in a
+ * second file of the same layout, one entry per parameter under the parameter's name, so the reference's reader and
+ * writer handle it too. */
+int znn_model_save_optimizer(znn_model* m, const char* path);
+int znn_model_load_optimizer(znn_model* m, const char* path);
 int znn_model_set_params(znn_model* m, const float* host_slab);
 int znn_model_get_params(znn_model* m, float* host_slab);
 int znn_model_get_grads(znn_model* m, float* host_slab);
@@ -71,7 +76,9 @@ int znn_model_get_velocities(znn_model* m, float* host_slab);
  * share the gradient buffer of their input instead of adding into it in backward), "lazy_zero_grad" (1/0, process-wide:
  * gradient buffers of intermediates are zero-filled only when first added to; GEMM arms overwrite them with beta = 0), "dp_bucket_floats",
  * "dp_overlap" (1/0), "cuda_graph" (1/0: capture the training step once per (input buffers, batch) and replay it;
- * MLP / CNN models with device-resident inputs on one GPU; lr and momentum are baked in at capture) */
+ * MLP / CNN models with device-resident inputs on one GPU; lr and momentum are baked in at capture),
+ * "targets_u8" (1/0: the targets pointer of znn_model_train_step holds byte labels, the reference's label type,
+ * e.g. the y_dest of znn_loader_next_into; default 0 = int32) */
 int znn_model_set_option(znn_model* m, const char* key, double value);
 /* One training step.  x: [batch, features] pixels (MLP/CNN) or [batch, seq] fp32 token ids (GPT); targets: batch
  * (or batch*seq) int32 labels.  on_device = 1: both pointers are device memory and are used in place.

@@ -139,3 +139,43 @@ def test_loader_feeds_the_loss_kernel(ds):
     lse = np.log(np.exp(z - z.max(1, keepdims=True)).sum(1)) + z.max(1)
     want = float(np.mean(lse - z[np.arange(bs), labels[order]]))
     assert abs(float(loss.to_host((1,))[0]) - want) <= 1e-5 * max(1.0, abs(want))
+
+
+def test_training_fed_by_the_device_loader_equals_training_fed_from_host_batches(ds):
+    """One epoch of the MLP example's loop (examples/fashion_mnist.zig:131-167) twice: batches copied from host
+    arrays in the loader's order with int32 labels, and batches gathered on the device with the byte labels used in
+    place.  Same parameters afterwards, bit for bit."""
+    from oracle import models as omodels
+    from znn_b200 import models
+    r = np.random.default_rng(12)
+    n, bs = 300, 64
+    images = r.random((n, 784), np.float32)
+    labels = r.integers(0, 10, n).astype(np.uint8)
+    P0 = omodels.init_params("mlp", (784, 128, 64, 10), seed=1)
+
+    def fresh(u8):
+        m = models.Model("mlp", (784, 128, 64, 10), arena_bytes=64 << 20)
+        m.set_params(P0)
+        m.set_option("lr", 0.05)
+        m.set_option("momentum", 0.9)
+        m.set_option("cuda_graph", 0)
+        m.set_option("targets_u8", u8)
+        return m
+
+    ref_loader = od.DataLoader(images, labels, bs, shuffle=True, seed=21, drop_last=True)
+    host_fed = fresh(0)
+    x, y = np.zeros((bs, 784), np.float32), np.zeros(bs, np.uint8)
+    while ref_loader.next_into(x, y):
+        host_fed.train_step(x, y.astype(np.int32))
+
+    data = ds.Dataset.from_arrays(images, labels, rows=28, cols=28)
+    loader = ds.DataLoader(data, bs, shuffle=True, seed=21, drop_last=True)
+    dev_fed = fresh(1)
+    x_dev, y_dev = dev_buffers(bs, 784)
+    steps = 0
+    while loader.next_into(x_dev, y_dev):
+        dev_fed.train_step_device(x_dev.ptr, y_dev.ptr, bs)
+        steps += 1
+    assert steps == n // bs
+    a, b = host_fed.get_params(), dev_fed.get_params()
+    assert all(np.array_equal(a[k], b[k]) for k in a)

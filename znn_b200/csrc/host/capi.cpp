@@ -211,6 +211,7 @@ struct znn_model {
     size_t in_features = 0, classes = 0;
     size_t dp_bucket_floats = 8u << 20;  // 32 MB buckets
     bool dp_overlap = true;
+    bool targets_u8 = false;          // targets are bytes, the reference's label type (src/dataset.zig:14-16)
     int last_ops = 0;
     std::unordered_map<const Tensor*, int> param_index;
     // CUDA-graph replay of the training step (option "cuda_graph"): the step's launch sequence is captured once
@@ -477,6 +478,10 @@ int znn_model_set_option(znn_model* m, const char* key, double value)
     }
     else if (k == "dp_bucket_floats") m->dp_bucket_floats = (size_t)value;
     else if (k == "dp_overlap") m->dp_overlap = (value != 0.0);
+    else if (k == "targets_u8") {
+        m->targets_u8 = (value != 0.0);
+        drop_graph(m);
+    }
     else throw Error(ZNN_ERR_INVALID, "unknown option '" + k + "'");
     ZNN_HOST_CATCH
 }
@@ -490,12 +495,14 @@ static float* run_train_step(znn_model* m, const float* x, const int32_t* target
     const size_t rows = (m->kind == ZNN_MODEL_GPT) ? (size_t)batch * seq : (size_t)batch;
     const int32_t* dev_targets = targets;
     if (!on_device) {
-        int32_t* t = (int32_t*)m->arena->alloc(rows * sizeof(int32_t));
-        check(znn_memcpy_h2d(t, targets, rows * sizeof(int32_t)), "upload targets");
+        const size_t bytes = rows * (m->targets_u8 ? 1 : sizeof(int32_t));
+        int32_t* t = (int32_t*)m->arena->alloc(bytes);
+        check(znn_memcpy_h2d(t, targets, bytes), "upload targets");
         dev_targets = t;  // the stream synchronisation of the input upload below covers this copy
     }
     Tensor* logits = model_forward(*m, g, x, batch, seq, on_device);
-    Tensor* loss = g.softmaxCrossEntropy(logits, dev_targets);
+    Tensor* loss = m->targets_u8 ? g.softmaxCrossEntropyU8(logits, reinterpret_cast<const uint8_t*>(dev_targets))
+                                 : g.softmaxCrossEntropy(logits, dev_targets);
     m->ps.zeroGrad();                        // model.zeroGrad() (fashion_mnist.zig:155)
     int world = 1;
     znn_dp_world(&world, nullptr);
@@ -786,9 +793,9 @@ static std::string checkpoint_header(const ParamStore& ps)
     return h;
 }
 
-int znn_model_save(znn_model* m, const char* path)
+// slab = the values slab (the model file) or the velocity slab (the optimizer-state file): same layout, same offsets
+static void save_slab(znn_model* m, const char* path, float* slab)
 {
-    ZNN_HOST_TRY
     if (!path) throw Error(ZNN_ERR_INVALID, "path is NULL");
     const std::string header = checkpoint_header(m->ps);
     FILE* f = fopen(path, "wb");
@@ -801,11 +808,24 @@ int znn_model_save(znn_model* m, const char* path)
     for (const ParamInfo& pi : m->ps.params()) {
         if (!ok) break;
         host.resize(pi.tensor->numel());
-        check(znn_memcpy_d2h(host.data(), pi.tensor->data, host.size() * sizeof(float)), "read parameter");
+        check(znn_memcpy_d2h(host.data(), slab + pi.offset, host.size() * sizeof(float)), "read parameter");
         ok = fwrite(host.data(), sizeof(float), host.size(), f) == host.size();
     }
     ok = (fclose(f) == 0) && ok;
     if (!ok) throw Error(ZNN_ERR_INVALID, std::string("write to ") + path + " failed");
+}
+
+int znn_model_save(znn_model* m, const char* path)
+{
+    ZNN_HOST_TRY
+    save_slab(m, path, m->ps.values());
+    ZNN_HOST_CATCH
+}
+
+int znn_model_save_optimizer(znn_model* m, const char* path)
+{
+    ZNN_HOST_TRY
+    save_slab(m, path, m->ps.velocities());
     ZNN_HOST_CATCH
 }
 
@@ -837,9 +857,8 @@ static std::vector<long long> json_int_array(const std::string& h, size_t p, siz
     return v;
 }
 
-int znn_model_load(znn_model* m, const char* path)
+static void load_slab(znn_model* m, const char* path, float* slab)
 {
-    ZNN_HOST_TRY
     if (!path) throw Error(ZNN_ERR_INVALID, "path is NULL");
     FILE* f = fopen(path, "rb");
     if (!f) throw Error(ZNN_ERR_INVALID, std::string("cannot open ") + path);
@@ -878,10 +897,23 @@ int znn_model_load(znn_model* m, const char* path)
         if (fseek(f, (long)(8 + hl + (uint64_t)offs[0]), SEEK_SET) != 0) throw Error(ZNN_ERR_INVALID, "checkpoint: seek failed");
         host.resize(pi.tensor->numel());
         if (fread(host.data(), 1, bytes, f) != bytes) throw Error(ZNN_ERR_INVALID, "checkpoint: truncated data for " + pi.name);
-        check(znn_memcpy_h2d(pi.tensor->data, host.data(), bytes), "write parameter");
+        check(znn_memcpy_h2d(slab + pi.offset, host.data(), bytes), "write parameter");
         check(znn_sync(), "znn_sync");
         current = (size_t)offs[1];
     }
+}
+
+int znn_model_load(znn_model* m, const char* path)
+{
+    ZNN_HOST_TRY
+    load_slab(m, path, m->ps.values());
+    ZNN_HOST_CATCH
+}
+
+int znn_model_load_optimizer(znn_model* m, const char* path)
+{
+    ZNN_HOST_TRY
+    load_slab(m, path, m->ps.velocities());
     ZNN_HOST_CATCH
 }
 

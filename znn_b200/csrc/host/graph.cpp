@@ -221,6 +221,18 @@ Tensor* Graph::softmaxCrossEntropy(Tensor* logits, const int32_t* dev_targets)
     return loss;
 }
 
+Tensor* Graph::softmaxCrossEntropyU8(Tensor* logits, const uint8_t* dev_targets)
+{
+    if (logits->shape.len != 2) throw Error(ZNN_ERR_INVALID, "softmaxCrossEntropy needs 2-D logits");
+    Tensor* loss = new_tensor(Shape{1, 1}, logits->requires_grad, false);
+    Op* o = new_op(OpType::SoftmaxCrossEntropy, {logits}, loss);
+    o->probs = (float*)arena_->alloc(logits->numel() * sizeof(float));
+    o->targets = reinterpret_cast<int32_t*>(const_cast<uint8_t*>(dev_targets));
+    o->targets_u8 = true;
+    o->forward();
+    return loss;
+}
+
 static bool g_alias_reshape_grad = true;
 void set_alias_reshape_grad(bool on) { g_alias_reshape_grad = on; }
 bool alias_reshape_grad() { return g_alias_reshape_grad; }
@@ -416,7 +428,9 @@ void Op::forward()
     case OpType::Relu: check(znn_relu_fwd(A->data, C->data, A->numel()), "Relu forward"); break;
     case OpType::Gelu: check(znn_gelu_fwd(A->data, C->data, A->numel()), "Gelu forward"); break;
     case OpType::SoftmaxCrossEntropy:
-        check(znn_softmax_xent_fwd(A->data, targets, probs, C->data, (int)A->shape.dims[0], (int)A->shape.dims[1]),
+        check(targets_u8 ? znn_softmax_xent_fwd_u8(A->data, reinterpret_cast<const uint8_t*>(targets), probs, C->data,
+                                                   (int)A->shape.dims[0], (int)A->shape.dims[1])
+                         : znn_softmax_xent_fwd(A->data, targets, probs, C->data, (int)A->shape.dims[0], (int)A->shape.dims[1]),
               "SoftmaxCrossEntropy forward");
         break;
     case OpType::Reshape: break;  // aliased data (autodiff.zig:272-275)
@@ -549,7 +563,9 @@ void Op::backward()
         // ignores loss.grad and has no requires_grad gate, as the reference (:758-774); a logits
         // tensor without a grad buffer simply has nothing to receive it
         if (A->grad)
-            check(znn_softmax_xent_bwd(probs, targets, A->grad, (int)A->shape.dims[0], (int)A->shape.dims[1]),
+            check(targets_u8 ? znn_softmax_xent_bwd_u8(probs, reinterpret_cast<const uint8_t*>(targets), A->grad,
+                                                       (int)A->shape.dims[0], (int)A->shape.dims[1])
+                             : znn_softmax_xent_bwd(probs, targets, A->grad, (int)A->shape.dims[0], (int)A->shape.dims[1]),
                   "SoftmaxCrossEntropy backward");
         break;
     case OpType::Reshape:

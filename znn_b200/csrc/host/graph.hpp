@@ -95,7 +95,8 @@ struct Op {
     float* scratch = nullptr;   // BatchMatMul role 2: one float per probability row (the D vector of the fused backward)
     bool skip_backward = false; // CausalSoftmax: its input gradient was already produced by the consumer's fused backward
     float* probs = nullptr;     // SoftmaxCrossEntropy: device M x N
-    int32_t* targets = nullptr; // SoftmaxCrossEntropy: device int32 labels
+    int32_t* targets = nullptr; // SoftmaxCrossEntropy: device int32 labels (device bytes when targets_u8)
+    bool targets_u8 = false;
     void forward();             // src/autodiff.zig:107-575
     void backward();            // src/autodiff.zig:579-1231
 };
@@ -143,6 +144,7 @@ public:
     Tensor* relu(Tensor* A);                                                // :1478
     Tensor* gelu(Tensor* A);                                                // :1508
     Tensor* softmaxCrossEntropy(Tensor* logits, const int32_t* dev_targets); // :1630 (int32 labels on device)
+    Tensor* softmaxCrossEntropyU8(Tensor* logits, const uint8_t* dev_targets); // the reference's own label type (u8)
     Tensor* reshape(Tensor* A, const Shape& new_shape);                     // :1329 (aliases data, own grad)
     Tensor* transposeND(Tensor* A, int dim0, int dim1);                     // :1378
     Tensor* mulScalar(Tensor* A, float v);                                  // :1910

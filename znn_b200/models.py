@@ -69,16 +69,25 @@ class Model:
     def load(self, path):
         lib().call("znn_model_load", self.h, str(path).encode())
 
+    def save_optimizer(self, path):
+        """The SGD velocities in a second file of the same layout (resume = load + load_optimizer)."""
+        lib().call("znn_model_save_optimizer", self.h, str(path).encode())
+
+    def load_optimizer(self, path):
+        lib().call("znn_model_load_optimizer", self.h, str(path).encode())
+
     def get_params(self): return self._get("znn_model_get_params")
     def get_grads(self): return self._get("znn_model_get_grads")
     def get_velocities(self): return self._get("znn_model_get_velocities")
 
     def set_option(self, key, value):
         lib().call("znn_model_set_option", self.h, key.encode(), float(value))
+        if key == "targets_u8":
+            self._targets_u8 = bool(value)
 
     def train_step(self, x, targets, seq=0, read_loss=True):
         x = np.ascontiguousarray(x, np.float32)
-        t = np.ascontiguousarray(targets, np.int32)
+        t = np.ascontiguousarray(targets, np.uint8 if getattr(self, "_targets_u8", False) else np.int32)
         batch = x.shape[0]
         loss = C.c_float()
         lib().call("znn_model_train_step", self.h, x.ctypes.data, t.ctypes.data, batch, seq, 0,
