@@ -605,7 +605,9 @@ def configs_part(args, L, torch, stream):
         return n
 
     res = {}
-    for name, fn in (("device_loader", epoch_device), ("host_batches", epoch_host)):
+    for name, fn in (("device_loader", epoch_device), ("host_batches", epoch_host), ("device_loader_graph", epoch_device)):
+        if name == "device_loader_graph":
+            m.set_option("cuda_graph", 1)
         fn()
         torch.cuda.synchronize()
         e0.record(stream)
@@ -615,6 +617,7 @@ def configs_part(args, L, torch, stream):
         res[name] = e0.elapsed_time(e1) * 1e3 / steps_run
     out["mlp_epoch_b64_input_pipeline"] = {
         "us_per_step_device_loader": res["device_loader"], "us_per_step_host_batches": res["host_batches"],
+        "us_per_step_device_loader_cuda_graph": res["device_loader_graph"],
         "samples": n_img, "note": "device loader: one gather launch per batch, byte labels used in place; host batches: "
                                   "numpy gather + one upload of pixels and labels per step"}
     m.close()
