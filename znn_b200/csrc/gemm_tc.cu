@@ -47,6 +47,12 @@ __device__ __forceinline__ void mbar_arrive_expect_tx(uint32_t bar, uint32_t byt
 // The suspend-time hint lets the hardware park the thread until the phase completes (or the hint runs out) instead
 // of returning at once: waiting roles then leave the issue slots and the shared-memory port to the working warps.
 constexpr uint32_t kWaitSuspendNs = 20000;
+#ifndef ZNN_WAIT_SLEEP_NS
+#define ZNN_WAIT_SLEEP_NS 128   // back-off between polls of a long wait; 0 = keep polling
+#endif
+#ifndef ZNN_WAIT_FAST_POLLS
+#define ZNN_WAIT_FAST_POLLS 8   // polls before a wait counts as long
+#endif
 __device__ __forceinline__ uint32_t mbar_try_wait(uint32_t bar, uint32_t parity)
 {
     uint32_t ok;
@@ -65,7 +71,7 @@ __device__ __forceinline__ bool mbar_wait_bounded(uint32_t bar, uint32_t parity)
 {
     if (mbar_try_wait(bar, parity)) return true;
 #pragma unroll 1
-    for (int i = 0; i < 8; i++)
+    for (int i = 0; i < ZNN_WAIT_FAST_POLLS; i++)
         if (mbar_try_wait(bar, parity)) return true;
     // a long wait: poll less often, so that waiting roles leave issue slots and the shared-memory port alone
     const uint64_t t0 = wait_clock();
@@ -73,7 +79,7 @@ __device__ __forceinline__ bool mbar_wait_bounded(uint32_t bar, uint32_t parity)
 #pragma unroll 1
         for (int i = 0; i < 128; i++) {
             if (mbar_try_wait(bar, parity)) return true;
-            __nanosleep(128);
+            if (ZNN_WAIT_SLEEP_NS > 0) __nanosleep(ZNN_WAIT_SLEEP_NS);
         }
         if (wait_clock() - t0 > kWaitLimitCycles) return false;
     }
@@ -663,7 +669,7 @@ __device__ __forceinline__ bool mbar_wait_bounded_cluster(uint32_t bar, uint32_t
 {
     if (mbar_try_wait_cluster(bar, parity)) return true;
 #pragma unroll 1
-    for (int i = 0; i < 8; i++)
+    for (int i = 0; i < ZNN_WAIT_FAST_POLLS; i++)
         if (mbar_try_wait_cluster(bar, parity)) return true;
     // a long wait: poll less often, so that waiting roles leave issue slots and the shared-memory port alone
     const uint64_t t0 = wait_clock();
@@ -671,7 +677,7 @@ __device__ __forceinline__ bool mbar_wait_bounded_cluster(uint32_t bar, uint32_t
 #pragma unroll 1
         for (int i = 0; i < 128; i++) {
             if (mbar_try_wait_cluster(bar, parity)) return true;
-            __nanosleep(128);
+            if (ZNN_WAIT_SLEEP_NS > 0) __nanosleep(ZNN_WAIT_SLEEP_NS);
         }
         if (wait_clock() - t0 > kWaitLimitCycles) return false;
     }
