@@ -141,7 +141,8 @@ def test_causal_softmax(ops, zo, ns, T):
     assert np.all(d3[:, iu[0], iu[1]] == 0.0)
 
 
-@pytest.mark.parametrize("rows,D", [(1, 1), (2, 3), (64, 512), (100, 768), (7, 1001)])
+@pytest.mark.parametrize("rows,D", [(1, 1), (2, 3), (64, 512), (100, 768), (7, 1001), (33, 4), (9, 256), (5, 260), (10, 772),
+                                    (3, 1024), (3, 1028)])
 def test_rmsnorm_layernorm(ops, zo, rows, D):
     r = rng(rows * 3 + D)
     X = r.standard_normal((rows, D), np.float32)
@@ -241,7 +242,8 @@ def test_maxpool2d_ties(ops, zo):
     np.testing.assert_array_equal(d1, d2)
 
 
-@pytest.mark.parametrize("V,D,shape", [(3, 4, (2, 2)), (50, 33, (4, 7)), (1000, 768, (2, 300)), (16, 2500, (3, 9))])
+@pytest.mark.parametrize("V,D,shape", [(3, 4, (2, 2)), (50, 33, (4, 7)), (1000, 768, (2, 300)), (16, 2500, (3, 9)),
+                                       (5, 64, (3, 1500)), (700, 40, (1, 2049)), (1, 8, (2, 2300))])
 def test_embedding(ops, zo, V, D, shape):
     r = rng(V + D)
     W = r.standard_normal((V, D), np.float32)

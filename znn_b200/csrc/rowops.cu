@@ -551,6 +551,88 @@ __global__ void rmsnorm_bwd_rows_kernel(const float* __restrict__ X, const float
     }
 }
 
+// Register-cached forms for rows of at most 128*V4 elements with D % 4 == 0 and 16-byte aligned pointers: every
+// operand is read once with 128-bit loads (the loops above read x three times with 32-bit loads).  Same expressions
+// per element; only the order of the row sums differs.
+template <int V4>
+__global__ void rmsnorm_fwd_reg_kernel(const float* __restrict__ X, const float* __restrict__ G, float eps,
+                                       float* __restrict__ Y, size_t rows, int D)
+{
+    const size_t row = blockIdx.x * (size_t)(blockDim.x >> 5) + (threadIdx.x >> 5);
+    if (row >= rows) return;
+    const int lane = threadIdx.x & 31, nv = D >> 2;
+    const float4* x = reinterpret_cast<const float4*>(X + row * D);
+    const float4* g = reinterpret_cast<const float4*>(G);
+    float4* y = reinterpret_cast<float4*>(Y + row * D);
+    float4 v[V4];
+    float s = 0.0f;
+#pragma unroll
+    for (int k = 0; k < V4; k++) {
+        const int i = lane + 32 * k;
+        if (i < nv) {
+            v[k] = x[i];
+            s += (v[k].x * v[k].x + v[k].y * v[k].y) + (v[k].z * v[k].z + v[k].w * v[k].w);
+        }
+    }
+    s = warp_sum(s);
+    const float rms = sqrtf(s / (float)D + eps);
+#pragma unroll
+    for (int k = 0; k < V4; k++) {
+        const int i = lane + 32 * k;
+        if (i < nv) {
+            const float4 gg = g[i];
+            y[i] = make_float4(v[k].x / rms * gg.x, v[k].y / rms * gg.y, v[k].z / rms * gg.z, v[k].w / rms * gg.w);
+        }
+    }
+}
+
+template <int V4>
+__global__ void rmsnorm_bwd_rows_reg_kernel(const float* __restrict__ X, const float* __restrict__ G,
+                                            const float* __restrict__ dY, float eps, float* __restrict__ dX,
+                                            float* __restrict__ rowscale, size_t rows, int D)
+{
+    const size_t row = blockIdx.x * (size_t)(blockDim.x >> 5) + (threadIdx.x >> 5);
+    if (row >= rows) return;
+    const int lane = threadIdx.x & 31, nv = D >> 2;
+    const float4* x = reinterpret_cast<const float4*>(X + row * D);
+    const float4* dy = reinterpret_cast<const float4*>(dY + row * D);
+    const float4* g = reinterpret_cast<const float4*>(G);
+    float4 xv[V4], gy[V4];   // x and G o dY
+    float s = 0.0f, t = 0.0f;
+#pragma unroll
+    for (int k = 0; k < V4; k++) {
+        const int i = lane + 32 * k;
+        if (i < nv) {
+            xv[k] = x[i];
+            s += (xv[k].x * xv[k].x + xv[k].y * xv[k].y) + (xv[k].z * xv[k].z + xv[k].w * xv[k].w);
+            if (dX) {
+                const float4 d = dy[i], gg = g[i];
+                gy[k] = make_float4(d.x * gg.x, d.y * gg.y, d.z * gg.z, d.w * gg.w);
+                t += (gy[k].x * xv[k].x + gy[k].y * xv[k].y) + (gy[k].z * xv[k].z + gy[k].w * xv[k].w);
+            }
+        }
+    }
+    s = warp_sum(s);
+    const float scale = 1.0f / sqrtf(s / (float)D + eps);
+    if (rowscale && lane == 0) rowscale[row] = scale;
+    if (!dX) return;
+    t = warp_sum(t);
+    float4* dx = reinterpret_cast<float4*>(dX + row * D);
+    const float fd = (float)D;
+#pragma unroll
+    for (int k = 0; k < V4; k++) {
+        const int i = lane + 32 * k;
+        if (i < nv) {
+            float4 o = dx[i];
+            o.x += scale * (gy[k].x - xv[k].x * scale * scale * t / fd);
+            o.y += scale * (gy[k].y - xv[k].y * scale * scale * t / fd);
+            o.z += scale * (gy[k].z - xv[k].z * scale * scale * t / fd);
+            o.w += scale * (gy[k].w - xv[k].w * scale * scale * t / fd);
+            dx[i] = o;
+        }
+    }
+}
+
 __global__ void layernorm_fwd_kernel(const float* __restrict__ X, const float* __restrict__ G,
                                      const float* __restrict__ Bt, float eps, float* __restrict__ Y, size_t rows, int D)
 {
@@ -617,13 +699,15 @@ __global__ void embedding_fwd_kernel(const float* __restrict__ W, const float* _
 
 // One block per vocabulary row: finds the positions that use this row (kept in
 // (b,t) order) and adds their dY rows one after the other, as the reference's
-// sequential scatter-add does for that row.
+// sequential scatter-add does for that row.  The ids are scanned 2048 at a time: warp w scans the w-th run of
+// 256 ids with ballots and lists its hits in its own part of `matches`, so a round needs two block barriers
+// and the lists, read warp after warp, are in ascending position order.
 __global__ void embedding_bwd_kernel(const float* __restrict__ ids, const float* __restrict__ dY,
                                      float* __restrict__ dW, int n, int D)
 {
-    __shared__ int matches[256];
+    constexpr int kPerWarp = 256, kRound = 8 * kPerWarp;
+    __shared__ int matches[kRound];
     __shared__ int warp_counts[8];
-    __shared__ int nmatch;
     const int v = blockIdx.x;
     const int lane = threadIdx.x & 31, w = threadIdx.x >> 5;
     // each thread owns columns threadIdx.x, +256, ... (D <= 256*8)
@@ -631,30 +715,29 @@ __global__ void embedding_bwd_kernel(const float* __restrict__ ids, const float*
 #pragma unroll
     for (int c = 0; c < 8; c++) acc[c] = 0.0f;
     bool any = false;
-    for (int base = 0; base < n; base += 256) {
-        const int i = base + threadIdx.x;
-        const bool hit = (i < n) && ((int)ids[i] == v);
-        const unsigned bal = __ballot_sync(0xffffffffu, hit);
-        if (lane == 0) warp_counts[w] = __popc(bal);
-        __syncthreads();
-        int off = 0;
-        for (int k = 0; k < w; k++) off += warp_counts[k];
-        if (hit) matches[off + __popc(bal & ((1u << lane) - 1))] = i;
-        if (threadIdx.x == 0) {
-            int t = 0;
-            for (int k = 0; k < 8; k++) t += warp_counts[k];
-            nmatch = t;
-        }
-        __syncthreads();
-        const int nm = nmatch;
-        for (int k = 0; k < nm; k++) {
-            const float* g = dY + (size_t)matches[k] * D;
+    for (int base = 0; base < n; base += kRound) {
+        int cw = 0;
 #pragma unroll
-            for (int c = 0; c < 8; c++) {
-                const int j = threadIdx.x + c * 256;
-                if (j < D) acc[c] += g[j];
+        for (int s = 0; s < kPerWarp / 32; s++) {
+            const int i = base + w * kPerWarp + s * 32 + lane;
+            const bool hit = (i < n) && ((int)ids[i] == v);
+            const unsigned bal = __ballot_sync(0xffffffffu, hit);
+            if (hit) matches[w * kPerWarp + cw + __popc(bal & ((1u << lane) - 1))] = i;
+            cw += __popc(bal);
+        }
+        if (lane == 0) warp_counts[w] = cw;
+        __syncthreads();
+        for (int ww = 0; ww < 8; ww++) {
+            const int nm = warp_counts[ww];
+            for (int k = 0; k < nm; k++) {
+                const float* g = dY + (size_t)matches[ww * kPerWarp + k] * D;
+#pragma unroll
+                for (int c = 0; c < 8; c++) {
+                    const int j = threadIdx.x + c * 256;
+                    if (j < D) acc[c] += g[j];
+                }
+                any = true;
             }
-            any = true;
         }
         __syncthreads();
     }
@@ -1129,7 +1212,12 @@ int znn_rmsnorm_fwd(const float* X, const float* G, float eps, float* Y, size_t 
 {
     if (rows == 0 || D <= 0) return ZNN_OK;
     ZNN_NEED_DEVICE();
-    rmsnorm_fwd_kernel<<<row_blocks(rows, 8), 256, 0, stream()>>>(X, G, eps, Y, rows, D);
+    const bool v4 = (D % 4 == 0) && ((((uintptr_t)X | (uintptr_t)G | (uintptr_t)Y) & 15) == 0);
+    const dim3 grid = row_blocks(rows, 8);
+    if (v4 && D <= 256) rmsnorm_fwd_reg_kernel<2><<<grid, 256, 0, stream()>>>(X, G, eps, Y, rows, D);
+    else if (v4 && D <= 768) rmsnorm_fwd_reg_kernel<6><<<grid, 256, 0, stream()>>>(X, G, eps, Y, rows, D);
+    else if (v4 && D <= 1024) rmsnorm_fwd_reg_kernel<8><<<grid, 256, 0, stream()>>>(X, G, eps, Y, rows, D);
+    else rmsnorm_fwd_kernel<<<grid, 256, 0, stream()>>>(X, G, eps, Y, rows, D);
     ZNN_LAUNCH_OK("rmsnorm_fwd_kernel");
     return ZNN_OK;
 }
@@ -1149,7 +1237,12 @@ int znn_rmsnorm_bwd(const float* X, const float* G, const float* dY, float eps, 
         rowscale = ws;
         partial = ws + rows;
     }
-    rmsnorm_bwd_rows_kernel<<<row_blocks(rows, 8), 256, 0, stream()>>>(X, G, dY, eps, dX, rowscale, rows, D);
+    const bool v4 = (D % 4 == 0) && ((((uintptr_t)X | (uintptr_t)G | (uintptr_t)dY | (uintptr_t)dX) & 15) == 0);
+    const dim3 rgrid = row_blocks(rows, 8);
+    if (v4 && D <= 256) rmsnorm_bwd_rows_reg_kernel<2><<<rgrid, 256, 0, stream()>>>(X, G, dY, eps, dX, rowscale, rows, D);
+    else if (v4 && D <= 768) rmsnorm_bwd_rows_reg_kernel<6><<<rgrid, 256, 0, stream()>>>(X, G, dY, eps, dX, rowscale, rows, D);
+    else if (v4 && D <= 1024) rmsnorm_bwd_rows_reg_kernel<8><<<rgrid, 256, 0, stream()>>>(X, G, dY, eps, dX, rowscale, rows, D);
+    else rmsnorm_bwd_rows_kernel<<<rgrid, 256, 0, stream()>>>(X, G, dY, eps, dX, rowscale, rows, D);
     ZNN_LAUNCH_OK("rmsnorm_bwd_rows_kernel");
     if (dG) {
         dim3 grid(ceil_div(D, 32), chunks), block(32, 8);
