@@ -796,8 +796,14 @@ def rowops_part(args, L, torch, stream):
     rec("sgd_momentum_step", 20 * n, lambda: L.call("znn_sgd_step", p(A), p(B), p(Cc), 1e-9, 0.9, 1.0, n))
     T = 1024
     ns = n // (T * T)
-    rec("causal_softmax_fwd", 8 * n, lambda: L.call("znn_causal_softmax_fwd", p(A), 0.125, p(Cc), ns, T))
-    rec("causal_softmax_bwd", 16 * n, lambda: L.call("znn_causal_softmax_bwd", p(Cc), p(B), 0.125, p(A), ns, T))
+    # fresh N(0,1) inputs: the in-place ops above have grown A and Cc, and expf takes a slow path for the strongly
+    # negative arguments such inputs produce (measured 500 us instead of 170 us for the same softmax)
+    A.normal_()
+    B.normal_()
+    # causal: the lower triangle (half the matrix) is read, the forward writes all of P, the backward updates dS's
+    # lower triangle only
+    rec("causal_softmax_fwd", 6 * n, lambda: L.call("znn_causal_softmax_fwd", p(A), 0.125, p(Cc), ns, T))
+    rec("causal_softmax_bwd", 8 * n, lambda: L.call("znn_causal_softmax_bwd", p(Cc), p(B), 0.125, p(A), ns, T))
     rec("softmax_fwd_rows1024", 8 * n, lambda: L.call("znn_softmax_fwd", p(A), p(Cc), n // T, T))
     D = 768
     rows = n // D
