@@ -62,7 +62,8 @@ int znn_model_save(znn_model* m, const char* path);
 int znn_model_load(znn_model* m, const char* path);
 /* Optimizer state for resuming (an extension: the reference's file holds parameters only): the SGD velocities in a
  * second file of the same layout, one entry per parameter under the parameter's name, so the reference's reader and
- * writer handle it too. */
+ * writer handle it too.  With the Adam optimizer the file holds the first moments and a second file, path + ".v2",
+ * the second moments; the step count is the "adam_t" option. */
 int znn_model_save_optimizer(znn_model* m, const char* path);
 int znn_model_load_optimizer(znn_model* m, const char* path);
 int znn_model_set_params(znn_model* m, const float* host_slab);
@@ -77,6 +78,8 @@ int znn_model_get_velocities(znn_model* m, float* host_slab);
  * gradient buffers of intermediates are zero-filled only when first added to; GEMM arms overwrite them with beta = 0), "dp_bucket_floats",
  * "dp_overlap" (1/0), "cuda_graph" (1/0: capture the training step once per (input buffers, batch) and replay it;
  * MLP / CNN models with device-resident inputs on one GPU; lr and momentum are baked in at capture),
+ * "optimizer" (0 = SGD with "lr" / "momentum" as the example programs use, 1 = Adam, src/optim.zig:69-152, with "lr",
+ * "beta1", "beta2", "eps" and the step count "adam_t"; no CUDA-graph replay with Adam: the step size changes per step),
  * "targets_u8" (1/0: the targets pointer of znn_model_train_step holds byte labels, the reference's label type,
  * e.g. the y_dest of znn_loader_next_into; default 0 = int32) */
 int znn_model_set_option(znn_model* m, const char* key, double value);

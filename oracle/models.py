@@ -145,12 +145,15 @@ class OracleTrainer:
     """The example programs' training step on the CPU oracle: new graph -> forward -> SoftmaxCrossEntropy ->
     zeroGrad -> backward -> SGD (examples/fashion_mnist.zig:131-167, src/optim.zig:50-66)."""
 
-    def __init__(self, kind, params, cfg=None, lr=0.01, momentum=0.9):
+    def __init__(self, kind, params, cfg=None, lr=0.01, momentum=0.9, adam=None):
+        """adam = (beta1, beta2, eps): AdamOptimizer (src/optim.zig:69-152) instead of SGD."""
         from . import ograph, zo
         self.og, self.zo = ograph, zo
         self.kind, self.cfg, self.lr, self.momentum = kind, cfg, lr, momentum
         self.P = {k: v.copy() for k, v in params.items()}
-        self.V = {k: np.zeros_like(v) for k, v in params.items()} if momentum > 0 else None
+        self.V = {k: np.zeros_like(v) for k, v in params.items()} if (momentum > 0 or adam) else None
+        self.adam, self.t = adam, 0.0
+        self.V2 = {k: np.zeros_like(v) for k, v in params.items()} if adam else None
         self.grads = None
 
     def forward_logits(self, g, P, x):
@@ -178,9 +181,15 @@ class OracleTrainer:
         return loss, logits
 
     def apply(self, grads, grad_scale=1.0):
+        if self.adam:
+            self.t += 1.0
         for k in self.P:
             gk = np.ascontiguousarray(grads[k], np.float32)
             if grad_scale != 1.0:
                 gk = (gk * np.float32(grad_scale)).astype(np.float32)
+            if self.adam:
+                self.zo.adam_step(self.P[k].reshape(-1), gk.reshape(-1), self.V[k].reshape(-1), self.V2[k].reshape(-1),
+                                  self.lr, self.adam[0], self.adam[1], self.adam[2], self.t)
+                continue
             self.zo.sgd_step(self.P[k].reshape(-1), gk.reshape(-1), self.V[k].reshape(-1) if self.V else None,
                              self.lr, self.momentum)

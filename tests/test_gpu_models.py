@@ -357,3 +357,65 @@ def test_resume_from_model_and_optimizer_files_continues_bit_identically(Model, 
     a, b = (tmp_path / "model").read_bytes(), (tmp_path / "optimizer").read_bytes()
     hl = int.from_bytes(a[:8], "little")
     assert len(a) == len(b) and a[:8 + hl] == b[:8 + hl] and a[8 + hl:] != b[8 + hl:]
+
+
+@pytest.mark.parametrize("kind,dims,cfg,seq,vocab", [
+    ("mlp", (784, 128, 64, 10), (784, 128, 64, 10), 0, 10),
+    ("gpt", (29, 8, 16, 2, 2), {"vocab_size": 29, "block_size": 8, "n_embd": 16, "n_head": 2, "n_layer": 2}, 8, 29),
+])
+def test_training_with_adam_matches_oracle(Model, kind, dims, cfg, seq, vocab):
+    """AdamOptimizer (src/optim.zig:69-152) as the model's optimizer: loss trajectory and parameters against the
+    oracle trainer running the restated step."""
+    r = np.random.default_rng(17)
+    P0 = models.init_params(kind, cfg, seed=3)
+    m = Model(kind, dims, arena_bytes=256 << 20)
+    m.set_params(P0)
+    for key, val in (("optimizer", 1), ("lr", 0.002), ("beta1", 0.5), ("beta2", 0.999), ("eps", 1e-8)):
+        m.set_option(key, val)
+    tr = models.OracleTrainer(kind, P0, cfg, lr=0.002, adam=(0.5, 0.999, 1e-8))
+    batch = 16
+    for s in range(20):
+        if kind == "gpt":
+            x = r.integers(0, vocab, (batch, seq)).astype(np.float32)
+            t = r.integers(0, vocab, batch * seq).astype(np.int32)
+        else:
+            x, t = pixels(r, batch), r.integers(0, 10, batch).astype(np.int32)
+        lo, _ = tr.step(x, t)
+        lg = m.train_step(x, t, seq=seq)
+        assert abs(lg - lo) <= 1e-4 * abs(lo), f"{kind} step {s}: loss {lg} vs oracle {lo}"
+    Pg = m.get_params()
+    for k in tr.P:
+        relclose(Pg[k], tr.P[k], 2e-3, f"{kind} {k} after 20 Adam steps", floor=1e-2)
+    with pytest.raises(RuntimeError):
+        m.set_option("optimizer", 2)
+
+
+def test_adam_resume_continues_bit_identically(Model, tmp_path):
+    dims = (784, 128, 64, 10)
+    r = np.random.default_rng(23)
+    batches = [(pixels(r, 32), r.integers(0, 10, 32).astype(np.int32)) for _ in range(6)]
+
+    def fresh(seed):
+        m = Model("mlp", dims, arena_bytes=64 << 20)
+        m.set_params(models.init_params("mlp", dims, seed=seed))
+        m.set_option("optimizer", 1)
+        m.set_option("lr", 0.001)
+        return m
+
+    m = fresh(2)
+    for x, t in batches[:3]:
+        m.train_step(x, t)
+    m.save(tmp_path / "model")
+    m.save_optimizer(tmp_path / "optimizer")
+    for x, t in batches[3:]:
+        m.train_step(x, t)
+    want = m.get_params()
+    resumed = fresh(9)
+    resumed.load(tmp_path / "model")
+    resumed.load_optimizer(tmp_path / "optimizer")
+    resumed.set_option("adam_t", 3)
+    for x, t in batches[3:]:
+        resumed.train_step(x, t)
+    got = resumed.get_params()
+    assert all(np.array_equal(got[k], want[k]) for k in want)
+    assert (tmp_path / "optimizer.v2").exists()

@@ -208,6 +208,8 @@ struct znn_model {
     TransformerBlock block;
     GPT gpt;
     SGDOptimizer opt;
+    AdamOptimizer adam;
+    bool use_adam = false;            // "optimizer" option: 0 = SGD (the example programs), 1 = Adam
     size_t in_features = 0, classes = 0;
     size_t dp_bucket_floats = 8u << 20;  // 32 MB buckets
     bool dp_overlap = true;
@@ -381,6 +383,7 @@ int znn_model_create(int kind, const long long* dims, int ndims, size_t arena_by
     for (size_t i = 0; i < m->ps.params().size(); i++) m->param_index[m->ps.params()[i].tensor] = (int)i;
     m->arena.reset(new Arena(arena_bytes));
     m->opt.ps = &m->ps;
+    m->adam.ps = &m->ps;
     *out = m.release();
     ZNN_HOST_CATCH
 }
@@ -461,7 +464,16 @@ int znn_model_set_option(znn_model* m, const char* key, double value)
 {
     ZNN_HOST_TRY
     const std::string k(key ? key : "");
-    if (k == "lr") m->opt.lr = (float)value;
+    if (k == "lr") m->opt.lr = m->adam.lr = (float)value;
+    else if (k == "optimizer") {
+        if (value != 0.0 && value != 1.0) throw Error(ZNN_ERR_INVALID, "optimizer: 0 = SGD, 1 = Adam");
+        m->use_adam = (value == 1.0);
+        drop_graph(m);
+    }
+    else if (k == "beta1") m->adam.beta1 = (float)value;
+    else if (k == "beta2") m->adam.beta2 = (float)value;
+    else if (k == "eps") m->adam.eps = (float)value;
+    else if (k == "adam_t") m->adam.t = (float)value;
     else if (k == "momentum") m->opt.momentum = (float)value;
     else if (k == "fused_softmax") {
         m->gpt.set_fused_softmax(value != 0.0);
@@ -518,7 +530,9 @@ static float* run_train_step(znn_model* m, const float* x, const int32_t* target
     } else {
         g.backward(loss);
     }
-    m->opt.step(1.0f / (float)world);        // optimizer.step(); 1/world turns the rank sum into the global mean
+    // optimizer.step(); 1/world turns the rank sum into the global mean
+    if (m->use_adam) m->adam.step(1.0f / (float)world);
+    else m->opt.step(1.0f / (float)world);
     m->last_ops = (int)g.ops().size();
     return loss->data;
 }
@@ -533,7 +547,7 @@ int znn_model_train_step(znn_model* m, const float* x, const int32_t* targets, i
     znn_dp_world(&world, nullptr);
     // Replay is possible when nothing in the step touches the host: device-resident inputs, one GPU, and a model
     // whose forward uploads nothing (the GPT forward uploads its position ids, so it always runs eagerly).
-    const bool can_replay = m->use_graph && on_device && world == 1 && m->kind != ZNN_MODEL_GPT && m->kind != ZNN_MODEL_BLOCK;
+    const bool can_replay = m->use_graph && !m->use_adam && on_device && world == 1 && m->kind != ZNN_MODEL_GPT && m->kind != ZNN_MODEL_BLOCK;
     float* loss_dev = nullptr;
     if (!can_replay) {
         loss_dev = run_train_step(m, x, targets, batch, seq, on_device != 0);
@@ -826,6 +840,7 @@ int znn_model_save_optimizer(znn_model* m, const char* path)
 {
     ZNN_HOST_TRY
     save_slab(m, path, m->ps.velocities());
+    if (m->use_adam) save_slab(m, (std::string(path) + ".v2").c_str(), m->ps.second_moments());
     ZNN_HOST_CATCH
 }
 
@@ -914,6 +929,7 @@ int znn_model_load_optimizer(znn_model* m, const char* path)
 {
     ZNN_HOST_TRY
     load_slab(m, path, m->ps.velocities());
+    if (m->use_adam) load_slab(m, (std::string(path) + ".v2").c_str(), m->ps.second_moments());
     ZNN_HOST_CATCH
 }
 

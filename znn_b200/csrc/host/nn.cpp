@@ -15,6 +15,7 @@ ParamStore::~ParamStore()
     if (w_) znn_free(w_);
     if (g_) znn_free(g_);
     if (v_) znn_free(v_);
+    if (v2_) znn_free(v2_);
 }
 
 Tensor* ParamStore::add(const std::string& name, const Shape& shape, size_t fan_in)
@@ -48,6 +49,17 @@ void ParamStore::finalize()
         pi.tensor->data = w_ + pi.offset;
         pi.tensor->grad = g_ + pi.offset;
     }
+}
+
+float* ParamStore::second_moments()
+{
+    if (!v2_ && w_) {
+        void* p = nullptr;
+        check(znn_malloc(&p, total_ * sizeof(float)), "ParamStore second moments");
+        v2_ = (float*)p;
+        check(znn_memset(v2_, 0, total_ * sizeof(float)), "znn_memset");
+    }
+    return v2_;
 }
 
 void ParamStore::zeroGrad()
@@ -276,6 +288,14 @@ void SGDOptimizer::step(float grad_scale) const
     check(znn_sgd_step(ps->values(), ps->grads(), momentum > 0.0f ? ps->velocities() : nullptr, lr, momentum, grad_scale,
                        ps->total()),
           "SGD step");
+}
+
+void AdamOptimizer::step(float grad_scale)
+{
+    t += 1.0f;
+    check(znn_adam_step(ps->values(), ps->grads(), ps->velocities(), ps->second_moments(), lr, beta1, beta2, eps, t,
+                        grad_scale, ps->total()),
+          "Adam step");
 }
 
 }  // namespace host

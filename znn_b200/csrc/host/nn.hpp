@@ -36,12 +36,13 @@ public:
     float* values() { return w_; }
     float* grads() { return g_; }
     float* velocities() { return v_; }
+    float* second_moments();         // Adam's v slab, allocated and zeroed on first use
     const std::vector<ParamInfo>& params() const { return params_; }
 
 private:
     std::vector<ParamInfo> params_;
     size_t total_ = 0;
-    float *w_ = nullptr, *g_ = nullptr, *v_ = nullptr;
+    float *w_ = nullptr, *g_ = nullptr, *v_ = nullptr, *v2_ = nullptr;
 };
 
 // Linear.forward runs the fused matmul+addBias op by default; false = the reference's two ops.
@@ -164,6 +165,15 @@ struct SGDOptimizer {
     ParamStore* ps = nullptr;
     float lr = 0.01f, momentum = 0.0f;
     void step(float grad_scale = 1.0f) const;
+};
+
+// src/optim.zig:69-152 over the flat slabs (first moments in the velocity slab, second moments in their own):
+// t += 1; lr_t = lr * sqrt(1 - beta2^t) / (1 - beta1^t) in fp32 on the host, then one kernel for all parameters
+struct AdamOptimizer {
+    ParamStore* ps = nullptr;
+    float lr = 0.001f, beta1 = 0.9f, beta2 = 0.999f, eps = 1e-8f;
+    float t = 0.0f;
+    void step(float grad_scale = 1.0f);
 };
 
 }  // namespace host
