@@ -370,9 +370,13 @@ def test_training_with_adam_matches_oracle(Model, kind, dims, cfg, seq, vocab):
     P0 = models.init_params(kind, cfg, seed=3)
     m = Model(kind, dims, arena_bytes=256 << 20)
     m.set_params(P0)
-    for key, val in (("optimizer", 1), ("lr", 0.002), ("beta1", 0.5), ("beta2", 0.999), ("eps", 1e-8)):
+    # Adam divides by sqrt(v): a gradient that is zero in exact arithmetic (the key bias of attention, which softmax
+    # cancels) holds rounding noise on both sides and would be normalised into full-size steps of random sign with the
+    # reference's default eps = 1e-8; the GPT case uses an eps above that noise and far below the real gradients
+    eps = 1e-4 if kind == "gpt" else 1e-8
+    for key, val in (("optimizer", 1), ("lr", 0.0005), ("beta1", 0.5), ("beta2", 0.999), ("eps", eps)):
         m.set_option(key, val)
-    tr = models.OracleTrainer(kind, P0, cfg, lr=0.002, adam=(0.5, 0.999, 1e-8))
+    tr = models.OracleTrainer(kind, P0, cfg, lr=0.0005, adam=(0.5, 0.999, eps))
     batch = 16
     for s in range(20):
         if kind == "gpt":
