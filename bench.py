@@ -443,6 +443,8 @@ def gpt_part(args, L, torch, dist, stream, world, rank, local):
     del P
     m.set_option("lr", 0.01)
     m.set_option("momentum", 0.9)
+    if args.dp_bucket_mb > 0:
+        m.set_option("dp_bucket_floats", args.dp_bucket_mb * (1 << 20) // 4)
     rr = np.random.default_rng(1000 + rank)             # each rank its own shard of the global batch
     ids = rr.integers(0, V, (B, T)).astype(np.float32)
     tgt = np.concatenate([ids[:, 1:], rr.integers(0, V, (B, 1))], axis=1).astype(np.int32)
@@ -836,6 +838,8 @@ def main():
     ap.add_argument("--n", type=int, default=8192)
     ap.add_argument("--impl", default="znn_b200", choices=["znn_b200", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--dp-bucket-mb", type=int, default=0,
+                    help="GPT workload, N > 1: size of the gradient all-reduce buckets in MB (0 = the library default, 32)")
     ap.add_argument("--shape", default="1024,64,1024,111,111,96",
                     help="--workload shape: M,N,K,trans_a,trans_b,batch of one (batched) product")
     ap.add_argument("--path", type=int, default=0, help="--workload shape: GEMM path (0 = automatic)")
