@@ -24,14 +24,20 @@ def _free_port():
     return p
 
 
-def _rank_main(rank, world, port, kind, cfg, steps, out_dir):
+def _trainer(models, kind, P0, cfg, adam):
+    if adam:
+        return models.OracleTrainer(kind, P0, cfg, lr=0.001, adam=adam)
+    return models.OracleTrainer(kind, P0, cfg, lr=0.05, momentum=0.9)
+
+
+def _rank_main(rank, world, port, kind, cfg, steps, out_dir, adam=None):
     sys.path.insert(0, ROOT)
     from oracle import models
     os.environ["MASTER_ADDR"] = "127.0.0.1"
     os.environ["MASTER_PORT"] = str(port)
     dist.init_process_group("gloo", rank=rank, world_size=world)
     P0 = models.init_params(kind, cfg, seed=5)
-    tr = models.OracleTrainer(kind, P0, cfg, lr=0.05, momentum=0.9)
+    tr = _trainer(models, kind, P0, cfg, adam)
     r = np.random.default_rng(17)                      # every rank draws the same global batches
     G = 8
     losses = []
@@ -57,16 +63,17 @@ def _rank_main(rank, world, port, kind, cfg, steps, out_dir):
     dist.destroy_process_group()
 
 
-@pytest.mark.parametrize("kind,cfg", [("mlp", (784, 32, 16, 10)), ("cnn_ref", None)])
-def test_two_cpu_ranks_match_single_process(tmp_path, kind, cfg):
+@pytest.mark.parametrize("kind,cfg,adam", [("mlp", (784, 32, 16, 10), None), ("cnn_ref", None, None),
+                                           ("mlp", (784, 32, 16, 10), (0.9, 0.999, 1e-6))])
+def test_two_cpu_ranks_match_single_process(tmp_path, kind, cfg, adam):
     sys.path.insert(0, ROOT)
     from oracle import models, zo
     zo.build()
     steps, world = 5, 2
-    mp.spawn(_rank_main, args=(world, _free_port(), kind, cfg, steps, str(tmp_path)), nprocs=world, join=True)
+    mp.spawn(_rank_main, args=(world, _free_port(), kind, cfg, steps, str(tmp_path), adam), nprocs=world, join=True)
     got = np.load(os.path.join(str(tmp_path), "dp.npz"))
     P0 = models.init_params(kind, cfg, seed=5)
-    tr = models.OracleTrainer(kind, P0, cfg, lr=0.05, momentum=0.9)
+    tr = _trainer(models, kind, P0, cfg, adam)
     r = np.random.default_rng(17)
     for s in range(steps):
         x = (r.integers(0, 256, (8, 784)).astype(np.float32) / np.float32(255.0)).astype(np.float32)
