@@ -139,7 +139,9 @@ int znn_dataset_load_idx(const char* images_path, const char* labels_path, float
     if (img.size() < 16) return znn::fail(ZNN_ERR_INVALID, "%s: EndOfStream in the header", images_path);
     if (be32(img.data()) != 0x00000803u) return znn::fail(ZNN_ERR_INVALID, "%s: InvalidMagicNumber", images_path);
     const uint32_t n = be32(img.data() + 4), r = be32(img.data() + 8), c = be32(img.data() + 12);
-    const size_t num_pixels = (size_t)n * r * c;
+    const size_t per_image = (size_t)r * c;   // < 2^64: two 32-bit factors
+    if (n != 0 && per_image > (size_t)-1 / n) return znn::fail(ZNN_ERR_INVALID, "%s: implausible header", images_path);
+    const size_t num_pixels = per_image * n;
     if (img.size() - 16 < num_pixels) return znn::fail(ZNN_ERR_INVALID, "%s: EndOfStream in the pixels", images_path);
     if (lab.size() < 8) return znn::fail(ZNN_ERR_INVALID, "%s: EndOfStream in the header", labels_path);
     if (be32(lab.data()) != 0x00000801u) return znn::fail(ZNN_ERR_INVALID, "%s: InvalidMagicNumber", labels_path);
