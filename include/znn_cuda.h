@@ -244,6 +244,9 @@ int znn_mul_scalar_bwd(const float* dC, float v, float* dA, size_t n);
 /* argmax over dim 0 or 1 of an M x N tensor, first maximum wins, result as fp32:
  * src/tensor.zig:813-851 (and the greedy pick of examples/transformer_gpt.zig:135-142) */
 int znn_argmax(const float* A, float* out, int M, int N, int dim);
+/* computeAccuracy of the example programs (examples/cnn.zig:193-205): argmax over each row of the M x N logits, compared
+ * with the byte labels; *acc (device memory) = correct / M. */
+int znn_accuracy_u8(const float* logits, const uint8_t* labels, int M, int N, float* acc);
 /* SGD with optional momentum: src/optim.zig:50-66. v may be NULL when momentum == 0.
  * grad_scale multiplies the gradient first (1.0 = reference; 1/world for data parallel). */
 int znn_sgd_step(float* w, const float* g, float* v, float lr, float momentum, float grad_scale, size_t n);

@@ -88,6 +88,11 @@ int znn_model_set_option(znn_model* m, const char* key, double value);
  * loss_host may be NULL (no read-back, no synchronisation). */
 int znn_model_train_step(znn_model* m, const float* x, const int32_t* targets, int batch, int seq, int on_device,
                          float* loss_host);
+/* One evaluation batch as the example programs' evaluateModel runs it (examples/cnn.zig:212-256): forward, mean
+ * cross-entropy loss, and computeAccuracy (:193-205) = fraction of rows whose argmax equals the byte label.  MLP / CNN
+ * models; x and labels are host memory, or device memory used in place when on_device = 1 (e.g. a loader's batch). */
+int znn_model_evaluate(znn_model* m, const float* x, const uint8_t* labels, int batch, int on_device, float* loss_host,
+                       float* acc_host);
 /* forward only; logits_host receives batch x classes (MLP/CNN) or batch*seq x vocab (GPT); may be NULL */
 int znn_model_forward(znn_model* m, const float* x, int batch, int seq, int on_device, float* logits_host);
 /* transformer block: y = block(x); backward from dy; x,dy,y host arrays of B*T*n_embd; dx may be NULL */

@@ -179,3 +179,38 @@ def test_training_fed_by_the_device_loader_equals_training_fed_from_host_batches
     assert steps == n // bs
     a, b = host_fed.get_params(), dev_fed.get_params()
     assert all(np.array_equal(a[k], b[k]) for k in a)
+
+
+def test_evaluation_over_the_loader_matches_oracle(ds):
+    """evaluateModel of the example programs (examples/cnn.zig:212-256): batches from the device loader (ragged last
+    batch, no shuffling), loss and accuracy per batch on the device, averaged over batches as the reference does."""
+    from oracle import models as omodels
+    from znn_b200 import models
+    r = np.random.default_rng(31)
+    n, bs, dims = 150, 64, (784, 128, 64, 10)
+    images = r.random((n, 784), np.float32)
+    labels = r.integers(0, 10, n).astype(np.uint8)
+    P0 = omodels.init_params("mlp", dims, seed=4)
+    m = models.Model("mlp", dims, arena_bytes=64 << 20)
+    m.set_params(P0)
+    tr = omodels.OracleTrainer("mlp", P0, dims)
+    data = ds.Dataset.from_arrays(images, labels, rows=28, cols=28)
+    loader = ds.DataLoader(data, bs)
+    x_dev, y_dev = dev_buffers(bs, 784)
+    got, want, start = [], [], 0
+    while True:
+        k = loader.peek_next_batch_size()
+        if k == 0:
+            break
+        assert loader.next_into(x_dev, y_dev) == k
+        got.append(m.evaluate_device(x_dev.ptr, y_dev.ptr, k))
+        loss, logits = tr.loss_and_grads(images[start:start + k], labels[start:start + k].astype(np.int32))
+        want.append((loss, float(np.mean(np.argmax(logits, 1) == labels[start:start + k]))))
+        start += k
+    assert [k for k in (64, 64, 22)] and len(got) == 3
+    for (lg, ag), (lo, ao) in zip(got, want):
+        assert abs(lg - lo) <= 1e-5 * abs(lo)
+        assert ag == np.float32(ao)
+    # host arrays through the same entry
+    lh, ah = m.evaluate(images[:64], labels[:64])
+    assert (lh, ah) == got[0]

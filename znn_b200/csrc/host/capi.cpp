@@ -613,6 +613,31 @@ int znn_model_forward(znn_model* m, const float* x, int batch, int seq, int on_d
     ZNN_HOST_CATCH
 }
 
+// One batch of the example programs' evaluateModel (examples/cnn.zig:212-256): forward, the mean cross-entropy
+// loss and computeAccuracy (:193-205) on the device; only the two scalars come back.
+int znn_model_evaluate(znn_model* m, const float* x, const uint8_t* labels, int batch, int on_device, float* loss_host,
+                       float* acc_host)
+{
+    ZNN_HOST_TRY
+    if (m->kind == ZNN_MODEL_GPT || m->kind == ZNN_MODEL_BLOCK) throw Error(ZNN_ERR_INVALID, "evaluate: classifier models only");
+    if (!x || !labels || batch <= 0) throw Error(ZNN_ERR_INVALID, "evaluate: x/labels is NULL or batch <= 0");
+    m->arena->reset();
+    Graph g(m->arena.get());
+    const uint8_t* dev_labels = labels;
+    if (!on_device) {
+        uint8_t* t = (uint8_t*)m->arena->alloc((size_t)batch);
+        check(znn_memcpy_h2d(t, labels, (size_t)batch), "upload labels");
+        dev_labels = t;
+    }
+    Tensor* logits = model_forward(*m, g, x, batch, 0, on_device != 0);
+    Tensor* loss = g.softmaxCrossEntropyU8(logits, dev_labels);
+    float* acc = (float*)m->arena->alloc(sizeof(float));
+    check(znn_accuracy_u8(logits->data, dev_labels, (int)logits->shape.dims[0], (int)logits->shape.dims[1], acc), "accuracy");
+    if (loss_host) check(znn_memcpy_d2h(loss_host, loss->data, sizeof(float)), "read loss");
+    if (acc_host) check(znn_memcpy_d2h(acc_host, acc, sizeof(float)), "read accuracy");
+    ZNN_HOST_CATCH
+}
+
 int znn_model_block_fwd_bwd(znn_model* m, const float* x, const float* dy, int B, int T, float* y, float* dx)
 {
     ZNN_HOST_TRY

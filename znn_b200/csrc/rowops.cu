@@ -959,6 +959,25 @@ __global__ void batch_gather_kernel(const float* __restrict__ images, const uint
     if (tid == 0 && labels && y_dest) y_dest[j] = labels[idx];
 }
 
+// fraction of rows whose predicted class (fp32 index, as argmax writes it) equals the byte label; one block,
+// integer count, so the result does not depend on the order of the rows
+__global__ void accuracy_u8_kernel(const float* __restrict__ preds, const uint8_t* __restrict__ labels, int n,
+                                   float* __restrict__ acc)
+{
+    __shared__ int warp_hits[32];
+    int hits = 0;
+    for (int i = threadIdx.x; i < n; i += blockDim.x) hits += ((int)preds[i] == (int)labels[i]) ? 1 : 0;
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) hits += __shfl_xor_sync(0xffffffffu, hits, o);
+    if ((threadIdx.x & 31) == 0) warp_hits[threadIdx.x >> 5] = hits;
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        int total = 0;
+        for (int w = 0; w < (int)(blockDim.x >> 5); w++) total += warp_hits[w];
+        *acc = (float)total / (float)n;
+    }
+}
+
 }  // namespace znn
 
 using namespace znn;
@@ -1433,6 +1452,20 @@ int znn_argmax(const float* A, float* out, int M, int N, int dim)
     if (dim == 1) argmax_rows_kernel<<<ceil_div(M, 8), 256, 0, stream()>>>(A, out, M, N);
     else argmax_cols_kernel<<<ceil_div(N, 128), 128, 0, stream()>>>(A, out, M, N);
     ZNN_LAUNCH_OK("argmax kernel");
+    return ZNN_OK;
+}
+
+int znn_accuracy_u8(const float* logits, const uint8_t* labels, int M, int N, float* acc)
+{
+    ZNN_REQUIRE(M > 0 && N > 0, "M and N must be positive");
+    ZNN_NEED_DEVICE();
+    ZNN_REQUIRE(logits && labels && acc, "NULL pointer");
+    float* preds = (float*)workspace((size_t)M * sizeof(float));
+    if (!preds) return fail(ZNN_ERR_NOMEM, "scratch for the predictions");
+    argmax_rows_kernel<<<ceil_div(M, 8), 256, 0, stream()>>>(logits, preds, M, N);
+    ZNN_LAUNCH_OK("argmax kernel");
+    accuracy_u8_kernel<<<1, 1024, 0, stream()>>>(preds, labels, M, acc);
+    ZNN_LAUNCH_OK("accuracy_u8_kernel");
     return ZNN_OK;
 }
 

@@ -97,6 +97,19 @@ class Model:
     def train_step_device(self, x_ptr, t_ptr, batch, seq=0, loss_ptr=None):
         lib().call("znn_model_train_step", self.h, x_ptr, t_ptr, batch, seq, 1, loss_ptr)
 
+    def evaluate(self, x, labels):
+        """(loss, accuracy) of one batch: host arrays, labels as bytes."""
+        x = np.ascontiguousarray(x, np.float32)
+        y = np.ascontiguousarray(labels, np.uint8)
+        loss, acc = C.c_float(), C.c_float()
+        lib().call("znn_model_evaluate", self.h, x.ctypes.data, y.ctypes.data, x.shape[0], 0, C.byref(loss), C.byref(acc))
+        return loss.value, acc.value
+
+    def evaluate_device(self, x_ptr, y_ptr, batch):
+        loss, acc = C.c_float(), C.c_float()
+        lib().call("znn_model_evaluate", self.h, x_ptr, y_ptr, batch, 1, C.byref(loss), C.byref(acc))
+        return loss.value, acc.value
+
     def forward(self, x, seq=0, classes=None):
         x = np.ascontiguousarray(x, np.float32)
         batch = x.shape[0]
