@@ -730,6 +730,24 @@ __device__ __forceinline__ void record_shape(const GemmTcParams& p, int bn, int 
     g_wait_record[14] = (int)(p.beta * 1000.0f); g_wait_record[15] = p.batch;
 }
 
+// Optional role profile (compile with -DZNN_ROLE_PROFILE; off in the product build): CTA pair 0's leader adds up, per
+// role, the cycles spent inside waits and the cycles of the whole role loop, and leaves them in g_wait_record[1..8]
+// ([0] = 2) for znn_gemm_wait_record to read: which role is the one that never waits is the pipeline's bottleneck.
+#ifdef ZNN_ROLE_PROFILE
+#define ZNN_PROF_DECL long long prof_wait = 0; const long long prof_t0 = clock64();
+#define ZNN_PROF_WAIT(expr) [&]() { const long long t_ = clock64(); const bool r_ = (expr); prof_wait += clock64() - t_; return r_; }()
+#define ZNN_PROF_END(role, cond)                                                       \
+    if (cond) {                                                                        \
+        g_wait_record[1 + 2 * (role)] = (int)(prof_wait >> 4);                         \
+        g_wait_record[2 + 2 * (role)] = (int)((clock64() - prof_t0) >> 4);             \
+        g_wait_record[0] = 2;                                                          \
+    }
+#else
+#define ZNN_PROF_DECL
+#define ZNN_PROF_WAIT(expr) (expr)
+#define ZNN_PROF_END(role, cond)
+#endif
+
 template <int BN>
 struct DirectCfg {
     static constexpr int kBRows = BN / 2;
@@ -1019,13 +1037,14 @@ gemm3x_direct_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_cons
     } else if (warp == 0) {
         // ---------------- TMA producer: raw fp32 tiles of this CTA's rows of A and of B ----------------
         if (lane == 0) {
+            ZNN_PROF_DECL
             uint32_t it = 0;
             for (int u = pair; u < total_units && ok; u += npairs) {
                 const DirectUnit d = direct_unit(p, u, cta_rank, BN);
                 for (int kb = 0; kb < d.kb_count; kb++, it++) {
                     const int s = it % S;
                     const uint32_t ph = (it / S) & 1;
-                    if (!mbar_wait_bounded(empty_bar(s), ph ^ 1)) { record_expiry(0, 0, u, it, cta_rank, pair); ok = false; break; }
+                    if (!ZNN_PROF_WAIT(mbar_wait_bounded(empty_bar(s), ph ^ 1))) { record_expiry(0, 0, u, it, cta_rank, pair); ok = false; break; }
                     const uint32_t st = smem_base + s * Cfg::kStageBytes;
                     const int k0 = (d.kb_first + kb) * kBK;
                     mbar_arrive_expect_tx(full_bar(s), Cfg::kABytes + Cfg::kBBytes);
@@ -1048,6 +1067,7 @@ gemm3x_direct_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_cons
                 }
             }
             if (!ok) atomicOr(p.status, ZNN_DEV_TMA_WAIT_EXPIRED);
+            ZNN_PROF_END(0, pair == 0 && cta_rank == 0)
         }
     } else if (warp == 1) {
         // ---------------- MMA issuer (leader CTA only) ----------------
@@ -1056,6 +1076,7 @@ gemm3x_direct_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_cons
             // descriptor start-address step per K=8 MMA, in 16-byte units
             constexpr uint32_t a_step = A_MN ? (1024 >> 4) : (32 >> 4);
             constexpr uint32_t b_step = B_MN ? (1024 >> 4) : (32 >> 4);
+            ZNN_PROF_DECL
             uint32_t it = 0, cc = 0;
             for (int u = pair; u < total_units && ok; u += npairs) {
                 const DirectUnit d = direct_unit(p, u, cta_rank, BN);
@@ -1063,14 +1084,14 @@ gemm3x_direct_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_cons
                 for (int c = 0; c < d.nchunks && ok; c++, cc++) {
                     const int buf = cc & 1;
                     // the epilogue warps must have drained this buffer (two chunks ago, possibly of the previous unit)
-                    if (!mbar_wait_bounded_cluster(acc_empty_bar(buf), ((cc >> 1) & 1) ^ 1)) { record_expiry(1, 3, u, cc, cta_rank, pair); ok = false; break; }
+                    if (!ZNN_PROF_WAIT(mbar_wait_bounded_cluster(acc_empty_bar(buf), ((cc >> 1) & 1) ^ 1))) { record_expiry(1, 3, u, cc, cta_rank, pair); ok = false; break; }
                     tc_fence_after();
                     const uint32_t d_tmem = tmem_base + (uint32_t)(buf * BN);
                     const int kb_end = min(d.kb_count, kb + chunk);
                     for (bool first = true; kb < kb_end; kb++, it++) {
                         const int s = it % S;
                         const uint32_t ph = (it / S) & 1;
-                        if (!mbar_wait_bounded_cluster(conv_bar(s), ph)) { record_expiry(1, 2, u, it, cta_rank, pair); ok = false; break; }
+                        if (!ZNN_PROF_WAIT(mbar_wait_bounded_cluster(conv_bar(s), ph))) { record_expiry(1, 2, u, it, cta_rank, pair); ok = false; break; }
                         tc_fence_after();
                         const uint32_t st = smem_base + s * Cfg::kStageBytes;
                         const uint64_t a_hi = A_MN ? make_mnmajor_sw128_desc(st) : make_kmajor_sw128_desc(st);
@@ -1092,6 +1113,7 @@ gemm3x_direct_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_cons
                 }
             }
             if (!ok) atomicOr(p.status, ZNN_DEV_MMA_WAIT_EXPIRED);
+            ZNN_PROF_END(1, pair == 0)
         }
     } else {
         // ---------------- converters: raw tile -> hi (in place) and lo ----------------
@@ -1102,6 +1124,7 @@ gemm3x_direct_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_cons
         const bool store_hi = (p.conv_mode == 0);
         bool got = true;
         uint32_t it = 0;
+        ZNN_PROF_DECL
         for (int u = pair; u < total_units && got; u += npairs) {
             const int kb_count = direct_unit_kb_count(p, u, BN);
             for (int kb = 0; kb < kb_count; kb++, it++) {
@@ -1109,7 +1132,7 @@ gemm3x_direct_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_cons
                 const int s = it % S;
                 const uint32_t ph = (it / S) & 1;
                 if (lane == 0) {
-                    got = mbar_wait_bounded(full_bar(s), ph);
+                    got = ZNN_PROF_WAIT(mbar_wait_bounded(full_bar(s), ph));
                     if (!got) record_expiry(2, 1, u, it, cta_rank, pair);
                 }
                 got = __shfl_sync(0xffffffffu, (int)got, 0) != 0;
@@ -1119,14 +1142,15 @@ gemm3x_direct_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_cons
                 // fp32 and at most 2^-10 |x|; the tensor core drops lo's own low bits, a 2^-21 relative effect
                 auto convert = [&](uint8_t* base, int nvec, int lo_off) {
                     constexpr int kT = 32 * kConvWarps;
+                    constexpr int kLd = 4;   // 16-byte loads in flight per thread
 #pragma unroll 1
-                    for (int i0 = ct; i0 < nvec; i0 += 4 * kT) {
-                        uint4 x[4];
+                    for (int i0 = ct; i0 < nvec; i0 += kLd * kT) {
+                        uint4 x[kLd];
 #pragma unroll
-                        for (int v = 0; v < 4; v++)
+                        for (int v = 0; v < kLd; v++)
                             if (i0 + v * kT < nvec) x[v] = *reinterpret_cast<const uint4*>(base + 16 * (i0 + v * kT));
 #pragma unroll
-                        for (int v = 0; v < 4; v++) {
+                        for (int v = 0; v < kLd; v++) {
                             if (i0 + v * kT >= nvec) continue;
                             uint4 h;
                             h.x = x[v].x & 0xFFFFE000u; h.y = x[v].y & 0xFFFFE000u;
@@ -1151,6 +1175,7 @@ gemm3x_direct_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_cons
             }
         }
         if (!got && lane == 0) atomicOr(p.status, ZNN_DEV_TMA_WAIT_EXPIRED);
+        ZNN_PROF_END(2, pair == 0 && cta_rank == 0 && ct == 0 && group == 0)
     }
     } else {
         asm volatile("setmaxnreg.inc.sync.aligned.u32 200;");
@@ -1167,6 +1192,7 @@ gemm3x_direct_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_cons
         const float alpha = to_partial ? 1.0f : p.alpha, beta = to_partial ? 0.0f : p.beta;
         bool got = true;
         uint32_t cc = 0;
+        ZNN_PROF_DECL
         for (int u = pair; u < total_units && got; u += npairs) {
             const DirectUnit d = direct_unit(p, u, cta_rank, BN);
             float acc[CPT];
@@ -1175,7 +1201,7 @@ gemm3x_direct_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_cons
             for (int c = 0; c < d.nchunks; c++, cc++) {
                 const int buf = cc & 1;
                 if (lane == 0) {
-                    got = mbar_wait_bounded(acc_full_bar(buf), (cc >> 1) & 1);
+                    got = ZNN_PROF_WAIT(mbar_wait_bounded(acc_full_bar(buf), (cc >> 1) & 1));
                     if (!got) record_expiry(3, 4, u, cc, cta_rank, pair);
                 }
                 got = __shfl_sync(0xffffffffu, (int)got, 0) != 0;
@@ -1214,6 +1240,7 @@ gemm3x_direct_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_cons
                 epilogue_store_rows<CPT>(acc, stage, lane, d.row0 + q * 32, d.col0 + half * CPT, p.M, p.N, out, out_ld, alpha, beta, bias);
         }
         if (!got && lane == 0) atomicOr(p.status, ZNN_DEV_EPI_WAIT_EXPIRED);
+        ZNN_PROF_END(3, pair == 0 && cta_rank == 0 && warp == kEpiWarp0 && lane == 0)
         }
     }
 
