@@ -893,6 +893,7 @@ __device__ __forceinline__ void epilogue_store_vec(const float (&acc)[CPT], floa
     float4 b4 = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
     if (bias && col_full) b4 = *reinterpret_cast<const float4*>(bias + col);
     const bool fast = !ep_p && beta == 0.0f && bias == nullptr && rows == 32 && cbase + CPT <= N;
+    const bool fast_p = ep_p && rows == 32 && cbase + CPT <= N;
     // The order in which the row groups (and the rows inside a group) leave is rotated by `rot` (warp and CTA pair):
     // when every warp of every SM writes rows 0, 1, 2, ... of a power-of-two-pitched C at the same time the stores
     // pile up on the same memory channels (measured with a stand-alone store kernel: 3.7 vs 6.0 TB/s).
@@ -919,6 +920,32 @@ __device__ __forceinline__ void epilogue_store_vec(const float (&acc)[CPT], floa
                 const float4 v = st4[rl * LPR + (my_f ^ (rl & 7) & (LPR - 1))];
                 *reinterpret_cast<float4*>(cp + (size_t)(ri * RPI) * out_ld) =
                     make_float4(alpha * v.x, alpha * v.y, alpha * v.z, alpha * v.w);
+            }
+            __syncwarp();
+            continue;
+        }
+        if (fast_p) {
+            // the same for the softmax-backward form: P and d for IB rows in flight, then IB load-combine-store chains
+            const size_t off0 = (size_t)(row_base + g * RPP + lane / LPR) * out_ld + col;
+            const float* const dp = ep_d + row_base + g * RPP + lane / LPR;
+#pragma unroll
+            for (int i0 = 0; i0 < NI; i0 += IB) {
+                float4 pv[IB];
+#pragma unroll
+                for (int i = 0; i < IB; i++) {
+                    const int ri = (i0 + i + rot) % NI;
+                    pv[i] = *reinterpret_cast<const float4*>(ep_p + off0 + (size_t)(ri * RPI) * out_ld);
+                }
+#pragma unroll
+                for (int i = 0; i < IB; i++) {
+                    const int ri = (i0 + i + rot) % NI;
+                    const int rl = ri * RPI + lane / LPR;
+                    const float4 v = st4[rl * LPR + (my_f ^ (rl & 7) & (LPR - 1))];
+                    const float dr = dp[ri * RPI];
+                    *reinterpret_cast<float4*>(out + off0 + (size_t)(ri * RPI) * out_ld) =
+                        make_float4((pv[i].x * (v.x - dr)) * alpha, (pv[i].y * (v.y - dr)) * alpha,
+                                    (pv[i].z * (v.z - dr)) * alpha, (pv[i].w * (v.w - dr)) * alpha);
+                }
             }
             __syncwarp();
             continue;
