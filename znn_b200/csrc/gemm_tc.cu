@@ -897,10 +897,11 @@ __device__ __forceinline__ void epilogue_store_vec(const float (&acc)[CPT], floa
     // The order in which the row groups (and the rows inside a group) leave is rotated by `rot` (warp and CTA pair):
     // when every warp of every SM writes rows 0, 1, 2, ... of a power-of-two-pitched C at the same time the stores
     // pile up on the same memory channels (measured with a stand-alone store kernel: 3.7 vs 6.0 TB/s).
-    if (fast && CPT >= 32) {
+    if (fast) {
         // full block, beta = 0, no bias: 32-column blocks staged by all 32 lanes (8 staging stores per block instead of
         // 32 by a quarter of the lanes), read back as 4 rows x 128 bytes per instruction
-        constexpr int NB = CPT / 32 > 0 ? CPT / 32 : 1;
+        static_assert(CPT % 32 == 0, "the column blocks are 32 wide");
+        constexpr int NB = CPT / 32;
         float* const cp = out + (size_t)(row_base + lane / 8) * out_ld + cbase + 4 * (lane % 8);
 #pragma unroll
         for (int b0 = 0; b0 < NB; b0++) {
@@ -933,21 +934,6 @@ __device__ __forceinline__ void epilogue_store_vec(const float (&acc)[CPT], floa
         }
         __syncwarp();
         constexpr int IB = NI < 4 ? NI : 4;   // old-C loads in flight per lane
-        if (fast) {
-            // full 32 x CPT block, beta = 0, no bias: no edge tests, one row pointer, NI independent load-scale-store
-            // chains (the epilogue warps are latency bound: two of them per scheduler)
-            float* const cp = out + (size_t)(row_base + g * RPP + lane / LPR) * out_ld + col;
-#pragma unroll
-            for (int i = 0; i < NI; i++) {
-                const int ri = (i + rot) % NI;
-                const int rl = ri * RPI + lane / LPR;
-                const float4 v = st4[rl * LPR + (my_f ^ (rl & 7) & (LPR - 1))];
-                *reinterpret_cast<float4*>(cp + (size_t)(ri * RPI) * out_ld) =
-                    make_float4(alpha * v.x, alpha * v.y, alpha * v.z, alpha * v.w);
-            }
-            __syncwarp();
-            continue;
-        }
         if (fast_p) {
             // the same for the softmax-backward form: P and d for IB rows in flight, then IB load-combine-store chains
             const size_t off0 = (size_t)(row_base + g * RPP + lane / LPR) * out_ld + col;
