@@ -922,6 +922,42 @@ __device__ __forceinline__ void epilogue_store_vec(const float (&acc)[CPT], floa
         }
         return;
     }
+    if (fast_p) {
+        // the softmax-backward form on full blocks, staged the same way: P for four row groups in flight, then four
+        // load-combine-store chains
+        constexpr int NB = CPT / 32;
+        const size_t off = (size_t)(row_base + lane / 8) * out_ld + cbase + 4 * (lane % 8);
+        const float* const dp = ep_d + row_base + lane / 8;
+#pragma unroll
+        for (int b0 = 0; b0 < NB; b0++) {
+#pragma unroll
+            for (int f = 0; f < 8; f++)
+                st4[lane * 8 + (f ^ (lane & 7))] =
+                    make_float4(acc[32 * b0 + 4 * f], acc[32 * b0 + 4 * f + 1], acc[32 * b0 + 4 * f + 2], acc[32 * b0 + 4 * f + 3]);
+            __syncwarp();
+#pragma unroll
+            for (int i0 = 0; i0 < 8; i0 += 4) {
+                float4 pv[4];
+#pragma unroll
+                for (int i = 0; i < 4; i++) {
+                    const int ri = (i0 + i + rot) % 8;
+                    pv[i] = *reinterpret_cast<const float4*>(ep_p + off + (size_t)(4 * ri) * out_ld + 32 * b0);
+                }
+#pragma unroll
+                for (int i = 0; i < 4; i++) {
+                    const int ri = (i0 + i + rot) % 8;
+                    const int r = 4 * ri + lane / 8;
+                    const float4 v = st4[r * 8 + ((lane % 8) ^ (r & 7))];
+                    const float dr = dp[4 * ri];
+                    *reinterpret_cast<float4*>(out + off + (size_t)(4 * ri) * out_ld + 32 * b0) =
+                        make_float4((pv[i].x * (v.x - dr)) * alpha, (pv[i].y * (v.y - dr)) * alpha,
+                                    (pv[i].z * (v.z - dr)) * alpha, (pv[i].w * (v.w - dr)) * alpha);
+                }
+            }
+            __syncwarp();
+        }
+        return;
+    }
     for (int g0 = 0; g0 < 32 / RPP; g0++) {
         const int g = (g0 + rot) % (32 / RPP);
         if (g * RPP >= rows) continue;
@@ -934,32 +970,6 @@ __device__ __forceinline__ void epilogue_store_vec(const float (&acc)[CPT], floa
         }
         __syncwarp();
         constexpr int IB = NI < 4 ? NI : 4;   // old-C loads in flight per lane
-        if (fast_p) {
-            // the same for the softmax-backward form: P and d for IB rows in flight, then IB load-combine-store chains
-            const size_t off0 = (size_t)(row_base + g * RPP + lane / LPR) * out_ld + col;
-            const float* const dp = ep_d + row_base + g * RPP + lane / LPR;
-#pragma unroll
-            for (int i0 = 0; i0 < NI; i0 += IB) {
-                float4 pv[IB];
-#pragma unroll
-                for (int i = 0; i < IB; i++) {
-                    const int ri = (i0 + i + rot) % NI;
-                    pv[i] = *reinterpret_cast<const float4*>(ep_p + off0 + (size_t)(ri * RPI) * out_ld);
-                }
-#pragma unroll
-                for (int i = 0; i < IB; i++) {
-                    const int ri = (i0 + i + rot) % NI;
-                    const int rl = ri * RPI + lane / LPR;
-                    const float4 v = st4[rl * LPR + (my_f ^ (rl & 7) & (LPR - 1))];
-                    const float dr = dp[ri * RPI];
-                    *reinterpret_cast<float4*>(out + off0 + (size_t)(ri * RPI) * out_ld) =
-                        make_float4((pv[i].x * (v.x - dr)) * alpha, (pv[i].y * (v.y - dr)) * alpha,
-                                    (pv[i].z * (v.z - dr)) * alpha, (pv[i].w * (v.w - dr)) * alpha);
-                }
-            }
-            __syncwarp();
-            continue;
-        }
 #pragma unroll
         for (int i0 = 0; i0 < NI; i0 += IB) {
             float4 old[IB];
