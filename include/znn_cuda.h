@@ -36,6 +36,7 @@ extern "C" {
 #define ZNN_DEV_TMA_WAIT_EXPIRED 1
 #define ZNN_DEV_MMA_WAIT_EXPIRED 2
 #define ZNN_DEV_EPI_WAIT_EXPIRED 4
+#define ZNN_DEV_BAD_INDEX 8        /* a token id, class label or sample index was outside its range */
 
 /* same constants as src/cblas.zig:5-8 */
 #define ZNN_ROW_MAJOR 101
@@ -46,6 +47,10 @@ extern "C" {
 /* ---- runtime (the reference allocates with Zig allocators: src/autodiff.zig:1301-1326,
  *      src/nn.zig:1352-1377; these are the device equivalents) ---- */
 int znn_init(int device);                 /* select device, create per-device state */
+/* Makes `device` the calling host thread's current device (cudaSetDevice) and creates its state on first use.  One host
+ * thread may drive several devices by switching between calls; streams, scratch blocks, the status word and kernel
+ * attributes are all kept per device. */
+int znn_set_device(int device);
 int znn_device_count(int* count);
 int znn_set_stream(void* cuda_stream);    /* cudaStream_t to launch on (NULL = shim-owned stream) */
 int znn_get_stream(void** cuda_stream);
@@ -55,13 +60,39 @@ int znn_free(void* ptr);
 int znn_memset(void* ptr, int value, size_t bytes);
 int znn_memcpy_h2d(void* dst, const void* src, size_t bytes);   /* async on the stream */
 int znn_memcpy_d2h(void* dst, const void* src, size_t bytes);   /* waits for completion */
+int znn_memcpy_d2h_async(void* dst, const void* src, size_t bytes); /* async on the stream (pinned dst); znn_sync() completes it */
 int znn_memcpy_d2d(void* dst, const void* src, size_t bytes);
 /* rows x width_bytes between pitched device arrays (async on the stream); used to append K/V rows to a decode cache */
 int znn_memcpy2d_d2d(void* dst, size_t dst_pitch, const void* src, size_t src_pitch, size_t width_bytes, size_t rows);
+/* Per-step bump allocator over one device block: the analogue of Graph.arena (std.heap.ArenaAllocator,
+ * src/autodiff.zig:1237-1258: every intermediate of a batch is freed at once by graph.deinit).  alloc returns
+ * 256-byte aligned device memory or ZNN_ERR_NOMEM when the block is exhausted; reset makes everything reusable. */
+typedef struct znn_arena znn_arena;
+int znn_arena_create(size_t bytes, znn_arena** out);
+int znn_arena_alloc(znn_arena* a, size_t bytes, void** ptr);
+int znn_arena_reset(znn_arena* a);
+int znn_arena_usage(znn_arena* a, size_t* used, size_t* high_water, size_t* capacity);
+int znn_arena_destroy(znn_arena* a);
+/* Persistent parameters (createPersistentTensor, src/nn.zig:1352-1369) as three contiguous device slabs -- values,
+ * gradients, SGD velocities, all zero at creation -- holding n tensors of counts[i] floats in the caller's
+ * collectParameters order (src/nn.zig:142-171), each starting 16-byte aligned.  One memset is model.zeroGrad()
+ * (:121-140), one kernel the optimizer step (src/optim.zig:50-66), one call the data-parallel gradient sum. */
+typedef struct znn_param_slab znn_param_slab;
+int znn_param_slab_create(const size_t* counts, int n, znn_param_slab** out);
+int znn_param_slab_total(znn_param_slab* s, size_t* total_floats);
+int znn_param_slab_tensor(znn_param_slab* s, int i, float** value, float** grad, float** velocity, size_t* offset);
+int znn_param_slab_zero_grad(znn_param_slab* s);
+int znn_param_slab_sgd_step(znn_param_slab* s, float lr, float momentum, float grad_scale);
+int znn_param_slab_allreduce_grads(znn_param_slab* s);   /* in-place sum over the data-parallel ranks */
+int znn_param_slab_destroy(znn_param_slab* s);
 int znn_last_error(char* buf, size_t buflen);
 int znn_device_status(int* status, int clear); /* syncs, reads (and clears) the device status word */
 int znn_gemm_workspace_reserve(size_t bytes);  /* pre-size the GEMM scratch (avoids cudaMalloc later) */
 int znn_launch_count(long long* count, int reset); /* kernels launched by this host thread so far */
+/* Scratch blocks are kept per (device, stream) and grow on demand; growing frees the old block after synchronising the
+ * stream and is refused during stream capture.  The counter increases whenever a block of the current device moved:
+ * whoever keeps raw scratch addresses alive across calls (a captured CUDA graph) compares it before reuse. */
+int znn_workspace_generation(unsigned long long* generation);
 
 /* ---- GEMM: replaces cblas_sgemm (src/cblas.zig:11-96; prototype :17-34) at its 8 call
  *      sites (src/tensor.zig:181,721; src/autodiff.zig:117,513,604,624,1143,1163).
@@ -141,28 +172,6 @@ int znn_gemm_set_chunk(int k_elements);
  * contraction (parameter gradients dW = X^T dY), K is cut into slices run by different CTAs and
  * the partial sums are added in a fixed order by a second kernel.  0 switches it off. */
 int znn_gemm_set_splitk(int enable);
-/* In-place path only: 1 (default) = the converter warps leave the raw fp32 tile as the hi operand:
- * the tensor core ignores the 13 low mantissa bits of a kind::tf32 operand (measured on B200: results
- * are bit-identical to mode 0); 0 = they also store hi = x with those bits cleared. */
-int znn_gemm_set_conv_mode(int mode);
-/* In-place path only: 1 (default) = persistent launch (one CTA pair per SM pair walks the output tiles, so the
- * next tile's main loop overlaps the previous tile's epilogue); 0 = one CTA pair per output tile. */
-int znn_gemm_set_persistent(int enable);
-/* In-place path only: 1 (default) = when the last round of the persistent walk would be less than 70 % full, its tiles
- * are cut into K-slices (whole accumulation chunks) run by otherwise idle CTA pairs; the slices' partial tiles are added
- * in slice order by a small second kernel (deterministic).  0 = every tile is one unit. */
-int znn_gemm_set_tail_split(int enable);
-/* Diagnostic: where the first bounded device-side wait of a tensor-core GEMM expired since the last call (16 ints:
- * claimed flag, role, barrier, work unit, counter, M, N, K, split-K slices, tile width, CTA rank, CTA pair, units,
- * pairs, beta*1000, batch); all zero when none did.  Reading clears the record. */
-int znn_gemm_wait_record(int* out16);
-/* Measurement aid: with profiling on, every tensor-core GEMM kernel launch (not its split
- * pre-pass) is bracketed by CUDA events on the launching stream; znn_gemm_profile_read waits
- * for them and returns the summed kernel time, the launch count and the algorithmic
- * floating-point operations (2*M*N*K*batch) of those launches, then clears the record. */
-int znn_gemm_profile(int enable);
-int znn_gemm_profile_read(double* kernel_ms, long long* launches, double* flops);
-
 /* ---- row-wise operators: the arms of Op.forward (src/autodiff.zig:107-575) and
  *      Op.backward (:579-1231) ---- */
 /* AddBias: src/autodiff.zig:134-147 / :652-672 */
@@ -179,7 +188,9 @@ int znn_gelu_bwd(const float* A, const float* dC, float* dA, size_t n);
 int znn_gelu_bwd_set(const float* A, const float* dC, float* dA, size_t n);
 /* SoftmaxCrossEntropy: :196-238 / :758-774; probs is the M x N buffer the reference keeps in
  * OpContext; loss is one device float.  Targets are int32 (the reference's []const u8 cannot
- * hold a vocabulary above 255); the _u8 form takes the reference's type. */
+ * hold a vocabulary above 255); the _u8 form takes the reference's type.  A target outside [0, N) is never used as
+ * an index: that row's loss (and the mean) becomes NaN and ZNN_DEV_BAD_INDEX is set in the device status word; the
+ * backward treats such a row as having no target column. */
 int znn_softmax_xent_fwd(const float* logits, const int32_t* targets, float* probs, float* loss, int M, int N);
 int znn_softmax_xent_fwd_u8(const float* logits, const uint8_t* targets, float* probs, float* loss, int M, int N);
 int znn_softmax_xent_bwd(const float* probs, const int32_t* targets, float* dlogits, int M, int N);
@@ -229,7 +240,9 @@ int znn_conv2d_bwd(const float* X, const float* W, const float* dY, float* dX, f
 int znn_maxpool2d_fwd(const float* X, float* Y, int32_t* idx, int N, int C, int H, int W, int pool, int stride);
 int znn_maxpool2d_bwd(const float* X, const float* dY, float* dX, int N, int C, int H, int W, int pool, int stride);
 /* Embedding (ids carried as fp32, as in the reference): :532-553 / :1183-1207.
- * The backward scatter-add is deterministic: rows with the same id are summed in (b,t) order. */
+ * The backward scatter-add is deterministic: rows with the same id are summed in (b,t) order.
+ * The reference asserts id < vocab (:547); here an id outside [0, vocab) is never dereferenced: the forward writes a zero
+ * row and sets ZNN_DEV_BAD_INDEX in the device status word, the backward ignores the position. */
 int znn_embedding_fwd(const float* W, const float* ids, float* Y, size_t n, int D, int vocab);
 int znn_embedding_bwd(const float* ids, const float* dY, float* dW, size_t n, int D, int vocab);
 /* Transpose of two dims of a rank<=8 tensor: :276-302 / :848-876 (bwd accumulates) */
@@ -258,12 +271,25 @@ int znn_adam_step(float* w, const float* g, float* m, float* v, float lr, float 
  * znn_pixels_to_unit: IDX pixel bytes -> fp32 pixel / 255.0, the conversion of loadImages (src/dataset.zig:53-63).
  * znn_batch_gather: the copy loop of DataLoader.nextInto (src/dataset.zig:211-220): for j < batch,
  *   x_dest[j, :] = images[indices[j], :] (input_dim floats) and y_dest[j] = labels[indices[j]].
- *   images, labels, indices and both destinations are device memory; labels and y_dest may both be NULL. */
+ *   images, labels, indices and both destinations are device memory; labels and y_dest may both be NULL.
+ *   num_samples is the number of rows of images: an index outside [0, num_samples) is never dereferenced; its slot is
+ *   zero-filled and ZNN_DEV_BAD_INDEX is set in the device status word. */
 int znn_pixels_to_unit(const uint8_t* pixels, float* out, size_t n);
 int znn_batch_gather(const float* images, const uint8_t* labels, const int32_t* indices, float* x_dest, uint8_t* y_dest,
-                     int batch, int input_dim);
+                     int batch, int input_dim, size_t num_samples);
 /* fill helpers (src/tensor.zig:354-379 fills; used for dC = 1 seeds and zeroGrad) */
 int znn_fill(float* dst, float value, size_t n);
+/* Weight initialisation on the device.
+ * znn_init_he_normal: initializeWeights (src/nn.zig:1336-1350): w[i] = N(0,1) * sqrt(2 / fan_in), one Box-Muller draw per
+ *   element, cosine branch, u1 redrawn while it is 0.
+ * znn_fill_normal / znn_fill_uniform: Tensor.fillNormal (src/tensor.zig:354-373: elements 2k, 2k+1 share one draw, cosine
+ *   then sine) and Tensor.fillUniform (:375-379).
+ * The distributions and the fan-in rule are the reference's.  The random STREAM is not: the reference draws from Zig's
+ * std.Random.DefaultPrng, these draw from a counter-based hash of (seed, element index), so the same seed gives different
+ * numbers than the reference would (parity of the stream is unpinned; parity tests share explicit weights instead). */
+int znn_init_he_normal(float* w, size_t n, size_t fan_in, unsigned long long seed);
+int znn_fill_normal(float* w, size_t n, float mean, float stddev, unsigned long long seed);
+int znn_fill_uniform(float* w, size_t n, float min_val, float max_val, unsigned long long seed);
 
 /* ---- data parallelism (new: the reference is single-process).  One process per GPU; the
  *      training step's only exchange is the sum of parameter gradients over ranks.
@@ -272,12 +298,27 @@ int znn_fill(float* dst, float value, size_t n);
  *      ordered after the work already queued on the compute stream; znn_dp_join makes the
  *      compute stream wait for them. ---- */
 int znn_dp_unique_id(char* out128);
-int znn_dp_init(int world, int rank, const char* id128);
+int znn_dp_init(int world, int rank, const char* id128);     /* one process per GPU: this process is `rank` of `world` */
+/* One process that drives devices 0 .. ndev-1 itself (ncclCommInitAll): device d becomes rank d.  The calling thread
+ * selects the rank it speaks for with znn_set_device; collective calls issued for several devices by ONE thread must be
+ * bracketed by znn_dp_group_begin / znn_dp_group_end (ncclGroupStart / ncclGroupEnd), or each device needs its own thread. */
+int znn_dp_init_all(int ndev);
+int znn_dp_group_begin(void);
+int znn_dp_group_end(void);
 int znn_dp_world(int* world, int* rank);
 int znn_dp_allreduce_async(float* buf, size_t count);   /* in-place fp32 sum */
 int znn_dp_join(void);
 int znn_dp_allreduce(float* buf, size_t count);
 int znn_dp_broadcast(float* buf, size_t count, int root);
+/* Failure detection.  znn_dp_set_timeout_ms(ms > 0), called before znn_dp_init, creates the communicator non-blocking:
+ * every NCCL call is then polled (ncclCommGetAsyncError) until NCCL has accepted it, at most ms milliseconds.
+ * znn_dp_wait(timeout_ms) blocks the HOST until the reductions queued so far have finished, polling the communicator's
+ * asynchronous error state meanwhile.  On an NCCL error or an expired deadline the communicator is aborted
+ * (ncclCommAbort) so that this rank does not stay blocked on a peer that is gone, and ZNN_ERR_NCCL is returned;
+ * later collective calls fail at once until znn_dp_finalize + znn_dp_init.  znn_dp_abort does the same on request. */
+int znn_dp_set_timeout_ms(long long ms);
+int znn_dp_wait(long long timeout_ms);
+int znn_dp_abort(void);
 int znn_dp_finalize(void);
 
 #ifdef __cplusplus

@@ -1,0 +1,65 @@
+/*
+ * znn_debug.h -- measurement aids, experiment switches and test hooks of libznn_cuda.so.
+ * Nothing here is part of the drop-in boundary (include/znn_cuda.h); a host program never needs these.
+ * Same conventions: 0 or a negative ZNN_ERR_* code.
+ */
+#ifndef ZNN_DEBUG_H
+#define ZNN_DEBUG_H
+#include <stddef.h>
+#include <stdint.h>
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* ---- switches of the in-place tensor-core GEMM (all default on) ---- */
+/* In-place path only: 1 (default) = the converter warps leave the raw fp32 tile as the hi operand:
+ * the tensor core ignores the 13 low mantissa bits of a kind::tf32 operand (measured on B200: results
+ * are bit-identical to mode 0); 0 = they also store hi = x with those bits cleared. */
+int znn_gemm_set_conv_mode(int mode);
+/* In-place path only: 1 (default) = persistent launch (one CTA pair per SM pair walks the output tiles, so the
+ * next tile's main loop overlaps the previous tile's epilogue); 0 = one CTA pair per output tile. */
+int znn_gemm_set_persistent(int enable);
+/* In-place path only: 1 (default) = when the last round of the persistent walk would be less than 70 % full, its tiles
+ * are cut into K-slices (whole accumulation chunks) run by otherwise idle CTA pairs; the slices' partial tiles are added
+ * in slice order by a small second kernel (deterministic).  0 = every tile is one unit. */
+int znn_gemm_set_tail_split(int enable);
+/* Diagnostic: where the first bounded device-side wait of a tensor-core GEMM expired since the last call (16 ints:
+ * claimed flag, role, barrier, work unit, counter, M, N, K, split-K slices, tile width, CTA rank, CTA pair, units,
+ * pairs, beta*1000, batch); all zero when none did.  Reading clears the record. */
+int znn_gemm_wait_record(int* out16);
+/* Measurement aid: with profiling on, every tensor-core GEMM kernel launch (not its split
+ * pre-pass) is bracketed by CUDA events on the launching stream; znn_gemm_profile_read waits
+ * for them and returns the summed kernel time, the launch count and the algorithmic
+ * floating-point operations (2*M*N*K*batch) of those launches, then clears the record. */
+int znn_gemm_profile(int enable);
+int znn_gemm_profile_read(double* kernel_ms, long long* launches, double* flops);
+
+/* ---- test hooks ---- */
+/* SM cycles a GEMM role waits on an mbarrier before it gives up, sets a ZNN_DEV_*_WAIT_EXPIRED bit in the device status
+ * word and leaves (default 4e9, about 2 s; 0 restores the default).  Applies to kernels launched afterwards. */
+int znn_debug_set_wait_limit(unsigned long long sm_cycles);
+/* Launches a one-thread kernel that waits, with the GEMM roles' own wait routine, on an mbarrier nothing arrives at, for
+ * at most limit_cycles (1 .. 2e9): the wait runs out, ZNN_DEV_TMA_WAIT_EXPIRED is set in the status word and the kernel
+ * returns normally.  Exercises the recovery path (status word -> later GEMMs return without work ->
+ * znn_device_status(clear = 1) restores service) without hanging, trapping or faulting anything. */
+int znn_debug_wait_probe(unsigned long long limit_cycles);
+/* Host-side fault injection: the n-th kernel launch from now (0 = the next one), by any host thread, is reported as a
+ * failed launch (ZNN_ERR_CUDA, "injected failure") although the kernel was enqueued; n < 0 disarms.  Lets tests check
+ * that callers unwind cleanly from an error in the middle of a step. */
+int znn_debug_fail_after(long long n);
+
+/* Runs the data-parallel bucket schedule (when each gradient bucket's all-reduce starts during the backward sweep)
+ * against a caller-supplied reduction, without a GPU: parameters at offsets[0..n_params) of a slab of `total` floats,
+ * buckets of at least bucket_floats, uses[i] tape ops reading parameter i; completion_order lists, one entry per tape op
+ * input, the parameter whose reader just ran backward.  fn(ctx, begin, count) is called for each bucket at the moment
+ * the real schedule would start its all-reduce, and for the rest at the end in slab order; a nonzero return stops all
+ * further reductions and comes back as this call's result. */
+typedef int (*znn_debug_allreduce_fn)(void* ctx, size_t begin, size_t count);
+int znn_debug_bucket_schedule_run(const size_t* offsets, int n_params, size_t total, size_t bucket_floats, const int* uses,
+                                  const int* completion_order, int n_events, znn_debug_allreduce_fn fn, void* ctx,
+                                  int* n_buckets);
+
+#ifdef __cplusplus
+}
+#endif
+#endif

@@ -66,6 +66,10 @@ int znn_model_load(znn_model* m, const char* path);
  * the second moments; the step count is the "adam_t" option. */
 int znn_model_save_optimizer(znn_model* m, const char* path);
 int znn_model_load_optimizer(znn_model* m, const char* path);
+/* The modules' own initialisation (src/nn.zig:22-23, :71-72, :520, :565): weights He-normal with the module's fan-in
+ * (znn_init_he_normal), biases 0, norm gains 1.  Parameter i draws with seed + i; the random stream is not the
+ * reference's (see znn_init_he_normal). */
+int znn_model_init_weights(znn_model* m, unsigned long long seed);
 int znn_model_set_params(znn_model* m, const float* host_slab);
 int znn_model_get_params(znn_model* m, float* host_slab);
 int znn_model_get_grads(znn_model* m, float* host_slab);
@@ -77,7 +81,8 @@ int znn_model_get_velocities(znn_model* m, float* host_slab);
  * share the gradient buffer of their input instead of adding into it in backward), "lazy_zero_grad" (1/0, process-wide:
  * gradient buffers of intermediates are zero-filled only when first added to; GEMM arms overwrite them with beta = 0), "dp_bucket_floats",
  * "dp_overlap" (1/0), "cuda_graph" (1/0: capture the training step once per (input buffers, batch) and replay it;
- * MLP / CNN models with device-resident inputs on one GPU; lr and momentum are baked in at capture),
+ * MLP / CNN models with device-resident inputs on one GPU; the capture is redone when lr, momentum or
+ * a fused_* option changes, or when one of the shim's scratch blocks has moved since),
  * "optimizer" (0 = SGD with "lr" / "momentum" as the example programs use, 1 = Adam, src/optim.zig:69-152, with "lr",
  * "beta1", "beta2", "eps" and the step count "adam_t"; no CUDA-graph replay with Adam: the step size changes per step),
  * "targets_u8" (1/0: the targets pointer of znn_model_train_step holds byte labels, the reference's label type,

@@ -1,4 +1,4 @@
-"""The C-ABI library loads and exports every symbol include/znn_cuda.h declares."""
+"""The C-ABI library loads and exports every symbol the headers under include/ declare."""
 import ctypes
 import os
 
@@ -25,7 +25,7 @@ def test_header_declares_the_hot_path():
 
 
 def test_every_declared_symbol_is_exported(dll):
-    for header in (_lib.HEADER, _lib.HOST_HEADER):
+    for header in _lib.ALL_HEADERS:
         decl = _lib.declared_functions(header)
         assert decl, header
         missing = [n for n, _ in decl if not hasattr(dll, n)]
@@ -34,7 +34,7 @@ def test_every_declared_symbol_is_exported(dll):
 
 def test_ctypes_signatures_resolve():
     L = _lib.lib()
-    for name, types in _lib.declared_functions() + _lib.declared_functions(_lib.HOST_HEADER):
+    for name, types in _lib.all_declared_functions():
         assert len(getattr(L.dll, name).argtypes) == len(types)
 
 

@@ -80,10 +80,10 @@ def test_gather_without_labels_and_unaligned_destination(ds):
     idx = r.integers(0, 50, 20).astype(np.int32)
     d_img, d_idx = ops.DevBuf.from_host(images), ops.DevBuf.from_host(idx)
     d_out = ops.DevBuf((20 * 8 + 1) * 4)
-    lib().call("znn_batch_gather", d_img.ptr, None, d_idx.ptr, d_out.ptr + 4, None, 20, 8)   # dst 4-byte aligned only
+    lib().call("znn_batch_gather", d_img.ptr, None, d_idx.ptr, d_out.ptr + 4, None, 20, 8, 50)   # dst 4-byte aligned only
     np.testing.assert_array_equal(d_out.to_host((20 * 8 + 1,))[1:].reshape(20, 8), images[idx])
     with pytest.raises(RuntimeError):
-        lib().call("znn_batch_gather", d_img.ptr, None, d_idx.ptr, d_out.ptr, d_idx.ptr, 20, 8)
+        lib().call("znn_batch_gather", d_img.ptr, None, d_idx.ptr, d_out.ptr, d_idx.ptr, 20, 8, 50)
 
 
 def test_load_idx_files(ds, tmp_path):

@@ -11,6 +11,8 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 LIB_PATH = os.path.join(HERE, "libznn_cuda.so")
 HEADER = os.path.join(os.path.dirname(HERE), "include", "znn_cuda.h")
 HOST_HEADER = os.path.join(os.path.dirname(HERE), "include", "znn_host.h")
+DEBUG_HEADER = os.path.join(os.path.dirname(HERE), "include", "znn_debug.h")
+ALL_HEADERS = (HEADER, HOST_HEADER, DEBUG_HEADER)
 
 _CTYPES = {
     "int": C.c_int, "float": C.c_float, "double": C.c_double, "size_t": C.c_size_t, "long long": C.c_longlong,
@@ -24,6 +26,11 @@ _CTYPES = {
     "uint8_t*": C.c_void_p, "float**": C.POINTER(C.c_void_p), "uint8_t**": C.POINTER(C.c_void_p),
     "unsigned*": C.POINTER(C.c_uint), "size_t*": C.POINTER(C.c_size_t),
     "znn_loader*": C.c_void_p, "znn_loader**": C.POINTER(C.c_void_p),
+    "unsigned long long": C.c_ulonglong, "unsigned long long*": C.POINTER(C.c_ulonglong),
+    "znn_arena*": C.c_void_p, "znn_arena**": C.POINTER(C.c_void_p),
+    "znn_param_slab*": C.c_void_p, "znn_param_slab**": C.POINTER(C.c_void_p),
+    "const size_t*": C.c_void_p, "const float**": C.c_void_p, "unsigned": C.c_uint,
+    "znn_debug_allreduce_fn": C.c_void_p,
 }
 
 
@@ -51,6 +58,13 @@ def declared_functions(header=HEADER):
     return out
 
 
+def all_declared_functions():
+    out = []
+    for h in ALL_HEADERS:
+        out += declared_functions(h)
+    return out
+
+
 class _Lib:
     def __init__(self):
         if not os.path.exists(LIB_PATH):
@@ -58,7 +72,7 @@ class _Lib:
                 f"{LIB_PATH} is missing: build it with `python -m znn_b200.build` (nvcc, sm_100a). "
                 "There is no CPU or PyTorch fallback.")
         self.dll = C.CDLL(LIB_PATH)
-        for name, types in declared_functions() + declared_functions(HOST_HEADER):
+        for name, types in all_declared_functions():
             fn = getattr(self.dll, name)
             fn.restype = C.c_int
             fn.argtypes = [_CTYPES[t] for t in types]

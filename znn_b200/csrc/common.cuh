@@ -27,6 +27,13 @@ void* workspace_slot(int slot, size_t bytes);
 
 int sm_count();
 
+// Counts the reallocations of scratch blocks on the current device: a holder of raw scratch addresses (a captured
+// CUDA graph) compares it with the value it saw when it took them.
+unsigned long long workspace_generation();
+
+// Test aid (znn_debug_fail_after): true once, for the launch the injected failure was armed for.
+bool inject_launch_failure();
+
 // Kernel-launch counter of the calling host thread (read by znn_launch_count).
 void count_launch();
 
@@ -45,6 +52,8 @@ void count_launch();
             return ::znn::fail(ZNN_ERR_CUDA, "launch of %s failed: %s", name,          \
                                cudaGetErrorString(_e));                                \
         ::znn::count_launch();                                                         \
+        if (::znn::inject_launch_failure())                                            \
+            return ::znn::fail(ZNN_ERR_CUDA, "launch of %s failed: injected failure (znn_debug_fail_after)", name); \
     } while (0)
 
 #define ZNN_REQUIRE(cond, ...)                                                         \

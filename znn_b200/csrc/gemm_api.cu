@@ -5,6 +5,7 @@
 #include <stdlib.h>
 
 #include "common.cuh"
+#include "../../include/znn_debug.h"
 
 namespace znn {
 
@@ -26,6 +27,8 @@ void tc_set_tail_split(int on);
 int tc_wait_record(int* out16);
 void tc_set_conv_mode(int m);
 int tc_profile_read(double* kernel_ms, long long* launches, double* flops);
+void tc_set_wait_limit(unsigned long long cycles);
+int tc_wait_probe(unsigned long long limit_cycles);
 
 // C = alpha * op(A) * op(B) + beta * C with fp32 FMAs, k ascending.
 // 64x64 output tile, 16-deep k slices, 256 threads, 4x4 outputs per thread.
@@ -322,6 +325,14 @@ int znn_gemm_set_conv_mode(int mode)
     tc_set_conv_mode(mode);
     return ZNN_OK;
 }
+
+int znn_debug_set_wait_limit(unsigned long long sm_cycles)
+{
+    tc_set_wait_limit(sm_cycles);
+    return ZNN_OK;
+}
+
+int znn_debug_wait_probe(unsigned long long limit_cycles) { return tc_wait_probe(limit_cycles); }
 
 int znn_gemm_profile(int enable) { return tc_profile_enable(enable); }
 

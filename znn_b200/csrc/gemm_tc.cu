@@ -66,8 +66,8 @@ __device__ __forceinline__ uint32_t mbar_try_wait(uint32_t bar, uint32_t parity)
     return ok;
 }
 
-// Waits at most ~2 s (4e9 SM cycles); false on expiry.
-__device__ __forceinline__ bool mbar_wait_bounded(uint32_t bar, uint32_t parity)
+// Waits at most `limit` SM cycles (default 4e9, ~2 s); false on expiry.
+__device__ __forceinline__ bool mbar_wait_bounded(uint32_t bar, uint32_t parity, uint64_t limit = kWaitLimitCycles)
 {
     if (mbar_try_wait(bar, parity)) return true;
 #pragma unroll 1
@@ -81,7 +81,7 @@ __device__ __forceinline__ bool mbar_wait_bounded(uint32_t bar, uint32_t parity)
             if (mbar_try_wait(bar, parity)) return true;
             if (ZNN_WAIT_SLEEP_NS > 0) __nanosleep(ZNN_WAIT_SLEEP_NS);
         }
-        if (wait_clock() - t0 > kWaitLimitCycles) return false;
+        if (wait_clock() - t0 > limit) return false;
     }
 }
 
@@ -255,6 +255,7 @@ struct GemmTcParams {
     float* C;
     long long ldc, stride_c;
     int* status;
+    unsigned long long wait_limit;   // SM cycles a role waits on an mbarrier before it gives up (znn_debug_set_wait_limit)
 };
 
 constexpr int kBK = 32;          // fp32 elements per k-block = one 128-byte swizzle row
@@ -438,7 +439,7 @@ gemm3x_tf32_kernel(const __grid_constant__ CUtensorMap tm_a_hi, const __grid_con
             for (int kb = 0; kb < kb_count; kb++) {
                 const int s = kb % Cfg::kStages;
                 const uint32_t ph = (kb / Cfg::kStages) & 1;
-                if (!mbar_wait_bounded(empty_bar(s), ph ^ 1)) { ok = false; break; }
+                if (!mbar_wait_bounded(empty_bar(s), ph ^ 1, p.wait_limit)) { ok = false; break; }
                 const uint32_t st = smem_base + s * Cfg::kStageBytes;
                 const int k0 = (kb_first + kb) * kBK;
                 if (CTAS == 1) {
@@ -468,14 +469,14 @@ gemm3x_tf32_kernel(const __grid_constant__ CUtensorMap tm_a_hi, const __grid_con
             for (int c = 0; c < nchunks && ok; c++) {
                 const int buf = c & 1;
                 // the epilogue warps must have drained this buffer (two chunks ago)
-                if (!mbar_wait_bounded(acc_empty_bar(buf), ((c >> 1) & 1) ^ 1)) { ok = false; break; }
+                if (!mbar_wait_bounded(acc_empty_bar(buf), ((c >> 1) & 1) ^ 1, p.wait_limit)) { ok = false; break; }
                 tc_fence_after();
                 const uint32_t d_tmem = tmem_base + (uint32_t)(buf * BN);
                 const int kb_end = min(kb_count, kb + chunk);
                 for (bool first = true; kb < kb_end; kb++) {
                     const int s = kb % Cfg::kStages;
                     const uint32_t ph = (kb / Cfg::kStages) & 1;
-                    if (!mbar_wait_bounded(full_bar(s), ph)) { ok = false; break; }
+                    if (!mbar_wait_bounded(full_bar(s), ph, p.wait_limit)) { ok = false; break; }
                     tc_fence_after();
                     const uint32_t st = smem_base + s * Cfg::kStageBytes;
                     const uint64_t a_hi = make_kmajor_sw128_desc(st);
@@ -511,7 +512,7 @@ gemm3x_tf32_kernel(const __grid_constant__ CUtensorMap tm_a_hi, const __grid_con
         bool got = true;
         for (int c = 0; c < nchunks; c++) {
             const int buf = c & 1;
-            if (lane == 0) got = mbar_wait_bounded(acc_full_bar(buf), (c >> 1) & 1);
+            if (lane == 0) got = mbar_wait_bounded(acc_full_bar(buf), (c >> 1) & 1, p.wait_limit);
             got = __shfl_sync(0xffffffffu, (int)got, 0) != 0;
             if (!got) break;
             tc_fence_after();
@@ -665,7 +666,7 @@ __device__ __forceinline__ uint32_t mbar_try_wait_cluster(uint32_t bar, uint32_t
     return ok;
 }
 
-__device__ __forceinline__ bool mbar_wait_bounded_cluster(uint32_t bar, uint32_t parity)
+__device__ __forceinline__ bool mbar_wait_bounded_cluster(uint32_t bar, uint32_t parity, uint64_t limit = kWaitLimitCycles)
 {
     if (mbar_try_wait_cluster(bar, parity)) return true;
 #pragma unroll 1
@@ -679,7 +680,7 @@ __device__ __forceinline__ bool mbar_wait_bounded_cluster(uint32_t bar, uint32_t
             if (mbar_try_wait_cluster(bar, parity)) return true;
             if (ZNN_WAIT_SLEEP_NS > 0) __nanosleep(ZNN_WAIT_SLEEP_NS);
         }
-        if (wait_clock() - t0 > kWaitLimitCycles) return false;
+        if (wait_clock() - t0 > limit) return false;
     }
 }
 
@@ -1111,7 +1112,7 @@ gemm3x_direct_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_cons
                 for (int kb = 0; kb < d.kb_count; kb++, it++) {
                     const int s = it % S;
                     const uint32_t ph = (it / S) & 1;
-                    if (!ZNN_PROF_WAIT(mbar_wait_bounded(empty_bar(s), ph ^ 1))) { record_expiry(0, 0, u, it, cta_rank, pair); ok = false; break; }
+                    if (!ZNN_PROF_WAIT(mbar_wait_bounded(empty_bar(s), ph ^ 1, p.wait_limit))) { record_expiry(0, 0, u, it, cta_rank, pair); ok = false; break; }
                     const uint32_t st = smem_base + s * Cfg::kStageBytes;
                     const int k0 = (d.kb_first + kb) * kBK;
                     mbar_arrive_expect_tx(full_bar(s), Cfg::kABytes + Cfg::kBBytes);
@@ -1151,14 +1152,14 @@ gemm3x_direct_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_cons
                 for (int c = 0; c < d.nchunks && ok; c++, cc++) {
                     const int buf = cc & 1;
                     // the epilogue warps must have drained this buffer (two chunks ago, possibly of the previous unit)
-                    if (!ZNN_PROF_WAIT(mbar_wait_bounded_cluster(acc_empty_bar(buf), ((cc >> 1) & 1) ^ 1))) { record_expiry(1, 3, u, cc, cta_rank, pair); ok = false; break; }
+                    if (!ZNN_PROF_WAIT(mbar_wait_bounded_cluster(acc_empty_bar(buf), ((cc >> 1) & 1) ^ 1, p.wait_limit))) { record_expiry(1, 3, u, cc, cta_rank, pair); ok = false; break; }
                     tc_fence_after();
                     const uint32_t d_tmem = tmem_base + (uint32_t)(buf * BN);
                     const int kb_end = min(d.kb_count, kb + chunk);
                     for (bool first = true; kb < kb_end; kb++, it++) {
                         const int s = it % S;
                         const uint32_t ph = (it / S) & 1;
-                        if (!ZNN_PROF_WAIT(mbar_wait_bounded_cluster(conv_bar(s), ph))) { record_expiry(1, 2, u, it, cta_rank, pair); ok = false; break; }
+                        if (!ZNN_PROF_WAIT(mbar_wait_bounded_cluster(conv_bar(s), ph, p.wait_limit))) { record_expiry(1, 2, u, it, cta_rank, pair); ok = false; break; }
                         tc_fence_after();
                         const uint32_t st = smem_base + s * Cfg::kStageBytes;
                         const uint64_t a_hi = A_MN ? make_mnmajor_sw128_desc(st) : make_kmajor_sw128_desc(st);
@@ -1199,7 +1200,7 @@ gemm3x_direct_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_cons
                 const int s = it % S;
                 const uint32_t ph = (it / S) & 1;
                 if (lane == 0) {
-                    got = ZNN_PROF_WAIT(mbar_wait_bounded(full_bar(s), ph));
+                    got = ZNN_PROF_WAIT(mbar_wait_bounded(full_bar(s), ph, p.wait_limit));
                     if (!got) record_expiry(2, 1, u, it, cta_rank, pair);
                 }
                 got = __shfl_sync(0xffffffffu, (int)got, 0) != 0;
@@ -1268,7 +1269,7 @@ gemm3x_direct_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_cons
             for (int c = 0; c < d.nchunks; c++, cc++) {
                 const int buf = cc & 1;
                 if (lane == 0) {
-                    got = ZNN_PROF_WAIT(mbar_wait_bounded(acc_full_bar(buf), (cc >> 1) & 1));
+                    got = ZNN_PROF_WAIT(mbar_wait_bounded(acc_full_bar(buf), (cc >> 1) & 1, p.wait_limit));
                     if (!got) record_expiry(3, 4, u, cc, cta_rank, pair);
                 }
                 got = __shfl_sync(0xffffffffu, (int)got, 0) != 0;
@@ -1429,9 +1430,33 @@ __global__ void tail_reduce_kernel(const GemmTcParams p)
     }
 }
 
+// Test aid for the bounded-wait recovery path: one thread waits, with the same wait routine as the GEMM roles, on an
+// mbarrier that nothing ever arrives at; when the limit runs out it records the expiry in the device status word, as
+// a GEMM role would, and returns.  No trap, no fault: the context stays usable.
+__global__ void wait_probe_kernel(int* status, unsigned long long limit)
+{
+    __shared__ __align__(8) uint64_t bar;
+    if (threadIdx.x == 0) {
+        const uint32_t b = smem_u32(&bar);
+        mbar_init(b, 1);
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        if (!mbar_wait_bounded(b, 0, limit)) atomicOr(status, ZNN_DEV_TMA_WAIT_EXPIRED);
+    }
+}
+
 // ---------------------------------------------------------------------------
 // host side
 // ---------------------------------------------------------------------------
+int tc_wait_probe(unsigned long long limit_cycles)
+{
+    int* status = device_status_word();
+    if (!status) return fail(ZNN_ERR_CUDA, "no device state (call znn_init first)");
+    if (limit_cycles == 0 || limit_cycles > 2000000000ull) return fail(ZNN_ERR_INVALID, "limit must be 1 .. 2e9 cycles");
+    wait_probe_kernel<<<1, 32, 0, stream()>>>(status, limit_cycles);
+    ZNN_LAUNCH_OK("wait_probe_kernel");
+    return ZNN_OK;
+}
+
 int launch_splitk_reduce(const float* partial, int splits, int M, int N, int batch, float alpha, float beta, float* C,
                          long long ldc, long long stride_c, const float* bias)
 {
@@ -1555,11 +1580,15 @@ template <int BN, int CTAS>
 static int launch_tc(const CUtensorMap* maps, const GemmTcParams& p, int batch)
 {
     using Cfg = TcCfg<BN, CTAS>;
-    static bool attr_set = false;
+    // the attribute is per device: a process that drives several GPUs sets it once on each
+    static bool attr_set[64] = {false};
     auto kern = gemm3x_tf32_kernel<BN, CTAS>;
-    if (!attr_set) {
+    int adev = 0;
+    ZNN_CUDA_OK(cudaGetDevice(&adev));
+    if (adev < 0 || adev >= 64) return fail(ZNN_ERR_INVALID, "device index %d out of range", adev);
+    if (!attr_set[adev]) {
         ZNN_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmemBytes));
-        attr_set = true;
+        attr_set[adev] = true;
     }
     cudaLaunchConfig_t cfg = {};
     const int splits = (p.k_blocks + p.kblocks_per_split - 1) / p.kblocks_per_split;
@@ -1578,9 +1607,13 @@ static int launch_tc(const CUtensorMap* maps, const GemmTcParams& p, int batch)
     ZNN_CUDA_OK(cudaLaunchKernelEx(&cfg, kern, maps[0], maps[1], maps[2], maps[3], p));
     prof_end(ev);
     count_launch();
+    if (inject_launch_failure()) return fail(ZNN_ERR_CUDA, "launch of the tensor-core GEMM failed: injected failure (znn_debug_fail_after)");
     return ZNN_OK;
 }
 
+static unsigned long long g_wait_limit = kWaitLimitCycles;
+void tc_set_wait_limit(unsigned long long cycles) { g_wait_limit = cycles ? cycles : kWaitLimitCycles; }
+unsigned long long tc_wait_limit() { return g_wait_limit; }
 static thread_local int t_conv_mode = 1;
 void tc_set_conv_mode(int m) { t_conv_mode = m; }
 static thread_local bool t_tail_split = true;
@@ -1728,6 +1761,7 @@ int gemm_tc(int ta, int tb, int M, int N, int K, float alpha, const float* A, lo
     p.tiles_m = tiles_m;
     p.tiles_n = tiles_n;
     p.alpha = alpha; p.beta = beta; p.C = C; p.ldc = ldc; p.stride_c = stride_c; p.status = status;
+    p.wait_limit = g_wait_limit;
 
     CUtensorMap maps[4];
     if ((rc = make_plane_map(&maps[0], a_hi, M, kpad, batch, kTileM))) return rc;
@@ -1776,11 +1810,15 @@ template <int BN, bool A_MN, bool B_MN>
 static int launch_direct(const CUtensorMap& ma, const CUtensorMap& mb, const GemmTcParams& p_in, int batch)
 {
     using Cfg = DirectCfg<BN>;
-    static bool attr_set = false;
+    // the attribute is per device: a process that drives several GPUs sets it once on each
+    static bool attr_set[64] = {false};
     auto kern = gemm3x_direct_kernel<BN, A_MN, B_MN>;
-    if (!attr_set) {
+    int dev = 0;
+    ZNN_CUDA_OK(cudaGetDevice(&dev));
+    if (dev < 0 || dev >= 64) return fail(ZNN_ERR_INVALID, "device index %d out of range", dev);
+    if (!attr_set[dev]) {
         ZNN_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmemBytes));
-        attr_set = true;
+        attr_set[dev] = true;
     }
     GemmTcParams p = p_in;
     p.splits = (p.k_blocks + p.kblocks_per_split - 1) / p.kblocks_per_split;
@@ -1805,9 +1843,6 @@ static int launch_direct(const CUtensorMap& ma, const CUtensorMap& mb, const Gem
     cfg.numAttrs = 1;
     // persistent: one CTA pair per pair of SMs that can hold one (asked of the driver once per device)
     static int pairs_by_device[64] = {0};
-    int dev = 0;
-    ZNN_CUDA_OK(cudaGetDevice(&dev));
-    if (dev < 0 || dev >= 64) return fail(ZNN_ERR_INVALID, "device index %d out of range", dev);
     if (pairs_by_device[dev] == 0) {
         cfg.gridDim = dim3((unsigned)sm_count(), 1, 1);
         int clusters = 0;
@@ -1823,6 +1858,7 @@ static int launch_direct(const CUtensorMap& ma, const CUtensorMap& mb, const Gem
     ZNN_CUDA_OK(cudaLaunchKernelEx(&cfg, kern, ma, mb, p));
     prof_end(ev);
     count_launch();
+    if (inject_launch_failure()) return fail(ZNN_ERR_CUDA, "launch of the tensor-core GEMM failed: injected failure (znn_debug_fail_after)");
     return ZNN_OK;
 }
 
@@ -1940,6 +1976,7 @@ int gemm_tc_direct(int ta, int tb, int M, int N, int K, float alpha, const float
         p.tri_n = n;
     }
     p.alpha = alpha; p.beta = beta; p.C = C; p.ldc = ldc; p.stride_c = stride_c; p.status = status;
+    p.wait_limit = g_wait_limit;
     if (pl.bn == 256) rc = launch_direct_major<256>(a_mn, b_mn, ma, mb, p, batch);
     else if (pl.bn == 128) rc = launch_direct_major<128>(a_mn, b_mn, ma, mb, p, batch);
     else rc = launch_direct_major<64>(a_mn, b_mn, ma, mb, p, batch);

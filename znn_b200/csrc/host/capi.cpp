@@ -8,6 +8,8 @@
 
 #include "../../../include/znn_cuda.h"
 #include "../../../include/znn_host.h"
+#include "../../../include/znn_debug.h"
+#include "bucket_schedule.hpp"
 #include "nn.hpp"
 
 namespace znn {
@@ -226,6 +228,9 @@ struct znn_model {
     int graph_batch = 0, graph_seen = 0;
     float* graph_loss = nullptr;
     long long graph_replays = 0;
+    // the captured kernels hold raw addresses of the shim's scratch blocks: the graph is only valid while none of
+    // them has moved since the capture (znn_workspace_generation)
+    unsigned long long graph_generation = 0;
 };
 
 static void drop_graph(znn_model* m)
@@ -237,69 +242,47 @@ static void drop_graph(znn_model* m)
 
 namespace {
 
-struct Bucket {
-    size_t begin, end;  // float range of the gradient slab
-    int pending;        // parameters whose gradient is not complete yet
-    bool fired;
-};
-
-// Starts the all-reduce of a gradient bucket as soon as the backward sweep has run
-// every op that writes into it.
+// Starts the all-reduce of a gradient bucket as soon as the backward sweep has run every op that writes into it
+// (the bookkeeping is BucketSchedule; this class maps tape ops to parameters and fires NCCL).
 class DpSchedule {
 public:
-    DpSchedule(znn_model& m, const Graph& g) : m_(m)
-    {
-        const auto& ps = m.ps.params();
-        remaining_.assign(ps.size(), 0);
-        for (const Op* op : g.ops())
-            for (const Tensor* in : op->inputs) {
-                auto it = m.param_index.find(in);
-                if (it != m.param_index.end()) remaining_[it->second]++;
-            }
-        bucket_of_.assign(ps.size(), 0);
-        size_t begin = 0;
-        for (size_t i = 0; i < ps.size(); i++) {
-            const size_t end = (i + 1 < ps.size()) ? ps[i + 1].offset : m.ps.total();
-            bucket_of_[i] = (int)buckets_.size();
-            if (end - begin >= m.dp_bucket_floats || i + 1 == ps.size()) {
-                buckets_.push_back(Bucket{begin, end, 0, false});
-                begin = end;
-            }
-        }
-        for (size_t i = 0; i < ps.size(); i++)
-            if (remaining_[i] > 0) buckets_[bucket_of_[i]].pending++;
-    }
+    DpSchedule(znn_model& m, const Graph& g) : m_(m), sched_(make(m, g)) {}
 
     void after(Op* op)
     {
         for (const Tensor* in : op->inputs) {
             auto it = m_.param_index.find(in);
             if (it == m_.param_index.end()) continue;
-            if (--remaining_[it->second] == 0) {
-                Bucket& b = buckets_[bucket_of_[it->second]];
-                if (--b.pending == 0) fire(b);
-            }
+            check(sched_.after(it->second), "gradient all-reduce");
         }
     }
 
     void finish()
     {
-        for (Bucket& b : buckets_)
-            if (!b.fired) fire(b);
+        check(sched_.finish(), "gradient all-reduce");
         check(znn_dp_join(), "znn_dp_join");
     }
 
-    size_t buckets() const { return buckets_.size(); }
+    size_t buckets() const { return sched_.buckets(); }
 
 private:
-    void fire(Bucket& b)
+    static BucketSchedule make(znn_model& m, const Graph& g)
     {
-        b.fired = true;
-        check(znn_dp_allreduce_async(m_.ps.grads() + b.begin, b.end - b.begin), "gradient all-reduce");
+        const auto& ps = m.ps.params();
+        std::vector<size_t> offsets(ps.size());
+        std::vector<int> uses(ps.size(), 0);
+        for (size_t i = 0; i < ps.size(); i++) offsets[i] = ps[i].offset;
+        for (const Op* op : g.ops())
+            for (const Tensor* in : op->inputs) {
+                auto it = m.param_index.find(in);
+                if (it != m.param_index.end()) uses[it->second]++;
+            }
+        float* grads = m.ps.grads();
+        return BucketSchedule(offsets, m.ps.total(), m.dp_bucket_floats, uses,
+                              [grads](size_t begin, size_t count) { return znn_dp_allreduce_async(grads + begin, count); });
     }
     znn_model& m_;
-    std::vector<int> remaining_, bucket_of_;
-    std::vector<Bucket> buckets_;
+    BucketSchedule sched_;
 };
 
 Tensor* wrap_device(Graph& g, const Shape& s, const float* dev)
@@ -464,6 +447,10 @@ int znn_model_set_option(znn_model* m, const char* key, double value)
 {
     ZNN_HOST_TRY
     const std::string k(key ? key : "");
+    // every option that changes a baked-in kernel argument or the launch sequence invalidates a captured step
+    if (k == "lr" || k == "momentum" || k.rfind("fused_", 0) == 0 || k == "causal_skip" || k == "alias_reshape_grad" ||
+        k == "lazy_zero_grad" || k == "fused_attention")
+        drop_graph(m);
     if (k == "lr") m->opt.lr = m->adam.lr = (float)value;
     else if (k == "optimizer") {
         if (value != 0.0 && value != 1.0) throw Error(ZNN_ERR_INVALID, "optimizer: 0 = SGD, 1 = Adam");
@@ -552,7 +539,9 @@ int znn_model_train_step(znn_model* m, const float* x, const int32_t* targets, i
     if (!can_replay) {
         loss_dev = run_train_step(m, x, targets, batch, seq, on_device != 0);
     } else {
-        if (m->graph_x != x || m->graph_t != targets || m->graph_batch != batch) {
+        unsigned long long gen = 0;
+        check(znn_workspace_generation(&gen), "znn_workspace_generation");
+        if (m->graph_x != x || m->graph_t != targets || m->graph_batch != batch || (m->graph_exec && gen != m->graph_generation)) {
             drop_graph(m);
             m->graph_x = x;
             m->graph_t = targets;
@@ -593,6 +582,7 @@ int znn_model_train_step(znn_model* m, const float* x, const int32_t* targets, i
                 m->graph_exec = nullptr;
                 throw Error(ZNN_ERR_CUDA, std::string("cudaGraphInstantiate: ") + cudaGetErrorString(e));
             }
+            check(znn_workspace_generation(&m->graph_generation), "znn_workspace_generation");
             if (cudaGraphLaunch(m->graph_exec, st) != cudaSuccess)
                 throw Error(ZNN_ERR_CUDA, std::string("cudaGraphLaunch: ") + cudaGetErrorString(cudaGetLastError()));
             m->graph_replays++;
@@ -976,6 +966,186 @@ int znn_model_last_step_ops(znn_model* m, int* n_ops)
 {
     ZNN_HOST_TRY
     if (n_ops) *n_ops = m->last_ops;
+    ZNN_HOST_CATCH
+}
+
+}  // extern "C"
+
+// ------------------------------------------------------------------ arena, parameter slabs, initialisation
+struct znn_arena {
+    std::unique_ptr<Arena> a;
+};
+
+struct znn_param_slab {
+    size_t total = 0;
+    std::vector<size_t> offsets;
+    float *w = nullptr, *g = nullptr, *v = nullptr;
+};
+
+extern "C" {
+
+int znn_arena_create(size_t bytes, znn_arena** out)
+{
+    ZNN_HOST_TRY
+    if (!out) throw Error(ZNN_ERR_INVALID, "out is NULL");
+    std::unique_ptr<znn_arena> a(new znn_arena());
+    a->a.reset(new Arena(bytes));
+    *out = a.release();
+    ZNN_HOST_CATCH
+}
+
+int znn_arena_alloc(znn_arena* a, size_t bytes, void** ptr)
+{
+    ZNN_HOST_TRY
+    if (!a || !ptr) throw Error(ZNN_ERR_INVALID, "arena/ptr is NULL");
+    *ptr = a->a->alloc(bytes);
+    ZNN_HOST_CATCH
+}
+
+int znn_arena_reset(znn_arena* a)
+{
+    ZNN_HOST_TRY
+    if (!a) throw Error(ZNN_ERR_INVALID, "arena is NULL");
+    a->a->reset();
+    ZNN_HOST_CATCH
+}
+
+int znn_arena_usage(znn_arena* a, size_t* used, size_t* high_water, size_t* capacity)
+{
+    ZNN_HOST_TRY
+    if (!a) throw Error(ZNN_ERR_INVALID, "arena is NULL");
+    if (used) *used = a->a->used();
+    if (high_water) *high_water = a->a->high_water();
+    if (capacity) *capacity = a->a->capacity();
+    ZNN_HOST_CATCH
+}
+
+int znn_arena_destroy(znn_arena* a)
+{
+    ZNN_HOST_TRY
+    if (a) {
+        znn_sync();
+        delete a;
+    }
+    ZNN_HOST_CATCH
+}
+
+int znn_param_slab_create(const size_t* counts, int n, znn_param_slab** out)
+{
+    ZNN_HOST_TRY
+    if (!counts || n <= 0 || !out) throw Error(ZNN_ERR_INVALID, "counts/out is NULL or n <= 0");
+    std::unique_ptr<znn_param_slab> s(new znn_param_slab());
+    for (int i = 0; i < n; i++) {
+        s->offsets.push_back(s->total);
+        s->total += (counts[i] + 3) & ~(size_t)3;   // every parameter starts 16-byte aligned
+    }
+    const size_t bytes = s->total * sizeof(float);
+    void* p = nullptr;
+    float** slabs[3] = {&s->w, &s->g, &s->v};
+    for (float** slab : slabs) {
+        const int rc = znn_malloc(&p, bytes);
+        if (rc != ZNN_OK) {
+            znn_free(s->w);
+            znn_free(s->g);
+            znn_free(s->v);
+            check(rc, "znn_param_slab_create");
+        }
+        *slab = (float*)p;
+        check(znn_memset(p, 0, bytes), "znn_memset");
+    }
+    *out = s.release();
+    ZNN_HOST_CATCH
+}
+
+int znn_param_slab_total(znn_param_slab* s, size_t* total_floats)
+{
+    ZNN_HOST_TRY
+    if (!s || !total_floats) throw Error(ZNN_ERR_INVALID, "slab/total_floats is NULL");
+    *total_floats = s->total;
+    ZNN_HOST_CATCH
+}
+
+int znn_param_slab_tensor(znn_param_slab* s, int i, float** value, float** grad, float** velocity, size_t* offset)
+{
+    ZNN_HOST_TRY
+    if (!s || i < 0 || (size_t)i >= s->offsets.size()) throw Error(ZNN_ERR_INVALID, "slab is NULL or index out of range");
+    const size_t off = s->offsets[i];
+    if (value) *value = s->w + off;
+    if (grad) *grad = s->g + off;
+    if (velocity) *velocity = s->v + off;
+    if (offset) *offset = off;
+    ZNN_HOST_CATCH
+}
+
+int znn_param_slab_zero_grad(znn_param_slab* s)
+{
+    ZNN_HOST_TRY
+    if (!s) throw Error(ZNN_ERR_INVALID, "slab is NULL");
+    check(znn_memset(s->g, 0, s->total * sizeof(float)), "zeroGrad");
+    ZNN_HOST_CATCH
+}
+
+int znn_param_slab_sgd_step(znn_param_slab* s, float lr, float momentum, float grad_scale)
+{
+    ZNN_HOST_TRY
+    if (!s) throw Error(ZNN_ERR_INVALID, "slab is NULL");
+    check(znn_sgd_step(s->w, s->g, momentum > 0.0f ? s->v : nullptr, lr, momentum, grad_scale, s->total), "SGD step");
+    ZNN_HOST_CATCH
+}
+
+int znn_param_slab_allreduce_grads(znn_param_slab* s)
+{
+    ZNN_HOST_TRY
+    if (!s) throw Error(ZNN_ERR_INVALID, "slab is NULL");
+    check(znn_dp_allreduce(s->g, s->total), "gradient all-reduce");
+    ZNN_HOST_CATCH
+}
+
+int znn_param_slab_destroy(znn_param_slab* s)
+{
+    ZNN_HOST_TRY
+    if (s) {
+        znn_sync();
+        znn_free(s->w);
+        znn_free(s->g);
+        znn_free(s->v);
+        delete s;
+    }
+    ZNN_HOST_CATCH
+}
+
+// The modules' init rule (src/nn.zig:22-23, :71-72, :520, :565): weights He-normal with the module's fan-in, biases 0,
+// norm gains 1.  Parameter i draws with seed + i.
+int znn_model_init_weights(znn_model* m, unsigned long long seed)
+{
+    ZNN_HOST_TRY
+    if (!m) throw Error(ZNN_ERR_INVALID, "model is NULL");
+    unsigned long long k = 0;
+    for (const ParamInfo& pi : m->ps.params()) {
+        const size_t n = pi.tensor->numel();
+        const bool is_bias = pi.name.size() >= 5 && pi.name.compare(pi.name.size() - 5, 5, ".bias") == 0;
+        if (pi.fan_in > 0) check(znn_init_he_normal(pi.tensor->data, n, pi.fan_in, seed + k), "znn_init_he_normal");
+        else check(znn_fill(pi.tensor->data, is_bias ? 0.0f : 1.0f, n), "znn_fill");
+        k++;
+    }
+    drop_graph(m);
+    ZNN_HOST_CATCH
+}
+
+int znn_debug_bucket_schedule_run(const size_t* offsets, int n_params, size_t total, size_t bucket_floats, const int* uses,
+                                  const int* completion_order, int n_events, znn_debug_allreduce_fn fn, void* ctx,
+                                  int* n_buckets)
+{
+    ZNN_HOST_TRY
+    if (!offsets || !uses || n_params <= 0 || !fn) throw Error(ZNN_ERR_INVALID, "offsets/uses/fn is NULL or n_params <= 0");
+    BucketSchedule sched(std::vector<size_t>(offsets, offsets + n_params), total, bucket_floats,
+                         std::vector<int>(uses, uses + n_params),
+                         [fn, ctx](size_t begin, size_t count) { return fn(ctx, begin, count); });
+    if (n_buckets) *n_buckets = (int)sched.buckets();
+    int rc = 0;
+    for (int e = 0; e < n_events && rc == 0; e++) rc = sched.after(completion_order[e]);
+    if (rc == 0) rc = sched.finish();
+    if (rc != 0) return znn::fail(rc, "bucket schedule: the reduction callback returned %d", rc);
     ZNN_HOST_CATCH
 }
 

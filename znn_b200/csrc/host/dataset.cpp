@@ -250,7 +250,7 @@ int znn_loader_next_into(znn_loader* l, float* x_dest, uint8_t* y_dest, size_t* 
     if (take == 0) return ZNN_OK;
     if (!x_dest || !y_dest) return znn::fail(ZNN_ERR_INVALID, "x_dest/y_dest is NULL");
     const int rc = znn_batch_gather(l->images, l->labels, l->d_indices + l->current_index, x_dest, y_dest, (int)take,
-                                    l->input_dim);
+                                    l->input_dim, l->num_samples);
     if (rc != ZNN_OK) return rc;
     l->current_index += take;
     *n = take;

@@ -279,7 +279,8 @@ static void colsum_plan(int M, int& chunks, int& rows_per_chunk)
 // ---------------------------------------------------------------------------
 template <class TargetT>
 __global__ void softmax_xent_fwd_kernel(const float* __restrict__ logits, const TargetT* __restrict__ targets,
-                                        float* __restrict__ probs, float* __restrict__ rowloss, int N)
+                                        float* __restrict__ probs, float* __restrict__ rowloss, int N,
+                                        int* __restrict__ status)
 {
     __shared__ float sh[32];
     const size_t row = blockIdx.x;
@@ -294,8 +295,15 @@ __global__ void softmax_xent_fwd_kernel(const float* __restrict__ logits, const 
     for (int j = threadIdx.x; j < N; j += blockDim.x) p[j] = expf(x[j] - mx) / sum;
     if (threadIdx.x == 0) {
         const int t = (int)targets[row];
-        const float pt = expf(x[t] - mx) / sum;
-        rowloss[row] = -logf(fmaxf(pt, 1e-15f));
+        if (t < 0 || t >= N) {
+            // a label outside [0, N): nothing is read through it; the row's loss (and so the mean) becomes NaN and the
+            // device status word says why (the reference asserts on the same condition)
+            rowloss[row] = CUDART_NAN_F;
+            if (status) atomicOr(status, ZNN_DEV_BAD_INDEX);
+        } else {
+            const float pt = expf(x[t] - mx) / sum;
+            rowloss[row] = -logf(fmaxf(pt, 1e-15f));
+        }
     }
 }
 
@@ -304,7 +312,7 @@ __global__ void softmax_xent_fwd_kernel(const float* __restrict__ logits, const 
 template <class TargetT, int V4>
 __global__ void __launch_bounds__(256)
 softmax_xent_fwd_reg_kernel(const float* __restrict__ logits, const TargetT* __restrict__ targets,
-                            float* __restrict__ probs, float* __restrict__ rowloss, int N)
+                            float* __restrict__ probs, float* __restrict__ rowloss, int N, int* __restrict__ status)
 {
     __shared__ float sh[32];
     const size_t row = blockIdx.x;
@@ -334,6 +342,10 @@ softmax_xent_fwd_reg_kernel(const float* __restrict__ logits, const TargetT* __r
     }
     sum = block_sum(sum, sh);
     const int t = (int)targets[row];
+    if ((t < 0 || t >= N) && threadIdx.x == 0) {   // see softmax_xent_fwd_kernel
+        rowloss[row] = CUDART_NAN_F;
+        if (status) atomicOr(status, ZNN_DEV_BAD_INDEX);
+    }
 #pragma unroll
     for (int k = 0; k < V4; k++) {
         const int j4 = threadIdx.x + 256 * k;
@@ -687,12 +699,19 @@ __global__ void layernorm_bwd_rows_kernel(const float* __restrict__ X, const flo
 // Embedding
 // ---------------------------------------------------------------------------
 __global__ void embedding_fwd_kernel(const float* __restrict__ W, const float* __restrict__ ids, float* __restrict__ Y,
-                                     size_t n, int D)
+                                     size_t n, int D, int vocab, int* __restrict__ status)
 {
     for (size_t i = blockIdx.x; i < n; i += gridDim.x) {
-        const size_t idx = (size_t)ids[i];
-        const float* w = W + idx * D;
+        const float idf = ids[i];
         float* y = Y + i * D;
+        if (!(idf >= 0.0f && idf < (float)vocab)) {
+            // an id outside [0, vocab) (the reference asserts idx < VocabSize): no table row is read, the output row is
+            // zero and the device status word says why
+            for (int j = threadIdx.x; j < D; j += blockDim.x) y[j] = 0.0f;
+            if (threadIdx.x == 0) atomicOr(status, ZNN_DEV_BAD_INDEX);
+            continue;
+        }
+        const float* w = W + (size_t)idf * D;
         for (int j = threadIdx.x; j < D; j += blockDim.x) y[j] = w[j];
     }
 }
@@ -944,19 +963,82 @@ __global__ void pixels_to_unit_kernel(const uint8_t* __restrict__ px, float* __r
 // one batch of sample rows and labels picked by index; blockIdx.y = slot in the batch
 __global__ void batch_gather_kernel(const float* __restrict__ images, const uint8_t* __restrict__ labels,
                                     const int32_t* __restrict__ indices, float* __restrict__ x_dest,
-                                    uint8_t* __restrict__ y_dest, int input_dim, int vec_ok)
+                                    uint8_t* __restrict__ y_dest, int input_dim, int vec_ok, size_t num_samples,
+                                    int* __restrict__ status)
 {
     const int j = blockIdx.y;
-    const size_t idx = (size_t)indices[j];
-    const float* src = images + idx * (size_t)input_dim;
+    const int32_t raw = indices[j];
     float* dst = x_dest + (size_t)j * input_dim;
     const int tid = blockIdx.x * blockDim.x + threadIdx.x, nth = gridDim.x * blockDim.x;
+    if (raw < 0 || (size_t)raw >= num_samples) {
+        // a sample index outside the dataset: nothing is read through it; the slot is zero-filled and flagged
+        for (int i = tid; i < input_dim; i += nth) dst[i] = 0.0f;
+        if (tid == 0) {
+            if (y_dest) y_dest[j] = 0;
+            atomicOr(status, ZNN_DEV_BAD_INDEX);
+        }
+        return;
+    }
+    const size_t idx = (size_t)raw;
+    const float* src = images + idx * (size_t)input_dim;
     if (vec_ok) {
         for (int i = tid; i < input_dim / 4; i += nth) reinterpret_cast<float4*>(dst)[i] = reinterpret_cast<const float4*>(src)[i];
     } else {
         for (int i = tid; i < input_dim; i += nth) dst[i] = src[i];
     }
     if (tid == 0 && labels && y_dest) y_dest[j] = labels[idx];
+}
+
+// ---------------------------------------------------------------------------
+// Random fills (weight initialisation)
+// ---------------------------------------------------------------------------
+// Counter-based generator: element i of a fill with seed s draws from hash(s, i, draw), so the result does not depend
+// on the launch geometry.  The reference draws from Zig's DefaultPrng stream, which cannot be reproduced here; the
+// distribution and the fan-in rule are the reference's, the stream is not.
+__device__ __forceinline__ uint64_t mix64(uint64_t z)
+{
+    z += 0x9E3779B97F4A7C15ull;
+    z = (z ^ (z >> 30)) * 0xBF58476D1CE4E5B9ull;
+    z = (z ^ (z >> 27)) * 0x94D049BB133111EBull;
+    return z ^ (z >> 31);
+}
+
+// uniform in [0, 1) with 24 random bits, the granularity of a float drawn as in std.Random.float(f32)
+__device__ __forceinline__ float uniform24(uint64_t seed, uint64_t index, uint32_t draw)
+{
+    const uint64_t h = mix64(mix64(seed ^ (index * 0xD1342543DE82EF95ull)) + draw);
+    return (float)(uint32_t)(h >> 40) * (1.0f / 16777216.0f);
+}
+
+// Box-Muller pair for element pair `pair` (src/nn.zig:1343-1350, src/tensor.zig:354-373): u1 is redrawn while it is 0
+__device__ __forceinline__ void box_muller(uint64_t seed, uint64_t pair, float& radius, float& angle)
+{
+    float u1 = 0.0f;
+    uint32_t draw = 0;
+    while (u1 == 0.0f && draw < 64) u1 = uniform24(seed, pair, draw++);
+    if (u1 == 0.0f) u1 = 1.0f / 16777216.0f;
+    const float u2 = uniform24(seed, pair, 64);
+    radius = sqrtf(-2.0f * logf(u1));
+    angle = 6.283185307179586f * u2;
+}
+
+// mode 0: every element its own draw, cosine branch only (initializeWeights / normalRandom of src/nn.zig:1336-1350);
+// mode 1: elements 2k and 2k+1 share one draw, cosine then sine (Tensor.fillNormal, src/tensor.zig:354-373)
+__global__ void fill_normal_kernel(float* __restrict__ w, size_t n, float mean, float stddev, uint64_t seed, int mode)
+{
+    for (size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x) {
+        float r, a;
+        box_muller(seed, mode == 0 ? i : (i >> 1), r, a);
+        const float z = (mode == 1 && (i & 1)) ? r * sinf(a) : r * cosf(a);
+        w[i] = mean + z * stddev;
+    }
+}
+
+// Tensor.fillUniform (src/tensor.zig:375-379)
+__global__ void fill_uniform_kernel(float* __restrict__ w, size_t n, float lo, float range, uint64_t seed)
+{
+    for (size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x)
+        w[i] = lo + uniform24(seed, i, 0) * range;
 }
 
 // fraction of rows whose predicted class (fp32 index, as argmax writes it) equals the byte label; one block,
@@ -1000,7 +1082,7 @@ int znn_pixels_to_unit(const uint8_t* pixels, float* out, size_t n)
 }
 
 int znn_batch_gather(const float* images, const uint8_t* labels, const int32_t* indices, float* x_dest, uint8_t* y_dest,
-                     int batch, int input_dim)
+                     int batch, int input_dim, size_t num_samples)
 {
     if (batch <= 0 || input_dim <= 0) return ZNN_OK;
     ZNN_NEED_DEVICE();
@@ -1011,8 +1093,41 @@ int znn_batch_gather(const float* images, const uint8_t* labels, const int32_t* 
                        (reinterpret_cast<uintptr_t>(x_dest) & 15) == 0;
     const int per_row = vec_ok ? input_dim / 4 : input_dim;
     const dim3 grid((unsigned)std::min(64, (per_row + kEwThreads - 1) / kEwThreads), (unsigned)batch);
-    batch_gather_kernel<<<grid, kEwThreads, 0, stream()>>>(images, labels, indices, x_dest, y_dest, input_dim, vec_ok);
+    batch_gather_kernel<<<grid, kEwThreads, 0, stream()>>>(images, labels, indices, x_dest, y_dest, input_dim, vec_ok,
+                                                           num_samples, device_status_word());
     ZNN_LAUNCH_OK("batch_gather_kernel");
+    return ZNN_OK;
+}
+
+int znn_init_he_normal(float* w, size_t n, size_t fan_in, unsigned long long seed)
+{
+    if (n == 0) return ZNN_OK;
+    ZNN_NEED_DEVICE();
+    ZNN_REQUIRE(w, "w is NULL");
+    ZNN_REQUIRE(fan_in > 0, "fan_in must be positive");
+    const float std_dev = sqrtf(2.0f / (float)fan_in);
+    fill_normal_kernel<<<ew_blocks(n), kEwThreads, 0, stream()>>>(w, n, 0.0f, std_dev, seed, 0);
+    ZNN_LAUNCH_OK("fill_normal_kernel");
+    return ZNN_OK;
+}
+
+int znn_fill_normal(float* w, size_t n, float mean, float stddev, unsigned long long seed)
+{
+    if (n == 0) return ZNN_OK;
+    ZNN_NEED_DEVICE();
+    ZNN_REQUIRE(w, "w is NULL");
+    fill_normal_kernel<<<ew_blocks(n), kEwThreads, 0, stream()>>>(w, n, mean, stddev, seed, 1);
+    ZNN_LAUNCH_OK("fill_normal_kernel");
+    return ZNN_OK;
+}
+
+int znn_fill_uniform(float* w, size_t n, float min_val, float max_val, unsigned long long seed)
+{
+    if (n == 0) return ZNN_OK;
+    ZNN_NEED_DEVICE();
+    ZNN_REQUIRE(w, "w is NULL");
+    fill_uniform_kernel<<<ew_blocks(n), kEwThreads, 0, stream()>>>(w, n, min_val, max_val - min_val, seed);
+    ZNN_LAUNCH_OK("fill_uniform_kernel");
     return ZNN_OK;
 }
 
@@ -1114,13 +1229,14 @@ static int xent_fwd(const float* logits, const T* targets, float* probs, float* 
     ZNN_REQUIRE(logits && targets && probs && loss, "NULL pointer");
     float* rowloss = (float*)workspace((size_t)M * sizeof(float));
     if (!rowloss) return fail(ZNN_ERR_NOMEM, "scratch for per-row losses");
+    int* status = device_status_word();
     const bool v4 = (N % 4 == 0) && ((((uintptr_t)logits | (uintptr_t)probs) & 15) == 0);
     if (v4 && N > 2048 && N <= 1024 * 8) {
-        if (N <= 1024 * 4) softmax_xent_fwd_reg_kernel<T, 4><<<M, 256, 0, stream()>>>(logits, targets, probs, rowloss, N);
-        else softmax_xent_fwd_reg_kernel<T, 8><<<M, 256, 0, stream()>>>(logits, targets, probs, rowloss, N);
+        if (N <= 1024 * 4) softmax_xent_fwd_reg_kernel<T, 4><<<M, 256, 0, stream()>>>(logits, targets, probs, rowloss, N, status);
+        else softmax_xent_fwd_reg_kernel<T, 8><<<M, 256, 0, stream()>>>(logits, targets, probs, rowloss, N, status);
     } else {
         const int threads = N >= 1024 ? 256 : (N >= 128 ? 128 : 32);
-        softmax_xent_fwd_kernel<T><<<M, threads, 0, stream()>>>(logits, targets, probs, rowloss, N);
+        softmax_xent_fwd_kernel<T><<<M, threads, 0, stream()>>>(logits, targets, probs, rowloss, N, status);
     }
     ZNN_LAUNCH_OK("softmax_xent_fwd_kernel");
     mean_rows_kernel<<<1, 1024, 0, stream()>>>(rowloss, loss, M);
@@ -1318,11 +1434,11 @@ int znn_layernorm_bwd(const float* X, const float* G, const float* dY, float eps
 
 int znn_embedding_fwd(const float* W, const float* ids, float* Y, size_t n, int D, int vocab)
 {
-    (void)vocab;
     if (n == 0 || D <= 0) return ZNN_OK;
     ZNN_NEED_DEVICE();
+    ZNN_REQUIRE(vocab > 0, "vocab must be positive");
     const unsigned blocks = (unsigned)(n < 65535u * 16u ? n : 65535u * 16u);
-    embedding_fwd_kernel<<<blocks, D >= 256 ? 256 : 64, 0, stream()>>>(W, ids, Y, n, D);
+    embedding_fwd_kernel<<<blocks, D >= 256 ? 256 : 64, 0, stream()>>>(W, ids, Y, n, D, vocab, device_status_word());
     ZNN_LAUNCH_OK("embedding_fwd_kernel");
     return ZNN_OK;
 }
@@ -1547,7 +1663,8 @@ extern "C" int znn_softmax_xent_fwd_static(const float* logits, const int32_t* t
     const int threads = N >= 1024 ? 256 : (N >= 128 ? 128 : 32);
     // Rows 0..M-1 of the array are overwritten before they are read, so nothing has
     // to be cleared; rows beyond M keep whatever an earlier call left there.
-    softmax_xent_fwd_kernel<int32_t><<<M, threads, 0, st>>>(logits, targets, probs, rowloss, N);
+    // no status word here (this entry point does not touch the shim's state): a label outside [0, N) makes the loss NaN
+    softmax_xent_fwd_kernel<int32_t><<<M, threads, 0, st>>>(logits, targets, probs, rowloss, N, nullptr);
     ZNN_LAUNCH_OK("softmax_xent_fwd_kernel (fixed scratch)");
     mean_rows_kernel<<<1, 1024, 0, st>>>(rowloss, loss, M);
     ZNN_LAUNCH_OK("mean_rows_kernel (fixed scratch)");

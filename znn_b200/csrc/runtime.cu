@@ -30,12 +30,23 @@ int fail(int code, const char* fmt, ...)
 
 constexpr int kMaxDev = 16;
 
+// Scratch blocks of one stream: slot 0 GEMM planes / partials / row-op partials, slot 1 conv im2col, slot 2 device
+// copies of host operands.  Work on one stream is ordered, so one set per (device, stream) can be reused call after
+// call; two host threads that launch on different streams get different sets and never share scratch.
+struct ScratchSet {
+    cudaStream_t st = nullptr;
+    bool used = false;
+    void* ws[3] = {nullptr, nullptr, nullptr};
+    size_t ws_bytes[3] = {0, 0, 0};
+};
+constexpr int kMaxScratchSets = 16;
+
 struct DeviceState {
     bool ready = false;
     cudaStream_t own_stream = nullptr;
     int* status = nullptr;  // device int
-    void* ws[3] = {nullptr, nullptr, nullptr};   // slot 0: GEMM planes / partials / row-op partials; slot 1: conv im2col; slot 2: device copies of host operands
-    size_t ws_bytes[3] = {0, 0, 0};
+    ScratchSet sets[kMaxScratchSets];
+    unsigned long long ws_generation = 0;   // bumped whenever a scratch block moves (is freed and allocated anew)
     int sms = 0;
 };
 
@@ -92,28 +103,83 @@ int sm_count()
     return s ? s->sms : 0;
 }
 
+static ScratchSet* scratch_set(DeviceState* s, cudaStream_t st)
+{
+    for (int i = 0; i < kMaxScratchSets; i++)
+        if (s->sets[i].used && s->sets[i].st == st) return &s->sets[i];
+    std::lock_guard<std::mutex> lk(g_mu);
+    for (int i = 0; i < kMaxScratchSets; i++)
+        if (s->sets[i].used && s->sets[i].st == st) return &s->sets[i];
+    for (int i = 0; i < kMaxScratchSets; i++)
+        if (!s->sets[i].used) {
+            s->sets[i].st = st;
+            s->sets[i].used = true;
+            return &s->sets[i];
+        }
+    return nullptr;
+}
+
 void* workspace_slot(int slot, size_t bytes)
 {
     DeviceState* s = cur(true);
     if (!s || slot < 0 || slot > 2) return nullptr;
-    if (bytes <= s->ws_bytes[slot]) return s->ws[slot];
+    const cudaStream_t st = stream();
+    ScratchSet* set = scratch_set(s, st);
+    if (!set) {
+        set_error("more than %d streams with their own scratch on one device", kMaxScratchSets);
+        return nullptr;
+    }
+    if (bytes <= set->ws_bytes[slot]) return set->ws[slot];
+    // Growing is refused while the stream is being captured: the synchronisation and the allocation below are not
+    // capturable, and a captured kernel must never hold a block that a later call may free.
+    cudaStreamCaptureStatus cap = cudaStreamCaptureStatusNone;
+    if (cudaStreamIsCapturing(st, &cap) == cudaSuccess && cap != cudaStreamCaptureStatusNone) {
+        set_error("scratch block would have to grow to %zu bytes during stream capture (run the step once eagerly, or "
+                  "call znn_gemm_workspace_reserve, before capturing)", bytes);
+        return nullptr;
+    }
     // Growing: everything queued so far may still read the old block.
-    cudaStreamSynchronize(stream());
-    if (s->ws[slot]) cudaFree(s->ws[slot]);
-    s->ws[slot] = nullptr;
-    s->ws_bytes[slot] = 0;
+    cudaStreamSynchronize(st);
+    if (set->ws[slot]) cudaFree(set->ws[slot]);
+    set->ws[slot] = nullptr;
+    set->ws_bytes[slot] = 0;
+    {
+        std::lock_guard<std::mutex> lk(g_mu);
+        s->ws_generation++;
+    }
     size_t want = bytes + (bytes >> 3);
-    if (cudaMalloc(&s->ws[slot], want) != cudaSuccess) {
+    if (cudaMalloc(&set->ws[slot], want) != cudaSuccess) {
         cudaGetLastError();
         want = bytes;
-        if (cudaMalloc(&s->ws[slot], want) != cudaSuccess) {
+        if (cudaMalloc(&set->ws[slot], want) != cudaSuccess) {
             cudaGetLastError();
             return nullptr;
         }
     }
-    s->ws_bytes[slot] = want;
-    return s->ws[slot];
+    set->ws_bytes[slot] = want;
+    return set->ws[slot];
 }
+
+unsigned long long workspace_generation()
+{
+    DeviceState* s = cur(true);
+    return s ? s->ws_generation : 0;
+}
+
+// Host-side fault injection for tests: the n-th kernel launch from now (of any host thread) is reported as failed.
+static long long g_fail_after = -1;
+bool inject_launch_failure()
+{
+    if (g_fail_after < 0) return false;
+    std::lock_guard<std::mutex> lk(g_mu);
+    if (g_fail_after < 0) return false;
+    if (g_fail_after-- == 0) {
+        g_fail_after = -1;
+        return true;
+    }
+    return false;
+}
+void set_fail_after(long long n) { std::lock_guard<std::mutex> lk(g_mu); g_fail_after = n; }
 
 void* workspace(size_t bytes) { return workspace_slot(0, bytes); }
 
@@ -152,6 +218,12 @@ int znn_init(int device)
                     prop.major, prop.minor);
     if (!cur(true)) return fail(ZNN_ERR_CUDA, "could not create per-device state");
     return ZNN_OK;
+}
+
+int znn_set_device(int device)
+{
+    // per-host-thread current device, as cudaSetDevice; the per-device state is created on first use
+    return znn_init(device);
 }
 
 int znn_set_stream(void* cuda_stream)
@@ -217,6 +289,13 @@ int znn_memcpy_d2h(void* dst, const void* src, size_t bytes)
     return ZNN_OK;
 }
 
+int znn_memcpy_d2h_async(void* dst, const void* src, size_t bytes)
+{
+    if (bytes == 0) return ZNN_OK;
+    ZNN_CUDA_OK(cudaMemcpyAsync(dst, src, bytes, cudaMemcpyDeviceToHost, stream()));
+    return ZNN_OK;
+}
+
 int znn_memcpy_d2d(void* dst, const void* src, size_t bytes)
 {
     if (bytes == 0) return ZNN_OK;
@@ -247,6 +326,19 @@ int znn_device_status(int* status, int clear)
     ZNN_CUDA_OK(cudaStreamSynchronize(stream()));
     ZNN_CUDA_OK(cudaMemcpy(status, w, sizeof(int), cudaMemcpyDeviceToHost));
     if (clear && *status) ZNN_CUDA_OK(cudaMemset(w, 0, sizeof(int)));
+    return ZNN_OK;
+}
+
+int znn_workspace_generation(unsigned long long* generation)
+{
+    ZNN_REQUIRE(generation, "generation is NULL");
+    *generation = workspace_generation();
+    return ZNN_OK;
+}
+
+int znn_debug_fail_after(long long n)
+{
+    set_fail_after(n);
     return ZNN_OK;
 }
 
