@@ -123,8 +123,30 @@ def cpu_step(zo, A, B, dC, Cm, dA, dB, n):
     zo.sgemm(112, 111, n, n, n, 1.0, A, n, dC, n, 1.0, dB, n)
 
 
-def cpu_measure(steps, warmup, budget_s=25.0, with_naive=True):
-    """Times the oracle's MatMul step on the host cores (bounded sample)."""
+def host_cores():
+    try:
+        return len(os.sched_getaffinity(0))
+    except AttributeError:
+        return os.cpu_count() or 1
+
+
+def set_blas_threads(info, n):
+    """The CPU arm uses every host core whatever OMP_NUM_THREADS the launcher exported (torchrun sets it to 1)."""
+    h = info.get("handle")
+    for sym in ("scipy_openblas_set_num_threads", "openblas_set_num_threads", "goto_set_num_threads"):
+        if h is not None and hasattr(h, sym):
+            getattr(h, sym)(C.c_int(n))
+            for gsym in ("scipy_openblas_get_num_threads", "openblas_get_num_threads"):
+                if hasattr(h, gsym):
+                    return int(getattr(h, gsym)())
+            return n
+    return info.get("threads") or 1
+
+
+def cpu_measure(steps, warmup, n=8192, budget_s=25.0, with_naive=True):
+    """Times the oracle's MatMul step (forward + dA + dB at size n, the GPU arm's own workload) on the host cores.
+    The sample is bounded in the number of steps, never in n: after the first step the step count is cut so that the
+    run fits budget_s."""
     import numpy as np
     from oracle import zo
     zo.build()
@@ -144,36 +166,62 @@ def cpu_measure(steps, warmup, budget_s=25.0, with_naive=True):
         out["naive_fallback_1thread_tflops"] = naive
         out["naive_sample"] = f"{m}^3 forward product, 1 thread (src/cblas.zig:37-96 restated)"
     if ptr is None:
-        out.update({"value": naive, "cores": 1, "sample": out.get("naive_sample", ""), "blas": "none found"})
+        out.update({"value": naive, "cores": 1, "sample": out.get("naive_sample", ""), "blas": "none found", "n": 768})
         return out
     zo.bind_sgemm(ptr)
-    cores = info.get("threads") or os.cpu_count()
-    # pick a size whose step fits the budget: probe at 1024
-    m = 1024
-    A, B = r.standard_normal((m, m), np.float32), r.standard_normal((m, m), np.float32)
-    Cm = np.zeros((m, m), np.float32)
-    zo.sgemm(111, 111, m, m, m, 1.0, A, m, B, m, 0.0, Cm, m)
-    t0 = time.perf_counter()
-    zo.sgemm(111, 111, m, m, m, 1.0, A, m, B, m, 0.0, Cm, m)
-    rate = 2.0 * m ** 3 / (time.perf_counter() - t0)
-    n = 8192
-    total_steps = steps + warmup
-    while n > 512 and 6.0 * n ** 3 * total_steps / rate > budget_s:
-        n //= 2
+    cores = set_blas_threads(info, host_cores())
     A, B, dC = (r.standard_normal((n, n), np.float32) for _ in range(3))
     Cm, dA, dB = (np.zeros((n, n), np.float32) for _ in range(3))
-    for _ in range(warmup):
-        cpu_step(zo, A, B, dC, Cm, dA, dB, n)
     t0 = time.perf_counter()
-    for _ in range(steps):
+    cpu_step(zo, A, B, dC, Cm, dA, dB, n)              # first step: untimed warm-up, and the measure for the cut
+    t_first = time.perf_counter() - t0
+    warm_run = 1
+    max_total = max(2, int(budget_s / max(t_first, 1e-3)))
+    while warm_run < warmup and warm_run + 1 < max_total:
+        cpu_step(zo, A, B, dC, Cm, dA, dB, n)
+        warm_run += 1
+    steps_run = max(1, min(steps, max_total - warm_run))
+    t0 = time.perf_counter()
+    for _ in range(steps_run):
         cpu_step(zo, A, B, dC, Cm, dA, dB, n)
     dt = time.perf_counter() - t0
     zo.bind_sgemm(None)
-    out.update({"value": 6.0 * n ** 3 * steps / dt / 1e12, "cores": int(cores), "ms_per_step": dt / steps * 1e3,
-                "sample": f"{steps} steps of fwd+dA+dB at n={n} (bounded sample of the n=8192 workload), "
-                          f"cblas_sgemm = {os.path.basename(info['path'])} with {cores} threads",
-                "n": n})
+    out.update({"value": 6.0 * n ** 3 * steps_run / dt / 1e12, "cores": int(cores), "ms_per_step": dt / steps_run * 1e3,
+                "sample": f"{steps_run} timed steps (of {steps} asked; {warm_run} warm-up) of fwd+dA+dB at n={n}, the GPU arm's own "
+                          f"size; cblas_sgemm = {os.path.basename(info['path'])} with {cores} threads on {host_cores()} host cores",
+                "n": n, "steps_run": steps_run, "warmup_run": warm_run})
     return out
+
+
+def gpt_cpu_measure(V, T, D, H, B, n_layer_full):
+    """One training step of the GPT configuration on the CPU oracle (literal reference op sequence, cblas_sgemm bound to
+    the host OpenBLAS with all cores, everything else the restated scalar loops on one thread).  Bounded sample: ONE
+    layer at full width, context and vocabulary; the full model's time is that of the sample scaled by the flop ratio."""
+    import numpy as np
+    from oracle import models, zo
+    ptr, info = zo.find_host_cblas()
+    if ptr is None:
+        return {"kind": "port", "unavailable": "no host CBLAS found for the oracle"}
+    zo.bind_sgemm(ptr)
+    cores = set_blas_threads(info, host_cores())
+    cfg = {"vocab_size": V, "block_size": T, "n_embd": D, "n_head": H, "n_layer": 1}
+    P0 = models.init_params("gpt", cfg, seed=1, scheme="n002")
+    r = np.random.default_rng(2)
+    x = r.integers(0, V, (B, T)).astype(np.float32)
+    t = r.integers(0, V, B * T).astype(np.int32)
+    tr = models.OracleTrainer("gpt", P0, cfg, lr=0.01, momentum=0.9)
+    t0 = time.perf_counter()
+    tr.step(x, t)
+    dt = time.perf_counter() - t0
+    zo.bind_sgemm(None)
+    layer = 3 * 2.0 * B * T * (4 * D * D + 8 * D * D + 2 * T * D)     # projections, FFN, attention (full square)
+    head = 3 * 2.0 * B * T * D * V
+    ratio = (n_layer_full * layer + head) / (layer + head)
+    return {"kind": "port", "unit": "tokens/s", "cores": int(cores), "value": B * T / (dt * ratio),
+            "sample_tokens_per_s": B * T / dt, "sample_s": dt,
+            "sample": f"one training step of a 1-layer model at full width (d_model {D}, context {T}, vocab {V}, batch {B}); "
+                      f"value = the sample's rate divided by the flop ratio {ratio:.2f} of the {n_layer_full}-layer model; "
+                      f"sgemm = OpenBLAS with {cores} threads, other ops scalar on one thread"}
 
 
 def run_reference(args):
@@ -182,13 +230,15 @@ def run_reference(args):
         return 0
     steps, warmup = max(1, args.steps), max(0, args.warmup)
     t_wall = time.perf_counter()
-    res = cpu_measure(steps, warmup, budget_s=60.0, with_naive=True)
+    res = cpu_measure(steps, warmup, n=args.n, budget_s=150.0, with_naive=True)
     line = {
         "impl": "reference", "metric": METRIC, "value": res["value"], "unit": UNIT, "n_gpus": args.gpus,
-        "steps": steps, "warmup": warmup, "ms_per_step": res.get("ms_per_step"), "higher_is_better": True,
+        "steps": res.get("steps_run", steps), "warmup": res.get("warmup_run", warmup), "steps_asked": steps,
+        "ms_per_step": res.get("ms_per_step"), "higher_is_better": True,
         "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-        "config": {"workload": f"matmul_sweep_square_{args.n}_fwd_dA_dB", "sample_n": res.get("n"),
-                   "note": "CPU path of the reference restated in C (oracle), cblas_sgemm bound to host OpenBLAS"},
+        "config": {"workload": f"matmul_sweep_square_{args.n}_fwd_dA_dB", "M": res.get("n"), "N": res.get("n"), "K": res.get("n"),
+                   "note": "CPU path of the reference restated in C (oracle port; the reference is Zig and cannot be built "
+                           "here), cblas_sgemm bound to the host OpenBLAS with every host core"},
         "cpu_baseline": {k: res[k] for k in res if k in ("value", "unit", "cores", "kind", "sample",
                                                          "naive_fallback_1thread_tflops", "naive_sample")},
         "e2e": {"value": res["value"], "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
@@ -367,17 +417,22 @@ def run_gpu(args):
         tf32_live = 2.0 * n ** 3 / (best * 1e-3) / 1e12
         torch.backends.cuda.matmul.allow_tf32 = False
 
-    gpt = None
+    gpt = sweep = configs = None
     if args.workload == "all":
         gpt = gpt_part(args, L, torch, dist, stream, world, rank, local)
+        if world == 1:
+            # the other shapes and configurations of the workload definition, compact, in the same record
+            peaks_now, _ = read_peaks()
+            sweep = sweep_compact(sweep_part(args, L, torch, stream), peaks_now)
+            configs = configs_compact(configs_part(args, L, torch, stream), peaks_now)
 
     if rank == 0:
         peaks, peaks_kind = read_peaks()
         # 3xTF32 ceiling: the TF32 dense rate is half the bf16 rate on this part, and each algorithmic flop costs
-        # three tensor-core passes.  The kernel is timed inside a long back-to-back loop under the power cap, so
-        # the denominator is the SUSTAINED measured bf16 rate; the fraction of the burst rate is given beside it.
-        peak = peaks["bf16_tflops_sustained"] / 2.0 / 3.0
-        peak_burst = peaks["bf16_tflops"] / 2.0 / 3.0
+        # three tensor-core passes.  The timed region lasts a fraction of a second, so the denominator is the BURST
+        # measured bf16 rate; the fraction of the sustained (seconds-long, power-capped) rate is given beside it.
+        peak = peaks["bf16_tflops"] / 2.0 / 3.0
+        peak_sustained = peaks["bf16_tflops_sustained"] / 2.0 / 3.0
         achieved = (kfl.value / (kms.value * 1e-3) / 1e12) if kms.value > 0 else None
         line = {
             "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": steps, "warmup": warmup,
@@ -388,15 +443,17 @@ def run_gpu(args):
                        "parallelism": "replicas only" if world > 1 else "single GPU"},
             "roofline": {"bound": "tensor", "achieved": achieved, "peak": peak, "unit": UNIT,
                          "frac": (achieved / peak) if achieved else None,
-                         # bytes per launch from the ncu capture of this workload (profiles/gemm3x_direct_kernel_n8192_dram_traffic.md)
                          "traffic": 2.714e9 if (n == 8192 and last_path == 4) else None,
+                         "traffic_source": "DRAM bytes per launch from a one-pass ncu capture of this workload (committed "
+                                           "summary); not measured in this run",
                          "algorithmic_bytes_per_launch": (3 + 4 + 4) * nbytes / 3.0,
                          "kernel": ("gemm3x_direct_kernel<256,*,*> (operands read in place)" if last_path == 4
                                     else "gemm3x_tf32_kernel<256,2> (pre-split operand planes)"),
                          "launches": kl.value,
                          "avg_launch_ms": (kms.value / kl.value) if kl.value else None,
-                         "peak_source": f"{peaks_kind}: bf16 sustained {peaks['bf16_tflops_sustained']} TF/s / 2 (tf32) / 3 (passes)",
-                         "peak_burst": peak_burst, "frac_of_burst_peak": (achieved / peak_burst) if achieved else None,
+                         "peak_source": f"{peaks_kind}: bf16 burst {peaks['bf16_tflops']} TF/s / 2 (tf32) / 3 (passes)",
+                         "peak_sustained": peak_sustained,
+                         "frac_of_sustained_peak": (achieved / peak_sustained) if achieved else None,
                          "cublas_tf32_live_tflops": tf32_live,
                          "frac_of_live_cublas_tf32_third": (achieved / (tf32_live / 3.0)) if (achieved and tf32_live) else None},
             "e2e": {"value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": 3 * nbytes, "d2h_bytes_per_step": 3 * nbytes,
@@ -405,12 +462,60 @@ def run_gpu(args):
         }
         if gpt is not None:
             line["gpt"] = gpt
+        if sweep is not None:
+            line["sweep"] = sweep
+        if configs is not None:
+            line["configs"] = configs
         if not args.no_cpu_baseline and world == 1:
-            line["cpu_baseline"] = {k: v for k, v in cpu_measure(2, 1, budget_s=20.0).items() if k != "n"}
+            line["cpu_baseline"] = {k: v for k, v in cpu_measure(3, 1, n=n, budget_s=20.0).items()
+                                    if k not in ("n", "steps_run", "warmup_run")}
+            if gpt is not None:
+                gpt["cpu_baseline"] = gpt_cpu_measure(8192, 1024, 768, 12, 8, 6)
         print(json.dumps(line), flush=True)
     if world > 1:
         dist.destroy_process_group()
     return 0
+
+
+def sweep_compact(rows, peaks):
+    """One entry per sweep shape: microseconds and TFLOP/s of the three products, and the fraction of the bound that
+    applies: the 3xTF32 tensor ceiling (burst) for the square shapes, the HBM time of the operands for the skinny ones."""
+    ceiling = peaks["bf16_tflops"] / 2.0 / 3.0
+    out = {}
+    for row in rows:
+        M, N, K = row["M"], row["N"], row["K"]
+        hbm_us = row["operand_MB"] * 1e6 / (peaks["hbm_gbs"] * 1e9) * 1e6
+        skinny = min(M, N) <= 64
+        e = {}
+        for k in ("fwd_NN", "dA_NT", "dB_TN"):
+            e[k] = {"us": round(row[k]["us"], 1), "tflops": round(row[k]["tflops"], 1),
+                    "frac": round((hbm_us / row[k]["us"]) if skinny else (row[k]["tflops"] / ceiling), 3)}
+        e["bound"] = ("hbm: operand bytes / measured copy bandwidth" if skinny else
+                      ("tensor (3xTF32 burst ceiling); launch-bound below 1024^3" if max(M, N, K) < 1024 else "tensor (3xTF32 burst ceiling)"))
+        e["l2_resident"] = row["l2_resident"]
+        out[f"{M}x{N}x{K}"] = e
+    return out
+
+
+def configs_compact(cfgs, peaks):
+    ceiling = peaks["bf16_tflops"] / 2.0 / 3.0
+    out = {}
+    for k, v in cfgs.items():
+        if "us_per_step" in v:
+            out[k] = {"us_per_step": round(v["us_per_step"], 1), "cuda_graph_us_per_step": round(v["cuda_graph_us_per_step"], 1),
+                      "e2e_us_per_step": round(v["e2e_us_per_step"], 1), "bound": v.get("bound", "launch-bound")}
+            if "tflops" in v:
+                out[k]["tflops"] = round(v["tflops"], 2)
+        elif "ms_fwd_bwd" in v:
+            out[k] = {"ms_fwd_bwd": round(v["ms_fwd_bwd"], 3), "tflops": round(v["tflops"], 1),
+                      "frac": round(v["tflops"] / ceiling, 3), "bound": "tensor (3xTF32 burst ceiling)",
+                      "ms_fwd_bwd_incl_host_copies": round(v["ms_fwd_bwd_incl_host_copies"], 2)}
+        elif "tokens_per_s" in v:
+            out[k] = {kk: v[kk] for kk in v if kk != "note"}
+            out[k]["bound"] = "launch-bound (about 200 launches per position, batch 64)"
+        else:
+            out[k] = {kk: (round(vv, 1) if isinstance(vv, float) else vv) for kk, vv in v.items() if kk != "note"}
+    return out
 
 
 def gpt_part(args, L, torch, dist, stream, world, rank, local):
@@ -480,7 +585,7 @@ def gpt_part(args, L, torch, dist, stream, world, rank, local):
     # end to end: token ids and targets from host memory every step, loss read back every step
     loss = m.train_step(ids, tgt, seq=T)
     barrier()
-    e2e_steps = min(steps, 5)
+    e2e_steps = steps            # the same count as the device-resident figure: both see the same clock behaviour
     e0.record(stream)
     for _ in range(e2e_steps):
         loss = m.train_step(ids, tgt, seq=T)
@@ -512,10 +617,79 @@ def gpt_part(args, L, torch, dist, stream, world, rank, local):
                              "share_of_step": (kms.value / ms) if ms > 0 else None},
         "model_flops_per_token": 349e6,
     }
+    if world > 1:
+        out["dp_parity"] = dp_parity_check(L, torch, dist, m, world, rank)
     m.close()
     if world > 1:
         L.call("znn_dp_finalize")
+        out["dp_parity"].update(dp_small_model_check(L, torch, dist, world, rank, phase="single", carry=out["dp_parity"]))
     return out
+
+
+def dp_parity_check(L, torch, dist, m, world, rank):
+    """Self-check of the data-parallel run, printed with the numbers: (1) after the timed steps every rank must hold
+    bit-identical parameters (same initial replica, same summed gradients, same update): a checksum of the parameter
+    slab is min- and max-reduced over the ranks; (2) a small GPT trained for a few steps with the batch sharded over
+    the ranks must follow the loss of the same model trained on the whole batch by one GPU (second half of the check
+    runs after the communicator is gone: dp_small_model_check(phase='single'))."""
+    import numpy as np
+    P = m.get_params()
+    h = 0
+    for name in sorted(P):
+        a = np.ascontiguousarray(P[name]).view(np.uint32).astype(np.uint64)
+        h = (h * 1000003 + int(a.sum() % (1 << 61)) + int((a[::7] * np.uint64(2654435761)).sum() % (1 << 61))) % (1 << 61)
+    t = torch.tensor([float(h % (1 << 52))], device="cuda", dtype=torch.float64)
+    lo, hi = t.clone(), t.clone()
+    dist.all_reduce(lo, op=dist.ReduceOp.MIN)
+    dist.all_reduce(hi, op=dist.ReduceOp.MAX)
+    res = {"replicas_bit_identical": bool(lo.item() == hi.item()), "param_checksum": int(lo.item())}
+    if not res["replicas_bit_identical"]:
+        raise SystemExit("data-parallel parity check failed: the ranks' parameter replicas differ after the timed steps")
+    res.update(dp_small_model_check(L, torch, dist, world, rank, phase="dp"))
+    return res
+
+
+def dp_small_model_check(L, torch, dist, world, rank, phase, carry=None):
+    import numpy as np
+    from znn_b200.models import Model
+    V, T, D, H, NL, Bper, steps = 96, 128, 128, 2, 2, 2, 5
+    dims = (V, T, D, H, NL)
+    r = np.random.default_rng(7)                         # the same on every rank
+    Bg = Bper * world
+    ids = r.integers(0, V, (steps, Bg, T)).astype(np.float32)
+    tgt = r.integers(0, V, (steps, Bg, T)).astype(np.int32)
+    m = Model("gpt", dims, arena_bytes=1 << 30)
+    P = {}
+    for name, shape, _, fan_in in m.params:
+        P[name] = (r.standard_normal(shape, np.float32) * np.float32(0.05)) if fan_in else (
+            np.ones(shape, np.float32) if "ln_" in name else np.zeros(shape, np.float32))
+    m.set_params(P)
+    m.set_option("lr", 0.05)
+    m.set_option("momentum", 0.9)
+    if phase == "dp":
+        losses = []
+        for s in range(steps):
+            sl = slice(rank * Bper, (rank + 1) * Bper)
+            local = m.train_step(ids[s, sl], tgt[s, sl], seq=T)
+            t = torch.tensor([local], device="cuda", dtype=torch.float64)
+            dist.all_reduce(t)                           # mean of equal shards' mean losses = the global mean loss
+            losses.append(float(t.item()) / world)
+        Pf = m.get_params()
+        m.close()
+        return {"small_gpt_dp_losses": losses, "_small_params": Pf}
+    losses = [m.train_step(ids[s], tgt[s], seq=T) for s in range(steps)]
+    Pf = m.get_params()
+    m.close()
+    dp_losses, dp_params = carry["small_gpt_dp_losses"], carry.pop("_small_params")
+    worst = max(abs(a - b) / abs(b) for a, b in zip(dp_losses, losses))
+    scale = max(float(np.abs(v).max()) for v in Pf.values())
+    perr = max(float(np.abs(Pf[k] - dp_params[k]).max()) for k in Pf) / scale
+    ok = worst <= 1e-4 and perr <= 1e-4
+    if not ok:
+        raise SystemExit(f"data-parallel parity check failed: loss rel {worst:.3e}, params {perr:.3e} of scale")
+    return {"small_gpt_single_gpu_losses": losses, "small_gpt_loss_max_rel_diff": worst,
+            "small_gpt_param_max_diff_of_scale": perr, "small_gpt_config": {"vocab": V, "context": T, "d_model": D, "heads": H,
+            "layers": NL, "global_batch": Bg, "steps": steps}, "bar": 1e-4, "passed": True}
 
 
 def configs_part(args, L, torch, stream):
@@ -566,7 +740,13 @@ def configs_part(args, L, torch, stream):
         ms_graph = time_steps(lambda: m.train_step_device(dx.data_ptr(), dt.data_ptr(), batch), 200)
         out[key] = {"us_per_step": ms * 1e3, "steps_per_s": 1e3 / ms, "images_per_s": batch * 1e3 / ms,
                     "cuda_graph_us_per_step": ms_graph * 1e3, "cuda_graph_images_per_s": batch * 1e3 / ms_graph,
-                    "e2e_us_per_step": ms_e2e * 1e3, "tape_ops": m.last_step_ops(), "bound": "launch latency"}
+                    "e2e_us_per_step": ms_e2e * 1e3, "tape_ops": m.last_step_ops(), "bound": "launch-bound"}
+        if kind == "cnn_padded":
+            # conv1 115.6 + conv2 1849.7 + fc1 205.5 + fc2 0.7 MFLOP forward; backward twice that less conv1's input gradient
+            flops = 2.0 * 256 * (28 * 28 * 32 * 9 + 14 * 14 * 64 * 288 + 3136 * 128 + 128 * 10)
+            flops = 3.0 * flops - 2.0 * 256 * 28 * 28 * 32 * 9
+            out[key]["tflops"] = flops / (ms_graph * 1e-3) / 1e12
+            out[key]["bound"] = "tensor for conv2 (M = 50176, N = 64, K = 288) and fc1; the rest launch-bound"
         m.close()
 
     # C1 fed by the device-resident loader: synthetic pixel bytes of the dataset's shape, converted on the device,

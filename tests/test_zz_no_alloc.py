@@ -1,7 +1,7 @@
 """znn_softmax_xent_fwd_static: the SoftmaxCrossEntropy forward for callers that must not
 allocate (fixed memory budgets, threads that cannot block in cudaMalloc).  It keeps its
 per-row losses in a fixed device array inside the library, so its output must equal the
-regular entry point's -- on a first call and again on a second call that reuses the array
+regular entry point's and the CPU oracle's -- on a first call and again on a second call that reuses the array
 with different, smaller inputs.  This file sorts last so that it runs after every other test."""
 import ctypes as C
 
@@ -39,6 +39,11 @@ def test_static_scratch_matches_regular_entry_point_twice():
         assert np.isfinite(l_new).all() and float(l_new[0]) > 0.0
         np.testing.assert_allclose(p_new, p_ref, rtol=RTOL, atol=1e-12)
         np.testing.assert_allclose(l_new, l_ref, rtol=RTOL)
+        # and against the CPU oracle's restatement of the reference loop (src/autodiff.zig:196-238)
+        from oracle import zo
+        l_cpu, p_cpu = zo.softmax_xent_fwd(X, t)
+        np.testing.assert_allclose(p_new, p_cpu, rtol=RTOL, atol=1e-12)
+        np.testing.assert_allclose(l_new, np.asarray(l_cpu).reshape(-1), rtol=RTOL)
     # beyond the fixed array: refused on the host, nothing is launched
     big = 65537
     with pytest.raises(ZnnError) as ei:

@@ -170,6 +170,19 @@ def matmul_fwd(A, B):
     return sgemm(NO_TRANS, NO_TRANS, M, N, K, 1.0, A, K, B, N, 0.0, out, N)
 
 
+def linear_fwd(X, W, bias):
+    """Linear.forward as one fused call: Y = X.W + bias (the bias is added in the GEMM epilogue)."""
+    _ensure()
+    X, W, bias = _f(X), _f(W), _f(bias).reshape(-1)
+    M, K = X.shape
+    N = W.shape[1]
+    dX, dW, db = _up(X), _up(W), _up(bias)
+    out = DevBuf(M * N * 4)
+    lib().call("znn_linear_fwd", dX.ptr, dW.ptr, db.ptr, out.ptr, M, K, N)
+    check_device_status()
+    return out.to_host((M, N))
+
+
 def matmul_bwd(A, B, dC, dA=None, dB=None):
     M, K = A.shape
     N = B.shape[1]
