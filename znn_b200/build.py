@@ -23,6 +23,7 @@ SOURCES = [
     ("runtime.cu", []),
     ("gemm_tc.cu", []),
     ("gemm_api.cu", []),
+    ("attn_tc.cu", []),
     ("hostop.cu", []),
     ("rowops.cu", ["-fmad=false"]),
     ("conv.cu", ["-fmad=false"]),

@@ -1,0 +1,795 @@
+// Fused causal self-attention on the 5th-generation tensor cores (sm_100a), forward and backward, at fp32 accuracy.
+//
+// Replaces the reference's chain transposeND x4 -> batchMatMul -> mulScalar -> mask -> add -> softmax -> batchMatMul ->
+// transposeND (src/nn.zig:796-906; the operator arms are src/autodiff.zig:485-531, :1054-1076, :1117-1182): the score
+// and probability matrices (B*nh*T*T floats each) never reach memory.  Q, K, V, O and their gradients are read and
+// written where the projections leave them ([B, T, nh, hs] or [B, nh, T, hs]: row pitch and head / batch strides are
+// arguments), so no head split or merge copy is needed either.
+//
+// One kernel template, four instantiations.  A work unit is 256 "rows" of one (batch, head) slice, held by a CTA pair
+// (cta_group::2, 128 rows per CTA), against a stream of 64-wide "column" blocks:
+//
+//   forward   rows = queries, columns = keys     S = Q.K^T         P = softmax (online)        O   += P.V
+//   dQ        rows = queries, columns = keys     S = Q.K^T, dP = dO.V^T   dS = P o (dP - D)    dQ  += dS.K
+//   dK        rows = keys,    columns = queries  S^T = K.Q^T, dP^T = V.dO^T  dS^T               dK  += dS^T.Q
+//   dV        rows = keys,    columns = queries  S^T = K.Q^T        P^T                         dV  += P^T.dO
+//
+// Every product is 3xTF32 (lo*hi + hi*lo + hi*hi of a hi/lo split, as in the GEMM kernels).  The first products of a
+// block take both operands from shared memory (the resident row operands X, and the block's column operands Y brought
+// by TMA, hi = the raw tile, lo written next to it by converter warps); their result lands in tensor memory, where
+// four "transform" warps (one thread per row) turn it into the left operand W of the second product -- hi in place
+// over S, lo beside it -- which the tensor core reads straight from tensor memory (A operand in tensor memory), with
+// the block's Z operand (MN-major, from TMA) in shared memory.  Each block's second product starts a fresh
+// accumulator that the transform warps add into fp32 registers (round to nearest; the tensor core's own accumulation
+// truncates), rescaled in the forward when the running row maximum moves.  Two S / W / accumulator buffers let block
+// c+1's first products run while block c is being transformed.
+//
+// Causal structure: forward and dQ walk the key blocks 0 .. diagonal; dK and dV walk the query blocks diagonal .. end;
+// elements above the diagonal are masked by index (the reference adds -1e9, which makes exp exactly 0).
+// No TMA multicast.  Every mbarrier wait is bounded (status word + early exit, as in the GEMM kernels).
+#include "tc_ptx.cuh"
+
+#include <math.h>
+
+namespace znn {
+
+enum { ATT_FWD = 0, ATT_BWD_Q = 1, ATT_BWD_K = 2, ATT_BWD_V = 3 };
+
+struct AttnParams {
+    int T, hs, nslices, nh;
+    int nrb, ncb;                 // 256-row blocks and 64-column blocks per slice
+    int t_first;                  // 1: tensor-map coordinates are (d, t, h, b); 0: (d, h, t, b) (the smaller stride first)
+    float scale, c2;              // c2 = scale * log2(e): the softmax runs in base 2
+    long long ld, stride_h, stride_b;   // row pitch, head stride, batch stride of Q / K / V / O and gradients, in floats
+    float* out;                   // O, dQ, dK or dV
+    float* lse;                   // [nslices, T] base-2 log-sum-exp of the scaled scores: written by the forward, read by the others
+    const float* dvec;            // [nslices, T] D = rowsum(dO o O) (dQ and dK)
+    int accumulate;               // backward: 1 = add into out (the reference's +=), 0 = store
+    int* status;
+    unsigned long long wait_limit;
+};
+
+constexpr int kAttThreads = 384;   // warp 0 TMA, warp 1 MMA + TMEM, warps 2-7 converters, warps 8-11 transform
+constexpr int kAttConvWarps = 6, kAttConvWarp0 = 2, kAttXfWarp0 = 8, kAttXfWarps = 4;
+constexpr int kRowsPerCta = 128, kColBlock = 64;
+
+template <int MODE>
+struct AttnCfg {
+    static constexpr int NX = (MODE == ATT_BWD_Q || MODE == ATT_BWD_K) ? 2 : 1;   // resident row operands (and first products)
+    static constexpr int kXTile = kRowsPerCta * 64 * 4;        // one plane (hi or lo) of a row operand: 128 x 64 floats
+    static constexpr int kXBytes = NX * 2 * kXTile;
+    static constexpr int kYTile = 32 * 64 * 4;                 // this CTA's 32 of the block's 64 columns x 64 floats
+    static constexpr int kYStage = NX * 2 * kYTile;
+    static constexpr int kZTile = 64 * 32 * 4;                 // 64 contraction rows x this CTA's 32 output columns
+    static constexpr int kZStage = 2 * kZTile;
+    static constexpr int NYS = NX == 2 ? 2 : 4;
+    static constexpr int NZS = NX == 2 ? 2 : 4;
+    static constexpr int kBarOff = kXBytes + NYS * kYStage + NZS * kZStage;
+    static constexpr int kSmemBytes = kBarOff + 1024 /*alignment*/ + 512 /*barriers*/;
+    static_assert(kSmemBytes <= 232448, "shared memory budget");
+};
+
+// tensor-memory columns (512 allocated): S / W_hi [2], W_lo [2], accumulator [2], dP [2]
+constexpr uint32_t kColS = 0, kColWlo = 128, kColAcc = 256, kColDp = 384;
+
+struct AttnUnit {
+    int slice, b, h, row0, cb0, nb;   // row0: first row of the pair's 256-row block; column blocks cb0 .. cb0 + nb - 1
+};
+
+template <int MODE>
+__device__ __forceinline__ AttnUnit attn_unit(const AttnParams& p, int u)
+{
+    AttnUnit d;
+    const int rbi = u / p.nslices;            // dearest row blocks first
+    d.slice = u - rbi * p.nslices;
+    d.b = d.slice / p.nh;
+    d.h = d.slice - d.b * p.nh;
+    if (MODE == ATT_FWD || MODE == ATT_BWD_Q) {
+        const int rb = p.nrb - 1 - rbi;
+        d.row0 = rb * 256;
+        d.cb0 = 0;
+        const int last = min(p.T, d.row0 + 256);   // columns 0 .. last - 1 can be visible to these rows
+        d.nb = (last + kColBlock - 1) / kColBlock;
+    } else {
+        d.row0 = rbi * 256;
+        d.cb0 = d.row0 / kColBlock;
+        d.nb = p.ncb - d.cb0;
+    }
+    return d;
+}
+
+__device__ __forceinline__ float fast_exp2(float x)
+{
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+}
+
+template <int MODE>
+__global__ void __launch_bounds__(kAttThreads, 1)
+attn_kernel(const __grid_constant__ CUtensorMap mx1, const __grid_constant__ CUtensorMap mx2,
+            const __grid_constant__ CUtensorMap my1, const __grid_constant__ CUtensorMap my2,
+            const __grid_constant__ CUtensorMap mz, const AttnParams p)
+{
+    using Cfg = AttnCfg<MODE>;
+    constexpr int NX = Cfg::NX, NYS = Cfg::NYS, NZS = Cfg::NZS;
+    extern __shared__ uint8_t smem_raw[];
+    const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+    uint8_t* smem_gen = smem_raw + (smem_base - smem_u32(smem_raw));
+    const uint32_t x_base = smem_base, y_base = x_base + Cfg::kXBytes, z_base = y_base + NYS * Cfg::kYStage;
+    const uint32_t bar_base = smem_base + Cfg::kBarOff;
+    // barriers.  "full": TMA -> converters (own CTA); "conv": converters of both CTAs -> MMA issuer (leader CTA);
+    // "empty": MMA commit -> TMA producers (both CTAs); s_full / acc_full: MMA commit -> transform warps (both CTAs);
+    // w_ready / acc_empty: transform warps of both CTAs -> MMA issuer.
+    int bi = 0;
+    const uint32_t x_full = bar_base + 8u * bi++, x_conv = bar_base + 8u * bi++, x_empty = bar_base + 8u * bi++;
+    const uint32_t y_full0 = bar_base + 8u * bi; bi += NYS;
+    const uint32_t y_conv0 = bar_base + 8u * bi; bi += NYS;
+    const uint32_t y_empty0 = bar_base + 8u * bi; bi += NYS;
+    const uint32_t z_full0 = bar_base + 8u * bi; bi += NZS;
+    const uint32_t z_conv0 = bar_base + 8u * bi; bi += NZS;
+    const uint32_t z_empty0 = bar_base + 8u * bi; bi += NZS;
+    const uint32_t s_full0 = bar_base + 8u * bi; bi += 2;
+    const uint32_t w_ready0 = bar_base + 8u * bi; bi += 2;
+    const uint32_t acc_full0 = bar_base + 8u * bi; bi += 2;
+    const uint32_t acc_empty0 = bar_base + 8u * bi; bi += 2;
+    const int kWordOff = 8 * bi;
+    volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(smem_gen + Cfg::kBarOff + kWordOff);
+    const uint32_t tmem_slot_addr = bar_base + kWordOff;
+    volatile uint32_t* abort_slot = tmem_slot + 1;
+    const uint32_t abort_slot_addr = tmem_slot_addr + 4;
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int cta_rank = (int)cluster_ctarank();
+    const bool leader = (cta_rank == 0);
+    const int pair = blockIdx.x >> 1, npairs = gridDim.x >> 1;
+    const int total_units = p.nslices * p.nrb;
+    const int kbh = p.hs >> 5;                    // 32-float k-blocks across the head dimension (1 or 2)
+
+    if (threadIdx.x == 0) {
+        mbar_init(x_full, 1);
+        mbar_init(x_conv, kAttConvWarps * 2);
+        mbar_init(x_empty, 1);
+        for (int s = 0; s < NYS; s++) {
+            mbar_init(y_full0 + 8u * s, 1);
+            mbar_init(y_conv0 + 8u * s, kAttConvWarps * 2);
+            mbar_init(y_empty0 + 8u * s, 1);
+        }
+        for (int s = 0; s < NZS; s++) {
+            mbar_init(z_full0 + 8u * s, 1);
+            mbar_init(z_conv0 + 8u * s, kAttConvWarps * 2);
+            mbar_init(z_empty0 + 8u * s, 1);
+        }
+        for (int b = 0; b < 2; b++) {
+            mbar_init(s_full0 + 8u * b, 1);
+            mbar_init(w_ready0 + 8u * b, kAttXfWarps * 2);
+            mbar_init(acc_full0 + 8u * b, 1);
+            mbar_init(acc_empty0 + 8u * b, kAttXfWarps * 2);
+        }
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        if (leader) {
+            const uint32_t prior = (uint32_t)(*reinterpret_cast<volatile int*>(p.status));
+            *abort_slot = prior;
+            asm volatile("st.shared::cluster.u32 [%0], %1;" ::"r"(mapa_shared(abort_slot_addr, 1)), "r"(prior) : "memory");
+        }
+    }
+    if (warp == 1) {
+        tmem_alloc<2>(tmem_slot_addr, 512);
+        tmem_relinquish<2>();
+    }
+    tc_fence_before();
+    __syncthreads();
+    cluster_sync_all();
+    tc_fence_after();
+    const uint32_t tmem_base = *tmem_slot;
+    const bool aborted = (*abort_slot != 0);
+
+    if (warp < kAttXfWarp0) {
+        asm volatile("setmaxnreg.dec.sync.aligned.u32 64;");
+        if (aborted) {
+        } else if (warp == 0) {
+            // ---------------- TMA producer ----------------
+            if (lane == 0) {
+                bool ok = true;
+                uint32_t ity = 0, itz = 0, ul = 0;
+                for (int u = pair; u < total_units && ok; u += npairs, ul++) {
+                    const AttnUnit d = attn_unit<MODE>(p, u);
+                    // the row operands of this unit, once the previous unit's first products no longer read them
+                    if (!mbar_wait_bounded(x_empty, (ul & 1) ^ 1, p.wait_limit)) { ok = false; break; }
+                    mbar_arrive_expect_tx(x_full, (uint32_t)(NX * kbh * 16384));
+                    const int xrow = d.row0 + cta_rank * kRowsPerCta;
+                    for (int kb = 0; kb < kbh; kb++) {
+                        if (p.t_first) tma_load_4d(x_base + kb * 16384, &mx1, x_full, 32 * kb, xrow, d.h, d.b);
+                        else tma_load_4d(x_base + kb * 16384, &mx1, x_full, 32 * kb, d.h, xrow, d.b);
+                        if (NX == 2) {
+                            if (p.t_first) tma_load_4d(x_base + 2 * Cfg::kXTile + kb * 16384, &mx2, x_full, 32 * kb, xrow, d.h, d.b);
+                            else tma_load_4d(x_base + 2 * Cfg::kXTile + kb * 16384, &mx2, x_full, 32 * kb, d.h, xrow, d.b);
+                        }
+                    }
+                    for (int c = 0; c < d.nb && ok; c++) {
+                        const int col0 = (d.cb0 + c) * kColBlock;
+                        {   // Y: this CTA's 32 of the block's 64 columns, K-major
+                            const int s = ity % NYS;
+                            if (!mbar_wait_bounded(y_empty0 + 8u * s, ((ity / NYS) & 1) ^ 1, p.wait_limit)) { ok = false; break; }
+                            const uint32_t fb = y_full0 + 8u * s, st = y_base + s * Cfg::kYStage;
+                            mbar_arrive_expect_tx(fb, (uint32_t)(NX * kbh * 4096));
+                            const int yrow = col0 + cta_rank * 32;
+                            for (int kb = 0; kb < kbh; kb++) {
+                                if (p.t_first) tma_load_4d(st + kb * 4096, &my1, fb, 32 * kb, yrow, d.h, d.b);
+                                else tma_load_4d(st + kb * 4096, &my1, fb, 32 * kb, d.h, yrow, d.b);
+                                if (NX == 2) {
+                                    if (p.t_first) tma_load_4d(st + 2 * Cfg::kYTile + kb * 4096, &my2, fb, 32 * kb, yrow, d.h, d.b);
+                                    else tma_load_4d(st + 2 * Cfg::kYTile + kb * 4096, &my2, fb, 32 * kb, d.h, yrow, d.b);
+                                }
+                            }
+                            ity++;
+                        }
+                        {   // Z: the block's 64 contraction rows x this CTA's 32 output columns, MN-major
+                            const int s = itz % NZS;
+                            if (!mbar_wait_bounded(z_empty0 + 8u * s, ((itz / NZS) & 1) ^ 1, p.wait_limit)) { ok = false; break; }
+                            const uint32_t fb = z_full0 + 8u * s, st = z_base + s * Cfg::kZStage;
+                            mbar_arrive_expect_tx(fb, 8192u);
+                            const int d0 = cta_rank * 32;     // beyond hs (hs = 32, second CTA): the box is zero-filled
+                            for (int kk = 0; kk < 2; kk++) {
+                                if (p.t_first) tma_load_4d(st + kk * 4096, &mz, fb, d0, col0 + 32 * kk, d.h, d.b);
+                                else tma_load_4d(st + kk * 4096, &mz, fb, d0, d.h, col0 + 32 * kk, d.b);
+                            }
+                            itz++;
+                        }
+                    }
+                }
+                if (!ok) atomicOr(p.status, ZNN_DEV_TMA_WAIT_EXPIRED);
+            }
+        } else if (warp == 1) {
+            // ---------------- MMA issuer (leader CTA only) ----------------
+            if (lane == 0 && leader) {
+                constexpr uint32_t idesc1 = make_tf32_idesc_major(256, 64, false, false);
+                constexpr uint32_t idesc2 = make_tf32_idesc_major(256, 64, false, true);
+                bool ok = true;
+                uint32_t ity = 0, itz = 0, ul = 0, g = 0;     // g: blocks issued so far (buffer = g & 1)
+                const int ksteps1 = p.hs >> 3;                // K = 8 per instruction
+                for (int u = pair; u < total_units && ok; u += npairs, ul++) {
+                    const AttnUnit d = attn_unit<MODE>(p, u);
+                    if (!mbar_wait_bounded_cluster(x_conv, ul & 1, p.wait_limit)) { ok = false; break; }
+                    tc_fence_after();
+                    // second product of the block issued `gp` blocks ago (program order: P1(c), P2(c-1), P1(c+1), ...)
+                    auto second = [&](uint32_t gb) -> bool {
+                        const uint32_t buf = gb & 1, ph = (gb >> 1) & 1;
+                        if (!mbar_wait_bounded_cluster(w_ready0 + 8u * buf, ph, p.wait_limit)) return false;
+                        const int s = itz % NZS;
+                        if (!mbar_wait_bounded_cluster(z_conv0 + 8u * s, (itz / NZS) & 1, p.wait_limit)) return false;
+                        if (!mbar_wait_bounded_cluster(acc_empty0 + 8u * buf, ph ^ 1, p.wait_limit)) return false;
+                        tc_fence_after();
+                        const uint32_t zt = z_base + s * Cfg::kZStage;
+                        const uint64_t z_hi = make_mnmajor_sw128_desc(zt), z_lo = make_mnmajor_sw128_desc(zt + Cfg::kZTile);
+                        const uint32_t a_hi = tmem_base + kColS + 64u * buf, a_lo = tmem_base + kColWlo + 64u * buf;
+                        const uint32_t d_acc = tmem_base + kColAcc + 64u * buf;
+                        constexpr uint32_t zstep = 1024 >> 4;
+#pragma unroll
+                        for (int k = 0; k < 8; k++) umma_tf32_ts_pair(d_acc, a_lo + 8u * k, z_hi + zstep * k, idesc2, k == 0 ? 0u : 1u);
+#pragma unroll
+                        for (int k = 0; k < 8; k++) umma_tf32_ts_pair(d_acc, a_hi + 8u * k, z_lo + zstep * k, idesc2, 1);
+#pragma unroll
+                        for (int k = 0; k < 8; k++) umma_tf32_ts_pair(d_acc, a_hi + 8u * k, z_hi + zstep * k, idesc2, 1);
+                        umma_commit_pair(acc_full0 + 8u * buf);
+                        umma_commit_pair(z_empty0 + 8u * s);
+                        itz++;
+                        return true;
+                    };
+                    for (int c = 0; c < d.nb && ok; c++, g++) {
+                        const uint32_t buf = g & 1;
+                        const int s = ity % NYS;
+                        if (!mbar_wait_bounded_cluster(y_conv0 + 8u * s, (ity / NYS) & 1, p.wait_limit)) { ok = false; break; }
+                        tc_fence_after();
+                        const uint32_t yt = y_base + s * Cfg::kYStage;
+#pragma unroll
+                        for (int which = 0; which < NX; which++) {
+                            const uint32_t xt = x_base + which * 2 * Cfg::kXTile, ytw = yt + which * 2 * Cfg::kYTile;
+                            const uint32_t d_tm = tmem_base + (which == 0 ? kColS : kColDp) + 64u * buf;
+                            // lo*hi, hi*lo, hi*hi; the k-steps walk the 32-float k-blocks of the head dimension
+                            for (int pass = 0; pass < 3; pass++) {
+                                const uint32_t xa = xt + (pass == 0 ? Cfg::kXTile : 0), yb = ytw + (pass == 1 ? Cfg::kYTile : 0);
+                                for (int k = 0; k < ksteps1; k++) {
+                                    const uint64_t da = make_kmajor_sw128_desc(xa + (k >> 2) * 16384) + 2u * (k & 3);
+                                    const uint64_t db = make_kmajor_sw128_desc(yb + (k >> 2) * 4096) + 2u * (k & 3);
+                                    umma_tf32<2>(d_tm, da, db, idesc1, (pass == 0 && k == 0) ? 0u : 1u);
+                                }
+                            }
+                        }
+                        umma_commit_pair(s_full0 + 8u * buf);
+                        umma_commit_pair(y_empty0 + 8u * s);
+                        ity++;
+                        if (c == d.nb - 1) umma_commit_pair(x_empty);   // the row operands are free once these products are done
+                        if (c >= 1 && !second(g - 1)) { ok = false; break; }
+                    }
+                    if (ok && !second(g - 1)) ok = false;
+                }
+                if (!ok) atomicOr(p.status, ZNN_DEV_MMA_WAIT_EXPIRED);
+            }
+        } else {
+            // ---------------- converters: lo = x - (x with the 13 low mantissa bits cleared), next to each landed tile ----------------
+            const int ct = threadIdx.x - 32 * kAttConvWarp0;          // 0 .. 191
+            constexpr int kT = 32 * kAttConvWarps;
+            const uint32_t x_conv_l = mapa_shared(x_conv, 0), y_conv_l0 = mapa_shared(y_conv0, 0), z_conv_l0 = mapa_shared(z_conv0, 0);
+            auto convert = [&](uint8_t* base, int nvec, int lo_off) {
+#pragma unroll 1
+                for (int i0 = ct; i0 < nvec; i0 += 4 * kT) {
+                    uint4 x[4];
+#pragma unroll
+                    for (int v = 0; v < 4; v++)
+                        if (i0 + v * kT < nvec) x[v] = *reinterpret_cast<const uint4*>(base + 16 * (i0 + v * kT));
+#pragma unroll
+                    for (int v = 0; v < 4; v++) {
+                        if (i0 + v * kT >= nvec) continue;
+                        float4 l;
+                        l.x = __uint_as_float(x[v].x) - __uint_as_float(x[v].x & 0xFFFFE000u);
+                        l.y = __uint_as_float(x[v].y) - __uint_as_float(x[v].y & 0xFFFFE000u);
+                        l.z = __uint_as_float(x[v].z) - __uint_as_float(x[v].z & 0xFFFFE000u);
+                        l.w = __uint_as_float(x[v].w) - __uint_as_float(x[v].w & 0xFFFFE000u);
+                        *reinterpret_cast<float4*>(base + 16 * (i0 + v * kT) + lo_off) = l;
+                    }
+                }
+            };
+            auto wait_full = [&](uint32_t bar, uint32_t ph) -> bool {
+                bool got = true;
+                if (lane == 0) got = mbar_wait_bounded(bar, ph, p.wait_limit);
+                return __shfl_sync(0xffffffffu, (int)got, 0) != 0;
+            };
+            auto done = [&](uint32_t leader_bar) {
+                asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+                __syncwarp();
+                if (lane == 0) mbar_arrive_remote(leader_bar);
+            };
+            bool got = true;
+            uint32_t ity = 0, itz = 0, ul = 0;
+            for (int u = pair; u < total_units && got; u += npairs, ul++) {
+                const AttnUnit d = attn_unit<MODE>(p, u);
+                if (!(got = wait_full(x_full, ul & 1))) break;
+                for (int w = 0; w < NX; w++) convert(smem_gen + w * 2 * Cfg::kXTile, kbh * 1024, Cfg::kXTile);
+                done(x_conv_l);
+                for (int c = 0; c < d.nb; c++) {
+                    {
+                        const int s = ity % NYS;
+                        if (!(got = wait_full(y_full0 + 8u * s, (ity / NYS) & 1))) break;
+                        uint8_t* st = smem_gen + Cfg::kXBytes + s * Cfg::kYStage;
+                        for (int w = 0; w < NX; w++) convert(st + w * 2 * Cfg::kYTile, kbh * 256, Cfg::kYTile);
+                        done(y_conv_l0 + 8u * s);
+                        ity++;
+                    }
+                    {
+                        const int s = itz % NZS;
+                        if (!(got = wait_full(z_full0 + 8u * s, (itz / NZS) & 1))) break;
+                        uint8_t* st = smem_gen + Cfg::kXBytes + NYS * Cfg::kYStage + s * Cfg::kZStage;
+                        convert(st, 512, Cfg::kZTile);
+                        done(z_conv_l0 + 8u * s);
+                        itz++;
+                    }
+                }
+            }
+            if (!got && lane == 0) atomicOr(p.status, ZNN_DEV_TMA_WAIT_EXPIRED);
+        }
+    } else {
+        asm volatile("setmaxnreg.inc.sync.aligned.u32 232;");
+        if (!aborted) {
+            // ---------------- transform warps: one thread per row of this CTA's 128 ----------------
+            const int q = warp & 3;
+            const int rloc = q * 32 + lane;
+            const uint32_t lane_sel = (uint32_t)(q * 32) << 16;
+            const uint32_t w_ready_l0 = mapa_shared(w_ready0, 0), acc_empty_l0 = mapa_shared(acc_empty0, 0);
+            const int hs = p.hs;
+            bool got = true;
+            uint32_t g = 0;
+            auto wait_bar = [&](uint32_t bar, uint32_t ph) -> bool {
+                bool ok = true;
+                if (lane == 0) ok = mbar_wait_bounded(bar, ph, p.wait_limit);
+                return __shfl_sync(0xffffffffu, (int)ok, 0) != 0;
+            };
+            for (int u = pair; u < total_units && got; u += npairs) {
+                const AttnUnit d = attn_unit<MODE>(p, u);
+                const int row = d.row0 + cta_rank * kRowsPerCta + rloc;       // absolute row inside the slice
+                const bool row_ok = row < p.T;
+                const size_t stat_off = (size_t)d.slice * p.T;
+                float acc[64];
+#pragma unroll
+                for (int i = 0; i < 64; i++) acc[i] = 0.0f;
+                float m_run = -CUDART_INF_F, l_run = 0.0f, corr_prev = 1.0f;   // forward
+                float lse_r = 0.0f, d_r = 0.0f;                               // dQ: this row's statistics
+                if (MODE == ATT_BWD_Q && row_ok) {
+                    lse_r = p.lse[stat_off + row];
+                    d_r = p.dvec[stat_off + row];
+                }
+                // adds the accumulator of block gb (buffer gb & 1) into the registers
+                auto drain = [&](uint32_t gb, float factor) -> bool {
+                    const uint32_t buf = gb & 1;
+                    if (!wait_bar(acc_full0 + 8u * buf, (gb >> 1) & 1)) return false;
+                    tc_fence_after();
+                    const uint32_t t0 = tmem_base + lane_sel + kColAcc + 64u * buf;
+#pragma unroll
+                    for (int j = 0; j < 2; j++) {
+                        float v[32];
+                        tmem_ld_32x32(t0 + 32u * j, v);
+#pragma unroll
+                        for (int i = 0; i < 32; i++) {
+                            if (MODE == ATT_FWD) acc[32 * j + i] = acc[32 * j + i] * factor + v[i];
+                            else acc[32 * j + i] += v[i];
+                        }
+                    }
+                    tc_fence_before();
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive_remote(acc_empty_l0 + 8u * buf);
+                    return true;
+                };
+                for (int c = 0; c < d.nb; c++, g++) {
+                    const uint32_t buf = g & 1;
+                    const int col0 = (d.cb0 + c) * kColBlock;
+                    if (!(got = wait_bar(s_full0 + 8u * buf, (g >> 1) & 1))) break;
+                    tc_fence_after();
+                    const uint32_t ts = tmem_base + lane_sel + kColS + 64u * buf;
+                    const uint32_t tl = tmem_base + lane_sel + kColWlo + 64u * buf;
+                    const uint32_t tdp = tmem_base + lane_sel + kColDp + 64u * buf;
+                    float corr = 1.0f;
+                    if (MODE == ATT_FWD) {
+                        float s[64];
+                        tmem_ld_32x32(ts, *reinterpret_cast<float(*)[32]>(&s[0]));
+                        tmem_ld_32x32(ts + 32u, *reinterpret_cast<float(*)[32]>(&s[32]));
+                        float mx = m_run;
+#pragma unroll
+                        for (int j = 0; j < 64; j++) {
+                            const float v = (col0 + j <= row) ? s[j] * p.c2 : -CUDART_INF_F;
+                            s[j] = v;
+                            mx = fmaxf(mx, v);
+                        }
+                        corr = fast_exp2(m_run - mx);
+                        float sum = 0.0f;
+#pragma unroll
+                        for (int h2 = 0; h2 < 2; h2++) {
+                            uint32_t hi[32], lo[32];
+#pragma unroll
+                            for (int j = 0; j < 32; j++) {
+                                const float pv = fast_exp2(s[32 * h2 + j] - mx);
+                                sum += pv;
+                                hi[j] = __float_as_uint(pv) & 0xFFFFE000u;
+                                lo[j] = __float_as_uint(pv - __uint_as_float(hi[j]));
+                            }
+                            tmem_st_32x32(ts + 32u * h2, hi);
+                            tmem_st_32x32(tl + 32u * h2, lo);
+                        }
+                        l_run = l_run * corr + sum;
+                        m_run = mx;
+                    } else {
+#pragma unroll
+                        for (int h2 = 0; h2 < 2; h2++) {
+                            float s[32];
+                            tmem_ld_32x32(ts + 32u * h2, s);
+                            uint32_t hi[32], lo[32];
+                            if (MODE == ATT_BWD_V) {
+                                // W = P^T: rows are keys, columns queries; statistics per column
+#pragma unroll
+                                for (int j4 = 0; j4 < 8; j4++) {
+                                    const int qc = col0 + 32 * h2 + 4 * j4;
+                                    float4 l4 = make_float4(0.f, 0.f, 0.f, 0.f);
+                                    if (qc < p.T) l4 = *reinterpret_cast<const float4*>(p.lse + stat_off + qc);
+                                    const float ls[4] = {l4.x, l4.y, l4.z, l4.w};
+#pragma unroll
+                                    for (int e = 0; e < 4; e++) {
+                                        const int j = 4 * j4 + e;
+                                        const bool vis = (row <= qc + e) && (qc + e < p.T);
+                                        const float pv = vis ? fast_exp2(fmaf(s[j], p.c2, -ls[e])) : 0.0f;
+                                        hi[j] = __float_as_uint(pv) & 0xFFFFE000u;
+                                        lo[j] = __float_as_uint(pv - __uint_as_float(hi[j]));
+                                    }
+                                }
+                            } else {
+                                float dp[32];
+                                tmem_ld_32x32(tdp + 32u * h2, dp);
+                                if (MODE == ATT_BWD_Q) {
+#pragma unroll
+                                    for (int j = 0; j < 32; j++) {
+                                        const bool vis = (col0 + 32 * h2 + j <= row);
+                                        const float pv = vis ? fast_exp2(fmaf(s[j], p.c2, -lse_r)) : 0.0f;
+                                        const float ds = (pv * (dp[j] - d_r)) * p.scale;
+                                        hi[j] = __float_as_uint(ds) & 0xFFFFE000u;
+                                        lo[j] = __float_as_uint(ds - __uint_as_float(hi[j]));
+                                    }
+                                } else {   // ATT_BWD_K
+#pragma unroll
+                                    for (int j4 = 0; j4 < 8; j4++) {
+                                        const int qc = col0 + 32 * h2 + 4 * j4;
+                                        float4 l4 = make_float4(0.f, 0.f, 0.f, 0.f), d4 = l4;
+                                        if (qc < p.T) {
+                                            l4 = *reinterpret_cast<const float4*>(p.lse + stat_off + qc);
+                                            d4 = *reinterpret_cast<const float4*>(p.dvec + stat_off + qc);
+                                        }
+                                        const float ls[4] = {l4.x, l4.y, l4.z, l4.w}, dd[4] = {d4.x, d4.y, d4.z, d4.w};
+#pragma unroll
+                                        for (int e = 0; e < 4; e++) {
+                                            const int j = 4 * j4 + e;
+                                            const bool vis = (row <= qc + e) && (qc + e < p.T);
+                                            const float pv = vis ? fast_exp2(fmaf(s[j], p.c2, -ls[e])) : 0.0f;
+                                            const float ds = (pv * (dp[j] - dd[e])) * p.scale;
+                                            hi[j] = __float_as_uint(ds) & 0xFFFFE000u;
+                                            lo[j] = __float_as_uint(ds - __uint_as_float(hi[j]));
+                                        }
+                                    }
+                                }
+                            }
+                            tmem_st_32x32(ts + 32u * h2, hi);
+                            tmem_st_32x32(tl + 32u * h2, lo);
+                        }
+                    }
+                    tmem_st_wait();
+                    tc_fence_before();
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive_remote(w_ready_l0 + 8u * buf);
+                    // the previous block's second product has had this block's transform time to finish
+                    if (c >= 1 && !(got = drain(g - 1, corr_prev))) break;
+                    corr_prev = corr;
+                }
+                if (!got) break;
+                if (!(got = drain(g - 1, corr_prev))) break;
+                // ---- the rows leave: O = acc / l and the row's log-sum-exp, or the gradient rows ----
+                if (row_ok) {
+                    float* dst = p.out + (size_t)d.b * p.stride_b + (size_t)d.h * p.stride_h + (size_t)row * p.ld;
+                    if (MODE == ATT_FWD) {
+                        const float inv = 1.0f / l_run;
+                        p.lse[stat_off + row] = m_run + log2f(l_run);
+#pragma unroll
+                        for (int i = 0; i < 64; i += 4)
+                            if (i < hs)
+                                *reinterpret_cast<float4*>(dst + i) = make_float4(acc[i] * inv, acc[i + 1] * inv, acc[i + 2] * inv, acc[i + 3] * inv);
+                    } else {
+#pragma unroll
+                        for (int i = 0; i < 64; i += 4) {
+                            if (i >= hs) continue;
+                            float4 o = make_float4(acc[i], acc[i + 1], acc[i + 2], acc[i + 3]);
+                            if (p.accumulate) {
+                                const float4 old = *reinterpret_cast<const float4*>(dst + i);
+                                o.x += old.x; o.y += old.y; o.z += old.z; o.w += old.w;
+                            }
+                            *reinterpret_cast<float4*>(dst + i) = o;
+                        }
+                    }
+                }
+            }
+            if (!got && lane == 0) atomicOr(p.status, ZNN_DEV_EPI_WAIT_EXPIRED);
+        }
+    }
+
+    tc_fence_before();
+    __syncthreads();
+    cluster_sync_all();
+    if (warp == 1) {
+        tc_fence_after();
+        tmem_dealloc<2>(tmem_base, 512);
+    }
+}
+
+// D[s, t] = sum_d dO[s, t, d] * O[s, t, d]  (= rowsum(dP o P) of the softmax backward): hs / 4 lanes per row
+__global__ void attn_rowdot_kernel(const float* __restrict__ dO, const float* __restrict__ O, float* __restrict__ D, int nslices,
+                                   int nh, int T, int hs, long long ld, long long stride_h, long long stride_b)
+{
+    const int lpr = hs >> 2;                            // lanes per row (8 or 16)
+    const int rows_per_warp = 32 / lpr;
+    const size_t warp_id = (blockIdx.x * (size_t)blockDim.x + threadIdx.x) >> 5;
+    const int lane = threadIdx.x & 31;
+    const size_t r = warp_id * rows_per_warp + lane / lpr;
+    const bool ok = r < (size_t)nslices * T;
+    float s = 0.0f;
+    if (ok) {
+        const int slice = (int)(r / T), t = (int)(r - (size_t)slice * T);
+        const int b = slice / nh, h = slice - b * nh;
+        const size_t off = (size_t)b * stride_b + (size_t)h * stride_h + (size_t)t * ld + 4 * (lane % lpr);
+        const float4 a = *reinterpret_cast<const float4*>(dO + off), o = *reinterpret_cast<const float4*>(O + off);
+        s = (a.x * o.x + a.y * o.y) + (a.z * o.z + a.w * o.w);
+    }
+    for (int o = lpr >> 1; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
+    if (ok && (lane % lpr) == 0) D[r] = s;
+}
+
+// ---------------------------------------------------------------------------
+// host side
+// ---------------------------------------------------------------------------
+typedef CUresult (*EncodeTiledFn4)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
+                                   const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                   CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static EncodeTiledFn4 attn_encode_fn()
+{
+    static EncodeTiledFn4 fn = nullptr;
+    if (!fn) {
+        void* q = nullptr;
+        cudaDriverEntryPointQueryResult r;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &q, cudaEnableDefault, &r) == cudaSuccess && r == cudaDriverEntryPointSuccess)
+            fn = (EncodeTiledFn4)q;
+    }
+    return fn;
+}
+
+struct AttnLayout {
+    int B, nh, T, hs;
+    long long ld, stride_h, stride_b;
+    bool t_first;
+};
+
+// box_rows > 0: K-major tile of box_rows rows x 32 floats (128-byte swizzle); box_rows == 0: MN-major 32 x 32 box
+static int make_attn_map(CUtensorMap* tm, const float* X, const AttnLayout& L, int box_rows)
+{
+    EncodeTiledFn4 enc = attn_encode_fn();
+    if (!enc) return fail(ZNN_ERR_CUDA, "cuTensorMapEncodeTiled entry point not available");
+    const cuuint32_t rows = box_rows > 0 ? (cuuint32_t)box_rows : 32u;
+    cuuint64_t dims[4], strides[3];
+    cuuint32_t box[4], estr[4] = {1, 1, 1, 1};
+    dims[0] = (cuuint64_t)L.hs;
+    box[0] = 32;
+    if (L.t_first) {
+        dims[1] = (cuuint64_t)L.T; dims[2] = (cuuint64_t)L.nh;
+        strides[0] = (cuuint64_t)L.ld * 4; strides[1] = (cuuint64_t)L.stride_h * 4;
+        box[1] = rows; box[2] = 1;
+    } else {
+        dims[1] = (cuuint64_t)L.nh; dims[2] = (cuuint64_t)L.T;
+        strides[0] = (cuuint64_t)L.stride_h * 4; strides[1] = (cuuint64_t)L.ld * 4;
+        box[1] = 1; box[2] = rows;
+    }
+    dims[3] = (cuuint64_t)L.B;
+    strides[2] = (cuuint64_t)L.stride_b * 4;
+    box[3] = 1;
+    const CUresult r = enc(tm, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, const_cast<float*>(X), dims, strides, box, estr,
+                           CU_TENSOR_MAP_INTERLEAVE_NONE,
+                           box_rows > 0 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B,
+                           CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) return fail(ZNN_ERR_CUDA, "cuTensorMapEncodeTiled (attention operand) failed with %d", (int)r);
+    return ZNN_OK;
+}
+
+unsigned long long tc_wait_limit();
+
+template <int MODE>
+static int launch_attn(const float* X1, const float* X2, const float* Y1, const float* Y2, const float* Z, const AttnLayout& L,
+                       AttnParams p)
+{
+    using Cfg = AttnCfg<MODE>;
+    auto kern = attn_kernel<MODE>;
+    static bool attr_set[64] = {false};
+    static int pairs_by_device[64] = {0};
+    int dev = 0;
+    ZNN_CUDA_OK(cudaGetDevice(&dev));
+    if (dev < 0 || dev >= 64) return fail(ZNN_ERR_INVALID, "device index %d out of range", dev);
+    if (!attr_set[dev]) {
+        ZNN_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmemBytes));
+        attr_set[dev] = true;
+    }
+    CUtensorMap mx1, mx2, my1, my2, mz;
+    int rc;
+    if ((rc = make_attn_map(&mx1, X1, L, kRowsPerCta))) return rc;
+    if ((rc = make_attn_map(&mx2, X2 ? X2 : X1, L, kRowsPerCta))) return rc;
+    if ((rc = make_attn_map(&my1, Y1, L, 32))) return rc;
+    if ((rc = make_attn_map(&my2, Y2 ? Y2 : Y1, L, 32))) return rc;
+    if ((rc = make_attn_map(&mz, Z, L, 0))) return rc;
+    cudaLaunchConfig_t cfg = {};
+    cfg.blockDim = dim3(kAttThreads, 1, 1);
+    cfg.dynamicSmemBytes = Cfg::kSmemBytes;
+    cfg.stream = stream();
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = 2;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    if (pairs_by_device[dev] == 0) {
+        cfg.gridDim = dim3((unsigned)sm_count(), 1, 1);
+        int clusters = 0;
+        if (cudaOccupancyMaxActiveClusters(&clusters, kern, &cfg) != cudaSuccess || clusters < 1) {
+            cudaGetLastError();
+            clusters = sm_count() / 2;
+        }
+        pairs_by_device[dev] = clusters;
+    }
+    const long units = (long)p.nslices * p.nrb;
+    const long pairs = units < pairs_by_device[dev] ? units : pairs_by_device[dev];
+    cfg.gridDim = dim3((unsigned)(2 * pairs), 1, 1);
+    ZNN_CUDA_OK(cudaLaunchKernelEx(&cfg, kern, mx1, mx2, my1, my2, mz, p));
+    count_launch();
+    if (inject_launch_failure()) return fail(ZNN_ERR_CUDA, "launch of the attention kernel failed: injected failure (znn_debug_fail_after)");
+    return ZNN_OK;
+}
+
+static int attn_check(const void* const* ptrs, int nptr, int B, int nh, int T, int hs, long long ld, long long stride_h,
+                      long long stride_b, AttnLayout* L)
+{
+    ZNN_REQUIRE(B > 0 && nh > 0 && T > 0, "empty attention problem");
+    if (!(hs == 32 || hs == 64)) return fail(ZNN_ERR_UNSUPPORTED, "fused attention: head size %d (32 or 64 supported)", hs);
+    if (T % 4 != 0) return fail(ZNN_ERR_UNSUPPORTED, "fused attention: T = %d is not a multiple of 4", T);
+    if ((ld & 3) || (stride_h & 3) || (stride_b & 3) || ld < hs)
+        return fail(ZNN_ERR_UNSUPPORTED, "fused attention: row pitch and strides must be multiples of 4 floats");
+    for (int i = 0; i < nptr; i++) {
+        ZNN_REQUIRE(ptrs[i], "NULL pointer");
+        if (reinterpret_cast<uintptr_t>(ptrs[i]) & 15) return fail(ZNN_ERR_UNSUPPORTED, "fused attention: pointers must be 16-byte aligned");
+    }
+    if ((long long)B * nh > 0x3fffffLL) return fail(ZNN_ERR_INVALID, "too many (batch, head) slices");
+    L->B = B; L->nh = nh; L->T = T; L->hs = hs;
+    L->ld = ld; L->stride_h = stride_h; L->stride_b = stride_b;
+    L->t_first = (ld <= stride_h);   // tensor-map dimensions in order of ascending stride
+    return ZNN_OK;
+}
+
+static AttnParams attn_params(const AttnLayout& L, float scale)
+{
+    AttnParams p;
+    p.T = L.T; p.hs = L.hs; p.nh = L.nh; p.nslices = L.B * L.nh;
+    p.nrb = (L.T + 255) / 256;
+    p.ncb = (L.T + kColBlock - 1) / kColBlock;
+    p.t_first = L.t_first ? 1 : 0;
+    p.scale = scale;
+    p.c2 = scale * 1.4426950408889634f;
+    p.ld = L.ld; p.stride_h = L.stride_h; p.stride_b = L.stride_b;
+    p.out = nullptr; p.lse = nullptr; p.dvec = nullptr;
+    p.accumulate = 0;
+    p.status = device_status_word();
+    p.wait_limit = tc_wait_limit();
+    return p;
+}
+
+}  // namespace znn
+
+using namespace znn;
+
+extern "C" {
+
+int znn_attn_fwd(const float* Q, const float* K, const float* V, float* O, float* LSE, int B, int nh, int T, int hs,
+                 long long ld, long long stride_h, long long stride_b, float scale)
+{
+    if (!stream()) return fail(ZNN_ERR_CUDA, "no CUDA device state; call znn_init (this library has no CPU fallback)");
+    AttnLayout L;
+    const void* ptrs[5] = {Q, K, V, O, LSE};
+    int rc = attn_check(ptrs, 5, B, nh, T, hs, ld, stride_h, stride_b, &L);
+    if (rc) return rc;
+    AttnParams p = attn_params(L, scale);
+    if (!p.status) return fail(ZNN_ERR_CUDA, "no device state (call znn_init first)");
+    p.out = O;
+    p.lse = LSE;
+    return launch_attn<ATT_FWD>(Q, nullptr, K, nullptr, V, L, p);
+}
+
+int znn_attn_bwd(const float* Q, const float* K, const float* V, const float* O, const float* dO, const float* LSE, float* dQ,
+                 float* dK, float* dV, int B, int nh, int T, int hs, long long ld, long long stride_h, long long stride_b,
+                 float scale, int accumulate)
+{
+    if (!stream()) return fail(ZNN_ERR_CUDA, "no CUDA device state; call znn_init (this library has no CPU fallback)");
+    AttnLayout L;
+    const void* ptrs[6] = {Q, K, V, O, dO, LSE};
+    int rc = attn_check(ptrs, 6, B, nh, T, hs, ld, stride_h, stride_b, &L);
+    if (rc) return rc;
+    const void* grads[3] = {dQ, dK, dV};
+    for (const void* g : grads)
+        if (g && (reinterpret_cast<uintptr_t>(g) & 15)) return fail(ZNN_ERR_UNSUPPORTED, "fused attention: pointers must be 16-byte aligned");
+    AttnParams p = attn_params(L, scale);
+    if (!p.status) return fail(ZNN_ERR_CUDA, "no device state (call znn_init first)");
+    p.accumulate = accumulate ? 1 : 0;
+    p.lse = const_cast<float*>(LSE);
+    if (dQ || dK) {
+        const size_t rows = (size_t)p.nslices * T;
+        float* D = (float*)workspace(rows * sizeof(float));
+        if (!D) return fail(ZNN_ERR_NOMEM, "scratch for the attention row sums");
+        const int rows_per_block = 256 / (hs / 4);
+        attn_rowdot_kernel<<<(unsigned)((rows + rows_per_block - 1) / rows_per_block), 256, 0, stream()>>>(
+            dO, O, D, p.nslices, nh, T, hs, ld, stride_h, stride_b);
+        ZNN_LAUNCH_OK("attn_rowdot_kernel");
+        p.dvec = D;
+    }
+    if (dQ) {
+        p.out = dQ;
+        if ((rc = launch_attn<ATT_BWD_Q>(Q, dO, K, V, K, L, p))) return rc;
+    }
+    if (dK) {
+        p.out = dK;
+        if ((rc = launch_attn<ATT_BWD_K>(K, V, Q, dO, Q, L, p))) return rc;
+    }
+    if (dV) {
+        p.out = dV;
+        if ((rc = launch_attn<ATT_BWD_V>(K, nullptr, Q, nullptr, dO, L, p))) return rc;
+    }
+    return ZNN_OK;
+}
+
+}  // extern "C"
