@@ -150,6 +150,28 @@ int znn_sgemm_batched_strided_tri(int trans_a, int trans_b, int M, int N, int K,
  * multiples of 4); returns ZNN_ERR_UNSUPPORTED otherwise and the caller uses the separate ops. */
 int znn_attn_dscores(const float* dO, const float* V, const float* P, const float* D, float scale, float* dS, int T, int hs,
                      int nslices);
+/* Causal self-attention as one fused operation (an addition; it replaces the chain of src/nn.zig:796-906 --
+ * transposeND x4, batchMatMul, mulScalar, mask, add, softmax, batchMatMul, transposeND -- whose operator arms are
+ * src/autodiff.zig:485-531, :1054-1076, :1117-1182):
+ *     O[b,h] = softmax_rows(scale * Q[b,h].K[b,h]^T + causal mask) . V[b,h]
+ * The T x T score and probability matrices are never written to memory: a CTA pair holds 256 rows of one (batch, head)
+ * slice, walks the 64-wide blocks of the other sequence dimension up to (or from) the diagonal, and keeps scores,
+ * probabilities and partial outputs in tensor memory; all products are 3xTF32 tcgen05 MMAs with fp32 promotion per block.
+ * Element (b, h, t, d) of Q, K, V, O, dO and the gradients lies at  b * stride_b + h * stride_h + t * ld + d  (floats):
+ *   [B, T, nh, hs] as the projections produce it:   ld = nh * hs, stride_h = hs,     stride_b = T * nh * hs
+ *   [B, nh, T, hs] as the reference's transposeND:   ld = hs,      stride_h = T * hs, stride_b = nh * T * hs
+ * so neither the head split nor the merge needs a copy.  LSE ([B * nh, T] floats) receives, per row, the base-2
+ * log-sum-exp of the scaled visible scores; the backward recomputes the probabilities from it.
+ * znn_attn_bwd: dQ, dK, dV (any may be NULL = requires_grad false) from dO, by three launches of the same kernel
+ * (dQ by query rows; dK and dV by key rows), deterministic (no atomics); accumulate = 1 adds into the gradients (the
+ * reference's +=), 0 stores them.
+ * Limits: hs = 32 or 64; T, ld and the strides multiples of 4; 16-byte aligned pointers; otherwise
+ * ZNN_ERR_UNSUPPORTED and the caller runs the separate operators. */
+int znn_attn_fwd(const float* Q, const float* K, const float* V, float* O, float* LSE, int B, int nh, int T, int hs,
+                 long long ld, long long stride_h, long long stride_b, float scale);
+int znn_attn_bwd(const float* Q, const float* K, const float* V, const float* O, const float* dO, const float* LSE, float* dQ,
+                 float* dK, float* dV, int B, int nh, int T, int hs, long long ld, long long stride_h, long long stride_b,
+                 float scale, int accumulate);
 /* out[r] = sum_j A[r,j] * B[r,j] for `rows` rows of D floats (the D vector above from dO and O) */
 int znn_rowdot(const float* A, const float* B, float* out, size_t rows, int D);
 /* Fused form of Linear.forward = addBias(matmul(x, W), b) (src/nn.zig:44-51): Y[M,N] = X[M,K].W[K,N] + bias[N]

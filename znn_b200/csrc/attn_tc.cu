@@ -30,6 +30,7 @@
 #include "tc_ptx.cuh"
 
 #include <math.h>
+#include <math_constants.h>
 
 namespace znn {
 

@@ -356,6 +356,48 @@ def attn_dscores(dO, V, P, scale):
     return out
 
 
+def _attn_layout(shape, layout):
+    if layout == "bhtd":
+        B, nh, T, hs = shape
+        return B, nh, T, hs, hs, T * hs, nh * T * hs
+    B, T, nh, hs = shape
+    return B, nh, T, hs, nh * hs, hs, T * nh * hs
+
+
+def attn_fwd(Q, K, V, scale, layout="bhtd"):
+    """Fused causal attention forward.  layout 'bhtd': arrays are [B, nh, T, hs]; 'bthd': [B, T, nh, hs].
+    Returns (O in the same layout, LSE [B*nh, T])."""
+    _ensure()
+    Q, K, V = _f(Q), _f(K), _f(V)
+    B, nh, T, hs, ld, sh, sb = _attn_layout(Q.shape, layout)
+    dQ_, dK_, dV_ = _up(Q), _up(K), _up(V)
+    dO, dL = DevBuf(Q.nbytes), DevBuf(B * nh * T * 4)
+    lib().call("znn_attn_fwd", dQ_.ptr, dK_.ptr, dV_.ptr, dO.ptr, dL.ptr, B, nh, T, hs, ld, sh, sb, scale)
+    check_device_status()
+    return dO.to_host(Q.shape), dL.to_host((B * nh, T))
+
+
+def attn_bwd(Q, K, V, O, dO, LSE, scale, layout="bhtd", grads=None, want=(True, True, True)):
+    """Fused causal attention backward: returns (dQ, dK, dV).  With grads = (dQ0, dK0, dV0) the results are added to
+    them (the reference's +=)."""
+    _ensure()
+    Q, K, V, O, dO, LSE = _f(Q), _f(K), _f(V), _f(O), _f(dO), _f(LSE)
+    B, nh, T, hs, ld, sh, sb = _attn_layout(Q.shape, layout)
+    bufs = [_up(a) for a in (Q, K, V, O, dO, LSE)]
+    outs = []
+    for i, w in enumerate(want):
+        if not w:
+            outs.append(None)
+        elif grads is not None:
+            outs.append(_up(grads[i]))
+        else:
+            outs.append(DevBuf(Q.nbytes))
+    lib().call("znn_attn_bwd", *[b.ptr for b in bufs], *[_ptr(o) for o in outs], B, nh, T, hs, ld, sh, sb, scale,
+               1 if grads is not None else 0)
+    check_device_status()
+    return tuple(o.to_host(Q.shape) if o is not None else None for o in outs)
+
+
 def rowdot(A, B):
     _ensure()
     A, B = _f(A), _f(B)
