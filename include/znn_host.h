@@ -8,7 +8,8 @@
  *    handles; `znn_graph_op` appends one op by its reference builder name
  *    ("matmul", "addBias", "relu", "gelu", "softmaxCrossEntropy", "reshape",
  *    "transposeND", "mulScalar", "add", "conv2d", "maxpool2d", "softmax",
- *    "rmsNorm", "batchMatMul", "embedding", plus the additions "causalSoftmax", "layerNorm", "linear").
+ *    "rmsNorm", "batchMatMul", "embedding", plus the additions "causalSoftmax", "layerNorm", "linear", "causalAttention"
+ *    (args: B, T, heads, scale)).
  *  - znn_model_*: the example programs' models (examples/fashion_mnist.zig,
  *    examples/cnn.zig, examples/transformer_block.zig, examples/transformer_gpt.zig)
  *    with their training step: new graph -> forward -> SoftmaxCrossEntropy ->
@@ -76,7 +77,9 @@ int znn_model_get_grads(znn_model* m, float* host_slab);
 int znn_model_get_velocities(znn_model* m, float* host_slab);
 /* keys: "lr", "momentum", "fused_softmax" (1/0), "fused_linear" (1/0, process-wide), "causal_skip" (1/0, process-wide: attention products
  * skip the tiles above the causal diagonal; needs fused_softmax), "fused_softmax_bwd" (1/0, process-wide: the gradient of the attention scores comes out of
- * the dO.V^T product's epilogue, no dP buffer and no separate softmax backward), "fused_qkt" (1/0, process-wide: attention scores as one
+ * the dO.V^T product's epilogue, no dP buffer and no separate softmax backward), "fused_attention" (1/0, process-wide, default 1: the whole attention chain
+ * as the one fused op znn_attn_fwd / znn_attn_bwd on the [B*T, C] projections when the head size is 32 or 64 and T a multiple
+ * of 4; needs fused_softmax; 0 = the separate products and softmax below), "fused_qkt" (1/0, process-wide: attention scores as one
  * Q.K^T op instead of a transposed copy of K and a product), "alias_reshape_grad" (1/0, process-wide: Reshape views
  * share the gradient buffer of their input instead of adding into it in backward), "lazy_zero_grad" (1/0, process-wide:
  * gradient buffers of intermediates are zero-filled only when first added to; GEMM arms overwrite them with beta = 0), "dp_bucket_floats",

@@ -238,20 +238,24 @@ def test_gpt_causal_tile_skipping(Model):
     res = []
     try:
         # hints on; hints off; and the reference's literal transposeND(K) + batchMatMul instead of the one Q.K^T op
-        for skip, qkt, fsb in ((1, 1, 1), (0, 1, 1), (0, 0, 0), (1, 0, 0), (1, 1, 0)):
+        # the last variant is the single fused attention op (znn_attn_fwd / znn_attn_bwd), the default
+        for skip, qkt, fsb, fa in ((1, 1, 1, 0), (0, 1, 1, 0), (0, 0, 0, 0), (1, 0, 0, 0), (1, 1, 0, 0), (1, 1, 1, 1)):
             m = Model("gpt", dims, arena_bytes=1 << 30)
             m.set_params(P0)
+            m.set_option("fused_attention", fa)
             m.set_option("causal_skip", skip)
             m.set_option("fused_qkt", qkt)
             m.set_option("fused_softmax_bwd", fsb)
             m.set_option("lr", 0.0)
-            res.append((m.train_step(x, t, seq=768), m.get_grads()))
+            res.append((m.train_step(x, t, seq=768), m.get_grads(), m.last_step_ops()))
     finally:
+        m.set_option("fused_attention", 1)
         m.set_option("causal_skip", 1)
         m.set_option("fused_qkt", 1)
         m.set_option("fused_softmax_bwd", 1)
     floor = 3e-2 * grad_floor(res[2][1])   # see test_gpt_literal_attention_path: noise of exactly-zero gradients
-    for i in (0, 1, 3, 4):
+    assert res[5][2] < res[0][2]          # the fused op replaces the transposes, products and softmax of the chain
+    for i in (0, 1, 3, 4, 5):
         assert abs(res[i][0] - res[2][0]) <= 1e-6 * abs(res[2][0])
         for k in res[i][1]:
             relclose(res[i][1][k], res[2][1][k], 1e-5, k, floor)

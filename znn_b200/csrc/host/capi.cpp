@@ -126,6 +126,8 @@ int znn_graph_op(znn_graph* zg, const char* name, const int* inputs, int n_input
     else if (op == "batchMatMul") out = g.batchMatMul(in(0), in(1));
     else if (op == "batchMatMulNT") out = g.batchMatMulNT(in(0), in(1));
     else if (op == "linear") out = g.linear(in(0), in(1), in(2));
+    else if (op == "causalAttention")
+        out = g.causalAttention(in(0), in(1), in(2), (size_t)arg(0), (size_t)arg(1), (size_t)arg(2), (float)arg(3));
     else if (op == "embedding") out = g.embedding(in(0), in(1));
     else throw Error(ZNN_ERR_INVALID, "unknown op '" + op + "'");
     zg->handles.push_back(out);
@@ -468,6 +470,7 @@ int znn_model_set_option(znn_model* m, const char* key, double value)
     } else if (k == "fused_linear") set_fused_linear(value != 0.0);
     else if (k == "causal_skip") set_causal_skip(value != 0.0);
     else if (k == "fused_qkt") set_fused_qkt(value != 0.0);
+    else if (k == "fused_attention") set_fused_attention(value != 0.0);
     else if (k == "fused_softmax_bwd") set_fused_softmax_bwd(value != 0.0);
     else if (k == "alias_reshape_grad") set_alias_reshape_grad(value != 0.0);
     else if (k == "lazy_zero_grad") set_lazy_zero_grad(value != 0.0);

@@ -336,6 +336,22 @@ Tensor* Graph::causalSoftmax(Tensor* S, float scale)
     return C;
 }
 
+Tensor* Graph::causalAttention(Tensor* q, Tensor* k, Tensor* v, size_t B, size_t T, size_t nh, float scale)
+{
+    if (q->shape.len != 2 || !(q->shape == k->shape) || !(q->shape == v->shape) || q->shape.dims[0] != B * T || nh == 0 ||
+        q->shape.dims[1] % nh != 0)
+        throw Error(ZNN_ERR_INVALID, "causalAttention: need q, k, v of shape [B*T, C] with C a multiple of the head count");
+    Tensor* y = new_tensor(q->shape, any_grad({q, k, v}), false);
+    Op* o = new_op(OpType::CausalAttention, {q, k, v}, y);
+    o->scalar = scale;
+    o->att_B = (int)B;
+    o->att_T = (int)T;
+    o->att_nh = (int)nh;
+    o->scratch = (float*)arena_->alloc(B * nh * T * sizeof(float));
+    o->forward();
+    return y;
+}
+
 Tensor* Graph::rmsNorm(Tensor* X, Tensor* G, float eps)
 {
     Tensor* Y = new_tensor(X->shape, any_grad({X, G}), false);
@@ -508,6 +524,13 @@ void Op::forward()
               "Embedding forward");
         break;
     }
+    case OpType::CausalAttention: {
+        const long long Cw = (long long)A->shape.dims[1], hs = Cw / att_nh;
+        check(znn_attn_fwd(A->data, inputs[1]->data, inputs[2]->data, C->data, scratch, att_B, att_nh, att_T, (int)hs, Cw, hs,
+                           (long long)att_T * Cw, scalar),
+              "CausalAttention forward");
+        break;
+    }
     }
 }
 
@@ -524,7 +547,7 @@ void Op::backward()
     // arms that only add need a defined buffer; the GEMM arms below overwrite a fresh one instead (beta = 0)
     // (so do Gelu, CausalSoftmax, Add, MulScalar, Reshape and Transpose, with a storing kernel or a plain copy)
     const bool can_store = type == OpType::MatMul || type == OpType::BatchMatMul || type == OpType::BatchMatMulNT ||
-                           type == OpType::LinearBias ||
+                           type == OpType::LinearBias || type == OpType::CausalAttention ||
                            type == OpType::Gelu || type == OpType::CausalSoftmax || type == OpType::Add ||
                            type == OpType::MulScalar || type == OpType::Reshape || type == OpType::Transpose;
     if (!can_store)
@@ -738,6 +761,25 @@ void Op::backward()
         if (W->requires_grad)
             check(znn_embedding_bwd(X->data, C->grad, W->grad, X->numel(), (int)W->shape.dims[1], (int)W->shape.dims[0]),
                   "Embedding backward");
+        break;
+    }
+    case OpType::CausalAttention: {
+        Tensor* Kt = inputs[1];
+        Tensor* Vt = inputs[2];
+        const long long Cw = (long long)A->shape.dims[1], hs = Cw / att_nh;
+        // one store/add switch for the three gradients: store when every wanted buffer is still untouched
+        bool fresh = true;
+        for (Tensor* t : inputs)
+            if (t->requires_grad && !grad_is_fresh(t)) fresh = false;
+        for (Tensor* t : inputs) {
+            if (!t->requires_grad) continue;
+            if (fresh) mark_grad_written(t);
+            else ensure_grad(t);
+        }
+        check(znn_attn_bwd(A->data, Kt->data, Vt->data, C->data, C->grad, scratch, A->requires_grad ? A->grad : nullptr,
+                           Kt->requires_grad ? Kt->grad : nullptr, Vt->requires_grad ? Vt->grad : nullptr, att_B, att_nh, att_T,
+                           (int)hs, Cw, hs, (long long)att_T * Cw, scalar, fresh ? 0 : 1),
+              "CausalAttention backward");
         break;
     }
     }

@@ -80,7 +80,9 @@ enum class OpType {
     CausalSoftmax,  // fused mulScalar + mask add + softmax of src/nn.zig:835-886 (an addition)
     LayerNorm,      // extension, no reference counterpart
     LinearBias,     // fused matmul + addBias of Linear.forward (src/nn.zig:44-51), an addition
-    BatchMatMulNT   // C = A.B^T per (batch, head) slice: transposeND(K) + batchMatMul of src/nn.zig:796-835 in one op, an addition
+    BatchMatMulNT,  // C = A.B^T per (batch, head) slice: transposeND(K) + batchMatMul of src/nn.zig:796-835 in one op, an addition
+    CausalAttention // the whole chain of src/nn.zig:796-906 (head split, Q.K^T, scale, mask, softmax, P.V, head merge) as one
+                    // fused op on the [B*T, C] projections (znn_attn_fwd / znn_attn_bwd), an addition
 };
 
 // src/autodiff.zig:100-105 (OpContext flattened)
@@ -91,6 +93,7 @@ struct Op {
     int dim0 = 0, dim1 = 0;     // Transpose
     int pool = 0, stride = 0;   // MaxPool2D
     int pad = 0;                // Conv2D (0 = reference)
+    int att_B = 0, att_T = 0, att_nh = 0;   // CausalAttention: batch, sequence length, heads (scratch = the rows' log-sum-exp)
     int tri_role = 0;           // BatchMatMul next to a causal softmax: 1 = C are the scores, 2 = A are the probabilities
     float* scratch = nullptr;   // BatchMatMul role 2: one float per probability row (the D vector of the fused backward)
     bool skip_backward = false; // CausalSoftmax: its input gradient was already produced by the consumer's fused backward
@@ -162,6 +165,9 @@ public:
     Tensor* batchMatMulNT(Tensor* A, Tensor* B, int tri_role = 0);
     Tensor* embedding(Tensor* W, Tensor* X);                                // :2160
     Tensor* causalSoftmax(Tensor* S, float scale);                          // fused addition
+    // y[B*T, C] = merge_heads(softmax(scale * Q_h.K_h^T + causal mask).V_h) for q, k, v of shape [B*T, C] with nh heads
+    // of C / nh columns each (src/nn.zig:796-906 in one op; no score matrix, no head split / merge copies)
+    Tensor* causalAttention(Tensor* q, Tensor* k, Tensor* v, size_t B, size_t T, size_t nh, float scale);
     Tensor* layerNorm(Tensor* X, Tensor* G, Tensor* B, float eps);          // extension
     Tensor* linear(Tensor* X, Tensor* W, Tensor* bias);                     // fused addBias(matmul(X, W), bias)
 

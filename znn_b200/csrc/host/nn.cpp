@@ -82,6 +82,10 @@ static bool g_causal_skip = true;
 void set_causal_skip(bool on) { g_causal_skip = on; }
 bool causal_skip() { return g_causal_skip; }
 
+static bool g_fused_attention = true;
+void set_fused_attention(bool on) { g_fused_attention = on; }
+bool fused_attention() { return g_fused_attention; }
+
 static bool g_fused_linear = true;
 void set_fused_linear(bool on) { g_fused_linear = on; }
 bool fused_linear() { return g_fused_linear; }
@@ -148,6 +152,12 @@ Tensor* CausalSelfAttention::forward(Graph& g, Tensor* x) const
     Tensor* q_2d = q_attn.forward(g, x_2d);
     Tensor* k_2d = k_attn.forward(g, x_2d);
     Tensor* v_2d = v_attn.forward(g, x_2d);
+    if (fused_softmax && g_fused_attention && (hs == 32 || hs == 64) && T % 4 == 0) {
+        // one op on the projections where they lie: the heads are read and written through strides
+        Tensor* y_2d = g.causalAttention(q_2d, k_2d, v_2d, B, T, nh, 1.0f / sqrtf((float)hs));
+        Tensor* out_2d = c_proj.forward(g, y_2d);
+        return g.reshape(out_2d, Shape{B, T, C});
+    }
     Tensor* q_4d = g.reshape(q_2d, Shape{B, T, nh, hs});
     Tensor* k_4d = g.reshape(k_2d, Shape{B, T, nh, hs});
     Tensor* v_4d = g.reshape(v_2d, Shape{B, T, nh, hs});

@@ -54,6 +54,10 @@ void set_fused_qkt(bool on);
 bool fused_qkt();
 void set_fused_linear(bool on);
 bool fused_linear();
+// The attention chain (head split, Q.K^T, scale + mask + softmax, P.V, head merge) as the one fused op whenever the
+// fused kernel takes the shape (head size 32 or 64, T a multiple of 4); default on, needs fused_softmax.
+void set_fused_attention(bool on);
+bool fused_attention();
 
 // src/nn.zig:10-52.  W is [in, out], b is [1, out]; forward = addBias(matmul(x, W), b)
 struct Linear {
