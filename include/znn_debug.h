@@ -34,6 +34,12 @@ int znn_gemm_wait_record(int* out16);
 int znn_gemm_profile(int enable);
 int znn_gemm_profile_read(double* kernel_ms, long long* launches, double* flops);
 
+/* Role profile of the fused attention kernels, filled only by a build with -DZNN_ATTN_PROFILE (all zero otherwise):
+ * cycles CTA pair 0's leader spent in each role's loop and inside each kind of wait, summed over the launches since
+ * the last read: [0] MMA loop, [1] x_conv, [2] y_conv, [3] w_ready, [4] z_conv, [5] acc_empty waits; [8] transform loop,
+ * [9] s_full, [10] acc_full waits; [12] TMA producer loop, [13] its waits; [14] converter loop, [15] its waits. */
+int znn_debug_attn_profile(long long* out16);
+
 /* ---- test hooks ---- */
 /* SM cycles a GEMM role waits on an mbarrier before it gives up, sets a ZNN_DEV_*_WAIT_EXPIRED bit in the device status
  * word and leaves (default 4e9, about 2 s; 0 restores the default).  Applies to kernels launched afterwards. */

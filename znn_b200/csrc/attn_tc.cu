@@ -99,6 +99,21 @@ __device__ __forceinline__ AttnUnit attn_unit(const AttnParams& p, int u)
     return d;
 }
 
+// Optional role profile (compile with -DZNN_ATTN_PROFILE; off in the product build): CTA pair 0's leader adds up, per
+// role, the cycles spent inside each kind of wait and the cycles of the whole role loop into g_attn_prof, which
+// znn_debug_attn_profile reads: [0] MMA loop, [1] x_conv, [2] y_conv, [3] w_ready, [4] z_conv, [5] acc_empty;
+// [8] transform loop, [9] s_full, [10] acc_full; [12] producer loop, [13] its waits; [14] converter loop, [15] its waits.
+__device__ long long g_attn_prof[16];
+#ifdef ZNN_ATTN_PROFILE
+#define ATT_PROF_T0 const long long prof_t0 = clock64();
+#define ATT_PROF_WAIT(slot, expr) [&]() { const long long t_ = clock64(); const bool r_ = (expr); if (prof_on) g_attn_prof[slot] += clock64() - t_; return r_; }()
+#define ATT_PROF_END(slot) if (prof_on) g_attn_prof[slot] += clock64() - prof_t0;
+#else
+#define ATT_PROF_T0
+#define ATT_PROF_WAIT(slot, expr) (expr)
+#define ATT_PROF_END(slot)
+#endif
+
 __device__ __forceinline__ float fast_exp2(float x)
 {
     float y;
@@ -146,6 +161,9 @@ attn_kernel(const __grid_constant__ CUtensorMap mx1, const __grid_constant__ CUt
     const int pair = blockIdx.x >> 1, npairs = gridDim.x >> 1;
     const int total_units = p.nslices * p.nrb;
     const int kbh = p.hs >> 5;                    // 32-float k-blocks across the head dimension (1 or 2)
+#ifdef ZNN_ATTN_PROFILE
+    const bool prof_on = (pair == 0 && cta_rank == 0 && lane == 0 && (warp <= 2 || warp == kAttXfWarp0));
+#endif
 
     if (threadIdx.x == 0) {
         mbar_init(x_full, 1);
@@ -193,10 +211,11 @@ attn_kernel(const __grid_constant__ CUtensorMap mx1, const __grid_constant__ CUt
             if (lane == 0) {
                 bool ok = true;
                 uint32_t ity = 0, itz = 0, ul = 0;
+                ATT_PROF_T0
                 for (int u = pair; u < total_units && ok; u += npairs, ul++) {
                     const AttnUnit d = attn_unit<MODE>(p, u);
                     // the row operands of this unit, once the previous unit's first products no longer read them
-                    if (!mbar_wait_bounded(x_empty, (ul & 1) ^ 1, p.wait_limit)) { ok = false; break; }
+                    if (!ATT_PROF_WAIT(13, mbar_wait_bounded(x_empty, (ul & 1) ^ 1, p.wait_limit))) { ok = false; break; }
                     mbar_arrive_expect_tx(x_full, (uint32_t)(NX * kbh * 16384));
                     const int xrow = d.row0 + cta_rank * kRowsPerCta;
                     for (int kb = 0; kb < kbh; kb++) {
@@ -211,7 +230,7 @@ attn_kernel(const __grid_constant__ CUtensorMap mx1, const __grid_constant__ CUt
                         const int col0 = (d.cb0 + c) * kColBlock;
                         {   // Y: this CTA's 32 of the block's 64 columns, K-major
                             const int s = ity % NYS;
-                            if (!mbar_wait_bounded(y_empty0 + 8u * s, ((ity / NYS) & 1) ^ 1, p.wait_limit)) { ok = false; break; }
+                            if (!ATT_PROF_WAIT(13, mbar_wait_bounded(y_empty0 + 8u * s, ((ity / NYS) & 1) ^ 1, p.wait_limit))) { ok = false; break; }
                             const uint32_t fb = y_full0 + 8u * s, st = y_base + s * Cfg::kYStage;
                             mbar_arrive_expect_tx(fb, (uint32_t)(NX * kbh * 4096));
                             const int yrow = col0 + cta_rank * 32;
@@ -227,7 +246,7 @@ attn_kernel(const __grid_constant__ CUtensorMap mx1, const __grid_constant__ CUt
                         }
                         {   // Z: the block's 64 contraction rows x this CTA's 32 output columns, MN-major
                             const int s = itz % NZS;
-                            if (!mbar_wait_bounded(z_empty0 + 8u * s, ((itz / NZS) & 1) ^ 1, p.wait_limit)) { ok = false; break; }
+                            if (!ATT_PROF_WAIT(13, mbar_wait_bounded(z_empty0 + 8u * s, ((itz / NZS) & 1) ^ 1, p.wait_limit))) { ok = false; break; }
                             const uint32_t fb = z_full0 + 8u * s, st = z_base + s * Cfg::kZStage;
                             mbar_arrive_expect_tx(fb, 8192u);
                             const int d0 = cta_rank * 32;     // beyond hs (hs = 32, second CTA): the box is zero-filled
@@ -240,6 +259,7 @@ attn_kernel(const __grid_constant__ CUtensorMap mx1, const __grid_constant__ CUt
                     }
                 }
                 if (!ok) atomicOr(p.status, ZNN_DEV_TMA_WAIT_EXPIRED);
+                ATT_PROF_END(12)
             }
         } else if (warp == 1) {
             // ---------------- MMA issuer (leader CTA only) ----------------
@@ -249,20 +269,22 @@ attn_kernel(const __grid_constant__ CUtensorMap mx1, const __grid_constant__ CUt
                 bool ok = true;
                 uint32_t ity = 0, itz = 0, ul = 0, g = 0;     // g: blocks issued so far (buffer = g & 1)
                 const int ksteps1 = p.hs >> 3;                // K = 8 per instruction
+                const uint64_t dx0 = make_kmajor_sw128_desc(x_base), dy0 = make_kmajor_sw128_desc(y_base);
+                const uint64_t dz0 = make_mnmajor_sw128_desc(z_base);
+                ATT_PROF_T0
                 for (int u = pair; u < total_units && ok; u += npairs, ul++) {
                     const AttnUnit d = attn_unit<MODE>(p, u);
-                    if (!mbar_wait_bounded_cluster(x_conv, ul & 1, p.wait_limit)) { ok = false; break; }
+                    if (!ATT_PROF_WAIT(1, mbar_wait_bounded_cluster(x_conv, ul & 1, p.wait_limit))) { ok = false; break; }
                     tc_fence_after();
                     // second product of the block issued `gp` blocks ago (program order: P1(c), P2(c-1), P1(c+1), ...)
                     auto second = [&](uint32_t gb) -> bool {
                         const uint32_t buf = gb & 1, ph = (gb >> 1) & 1;
-                        if (!mbar_wait_bounded_cluster(w_ready0 + 8u * buf, ph, p.wait_limit)) return false;
+                        if (!ATT_PROF_WAIT(3, mbar_wait_bounded_cluster(w_ready0 + 8u * buf, ph, p.wait_limit))) return false;
                         const int s = itz % NZS;
-                        if (!mbar_wait_bounded_cluster(z_conv0 + 8u * s, (itz / NZS) & 1, p.wait_limit)) return false;
-                        if (!mbar_wait_bounded_cluster(acc_empty0 + 8u * buf, ph ^ 1, p.wait_limit)) return false;
+                        if (!ATT_PROF_WAIT(4, mbar_wait_bounded_cluster(z_conv0 + 8u * s, (itz / NZS) & 1, p.wait_limit))) return false;
+                        if (!ATT_PROF_WAIT(5, mbar_wait_bounded_cluster(acc_empty0 + 8u * buf, ph ^ 1, p.wait_limit))) return false;
                         tc_fence_after();
-                        const uint32_t zt = z_base + s * Cfg::kZStage;
-                        const uint64_t z_hi = make_mnmajor_sw128_desc(zt), z_lo = make_mnmajor_sw128_desc(zt + Cfg::kZTile);
+                        const uint64_t z_hi = dz0 + (uint64_t)((s * Cfg::kZStage) >> 4), z_lo = z_hi + (Cfg::kZTile >> 4);
                         const uint32_t a_hi = tmem_base + kColS + 64u * buf, a_lo = tmem_base + kColWlo + 64u * buf;
                         const uint32_t d_acc = tmem_base + kColAcc + 64u * buf;
                         constexpr uint32_t zstep = 1024 >> 4;
@@ -280,22 +302,32 @@ attn_kernel(const __grid_constant__ CUtensorMap mx1, const __grid_constant__ CUt
                     for (int c = 0; c < d.nb && ok; c++, g++) {
                         const uint32_t buf = g & 1;
                         const int s = ity % NYS;
-                        if (!mbar_wait_bounded_cluster(y_conv0 + 8u * s, (ity / NYS) & 1, p.wait_limit)) { ok = false; break; }
+                        if (!ATT_PROF_WAIT(2, mbar_wait_bounded_cluster(y_conv0 + 8u * s, (ity / NYS) & 1, p.wait_limit))) { ok = false; break; }
                         tc_fence_after();
-                        const uint32_t yt = y_base + s * Cfg::kYStage;
 #pragma unroll
                         for (int which = 0; which < NX; which++) {
-                            const uint32_t xt = x_base + which * 2 * Cfg::kXTile, ytw = yt + which * 2 * Cfg::kYTile;
+                            // descriptors differ from the base ones by constant offsets (in 16-byte units): nothing but
+                            // 64-bit adds per instruction, which matters because one thread issues them all
+                            const uint64_t xa_hi = dx0 + (uint64_t)((which * 2 * Cfg::kXTile) >> 4), xa_lo = xa_hi + (Cfg::kXTile >> 4);
+                            const uint64_t yb_hi = dy0 + (uint64_t)((s * Cfg::kYStage + which * 2 * Cfg::kYTile) >> 4);
+                            const uint64_t yb_lo = yb_hi + (Cfg::kYTile >> 4);
                             const uint32_t d_tm = tmem_base + (which == 0 ? kColS : kColDp) + 64u * buf;
-                            // lo*hi, hi*lo, hi*hi; the k-steps walk the 32-float k-blocks of the head dimension
-                            for (int pass = 0; pass < 3; pass++) {
-                                const uint32_t xa = xt + (pass == 0 ? Cfg::kXTile : 0), yb = ytw + (pass == 1 ? Cfg::kYTile : 0);
-                                for (int k = 0; k < ksteps1; k++) {
-                                    const uint64_t da = make_kmajor_sw128_desc(xa + (k >> 2) * 16384) + 2u * (k & 3);
-                                    const uint64_t db = make_kmajor_sw128_desc(yb + (k >> 2) * 4096) + 2u * (k & 3);
-                                    umma_tf32<2>(d_tm, da, db, idesc1, (pass == 0 && k == 0) ? 0u : 1u);
-                                }
-                            }
+                            // lo*hi, hi*lo, hi*hi; k-step k lies in k-block k / 4 (16 KB apart in X, 4 KB in Y), 32 bytes per step
+#pragma unroll
+                            for (int k = 0; k < 8; k++)
+                                if (k < ksteps1)
+                                    umma_tf32<2>(d_tm, xa_lo + (uint64_t)((k >> 2) * 1024 + (k & 3) * 2), yb_hi + (uint64_t)((k >> 2) * 256 + (k & 3) * 2),
+                                                 idesc1, k == 0 ? 0u : 1u);
+#pragma unroll
+                            for (int k = 0; k < 8; k++)
+                                if (k < ksteps1)
+                                    umma_tf32<2>(d_tm, xa_hi + (uint64_t)((k >> 2) * 1024 + (k & 3) * 2), yb_lo + (uint64_t)((k >> 2) * 256 + (k & 3) * 2),
+                                                 idesc1, 1);
+#pragma unroll
+                            for (int k = 0; k < 8; k++)
+                                if (k < ksteps1)
+                                    umma_tf32<2>(d_tm, xa_hi + (uint64_t)((k >> 2) * 1024 + (k & 3) * 2), yb_hi + (uint64_t)((k >> 2) * 256 + (k & 3) * 2),
+                                                 idesc1, 1);
                         }
                         umma_commit_pair(s_full0 + 8u * buf);
                         umma_commit_pair(y_empty0 + 8u * s);
@@ -306,6 +338,7 @@ attn_kernel(const __grid_constant__ CUtensorMap mx1, const __grid_constant__ CUt
                     if (ok && !second(g - 1)) ok = false;
                 }
                 if (!ok) atomicOr(p.status, ZNN_DEV_MMA_WAIT_EXPIRED);
+                ATT_PROF_END(0)
             }
         } else {
             // ---------------- converters: lo = x - (x with the 13 low mantissa bits cleared), next to each landed tile ----------------
@@ -333,7 +366,7 @@ attn_kernel(const __grid_constant__ CUtensorMap mx1, const __grid_constant__ CUt
             };
             auto wait_full = [&](uint32_t bar, uint32_t ph) -> bool {
                 bool got = true;
-                if (lane == 0) got = mbar_wait_bounded(bar, ph, p.wait_limit);
+                if (lane == 0) got = ATT_PROF_WAIT(15, mbar_wait_bounded(bar, ph, p.wait_limit));
                 return __shfl_sync(0xffffffffu, (int)got, 0) != 0;
             };
             auto done = [&](uint32_t leader_bar) {
@@ -343,6 +376,7 @@ attn_kernel(const __grid_constant__ CUtensorMap mx1, const __grid_constant__ CUt
             };
             bool got = true;
             uint32_t ity = 0, itz = 0, ul = 0;
+            ATT_PROF_T0
             for (int u = pair; u < total_units && got; u += npairs, ul++) {
                 const AttnUnit d = attn_unit<MODE>(p, u);
                 if (!(got = wait_full(x_full, ul & 1))) break;
@@ -368,6 +402,7 @@ attn_kernel(const __grid_constant__ CUtensorMap mx1, const __grid_constant__ CUt
                 }
             }
             if (!got && lane == 0) atomicOr(p.status, ZNN_DEV_TMA_WAIT_EXPIRED);
+            ATT_PROF_END(14)
         }
     } else {
         asm volatile("setmaxnreg.inc.sync.aligned.u32 232;");
@@ -380,11 +415,12 @@ attn_kernel(const __grid_constant__ CUtensorMap mx1, const __grid_constant__ CUt
             const int hs = p.hs;
             bool got = true;
             uint32_t g = 0;
-            auto wait_bar = [&](uint32_t bar, uint32_t ph) -> bool {
+            auto wait_bar = [&](uint32_t bar, uint32_t ph, int slot) -> bool {
                 bool ok = true;
-                if (lane == 0) ok = mbar_wait_bounded(bar, ph, p.wait_limit);
+                if (lane == 0) ok = ATT_PROF_WAIT(slot, mbar_wait_bounded(bar, ph, p.wait_limit));
                 return __shfl_sync(0xffffffffu, (int)ok, 0) != 0;
             };
+            ATT_PROF_T0
             for (int u = pair; u < total_units && got; u += npairs) {
                 const AttnUnit d = attn_unit<MODE>(p, u);
                 const int row = d.row0 + cta_rank * kRowsPerCta + rloc;       // absolute row inside the slice
@@ -402,7 +438,7 @@ attn_kernel(const __grid_constant__ CUtensorMap mx1, const __grid_constant__ CUt
                 // adds the accumulator of block gb (buffer gb & 1) into the registers
                 auto drain = [&](uint32_t gb, float factor) -> bool {
                     const uint32_t buf = gb & 1;
-                    if (!wait_bar(acc_full0 + 8u * buf, (gb >> 1) & 1)) return false;
+                    if (!wait_bar(acc_full0 + 8u * buf, (gb >> 1) & 1, 10)) return false;
                     tc_fence_after();
                     const uint32_t t0 = tmem_base + lane_sel + kColAcc + 64u * buf;
 #pragma unroll
@@ -423,7 +459,7 @@ attn_kernel(const __grid_constant__ CUtensorMap mx1, const __grid_constant__ CUt
                 for (int c = 0; c < d.nb; c++, g++) {
                     const uint32_t buf = g & 1;
                     const int col0 = (d.cb0 + c) * kColBlock;
-                    if (!(got = wait_bar(s_full0 + 8u * buf, (g >> 1) & 1))) break;
+                    if (!(got = wait_bar(s_full0 + 8u * buf, (g >> 1) & 1, 9))) break;
                     tc_fence_after();
                     const uint32_t ts = tmem_base + lane_sel + kColS + 64u * buf;
                     const uint32_t tl = tmem_base + lane_sel + kColWlo + 64u * buf;
@@ -553,6 +589,7 @@ attn_kernel(const __grid_constant__ CUtensorMap mx1, const __grid_constant__ CUt
                 }
             }
             if (!got && lane == 0) atomicOr(p.status, ZNN_DEV_EPI_WAIT_EXPIRED);
+            ATT_PROF_END(8)
         }
     }
 
@@ -643,6 +680,14 @@ static int make_attn_map(CUtensorMap* tm, const float* X, const AttnLayout& L, i
 }
 
 unsigned long long tc_wait_limit();
+
+int attn_profile_read(long long* out16)
+{
+    ZNN_CUDA_OK(cudaMemcpyFromSymbol(out16, g_attn_prof, 16 * sizeof(long long)));
+    long long zero[16] = {0};
+    ZNN_CUDA_OK(cudaMemcpyToSymbol(g_attn_prof, zero, sizeof(zero)));
+    return ZNN_OK;
+}
 
 template <int MODE>
 static int launch_attn(const float* X1, const float* X2, const float* Y1, const float* Y2, const float* Z, const AttnLayout& L,
@@ -736,6 +781,12 @@ static AttnParams attn_params(const AttnLayout& L, float scale)
 using namespace znn;
 
 extern "C" {
+
+int znn_debug_attn_profile(long long* out16)
+{
+    ZNN_REQUIRE(out16, "out16 is NULL");
+    return attn_profile_read(out16);
+}
 
 int znn_attn_fwd(const float* Q, const float* K, const float* V, float* O, float* LSE, int B, int nh, int T, int hs,
                  long long ld, long long stride_h, long long stride_b, float scale)
