@@ -37,8 +37,10 @@ int znn_gemm_profile_read(double* kernel_ms, long long* launches, double* flops)
 /* Role profile of the fused attention kernels, filled only by a build with -DZNN_ATTN_PROFILE (all zero otherwise):
  * cycles CTA pair 0's leader spent in each role's loop and inside each kind of wait, summed over the launches since
  * the last read: [0] MMA loop, [1] x_conv, [2] y_conv, [3] w_ready, [4] z_conv, [5] acc_empty waits; [8] transform loop,
- * [9] s_full, [10] acc_full waits; [12] TMA producer loop, [13] its waits; [14] converter loop, [15] its waits. */
-int znn_debug_attn_profile(long long* out16);
+ * [9] s_full, [10] acc_full waits; [12] TMA producer loop, [13] its waits; [14] converter loop, [15] its waits;
+ * [16] converter proxy fence, [17] fence + arrival; transform: [18] score load, [19] W store + hand-off, [20] accumulator drain,
+ * [21] load-to-hand-off of one block.  32 values. */
+int znn_debug_attn_profile(long long* out32);
 
 /* ---- test hooks ---- */
 /* SM cycles a GEMM role waits on an mbarrier before it gives up, sets a ZNN_DEV_*_WAIT_EXPIRED bit in the device status

@@ -50,8 +50,8 @@ struct AttnParams {
     unsigned long long wait_limit;
 };
 
-constexpr int kAttThreads = 384;   // warp 0 TMA, warp 1 MMA + TMEM, warps 2-7 converters, warps 8-11 transform
-constexpr int kAttConvWarps = 6, kAttConvWarp0 = 2, kAttXfWarp0 = 8, kAttXfWarps = 4;
+constexpr int kAttThreads = 512;   // warp 0 TMA, warp 1 MMA + TMEM, warps 2-7 converters, warps 8-15 transform
+constexpr int kAttConvWarps = 6, kAttConvWarp0 = 2, kAttXfWarp0 = 8, kAttXfWarps = 8;
 constexpr int kRowsPerCta = 128, kColBlock = 64;
 
 template <int MODE>
@@ -66,7 +66,7 @@ struct AttnCfg {
     static constexpr int NYS = NX == 2 ? 2 : 4;
     static constexpr int NZS = NX == 2 ? 2 : 4;
     static constexpr int kBarOff = kXBytes + NYS * kYStage + NZS * kZStage;
-    static constexpr int kSmemBytes = kBarOff + 1024 /*alignment*/ + 512 /*barriers*/;
+    static constexpr int kSmemBytes = kBarOff + 1024 /*alignment*/ + 512 /*barriers*/ + (MODE == ATT_FWD ? 2048 : 0) /*row-maximum exchange*/;
     static_assert(kSmemBytes <= 232448, "shared memory budget");
 };
 
@@ -103,12 +103,25 @@ __device__ __forceinline__ AttnUnit attn_unit(const AttnParams& p, int u)
 // role, the cycles spent inside each kind of wait and the cycles of the whole role loop into g_attn_prof, which
 // znn_debug_attn_profile reads: [0] MMA loop, [1] x_conv, [2] y_conv, [3] w_ready, [4] z_conv, [5] acc_empty;
 // [8] transform loop, [9] s_full, [10] acc_full; [12] producer loop, [13] its waits; [14] converter loop, [15] its waits.
-__device__ long long g_attn_prof[16];
+__device__ long long g_attn_prof[32];
 #ifdef ZNN_ATTN_PROFILE
 #define ATT_PROF_T0 const long long prof_t0 = clock64();
-#define ATT_PROF_WAIT(slot, expr) [&]() { const long long t_ = clock64(); const bool r_ = (expr); if (prof_on) g_attn_prof[slot] += clock64() - t_; return r_; }()
-#define ATT_PROF_END(slot) if (prof_on) g_attn_prof[slot] += clock64() - prof_t0;
+#define ATT_PROF_WAIT(slot, expr) [&]() { const long long t_ = clock64(); const bool r_ = (expr); prof_acc[slot] += clock64() - t_; return r_; }()
+#define ATT_PROF_END(slot)                                                                         \
+    if (prof_on) {                                                                                 \
+        prof_acc[slot] += clock64() - prof_t0;                                                     \
+        for (int i_ = 0; i_ < 32; i_++)                                                            \
+            if (prof_acc[i_]) atomicAdd((unsigned long long*)&g_attn_prof[i_], (unsigned long long)prof_acc[i_]); \
+    }
+#define ATT_PROF_MARK const long long prof_m = clock64();
+#define ATT_PROF_ADD(slot) prof_acc[slot] += clock64() - prof_m;
+#define ATT_PROF_MARK2(name) const long long name = clock64();
+#define ATT_PROF_ADD2(slot, name) prof_acc[slot] += clock64() - name;
 #else
+#define ATT_PROF_MARK
+#define ATT_PROF_ADD(slot)
+#define ATT_PROF_MARK2(name)
+#define ATT_PROF_ADD2(slot, name)
 #define ATT_PROF_T0
 #define ATT_PROF_WAIT(slot, expr) (expr)
 #define ATT_PROF_END(slot)
@@ -155,7 +168,9 @@ attn_kernel(const __grid_constant__ CUtensorMap mx1, const __grid_constant__ CUt
     volatile uint32_t* abort_slot = tmem_slot + 1;
     const uint32_t abort_slot_addr = tmem_slot_addr + 4;
 
-    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    // the warp index through a shuffle: the compiler then knows it is the same in all lanes, and the code of the MMA
+    // warp below (executed by all its lanes, with one elected lane issuing) stays on the uniform datapath
+    const int warp = __shfl_sync(0xffffffffu, (int)(threadIdx.x >> 5), 0), lane = threadIdx.x & 31;
     const int cta_rank = (int)cluster_ctarank();
     const bool leader = (cta_rank == 0);
     const int pair = blockIdx.x >> 1, npairs = gridDim.x >> 1;
@@ -163,6 +178,9 @@ attn_kernel(const __grid_constant__ CUtensorMap mx1, const __grid_constant__ CUt
     const int kbh = p.hs >> 5;                    // 32-float k-blocks across the head dimension (1 or 2)
 #ifdef ZNN_ATTN_PROFILE
     const bool prof_on = (pair == 0 && cta_rank == 0 && lane == 0 && (warp <= 2 || warp == kAttXfWarp0));
+    long long prof_acc[32];      // in registers; written once at the end of the role
+#pragma unroll
+    for (int i = 0; i < 32; i++) prof_acc[i] = 0;
 #endif
 
     if (threadIdx.x == 0) {
@@ -204,7 +222,7 @@ attn_kernel(const __grid_constant__ CUtensorMap mx1, const __grid_constant__ CUt
     const bool aborted = (*abort_slot != 0);
 
     if (warp < kAttXfWarp0) {
-        asm volatile("setmaxnreg.dec.sync.aligned.u32 64;");
+        asm volatile("setmaxnreg.dec.sync.aligned.u32 80;");
         if (aborted) {
         } else if (warp == 0) {
             // ---------------- TMA producer ----------------
@@ -263,7 +281,17 @@ attn_kernel(const __grid_constant__ CUtensorMap mx1, const __grid_constant__ CUt
             }
         } else if (warp == 1) {
             // ---------------- MMA issuer (leader CTA only) ----------------
-            if (lane == 0 && leader) {
+            // All 32 lanes run the loop and compute the (warp-uniform) descriptors; lane 0 polls the barriers and one
+            // elected lane issues the instructions.  Descriptors computed by a single diverged thread instead gave wrong
+            // products once the instructions followed each other closely (measured: correct again with a pause
+            // between them), and cost about twice the issue time.
+            if (leader) {
+                const bool elected = elect_one();
+                auto warp_wait = [&](uint32_t bar, uint32_t parity) -> bool {
+                    bool r = true;
+                    if (lane == 0) r = mbar_wait_bounded_tight(bar, parity, p.wait_limit);
+                    return __shfl_sync(0xffffffffu, (int)r, 0) != 0;
+                };
                 constexpr uint32_t idesc1 = make_tf32_idesc_major(256, 64, false, false);
                 constexpr uint32_t idesc2 = make_tf32_idesc_major(256, 64, false, true);
                 bool ok = true;
@@ -274,36 +302,42 @@ attn_kernel(const __grid_constant__ CUtensorMap mx1, const __grid_constant__ CUt
                 ATT_PROF_T0
                 for (int u = pair; u < total_units && ok; u += npairs, ul++) {
                     const AttnUnit d = attn_unit<MODE>(p, u);
-                    if (!ATT_PROF_WAIT(1, mbar_wait_bounded_cluster(x_conv, ul & 1, p.wait_limit))) { ok = false; break; }
+                    if (!ATT_PROF_WAIT(1, warp_wait(x_conv, ul & 1))) { ok = false; break; }
                     tc_fence_after();
                     // second product of the block issued `gp` blocks ago (program order: P1(c), P2(c-1), P1(c+1), ...)
                     auto second = [&](uint32_t gb) -> bool {
                         const uint32_t buf = gb & 1, ph = (gb >> 1) & 1;
-                        if (!ATT_PROF_WAIT(3, mbar_wait_bounded_cluster(w_ready0 + 8u * buf, ph, p.wait_limit))) return false;
+                        if (!ATT_PROF_WAIT(3, warp_wait(w_ready0 + 8u * buf, ph))) return false;
                         const int s = itz % NZS;
-                        if (!ATT_PROF_WAIT(4, mbar_wait_bounded_cluster(z_conv0 + 8u * s, (itz / NZS) & 1, p.wait_limit))) return false;
-                        if (!ATT_PROF_WAIT(5, mbar_wait_bounded_cluster(acc_empty0 + 8u * buf, ph ^ 1, p.wait_limit))) return false;
+                        if (!ATT_PROF_WAIT(4, warp_wait(z_conv0 + 8u * s, (itz / NZS) & 1))) return false;
+                        if (!ATT_PROF_WAIT(5, warp_wait(acc_empty0 + 8u * buf, ph ^ 1))) return false;
                         tc_fence_after();
                         const uint64_t z_hi = dz0 + (uint64_t)((s * Cfg::kZStage) >> 4), z_lo = z_hi + (Cfg::kZTile >> 4);
                         const uint32_t a_hi = tmem_base + kColS + 64u * buf, a_lo = tmem_base + kColWlo + 64u * buf;
                         const uint32_t d_acc = tmem_base + kColAcc + 64u * buf;
                         constexpr uint32_t zstep = 1024 >> 4;
+                        ATT_PROF_MARK
+                        if (elected) {
 #pragma unroll
-                        for (int k = 0; k < 8; k++) umma_tf32_ts_pair(d_acc, a_lo + 8u * k, z_hi + zstep * k, idesc2, k == 0 ? 0u : 1u);
+                            for (int k = 0; k < 8; k++) umma_tf32_ts_pair(d_acc, a_lo + 8u * k, z_hi + zstep * k, idesc2, k == 0 ? 0u : 1u);
 #pragma unroll
-                        for (int k = 0; k < 8; k++) umma_tf32_ts_pair(d_acc, a_hi + 8u * k, z_lo + zstep * k, idesc2, 1);
+                            for (int k = 0; k < 8; k++) umma_tf32_ts_pair(d_acc, a_hi + 8u * k, z_lo + zstep * k, idesc2, 1);
 #pragma unroll
-                        for (int k = 0; k < 8; k++) umma_tf32_ts_pair(d_acc, a_hi + 8u * k, z_hi + zstep * k, idesc2, 1);
-                        umma_commit_pair(acc_full0 + 8u * buf);
-                        umma_commit_pair(z_empty0 + 8u * s);
+                            for (int k = 0; k < 8; k++) umma_tf32_ts_pair(d_acc, a_hi + 8u * k, z_hi + zstep * k, idesc2, 1);
+                            umma_commit_pair(acc_full0 + 8u * buf);
+                            umma_commit_pair(z_empty0 + 8u * s);
+                        }
+                        __syncwarp();
+                        ATT_PROF_ADD(7)
                         itz++;
                         return true;
                     };
                     for (int c = 0; c < d.nb && ok; c++, g++) {
                         const uint32_t buf = g & 1;
                         const int s = ity % NYS;
-                        if (!ATT_PROF_WAIT(2, mbar_wait_bounded_cluster(y_conv0 + 8u * s, (ity / NYS) & 1, p.wait_limit))) { ok = false; break; }
+                        if (!ATT_PROF_WAIT(2, warp_wait(y_conv0 + 8u * s, (ity / NYS) & 1))) { ok = false; break; }
                         tc_fence_after();
+                        ATT_PROF_MARK
 #pragma unroll
                         for (int which = 0; which < NX; which++) {
                             // descriptors differ from the base ones by constant offsets (in 16-byte units): nothing but
@@ -312,6 +346,7 @@ attn_kernel(const __grid_constant__ CUtensorMap mx1, const __grid_constant__ CUt
                             const uint64_t yb_hi = dy0 + (uint64_t)((s * Cfg::kYStage + which * 2 * Cfg::kYTile) >> 4);
                             const uint64_t yb_lo = yb_hi + (Cfg::kYTile >> 4);
                             const uint32_t d_tm = tmem_base + (which == 0 ? kColS : kColDp) + 64u * buf;
+                            if (!elected) continue;
                             // lo*hi, hi*lo, hi*hi; k-step k lies in k-block k / 4 (16 KB apart in X, 4 KB in Y), 32 bytes per step
 #pragma unroll
                             for (int k = 0; k < 8; k++)
@@ -329,15 +364,19 @@ attn_kernel(const __grid_constant__ CUtensorMap mx1, const __grid_constant__ CUt
                                     umma_tf32<2>(d_tm, xa_hi + (uint64_t)((k >> 2) * 1024 + (k & 3) * 2), yb_hi + (uint64_t)((k >> 2) * 256 + (k & 3) * 2),
                                                  idesc1, 1);
                         }
-                        umma_commit_pair(s_full0 + 8u * buf);
-                        umma_commit_pair(y_empty0 + 8u * s);
+                        if (elected) {
+                            umma_commit_pair(s_full0 + 8u * buf);
+                            umma_commit_pair(y_empty0 + 8u * s);
+                            if (c == d.nb - 1) umma_commit_pair(x_empty);   // the row operands are free once these products are done
+                        }
+                        __syncwarp();
+                        ATT_PROF_ADD(6)
                         ity++;
-                        if (c == d.nb - 1) umma_commit_pair(x_empty);   // the row operands are free once these products are done
                         if (c >= 1 && !second(g - 1)) { ok = false; break; }
                     }
                     if (ok && !second(g - 1)) ok = false;
                 }
-                if (!ok) atomicOr(p.status, ZNN_DEV_MMA_WAIT_EXPIRED);
+                if (!ok && lane == 0) atomicOr(p.status, ZNN_DEV_MMA_WAIT_EXPIRED);
                 ATT_PROF_END(0)
             }
         } else {
@@ -366,13 +405,16 @@ attn_kernel(const __grid_constant__ CUtensorMap mx1, const __grid_constant__ CUt
             };
             auto wait_full = [&](uint32_t bar, uint32_t ph) -> bool {
                 bool got = true;
-                if (lane == 0) got = ATT_PROF_WAIT(15, mbar_wait_bounded(bar, ph, p.wait_limit));
+                if (lane == 0) got = ATT_PROF_WAIT(15, mbar_wait_bounded_tight(bar, ph, p.wait_limit));
                 return __shfl_sync(0xffffffffu, (int)got, 0) != 0;
             };
             auto done = [&](uint32_t leader_bar) {
+                ATT_PROF_MARK2(pf)
                 asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+                ATT_PROF_ADD2(16, pf)
                 __syncwarp();
                 if (lane == 0) mbar_arrive_remote(leader_bar);
+                ATT_PROF_ADD2(17, pf)
             };
             bool got = true;
             uint32_t ity = 0, itz = 0, ul = 0;
@@ -405,186 +447,192 @@ attn_kernel(const __grid_constant__ CUtensorMap mx1, const __grid_constant__ CUt
             ATT_PROF_END(14)
         }
     } else {
-        asm volatile("setmaxnreg.inc.sync.aligned.u32 232;");
+        asm volatile("setmaxnreg.inc.sync.aligned.u32 168;");
         if (!aborted) {
-            // ---------------- transform warps: one thread per row of this CTA's 128 ----------------
-            const int q = warp & 3;
+            // ---------------- transform warps: two threads per row of this CTA's 128, 32 columns each ----------------
+            // Warp w works on tensor-memory lanes 32 * (w & 3) .. + 31 (the quarter a warp may access) and on columns
+            // 32 * half .. + 31 of every 64-wide block (S, dP, W and the accumulator alike), half = (w - 8) / 4.
+            const int q = warp & 3, half = (warp - kAttXfWarp0) >> 2;
             const int rloc = q * 32 + lane;
             const uint32_t lane_sel = (uint32_t)(q * 32) << 16;
+            const uint32_t col_sel = 32u * (uint32_t)half;
             const uint32_t w_ready_l0 = mapa_shared(w_ready0, 0), acc_empty_l0 = mapa_shared(acc_empty0, 0);
             const int hs = p.hs;
+            // forward: the two threads of a row exchange their block maxima (and, at the end, their sums) here
+            float* const exch = reinterpret_cast<float*>(smem_gen + Cfg::kBarOff + 512);   // [2 parities][2 halves][128 rows]
             bool got = true;
             uint32_t g = 0;
             auto wait_bar = [&](uint32_t bar, uint32_t ph, int slot) -> bool {
                 bool ok = true;
-                if (lane == 0) ok = ATT_PROF_WAIT(slot, mbar_wait_bounded(bar, ph, p.wait_limit));
+                if (lane == 0) ok = ATT_PROF_WAIT(slot, mbar_wait_bounded_tight(bar, ph, p.wait_limit));
                 return __shfl_sync(0xffffffffu, (int)ok, 0) != 0;
             };
+            auto pair_sync = [&]() { asm volatile("bar.sync %0, 64;" ::"r"(1 + q) : "memory"); };   // the two warps of a lane quarter
             ATT_PROF_T0
-            for (int u = pair; u < total_units && got; u += npairs) {
+            // After an expired wait (got = false) a warp keeps walking its blocks without touching barriers or tensor
+            // memory, so that the pair_sync calls of the forward stay matched with its partner warp's.
+            for (int u = pair; u < total_units; u += npairs) {
                 const AttnUnit d = attn_unit<MODE>(p, u);
                 const int row = d.row0 + cta_rank * kRowsPerCta + rloc;       // absolute row inside the slice
                 const bool row_ok = row < p.T;
                 const size_t stat_off = (size_t)d.slice * p.T;
-                float acc[64];
+                float acc[32];
 #pragma unroll
-                for (int i = 0; i < 64; i++) acc[i] = 0.0f;
+                for (int i = 0; i < 32; i++) acc[i] = 0.0f;
                 float m_run = -CUDART_INF_F, l_run = 0.0f, corr_prev = 1.0f;   // forward
                 float lse_r = 0.0f, d_r = 0.0f;                               // dQ: this row's statistics
                 if (MODE == ATT_BWD_Q && row_ok) {
                     lse_r = p.lse[stat_off + row];
                     d_r = p.dvec[stat_off + row];
                 }
-                // adds the accumulator of block gb (buffer gb & 1) into the registers
+                // adds this thread's 32 columns of block gb's accumulator (buffer gb & 1) into the registers
                 auto drain = [&](uint32_t gb, float factor) -> bool {
                     const uint32_t buf = gb & 1;
                     if (!wait_bar(acc_full0 + 8u * buf, (gb >> 1) & 1, 10)) return false;
+                    ATT_PROF_MARK2(pd)
                     tc_fence_after();
-                    const uint32_t t0 = tmem_base + lane_sel + kColAcc + 64u * buf;
+                    float v[32];
+                    tmem_ld_32x32(tmem_base + lane_sel + kColAcc + 64u * buf + col_sel, v);
 #pragma unroll
-                    for (int j = 0; j < 2; j++) {
-                        float v[32];
-                        tmem_ld_32x32(t0 + 32u * j, v);
-#pragma unroll
-                        for (int i = 0; i < 32; i++) {
-                            if (MODE == ATT_FWD) acc[32 * j + i] = acc[32 * j + i] * factor + v[i];
-                            else acc[32 * j + i] += v[i];
-                        }
+                    for (int i = 0; i < 32; i++) {
+                        if (MODE == ATT_FWD) acc[i] = acc[i] * factor + v[i];
+                        else acc[i] += v[i];
                     }
                     tc_fence_before();
                     __syncwarp();
                     if (lane == 0) mbar_arrive_remote(acc_empty_l0 + 8u * buf);
+                    ATT_PROF_ADD2(20, pd)
                     return true;
                 };
                 for (int c = 0; c < d.nb; c++, g++) {
                     const uint32_t buf = g & 1;
-                    const int col0 = (d.cb0 + c) * kColBlock;
-                    if (!(got = wait_bar(s_full0 + 8u * buf, (g >> 1) & 1, 9))) break;
+                    const int col0 = (d.cb0 + c) * kColBlock + 32 * half;     // this thread's first column of the block
+                    if (got) got = wait_bar(s_full0 + 8u * buf, (g >> 1) & 1, 9);
+                    if (!got) {
+                        if (MODE == ATT_FWD) pair_sync();
+                        continue;
+                    }
+                    ATT_PROF_MARK2(pt)
                     tc_fence_after();
-                    const uint32_t ts = tmem_base + lane_sel + kColS + 64u * buf;
-                    const uint32_t tl = tmem_base + lane_sel + kColWlo + 64u * buf;
-                    const uint32_t tdp = tmem_base + lane_sel + kColDp + 64u * buf;
+                    const uint32_t ts = tmem_base + lane_sel + kColS + 64u * buf + col_sel;
+                    const uint32_t tl = tmem_base + lane_sel + kColWlo + 64u * buf + col_sel;
+                    const uint32_t tdp = tmem_base + lane_sel + kColDp + 64u * buf + col_sel;
                     float corr = 1.0f;
+                    float s[32];
+                    tmem_ld_32x32(ts, s);
+                    ATT_PROF_ADD2(18, pt)
+                    uint32_t hi[32], lo[32];
                     if (MODE == ATT_FWD) {
-                        float s[64];
-                        tmem_ld_32x32(ts, *reinterpret_cast<float(*)[32]>(&s[0]));
-                        tmem_ld_32x32(ts + 32u, *reinterpret_cast<float(*)[32]>(&s[32]));
                         float mx = m_run;
 #pragma unroll
-                        for (int j = 0; j < 64; j++) {
+                        for (int j = 0; j < 32; j++) {
                             const float v = (col0 + j <= row) ? s[j] * p.c2 : -CUDART_INF_F;
                             s[j] = v;
                             mx = fmaxf(mx, v);
                         }
+                        // the row's maximum over both halves of the block
+                        float* const ex = exch + (g & 1) * 256;
+                        ex[half * 128 + rloc] = mx;
+                        pair_sync();
+                        mx = fmaxf(mx, ex[(half ^ 1) * 128 + rloc]);
                         corr = fast_exp2(m_run - mx);
                         float sum = 0.0f;
 #pragma unroll
-                        for (int h2 = 0; h2 < 2; h2++) {
-                            uint32_t hi[32], lo[32];
+                        for (int j = 0; j < 32; j++) {
+                            const float pv = fast_exp2(s[j] - mx);
+                            sum += pv;
+                            hi[j] = __float_as_uint(pv) & 0xFFFFE000u;
+                            lo[j] = __float_as_uint(pv - __uint_as_float(hi[j]));
+                        }
+                        l_run = l_run * corr + sum;     // this thread's columns only; the halves are added at the end
+                        m_run = mx;
+                    } else if (MODE == ATT_BWD_V) {
+                        // W = P^T: rows are keys, columns queries; statistics per column
 #pragma unroll
-                            for (int j = 0; j < 32; j++) {
-                                const float pv = fast_exp2(s[32 * h2 + j] - mx);
-                                sum += pv;
+                        for (int j4 = 0; j4 < 8; j4++) {
+                            const int qc = col0 + 4 * j4;
+                            float4 l4 = make_float4(0.f, 0.f, 0.f, 0.f);
+                            if (qc < p.T) l4 = *reinterpret_cast<const float4*>(p.lse + stat_off + qc);
+                            const float ls[4] = {l4.x, l4.y, l4.z, l4.w};
+#pragma unroll
+                            for (int e = 0; e < 4; e++) {
+                                const int j = 4 * j4 + e;
+                                const bool vis = (row <= qc + e) && (qc + e < p.T);
+                                const float pv = vis ? fast_exp2(fmaf(s[j], p.c2, -ls[e])) : 0.0f;
                                 hi[j] = __float_as_uint(pv) & 0xFFFFE000u;
                                 lo[j] = __float_as_uint(pv - __uint_as_float(hi[j]));
                             }
-                            tmem_st_32x32(ts + 32u * h2, hi);
-                            tmem_st_32x32(tl + 32u * h2, lo);
                         }
-                        l_run = l_run * corr + sum;
-                        m_run = mx;
                     } else {
+                        float dp[32];
+                        tmem_ld_32x32(tdp, dp);
+                        if (MODE == ATT_BWD_Q) {
 #pragma unroll
-                        for (int h2 = 0; h2 < 2; h2++) {
-                            float s[32];
-                            tmem_ld_32x32(ts + 32u * h2, s);
-                            uint32_t hi[32], lo[32];
-                            if (MODE == ATT_BWD_V) {
-                                // W = P^T: rows are keys, columns queries; statistics per column
+                            for (int j = 0; j < 32; j++) {
+                                const bool vis = (col0 + j <= row);
+                                const float pv = vis ? fast_exp2(fmaf(s[j], p.c2, -lse_r)) : 0.0f;
+                                const float ds = (pv * (dp[j] - d_r)) * p.scale;
+                                hi[j] = __float_as_uint(ds) & 0xFFFFE000u;
+                                lo[j] = __float_as_uint(ds - __uint_as_float(hi[j]));
+                            }
+                        } else {   // ATT_BWD_K
 #pragma unroll
-                                for (int j4 = 0; j4 < 8; j4++) {
-                                    const int qc = col0 + 32 * h2 + 4 * j4;
-                                    float4 l4 = make_float4(0.f, 0.f, 0.f, 0.f);
-                                    if (qc < p.T) l4 = *reinterpret_cast<const float4*>(p.lse + stat_off + qc);
-                                    const float ls[4] = {l4.x, l4.y, l4.z, l4.w};
-#pragma unroll
-                                    for (int e = 0; e < 4; e++) {
-                                        const int j = 4 * j4 + e;
-                                        const bool vis = (row <= qc + e) && (qc + e < p.T);
-                                        const float pv = vis ? fast_exp2(fmaf(s[j], p.c2, -ls[e])) : 0.0f;
-                                        hi[j] = __float_as_uint(pv) & 0xFFFFE000u;
-                                        lo[j] = __float_as_uint(pv - __uint_as_float(hi[j]));
-                                    }
+                            for (int j4 = 0; j4 < 8; j4++) {
+                                const int qc = col0 + 4 * j4;
+                                float4 l4 = make_float4(0.f, 0.f, 0.f, 0.f), d4 = l4;
+                                if (qc < p.T) {
+                                    l4 = *reinterpret_cast<const float4*>(p.lse + stat_off + qc);
+                                    d4 = *reinterpret_cast<const float4*>(p.dvec + stat_off + qc);
                                 }
-                            } else {
-                                float dp[32];
-                                tmem_ld_32x32(tdp + 32u * h2, dp);
-                                if (MODE == ATT_BWD_Q) {
+                                const float ls[4] = {l4.x, l4.y, l4.z, l4.w}, dd[4] = {d4.x, d4.y, d4.z, d4.w};
 #pragma unroll
-                                    for (int j = 0; j < 32; j++) {
-                                        const bool vis = (col0 + 32 * h2 + j <= row);
-                                        const float pv = vis ? fast_exp2(fmaf(s[j], p.c2, -lse_r)) : 0.0f;
-                                        const float ds = (pv * (dp[j] - d_r)) * p.scale;
-                                        hi[j] = __float_as_uint(ds) & 0xFFFFE000u;
-                                        lo[j] = __float_as_uint(ds - __uint_as_float(hi[j]));
-                                    }
-                                } else {   // ATT_BWD_K
-#pragma unroll
-                                    for (int j4 = 0; j4 < 8; j4++) {
-                                        const int qc = col0 + 32 * h2 + 4 * j4;
-                                        float4 l4 = make_float4(0.f, 0.f, 0.f, 0.f), d4 = l4;
-                                        if (qc < p.T) {
-                                            l4 = *reinterpret_cast<const float4*>(p.lse + stat_off + qc);
-                                            d4 = *reinterpret_cast<const float4*>(p.dvec + stat_off + qc);
-                                        }
-                                        const float ls[4] = {l4.x, l4.y, l4.z, l4.w}, dd[4] = {d4.x, d4.y, d4.z, d4.w};
-#pragma unroll
-                                        for (int e = 0; e < 4; e++) {
-                                            const int j = 4 * j4 + e;
-                                            const bool vis = (row <= qc + e) && (qc + e < p.T);
-                                            const float pv = vis ? fast_exp2(fmaf(s[j], p.c2, -ls[e])) : 0.0f;
-                                            const float ds = (pv * (dp[j] - dd[e])) * p.scale;
-                                            hi[j] = __float_as_uint(ds) & 0xFFFFE000u;
-                                            lo[j] = __float_as_uint(ds - __uint_as_float(hi[j]));
-                                        }
-                                    }
+                                for (int e = 0; e < 4; e++) {
+                                    const int j = 4 * j4 + e;
+                                    const bool vis = (row <= qc + e) && (qc + e < p.T);
+                                    const float pv = vis ? fast_exp2(fmaf(s[j], p.c2, -ls[e])) : 0.0f;
+                                    const float ds = (pv * (dp[j] - dd[e])) * p.scale;
+                                    hi[j] = __float_as_uint(ds) & 0xFFFFE000u;
+                                    lo[j] = __float_as_uint(ds - __uint_as_float(hi[j]));
                                 }
                             }
-                            tmem_st_32x32(ts + 32u * h2, hi);
-                            tmem_st_32x32(tl + 32u * h2, lo);
                         }
                     }
+                    ATT_PROF_MARK2(ps)
+                    tmem_st_32x32(ts, hi);
+                    tmem_st_32x32(tl, lo);
                     tmem_st_wait();
                     tc_fence_before();
                     __syncwarp();
                     if (lane == 0) mbar_arrive_remote(w_ready_l0 + 8u * buf);
+                    ATT_PROF_ADD2(19, ps)
+                    ATT_PROF_ADD2(21, pt)
                     // the previous block's second product has had this block's transform time to finish
-                    if (c >= 1 && !(got = drain(g - 1, corr_prev))) break;
+                    if (c >= 1) got = drain(g - 1, corr_prev);
                     corr_prev = corr;
                 }
-                if (!got) break;
-                if (!(got = drain(g - 1, corr_prev))) break;
+                if (got) got = drain(g - 1, corr_prev);
                 // ---- the rows leave: O = acc / l and the row's log-sum-exp, or the gradient rows ----
-                if (row_ok) {
-                    float* dst = p.out + (size_t)d.b * p.stride_b + (size_t)d.h * p.stride_h + (size_t)row * p.ld;
-                    if (MODE == ATT_FWD) {
-                        const float inv = 1.0f / l_run;
-                        p.lse[stat_off + row] = m_run + log2f(l_run);
+                float inv = 1.0f;
+                if (MODE == ATT_FWD) {
+                    float* const ex = exch + (g & 1) * 256;
+                    ex[half * 128 + rloc] = l_run;
+                    pair_sync();
+                    const float l_all = l_run + ex[(half ^ 1) * 128 + rloc];
+                    inv = 1.0f / l_all;
+                    if (row_ok && got && half == 0) p.lse[stat_off + row] = m_run + log2f(l_all);
+                    pair_sync();      // the slot may be rewritten by the next unit's first block (same parity)
+                }
+                if (row_ok && got) {
+                    float* dst = p.out + (size_t)d.b * p.stride_b + (size_t)d.h * p.stride_h + (size_t)row * p.ld + 32 * half;
 #pragma unroll
-                        for (int i = 0; i < 64; i += 4)
-                            if (i < hs)
-                                *reinterpret_cast<float4*>(dst + i) = make_float4(acc[i] * inv, acc[i + 1] * inv, acc[i + 2] * inv, acc[i + 3] * inv);
-                    } else {
-#pragma unroll
-                        for (int i = 0; i < 64; i += 4) {
-                            if (i >= hs) continue;
-                            float4 o = make_float4(acc[i], acc[i + 1], acc[i + 2], acc[i + 3]);
-                            if (p.accumulate) {
-                                const float4 old = *reinterpret_cast<const float4*>(dst + i);
-                                o.x += old.x; o.y += old.y; o.z += old.z; o.w += old.w;
-                            }
-                            *reinterpret_cast<float4*>(dst + i) = o;
+                    for (int i = 0; i < 32; i += 4) {
+                        if (32 * half + i >= hs) continue;
+                        float4 o = make_float4(acc[i] * inv, acc[i + 1] * inv, acc[i + 2] * inv, acc[i + 3] * inv);
+                        if (MODE != ATT_FWD && p.accumulate) {
+                            const float4 old = *reinterpret_cast<const float4*>(dst + i);
+                            o.x += old.x; o.y += old.y; o.z += old.z; o.w += old.w;
                         }
+                        *reinterpret_cast<float4*>(dst + i) = o;
                     }
                 }
             }
@@ -681,10 +729,10 @@ static int make_attn_map(CUtensorMap* tm, const float* X, const AttnLayout& L, i
 
 unsigned long long tc_wait_limit();
 
-int attn_profile_read(long long* out16)
+int attn_profile_read(long long* out32)
 {
-    ZNN_CUDA_OK(cudaMemcpyFromSymbol(out16, g_attn_prof, 16 * sizeof(long long)));
-    long long zero[16] = {0};
+    ZNN_CUDA_OK(cudaMemcpyFromSymbol(out32, g_attn_prof, 32 * sizeof(long long)));
+    long long zero[32] = {0};
     ZNN_CUDA_OK(cudaMemcpyToSymbol(g_attn_prof, zero, sizeof(zero)));
     return ZNN_OK;
 }
@@ -782,10 +830,10 @@ using namespace znn;
 
 extern "C" {
 
-int znn_debug_attn_profile(long long* out16)
+int znn_debug_attn_profile(long long* out32)
 {
-    ZNN_REQUIRE(out16, "out16 is NULL");
-    return attn_profile_read(out16);
+    ZNN_REQUIRE(out32, "out32 is NULL");
+    return attn_profile_read(out32);
 }
 
 int znn_attn_fwd(const float* Q, const float* K, const float* V, float* O, float* LSE, int B, int nh, int T, int hs,

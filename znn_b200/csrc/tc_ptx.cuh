@@ -267,6 +267,32 @@ __host__ __device__ constexpr uint32_t make_tf32_idesc_major(int mma_m, int mma_
     return make_tf32_idesc(mma_m, mma_n) | ((a_mn ? 1u : 0u) << 15) | ((b_mn ? 1u : 0u) << 16);
 }
 
+// The same wait without the back-off between polls, for roles on a latency-critical path with few warps per SM (each
+// poll may still be parked by the hardware until the phase completes).  Bounded like the others.
+__device__ __forceinline__ bool mbar_wait_bounded_tight(uint32_t bar, uint32_t parity, uint64_t limit = kWaitLimitCycles)
+{
+    if (mbar_try_wait(bar, parity)) return true;
+    const uint64_t t0 = wait_clock();
+    for (;;) {
+#pragma unroll 1
+        for (int i = 0; i < 256; i++)
+            if (mbar_try_wait(bar, parity)) return true;
+        if (wait_clock() - t0 > limit) return false;
+    }
+}
+
+// One lane of the (converged) warp; the same lane every time it is asked for.
+__device__ __forceinline__ bool elect_one()
+{
+    uint32_t pred = 0;
+    asm volatile(
+        "{\n\t.reg .b32 rx;\n\t.reg .pred px;\n\t"
+        "elect.sync rx|px, 0xffffffff;\n\t"
+        "selp.u32 %0, 1, 0, px;\n\t}"
+        : "=r"(pred));
+    return pred != 0;
+}
+
 // 4-d tiled TMA load (no multicast); the box lands in this CTA's shared memory and signals this CTA's mbarrier.
 __device__ __forceinline__ void tma_load_4d(uint32_t dst, const CUtensorMap* tm, uint32_t bar, int c0, int c1, int c2, int c3)
 {
