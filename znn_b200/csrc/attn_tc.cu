@@ -9,20 +9,24 @@
 // One kernel template, four instantiations.  A work unit is 256 "rows" of one (batch, head) slice, held by a CTA pair
 // (cta_group::2, 128 rows per CTA), against a stream of 64-wide "column" blocks:
 //
-//   forward   rows = queries, columns = keys     S = Q.K^T         P = softmax (online)        O   += P.V
-//   dQ        rows = queries, columns = keys     S = Q.K^T, dP = dO.V^T   dS = P o (dP - D)    dQ  += dS.K
-//   dK        rows = keys,    columns = queries  S^T = K.Q^T, dP^T = V.dO^T  dS^T               dK  += dS^T.Q
-//   dV        rows = keys,    columns = queries  S^T = K.Q^T        P^T                         dV  += P^T.dO
+//   forward   rows = queries, columns = keys     S = Q.K^T                   P = softmax (online)     O  += P.V
+//   dQ        rows = queries, columns = keys     S = Q.K^T, dP = dO.V^T      dS = P o (dP - D)        dQ += dS.K
+//   dK        rows = keys,    columns = queries  S^T = K.Q^T, dP^T = V.dO^T  dS^T                     dK += dS^T.Q
+//   dV        rows = keys,    columns = queries  S^T = K.Q^T                 P^T                      dV += P^T.dO
 //
-// Every product is 3xTF32 (lo*hi + hi*lo + hi*hi of a hi/lo split, as in the GEMM kernels).  The first products of a
-// block take both operands from shared memory (the resident row operands X, and the block's column operands Y brought
-// by TMA, hi = the raw tile, lo written next to it by converter warps); their result lands in tensor memory, where
-// four "transform" warps (one thread per row) turn it into the left operand W of the second product -- hi in place
-// over S, lo beside it -- which the tensor core reads straight from tensor memory (A operand in tensor memory), with
-// the block's Z operand (MN-major, from TMA) in shared memory.  Each block's second product starts a fresh
-// accumulator that the transform warps add into fp32 registers (round to nearest; the tensor core's own accumulation
-// truncates), rescaled in the forward when the running row maximum moves.  Two S / W / accumulator buffers let block
-// c+1's first products run while block c is being transformed.
+// Every product is 3xTF32 (lo*hi + hi*lo + hi*hi of a hi/lo split, as in the GEMM kernels).
+//  * The row operand X1 of the first product (Q or K) lives in TENSOR MEMORY for the whole unit: the transform threads
+//    read their rows from global memory, split them and store hi and lo with tcgen05.st; the product takes its A operand
+//    from there.  (With A in shared memory a 256 x 64 x 8 instruction reads 4 KB of A per SM for 44 cycles of math, which
+//    saturates the shared-memory port and starves TMA and the converter warps: measured.)
+//  * The second row operand of dQ / dK (dO or V) does not fit in tensor memory beside the rest and stays in shared
+//    memory (TMA + converter warps), as do all column operands: Y (K-major, for the first products) and Z (MN-major,
+//    for the second product), hi = the raw tile from TMA, lo written next to it by converter warps.
+//  * The first products land in tensor memory, where eight transform warps (two threads per row, 32 columns each) turn
+//    them into the left operand W of the second product -- hi in place over S, lo beside it -- which the tensor core
+//    again reads from tensor memory.  Each block's second product starts a fresh accumulator that the transform warps
+//    add into fp32 registers (round to nearest; the tensor core's own accumulation truncates), rescaled in the forward
+//    when the running row maximum moves.  Two S buffers let block c+1's first products run while block c is transformed.
 //
 // Causal structure: forward and dQ walk the key blocks 0 .. diagonal; dK and dV walk the query blocks diagonal .. end;
 // elements above the diagonal are masked by index (the reference adds -1e9, which makes exp exactly 0).
@@ -42,6 +46,7 @@ struct AttnParams {
     int t_first;                  // 1: tensor-map coordinates are (d, t, h, b); 0: (d, h, t, b) (the smaller stride first)
     float scale, c2;              // c2 = scale * log2(e): the softmax runs in base 2
     long long ld, stride_h, stride_b;   // row pitch, head stride, batch stride of Q / K / V / O and gradients, in floats
+    const float* x1;              // the row operand kept in tensor memory: Q (forward, dQ) or K (dK, dV)
     float* out;                   // O, dQ, dK or dV
     float* lse;                   // [nslices, T] base-2 log-sum-exp of the scaled scores: written by the forward, read by the others
     const float* dvec;            // [nslices, T] D = rowsum(dO o O) (dQ and dK)
@@ -56,22 +61,30 @@ constexpr int kRowsPerCta = 128, kColBlock = 64;
 
 template <int MODE>
 struct AttnCfg {
-    static constexpr int NX = (MODE == ATT_BWD_Q || MODE == ATT_BWD_K) ? 2 : 1;   // resident row operands (and first products)
-    static constexpr int kXTile = kRowsPerCta * 64 * 4;        // one plane (hi or lo) of a row operand: 128 x 64 floats
-    static constexpr int kXBytes = NX * 2 * kXTile;
+    static constexpr int NX = (MODE == ATT_BWD_Q || MODE == ATT_BWD_K) ? 2 : 1;   // first products per block
+    static constexpr int kXTile = kRowsPerCta * 64 * 4;        // one plane (hi or lo) of the shared-memory row operand
+    static constexpr int kXBytes = NX == 2 ? 2 * kXTile : 0;   // X2 (dO or V) of dQ / dK
     static constexpr int kYTile = 32 * 64 * 4;                 // this CTA's 32 of the block's 64 columns x 64 floats
     static constexpr int kYStage = NX * 2 * kYTile;
     static constexpr int kZTile = 64 * 32 * 4;                 // 64 contraction rows x this CTA's 32 output columns
     static constexpr int kZStage = 2 * kZTile;
-    static constexpr int NYS = NX == 2 ? 2 : 4;
-    static constexpr int NZS = NX == 2 ? 2 : 4;
+#ifndef ZNN_ATT_STAGES1
+#define ZNN_ATT_STAGES1 3      // three stages measured faster than six (161 against 175 us on the forward at 96 x 1024 x 64)
+#endif
+    static constexpr int NYS = NX == 2 ? 3 : ZNN_ATT_STAGES1;
+    static constexpr int NZS = NX == 2 ? 3 : ZNN_ATT_STAGES1;
     static constexpr int kBarOff = kXBytes + NYS * kYStage + NZS * kZStage;
-    static constexpr int kSmemBytes = kBarOff + 1024 /*alignment*/ + 512 /*barriers*/ + (MODE == ATT_FWD ? 2048 : 0) /*row-maximum exchange*/;
+    static constexpr int kExchBytes = MODE == ATT_FWD ? 2048 : 0;   // row-maximum exchange between the two threads of a row
+    static constexpr int kSmemBytes = kBarOff + 1024 /*alignment*/ + 512 /*barriers*/ + kExchBytes;
     static_assert(kSmemBytes <= 232448, "shared memory budget");
+    // tensor-memory columns (512 allocated): X1 hi | X1 lo | S / W_hi [2] | then, forward and dV: W_lo [2], accumulator [2];
+    // dQ and dK: dP [2], W_lo [1], accumulator [1]
+    static constexpr int NWB = NX == 2 ? 1 : 2;                // W_lo / accumulator buffers
+    static constexpr uint32_t kColXhi = 0, kColXlo = 64, kColS = 128;
+    static constexpr uint32_t kColDp = 256;
+    static constexpr uint32_t kColWlo = NX == 2 ? 384 : 256;
+    static constexpr uint32_t kColAcc = NX == 2 ? 448 : 384;
 };
-
-// tensor-memory columns (512 allocated): S / W_hi [2], W_lo [2], accumulator [2], dP [2]
-constexpr uint32_t kColS = 0, kColWlo = 128, kColAcc = 256, kColDp = 384;
 
 struct AttnUnit {
     int slice, b, h, row0, cb0, nb;   // row0: first row of the pair's 256-row block; column blocks cb0 .. cb0 + nb - 1
@@ -101,8 +114,10 @@ __device__ __forceinline__ AttnUnit attn_unit(const AttnParams& p, int u)
 
 // Optional role profile (compile with -DZNN_ATTN_PROFILE; off in the product build): CTA pair 0's leader adds up, per
 // role, the cycles spent inside each kind of wait and the cycles of the whole role loop into g_attn_prof, which
-// znn_debug_attn_profile reads: [0] MMA loop, [1] x_conv, [2] y_conv, [3] w_ready, [4] z_conv, [5] acc_empty;
-// [8] transform loop, [9] s_full, [10] acc_full; [12] producer loop, [13] its waits; [14] converter loop, [15] its waits.
+// znn_debug_attn_profile reads: [0] MMA loop, [1] x waits, [2] y_conv, [3] w_ready, [4] z_conv, [5] acc_empty, [6] issue of
+// the first products, [7] issue of the second products; [8] transform loop, [9] s_full, [10] acc_full, [11] row operand
+// load; [12] producer loop, [13] its waits; [14] converter loop, [15] its waits, [17] fence + arrival; transform:
+// [18] score load, [19] W store + hand-off, [20] accumulator drain, [21] load-to-hand-off of one block.
 __device__ long long g_attn_prof[32];
 #ifdef ZNN_ATTN_PROFILE
 #define ATT_PROF_T0 const long long prof_t0 = clock64();
@@ -113,13 +128,9 @@ __device__ long long g_attn_prof[32];
         for (int i_ = 0; i_ < 32; i_++)                                                            \
             if (prof_acc[i_]) atomicAdd((unsigned long long*)&g_attn_prof[i_], (unsigned long long)prof_acc[i_]); \
     }
-#define ATT_PROF_MARK const long long prof_m = clock64();
-#define ATT_PROF_ADD(slot) prof_acc[slot] += clock64() - prof_m;
 #define ATT_PROF_MARK2(name) const long long name = clock64();
 #define ATT_PROF_ADD2(slot, name) prof_acc[slot] += clock64() - name;
 #else
-#define ATT_PROF_MARK
-#define ATT_PROF_ADD(slot)
 #define ATT_PROF_MARK2(name)
 #define ATT_PROF_ADD2(slot, name)
 #define ATT_PROF_T0
@@ -134,24 +145,33 @@ __device__ __forceinline__ float fast_exp2(float x)
     return y;
 }
 
+__device__ __forceinline__ void split_hi_lo(float x, uint32_t& hi, uint32_t& lo)
+{
+    hi = __float_as_uint(x) & 0xFFFFE000u;                   // exactly a TF32 value
+    lo = __float_as_uint(x - __uint_as_float(hi));           // exact in fp32, at most 2^-10 |x|
+}
+
 template <int MODE>
 __global__ void __launch_bounds__(kAttThreads, 1)
-attn_kernel(const __grid_constant__ CUtensorMap mx1, const __grid_constant__ CUtensorMap mx2,
-            const __grid_constant__ CUtensorMap my1, const __grid_constant__ CUtensorMap my2,
-            const __grid_constant__ CUtensorMap mz, const AttnParams p)
+attn_kernel(const __grid_constant__ CUtensorMap mx2, const __grid_constant__ CUtensorMap my1,
+            const __grid_constant__ CUtensorMap my2, const __grid_constant__ CUtensorMap mz, const AttnParams p)
 {
     using Cfg = AttnCfg<MODE>;
-    constexpr int NX = Cfg::NX, NYS = Cfg::NYS, NZS = Cfg::NZS;
+    constexpr int NX = Cfg::NX, NYS = Cfg::NYS, NZS = Cfg::NZS, NWB = Cfg::NWB;
+    constexpr uint32_t kColS = Cfg::kColS, kColDp = Cfg::kColDp, kColWlo = Cfg::kColWlo, kColAcc = Cfg::kColAcc;
     extern __shared__ uint8_t smem_raw[];
     const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
     uint8_t* smem_gen = smem_raw + (smem_base - smem_u32(smem_raw));
     const uint32_t x_base = smem_base, y_base = x_base + Cfg::kXBytes, z_base = y_base + NYS * Cfg::kYStage;
     const uint32_t bar_base = smem_base + Cfg::kBarOff;
     // barriers.  "full": TMA -> converters (own CTA); "conv": converters of both CTAs -> MMA issuer (leader CTA);
-    // "empty": MMA commit -> TMA producers (both CTAs); s_full / acc_full: MMA commit -> transform warps (both CTAs);
-    // w_ready / acc_empty: transform warps of both CTAs -> MMA issuer.
+    // "empty": MMA commit -> TMA producers (both CTAs); x1_ready: transform warps of both CTAs -> MMA issuer;
+    // s_full / acc_full: MMA commit -> transform warps (both CTAs); w_ready: transform warps of both CTAs -> MMA issuer.
+    // (w_ready of block g also tells that the accumulator and W_lo buffers block g will use have been drained: the same
+    // warps drained them earlier in program order.)
     int bi = 0;
     const uint32_t x_full = bar_base + 8u * bi++, x_conv = bar_base + 8u * bi++, x_empty = bar_base + 8u * bi++;
+    const uint32_t x1_ready = bar_base + 8u * bi++;
     const uint32_t y_full0 = bar_base + 8u * bi; bi += NYS;
     const uint32_t y_conv0 = bar_base + 8u * bi; bi += NYS;
     const uint32_t y_empty0 = bar_base + 8u * bi; bi += NYS;
@@ -161,7 +181,6 @@ attn_kernel(const __grid_constant__ CUtensorMap mx1, const __grid_constant__ CUt
     const uint32_t s_full0 = bar_base + 8u * bi; bi += 2;
     const uint32_t w_ready0 = bar_base + 8u * bi; bi += 2;
     const uint32_t acc_full0 = bar_base + 8u * bi; bi += 2;
-    const uint32_t acc_empty0 = bar_base + 8u * bi; bi += 2;
     const int kWordOff = 8 * bi;
     volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(smem_gen + Cfg::kBarOff + kWordOff);
     const uint32_t tmem_slot_addr = bar_base + kWordOff;
@@ -176,32 +195,42 @@ attn_kernel(const __grid_constant__ CUtensorMap mx1, const __grid_constant__ CUt
     const int pair = blockIdx.x >> 1, npairs = gridDim.x >> 1;
     const int total_units = p.nslices * p.nrb;
     const int kbh = p.hs >> 5;                    // 32-float k-blocks across the head dimension (1 or 2)
+    // The k-th unit of this CTA pair, or -1.  Units are sorted dearest first; round k deals units k * npairs .. to the
+    // pairs in alternating direction, so that a pair that got a dear unit in one round gets a cheap one in the next
+    // (60 -> 56 blocks for the busiest pair at 96 slices x 1024 positions, against a mean of 51.9).
+    auto unit_of = [&](int k) -> int {
+        const int u = k * npairs + ((k & 1) ? npairs - 1 - pair : pair);
+        return u < total_units ? u : -1;
+    };
 #ifdef ZNN_ATTN_PROFILE
-    const bool prof_on = (pair == 0 && cta_rank == 0 && lane == 0 && (warp <= 2 || warp == kAttXfWarp0));
+    volatile long long* const tstamp = reinterpret_cast<volatile long long*>(smem_gen + Cfg::kBarOff + 512 - 128);   // 16 slots
+    const bool prof_on = (pair == 0 && cta_rank == 0 && lane == 0 && (warp <= 3 || warp == kAttXfWarp0));
+    const int pslot = (warp == 3) ? 8 : 0;     // a Z converter warp reports in slots 22..25
     long long prof_acc[32];      // in registers; written once at the end of the role
 #pragma unroll
     for (int i = 0; i < 32; i++) prof_acc[i] = 0;
 #endif
 
     if (threadIdx.x == 0) {
+        static_assert(8 * (4 + 3 * NYS + 3 * NZS + 6) + 8 <= 512, "barrier block overflows");
         mbar_init(x_full, 1);
         mbar_init(x_conv, kAttConvWarps * 2);
         mbar_init(x_empty, 1);
+        mbar_init(x1_ready, kAttXfWarps * 2);
         for (int s = 0; s < NYS; s++) {
             mbar_init(y_full0 + 8u * s, 1);
-            mbar_init(y_conv0 + 8u * s, kAttConvWarps * 2);
+            mbar_init(y_conv0 + 8u * s, 2);           // one converter warp per CTA
             mbar_init(y_empty0 + 8u * s, 1);
         }
         for (int s = 0; s < NZS; s++) {
             mbar_init(z_full0 + 8u * s, 1);
-            mbar_init(z_conv0 + 8u * s, kAttConvWarps * 2);
+            mbar_init(z_conv0 + 8u * s, 2);
             mbar_init(z_empty0 + 8u * s, 1);
         }
         for (int b = 0; b < 2; b++) {
             mbar_init(s_full0 + 8u * b, 1);
             mbar_init(w_ready0 + 8u * b, kAttXfWarps * 2);
             mbar_init(acc_full0 + 8u * b, 1);
-            mbar_init(acc_empty0 + 8u * b, kAttXfWarps * 2);
         }
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
         if (leader) {
@@ -228,27 +257,25 @@ attn_kernel(const __grid_constant__ CUtensorMap mx1, const __grid_constant__ CUt
             // ---------------- TMA producer ----------------
             if (lane == 0) {
                 bool ok = true;
-                uint32_t ity = 0, itz = 0, ul = 0;
+                uint32_t it = 0, ul = 0;
                 ATT_PROF_T0
-                for (int u = pair; u < total_units && ok; u += npairs, ul++) {
+                for (int k = 0, u; (u = unit_of(k)) >= 0 && ok; k++, ul++) {
                     const AttnUnit d = attn_unit<MODE>(p, u);
-                    // the row operands of this unit, once the previous unit's first products no longer read them
-                    if (!ATT_PROF_WAIT(13, mbar_wait_bounded(x_empty, (ul & 1) ^ 1, p.wait_limit))) { ok = false; break; }
-                    mbar_arrive_expect_tx(x_full, (uint32_t)(NX * kbh * 16384));
-                    const int xrow = d.row0 + cta_rank * kRowsPerCta;
-                    for (int kb = 0; kb < kbh; kb++) {
-                        if (p.t_first) tma_load_4d(x_base + kb * 16384, &mx1, x_full, 32 * kb, xrow, d.h, d.b);
-                        else tma_load_4d(x_base + kb * 16384, &mx1, x_full, 32 * kb, d.h, xrow, d.b);
-                        if (NX == 2) {
-                            if (p.t_first) tma_load_4d(x_base + 2 * Cfg::kXTile + kb * 16384, &mx2, x_full, 32 * kb, xrow, d.h, d.b);
-                            else tma_load_4d(x_base + 2 * Cfg::kXTile + kb * 16384, &mx2, x_full, 32 * kb, d.h, xrow, d.b);
+                    if (NX == 2) {
+                        // the shared-memory row operand of this unit, once the previous unit's first products no longer read it
+                        if (!ATT_PROF_WAIT(13, mbar_wait_bounded(x_empty, (ul & 1) ^ 1, p.wait_limit))) { ok = false; break; }
+                        mbar_arrive_expect_tx(x_full, (uint32_t)(kbh * 16384));
+                        const int xrow = d.row0 + cta_rank * kRowsPerCta;
+                        for (int kb = 0; kb < kbh; kb++) {
+                            if (p.t_first) tma_load_4d(x_base + kb * 16384, &mx2, x_full, 32 * kb, xrow, d.h, d.b);
+                            else tma_load_4d(x_base + kb * 16384, &mx2, x_full, 32 * kb, d.h, xrow, d.b);
                         }
                     }
-                    for (int c = 0; c < d.nb && ok; c++) {
+                    for (int c = 0; c < d.nb && ok; c++, it++) {
                         const int col0 = (d.cb0 + c) * kColBlock;
                         {   // Y: this CTA's 32 of the block's 64 columns, K-major
-                            const int s = ity % NYS;
-                            if (!ATT_PROF_WAIT(13, mbar_wait_bounded(y_empty0 + 8u * s, ((ity / NYS) & 1) ^ 1, p.wait_limit))) { ok = false; break; }
+                            const int s = it % NYS;
+                            if (!ATT_PROF_WAIT(13, mbar_wait_bounded(y_empty0 + 8u * s, ((it / NYS) & 1) ^ 1, p.wait_limit))) { ok = false; break; }
                             const uint32_t fb = y_full0 + 8u * s, st = y_base + s * Cfg::kYStage;
                             mbar_arrive_expect_tx(fb, (uint32_t)(NX * kbh * 4096));
                             const int yrow = col0 + cta_rank * 32;
@@ -260,11 +287,10 @@ attn_kernel(const __grid_constant__ CUtensorMap mx1, const __grid_constant__ CUt
                                     else tma_load_4d(st + 2 * Cfg::kYTile + kb * 4096, &my2, fb, 32 * kb, d.h, yrow, d.b);
                                 }
                             }
-                            ity++;
                         }
                         {   // Z: the block's 64 contraction rows x this CTA's 32 output columns, MN-major
-                            const int s = itz % NZS;
-                            if (!ATT_PROF_WAIT(13, mbar_wait_bounded(z_empty0 + 8u * s, ((itz / NZS) & 1) ^ 1, p.wait_limit))) { ok = false; break; }
+                            const int s = it % NZS;
+                            if (!ATT_PROF_WAIT(13, mbar_wait_bounded(z_empty0 + 8u * s, ((it / NZS) & 1) ^ 1, p.wait_limit))) { ok = false; break; }
                             const uint32_t fb = z_full0 + 8u * s, st = z_base + s * Cfg::kZStage;
                             mbar_arrive_expect_tx(fb, 8192u);
                             const int d0 = cta_rank * 32;     // beyond hs (hs = 32, second CTA): the box is zero-filled
@@ -272,7 +298,6 @@ attn_kernel(const __grid_constant__ CUtensorMap mx1, const __grid_constant__ CUt
                                 if (p.t_first) tma_load_4d(st + kk * 4096, &mz, fb, d0, col0 + 32 * kk, d.h, d.b);
                                 else tma_load_4d(st + kk * 4096, &mz, fb, d0, d.h, col0 + 32 * kk, d.b);
                             }
-                            itz++;
                         }
                     }
                 }
@@ -295,187 +320,256 @@ attn_kernel(const __grid_constant__ CUtensorMap mx1, const __grid_constant__ CUt
                 constexpr uint32_t idesc1 = make_tf32_idesc_major(256, 64, false, false);
                 constexpr uint32_t idesc2 = make_tf32_idesc_major(256, 64, false, true);
                 bool ok = true;
-                uint32_t ity = 0, itz = 0, ul = 0, g = 0;     // g: blocks issued so far (buffer = g & 1)
+                uint32_t it = 0, ul = 0, g = 0;               // it: blocks whose first products were issued; g: the same, named for the buffers
                 const int ksteps1 = p.hs >> 3;                // K = 8 per instruction
                 const uint64_t dx0 = make_kmajor_sw128_desc(x_base), dy0 = make_kmajor_sw128_desc(y_base);
                 const uint64_t dz0 = make_mnmajor_sw128_desc(z_base);
+                uint32_t itz = 0;
                 ATT_PROF_T0
-                for (int u = pair; u < total_units && ok; u += npairs, ul++) {
-                    const AttnUnit d = attn_unit<MODE>(p, u);
-                    if (!ATT_PROF_WAIT(1, warp_wait(x_conv, ul & 1))) { ok = false; break; }
+                // second product of block gb (program order: P1(c), P2(c-1), P1(c+1), P2(c), ...)
+                auto second = [&](uint32_t gb) -> bool {
+                    const uint32_t sbuf = gb & 1, wbuf = gb % NWB;
+                    if (!ATT_PROF_WAIT(3, warp_wait(w_ready0 + 8u * sbuf, (gb >> 1) & 1))) return false;
+#ifdef ZNN_ATTN_PROFILE
+                    if (prof_on) { prof_acc[27] += clock64() - tstamp[4 + (gb & 3)]; prof_acc[29] += 1; }
+#endif
+                    const int s = itz % NZS;
+                    if (!ATT_PROF_WAIT(4, warp_wait(z_conv0 + 8u * s, (itz / NZS) & 1))) return false;
                     tc_fence_after();
-                    // second product of the block issued `gp` blocks ago (program order: P1(c), P2(c-1), P1(c+1), ...)
-                    auto second = [&](uint32_t gb) -> bool {
-                        const uint32_t buf = gb & 1, ph = (gb >> 1) & 1;
-                        if (!ATT_PROF_WAIT(3, warp_wait(w_ready0 + 8u * buf, ph))) return false;
-                        const int s = itz % NZS;
-                        if (!ATT_PROF_WAIT(4, warp_wait(z_conv0 + 8u * s, (itz / NZS) & 1))) return false;
-                        if (!ATT_PROF_WAIT(5, warp_wait(acc_empty0 + 8u * buf, ph ^ 1))) return false;
-                        tc_fence_after();
-                        const uint64_t z_hi = dz0 + (uint64_t)((s * Cfg::kZStage) >> 4), z_lo = z_hi + (Cfg::kZTile >> 4);
-                        const uint32_t a_hi = tmem_base + kColS + 64u * buf, a_lo = tmem_base + kColWlo + 64u * buf;
-                        const uint32_t d_acc = tmem_base + kColAcc + 64u * buf;
-                        constexpr uint32_t zstep = 1024 >> 4;
-                        ATT_PROF_MARK
-                        if (elected) {
+                    const uint64_t z_hi = dz0 + (uint64_t)((s * Cfg::kZStage) >> 4), z_lo = z_hi + (Cfg::kZTile >> 4);
+                    const uint32_t a_hi = tmem_base + kColS + 64u * sbuf, a_lo = tmem_base + kColWlo + 64u * wbuf;
+                    const uint32_t d_acc = tmem_base + kColAcc + 64u * wbuf;
+                    constexpr uint32_t zstep = 1024 >> 4;
+                    ATT_PROF_MARK2(pm)
+                    if (elected) {
 #pragma unroll
-                            for (int k = 0; k < 8; k++) umma_tf32_ts_pair(d_acc, a_lo + 8u * k, z_hi + zstep * k, idesc2, k == 0 ? 0u : 1u);
+                        for (int k = 0; k < 8; k++) umma_tf32_ts_pair(d_acc, a_lo + 8u * k, z_hi + zstep * k, idesc2, k == 0 ? 0u : 1u);
 #pragma unroll
-                            for (int k = 0; k < 8; k++) umma_tf32_ts_pair(d_acc, a_hi + 8u * k, z_lo + zstep * k, idesc2, 1);
+                        for (int k = 0; k < 8; k++) umma_tf32_ts_pair(d_acc, a_hi + 8u * k, z_lo + zstep * k, idesc2, 1);
 #pragma unroll
-                            for (int k = 0; k < 8; k++) umma_tf32_ts_pair(d_acc, a_hi + 8u * k, z_hi + zstep * k, idesc2, 1);
-                            umma_commit_pair(acc_full0 + 8u * buf);
-                            umma_commit_pair(z_empty0 + 8u * s);
-                        }
-                        __syncwarp();
-                        ATT_PROF_ADD(7)
-                        itz++;
-                        return true;
-                    };
-                    for (int c = 0; c < d.nb && ok; c++, g++) {
+                        for (int k = 0; k < 8; k++) umma_tf32_ts_pair(d_acc, a_hi + 8u * k, z_hi + zstep * k, idesc2, 1);
+                        umma_commit_pair(acc_full0 + 8u * wbuf);
+                        umma_commit_pair(z_empty0 + 8u * s);
+                    }
+                    __syncwarp();
+                    ATT_PROF_ADD2(7, pm)
+                    itz++;
+                    return true;
+                };
+                for (int k = 0, u; (u = unit_of(k)) >= 0 && ok; k++, ul++) {
+                    const AttnUnit d = attn_unit<MODE>(p, u);
+                    if (!ATT_PROF_WAIT(1, warp_wait(x1_ready, ul & 1))) { ok = false; break; }
+                    if (NX == 2 && !ATT_PROF_WAIT(1, warp_wait(x_conv, ul & 1))) { ok = false; break; }
+                    tc_fence_after();
+                    for (int c = 0; c < d.nb && ok; c++, g++, it++) {
                         const uint32_t buf = g & 1;
-                        const int s = ity % NYS;
-                        if (!ATT_PROF_WAIT(2, warp_wait(y_conv0 + 8u * s, (ity / NYS) & 1))) { ok = false; break; }
+                        const int s = it % NYS;
+                        if (!ATT_PROF_WAIT(2, warp_wait(y_conv0 + 8u * s, (it / NYS) & 1))) { ok = false; break; }
                         tc_fence_after();
-                        ATT_PROF_MARK
-#pragma unroll
-                        for (int which = 0; which < NX; which++) {
-                            // descriptors differ from the base ones by constant offsets (in 16-byte units): nothing but
-                            // 64-bit adds per instruction, which matters because one thread issues them all
-                            const uint64_t xa_hi = dx0 + (uint64_t)((which * 2 * Cfg::kXTile) >> 4), xa_lo = xa_hi + (Cfg::kXTile >> 4);
-                            const uint64_t yb_hi = dy0 + (uint64_t)((s * Cfg::kYStage + which * 2 * Cfg::kYTile) >> 4);
-                            const uint64_t yb_lo = yb_hi + (Cfg::kYTile >> 4);
-                            const uint32_t d_tm = tmem_base + (which == 0 ? kColS : kColDp) + 64u * buf;
-                            if (!elected) continue;
-                            // lo*hi, hi*lo, hi*hi; k-step k lies in k-block k / 4 (16 KB apart in X, 4 KB in Y), 32 bytes per step
-#pragma unroll
-                            for (int k = 0; k < 8; k++)
-                                if (k < ksteps1)
-                                    umma_tf32<2>(d_tm, xa_lo + (uint64_t)((k >> 2) * 1024 + (k & 3) * 2), yb_hi + (uint64_t)((k >> 2) * 256 + (k & 3) * 2),
-                                                 idesc1, k == 0 ? 0u : 1u);
-#pragma unroll
-                            for (int k = 0; k < 8; k++)
-                                if (k < ksteps1)
-                                    umma_tf32<2>(d_tm, xa_hi + (uint64_t)((k >> 2) * 1024 + (k & 3) * 2), yb_lo + (uint64_t)((k >> 2) * 256 + (k & 3) * 2),
-                                                 idesc1, 1);
-#pragma unroll
-                            for (int k = 0; k < 8; k++)
-                                if (k < ksteps1)
-                                    umma_tf32<2>(d_tm, xa_hi + (uint64_t)((k >> 2) * 1024 + (k & 3) * 2), yb_hi + (uint64_t)((k >> 2) * 256 + (k & 3) * 2),
-                                                 idesc1, 1);
-                        }
+                        ATT_PROF_MARK2(pm)
                         if (elected) {
+                            // descriptors differ from the base ones by constant offsets (in 16-byte units): k-step k lies in
+                            // k-block k / 4 (4 KB apart in Y, 16 KB in the shared-memory X), 32 bytes per step
+                            const uint64_t yb_hi = dy0 + (uint64_t)((s * Cfg::kYStage) >> 4), yb_lo = yb_hi + (Cfg::kYTile >> 4);
+                            const uint32_t x_hi = tmem_base + Cfg::kColXhi, x_lo = tmem_base + Cfg::kColXlo;
+                            const uint32_t d_s = tmem_base + kColS + 64u * buf;
+                            // S = X1.Y1^T with X1 in tensor memory: lo*hi, hi*lo, hi*hi
+#pragma unroll
+                            for (int k = 0; k < 8; k++)
+                                if (k < ksteps1) umma_tf32_ts_pair(d_s, x_lo + 8u * k, yb_hi + (uint64_t)((k >> 2) * 256 + (k & 3) * 2), idesc1, k == 0 ? 0u : 1u);
+#pragma unroll
+                            for (int k = 0; k < 8; k++)
+                                if (k < ksteps1) umma_tf32_ts_pair(d_s, x_hi + 8u * k, yb_lo + (uint64_t)((k >> 2) * 256 + (k & 3) * 2), idesc1, 1);
+#pragma unroll
+                            for (int k = 0; k < 8; k++)
+                                if (k < ksteps1) umma_tf32_ts_pair(d_s, x_hi + 8u * k, yb_hi + (uint64_t)((k >> 2) * 256 + (k & 3) * 2), idesc1, 1);
+                            if (NX == 2) {
+                                // dP = X2.Y2^T with X2 in shared memory
+                                const uint64_t xa_hi = dx0, xa_lo = dx0 + (Cfg::kXTile >> 4);
+                                const uint64_t y2_hi = yb_hi + (uint64_t)((2 * Cfg::kYTile) >> 4), y2_lo = y2_hi + (Cfg::kYTile >> 4);
+                                const uint32_t d_dp = tmem_base + kColDp + 64u * buf;
+#pragma unroll
+                                for (int k = 0; k < 8; k++)
+                                    if (k < ksteps1)
+                                        umma_tf32<2>(d_dp, xa_lo + (uint64_t)((k >> 2) * 1024 + (k & 3) * 2), y2_hi + (uint64_t)((k >> 2) * 256 + (k & 3) * 2), idesc1, k == 0 ? 0u : 1u);
+#pragma unroll
+                                for (int k = 0; k < 8; k++)
+                                    if (k < ksteps1)
+                                        umma_tf32<2>(d_dp, xa_hi + (uint64_t)((k >> 2) * 1024 + (k & 3) * 2), y2_lo + (uint64_t)((k >> 2) * 256 + (k & 3) * 2), idesc1, 1);
+#pragma unroll
+                                for (int k = 0; k < 8; k++)
+                                    if (k < ksteps1)
+                                        umma_tf32<2>(d_dp, xa_hi + (uint64_t)((k >> 2) * 1024 + (k & 3) * 2), y2_hi + (uint64_t)((k >> 2) * 256 + (k & 3) * 2), idesc1, 1);
+                            }
                             umma_commit_pair(s_full0 + 8u * buf);
                             umma_commit_pair(y_empty0 + 8u * s);
-                            if (c == d.nb - 1) umma_commit_pair(x_empty);   // the row operands are free once these products are done
+#ifdef ZNN_ATTN_PROFILE
+                            tstamp[g & 3] = clock64();
+#endif
+                            if (NX == 2 && c == d.nb - 1) umma_commit_pair(x_empty);   // the shared-memory row operand is free after these
                         }
                         __syncwarp();
-                        ATT_PROF_ADD(6)
-                        ity++;
-                        if (c >= 1 && !second(g - 1)) { ok = false; break; }
+                        ATT_PROF_ADD2(6, pm)
+                        // the previous block's second product (of this unit or of the one before): program order
+                        // P1(g), P2(g-1), P1(g+1), P2(g), ... runs on across units
+                        if (g >= 1 && !second(g - 1)) { ok = false; break; }
                     }
-                    if (ok && !second(g - 1)) ok = false;
                 }
+                if (ok && g >= 1 && !second(g - 1)) ok = false;
                 if (!ok && lane == 0) atomicOr(p.status, ZNN_DEV_MMA_WAIT_EXPIRED);
                 ATT_PROF_END(0)
             }
         } else {
             // ---------------- converters: lo = x - (x with the 13 low mantissa bits cleared), next to each landed tile ----------------
-            const int ct = threadIdx.x - 32 * kAttConvWarp0;          // 0 .. 191
-            constexpr int kT = 32 * kAttConvWarps;
+            // Handing a converted tile to the tensor core (proxy fence, barrier arrival) costs a warp about 1500 cycles
+            // (measured), several times the conversion itself.  Each of the six warps therefore works alone on its own
+            // tiles: warps 0, 2, 4 take the Y tiles of blocks 0, 1, 2 (mod 3), warps 1, 3, 5 the Z tiles, so six hand-offs
+            // are in flight at a time.  The shared-memory row operand (dQ, dK) is converted by all six together.
+            const int cw = warp - kAttConvWarp0;                               // 0 .. 5
+            const int kind = cw & 1, turn = cw >> 1;                           // Y or Z; which blocks (mod 3)
+            const int ct = threadIdx.x - 32 * kAttConvWarp0;                   // 0 .. 191 over all converter warps
             const uint32_t x_conv_l = mapa_shared(x_conv, 0), y_conv_l0 = mapa_shared(y_conv0, 0), z_conv_l0 = mapa_shared(z_conv0, 0);
-            auto convert = [&](uint8_t* base, int nvec, int lo_off) {
+            auto convert = [&](uint8_t* base, int nvec, int lo_off, int tid, int nthr) {
 #pragma unroll 1
-                for (int i0 = ct; i0 < nvec; i0 += 4 * kT) {
+                for (int i0 = tid; i0 < nvec; i0 += 4 * nthr) {
                     uint4 x[4];
 #pragma unroll
                     for (int v = 0; v < 4; v++)
-                        if (i0 + v * kT < nvec) x[v] = *reinterpret_cast<const uint4*>(base + 16 * (i0 + v * kT));
+                        if (i0 + v * nthr < nvec) x[v] = *reinterpret_cast<const uint4*>(base + 16 * (i0 + v * nthr));
 #pragma unroll
                     for (int v = 0; v < 4; v++) {
-                        if (i0 + v * kT >= nvec) continue;
+                        if (i0 + v * nthr >= nvec) continue;
                         float4 l;
                         l.x = __uint_as_float(x[v].x) - __uint_as_float(x[v].x & 0xFFFFE000u);
                         l.y = __uint_as_float(x[v].y) - __uint_as_float(x[v].y & 0xFFFFE000u);
                         l.z = __uint_as_float(x[v].z) - __uint_as_float(x[v].z & 0xFFFFE000u);
                         l.w = __uint_as_float(x[v].w) - __uint_as_float(x[v].w & 0xFFFFE000u);
-                        *reinterpret_cast<float4*>(base + 16 * (i0 + v * kT) + lo_off) = l;
+                        *reinterpret_cast<float4*>(base + 16 * (i0 + v * nthr) + lo_off) = l;
                     }
                 }
             };
             auto wait_full = [&](uint32_t bar, uint32_t ph) -> bool {
                 bool got = true;
-                if (lane == 0) got = ATT_PROF_WAIT(15, mbar_wait_bounded_tight(bar, ph, p.wait_limit));
+                #ifdef ZNN_ATT_CONV_SLEEPY
+                if (lane == 0) got = ATT_PROF_WAIT(15 + pslot, mbar_wait_bounded(bar, ph, p.wait_limit));
+#else
+                if (lane == 0) got = ATT_PROF_WAIT(15 + pslot, mbar_wait_bounded_tight(bar, ph, p.wait_limit));
+#endif
                 return __shfl_sync(0xffffffffu, (int)got, 0) != 0;
             };
             auto done = [&](uint32_t leader_bar) {
+                asm volatile("" ::: "memory");
                 ATT_PROF_MARK2(pf)
                 asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-                ATT_PROF_ADD2(16, pf)
                 __syncwarp();
                 if (lane == 0) mbar_arrive_remote(leader_bar);
-                ATT_PROF_ADD2(17, pf)
+                ATT_PROF_ADD2(17 + pslot, pf)
             };
+            static_assert(NYS % 3 == 0 && NZS % 3 == 0, "a converter warp always meets the same ring slots");
             bool got = true;
-            uint32_t ity = 0, itz = 0, ul = 0;
+            uint32_t it = 0, ul = 0;       // it: blocks seen so far (the ring counter of both streams)
             ATT_PROF_T0
-            for (int u = pair; u < total_units && got; u += npairs, ul++) {
+            for (int k = 0, u; (u = unit_of(k)) >= 0 && got; k++, ul++) {
                 const AttnUnit d = attn_unit<MODE>(p, u);
-                if (!(got = wait_full(x_full, ul & 1))) break;
-                for (int w = 0; w < NX; w++) convert(smem_gen + w * 2 * Cfg::kXTile, kbh * 1024, Cfg::kXTile);
-                done(x_conv_l);
-                for (int c = 0; c < d.nb; c++) {
-                    {
-                        const int s = ity % NYS;
-                        if (!(got = wait_full(y_full0 + 8u * s, (ity / NYS) & 1))) break;
+                if (NX == 2) {
+                    if (!(got = wait_full(x_full, ul & 1))) break;
+                    convert(smem_gen, kbh * 1024, Cfg::kXTile, ct, 32 * kAttConvWarps);
+                    done(x_conv_l);
+                }
+                for (int c = 0; c < d.nb; c++, it++) {
+                    if ((int)(it % 3) != turn) continue;
+                    if (kind == 0) {
+                        const int s = it % NYS;
+                        if (!(got = wait_full(y_full0 + 8u * s, (it / NYS) & 1))) break;
                         uint8_t* st = smem_gen + Cfg::kXBytes + s * Cfg::kYStage;
-                        for (int w = 0; w < NX; w++) convert(st + w * 2 * Cfg::kYTile, kbh * 256, Cfg::kYTile);
+                        for (int w = 0; w < NX; w++) convert(st + w * 2 * Cfg::kYTile, kbh * 256, Cfg::kYTile, lane, 32);
                         done(y_conv_l0 + 8u * s);
-                        ity++;
-                    }
-                    {
-                        const int s = itz % NZS;
-                        if (!(got = wait_full(z_full0 + 8u * s, (itz / NZS) & 1))) break;
+                    } else {
+                        const int s = it % NZS;
+                        if (!(got = wait_full(z_full0 + 8u * s, (it / NZS) & 1))) break;
                         uint8_t* st = smem_gen + Cfg::kXBytes + NYS * Cfg::kYStage + s * Cfg::kZStage;
-                        convert(st, 512, Cfg::kZTile);
+#ifdef ZNN_ATT_SKIP_ZCONV
+                        (void)st;
+                        if (lane == 0) mbar_arrive_remote(z_conv_l0 + 8u * s);     // timing experiment only: results are wrong
+#else
+                        convert(st, 512, Cfg::kZTile, lane, 32);
                         done(z_conv_l0 + 8u * s);
-                        itz++;
+#endif
                     }
                 }
             }
             if (!got && lane == 0) atomicOr(p.status, ZNN_DEV_TMA_WAIT_EXPIRED);
-            ATT_PROF_END(14)
+            ATT_PROF_END(14 + pslot)
         }
     } else {
         asm volatile("setmaxnreg.inc.sync.aligned.u32 168;");
         if (!aborted) {
             // ---------------- transform warps: two threads per row of this CTA's 128, 32 columns each ----------------
             // Warp w works on tensor-memory lanes 32 * (w & 3) .. + 31 (the quarter a warp may access) and on columns
-            // 32 * half .. + 31 of every 64-wide block (S, dP, W and the accumulator alike), half = (w - 8) / 4.
+            // 32 * half .. + 31 of every 64-wide block (X1, S, dP, W and the accumulator alike), half = (w - 8) / 4.
             const int q = warp & 3, half = (warp - kAttXfWarp0) >> 2;
             const int rloc = q * 32 + lane;
             const uint32_t lane_sel = (uint32_t)(q * 32) << 16;
             const uint32_t col_sel = 32u * (uint32_t)half;
-            const uint32_t w_ready_l0 = mapa_shared(w_ready0, 0), acc_empty_l0 = mapa_shared(acc_empty0, 0);
+            const uint32_t w_ready_l0 = mapa_shared(w_ready0, 0);
+            const uint32_t x1_ready_l = mapa_shared(x1_ready, 0);
             const int hs = p.hs;
             // forward: the two threads of a row exchange their block maxima (and, at the end, their sums) here
             float* const exch = reinterpret_cast<float*>(smem_gen + Cfg::kBarOff + 512);   // [2 parities][2 halves][128 rows]
             bool got = true;
-            uint32_t g = 0;
+            uint32_t g = 0, ul = 0;
+            // every lane polls (one warp-wide instruction per poll; no broadcast afterwards); the vote keeps the warp's
+            // decision uniform should the limit run out for some lanes only
             auto wait_bar = [&](uint32_t bar, uint32_t ph, int slot) -> bool {
-                bool ok = true;
-                if (lane == 0) ok = ATT_PROF_WAIT(slot, mbar_wait_bounded_tight(bar, ph, p.wait_limit));
-                return __shfl_sync(0xffffffffu, (int)ok, 0) != 0;
+#ifdef ZNN_ATT_XF_SLEEPY
+                const bool ok = ATT_PROF_WAIT(slot, mbar_wait_bounded(bar, ph, p.wait_limit));
+#else
+                const bool ok = ATT_PROF_WAIT(slot, mbar_wait_bounded_tight(bar, ph, p.wait_limit));
+#endif
+                return __all_sync(0xffffffffu, ok);
             };
             auto pair_sync = [&]() { asm volatile("bar.sync %0, 64;" ::"r"(1 + q) : "memory"); };   // the two warps of a lane quarter
             ATT_PROF_T0
+            // This thread's 32 columns of its row of X1 for unit `un`: global memory -> registers ...
+            auto load_x1 = [&](int un, float4 (&xr)[8]) {
+                const AttnUnit dn = attn_unit<MODE>(p, un);
+                const int rown = dn.row0 + cta_rank * kRowsPerCta + rloc;
+                const bool have = rown < p.T && 32 * half < hs;
+                const float* src = p.x1 + (size_t)dn.b * p.stride_b + (size_t)dn.h * p.stride_h + (size_t)rown * p.ld + 32 * half;
+#pragma unroll
+                for (int i = 0; i < 8; i++) xr[i] = have ? *reinterpret_cast<const float4*>(src + 4 * i) : make_float4(0.f, 0.f, 0.f, 0.f);
+            };
+            // ... -> hi / lo -> tensor memory, and the MMA issuer is told.  Called once the first products of the previous
+            // unit have completed (they read the old rows).
+            auto store_x1 = [&](const float4 (&xr)[8]) {
+                uint32_t hi[32], lo[32];
+#pragma unroll
+                for (int i = 0; i < 8; i++) {
+                    split_hi_lo(xr[i].x, hi[4 * i], lo[4 * i]);
+                    split_hi_lo(xr[i].y, hi[4 * i + 1], lo[4 * i + 1]);
+                    split_hi_lo(xr[i].z, hi[4 * i + 2], lo[4 * i + 2]);
+                    split_hi_lo(xr[i].w, hi[4 * i + 3], lo[4 * i + 3]);
+                }
+                tmem_st_32x32(tmem_base + lane_sel + Cfg::kColXhi + col_sel, hi);
+                tmem_st_32x32(tmem_base + lane_sel + Cfg::kColXlo + col_sel, lo);
+                tmem_st_wait();
+                tc_fence_before();
+                __syncwarp();
+                if (lane == 0) mbar_arrive_remote(x1_ready_l);
+            };
+            if (unit_of(0) >= 0) {
+                float4 xr[8];
+                load_x1(unit_of(0), xr);
+                store_x1(xr);
+            }
             // After an expired wait (got = false) a warp keeps walking its blocks without touching barriers or tensor
             // memory, so that the pair_sync calls of the forward stay matched with its partner warp's.
-            for (int u = pair; u < total_units; u += npairs) {
+            for (int k = 0, u; (u = unit_of(k)) >= 0; k++, ul++) {
                 const AttnUnit d = attn_unit<MODE>(p, u);
                 const int row = d.row0 + cta_rank * kRowsPerCta + rloc;       // absolute row inside the slice
                 const bool row_ok = row < p.T;
                 const size_t stat_off = (size_t)d.slice * p.T;
+                const size_t row_off = (size_t)d.b * p.stride_b + (size_t)d.h * p.stride_h + (size_t)row * p.ld + 32 * half;
                 float acc[32];
 #pragma unroll
                 for (int i = 0; i < 32; i++) acc[i] = 0.0f;
@@ -485,14 +579,14 @@ attn_kernel(const __grid_constant__ CUtensorMap mx1, const __grid_constant__ CUt
                     lse_r = p.lse[stat_off + row];
                     d_r = p.dvec[stat_off + row];
                 }
-                // adds this thread's 32 columns of block gb's accumulator (buffer gb & 1) into the registers
+                // adds this thread's 32 columns of block gb's accumulator into the registers
                 auto drain = [&](uint32_t gb, float factor) -> bool {
-                    const uint32_t buf = gb & 1;
-                    if (!wait_bar(acc_full0 + 8u * buf, (gb >> 1) & 1, 10)) return false;
+                    const uint32_t wbuf = gb % NWB;
+                    if (!wait_bar(acc_full0 + 8u * wbuf, (gb / NWB) & 1, 10)) return false;
                     ATT_PROF_MARK2(pd)
                     tc_fence_after();
                     float v[32];
-                    tmem_ld_32x32(tmem_base + lane_sel + kColAcc + 64u * buf + col_sel, v);
+                    tmem_ld_32x32(tmem_base + lane_sel + kColAcc + 64u * wbuf + col_sel, v);
 #pragma unroll
                     for (int i = 0; i < 32; i++) {
                         if (MODE == ATT_FWD) acc[i] = acc[i] * factor + v[i];
@@ -500,22 +594,30 @@ attn_kernel(const __grid_constant__ CUtensorMap mx1, const __grid_constant__ CUt
                     }
                     tc_fence_before();
                     __syncwarp();
-                    if (lane == 0) mbar_arrive_remote(acc_empty_l0 + 8u * buf);
                     ATT_PROF_ADD2(20, pd)
                     return true;
                 };
                 for (int c = 0; c < d.nb; c++, g++) {
-                    const uint32_t buf = g & 1;
+                    const uint32_t buf = g & 1, wbuf = g % NWB;
                     const int col0 = (d.cb0 + c) * kColBlock + 32 * half;     // this thread's first column of the block
+                    // last block of the unit: the next unit's X1 rows are fetched now and go to tensor memory as soon as this
+                    // block's first products (the last readers of the old rows) are done, so that the MMA issuer can run on
+                    const bool next_x1 = got && c == d.nb - 1 && unit_of(k + 1) >= 0;
+                    float4 xn[8];
+                    if (next_x1) load_x1(unit_of(k + 1), xn);
                     if (got) got = wait_bar(s_full0 + 8u * buf, (g >> 1) & 1, 9);
                     if (!got) {
                         if (MODE == ATT_FWD) pair_sync();
                         continue;
                     }
                     ATT_PROF_MARK2(pt)
+#ifdef ZNN_ATTN_PROFILE
+                    if (prof_on) { prof_acc[26] += clock64() - tstamp[g & 3]; prof_acc[28] += 1; }
+#endif
                     tc_fence_after();
+                    if (next_x1) store_x1(xn);
                     const uint32_t ts = tmem_base + lane_sel + kColS + 64u * buf + col_sel;
-                    const uint32_t tl = tmem_base + lane_sel + kColWlo + 64u * buf + col_sel;
+                    const uint32_t tl = tmem_base + lane_sel + kColWlo + 64u * wbuf + col_sel;
                     const uint32_t tdp = tmem_base + lane_sel + kColDp + 64u * buf + col_sel;
                     float corr = 1.0f;
                     float s[32];
@@ -523,28 +625,30 @@ attn_kernel(const __grid_constant__ CUtensorMap mx1, const __grid_constant__ CUt
                     ATT_PROF_ADD2(18, pt)
                     uint32_t hi[32], lo[32];
                     if (MODE == ATT_FWD) {
-                        float mx = m_run;
+                        // m_run is kept in the scaled (base-2 exponent) domain; c2 > 0, so the maximum commutes with the scaling
+                        const bool diag = col0 + 31 > d.row0 + cta_rank * kRowsPerCta + q * 32;   // warp-uniform: some element may be masked
+                        if (diag) {
 #pragma unroll
-                        for (int j = 0; j < 32; j++) {
-                            const float v = (col0 + j <= row) ? s[j] * p.c2 : -CUDART_INF_F;
-                            s[j] = v;
-                            mx = fmaxf(mx, v);
+                            for (int j = 0; j < 32; j++) s[j] = (col0 + j <= row) ? s[j] : -CUDART_INF_F;
                         }
+                        float m4[4] = {s[0], s[1], s[2], s[3]};
+#pragma unroll
+                        for (int j = 4; j < 32; j++) m4[j & 3] = fmaxf(m4[j & 3], s[j]);
+                        float mx = fmaxf(m_run, fmaxf(fmaxf(m4[0], m4[1]), fmaxf(m4[2], m4[3])) * p.c2);
                         // the row's maximum over both halves of the block
                         float* const ex = exch + (g & 1) * 256;
                         ex[half * 128 + rloc] = mx;
                         pair_sync();
                         mx = fmaxf(mx, ex[(half ^ 1) * 128 + rloc]);
                         corr = fast_exp2(m_run - mx);
-                        float sum = 0.0f;
+                        float s4[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
                         for (int j = 0; j < 32; j++) {
-                            const float pv = fast_exp2(s[j] - mx);
-                            sum += pv;
-                            hi[j] = __float_as_uint(pv) & 0xFFFFE000u;
-                            lo[j] = __float_as_uint(pv - __uint_as_float(hi[j]));
+                            const float pv = fast_exp2(fmaf(s[j], p.c2, -mx));
+                            s4[j & 3] += pv;
+                            split_hi_lo(pv, hi[j], lo[j]);
                         }
-                        l_run = l_run * corr + sum;     // this thread's columns only; the halves are added at the end
+                        l_run = l_run * corr + ((s4[0] + s4[1]) + (s4[2] + s4[3]));     // this thread's columns only; the halves are added at the end
                         m_run = mx;
                     } else if (MODE == ATT_BWD_V) {
                         // W = P^T: rows are keys, columns queries; statistics per column
@@ -559,8 +663,7 @@ attn_kernel(const __grid_constant__ CUtensorMap mx1, const __grid_constant__ CUt
                                 const int j = 4 * j4 + e;
                                 const bool vis = (row <= qc + e) && (qc + e < p.T);
                                 const float pv = vis ? fast_exp2(fmaf(s[j], p.c2, -ls[e])) : 0.0f;
-                                hi[j] = __float_as_uint(pv) & 0xFFFFE000u;
-                                lo[j] = __float_as_uint(pv - __uint_as_float(hi[j]));
+                                split_hi_lo(pv, hi[j], lo[j]);
                             }
                         }
                     } else {
@@ -571,9 +674,7 @@ attn_kernel(const __grid_constant__ CUtensorMap mx1, const __grid_constant__ CUt
                             for (int j = 0; j < 32; j++) {
                                 const bool vis = (col0 + j <= row);
                                 const float pv = vis ? fast_exp2(fmaf(s[j], p.c2, -lse_r)) : 0.0f;
-                                const float ds = (pv * (dp[j] - d_r)) * p.scale;
-                                hi[j] = __float_as_uint(ds) & 0xFFFFE000u;
-                                lo[j] = __float_as_uint(ds - __uint_as_float(hi[j]));
+                                split_hi_lo((pv * (dp[j] - d_r)) * p.scale, hi[j], lo[j]);
                             }
                         } else {   // ATT_BWD_K
 #pragma unroll
@@ -590,24 +691,31 @@ attn_kernel(const __grid_constant__ CUtensorMap mx1, const __grid_constant__ CUt
                                     const int j = 4 * j4 + e;
                                     const bool vis = (row <= qc + e) && (qc + e < p.T);
                                     const float pv = vis ? fast_exp2(fmaf(s[j], p.c2, -ls[e])) : 0.0f;
-                                    const float ds = (pv * (dp[j] - dd[e])) * p.scale;
-                                    hi[j] = __float_as_uint(ds) & 0xFFFFE000u;
-                                    lo[j] = __float_as_uint(ds - __uint_as_float(hi[j]));
+                                    split_hi_lo((pv * (dp[j] - dd[e])) * p.scale, hi[j], lo[j]);
                                 }
                             }
                         }
                     }
                     ATT_PROF_MARK2(ps)
                     tmem_st_32x32(ts, hi);
+                    if (NWB == 1 && c >= 1) {
+                        // one W_lo / accumulator buffer (dQ, dK): the previous block's second product must have finished reading
+                        // W_lo before it is overwritten; its accumulator is drained at the same time
+                        got = drain(g - 1, corr_prev);
+                        if (!got) continue;
+                    }
                     tmem_st_32x32(tl, lo);
                     tmem_st_wait();
                     tc_fence_before();
                     __syncwarp();
+#ifdef ZNN_ATTN_PROFILE
+                    if (prof_on) tstamp[4 + (g & 3)] = clock64();
+#endif
                     if (lane == 0) mbar_arrive_remote(w_ready_l0 + 8u * buf);
                     ATT_PROF_ADD2(19, ps)
                     ATT_PROF_ADD2(21, pt)
-                    // the previous block's second product has had this block's transform time to finish
-                    if (c >= 1) got = drain(g - 1, corr_prev);
+                    // two buffers: the previous block's second product has had this block's transform time to finish
+                    if (NWB == 2 && c >= 1) got = drain(g - 1, corr_prev);
                     corr_prev = corr;
                 }
                 if (got) got = drain(g - 1, corr_prev);
@@ -623,7 +731,7 @@ attn_kernel(const __grid_constant__ CUtensorMap mx1, const __grid_constant__ CUt
                     pair_sync();      // the slot may be rewritten by the next unit's first block (same parity)
                 }
                 if (row_ok && got) {
-                    float* dst = p.out + (size_t)d.b * p.stride_b + (size_t)d.h * p.stride_h + (size_t)row * p.ld + 32 * half;
+                    float* dst = p.out + row_off;
 #pragma unroll
                     for (int i = 0; i < 32; i += 4) {
                         if (32 * half + i >= hs) continue;
@@ -752,9 +860,9 @@ static int launch_attn(const float* X1, const float* X2, const float* Y1, const 
         ZNN_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmemBytes));
         attr_set[dev] = true;
     }
-    CUtensorMap mx1, mx2, my1, my2, mz;
+    CUtensorMap mx2, my1, my2, mz;
     int rc;
-    if ((rc = make_attn_map(&mx1, X1, L, kRowsPerCta))) return rc;
+    p.x1 = X1;
     if ((rc = make_attn_map(&mx2, X2 ? X2 : X1, L, kRowsPerCta))) return rc;
     if ((rc = make_attn_map(&my1, Y1, L, 32))) return rc;
     if ((rc = make_attn_map(&my2, Y2 ? Y2 : Y1, L, 32))) return rc;
@@ -782,7 +890,7 @@ static int launch_attn(const float* X1, const float* X2, const float* Y1, const 
     const long units = (long)p.nslices * p.nrb;
     const long pairs = units < pairs_by_device[dev] ? units : pairs_by_device[dev];
     cfg.gridDim = dim3((unsigned)(2 * pairs), 1, 1);
-    ZNN_CUDA_OK(cudaLaunchKernelEx(&cfg, kern, mx1, mx2, my1, my2, mz, p));
+    ZNN_CUDA_OK(cudaLaunchKernelEx(&cfg, kern, mx2, my1, my2, mz, p));
     count_launch();
     if (inject_launch_failure()) return fail(ZNN_ERR_CUDA, "launch of the attention kernel failed: injected failure (znn_debug_fail_after)");
     return ZNN_OK;
@@ -817,7 +925,7 @@ static AttnParams attn_params(const AttnLayout& L, float scale)
     p.scale = scale;
     p.c2 = scale * 1.4426950408889634f;
     p.ld = L.ld; p.stride_h = L.stride_h; p.stride_b = L.stride_b;
-    p.out = nullptr; p.lse = nullptr; p.dvec = nullptr;
+    p.x1 = nullptr; p.out = nullptr; p.lse = nullptr; p.dvec = nullptr;
     p.accumulate = 0;
     p.status = device_status_word();
     p.wait_limit = tc_wait_limit();
