@@ -20,6 +20,7 @@ The default run (--workload all) prints ONE JSON line: the MatMul step (value, r
 e2e through znn_matmul_host_fwd_bwd with pinned host tensors, cpu_baseline, clocks) with a "gpt" object inside
 (GPT training step of the workload definition, tokens/s).  Other workloads, one JSON line each:
   --workload matmul | gpt   one of the two parts alone (used for profiler captures)
+  --workload cnn_dp         the padded CNN step, global batch 256 split over the ranks (data parallel, strong scaling)
   --workload sweep          every shape of the MatMul sweep, forward and both backward products
   --workload configs        MLP / CNN / transformer-block / greedy-decode configurations
   --workload rowops         HBM bandwidth of the row-wise kernels
@@ -297,6 +298,14 @@ def run_gpu(args):
         if world > 1:
             dist.destroy_process_group()
         return 0
+    if args.workload == "cnn_dp":       # the data-parallel CNN step alone
+        cnn = cnn_dp_part(args, L, torch, dist, stream, world, rank)
+        if rank == 0:
+            cnn.update({"higher_is_better": True, "vs_baseline": None, "dtype": "f32", "data": "synthetic"})
+            print(json.dumps(cnn), flush=True)
+        if world > 1:
+            dist.destroy_process_group()
+        return 0
     if args.workload == "gpt":          # the GPT training step alone (used for profiling captures)
         gpt = gpt_part(args, L, torch, dist, stream, world, rank, local)
         if rank == 0:
@@ -417,9 +426,10 @@ def run_gpu(args):
         tf32_live = 2.0 * n ** 3 / (best * 1e-3) / 1e12
         torch.backends.cuda.matmul.allow_tf32 = False
 
-    gpt = sweep = configs = None
+    gpt = sweep = configs = cnn = None
     if args.workload == "all":
         gpt = gpt_part(args, L, torch, dist, stream, world, rank, local)
+        cnn = cnn_dp_part(args, L, torch, dist, stream, world, rank)
         if world == 1:
             # the other shapes and configurations of the workload definition, compact, in the same record
             peaks_now, _ = read_peaks()
@@ -462,6 +472,8 @@ def run_gpu(args):
         }
         if gpt is not None:
             line["gpt"] = gpt
+        if cnn is not None:
+            line["cnn"] = cnn
         if sweep is not None:
             line["sweep"] = sweep
         if configs is not None:
@@ -475,6 +487,111 @@ def run_gpu(args):
     if world > 1:
         dist.destroy_process_group()
     return 0
+
+
+def dp_init(L, torch, dist, world, rank):
+    """One NCCL communicator per rank for the shim's gradient exchange; the 128-byte id travels over torch.distributed."""
+    if world <= 1:
+        return
+    uid = torch.zeros(128, dtype=torch.uint8, device="cuda")
+    if rank == 0:
+        buf = C.create_string_buffer(128)
+        L.call("znn_dp_unique_id", buf)
+        uid.copy_(torch.frombuffer(bytearray(buf.raw), dtype=torch.uint8))
+    dist.broadcast(uid, src=0)
+    torch.cuda.synchronize()
+    L.call("znn_dp_init", world, rank, bytes(uid.cpu().numpy().tobytes()))
+
+
+def param_checksum(m):
+    """A position-sensitive checksum of every parameter's bit pattern (below 2^52, so that it survives a float64)."""
+    import numpy as np
+    P = m.get_params()
+    h = 0
+    for name in sorted(P):
+        a = np.ascontiguousarray(P[name]).view(np.uint32).astype(np.uint64)
+        h = (h * 1000003 + int(a.sum() % (1 << 61)) + int((a[::7] * np.uint64(2654435761)).sum() % (1 << 61))) % (1 << 61)
+    return h % (1 << 52)
+
+
+def cnn_dp_part(args, L, torch, dist, stream, world, rank):
+    """Config 3 data parallel (strong scaling): the padded CNN (1->32->64 3x3 pad 1, 3136->128->10) on a GLOBAL batch of
+    256 images split evenly over the ranks, gradients summed by NCCL and applied with 1/world.  Self-check printed with
+    the numbers: replicas bit-identical after the timed steps, and the loss of the first five steps equal (1e-4) to the
+    same model trained on the whole batch by one GPU."""
+    import numpy as np
+    from znn_b200.models import Model
+    G = 256
+    if G % world:
+        return {"unavailable": f"global batch {G} does not split over {world} ranks"}
+    Bper = G // world
+    r = np.random.default_rng(5)                          # the same on every rank
+    steps_check = 5
+    X = (r.integers(0, 256, (steps_check, G, 784)).astype(np.float32) / np.float32(255.0))
+    Y = r.integers(0, 10, (steps_check, G)).astype(np.int32)
+
+    def fresh():
+        m = Model("cnn_padded", (), arena_bytes=2 << 30)
+        rr = np.random.default_rng(6)
+        P = {}
+        for name, shape, _, fan_in in m.params:
+            P[name] = ((rr.standard_normal(shape, np.float32) * np.float32((2.0 / fan_in) ** 0.5)) if fan_in
+                       else np.zeros(shape, np.float32))
+        m.set_params(P)
+        m.set_option("lr", 0.01)
+        m.set_option("momentum", 0.9)
+        return m
+
+    dp_init(L, torch, dist, world, rank)
+    m = fresh()
+    sl = slice(rank * Bper, (rank + 1) * Bper)
+    dp_losses = []
+    for s in range(steps_check):
+        local = m.train_step(X[s, sl], Y[s, sl])
+        t = torch.tensor([local], device="cuda", dtype=torch.float64)
+        if world > 1:
+            dist.all_reduce(t)
+        dp_losses.append(float(t.item()) / world)
+    dx, dt = torch.from_numpy(X[0, sl].copy()).cuda(), torch.from_numpy(Y[0, sl].copy()).cuda()
+    steps, warmup = 100, 10
+    for _ in range(warmup):
+        m.train_step_device(dx.data_ptr(), dt.data_ptr(), Bper)
+    if world > 1:
+        dist.barrier()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record(stream)
+    for _ in range(steps):
+        m.train_step_device(dx.data_ptr(), dt.data_ptr(), Bper)
+    e1.record(stream)
+    if world > 1:
+        dist.barrier()
+    torch.cuda.synchronize()
+    t = torch.tensor([e0.elapsed_time(e1)], device="cuda", dtype=torch.float64)
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    ms = float(t.item())
+    h = torch.tensor([float(param_checksum(m))], device="cuda", dtype=torch.float64)
+    lo, hi = h.clone(), h.clone()
+    if world > 1:
+        dist.all_reduce(lo, op=dist.ReduceOp.MIN)
+        dist.all_reduce(hi, op=dist.ReduceOp.MAX)
+    identical = bool(lo.item() == hi.item())
+    m.close()
+    if world > 1:
+        L.call("znn_dp_finalize")
+    m1 = fresh()                                          # the same five steps on the whole batch, one GPU, no exchange
+    single = [m1.train_step(X[s], Y[s]) for s in range(steps_check)]
+    m1.close()
+    worst = max(abs(a - b) / abs(b) for a, b in zip(dp_losses, single))
+    if not identical or worst > 1e-4:
+        raise SystemExit(f"CNN data-parallel parity check failed: replicas identical {identical}, loss rel diff {worst:.3e}")
+    return {"metric": "cnn_train_images_per_s", "value": G * steps / (ms * 1e-3), "unit": "images/s", "n_gpus": world,
+            "steps": steps, "warmup": warmup, "ms_per_step": ms / steps, "scaling": "strong",
+            "config": {"workload": "cnn_padded_train_step", "global_batch": G, "per_gpu_batch": Bper, "parallelism": f"dp{world}",
+                       "optimizer": "SGD momentum 0.9"},
+            "dp_parity": {"replicas_bit_identical": identical, "loss_max_rel_diff_vs_single_gpu": worst, "steps": steps_check,
+                          "bar": 1e-4, "passed": True}}
 
 
 def sweep_compact(rows, peaks):
@@ -527,15 +644,7 @@ def gpt_part(args, L, torch, dist, stream, world, rank, local):
     from znn_b200.models import Model
 
     V, T, D, H, NL, B = 8192, 1024, 768, 12, 6, 8
-    if world > 1:
-        uid = torch.zeros(128, dtype=torch.uint8, device="cuda")
-        if rank == 0:
-            buf = C.create_string_buffer(128)
-            L.call("znn_dp_unique_id", buf)
-            uid.copy_(torch.frombuffer(bytearray(buf.raw), dtype=torch.uint8))
-        dist.broadcast(uid, src=0)
-        torch.cuda.synchronize()
-        L.call("znn_dp_init", world, rank, bytes(uid.cpu().numpy().tobytes()))
+    dp_init(L, torch, dist, world, rank)
     m = Model("gpt", (V, T, D, H, NL), arena_bytes=30 << 30)
     r = np.random.default_rng(42)                       # the same seed on every rank: identical replicas
     P = {}
@@ -632,12 +741,7 @@ def dp_parity_check(L, torch, dist, m, world, rank):
     slab is min- and max-reduced over the ranks; (2) a small GPT trained for a few steps with the batch sharded over
     the ranks must follow the loss of the same model trained on the whole batch by one GPU (second half of the check
     runs after the communicator is gone: dp_small_model_check(phase='single'))."""
-    import numpy as np
-    P = m.get_params()
-    h = 0
-    for name in sorted(P):
-        a = np.ascontiguousarray(P[name]).view(np.uint32).astype(np.uint64)
-        h = (h * 1000003 + int(a.sum() % (1 << 61)) + int((a[::7] * np.uint64(2654435761)).sum() % (1 << 61))) % (1 << 61)
+    h = param_checksum(m)
     t = torch.tensor([float(h % (1 << 52))], device="cuda", dtype=torch.float64)
     lo, hi = t.clone(), t.clone()
     dist.all_reduce(lo, op=dist.ReduceOp.MIN)
@@ -1023,7 +1127,7 @@ def main():
     ap.add_argument("--shape", default="1024,64,1024,111,111,96",
                     help="--workload shape: M,N,K,trans_a,trans_b,batch of one (batched) product")
     ap.add_argument("--path", type=int, default=0, help="--workload shape: GEMM path (0 = automatic)")
-    ap.add_argument("--workload", default="all", choices=["all", "matmul", "gpt", "configs", "rowops", "shape", "sweep"],
+    ap.add_argument("--workload", default="all", choices=["all", "matmul", "gpt", "cnn_dp", "configs", "rowops", "shape", "sweep"],
                     help="matmul: the headline MatMul sweep step only; all: also the GPT training step; "
                          "configs: the MLP / CNN / block / decode configs on one GPU")
     args = ap.parse_args()

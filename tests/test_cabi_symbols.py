@@ -32,6 +32,20 @@ def test_every_declared_symbol_is_exported(dll):
         assert not missing, f"declared in {header} but not exported: {missing}"
 
 
+def test_zig_binding_declares_every_function_of_the_cuda_header():
+    """znn_b200/bindings/cuda.zig is the reference-side binding file: one `pub extern fn` per function of
+    include/znn_cuda.h, with the same number of parameters."""
+    import re
+    here = os.path.dirname(os.path.abspath(_lib.__file__))
+    zig = open(os.path.join(here, "bindings", "cuda.zig")).read()
+    decls = {m.group(1): m.group(2) for m in re.finditer(r"pub extern fn (\w+)\(([^)]*)\)", zig)}
+    header = [h for h in _lib.ALL_HEADERS if h.endswith("znn_cuda.h")][0]
+    for name, types in _lib.declared_functions(header):
+        assert name in decls, f"{name} missing from cuda.zig"
+        nargs = len([a for a in decls[name].split(",") if a.strip()])
+        assert nargs == len(types), f"{name}: {nargs} parameters in cuda.zig, {len(types)} in the header"
+
+
 def test_ctypes_signatures_resolve():
     L = _lib.lib()
     for name, types in _lib.all_declared_functions():
