@@ -42,6 +42,17 @@ int znn_gemm_profile_read(double* kernel_ms, long long* launches, double* flops)
  * [21] load-to-hand-off of one block.  32 values. */
 int znn_debug_attn_profile(long long* out32);
 
+/* Conv2D path of the calling host thread: 0 (default) = layers with Ci*KH*KW >= 64 taps, at most 64 output channels and at
+ * least 4096 output pixels run as implicit-im2col GEMMs on the tensor cores; 1 = never (direct kernels and the explicit
+ * im2col lowering), for A/B comparisons. */
+int znn_debug_set_conv_path(int mode);
+/* Role profile of the tensor-core convolution kernel, filled only by a build with -DZNN_CONV_PROFILE (all zero otherwise):
+ * cycles one lane of each role of CTA 0 spent, summed over the launches since the last read: [0] producer loop, [1] gather
+ * issue, [2] wait for a free stage, [3] split + store, [4] proxy fence, [5] hand-off; [6] MMA loop, [7] wait for a full
+ * stage, [8] wait for a drained accumulator, [9] issue; [10] epilogue loop, [11] wait for a finished chunk, [12] drain,
+ * [13] store.  16 values. */
+int znn_debug_conv_profile(long long* out16);
+
 /* ---- test hooks ---- */
 /* SM cycles a GEMM role waits on an mbarrier before it gives up, sets a ZNN_DEV_*_WAIT_EXPIRED bit in the device status
  * word and leaves (default 4e9, about 2 s; 0 restores the default).  Applies to kernels launched afterwards. */

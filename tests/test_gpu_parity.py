@@ -204,6 +204,62 @@ def test_conv2d(ops, zo, N, Ci, H, W, Co, K, pad):
     close(g1, h1, rtol=3e-5, what="conv dW only")
 
 
+TC_CONV_CASES = [
+    # N, Ci, H, W, Co, KH, KW, pad: layers the tensor-core path takes (>= 64 taps, <= 64 channels, >= 4096 pixels)
+    (256, 32, 14, 14, 64, 3, 3, 1),   # second layer of the padded CNN at its stated batch
+    (64, 8, 16, 16, 16, 3, 3, 1),     # 32-wide column tile
+    (48, 12, 11, 13, 20, 3, 3, 0),    # ragged, no padding
+    (32, 7, 12, 12, 33, 5, 5, 2),     # 825 taps in the data gradient: several accumulation chunks
+    (40, 9, 10, 14, 24, 3, 5, 1),     # KH != KW
+]
+
+
+@pytest.mark.parametrize("N,Ci,H,W,Co,KH,KW,pad", TC_CONV_CASES)
+def test_conv2d_tensor_path(ops, zo, N, Ci, H, W, Co, KH, KW, pad):
+    """Implicit-im2col GEMM path against the reference loops (src/tensor.zig:523-585, src/autodiff.zig:929-995):
+    forward and dX within 1e-5 of scale, dW and dbias within 3e-5; and against the direct/im2col path of the library."""
+    from znn_b200 import _lib
+    L = _lib.lib()
+    r = rng(N + Ci * 10 + H * 100 + Co * 1000 + pad + KW)
+    X = r.random((N, Ci, H, W), np.float32)
+    Wt = (r.standard_normal((Co, Ci, KH, KW)) * 0.3).astype(np.float32)
+    b = (r.standard_normal(Co) * 0.1).astype(np.float32)
+    Y1, Y2 = ops.conv2d_fwd(X, Wt, b, pad), zo.conv2d_fwd(X, Wt, b, pad)
+    close(Y1, Y2, what="conv fwd (tensor path)")
+    close(ops.conv2d_fwd(X, Wt, None, pad), zo.conv2d_fwd(X, Wt, None, pad), what="conv fwd without bias")
+    dY = r.standard_normal(Y2.shape, np.float32)
+    dY[r.random(Y2.shape) < 0.3] = 0.0
+    # the backward arms accumulate: start from non-zero gradients
+    g0 = [r.standard_normal(X.shape, np.float32), r.standard_normal(Wt.shape, np.float32), r.standard_normal(Co).astype(np.float32)]
+    g = [a.copy() for a in g0]
+    h = [a.copy() for a in g0]
+    ops.conv2d_bwd(X, Wt, dY, g[0], g[1], g[2], pad)
+    zo.conv2d_bwd(X, Wt, dY, h[0], h[1], h[2], pad)
+    close(g[0], h[0], what="conv dX")
+    close(g[1], h[1], rtol=3e-5, what="conv dW")
+    close(g[2], h[2], rtol=3e-5, what="conv dbias")
+    L.call("znn_debug_set_conv_path", 1)
+    try:
+        Yd = ops.conv2d_fwd(X, Wt, b, pad)
+        d = [a.copy() for a in g0]
+        ops.conv2d_bwd(X, Wt, dY, d[0], d[1], d[2], pad)
+    finally:
+        L.call("znn_debug_set_conv_path", 0)
+    np.testing.assert_array_equal(Yd, Y2)      # the direct kernel keeps the reference's order: bit-exact
+    close(g[0], d[0], what="dX, tensor path vs im2col path")
+    close(g[1], d[1], rtol=3e-5, what="dW, tensor path vs im2col path")
+    # weight gradient alone (first layer of a network), data gradient alone
+    g1, h1 = np.zeros_like(Wt), np.zeros_like(Wt)
+    ops.conv2d_bwd(X, Wt, dY, None, g1, None, pad)
+    zo.conv2d_bwd(X, Wt, dY, None, h1, None, pad)
+    close(g1, h1, rtol=3e-5, what="conv dW only")
+    g2, h2 = np.zeros_like(X), np.zeros_like(X)
+    ops.conv2d_bwd(X, Wt, dY, g2, None, None, pad)
+    zo.conv2d_bwd(X, Wt, dY, h2, None, None, pad)
+    close(g2, h2, what="conv dX only")
+    ops.check_device_status()
+
+
 @pytest.mark.parametrize("N,C,H,W,pool,stride", [(1, 1, 4, 4, 2, 2), (64, 4, 26, 26, 2, 2), (64, 8, 11, 11, 2, 2),
                                                 (8, 32, 28, 28, 2, 2), (3, 2, 7, 9, 3, 2), (2, 2, 8, 8, 3, 1)])
 def test_maxpool2d(ops, zo, N, C, H, W, pool, stride):

@@ -27,6 +27,7 @@ SOURCES = [
     ("hostop.cu", []),
     ("rowops.cu", ["-fmad=false"]),
     ("conv.cu", ["-fmad=false"]),
+    ("conv_tc.cu", []),
     ("dp.cu", []),
     ("host/graph.cpp", []),
     ("host/nn.cpp", []),

@@ -11,6 +11,7 @@
 // -fmad=false, its rounding points: the forward pass is bit-identical to the
 // reference loops, which is what keeps MaxPool argmax indices bit-exact.
 #include "common.cuh"
+#include "../../include/znn_debug.h"
 
 namespace znn {
 
@@ -248,11 +249,120 @@ __global__ void col2im_add_kernel(const float* __restrict__ dcol, float* __restr
     }
 }
 
+// ---- weight and bias gradients of a layer with few taps (K = Ci*KH*KW <= 40): no im2col matrix, no GEMM ----
+// A block walks its share of the output pixels in tiles of 128: the taps under the tile's pixels and the tile of dY go
+// to shared memory (coalesced along the pixels), then thread (co, k) adds the tile's 128 products to its sum; k = K is
+// the bias column (a tap that is always 1).  Blocks write partial sums; a second kernel adds them in block order.
+constexpr int kSkTile = 128;
+constexpr int kSkThreads = 320;
+__global__ void __launch_bounds__(kSkThreads)
+conv2d_bwd_weight_smallk_kernel(const float* __restrict__ X, const float* __restrict__ dY, float* __restrict__ partial,
+                                int Ci, int H, int Wd, int Co, int KH, int KW, int pad, int Ho, int Wo, long long P,
+                                long long pix_per_block)
+{
+    extern __shared__ float sh[];
+    const int K = Ci * KH * KW, K1 = K + 1;
+    constexpr int pitch = kSkTile + 1;
+    float* const cols = sh;                 // [K1][pitch]
+    float* const dys = sh + K1 * pitch;     // [Co][pitch]
+    const int pairs = Co * K1;
+    const int i0 = threadIdx.x, i1 = threadIdx.x + kSkThreads;
+    const int co0 = i0 / K1, k0 = i0 - co0 * K1, co1 = i1 / K1, k1 = i1 - co1 * K1;
+    float acc0 = 0.0f, acc1 = 0.0f;
+    const int HoWo = Ho * Wo;
+    const long long p_begin = blockIdx.x * pix_per_block;
+    const long long p_end = p_begin + pix_per_block < P ? p_begin + pix_per_block : P;
+    for (long long t0 = p_begin; t0 < p_end; t0 += kSkTile) {
+        for (int i = threadIdx.x; i < K1 * kSkTile; i += kSkThreads) {
+            const int k = i / kSkTile, j = i - k * kSkTile;
+            const long long pix = t0 + j;
+            float v = 0.0f;
+            if (pix < p_end) {
+                if (k == K) {
+                    v = 1.0f;
+                } else {
+                    const int n = (int)(pix / HoWo), hw = (int)(pix - (long long)n * HoWo);
+                    const int h = hw / Wo, w = hw - h * Wo;
+                    const int kw = k % KW, kh = (k / KW) % KH, ci = k / (KW * KH);
+                    const int ih = h + kh - pad, iw = w + kw - pad;
+                    if (ih >= 0 && ih < H && iw >= 0 && iw < Wd) v = X[(((size_t)n * Ci + ci) * H + ih) * Wd + iw];
+                }
+            }
+            cols[k * pitch + j] = v;
+        }
+        for (int i = threadIdx.x; i < Co * kSkTile; i += kSkThreads) {
+            const int co = i / kSkTile, j = i - co * kSkTile;
+            const long long pix = t0 + j;
+            float v = 0.0f;
+            if (pix < p_end) {
+                const int n = (int)(pix / HoWo), hw = (int)(pix - (long long)n * HoWo);
+                v = dY[((size_t)n * Co + co) * HoWo + hw];
+            }
+            dys[co * pitch + j] = v;
+        }
+        __syncthreads();
+        if (i0 < pairs) {
+            const float* a = dys + co0 * pitch;
+            const float* b = cols + k0 * pitch;
+#pragma unroll 8
+            for (int j = 0; j < kSkTile; j++) acc0 += a[j] * b[j];
+        }
+        if (i1 < pairs) {
+            const float* a = dys + co1 * pitch;
+            const float* b = cols + k1 * pitch;
+#pragma unroll 8
+            for (int j = 0; j < kSkTile; j++) acc1 += a[j] * b[j];
+        }
+        __syncthreads();
+    }
+    if (i0 < pairs) partial[(size_t)blockIdx.x * pairs + i0] = acc0;
+    if (i1 < pairs) partial[(size_t)blockIdx.x * pairs + i1] = acc1;
+}
+
+__global__ void conv2d_bwd_weight_smallk_reduce_kernel(const float* __restrict__ partial, int blocks, int Co, int K,
+                                                       float* __restrict__ dW, float* __restrict__ dbias)
+{
+    const int K1 = K + 1, pairs = Co * K1;
+    const int i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= pairs) return;
+    const int co = i / K1, k = i - co * K1;
+    if ((k == K) ? !dbias : !dW) return;
+    float s = 0.0f;
+    for (int b = 0; b < blocks; b++) s += partial[(size_t)b * pairs + i];
+    if (k == K) dbias[co] += s;
+    else dW[(size_t)co * K + k] += s;
+}
+
+// the tensor-core path (conv_tc.cu)
+bool conv_tc_applicable(long long n, int C, int H, int W, int Co, int KH, int KW, int Ho, int Wo);
+int conv_tc_forward(const float* src, const float* wm, const float* bias, float* out, int N, int C, int H, int W, int Co,
+                    int KH, int KW, int pad_h, int pad_w, int accumulate);
+void conv_set_path(int mode);
+int conv_profile_read(long long* out16);
+size_t conv_tc_wgrad_scratch(long long P, int K, int Co);
+int conv_tc_wgrad(const float* X, const float* dY, float* dW, float* dbias, float* scratch, int N, int Ci, int H, int W,
+                  int Co, int KH, int KW, int pad, int Ho, int Wo);
+int conv_tc_dgrad(const float* dY, const float* Wgt, float* dX, float* wt, int N, int Ci, int H, int W, int Co, int KH, int KW,
+                  int pad, int Ho, int Wo);
+
 }  // namespace znn
 
 using namespace znn;
 
 extern "C" {
+
+int znn_debug_set_conv_path(int mode)
+{
+    ZNN_REQUIRE(mode == 0 || mode == 1, "mode is 0 or 1");
+    conv_set_path(mode);
+    return ZNN_OK;
+}
+
+int znn_debug_conv_profile(long long* out16)
+{
+    ZNN_REQUIRE(out16, "out16 is NULL");
+    return conv_profile_read(out16);
+}
 
 int znn_conv2d_fwd(const float* X, const float* W, const float* bias, float* Y, int N, int Ci, int H, int Wd, int Co,
                    int KH, int KW, int pad)
@@ -263,6 +373,8 @@ int znn_conv2d_fwd(const float* X, const float* W, const float* bias, float* Y, 
     if (N == 0) return ZNN_OK;
     if (!stream()) return fail(ZNN_ERR_CUDA, "no CUDA device state; call znn_init (no CPU fallback)");
     ZNN_REQUIRE(X && W && Y, "NULL pointer");
+    if (conv_tc_applicable(N, Ci, H, Wd, Co, KH, KW, Ho, Wo))   // implicit-im2col GEMM on the tensor cores
+        return conv_tc_forward(X, W, bias, Y, N, Ci, H, Wd, Co, KH, KW, pad, pad, 0);
     const size_t smem = (size_t)kCoTile * Ci * KH * KW * sizeof(float);
     ZNN_REQUIRE(smem <= 96 * 1024, "Ci*KH*KW = %d is beyond what the direct kernel keeps in shared memory", Ci * KH * KW);
     if (smem > 48 * 1024)
@@ -285,6 +397,51 @@ int znn_conv2d_bwd(const float* X, const float* W, const float* dY, float* dX, f
     ZNN_REQUIRE(X && W && dY, "NULL pointer");
     const size_t P = (size_t)N * Ho * Wo;   // output pixels
     const int K = Ci * KH * KW;
+    {
+        // Tensor-core path: weight (and bias) gradient with the pixels as the contraction, data gradient as a
+        // convolution of dY with the flipped weights; neither writes an im2col matrix.  What it does not take
+        // falls through to the paths below.
+        const bool tc_w = (dW || dbias) && conv_tc_applicable(N, Ci, H, Wd, Co, KH, KW, Ho, Wo);
+        const bool tc_x = dX && pad <= KH - 1 && pad <= KW - 1 && conv_tc_applicable(N, Co, Ho, Wo, Ci, KH, KW, H, Wd);
+        if (tc_w || tc_x) {
+            const size_t wg_f = tc_w ? conv_tc_wgrad_scratch((long long)P, K, Co) : 0;
+            const size_t wt_f = tc_x ? (size_t)Co * K : 0;
+            float* ws = (float*)workspace_slot(1, (wg_f + wt_f) * sizeof(float));
+            if (!ws) return fail(ZNN_ERR_NOMEM, "conv backward scratch (%zu bytes)", (wg_f + wt_f) * sizeof(float));
+            int rc;
+            if (tc_w) {
+                if ((rc = conv_tc_wgrad(X, dY, dW, dbias, ws, N, Ci, H, Wd, Co, KH, KW, pad, Ho, Wo))) return rc;
+                dW = nullptr;
+                dbias = nullptr;
+            }
+            if (tc_x) {
+                if ((rc = conv_tc_dgrad(dY, W, dX, ws + wg_f, N, Ci, H, Wd, Co, KH, KW, pad, Ho, Wo))) return rc;
+                dX = nullptr;
+            }
+            if (!dW && !dbias && !dX) return ZNN_OK;
+        }
+    }
+    if ((dW || dbias) && P >= 4096 && K <= 40 && Co <= 64 && Co * (K + 1) <= 2 * kSkThreads) {
+        // few taps: per-block partial sums over the pixels, added in block order (no im2col matrix, no GEMM)
+        const int blocks = sm_count() * 2;
+        long long per = ((long long)P + blocks - 1) / blocks;
+        per = (per + kSkTile - 1) / kSkTile * kSkTile;
+        const int used = (int)(((long long)P + per - 1) / per);
+        const int pairs = Co * (K + 1);
+        float* part = (float*)workspace_slot(1, (size_t)used * pairs * sizeof(float));
+        if (!part) return fail(ZNN_ERR_NOMEM, "conv backward scratch");
+        const size_t smem = (size_t)(K + 1 + Co) * (kSkTile + 1) * sizeof(float);
+        if (smem > 48 * 1024)
+            ZNN_CUDA_OK(cudaFuncSetAttribute(conv2d_bwd_weight_smallk_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+        conv2d_bwd_weight_smallk_kernel<<<used, kSkThreads, smem, stream()>>>(X, dY, part, Ci, H, Wd, Co, KH, KW, pad, Ho, Wo,
+                                                                              (long long)P, per);
+        ZNN_LAUNCH_OK("conv2d_bwd_weight_smallk_kernel");
+        conv2d_bwd_weight_smallk_reduce_kernel<<<(pairs + 127) / 128, 128, 0, stream()>>>(part, used, Co, K, dW, dbias);
+        ZNN_LAUNCH_OK("conv2d_bwd_weight_smallk_reduce_kernel");
+        dW = nullptr;
+        dbias = nullptr;
+        if (!dX) return ZNN_OK;
+    }
     // Large layers: lower the backward pass to GEMMs over an explicit im2col matrix (the contraction runs
     // on the tensor cores / the split-K FMA kernel).  Tiny layers keep the direct kernels below.
     if (P >= 4096 && P * (size_t)K <= ((size_t)1 << 31) && P <= 0x7fffffff / 2) {
