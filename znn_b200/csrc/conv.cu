@@ -254,11 +254,11 @@ __global__ void col2im_add_kernel(const float* __restrict__ dcol, float* __restr
 // to shared memory (coalesced along the pixels), then thread (co, k) adds the tile's 128 products to its sum; k = K is
 // the bias column (a tap that is always 1).  Blocks write partial sums; a second kernel adds them in block order.
 constexpr int kSkTile = 128;
-constexpr int kSkThreads = 320;
+constexpr int kSkThreads = 384;
 __global__ void __launch_bounds__(kSkThreads)
 conv2d_bwd_weight_smallk_kernel(const float* __restrict__ X, const float* __restrict__ dY, float* __restrict__ partial,
-                                int Ci, int H, int Wd, int Co, int KH, int KW, int pad, int Ho, int Wo, long long P,
-                                long long pix_per_block)
+                                int Ci, int H, int Wd, int Co, int KH, int KW, int pad, int Ho, int Wo, int P,
+                                int pix_per_block)
 {
     extern __shared__ float sh[];
     const int K = Ci * KH * KW, K1 = K + 1;
@@ -269,49 +269,51 @@ conv2d_bwd_weight_smallk_kernel(const float* __restrict__ X, const float* __rest
     const int i0 = threadIdx.x, i1 = threadIdx.x + kSkThreads;
     const int co0 = i0 / K1, k0 = i0 - co0 * K1, co1 = i1 / K1, k1 = i1 - co1 * K1;
     float acc0 = 0.0f, acc1 = 0.0f;
-    const int HoWo = Ho * Wo;
-    const long long p_begin = blockIdx.x * pix_per_block;
-    const long long p_end = p_begin + pix_per_block < P ? p_begin + pix_per_block : P;
-    for (long long t0 = p_begin; t0 < p_end; t0 += kSkTile) {
-        for (int i = threadIdx.x; i < K1 * kSkTile; i += kSkThreads) {
-            const int k = i / kSkTile, j = i - k * kSkTile;
-            const long long pix = t0 + j;
-            float v = 0.0f;
-            if (pix < p_end) {
-                if (k == K) {
-                    v = 1.0f;
-                } else {
-                    const int n = (int)(pix / HoWo), hw = (int)(pix - (long long)n * HoWo);
-                    const int h = hw / Wo, w = hw - h * Wo;
-                    const int kw = k % KW, kh = (k / KW) % KH, ci = k / (KW * KH);
-                    const int ih = h + kh - pad, iw = w + kw - pad;
-                    if (ih >= 0 && ih < H && iw >= 0 && iw < Wd) v = X[(((size_t)n * Ci + ci) * H + ih) * Wd + iw];
-                }
-            }
-            cols[k * pitch + j] = v;
+    const int HoWo = Ho * Wo, HW = H * Wd;
+    const int p_begin = blockIdx.x * pix_per_block;
+    const int p_end = min(P, p_begin + pix_per_block);
+    // loading: thread = (pixel j of the tile, one of three row groups); the pixel is decoded once per tile
+    const int j = threadIdx.x & (kSkTile - 1), grp = threadIdx.x / kSkTile;
+    for (int t0 = p_begin; t0 < p_end; t0 += kSkTile) {
+        const int pix = t0 + j;
+        const bool pv = pix < p_end;
+        int n = 0, h = 0, w = 0, hw = 0;
+        if (pv) {
+            n = pix / HoWo; hw = pix - n * HoWo;
+            h = hw / Wo; w = hw - h * Wo;
         }
-        for (int i = threadIdx.x; i < Co * kSkTile; i += kSkThreads) {
-            const int co = i / kSkTile, j = i - co * kSkTile;
-            const long long pix = t0 + j;
-            float v = 0.0f;
-            if (pix < p_end) {
-                const int n = (int)(pix / HoWo), hw = (int)(pix - (long long)n * HoWo);
-                v = dY[((size_t)n * Co + co) * HoWo + hw];
+        const float* const xn = X + (size_t)n * Ci * HW;
+        const float* const dyn = dY + (size_t)n * Co * HoWo + hw;
+        for (int row = grp; row < K1 + Co; row += kSkThreads / kSkTile) {
+            if (row < K1) {
+                float v = 0.0f;
+                if (pv) {
+                    if (row == K) {
+                        v = 1.0f;
+                    } else {
+                        const int kw = row % KW, kh = (row / KW) % KH, ci = row / (KW * KH);
+                        const int ih = h + kh - pad, iw = w + kw - pad;
+                        if (ih >= 0 && ih < H && iw >= 0 && iw < Wd) v = xn[(size_t)ci * HW + ih * Wd + iw];
+                    }
+                }
+                cols[row * pitch + j] = v;
+            } else {
+                const int co = row - K1;
+                dys[co * pitch + j] = pv ? dyn[(size_t)co * HoWo] : 0.0f;
             }
-            dys[co * pitch + j] = v;
         }
         __syncthreads();
         if (i0 < pairs) {
             const float* a = dys + co0 * pitch;
             const float* b = cols + k0 * pitch;
 #pragma unroll 8
-            for (int j = 0; j < kSkTile; j++) acc0 += a[j] * b[j];
+            for (int jj = 0; jj < kSkTile; jj++) acc0 += a[jj] * b[jj];
         }
         if (i1 < pairs) {
             const float* a = dys + co1 * pitch;
             const float* b = cols + k1 * pitch;
 #pragma unroll 8
-            for (int j = 0; j < kSkTile; j++) acc1 += a[j] * b[j];
+            for (int jj = 0; jj < kSkTile; jj++) acc1 += a[jj] * b[jj];
         }
         __syncthreads();
     }
@@ -421,7 +423,7 @@ int znn_conv2d_bwd(const float* X, const float* W, const float* dY, float* dX, f
             if (!dW && !dbias && !dX) return ZNN_OK;
         }
     }
-    if ((dW || dbias) && P >= 4096 && K <= 40 && Co <= 64 && Co * (K + 1) <= 2 * kSkThreads) {
+    if ((dW || dbias) && P >= 4096 && P < ((size_t)1 << 30) && K <= 40 && Co <= 64 && Co * (K + 1) <= 2 * kSkThreads) {
         // few taps: per-block partial sums over the pixels, added in block order (no im2col matrix, no GEMM)
         const int blocks = sm_count() * 2;
         long long per = ((long long)P + blocks - 1) / blocks;
@@ -434,7 +436,7 @@ int znn_conv2d_bwd(const float* X, const float* W, const float* dY, float* dX, f
         if (smem > 48 * 1024)
             ZNN_CUDA_OK(cudaFuncSetAttribute(conv2d_bwd_weight_smallk_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
         conv2d_bwd_weight_smallk_kernel<<<used, kSkThreads, smem, stream()>>>(X, dY, part, Ci, H, Wd, Co, KH, KW, pad, Ho, Wo,
-                                                                              (long long)P, per);
+                                                                              (int)P, (int)per);
         ZNN_LAUNCH_OK("conv2d_bwd_weight_smallk_kernel");
         conv2d_bwd_weight_smallk_reduce_kernel<<<(pairs + 127) / 128, 128, 0, stream()>>>(part, used, Co, K, dW, dbias);
         ZNN_LAUNCH_OK("conv2d_bwd_weight_smallk_reduce_kernel");

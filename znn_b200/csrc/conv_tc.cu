@@ -132,7 +132,8 @@ __global__ void __launch_bounds__(kCvThreads, 1) conv_tc_kernel(const ConvTcPara
     static_assert(8 * (2 * S + 4) <= 96, "barrier block");
     volatile uint32_t* const words = reinterpret_cast<volatile uint32_t*>(smem_gen + S * kStageBytes + 96);
     const uint32_t tmem_slot_addr = bar_base + 96;
-    int2* const tab = reinterpret_cast<int2*>(smem_gen + S * kStageBytes + 128);
+    float* const sbias = reinterpret_cast<float*>(smem_gen + S * kStageBytes + 128);   // [NT], zero past Co
+    int2* const tab = reinterpret_cast<int2*>(smem_gen + S * kStageBytes + 128 + NT * 4);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int HW = p.H * p.W, HoWo = p.Ho * p.Wo;
@@ -153,6 +154,8 @@ __global__ void __launch_bounds__(kCvThreads, 1) conv_tc_kernel(const ConvTcPara
         tmem_alloc<1>(tmem_slot_addr, kTmemCols);
         tmem_relinquish<1>();
     }
+    if (threadIdx.x < NT)
+        sbias[threadIdx.x] = (MODE == CV_FWD && p.bias && (int)threadIdx.x < p.Co) ? p.bias[threadIdx.x] : 0.0f;
     // Table entry k = (ci, kh, kw): x = offset of the element from the row's own pixel, y = tap = kh * KW + kw, the bit
     // of the row's border mask that says whether the element lies inside the input (31 = beyond K: never valid).
     // Channel-major order keeps the taps of one channel together: they touch the same few cache lines.
@@ -241,7 +244,7 @@ __global__ void __launch_bounds__(kCvThreads, 1) conv_tc_kernel(const ConvTcPara
                 const uint32_t pmask = pvalid ? tap_mask(h, w) : 0u;
 #pragma unroll
                 for (int i = 0; i < 16; i++) {
-                    const int kg = un.mt * 128 + pw + kCvProducerWarps * i;
+                    const int kg = un.mt * 128 + 16 * pw + i;   // consecutive taps: the same few cache lines
                     const int2 te = tab[kg];
                     float x = ((pmask >> te.y) & 1u) ? __ldg(srow + te.x) : 0.0f;
                     if (kg == p.K) x = pvalid ? 1.0f : 0.0f;   // the bias row: sums dY over the pixels
@@ -250,7 +253,7 @@ __global__ void __launch_bounds__(kCvThreads, 1) conv_tc_kernel(const ConvTcPara
                 const float* const drow = p.bmat + (long long)n * p.Co * HoWo + hw;
 #pragma unroll
                 for (int i = 0; i < NT / kCvProducerWarps; i++) {
-                    const int row = pw + kCvProducerWarps * i;
+                    const int row = (NT / kCvProducerWarps) * pw + i;
                     xb[i] = (pvalid && row < p.Co) ? __ldg(drow + (long long)row * HoWo) : 0.0f;
                 }
             }
@@ -310,7 +313,7 @@ __global__ void __launch_bounds__(kCvThreads, 1) conv_tc_kernel(const ConvTcPara
                 const int soff = ((lane >> 2) << 4), sw = (lane & 3) * 4;
 #pragma unroll
                 for (int i = 0; i < 16; i++) {
-                    const int row = pw + kCvProducerWarps * i;
+                    const int row = 16 * pw + i;
                     float hi, lo;
                     split_tf32(ya[i], hi, lo);
                     const int off = row * 128 + (soff ^ ((row & 7) << 4)) + sw;
@@ -319,7 +322,7 @@ __global__ void __launch_bounds__(kCvThreads, 1) conv_tc_kernel(const ConvTcPara
                 }
 #pragma unroll
                 for (int i = 0; i < NT / kCvProducerWarps; i++) {
-                    const int row = pw + kCvProducerWarps * i;
+                    const int row = (NT / kCvProducerWarps) * pw + i;
                     float hi, lo;
                     split_tf32(yb[i], hi, lo);
                     const int off = row * 128 + (soff ^ ((row & 7) << 4)) + sw;
@@ -425,13 +428,21 @@ __global__ void __launch_bounds__(kCvThreads, 1) conv_tc_kernel(const ConvTcPara
                 if (pp < p.P) {
                     const int n = (int)(pp / HoWo), hw = (int)(pp - (long long)n * HoWo);
                     float* const o = p.out + (long long)n * p.Co * HoWo + hw;
+                    // sixteen channels at a time, the loads of the old values (accumulating form) issued together:
+                    // one store per channel, each a run of consecutive pixels across the warp
 #pragma unroll
-                    for (int c = 0; c < NT; c++) {
-                        if (c < p.Co) {
-                            float* const oc = o + (long long)c * HoWo;
-                            if (p.accumulate) *oc += acc[c];
-                            else *oc = p.bias ? acc[c] + __ldg(p.bias + c) : acc[c];
+                    for (int c0 = 0; c0 < NT; c0 += 16) {
+                        float add[16];
+                        if (p.accumulate) {
+#pragma unroll
+                            for (int j = 0; j < 16; j++) add[j] = (c0 + j < p.Co) ? o[(long long)(c0 + j) * HoWo] : 0.0f;
+                        } else {
+#pragma unroll
+                            for (int j = 0; j < 16; j++) add[j] = sbias[c0 + j];
                         }
+#pragma unroll
+                        for (int j = 0; j < 16; j++)
+                            if (c0 + j < p.Co) o[(long long)(c0 + j) * HoWo] = acc[c0 + j] + add[j];
                     }
                 }
             } else {
@@ -486,7 +497,7 @@ int launch_conv_tc(const ConvTcParams& p)
     int dev = 0;
     ZNN_CUDA_OK(cudaGetDevice(&dev));
     const int tab = (MODE == CV_FWD) ? p.kblocks * 32 : p.rows;
-    const size_t smem = (size_t)kCvStages * (2 * kCvABytes + 2 * NT * 128) + 1024 + 128 + (size_t)tab * sizeof(int2);
+    const size_t smem = (size_t)kCvStages * (2 * kCvABytes + 2 * NT * 128) + 1024 + 128 + NT * 4 + (size_t)tab * sizeof(int2);
     if (smem > 227 * 1024) return fail(ZNN_ERR_UNSUPPORTED, "conv tensor path: tap table beyond shared memory");
     if (dev < 64 && !attr_set[dev]) {
         ZNN_CUDA_OK(cudaFuncSetAttribute(conv_tc_kernel<MODE, NT>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024));
