@@ -20,6 +20,8 @@ The default run (--workload all) prints ONE JSON line: the MatMul step (value, r
 e2e through znn_matmul_host_fwd_bwd with pinned host tensors, cpu_baseline, clocks) with a "gpt" object inside
 (GPT training step of the workload definition, tokens/s).  Other workloads, one JSON line each:
   --workload matmul | gpt   one of the two parts alone (used for profiler captures)
+  --workload attention      the fused causal-attention kernels at the sizes of configs 5 and 4 (--small: one size, few launches)
+  --workload conv           the Conv2D entry points at the padded CNN's layer shapes, both paths (--small: few launches)
   --workload cnn_dp         the padded CNN step, global batch 256 split over the ranks (data parallel, strong scaling)
   --workload sweep          every shape of the MatMul sweep, forward and both backward products
   --workload configs        MLP / CNN / transformer-block / greedy-decode configurations
@@ -295,6 +297,14 @@ def run_gpu(args):
         if rank == 0:
             print(json.dumps({"metric": "config_timings", "n_gpus": 1, "data": "synthetic",
                               "configs": configs_part(args, L, torch, stream)}), flush=True)
+        if world > 1:
+            dist.destroy_process_group()
+        return 0
+    if args.workload in ("attention", "conv"):
+        part = attention_part(args, L, torch, stream) if args.workload == "attention" else conv_part(args, L, torch, stream)
+        if rank == 0:
+            print(json.dumps({"metric": args.workload + "_kernels", "n_gpus": 1, "data": "synthetic", "dtype": "f32 (3xTF32)",
+                              args.workload: part}), flush=True)
         if world > 1:
             dist.destroy_process_group()
         return 0
@@ -1037,6 +1047,106 @@ def shape_part(args, L, torch, stream):
             "tflops": 2.0 * M * N * K * batch / us / 1e6, "rel_err_slice0_vs_fp64": err}
 
 
+def attention_part(args, L, torch, stream):
+    """The fused causal-attention kernels (znn_attn_fwd / znn_attn_bwd) at the sizes of configs 5 and 4, each launch
+    timed alone with CUDA events on the launching stream: forward, and the three backward kernels one at a time.
+    TFLOP/s = causal algorithmic flops (half the square) / time; fraction of the 3xTF32 burst ceiling."""
+    peaks, kind = read_peaks()
+    ceiling = peaks["bf16_tflops"] / 2.0 / 3.0
+    res = {}
+    p = lambda t: C.c_void_p(t.data_ptr()) if t is not None else None
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+
+    def timeit(fn, n=20):
+        for _ in range(3):
+            fn()
+        torch.cuda.synchronize()
+        e0.record(stream)
+        for _ in range(n):
+            fn()
+        e1.record(stream)
+        torch.cuda.synchronize()
+        return e0.elapsed_time(e1) / n * 1e3
+
+    shapes = {"gpt_b8_h12_t1024_hs64": (8, 12, 1024, 64), "block_b32_h8_t256_hs64": (32, 8, 256, 64)}
+    if args.small:
+        shapes = {"gpt_b8_h12_t1024_hs64": (8, 12, 1024, 64)}
+    for name, (B, nh, T, hs) in shapes.items():
+        Cw = nh * hs
+        g = torch.Generator(device="cuda").manual_seed(1)
+        Q, K, V, dO = (torch.randn((B * T, Cw), device="cuda", generator=g) for _ in range(4))
+        O, dQ, dK, dV = (torch.empty_like(Q) for _ in range(4))
+        LSE = torch.empty((B * nh, T), device="cuda")
+        sc = 1.0 / hs ** 0.5
+
+        def fwd():
+            L.call("znn_attn_fwd", p(Q), p(K), p(V), p(O), p(LSE), B, nh, T, hs, Cw, hs, T * Cw, sc)
+
+        def bwd(q, k, v):
+            L.call("znn_attn_bwd", p(Q), p(K), p(V), p(O), p(dO), p(LSE), p(dQ) if q else None, p(dK) if k else None,
+                   p(dV) if v else None, B, nh, T, hs, Cw, hs, T * Cw, sc, 0)
+
+        prod = 2.0 * B * nh * T * T * hs / 2            # one causal product
+        rows = {"fwd": (timeit(fwd, 3 if args.small else 20), 2 * prod),
+                "dQ": (timeit(lambda: bwd(1, 0, 0), 3 if args.small else 20), 3 * prod),   # S, dP, dS.K
+                "dK": (timeit(lambda: bwd(0, 1, 0), 3 if args.small else 20), 3 * prod),   # S^T, dP^T, dS^T.Q
+                "dV": (timeit(lambda: bwd(0, 0, 1), 3 if args.small else 20), 2 * prod)}   # S^T, P^T.dO
+        st = C.c_int()
+        L.call("znn_device_status", C.byref(st), 1)
+        res[name] = {k: {"us": round(us, 1), "tflops": round(fl / us / 1e6, 1), "frac": round(fl / us / 1e6 / ceiling, 3)}
+                     for k, (us, fl) in rows.items()}
+        res[name]["layer_us"] = round(sum(us for us, _ in rows.values()), 1)
+        res[name]["io_MB_fwd"] = round(4 * B * T * Cw * 4 / 1e6, 1)
+        res[name]["device_status"] = st.value
+    res["ceiling"] = f"{kind}: bf16 burst {peaks['bf16_tflops']} TF/s / 2 / 3"
+    return res
+
+
+def conv_part(args, L, torch, stream):
+    """Conv2D entry points at the layer shapes of config 3 (padded CNN, batch 256), each launch timed alone with CUDA
+    events: tensor-core path (implicit im2col) against the direct / explicit-im2col path of the same library."""
+    p = lambda t: C.c_void_p(t.data_ptr()) if t is not None else None
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+
+    def timeit(fn, n=20):
+        for _ in range(3):
+            fn()
+        torch.cuda.synchronize()
+        e0.record(stream)
+        for _ in range(n):
+            fn()
+        e1.record(stream)
+        torch.cuda.synchronize()
+        return e0.elapsed_time(e1) / n * 1e3
+
+    res = {}
+    n_it = 3 if args.small else 20
+    for name, (N, Ci, H, W, Co, K, pad) in {"conv2_b256_32to64_14x14": (256, 32, 14, 14, 64, 3, 1),
+                                            "conv1_b256_1to32_28x28": (256, 1, 28, 28, 32, 3, 1)}.items():
+        Ho, Wo = H + 2 * pad - K + 1, W + 2 * pad - K + 1
+        X = torch.rand(N, Ci, H, W, device="cuda")
+        Wt = torch.randn(Co, Ci, K, K, device="cuda") * 0.1
+        b = torch.randn(Co, device="cuda")
+        Y = torch.empty(N, Co, Ho, Wo, device="cuda")
+        dY = torch.randn_like(Y)
+        dX, dW, db = torch.zeros_like(X), torch.zeros_like(Wt), torch.zeros_like(b)
+        fl = 2.0 * N * Ho * Wo * Ci * K * K * Co
+        row = {}
+        for path, label in ((0, "default"), (1, "direct_or_explicit_im2col")):
+            L.call("znn_debug_set_conv_path", path)
+            f = timeit(lambda: L.call("znn_conv2d_fwd", p(X), p(Wt), p(b), p(Y), N, Ci, H, W, Co, K, K, pad), n_it)
+            bw = timeit(lambda: L.call("znn_conv2d_bwd", p(X), p(Wt), p(dY), None, p(dW), p(db), N, Ci, H, W, Co, K, K, pad), n_it)
+            bx = timeit(lambda: L.call("znn_conv2d_bwd", p(X), p(Wt), p(dY), p(dX), None, None, N, Ci, H, W, Co, K, K, pad), n_it)
+            row[label] = {"fwd_us": round(f, 1), "dW_dbias_us": round(bw, 1), "dX_us": round(bx, 1),
+                          "fwd_tflops": round(fl / f / 1e6, 2)}
+        L.call("znn_debug_set_conv_path", 0)
+        res[name] = row
+    st = C.c_int()
+    L.call("znn_device_status", C.byref(st), 1)
+    res["device_status"] = st.value
+    return res
+
+
 def rowops_part(args, L, torch, stream):
     """Row-wise / elementwise kernels at transformer sizes, each timed alone with CUDA events on the launching
     stream; working sets exceed the 126 MB L2.  GB/s = algorithmic bytes per launch / time, compared with the
@@ -1122,12 +1232,14 @@ def main():
     ap.add_argument("--n", type=int, default=8192)
     ap.add_argument("--impl", default="znn_b200", choices=["znn_b200", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--small", action="store_true",
+                    help="--workload attention|conv: one size and three timed launches per kernel (for profiler captures)")
     ap.add_argument("--dp-bucket-mb", type=int, default=0,
                     help="GPT workload, N > 1: size of the gradient all-reduce buckets in MB (0 = the library default, 32)")
     ap.add_argument("--shape", default="1024,64,1024,111,111,96",
                     help="--workload shape: M,N,K,trans_a,trans_b,batch of one (batched) product")
     ap.add_argument("--path", type=int, default=0, help="--workload shape: GEMM path (0 = automatic)")
-    ap.add_argument("--workload", default="all", choices=["all", "matmul", "gpt", "cnn_dp", "configs", "rowops", "shape", "sweep"],
+    ap.add_argument("--workload", default="all", choices=["all", "matmul", "gpt", "cnn_dp", "configs", "rowops", "shape", "sweep", "attention", "conv"],
                     help="matmul: the headline MatMul sweep step only; all: also the GPT training step; "
                          "configs: the MLP / CNN / block / decode configs on one GPU")
     args = ap.parse_args()

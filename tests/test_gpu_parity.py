@@ -142,7 +142,7 @@ def test_causal_softmax(ops, zo, ns, T):
 
 
 @pytest.mark.parametrize("rows,D", [(1, 1), (2, 3), (64, 512), (100, 768), (7, 1001), (33, 4), (9, 256), (5, 260), (10, 772),
-                                    (3, 1024), (3, 1028)])
+                                    (3, 1024), (3, 1028), (5000, 768), (9000, 256)])
 def test_rmsnorm_layernorm(ops, zo, rows, D):
     r = rng(rows * 3 + D)
     X = r.standard_normal((rows, D), np.float32)
@@ -314,7 +314,8 @@ def test_embedding(ops, zo, V, D, shape):
 
 
 @pytest.mark.parametrize("shape,d0,d1", [((2, 3), 0, 1), ((4, 16, 12, 64), 1, 2), ((2, 3, 5, 7), 2, 3),
-                                          ((2, 12, 100, 64), 2, 3), ((3, 4, 5), 0, 2), ((33, 65), 0, 1)])
+                                          ((2, 12, 100, 64), 2, 3), ((3, 4, 5), 0, 2), ((33, 65), 0, 1), ((3, 132, 72), 1, 2),
+                                          ((5, 200, 68), 1, 2)])
 def test_transpose(ops, zo, shape, d0, d1):
     r = rng(sum(shape))
     A = r.standard_normal(shape, np.float32)

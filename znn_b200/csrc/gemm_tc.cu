@@ -671,6 +671,46 @@ __device__ __forceinline__ void epilogue_store_vec(const float (&acc)[CPT], floa
         }
         return;
     }
+    if (!ep_p && rows == 32 && cbase + CPT <= N) {
+        // full block with a bias row and / or beta != 0 (every Linear forward, every accumulating gradient product):
+        // staged like the form above; the old values of C for four row groups are loaded together, then four
+        // combine-and-store chains.  Same arithmetic order as the general form below: alpha * acc, + bias, + beta * old.
+        constexpr int NB = CPT / 32;
+        const size_t off = (size_t)(row_base + lane / 8) * out_ld + cbase + 4 * (lane % 8);
+#pragma unroll
+        for (int b0 = 0; b0 < NB; b0++) {
+#pragma unroll
+            for (int f = 0; f < 8; f++)
+                st4[lane * 8 + (f ^ (lane & 7))] =
+                    make_float4(acc[32 * b0 + 4 * f], acc[32 * b0 + 4 * f + 1], acc[32 * b0 + 4 * f + 2], acc[32 * b0 + 4 * f + 3]);
+            __syncwarp();
+            float4 bb = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+            if (bias) bb = *reinterpret_cast<const float4*>(bias + cbase + 32 * b0 + 4 * (lane % 8));
+#pragma unroll
+            for (int i0 = 0; i0 < 8; i0 += 4) {
+                float4 old[4];
+                if (beta != 0.0f) {
+#pragma unroll
+                    for (int i = 0; i < 4; i++) {
+                        const int ri = (i0 + i + rot) % 8;
+                        old[i] = *reinterpret_cast<const float4*>(out + off + (size_t)(4 * ri) * out_ld + 32 * b0);
+                    }
+                }
+#pragma unroll
+                for (int i = 0; i < 4; i++) {
+                    const int ri = (i0 + i + rot) % 8;
+                    const int r = 4 * ri + lane / 8;
+                    const float4 v = st4[r * 8 + ((lane % 8) ^ (r & 7))];
+                    float4 o = make_float4(alpha * v.x, alpha * v.y, alpha * v.z, alpha * v.w);
+                    if (bias) { o.x += bb.x; o.y += bb.y; o.z += bb.z; o.w += bb.w; }
+                    if (beta != 0.0f) { o.x += beta * old[i].x; o.y += beta * old[i].y; o.z += beta * old[i].z; o.w += beta * old[i].w; }
+                    *reinterpret_cast<float4*>(out + off + (size_t)(4 * ri) * out_ld + 32 * b0) = o;
+                }
+            }
+            __syncwarp();
+        }
+        return;
+    }
     if (fast_p) {
         // the softmax-backward form on full blocks, staged the same way: P for four row groups in flight, then four
         // load-combine-store chains

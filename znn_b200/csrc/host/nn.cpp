@@ -152,7 +152,8 @@ Tensor* CausalSelfAttention::forward(Graph& g, Tensor* x) const
     Tensor* q_2d = q_attn.forward(g, x_2d);
     Tensor* k_2d = k_attn.forward(g, x_2d);
     Tensor* v_2d = v_attn.forward(g, x_2d);
-    if (fused_softmax && g_fused_attention && (hs == 32 || hs == 64) && T % 4 == 0) {
+    // (short sequences keep the separate products: a 256-row unit of the fused kernel is mostly empty below T = 128)
+    if (fused_softmax && g_fused_attention && (hs == 32 || hs == 64) && T % 4 == 0 && T >= 128) {
         // one op on the projections where they lie: the heads are read and written through strides
         Tensor* y_2d = g.causalAttention(q_2d, k_2d, v_2d, B, T, nh, 1.0f / sqrtf((float)hs));
         Tensor* out_2d = c_proj.forward(g, y_2d);

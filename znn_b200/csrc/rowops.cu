@@ -645,6 +645,80 @@ __global__ void rmsnorm_bwd_rows_reg_kernel(const float* __restrict__ X, const f
     }
 }
 
+// The same with the gain gradient in the same pass: a warp walks rows gw, gw + nw, ... and keeps its share of
+// dG[c] = sum_r dY[r,c] * x[r,c] * scale_r in registers; the block's eight warps are added in warp order and the
+// block's partial row goes to partial[blockIdx.x][D] (a second kernel adds the blocks in order: deterministic for a
+// given grid).  X and dY are read once: 16 bytes per element with the accumulating dX.
+template <int V4>
+__global__ void __launch_bounds__(256)
+rmsnorm_bwd_dg_reg_kernel(const float* __restrict__ X, const float* __restrict__ G, const float* __restrict__ dY, float eps,
+                          float* __restrict__ dX, float* __restrict__ partial, size_t rows, int D)
+{
+    __shared__ float4 red[8][32 * V4];
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nv = D >> 2;
+    const size_t gw = blockIdx.x * (size_t)8 + warp, nw = (size_t)gridDim.x * 8;
+    const float4* g = reinterpret_cast<const float4*>(G);
+    float4 dg[V4];
+#pragma unroll
+    for (int k = 0; k < V4; k++) dg[k] = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+    const float fd = (float)D;
+    for (size_t row = gw; row < rows; row += nw) {
+        const float4* x = reinterpret_cast<const float4*>(X + row * D);
+        const float4* dy = reinterpret_cast<const float4*>(dY + row * D);
+        float4 xv[V4], dv[V4], ov[V4];   // the old dX is fetched with X and dY: one memory latency per row
+        float4* dx = dX ? reinterpret_cast<float4*>(dX + row * D) : nullptr;
+        float s = 0.0f, t = 0.0f;
+#pragma unroll
+        for (int k = 0; k < V4; k++) {
+            const int i = lane + 32 * k;
+            if (i < nv) {
+                xv[k] = x[i];
+                dv[k] = dy[i];
+                if (dx) ov[k] = dx[i];
+            }
+        }
+#pragma unroll
+        for (int k = 0; k < V4; k++) {
+            const int i = lane + 32 * k;
+            if (i < nv) {
+                const float4 gg = g[i];
+                s += (xv[k].x * xv[k].x + xv[k].y * xv[k].y) + (xv[k].z * xv[k].z + xv[k].w * xv[k].w);
+                t += ((dv[k].x * gg.x) * xv[k].x + (dv[k].y * gg.y) * xv[k].y) + ((dv[k].z * gg.z) * xv[k].z + (dv[k].w * gg.w) * xv[k].w);
+            }
+        }
+        s = warp_sum(s);
+        t = warp_sum(t);
+        const float scale = 1.0f / sqrtf(s / fd + eps);
+#pragma unroll
+        for (int k = 0; k < V4; k++) {
+            const int i = lane + 32 * k;
+            if (i < nv) {
+                dg[k].x += dv[k].x * xv[k].x * scale; dg[k].y += dv[k].y * xv[k].y * scale;
+                dg[k].z += dv[k].z * xv[k].z * scale; dg[k].w += dv[k].w * xv[k].w * scale;
+                if (dx) {
+                    const float4 gg = g[i];
+                    float4 o = ov[k];
+                    o.x += scale * (dv[k].x * gg.x - xv[k].x * scale * scale * t / fd);
+                    o.y += scale * (dv[k].y * gg.y - xv[k].y * scale * scale * t / fd);
+                    o.z += scale * (dv[k].z * gg.z - xv[k].z * scale * scale * t / fd);
+                    o.w += scale * (dv[k].w * gg.w - xv[k].w * scale * scale * t / fd);
+                    dx[i] = o;
+                }
+            }
+        }
+    }
+#pragma unroll
+    for (int k = 0; k < V4; k++) red[warp][lane + 32 * k] = dg[k];
+    __syncthreads();
+    float4* out = reinterpret_cast<float4*>(partial + (size_t)blockIdx.x * D);
+    for (int i = threadIdx.x; i < nv; i += 256) {
+        float4 u = red[0][i];
+#pragma unroll
+        for (int w = 1; w < 8; w++) { const float4 v = red[w][i]; u.x += v.x; u.y += v.y; u.z += v.z; u.w += v.w; }
+        out[i] = u;
+    }
+}
+
 __global__ void layernorm_fwd_kernel(const float* __restrict__ X, const float* __restrict__ G,
                                      const float* __restrict__ Bt, float eps, float* __restrict__ Y, size_t rows, int D)
 {
@@ -713,6 +787,25 @@ __global__ void embedding_fwd_kernel(const float* __restrict__ W, const float* _
         }
         const float* w = W + (size_t)idf * D;
         for (int j = threadIdx.x; j < D; j += blockDim.x) y[j] = w[j];
+    }
+}
+
+// One warp per output row, 16-byte copies (D a multiple of 4, 16-byte aligned table and output).
+__global__ void embedding_fwd_vec_kernel(const float4* __restrict__ W, const float* __restrict__ ids, float4* __restrict__ Y,
+                                         size_t n, int D4, int vocab, int* __restrict__ status)
+{
+    const int lane = threadIdx.x & 31;
+    const size_t nw = (size_t)gridDim.x * (blockDim.x >> 5);
+    for (size_t i = blockIdx.x * (size_t)(blockDim.x >> 5) + (threadIdx.x >> 5); i < n; i += nw) {
+        const float idf = ids[i];
+        float4* y = Y + i * D4;
+        if (!(idf >= 0.0f && idf < (float)vocab)) {
+            for (int j = lane; j < D4; j += 32) y[j] = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+            if (lane == 0) atomicOr(status, ZNN_DEV_BAD_INDEX);
+            continue;
+        }
+        const float4* w = W + (size_t)idf * D4;
+        for (int j = lane; j < D4; j += 32) y[j] = w[j];
     }
 }
 
@@ -855,6 +948,39 @@ __global__ void transpose_last2_kernel(const float* __restrict__ in, float* __re
         if (orow < in_cols && ocol < in_rows) {
             float* p = dst + (size_t)orow * in_rows + ocol;
             if (Backward) *p += tile[threadIdx.x][j]; else *p = tile[threadIdx.x][j];
+        }
+    }
+}
+
+// The same through a 64 x 64 tile with 16-byte global accesses in both directions (R and Cc multiples of 4, 16-byte
+// aligned tensors): 16 KB per block instead of 4 KB and a quarter of the memory instructions.
+template <bool Backward>
+__global__ void __launch_bounds__(256) transpose_last2_vec_kernel(const float* __restrict__ in, float* __restrict__ out, int R, int Cc)
+{
+    __shared__ float tile[64][65];
+    const size_t slice = blockIdx.z;
+    const int in_rows = Backward ? Cc : R, in_cols = Backward ? R : Cc;
+    const float* src = in + slice * (size_t)R * Cc;
+    float* dst = out + slice * (size_t)R * Cc;
+    const int c0 = blockIdx.x * 64, r0 = blockIdx.y * 64;
+#pragma unroll
+    for (int k = 0; k < 4; k++) {
+        const int idx = threadIdx.x + 256 * k, r = idx >> 4, c4 = idx & 15;
+        const int gr = r0 + r, gc = c0 + 4 * c4;
+        float4 v = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+        if (gr < in_rows && gc < in_cols) v = *reinterpret_cast<const float4*>(src + (size_t)gr * in_cols + gc);
+        tile[r][4 * c4] = v.x; tile[r][4 * c4 + 1] = v.y; tile[r][4 * c4 + 2] = v.z; tile[r][4 * c4 + 3] = v.w;
+    }
+    __syncthreads();
+#pragma unroll
+    for (int k = 0; k < 4; k++) {
+        const int idx = threadIdx.x + 256 * k, orow = idx >> 4, oc4 = idx & 15;   // output is [in_cols, in_rows]
+        const int go = c0 + orow, gc = r0 + 4 * oc4;
+        if (go < in_cols && gc < in_rows) {
+            float4 v = make_float4(tile[4 * oc4][orow], tile[4 * oc4 + 1][orow], tile[4 * oc4 + 2][orow], tile[4 * oc4 + 3][orow]);
+            float4* p = reinterpret_cast<float4*>(dst + (size_t)go * in_rows + gc);
+            if (Backward) { const float4 o = *p; v.x += o.x; v.y += o.y; v.z += o.z; v.w += o.w; }
+            *p = v;
         }
     }
 }
@@ -1362,6 +1488,22 @@ int znn_rmsnorm_bwd(const float* X, const float* G, const float* dY, float eps, 
     if (rows == 0 || D <= 0 || (!dX && !dG)) return ZNN_OK;
     ZNN_NEED_DEVICE();
     ZNN_REQUIRE(rows <= 0x7fffffff, "too many rows");
+    const bool v4 = (D % 4 == 0) && ((((uintptr_t)X | (uintptr_t)G | (uintptr_t)dY | (uintptr_t)dX) & 15) == 0);
+    if (dG && v4 && D <= 1024) {
+        // one pass: dX and per-block partial rows of dG, then the blocks are added in order
+        size_t blocks = (rows + 7) / 8;
+        const size_t cap = (size_t)sm_count() * 4;
+        if (blocks > cap) blocks = cap;
+        float* partial = (float*)workspace(blocks * (size_t)D * sizeof(float));
+        if (!partial) return fail(ZNN_ERR_NOMEM, "scratch for RmsNorm backward");
+        if (D <= 256) rmsnorm_bwd_dg_reg_kernel<2><<<(unsigned)blocks, 256, 0, stream()>>>(X, G, dY, eps, dX, partial, rows, D);
+        else if (D <= 768) rmsnorm_bwd_dg_reg_kernel<6><<<(unsigned)blocks, 256, 0, stream()>>>(X, G, dY, eps, dX, partial, rows, D);
+        else rmsnorm_bwd_dg_reg_kernel<8><<<(unsigned)blocks, 256, 0, stream()>>>(X, G, dY, eps, dX, partial, rows, D);
+        ZNN_LAUNCH_OK("rmsnorm_bwd_dg_reg_kernel");
+        colsum_stage2_kernel<<<ceil_div(D, 32), dim3(32, 8), 0, stream()>>>(partial, dG, (int)blocks, D);
+        ZNN_LAUNCH_OK("colsum_stage2_kernel");
+        return ZNN_OK;
+    }
     int chunks = 0, rpc = 0;
     float* rowscale = nullptr;
     float* partial = nullptr;
@@ -1372,7 +1514,6 @@ int znn_rmsnorm_bwd(const float* X, const float* G, const float* dY, float eps, 
         rowscale = ws;
         partial = ws + rows;
     }
-    const bool v4 = (D % 4 == 0) && ((((uintptr_t)X | (uintptr_t)G | (uintptr_t)dY | (uintptr_t)dX) & 15) == 0);
     const dim3 rgrid = row_blocks(rows, 8);
     if (v4 && D <= 256) rmsnorm_bwd_rows_reg_kernel<2><<<rgrid, 256, 0, stream()>>>(X, G, dY, eps, dX, rowscale, rows, D);
     else if (v4 && D <= 768) rmsnorm_bwd_rows_reg_kernel<6><<<rgrid, 256, 0, stream()>>>(X, G, dY, eps, dX, rowscale, rows, D);
@@ -1437,6 +1578,15 @@ int znn_embedding_fwd(const float* W, const float* ids, float* Y, size_t n, int 
     if (n == 0 || D <= 0) return ZNN_OK;
     ZNN_NEED_DEVICE();
     ZNN_REQUIRE(vocab > 0, "vocab must be positive");
+    if ((D & 3) == 0 && (((uintptr_t)W | (uintptr_t)Y) & 15) == 0) {
+        size_t vblocks = (n + 7) / 8;
+        const size_t cap = (size_t)sm_count() * 32;
+        if (vblocks > cap) vblocks = cap;
+        embedding_fwd_vec_kernel<<<(unsigned)vblocks, 256, 0, stream()>>>((const float4*)W, ids, (float4*)Y, n, D / 4, vocab,
+                                                                          device_status_word());
+        ZNN_LAUNCH_OK("embedding_fwd_vec_kernel");
+        return ZNN_OK;
+    }
     const unsigned blocks = (unsigned)(n < 65535u * 16u ? n : 65535u * 16u);
     embedding_fwd_kernel<<<blocks, D >= 256 ? 256 : 64, 0, stream()>>>(W, ids, Y, n, D, vocab, device_status_word());
     ZNN_LAUNCH_OK("embedding_fwd_kernel");
@@ -1468,6 +1618,14 @@ static int transpose_impl(const float* in, float* out, const int64_t* dims, int 
         size_t slices = 1;
         for (int k = 0; k < rank - 2; k++) slices *= (size_t)dims[k];
         const int R = (int)dims[rank - 2], Cc = (int)dims[rank - 1];
+        if (slices <= 65535 && (R & 3) == 0 && (Cc & 3) == 0 && (((uintptr_t)in | (uintptr_t)out) & 15) == 0) {
+            const int in_rows = backward ? Cc : R, in_cols = backward ? R : Cc;
+            dim3 grid(ceil_div(in_cols, 64), ceil_div(in_rows, 64), (unsigned)slices);
+            if (backward) transpose_last2_vec_kernel<true><<<grid, 256, 0, stream()>>>(in, out, R, Cc);
+            else transpose_last2_vec_kernel<false><<<grid, 256, 0, stream()>>>(in, out, R, Cc);
+            ZNN_LAUNCH_OK("transpose_last2_vec_kernel");
+            return ZNN_OK;
+        }
         if (slices <= 65535) {
             const int in_rows = backward ? Cc : R, in_cols = backward ? R : Cc;
             dim3 grid(ceil_div(in_cols, 32), ceil_div(in_rows, 32), (unsigned)slices), block(32, 8);
