@@ -667,6 +667,8 @@ def gpt_part(args, L, torch, dist, stream, world, rank, local):
     del P
     m.set_option("lr", 0.01)
     m.set_option("momentum", 0.9)
+    if os.environ.get("ZNN_BENCH_FUSED_EPILOGUE"):      # A/B of the epilogue forms (bit mask, see znn_host.h)
+        m.set_option("fused_epilogue", int(os.environ["ZNN_BENCH_FUSED_EPILOGUE"]))
     if args.dp_bucket_mb > 0:
         m.set_option("dp_bucket_floats", args.dp_bucket_mb * (1 << 20) // 4)
     rr = np.random.default_rng(1000 + rank)             # each rank its own shard of the global batch

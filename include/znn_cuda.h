@@ -180,6 +180,18 @@ int znn_rowdot(const float* A, const float* B, float* out, size_t rows, int D);
  * dbias += column sums of dY; NULL gradient pointers are skipped. */
 int znn_linear_fwd(const float* X, const float* W, const float* bias, float* Y, int M, int K, int N);
 int znn_linear_bwd(const float* X, const float* W, const float* dY, float* dX, float* dW, float* dbias, int M, int K, int N);
+/* Linear with the next elementwise step folded into the GEMM epilogue (src/nn.zig:660-668: gelu(c_fc(x)); :996-1021:
+ * x + c_proj(...)):  h = X.W + bias (+ residual);  Y = act(h),  act = 0 none, 1 ReLU, 2 GELU (erf form, autodiff.zig:156-165).
+ * pre (may be NULL) receives h, which the activation's backward needs; residual (may be NULL) has Y's shape.
+ * Values equal the separate ops to fp32 rounding of the same sum.  ZNN_ERR_UNSUPPORTED when the product is too small for
+ * the tensor-core path or a pointer is not 16-byte aligned / N not a multiple of 4: the caller keeps the separate ops. */
+int znn_linear_fwd_ex(const float* X, const float* W, const float* bias, float* Y, float* pre, const float* residual, int M,
+                      int K, int N, int act);
+/* Backward of Linear whose input X is act(x_pre) of the layer below: dX receives the gradient with respect to x_pre,
+ * dX (+)= (dY.W^T) o act'(x_pre) (dx_fresh = 1 stores, 0 accumulates); dW, dbias as znn_linear_bwd.  x_act = 0: plain
+ * znn_linear_bwd.  Same ZNN_ERR_UNSUPPORTED rule. */
+int znn_linear_bwd_ex(const float* X, const float* W, const float* dY, float* dX, float* dW, float* dbias, int M, int K, int N,
+                      const float* x_pre, int x_act, int dx_fresh);
 /* path: 0 = automatic, 1 = fp32 FMA kernel, 2 = tcgen05 one CTA per tile over pre-split operand
  * planes, 3 = tcgen05 CTA pairs over pre-split planes, 4 = tcgen05 CTA pairs reading the operands
  * in place (hi/lo split in shared memory; needs 16-byte aligned bases and leading dimensions that

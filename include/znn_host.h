@@ -79,7 +79,10 @@ int znn_model_get_velocities(znn_model* m, float* host_slab);
  * skip the tiles above the causal diagonal; needs fused_softmax), "fused_softmax_bwd" (1/0, process-wide: the gradient of the attention scores comes out of
  * the dO.V^T product's epilogue, no dP buffer and no separate softmax backward), "fused_attention" (1/0, process-wide, default 1: the whole attention chain
  * as the one fused op znn_attn_fwd / znn_attn_bwd on the [B*T, C] projections when the head size is 32 or 64 and T a multiple
- * of 4; needs fused_softmax; 0 = the separate products and softmax below), "fused_qkt" (1/0, process-wide: attention scores as one
+ * of 4; needs fused_softmax; 0 = the separate products and softmax below), "fused_epilogue" (bit mask, process-wide, default 2: 1 = the residual add
+ * after an output projection, 2 = ReLU after a Linear and its derivative in backward, 4 = GELU forward, 8 = GELU derivative
+ * backward run in the epilogue of the neighbouring GEMM, znn_linear_fwd_ex / znn_linear_bwd_ex; the tape keeps the separate
+ * ops; only the ReLU form is on by default: the others measured slower than the separate kernels on the GPT step), "fused_qkt" (1/0, process-wide: attention scores as one
  * Q.K^T op instead of a transposed copy of K and a product), "alias_reshape_grad" (1/0, process-wide: Reshape views
  * share the gradient buffer of their input instead of adding into it in backward), "lazy_zero_grad" (1/0, process-wide:
  * gradient buffers of intermediates are zero-filled only when first added to; GEMM arms overwrite them with beta = 0), "dp_bucket_floats",

@@ -377,3 +377,72 @@ def test_tail_split_on_and_off(ops, form):
     np.testing.assert_array_equal(outs[0][0], outs[1][0])
     assert outs[0][1] == outs[2][1] + 1, (outs[0][1], outs[2][1])
     ops.check_device_status()
+
+
+def _gelu64(h):
+    from math import erf, sqrt
+    return 0.5 * h * (1.0 + np.vectorize(erf)(h / sqrt(2.0)))
+
+
+def _gelu_grad64(h):
+    from math import erf, sqrt, pi
+    cdf = 0.5 * (1.0 + np.vectorize(erf)(h / sqrt(2.0)))
+    return cdf + h * np.exp(-0.5 * h * h) / sqrt(2.0 * pi)
+
+
+@pytest.mark.parametrize("M,K,N", [(512, 512, 256), (1000, 200, 516), (1024, 256, 1280), (2048, 768, 3072)])
+@pytest.mark.parametrize("act,res", [(0, True), (1, False), (2, False), (1, True)])
+def test_linear_with_activation_and_residual_epilogue(ops, M, K, N, act, res):
+    """znn_linear_fwd_ex: the activation (src/autodiff.zig:148-165) and the residual add (src/nn.zig:996-1021) in the
+    GEMM epilogue, against the same steps in float64; the pre-activation copy equals the plain fused Linear bit for bit."""
+    r = np.random.default_rng(M + K + N + 7 * act)
+    X = r.standard_normal((M, K), np.float32)
+    W = (r.standard_normal((K, N)) / np.sqrt(K)).astype(np.float32)
+    b = r.standard_normal(N).astype(np.float32)
+    R = r.standard_normal((M, N), np.float32) if res else None
+    Y, H = ops.linear_fwd_ex(X, W, b, act, R, want_pre=True)
+    h64 = X.astype(np.float64) @ W.astype(np.float64) + b
+    if res:
+        h64 = h64 + R
+    y64 = h64 if act == 0 else (np.maximum(h64, 0.0) if act == 1 else _gelu64(h64))
+    scale = float(np.abs(h64).max())
+    assert float(np.abs(H - h64).max()) <= 1e-5 * scale
+    assert float(np.abs(Y - y64).max()) <= 1e-5 * scale
+    if not res:
+        np.testing.assert_array_equal(H, ops.linear_fwd(X, W, b))
+    # the activation of the stored pre-activation, by the stand-alone kernel, equals the fused output to rounding
+    if act == 1:
+        np.testing.assert_array_equal(Y, np.maximum(H, 0.0))
+    elif act == 2:
+        assert float(np.abs(Y - ops.gelu_fwd(H)).max()) <= 1e-6 * scale
+
+
+@pytest.mark.parametrize("M,K,N", [(512, 256, 512), (1000, 516, 200), (2048, 3072, 768)])
+@pytest.mark.parametrize("x_act", [1, 2])
+@pytest.mark.parametrize("fresh", [1, 0])
+def test_linear_backward_with_activation_gradient_epilogue(ops, M, K, N, x_act, fresh):
+    """znn_linear_bwd_ex: dX = (dY.W^T) o act'(x_pre) in the epilogue of the data-gradient product, stored or added."""
+    r = np.random.default_rng(M + K + N + x_act)
+    pre = r.standard_normal((M, K), np.float32)
+    X = (np.maximum(pre, 0.0) if x_act == 1 else _gelu64(pre.astype(np.float64))).astype(np.float32)
+    W = (r.standard_normal((K, N)) / np.sqrt(K)).astype(np.float32)
+    dY = r.standard_normal((M, N), np.float32)
+    dX0 = r.standard_normal((M, K), np.float32)
+    dX, dW, db = dX0.copy(), np.zeros((K, N), np.float32), np.zeros(N, np.float32)
+    ops.linear_bwd_ex(X, W, dY, dX, dW, db, pre, x_act, fresh)
+    g = dY.astype(np.float64) @ W.astype(np.float64).T
+    g = g * ((pre > 0) if x_act == 1 else _gelu_grad64(pre.astype(np.float64)))
+    want = g + (0.0 if fresh else dX0)
+    scale = float(np.abs(want).max())
+    assert float(np.abs(dX - want).max()) <= 1e-5 * scale
+    dW64 = X.astype(np.float64).T @ dY
+    assert float(np.abs(dW - dW64).max()) <= 1e-5 * float(np.abs(dW64).max())
+    assert float(np.abs(db - dY.sum(0, dtype=np.float64)).max()) <= 3e-5 * float(np.abs(dY.sum(0)).max())
+
+
+def test_fused_epilogue_refuses_small_products(ops):
+    """Below the tensor-core threshold the epilogue forms do not exist: a clear refusal, the caller keeps the two ops."""
+    from znn_b200._lib import ZnnError
+    X, W, b = np.ones((64, 32), np.float32), np.ones((32, 64), np.float32), np.zeros(64, np.float32)
+    with pytest.raises(ZnnError):
+        ops.linear_fwd_ex(X, W, b, act=1)

@@ -427,3 +427,66 @@ def test_adam_resume_continues_bit_identically(Model, tmp_path):
     got = resumed.get_params()
     assert all(np.array_equal(got[k], want[k]) for k in want)
     assert (tmp_path / "optimizer.v2").exists()
+
+
+def _launches_of(lib_, fn):
+    import ctypes as C
+    n = C.c_longlong(0)
+    lib_.call("znn_launch_count", C.byref(n), 1)
+    out = fn()
+    lib_.call("znn_launch_count", C.byref(n), 0)
+    return out, n.value
+
+
+def test_fused_epilogues_match_the_separate_ops(Model):
+    """Option fused_epilogue (bit mask; 15 = every form): GELU / ReLU after a Linear, the residual adds of a transformer
+    block and the activation derivative in backward run in GEMM epilogues (znn_linear_fwd_ex / znn_linear_bwd_ex).  The
+    tape is the same; loss and every gradient must equal the separate kernels' to fp32 rounding, with fewer launches."""
+    from znn_b200 import _lib
+    L = _lib.lib()
+    # GPT at a width that reaches the tensor-core path (the epilogue forms live there)
+    cfg = {"vocab_size": 128, "block_size": 768, "n_embd": 128, "n_head": 2, "n_layer": 2}
+    dims = (128, 768, 128, 2, 2)
+    r = np.random.default_rng(18)
+    P0 = models.init_params("gpt", cfg, seed=19)
+    x = r.integers(0, 128, (2, 768)).astype(np.float32)
+    t = r.integers(0, 128, (2, 768)).astype(np.int32)
+    res = []
+    try:
+        for fe in (15, 0):
+            m = Model("gpt", dims, arena_bytes=1 << 30)
+            m.set_params(P0)
+            m.set_option("fused_epilogue", fe)
+            m.set_option("lr", 0.0)
+            loss, launches = _launches_of(L, lambda: m.train_step(x, t, seq=768))
+            res.append((loss, m.get_grads(), m.last_step_ops(), launches))
+            m.close()
+    finally:
+        m2 = Model("mlp", (784, 128, 64, 10), arena_bytes=64 << 20)
+        m2.set_option("fused_epilogue", 2)
+        m2.close()
+    assert res[0][2] <= res[1][2] + 2 * 2               # the same ops on the tape, plus two Reshape views of the residual per layer
+    assert res[0][3] <= res[1][3] - 4 * 2               # GELU forward and backward, two residual adds: per layer
+    assert abs(res[0][0] - res[1][0]) <= 1e-6 * abs(res[1][0])
+    floor = 3e-2 * grad_floor(res[1][1])
+    for k in res[0][1]:
+        relclose(res[0][1][k], res[1][1][k], 1e-5, k, floor)
+    # MLP with ReLU at a batch whose first layer reaches the tensor-core path; the second layer falls back
+    P1 = models.init_params("mlp", (784, 128, 64, 10), seed=23)
+    xb, tb = pixels(r, 4096), r.integers(0, 10, 4096).astype(np.int32)
+    out = []
+    try:
+        for fe in (15, 0):
+            m = Model("mlp", (784, 128, 64, 10), arena_bytes=256 << 20)
+            m.set_params(P1)
+            m.set_option("fused_epilogue", fe)
+            m.set_option("lr", 0.0)
+            out.append((m.train_step(xb, tb), m.get_grads()))
+            m.close()
+    finally:
+        m2 = Model("mlp", (784, 128, 64, 10), arena_bytes=64 << 20)
+        m2.set_option("fused_epilogue", 2)
+        m2.close()
+    assert abs(out[0][0] - out[1][0]) <= 1e-6 * abs(out[1][0])
+    for k in out[0][1]:
+        relclose(out[0][1][k], out[1][1][k], 1e-5, k, 1e-2 * grad_floor(out[1][1]))

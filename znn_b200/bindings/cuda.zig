@@ -61,7 +61,7 @@ pub fn sgemm_void(order: c_int, trans_a: c_int, trans_b: c_int, m: c_int, n: c_i
 
 pub extern fn znn_init(device: c_int) c_int;
 pub extern fn znn_set_device(device: c_int) c_int;
-pub extern fn znn_device_count(count: *c_int) c_int;
+pub extern fn znn_device_count(count: ?*c_int) c_int;
 pub extern fn znn_set_stream(cuda_stream: ?*anyopaque) c_int;
 pub extern fn znn_get_stream(cuda_stream: *?*anyopaque) c_int;
 pub extern fn znn_sync() c_int;
@@ -78,7 +78,7 @@ pub extern fn znn_arena_alloc(a: ?*znn_arena, bytes: usize, ptr: *?*anyopaque) c
 pub extern fn znn_arena_reset(a: ?*znn_arena) c_int;
 pub extern fn znn_arena_usage(a: ?*znn_arena, used: ?*usize, high_water: ?*usize, capacity: ?*usize) c_int;
 pub extern fn znn_arena_destroy(a: ?*znn_arena) c_int;
-pub extern fn znn_param_slab_create(counts: [*]const usize, n: c_int, out: *?*znn_param_slab) c_int;
+pub extern fn znn_param_slab_create(counts: ?[*]const usize, n: c_int, out: *?*znn_param_slab) c_int;
 pub extern fn znn_param_slab_total(s: ?*znn_param_slab, total_floats: ?*usize) c_int;
 pub extern fn znn_param_slab_tensor(s: ?*znn_param_slab, i: c_int, value: *?[*]f32, grad: *?[*]f32, velocity: *?[*]f32, offset: ?*usize) c_int;
 pub extern fn znn_param_slab_zero_grad(s: ?*znn_param_slab) c_int;
@@ -86,10 +86,10 @@ pub extern fn znn_param_slab_sgd_step(s: ?*znn_param_slab, lr: f32, momentum: f3
 pub extern fn znn_param_slab_allreduce_grads(s: ?*znn_param_slab) c_int;
 pub extern fn znn_param_slab_destroy(s: ?*znn_param_slab) c_int;
 pub extern fn znn_last_error(buf: [*]u8, buflen: usize) c_int;
-pub extern fn znn_device_status(status: *c_int, clear: c_int) c_int;
+pub extern fn znn_device_status(status: ?*c_int, clear: c_int) c_int;
 pub extern fn znn_gemm_workspace_reserve(bytes: usize) c_int;
 pub extern fn znn_launch_count(count: ?*c_longlong, reset: c_int) c_int;
-pub extern fn znn_workspace_generation(generation: *c_ulonglong) c_int;
+pub extern fn znn_workspace_generation(generation: ?*c_ulonglong) c_int;
 pub extern fn znn_sgemm(order: c_int, trans_a: c_int, trans_b: c_int, M: c_int, N: c_int, K: c_int, alpha: f32, A: ?[*]const f32, lda: c_int, B: ?[*]const f32, ldb: c_int, beta: f32, C: ?[*]f32, ldc: c_int) c_int;
 pub extern fn znn_sgemm_batched_strided(trans_a: c_int, trans_b: c_int, M: c_int, N: c_int, K: c_int, alpha: f32, A: ?[*]const f32, lda: c_int, stride_a: c_longlong, B: ?[*]const f32, ldb: c_int, stride_b: c_longlong, beta: f32, C: ?[*]f32, ldc: c_int, stride_c: c_longlong, batch: c_int) c_int;
 pub extern fn znn_sgemm_host(order: c_int, trans_a: c_int, trans_b: c_int, M: c_int, N: c_int, K: c_int, alpha: f32, A: ?[*]const f32, lda: c_int, B: ?[*]const f32, ldb: c_int, beta: f32, C: ?[*]f32, ldc: c_int, panels: c_int) c_int;
@@ -101,6 +101,8 @@ pub extern fn znn_attn_bwd(Q: ?[*]const f32, K: ?[*]const f32, V: ?[*]const f32,
 pub extern fn znn_rowdot(A: ?[*]const f32, B: ?[*]const f32, out: ?[*]f32, rows: usize, D: c_int) c_int;
 pub extern fn znn_linear_fwd(X: ?[*]const f32, W: ?[*]const f32, bias: ?[*]const f32, Y: ?[*]f32, M: c_int, K: c_int, N: c_int) c_int;
 pub extern fn znn_linear_bwd(X: ?[*]const f32, W: ?[*]const f32, dY: ?[*]const f32, dX: ?[*]f32, dW: ?[*]f32, dbias: ?[*]f32, M: c_int, K: c_int, N: c_int) c_int;
+pub extern fn znn_linear_fwd_ex(X: ?[*]const f32, W: ?[*]const f32, bias: ?[*]const f32, Y: ?[*]f32, pre: ?[*]f32, residual: ?[*]const f32, M: c_int, K: c_int, N: c_int, act: c_int) c_int;
+pub extern fn znn_linear_bwd_ex(X: ?[*]const f32, W: ?[*]const f32, dY: ?[*]const f32, dX: ?[*]f32, dW: ?[*]f32, dbias: ?[*]f32, M: c_int, K: c_int, N: c_int, x_pre: ?[*]const f32, x_act: c_int, dx_fresh: c_int) c_int;
 pub extern fn znn_gemm_set_path(path: c_int) c_int;
 pub extern fn znn_gemm_last_path() c_int;
 pub extern fn znn_gemm_set_chunk(k_elements: c_int) c_int;
@@ -132,8 +134,8 @@ pub extern fn znn_maxpool2d_fwd(X: ?[*]const f32, Y: ?[*]f32, idx: ?[*]i32, N: c
 pub extern fn znn_maxpool2d_bwd(X: ?[*]const f32, dY: ?[*]const f32, dX: ?[*]f32, N: c_int, C: c_int, H: c_int, W: c_int, pool: c_int, stride: c_int) c_int;
 pub extern fn znn_embedding_fwd(W: ?[*]const f32, ids: ?[*]const f32, Y: ?[*]f32, n: usize, D: c_int, vocab: c_int) c_int;
 pub extern fn znn_embedding_bwd(ids: ?[*]const f32, dY: ?[*]const f32, dW: ?[*]f32, n: usize, D: c_int, vocab: c_int) c_int;
-pub extern fn znn_transpose_fwd(A: ?[*]const f32, C: ?[*]f32, dims: [*]const i64, rank: c_int, d0: c_int, d1: c_int) c_int;
-pub extern fn znn_transpose_bwd(dC: ?[*]const f32, dA: ?[*]f32, dims: [*]const i64, rank: c_int, d0: c_int, d1: c_int) c_int;
+pub extern fn znn_transpose_fwd(A: ?[*]const f32, C: ?[*]f32, dims: ?[*]const i64, rank: c_int, d0: c_int, d1: c_int) c_int;
+pub extern fn znn_transpose_bwd(dC: ?[*]const f32, dA: ?[*]f32, dims: ?[*]const i64, rank: c_int, d0: c_int, d1: c_int) c_int;
 pub extern fn znn_add_fwd(A: ?[*]const f32, B: ?[*]const f32, C: ?[*]f32, n: usize) c_int;
 pub extern fn znn_accumulate(src: ?[*]const f32, dst: ?[*]f32, n: usize) c_int;
 pub extern fn znn_mul_scalar_fwd(A: ?[*]const f32, v: f32, C: ?[*]f32, n: usize) c_int;
@@ -153,7 +155,7 @@ pub extern fn znn_dp_init(world: c_int, rank: c_int, id128: [*:0]const u8) c_int
 pub extern fn znn_dp_init_all(ndev: c_int) c_int;
 pub extern fn znn_dp_group_begin() c_int;
 pub extern fn znn_dp_group_end() c_int;
-pub extern fn znn_dp_world(world: *c_int, rank: *c_int) c_int;
+pub extern fn znn_dp_world(world: ?*c_int, rank: ?*c_int) c_int;
 pub extern fn znn_dp_allreduce_async(buf: ?[*]f32, count: usize) c_int;
 pub extern fn znn_dp_join() c_int;
 pub extern fn znn_dp_allreduce(buf: ?[*]f32, count: usize) c_int;

@@ -16,7 +16,8 @@ bool gemm_tc_direct_eligible(const float* A, long long lda, long long stride_a, 
                              long long stride_b, int batch);
 int gemm_tc_direct(int ta, int tb, int M, int N, int K, float alpha, const float* A, long long lda, long long stride_a,
                    const float* B, long long ldb, long long stride_b, float beta, float* C, long long ldc,
-                   long long stride_c, int batch, const float* bias, int tri, const float* ep_p, const float* ep_d);
+                   long long stride_c, int batch, const float* bias, int tri, const float* ep_p, const float* ep_d,
+                   int ep_act, float* ep_out2, const float* ep_res, const float* ep_dpre);
 int launch_splitk_reduce(const float* partial, int splits, int M, int N, int batch, float alpha, float beta, float* C,
                          long long ldc, long long stride_c, const float* bias);
 int tc_profile_enable(int enable);
@@ -123,7 +124,8 @@ static thread_local int t_last_path = 0;  // taken by the last call
 static int gemm_dispatch(int ta, int tb, int M, int N, int K, float alpha, const float* A, long long lda,
                          long long stride_a, const float* B, long long ldb, long long stride_b, float beta, float* C,
                          long long ldc, long long stride_c, int batch, const float* bias = nullptr, int tri = 0,
-                         const float* ep_p = nullptr, const float* ep_d = nullptr)
+                         const float* ep_p = nullptr, const float* ep_d = nullptr, int ep_act = 0, float* ep_out2 = nullptr,
+                         const float* ep_res = nullptr, const float* ep_dpre = nullptr)
 {
     ZNN_REQUIRE(ta == ZNN_NO_TRANS || ta == ZNN_TRANS, "trans_a must be 111 or 112");
     ZNN_REQUIRE(tb == ZNN_NO_TRANS || tb == ZNN_TRANS, "trans_b must be 111 or 112");
@@ -148,7 +150,7 @@ static int gemm_dispatch(int ta, int tb, int M, int N, int K, float alpha, const
 
     int path = t_path;
     const bool direct_ok = gemm_tc_direct_eligible(A, lda, stride_a, B, ldb, stride_b, batch);
-    if (ep_p) {   // the fused epilogue exists on the in-place tensor-core path only
+    if (ep_p || ep_act != 0 || ep_res) {   // the fused epilogues exist on the in-place tensor-core path only
         if (!direct_ok) return fail(ZNN_ERR_UNSUPPORTED, "fused epilogue: operands not readable in place");
         path = 4;
     }
@@ -168,7 +170,7 @@ static int gemm_dispatch(int ta, int tb, int M, int N, int K, float alpha, const
     t_last_path = path;
     if (path >= 2) {
         int rc = (path == 4) ? gemm_tc_direct(ta, tb, M, N, K, alpha, A, lda, stride_a, B, ldb, stride_b, beta, C, ldc,
-                                              stride_c, batch, bias, tri, ep_p, ep_d)
+                                              stride_c, batch, bias, tri, ep_p, ep_d, ep_act, ep_out2, ep_res, ep_dpre)
                              : gemm_tc(ta, tb, M, N, K, alpha, A, lda, stride_a, B, ldb, stride_b, beta, C, ldc, stride_c,
                                        batch, path == 2 ? 1 : 2, bias);
         // Debug aid (environment ZNN_GEMM_CHECK=1): wait for every tensor-core product and name the first one
@@ -275,6 +277,37 @@ int znn_linear_bwd(const float* X, const float* W, const float* dY, float* dX, f
     int rc;
     if (dbias && (rc = znn_add_bias_bwd(dY, nullptr, dbias, M, N))) return rc;
     if (dX && (rc = gemm_dispatch(ZNN_NO_TRANS, ZNN_TRANS, M, K, N, 1.0f, dY, N, 0, W, N, 0, 1.0f, dX, K, 0, 1))) return rc;
+    if (dW && (rc = gemm_dispatch(ZNN_TRANS, ZNN_NO_TRANS, K, N, M, 1.0f, X, K, 0, dY, N, 0, 1.0f, dW, N, 0, 1))) return rc;
+    return ZNN_OK;
+}
+
+int znn_linear_fwd_ex(const float* X, const float* W, const float* bias, float* Y, float* pre, const float* residual, int M,
+                      int K, int N, int act)
+{
+    ZNN_REQUIRE(bias, "bias is NULL");
+    ZNN_REQUIRE(act >= 0 && act <= 2, "act is 0 (none), 1 (ReLU) or 2 (GELU)");
+    if (act == 0 && !residual) return znn_linear_fwd(X, W, bias, Y, M, K, N);
+    // the epilogue forms live on the tensor-core path: shapes the dispatcher sends to the FMA kernel keep the two-op form
+    if (!(2.0 * M * N * (double)K >= 1.3e8 && M >= 64 && N >= 32 && K >= 32))
+        return fail(ZNN_ERR_UNSUPPORTED, "fused epilogue: product too small for the tensor-core path");
+    return gemm_dispatch(ZNN_NO_TRANS, ZNN_NO_TRANS, M, N, K, 1.0f, X, K, 0, W, N, 0, 0.0f, Y, N, 0, 1, bias, 0, nullptr, nullptr,
+                         act, pre, residual, nullptr);
+}
+
+int znn_linear_bwd_ex(const float* X, const float* W, const float* dY, float* dX, float* dW, float* dbias, int M, int K, int N,
+                      const float* x_pre, int x_act, int dx_fresh)
+{
+    ZNN_REQUIRE(x_act >= 0 && x_act <= 2, "x_act is 0 (none), 1 (ReLU) or 2 (GELU)");
+    if (x_act == 0 || !dX) return znn_linear_bwd(X, W, dY, dX, dW, dbias, M, K, N);
+    ZNN_REQUIRE(x_pre, "x_pre is NULL");
+    if (!(2.0 * M * N * (double)K >= 1.3e8 && M >= 64 && K >= 32 && N >= 32))
+        return fail(ZNN_ERR_UNSUPPORTED, "fused epilogue: product too small for the tensor-core path");
+    int rc;
+    // dX (+)= (dY . W^T) o act'(x_pre): the gradient with respect to the pre-activation of the layer below
+    if ((rc = gemm_dispatch(ZNN_NO_TRANS, ZNN_TRANS, M, K, N, 1.0f, dY, N, 0, W, N, 0, dx_fresh ? 0.0f : 1.0f, dX, K, 0, 1, nullptr,
+                            0, nullptr, nullptr, 2 + x_act, nullptr, nullptr, x_pre)))
+        return rc;
+    if (dbias && (rc = znn_add_bias_bwd(dY, nullptr, dbias, M, N))) return rc;
     if (dW && (rc = gemm_dispatch(ZNN_TRANS, ZNN_NO_TRANS, K, N, M, 1.0f, X, K, 0, dY, N, 0, 1.0f, dW, N, 0, 1))) return rc;
     return ZNN_OK;
 }

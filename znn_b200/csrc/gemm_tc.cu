@@ -48,6 +48,14 @@ struct GemmTcParams {
     // and d one float per row and batch slice; nullptr = the ordinary epilogue
     const float* ep_p;
     const float* ep_d;
+    // in-place kernel, activation / residual epilogue (batch 1, 16-byte form; all laid out like C):
+    //   ep_act 1 = ReLU, 2 = GELU: C = act(h) with h = alpha * A.B + bias (+ ep_res); ep_out2 (optional) receives h;
+    //   ep_act 3 = ReLU', 4 = GELU': C = (alpha * A.B) o act'(ep_dpre) + beta * C  (the gradient of the layer below);
+    //   ep_act 0 with ep_res: C = alpha * A.B + bias + ep_res (residual connection).
+    int ep_act;
+    float* ep_out2;
+    const float* ep_res;
+    const float* ep_dpre;
     // in-place kernel, triangular hint: the tiles of one slice that have work, dearest first (tile_m << 8 | tile_n);
     // units are then (table entry, slice) with the slice running fastest, so that the walk deals every CTA pair the
     // same mix of dear and cheap tiles.  tri_n = 0: no table (more than 64 tiles per slice), plain order.
@@ -575,6 +583,48 @@ __device__ __forceinline__ int direct_unit_kb_count(const GemmTcParams& p, int u
     return min(p.k_blocks - split * p.kblocks_per_split, p.kblocks_per_split);
 }
 
+// Activation / residual extension of the epilogue (see GemmTcParams::ep_act); pointers are laid out like C.
+struct EpiExt {
+    int act;
+    float* out2;
+    const float* res;
+    const float* dpre;
+};
+
+__device__ __forceinline__ float gelu_exact(float x) { return 0.5f * x * (1.0f + erff(x * 0.70710678118654752440f)); }
+__device__ __forceinline__ float gelu_exact_grad(float x)
+{
+    const float cdf = 0.5f * (1.0f + erff(x * 0.70710678118654752440f));
+    const float pdf = 0.3989422804014327f * expf(-0.5f * x * x);
+    return cdf + x * pdf;
+}
+// h = alpha * acc + bias so far.  Forward forms: + residual, keep h, activate.  Gradient forms: multiply by act'(pre).
+__device__ __forceinline__ float4 epi_ext_apply(float4 o, const EpiExt& x, size_t off)
+{
+    if (x.act >= 3) {
+        const float4 pre = *reinterpret_cast<const float4*>(x.dpre + off);
+        if (x.act == 3) {
+            o.x = pre.x > 0.0f ? o.x : 0.0f; o.y = pre.y > 0.0f ? o.y : 0.0f;
+            o.z = pre.z > 0.0f ? o.z : 0.0f; o.w = pre.w > 0.0f ? o.w : 0.0f;
+        } else {
+            o.x *= gelu_exact_grad(pre.x); o.y *= gelu_exact_grad(pre.y);
+            o.z *= gelu_exact_grad(pre.z); o.w *= gelu_exact_grad(pre.w);
+        }
+        return o;
+    }
+    if (x.res) {
+        const float4 r = *reinterpret_cast<const float4*>(x.res + off);
+        o.x += r.x; o.y += r.y; o.z += r.z; o.w += r.w;
+    }
+    if (x.out2) *reinterpret_cast<float4*>(x.out2 + off) = o;
+    if (x.act == 1) {
+        o.x = fmaxf(o.x, 0.0f); o.y = fmaxf(o.y, 0.0f); o.z = fmaxf(o.z, 0.0f); o.w = fmaxf(o.w, 0.0f);
+    } else if (x.act == 2) {
+        o.x = gelu_exact(o.x); o.y = gelu_exact(o.y); o.z = gelu_exact(o.z); o.w = gelu_exact(o.w);
+    }
+    return o;
+}
+
 // Final store of one epilogue warp's 32 x CPT sub-tile (each thread holds one row in registers).
 template <int CPT>
 __device__ __forceinline__ void epilogue_store_rows(const float (&acc)[CPT], float* stage, int lane, int row_base, int cbase,
@@ -625,8 +675,9 @@ template <int CPT>
 __device__ __forceinline__ void epilogue_store_vec(const float (&acc)[CPT], float* stage, int lane, int row_base, int cbase,
                                                    int M, int N, float* out, long long out_ld, float alpha, float beta,
                                                    const float* bias, int rot, const float* ep_p = nullptr,
-                                                   const float* ep_d = nullptr)
+                                                   const float* ep_d = nullptr, const EpiExt ex = EpiExt{0, nullptr, nullptr, nullptr})
 {
+    const bool has_ex = ex.act != 0 || ex.res != nullptr;
     // ep_p != nullptr: softmax-backward form, out = alpha * P o (acc - d[row]) with P laid out like out and d one
     // value per row of this slice (beta and bias unused, N a multiple of 4)
     constexpr int LPR = CPT / 4;          // lanes (float4) per row
@@ -641,7 +692,7 @@ __device__ __forceinline__ void epilogue_store_vec(const float (&acc)[CPT], floa
     const bool col_full = col + 3 < N;
     float4 b4 = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
     if (bias && col_full) b4 = *reinterpret_cast<const float4*>(bias + col);
-    const bool fast = !ep_p && beta == 0.0f && bias == nullptr && rows == 32 && cbase + CPT <= N;
+    const bool fast = !ep_p && !has_ex && beta == 0.0f && bias == nullptr && rows == 32 && cbase + CPT <= N;
     const bool fast_p = ep_p && rows == 32 && cbase + CPT <= N;
     // The order in which the row groups (and the rows inside a group) leave is rotated by `rot` (warp and CTA pair):
     // when every warp of every SM writes rows 0, 1, 2, ... of a power-of-two-pitched C at the same time the stores
@@ -703,6 +754,7 @@ __device__ __forceinline__ void epilogue_store_vec(const float (&acc)[CPT], floa
                     const float4 v = st4[r * 8 + ((lane % 8) ^ (r & 7))];
                     float4 o = make_float4(alpha * v.x, alpha * v.y, alpha * v.z, alpha * v.w);
                     if (bias) { o.x += bb.x; o.y += bb.y; o.z += bb.z; o.w += bb.w; }
+                    if (has_ex) o = epi_ext_apply(o, ex, off + (size_t)(4 * ri) * out_ld + 32 * b0);
                     if (beta != 0.0f) { o.x += beta * old[i].x; o.y += beta * old[i].y; o.z += beta * old[i].z; o.w += beta * old[i].w; }
                     *reinterpret_cast<float4*>(out + off + (size_t)(4 * ri) * out_ld + 32 * b0) = o;
                 }
@@ -791,6 +843,10 @@ __device__ __forceinline__ void epilogue_store_vec(const float (&acc)[CPT], floa
                 float o[4] = {alpha * v.x, alpha * v.y, alpha * v.z, alpha * v.w};
                 if (col_full) {
                     o[0] += b4.x; o[1] += b4.y; o[2] += b4.z; o[3] += b4.w;
+                    if (has_ex) {   // (the extension exists in the 16-byte form only: N is a multiple of 4 then)
+                        const float4 t4 = epi_ext_apply(make_float4(o[0], o[1], o[2], o[3]), ex, (size_t)(row_base + r) * out_ld + col);
+                        o[0] = t4.x; o[1] = t4.y; o[2] = t4.z; o[3] = t4.w;
+                    }
                     if (beta != 0.0f) {
                         o[0] += beta * old[i].x; o[1] += beta * old[i].y; o[2] += beta * old[i].z; o[3] += beta * old[i].w;
                     }
@@ -1087,7 +1143,8 @@ gemm3x_direct_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_cons
             if (vec_ok)
                 epilogue_store_vec<CPT>(acc, stage, lane, d.row0 + q * 32, d.col0 + half * CPT, p.M, p.N, out, out_ld, alpha, beta, bias,
                                         warp + pair, p.ep_p ? p.ep_p + (size_t)d.batch * p.stride_c : nullptr,
-                                        p.ep_d ? p.ep_d + (size_t)d.batch * p.M : nullptr);
+                                        p.ep_d ? p.ep_d + (size_t)d.batch * p.M : nullptr,
+                                        EpiExt{p.ep_act, p.ep_out2, p.ep_res, p.ep_dpre});
             else
                 epilogue_store_rows<CPT>(acc, stage, lane, d.row0 + q * 32, d.col0 + half * CPT, p.M, p.N, out, out_ld, alpha, beta, bias);
         }
@@ -1196,6 +1253,11 @@ __global__ void tail_reduce_kernel(const GemmTcParams p)
         if (p.bias) {
             const float4 b4 = *reinterpret_cast<const float4*>(p.bias + col);
             o[0] += b4.x; o[1] += b4.y; o[2] += b4.z; o[3] += b4.w;
+        }
+        if (p.ep_act != 0 || p.ep_res) {
+            const float4 t4 = epi_ext_apply(make_float4(o[0], o[1], o[2], o[3]), EpiExt{p.ep_act, p.ep_out2, p.ep_res, p.ep_dpre},
+                                            (size_t)row * p.ldc + col);
+            o[0] = t4.x; o[1] = t4.y; o[2] = t4.z; o[3] = t4.w;
         }
         if (p.beta != 0.0f) {
             const float4 old = *reinterpret_cast<const float4*>(dst);
@@ -1540,6 +1602,7 @@ int gemm_tc(int ta, int tb, int M, int N, int K, float alpha, const float* A, lo
     p.partial = splits > 1 ? (b_lo + b_plane) : nullptr;
     p.ep_p = nullptr;
     p.ep_d = nullptr;
+    p.ep_act = 0; p.ep_out2 = nullptr; p.ep_res = nullptr; p.ep_dpre = nullptr;
     p.conv_mode = 0;
     p.bias = bias;
     p.tiles_m = tiles_m;
@@ -1666,10 +1729,20 @@ bool gemm_tc_direct_eligible(const float* A, long long lda, long long stride_a, 
 
 int gemm_tc_direct(int ta, int tb, int M, int N, int K, float alpha, const float* A, long long lda, long long stride_a,
                    const float* B, long long ldb, long long stride_b, float beta, float* C, long long ldc,
-                   long long stride_c, int batch, const float* bias, int tri, const float* ep_p, const float* ep_d)
+                   long long stride_c, int batch, const float* bias, int tri, const float* ep_p, const float* ep_d,
+                   int ep_act, float* ep_out2, const float* ep_res, const float* ep_dpre)
 {
     int* status = device_status_word();
     if (!status) return fail(ZNN_ERR_CUDA, "no device state (call znn_init first)");
+    const bool has_ex = ep_act != 0 || ep_res != nullptr;
+    if (has_ex) {
+        // 16-byte form only, one slice, whole-K tiles (slices of a tail split are finished by the reduce kernel, which
+        // knows the extension; split-K is switched off below)
+        auto al = [](const void* q) { return (reinterpret_cast<uintptr_t>(q) & 15) == 0; };
+        if ((N & 3) || (ldc & 3) || !al(C) || !al(bias) || !al(ep_out2) || !al(ep_res) || !al(ep_dpre) || batch != 1 || ep_p ||
+            tri != 0 || (ep_act >= 3 && !ep_dpre) || (ep_act < 3 && beta != 0.0f) || ep_act < 0 || ep_act > 4)
+            return fail(ZNN_ERR_UNSUPPORTED, "activation / residual epilogue: unaligned output or unsupported arguments");
+    }
     if (ep_p) {
         // the softmax-backward epilogue exists in the 16-byte form only, and never meets partial tiles
         if ((N & 3) || (ldc & 3) || (reinterpret_cast<uintptr_t>(C) & 15) || (reinterpret_cast<uintptr_t>(ep_p) & 15) ||
@@ -1678,7 +1751,7 @@ int gemm_tc_direct(int ta, int tb, int M, int N, int K, float alpha, const float
     }
     const bool tail_ok = t_tail_split && t_persistent && tri == 0 && !ep_p;
     TcPlan pl = make_plan(M, N, K, batch, 2, tail_ok);
-    if ((tri != 0 || ep_p) && pl.splits > 1) {   // the triangular k-ranges are per tile; no split-K on top of them
+    if ((tri != 0 || ep_p || has_ex) && pl.splits > 1) {   // the triangular k-ranges are per tile; no split-K on top of them
         pl.splits = 1;
         pl.kbps = ((pl.k_blocks + pl.chunk - 1) / pl.chunk) * pl.chunk;
     }
@@ -1721,6 +1794,7 @@ int gemm_tc_direct(int ta, int tb, int M, int N, int K, float alpha, const float
     p.tail_partial = tail_partial;
     p.ep_p = ep_p;
     p.ep_d = ep_d;
+    p.ep_act = ep_act; p.ep_out2 = ep_out2; p.ep_res = ep_res; p.ep_dpre = ep_dpre;
     // The hint works through a table of the slice's tiles (which have work, and which k-blocks); a slice of more than
     // 64 tiles is computed in full instead (the hint never changes values that may be read).
     p.tri_n = 0;

@@ -471,6 +471,7 @@ int znn_model_set_option(znn_model* m, const char* key, double value)
     else if (k == "causal_skip") set_causal_skip(value != 0.0);
     else if (k == "fused_qkt") set_fused_qkt(value != 0.0);
     else if (k == "fused_attention") set_fused_attention(value != 0.0);
+    else if (k == "fused_epilogue") set_fused_epilogue((int)value);
     else if (k == "fused_softmax_bwd") set_fused_softmax_bwd(value != 0.0);
     else if (k == "alias_reshape_grad") set_alias_reshape_grad(value != 0.0);
     else if (k == "lazy_zero_grad") set_lazy_zero_grad(value != 0.0);

@@ -122,6 +122,10 @@ void mark_grad_written(Tensor* t) { grad_root(t)->grad_valid = true; }
 
 bool grad_is_fresh(Tensor* t) { return t->grad && !grad_root(t)->grad_valid; }
 
+static int g_fused_epilogue = 2;
+void set_fused_epilogue(int mask) { g_fused_epilogue = mask; }
+int fused_epilogue() { return g_fused_epilogue; }
+
 static bool g_fused_softmax_bwd = true;
 void set_fused_softmax_bwd(bool on) { g_fused_softmax_bwd = on; }
 bool fused_softmax_bwd() { return g_fused_softmax_bwd; }
@@ -151,6 +155,7 @@ Op* Graph::new_op(OpType type, std::initializer_list<Tensor*> inputs, Tensor* ou
     o->inputs.assign(inputs.begin(), inputs.end());
     o->outputs.push_back(out);
     out->creator = o;
+    for (Tensor* in : o->inputs) in->consumers++;
     ops_.push_back(o);
     return o;
 }
@@ -377,6 +382,50 @@ Tensor* Graph::linear(Tensor* X, Tensor* W, Tensor* bias)
     Tensor* Y = new_tensor(Shape{X->shape.dims[0], W->shape.dims[1]}, any_grad({X, W, bias}), false);
     new_op(OpType::LinearBias, {X, W, bias}, Y)->forward();
     return Y;
+}
+
+Tensor* Graph::linearAct(Tensor* X, Tensor* W, Tensor* bias, OpType act)
+{
+    if (act != OpType::Relu && act != OpType::Gelu) throw Error(ZNN_ERR_INVALID, "linearAct: the activation is Relu or Gelu");
+    if (X->shape.len < 2 || W->shape.len < 2 || X->shape.dims[1] != W->shape.dims[0] || bias->numel() != W->shape.dims[1])
+        throw Error(ZNN_ERR_INVALID, "linear: need X [M,K], W [K,N], bias [N]");
+    Tensor* H = new_tensor(Shape{X->shape.dims[0], W->shape.dims[1]}, any_grad({X, W, bias}), false);
+    Op* lin = new_op(OpType::LinearBias, {X, W, bias}, H);
+    Tensor* A = new_tensor(H->shape, H->requires_grad, false);
+    Op* a = new_op(act, {H}, A);
+    int rc = ZNN_ERR_UNSUPPORTED;
+    if (g_fused_epilogue & (act == OpType::Relu ? 2 : 4))
+        rc = znn_linear_fwd_ex(X->data, W->data, bias->data, A->data, H->data, nullptr, (int)X->shape.dims[0],
+                               (int)X->shape.dims[1], (int)W->shape.dims[1], act == OpType::Relu ? 1 : 2);
+    if (rc == ZNN_ERR_UNSUPPORTED) {   // small or unaligned: the two kernels
+        lin->forward();
+        a->forward();
+    } else {
+        check(rc, "Linear + activation forward");
+    }
+    return A;
+}
+
+Tensor* Graph::linearResidual(Tensor* X, Tensor* W, Tensor* bias, Tensor* R)
+{
+    if (X->shape.len < 2 || W->shape.len < 2 || X->shape.dims[1] != W->shape.dims[0] || bias->numel() != W->shape.dims[1])
+        throw Error(ZNN_ERR_INVALID, "linear: need X [M,K], W [K,N], bias [N]");
+    if (R->numel() != X->shape.dims[0] * W->shape.dims[1]) throw Error(ZNN_ERR_INVALID, "linearResidual: residual size");
+    Tensor* L = new_tensor(Shape{X->shape.dims[0], W->shape.dims[1]}, any_grad({X, W, bias}), false);
+    Op* lin = new_op(OpType::LinearBias, {X, W, bias}, L);
+    Tensor* S = new_tensor(L->shape, any_grad({R, L}), false);
+    Op* add = new_op(OpType::Add, {R, L}, S);
+    int rc = ZNN_ERR_UNSUPPORTED;
+    if (g_fused_epilogue & 1)   // S = X.W + bias + R in one kernel; L's values are never needed (no backward arm reads them)
+        rc = znn_linear_fwd_ex(X->data, W->data, bias->data, S->data, nullptr, R->data, (int)X->shape.dims[0],
+                               (int)X->shape.dims[1], (int)W->shape.dims[1], 0);
+    if (rc == ZNN_ERR_UNSUPPORTED) {
+        lin->forward();
+        add->forward();
+    } else {
+        check(rc, "Linear + residual forward");
+    }
+    return S;
 }
 
 Tensor* Graph::batchMatMul(Tensor* A, Tensor* B, int tri_role)
@@ -679,9 +728,29 @@ void Op::backward()
             check(znn_add_bias_bwd(C->grad, nullptr, b->grad, M, N), "Linear backward dbias");
         }
         if (A->requires_grad) {
-            const float beta = claim_grad_overwrite(A) ? 0.0f : 1.0f;
-            check(znn_sgemm(ZNN_ROW_MAJOR, ZNN_NO_TRANS, ZNN_TRANS, M, K, N, 1.0f, C->grad, N, W->data, N, beta, A->grad, K),
-                  "Linear backward dX");
+            // X = act(H) read by this op alone: the activation's derivative rides in the epilogue of dY.W^T, the result
+            // is the gradient of H and the activation op's own backward is skipped
+            Op* prod = A->creator;
+            bool fused = false;
+            if (prod && (prod->type == OpType::Relu ? (g_fused_epilogue & 2) : prod->type == OpType::Gelu ? (g_fused_epilogue & 8) : 0) &&
+                A->consumers == 1 &&
+                prod->inputs[0]->requires_grad && prod->inputs[0]->grad && grad_is_fresh(A)) {
+                Tensor* H = prod->inputs[0];
+                const int rc = znn_linear_bwd_ex(A->data, W->data, C->grad, H->grad, nullptr, nullptr, M, K, N, H->data,
+                                                 prod->type == OpType::Relu ? 1 : 2, grad_is_fresh(H) ? 1 : 0);
+                if (rc == ZNN_OK) {
+                    mark_grad_written(H);
+                    prod->skip_backward = true;
+                    fused = true;
+                } else if (rc != ZNN_ERR_UNSUPPORTED) {
+                    check(rc, "Linear backward dX with the activation gradient");
+                }
+            }
+            if (!fused) {
+                const float beta = claim_grad_overwrite(A) ? 0.0f : 1.0f;
+                check(znn_sgemm(ZNN_ROW_MAJOR, ZNN_NO_TRANS, ZNN_TRANS, M, K, N, 1.0f, C->grad, N, W->data, N, beta, A->grad, K),
+                      "Linear backward dX");
+            }
         }
         if (W->requires_grad) {
             const float beta = claim_grad_overwrite(W) ? 0.0f : 1.0f;

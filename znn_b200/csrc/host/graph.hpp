@@ -54,6 +54,7 @@ struct Tensor {
     // A Reshape view that shares its input's buffer points at the owner, whose flag counts.
     bool grad_valid = true;
     Tensor* grad_owner = nullptr;
+    int consumers = 0;   // ops that read this tensor (counted while the tape is built)
     size_t numel() const { return shape.numel(); }
 };
 
@@ -72,6 +73,15 @@ void set_fused_softmax_bwd(bool on);
 bool fused_softmax_bwd();
 void set_lazy_zero_grad(bool on);
 bool lazy_zero_grad();
+// The elementwise step after (or before, in the backward) a Linear runs in the GEMM's epilogue where the shapes allow
+// (znn_linear_fwd_ex / znn_linear_bwd_ex).  The tape keeps the separate ops; only which kernels fill their tensors changes.
+// Bit mask: 1 = residual add after an output projection, 2 = ReLU forward and its derivative backward, 4 = GELU forward,
+// 8 = GELU derivative backward.  Default 2.  The epilogue warps of the GEMM kernel are its latency-bound role: measured on
+// the GPT step (18.79 ms with mask 0), the residual form costs +0.08 ms net (one more 16-byte load per stored float4
+// against two 25 MB add kernels saved per layer), GELU forward +0.5 ms and its derivative +0.95 ms (erf and exp per
+// element in the epilogue against bandwidth-bound stand-alone kernels).  ReLU is free (one max per element).
+void set_fused_epilogue(int mask);
+int fused_epilogue();
 
 // hot-path subset of src/autodiff.zig:14-40, plus two additions
 enum class OpType {
@@ -170,6 +180,11 @@ public:
     Tensor* causalAttention(Tensor* q, Tensor* k, Tensor* v, size_t B, size_t T, size_t nh, float scale);
     Tensor* layerNorm(Tensor* X, Tensor* G, Tensor* B, float eps);          // extension
     Tensor* linear(Tensor* X, Tensor* W, Tensor* bias);                     // fused addBias(matmul(X, W), bias)
+    // act(linear(X, W, bias)) with act = Relu or Gelu: the tape gets the Linear and the activation op, one GEMM fills both
+    // outputs (pre-activation and activation) when the epilogue form applies
+    Tensor* linearAct(Tensor* X, Tensor* W, Tensor* bias, OpType act);
+    // add(R, linear(X, W, bias)): the residual is added in the GEMM's epilogue when the form applies
+    Tensor* linearResidual(Tensor* X, Tensor* W, Tensor* bias, Tensor* R);
 
     // `after_op(op)` is called after a tape op has run its
     // backward arm; data-parallel training uses it to start gradient all-reduces.

@@ -96,6 +96,19 @@ Tensor* Linear::forward(Graph& g, Tensor* x) const
     return g.addBias(g.matmul(x, weight), bias);
 }
 
+Tensor* Linear::forward_act(Graph& g, Tensor* x, OpType act) const
+{
+    if (g_fused_linear && (fused_epilogue() & (act == OpType::Relu ? 2 : 4))) return g.linearAct(x, weight, bias, act);
+    Tensor* h = forward(g, x);
+    return act == OpType::Relu ? g.relu(h) : g.gelu(h);
+}
+
+Tensor* Linear::forward_residual(Graph& g, Tensor* x, Tensor* r) const
+{
+    if (g_fused_linear && (fused_epilogue() & 1)) return g.linearResidual(x, weight, bias, r);
+    return g.add(r, forward(g, x));
+}
+
 Conv2D::Conv2D(ParamStore& ps, const std::string& name, size_t in_ch, size_t out_ch, size_t k, int pad_) : pad(pad_)
 {
     weight = ps.add(name + ".weight", Shape{out_ch, in_ch, k, k}, in_ch * k * k);
@@ -123,15 +136,20 @@ MLP::MLP(ParamStore& ps, const std::string& name, size_t dim, size_t hidden)
 {
 }
 
-Tensor* MLP::forward(Graph& g, Tensor* x) const
+Tensor* MLP::forward(Graph& g, Tensor* x, Tensor* residual) const
 {
-    // src/nn.zig:638-685
+    // src/nn.zig:638-685 (and the residual add of :1016-1020 when the caller hands it in)
     const bool is_3d = (x->shape.len == 3);
     Tensor* x_2d = x;
     if (is_3d) x_2d = g.reshape(x, Shape{x->shape.dims[0] * x->shape.dims[1], x->shape.dims[2]});
-    Tensor* h1 = c_fc.forward(g, x_2d);
-    Tensor* a1 = g.gelu(h1);
-    Tensor* h2 = c_proj.forward(g, a1);
+    Tensor* a1 = c_fc.forward_act(g, x_2d, OpType::Gelu);
+    Tensor* h2;
+    if (residual) {
+        Tensor* r_2d = residual->shape.len == 2 ? residual : g.reshape(residual, x_2d->shape);
+        h2 = c_proj.forward_residual(g, a1, r_2d);
+    } else {
+        h2 = c_proj.forward(g, a1);
+    }
     if (is_3d) return g.reshape(h2, x->shape);
     return h2;
 }
@@ -143,7 +161,7 @@ CausalSelfAttention::CausalSelfAttention(ParamStore& ps, const std::string& name
 {
 }
 
-Tensor* CausalSelfAttention::forward(Graph& g, Tensor* x) const
+Tensor* CausalSelfAttention::forward(Graph& g, Tensor* x, Tensor* residual) const
 {
     // src/nn.zig:752-937, same op sequence
     const size_t B = x->shape.dims[0], T = x->shape.dims[1], C = x->shape.dims[2];
@@ -156,7 +174,7 @@ Tensor* CausalSelfAttention::forward(Graph& g, Tensor* x) const
     if (fused_softmax && g_fused_attention && (hs == 32 || hs == 64) && T % 4 == 0 && T >= 128) {
         // one op on the projections where they lie: the heads are read and written through strides
         Tensor* y_2d = g.causalAttention(q_2d, k_2d, v_2d, B, T, nh, 1.0f / sqrtf((float)hs));
-        Tensor* out_2d = c_proj.forward(g, y_2d);
+        Tensor* out_2d = residual ? c_proj.forward_residual(g, y_2d, g.reshape(residual, Shape{B * T, C})) : c_proj.forward(g, y_2d);
         return g.reshape(out_2d, Shape{B, T, C});
     }
     Tensor* q_4d = g.reshape(q_2d, Shape{B, T, nh, hs});
@@ -193,7 +211,7 @@ Tensor* CausalSelfAttention::forward(Graph& g, Tensor* x) const
     Tensor* y_trans = g.transposeND(y_4d, 1, 2);
     Tensor* y_3d = g.reshape(y_trans, Shape{B, T, C});
     Tensor* y_2d = g.reshape(y_3d, Shape{B * T, C});
-    Tensor* out_2d = c_proj.forward(g, y_2d);
+    Tensor* out_2d = residual ? c_proj.forward_residual(g, y_2d, g.reshape(residual, Shape{B * T, C})) : c_proj.forward(g, y_2d);
     return g.reshape(out_2d, Shape{B, T, C});
 }
 
@@ -207,6 +225,11 @@ Tensor* TransformerBlock::forward(Graph& g, Tensor* x) const
 {
     // src/nn.zig:996-1021
     Tensor* x_norm1 = ln_1.forward(g, x);
+    if (fused_epilogue() & 1) {   // the two residual adds ride in the epilogues of the output projections
+        Tensor* x1 = attn.forward(g, x_norm1, x);
+        Tensor* x_norm2 = ln_2.forward(g, x1);
+        return mlp.forward(g, x_norm2, x1);
+    }
     Tensor* x_attn = attn.forward(g, x_norm1);
     Tensor* x1 = g.add(x, x_attn);
     Tensor* x_norm2 = ln_2.forward(g, x1);
@@ -255,8 +278,8 @@ MlpNet::MlpNet(ParamStore& ps, size_t in, size_t h1, size_t h2, size_t out)
 
 Tensor* MlpNet::forward(Graph& g, Tensor* x) const
 {
-    Tensor* a1 = g.relu(fc1.forward(g, x));
-    Tensor* a2 = g.relu(fc2.forward(g, a1));
+    Tensor* a1 = fc1.forward_act(g, x, OpType::Relu);
+    Tensor* a2 = fc2.forward_act(g, a1, OpType::Relu);
     return fc3.forward(g, a2);
 }
 

@@ -66,6 +66,8 @@ struct Linear {
     Linear() = default;
     Linear(ParamStore& ps, const std::string& name, size_t in_features, size_t out_features);
     Tensor* forward(Graph& g, Tensor* x) const;
+    Tensor* forward_act(Graph& g, Tensor* x, OpType act) const;        // act(forward(x)), act = Relu or Gelu
+    Tensor* forward_residual(Graph& g, Tensor* x, Tensor* r) const;    // r + forward(x)
 };
 
 // src/nn.zig:54-96.  weight [Co, Ci, k, k], bias [Co]; pad is an extension (0 = reference)
@@ -100,7 +102,7 @@ struct MLP {
     Linear c_fc, c_proj;
     MLP() = default;
     MLP(ParamStore& ps, const std::string& name, size_t dim, size_t hidden);
-    Tensor* forward(Graph& g, Tensor* x) const;
+    Tensor* forward(Graph& g, Tensor* x, Tensor* residual = nullptr) const;   // residual: returns residual + mlp(x)
 };
 
 // src/nn.zig:700-938.  fused_softmax = true replaces the reference's
@@ -113,7 +115,7 @@ struct CausalSelfAttention {
     bool fused_softmax = true;
     CausalSelfAttention() = default;
     CausalSelfAttention(ParamStore& ps, const std::string& name, size_t n_embd, size_t n_head);
-    Tensor* forward(Graph& g, Tensor* x) const;
+    Tensor* forward(Graph& g, Tensor* x, Tensor* residual = nullptr) const;   // residual: returns residual + attn(x)
 };
 
 // src/nn.zig:950-1022: x1 = x + attn(rms1(x)); out = x1 + mlp(rms2(x1))

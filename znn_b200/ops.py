@@ -183,6 +183,38 @@ def linear_fwd(X, W, bias):
     return out.to_host((M, N))
 
 
+def linear_fwd_ex(X, W, bias, act=0, residual=None, want_pre=False):
+    """Linear with the activation (1 ReLU, 2 GELU) and / or the residual add in the GEMM epilogue; returns Y (and the
+    pre-activation h when asked)."""
+    _ensure()
+    X, W, bias = _f(X), _f(W), _f(bias).reshape(-1)
+    M, K = X.shape
+    N = W.shape[1]
+    dX, dW, db = _up(X), _up(W), _up(bias)
+    dr = _up(_f(residual)) if residual is not None else None
+    out = DevBuf(M * N * 4)
+    pre = DevBuf(M * N * 4) if want_pre else None
+    lib().call("znn_linear_fwd_ex", dX.ptr, dW.ptr, db.ptr, out.ptr, pre.ptr if pre else None, dr.ptr if dr else None,
+               M, K, N, act)
+    check_device_status()
+    if want_pre:
+        return out.to_host((M, N)), pre.to_host((M, N))
+    return out.to_host((M, N))
+
+
+def linear_bwd_ex(X, W, dY, dX, dW, dbias, x_pre, x_act, dx_fresh):
+    """Backward of Linear whose input is act(x_pre): dX receives the gradient with respect to x_pre."""
+    _ensure()
+    M, K = X.shape
+    N = W.shape[1]
+    x, w, dy, dx, dw, db, xp = _up(_f(X)), _up(_f(W)), _up(_f(dY)), _up(dX), _up(dW), _up(dbias), _up(_f(x_pre))
+    lib().call("znn_linear_bwd_ex", x.ptr, w.ptr, dy.ptr, _ptr(dx), _ptr(dw), _ptr(db), M, K, N, xp.ptr, x_act, dx_fresh)
+    check_device_status()
+    for host, dev in ((dX, dx), (dW, dw), (dbias, db)):
+        if host is not None:
+            dev.into(host)
+
+
 def matmul_bwd(A, B, dC, dA=None, dB=None):
     M, K = A.shape
     N = B.shape[1]
