@@ -703,6 +703,24 @@ def gpt_part(args, L, torch, dist, stream, world, rank, local):
     kms, kl, kfl = C.c_double(0), C.c_longlong(0), C.c_double(0)
     L.call("znn_gemm_profile_read", C.byref(kms), C.byref(kl), C.byref(kfl))
     L.call("znn_gemm_profile", 0)
+    eager_ms = ms
+    replayed = False
+    if world == 1 and not os.environ.get("ZNN_BENCH_NO_GRAPH"):
+        # One GPU: the step uploads nothing, so it is captured once into a CUDA graph and replayed (the same kernels in
+        # the same order, bit-identical results: tests/test_gpu_models.py); the eager figure above stays in the line.
+        m.set_option("cuda_graph", 1)
+        for _ in range(warmup + 2):              # eager sizing step, capture, replays
+            m.train_step_device(d_ids.data_ptr(), d_tgt.data_ptr(), B, T)
+        barrier()
+        replayed = m.graph_replays() > 0
+        if replayed:
+            e0.record(stream)
+            for _ in range(steps):
+                m.train_step_device(d_ids.data_ptr(), d_tgt.data_ptr(), B, T)
+            e1.record(stream)
+            barrier()
+            ms = float(e0.elapsed_time(e1))
+        m.set_option("cuda_graph", 0)
     # end to end: token ids and targets from host memory every step, loss read back every step
     loss = m.train_step(ids, tgt, seq=T)
     barrier()
@@ -732,6 +750,9 @@ def gpt_part(args, L, torch, dist, stream, world, rank, local):
         "e2e": {"value": world * B * T * e2e_steps / (e2e_ms * 1e-3), "unit": "tokens/s",
                 "h2d_bytes_per_step": ids.nbytes + tgt.nbytes, "d2h_bytes_per_step": 4, "steps": e2e_steps},
         "gpu_launches": cnt.value, "tape_ops": m.last_step_ops(), "last_loss": loss,
+        "cuda_graph_replay": replayed, "eager_ms_per_step": eager_ms / steps,
+        "launch_note": ("kernels of the eager pass of the same steps; the timed steps replay the same kernels from one "
+                        "captured graph" if replayed else "kernels launched in the timed steps"),
         "arena_high_water_gb": m.arena_high_water() / 2 ** 30,
         "tensor_core_gemm": {"launches": kl.value, "kernel_ms_per_step": kms.value / steps,
                              "tflops": (kfl.value / (kms.value * 1e-3) / 1e12) if kms.value > 0 else None,

@@ -313,6 +313,9 @@ int znn_batch_gather(const float* images, const uint8_t* labels, const int32_t* 
                      int batch, int input_dim, size_t num_samples);
 /* fill helpers (src/tensor.zig:354-379 fills; used for dC = 1 seeds and zeroGrad) */
 int znn_fill(float* dst, float value, size_t n);
+/* dst[i] = i mod period as floats: the position ids of a [batch, T] window (GPT.forward, src/nn.zig:1183-1196), made on the
+ * device so that a training step uploads nothing */
+int znn_iota_mod(float* dst, size_t n, int period);
 /* Weight initialisation on the device.
  * znn_init_he_normal: initializeWeights (src/nn.zig:1336-1350): w[i] = N(0,1) * sqrt(2 / fan_in), one Box-Muller draw per
  *   element, cosine branch, u1 redrawn while it is 0.

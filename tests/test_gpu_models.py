@@ -490,3 +490,47 @@ def test_fused_epilogues_match_the_separate_ops(Model):
     assert abs(out[0][0] - out[1][0]) <= 1e-6 * abs(out[1][0])
     for k in out[0][1]:
         relclose(out[0][1][k], out[1][1][k], 1e-5, k, 1e-2 * grad_floor(out[1][1]))
+
+
+@pytest.mark.parametrize("dims,batch", [((61, 24, 32, 4, 2), 3), ((128, 256, 128, 2, 2), 4)])
+def test_gpt_cuda_graph_replay_matches_eager(Model, dims, batch):
+    """The GPT training step uploads nothing (position ids are written on the device), so it can be captured and
+    replayed like the MLP / CNN steps: identical losses and parameters, step after step, with new token ids copied into
+    the same device buffers.  The second size runs the fused attention kernels and the tensor-core GEMMs."""
+    import ctypes as C
+    from znn_b200 import ops
+    V, T, D, H, NL = dims
+    cfg = {"vocab_size": V, "block_size": T, "n_embd": D, "n_head": H, "n_layer": NL}
+    r = np.random.default_rng(55)
+    P0 = models.init_params("gpt", cfg, seed=56)
+    batches = []
+    for _ in range(5):
+        x = r.integers(0, V, (batch, T)).astype(np.float32)
+        t = np.concatenate([x[:, 1:], r.integers(0, V, (batch, 1))], axis=1).astype(np.int32)
+        batches.append((x, t))
+    finals, losses = [], []
+    lib_ = ops.lib()
+    for use_graph in (0, 1):
+        m = Model("gpt", dims, arena_bytes=512 << 20)
+        m.set_params(P0)
+        m.set_option("lr", 0.05)
+        m.set_option("momentum", 0.9)
+        m.set_option("cuda_graph", use_graph)
+        dx, dt = ops.DevBuf(batch * T * 4), ops.DevBuf(batch * T * 4)
+        ls = []
+        for x, t in batches:
+            lib_.call("znn_memcpy_h2d", dx.ptr, x.ctypes.data, x.nbytes)
+            lib_.call("znn_memcpy_h2d", dt.ptr, t.ctypes.data, t.nbytes)
+            lib_.call("znn_sync")
+            loss = C.c_float()
+            lib_.call("znn_model_train_step", m.h, dx.ptr, dt.ptr, batch, T, 1, C.byref(loss))
+            ls.append(loss.value)
+        if use_graph:
+            assert m.graph_replays() == len(batches) - 1
+        finals.append(m.get_params())
+        losses.append(ls)
+        m.close()
+    ops.check_device_status()
+    assert losses[0] == losses[1]
+    for k in finals[0]:
+        np.testing.assert_array_equal(finals[0][k], finals[1][k])

@@ -147,6 +147,7 @@ pub extern fn znn_adam_step(w: ?[*]f32, g: ?[*]const f32, m: ?[*]f32, v: ?[*]f32
 pub extern fn znn_pixels_to_unit(pixels: ?[*]const u8, out: ?[*]f32, n: usize) c_int;
 pub extern fn znn_batch_gather(images: ?[*]const f32, labels: ?[*]const u8, indices: ?[*]const i32, x_dest: ?[*]f32, y_dest: ?[*]u8, batch: c_int, input_dim: c_int, num_samples: usize) c_int;
 pub extern fn znn_fill(dst: ?[*]f32, value: f32, n: usize) c_int;
+pub extern fn znn_iota_mod(dst: ?[*]f32, n: usize, period: c_int) c_int;
 pub extern fn znn_init_he_normal(w: ?[*]f32, n: usize, fan_in: usize, seed: c_ulonglong) c_int;
 pub extern fn znn_fill_normal(w: ?[*]f32, n: usize, mean: f32, stddev: f32, seed: c_ulonglong) c_int;
 pub extern fn znn_fill_uniform(w: ?[*]f32, n: usize, min_val: f32, max_val: f32, seed: c_ulonglong) c_int;

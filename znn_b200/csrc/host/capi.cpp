@@ -227,7 +227,7 @@ struct znn_model {
     cudaGraphExec_t graph_exec = nullptr;
     const void* graph_x = nullptr;
     const void* graph_t = nullptr;
-    int graph_batch = 0, graph_seen = 0;
+    int graph_batch = 0, graph_seq = 0, graph_seen = 0;
     float* graph_loss = nullptr;
     long long graph_replays = 0;
     // the captured kernels hold raw addresses of the shim's scratch blocks: the graph is only valid while none of
@@ -536,20 +536,22 @@ int znn_model_train_step(znn_model* m, const float* x, const int32_t* targets, i
     if (m->kind == ZNN_MODEL_GPT && seq <= 0) throw Error(ZNN_ERR_INVALID, "seq must be positive");
     int world = 1;
     znn_dp_world(&world, nullptr);
-    // Replay is possible when nothing in the step touches the host: device-resident inputs, one GPU, and a model
-    // whose forward uploads nothing (the GPT forward uploads its position ids, so it always runs eagerly).
-    const bool can_replay = m->use_graph && !m->use_adam && on_device && world == 1 && m->kind != ZNN_MODEL_GPT && m->kind != ZNN_MODEL_BLOCK;
+    // Replay is possible when nothing in the step touches the host: device-resident inputs and one GPU (the gradient
+    // exchange polls its communicator from the host).
+    const bool can_replay = m->use_graph && !m->use_adam && on_device && world == 1 && m->kind != ZNN_MODEL_BLOCK;
     float* loss_dev = nullptr;
     if (!can_replay) {
         loss_dev = run_train_step(m, x, targets, batch, seq, on_device != 0);
     } else {
         unsigned long long gen = 0;
         check(znn_workspace_generation(&gen), "znn_workspace_generation");
-        if (m->graph_x != x || m->graph_t != targets || m->graph_batch != batch || (m->graph_exec && gen != m->graph_generation)) {
+        if (m->graph_x != x || m->graph_t != targets || m->graph_batch != batch || m->graph_seq != seq ||
+            (m->graph_exec && gen != m->graph_generation)) {
             drop_graph(m);
             m->graph_x = x;
             m->graph_t = targets;
             m->graph_batch = batch;
+            m->graph_seq = seq;
         }
         if (m->graph_exec) {
             void* st = nullptr;

@@ -258,10 +258,10 @@ Tensor* GPT::forward(Graph& g, Tensor* ids) const
     const size_t B = ids->shape.dims[0], T = ids->shape.dims[1];
     if (T > cfg.block_size) throw Error(ZNN_ERR_INVALID, "GPT.forward: sequence longer than block_size");
     Tensor* tok_emb = token_embedding.forward(g, ids);
-    std::vector<float> pos(B * T);
-    for (size_t b = 0; b < B; b++)
-        for (size_t t = 0; t < T; t++) pos[b * T + t] = (float)t;
-    Tensor* pos_node = g.array(Shape{B, T}, pos.data(), false);
+    // the position ids 0..T-1 of every row, written on the device (the reference fills them on the host): the step
+    // then uploads nothing and can be captured into a CUDA graph
+    Tensor* pos_node = g.tensorND(Shape{B, T}, false);
+    check(znn_iota_mod(pos_node->data, B * T, (int)T), "position ids");
     Tensor* pos_emb = position_embedding.forward(g, pos_node);
     Tensor* cur = g.add(tok_emb, pos_emb);
     for (const TransformerBlock& blk : h) cur = blk.forward(g, cur);

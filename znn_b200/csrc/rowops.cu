@@ -159,6 +159,13 @@ struct AccF { __device__ float operator()(float s, float d) const { return d + s
 struct MulF { float v; __device__ float operator()(float a) const { return a * v; } };
 struct MulAccF { float v; __device__ float operator()(float dc, float da) const { return da + dc * v; } };
 
+// dst[i] = i mod period: the position ids of a [batch, T] window (src/nn.zig:1183-1196 builds them on the host)
+__global__ void iota_mod_kernel(float* dst, size_t n, int period)
+{
+    for (size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x)
+        dst[i] = (float)(i % (size_t)period);
+}
+
 __global__ void fill_kernel(float* dst, float v, size_t n)
 {
     for (size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x) dst[i] = v;
@@ -1264,6 +1271,16 @@ int znn_fill(float* dst, float value, size_t n)
     ZNN_REQUIRE(dst, "dst is NULL");
     fill_kernel<<<ew_blocks(n), kEwThreads, 0, stream()>>>(dst, value, n);
     ZNN_LAUNCH_OK("fill_kernel");
+    return ZNN_OK;
+}
+
+int znn_iota_mod(float* dst, size_t n, int period)
+{
+    if (n == 0) return ZNN_OK;
+    ZNN_NEED_DEVICE();
+    ZNN_REQUIRE(dst && period > 0, "dst is NULL or period <= 0");
+    iota_mod_kernel<<<ew_blocks(n), kEwThreads, 0, stream()>>>(dst, n, period);
+    ZNN_LAUNCH_OK("iota_mod_kernel");
     return ZNN_OK;
 }
 
