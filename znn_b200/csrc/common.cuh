@@ -25,6 +25,12 @@ void* workspace(size_t bytes);
 // slot 2 holds the device copies of host operands (znn_sgemm_host, znn_matmul_host_fwd_bwd)
 void* workspace_slot(int slot, size_t bytes);
 
+// kScratchCounters zero-initialised words per (device, stream), for kernels whose last block to finish completes a
+// reduction: such a kernel counts its blocks with atomicAdd and must leave the words it used at zero again.  nullptr
+// when they cannot be had (first use during a stream capture): callers then take their two-kernel form.
+constexpr int kScratchCounters = 4096;
+unsigned* scratch_counters();
+
 int sm_count();
 
 // Counts the reallocations of scratch blocks on the current device: a holder of raw scratch addresses (a captured

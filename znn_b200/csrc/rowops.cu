@@ -200,9 +200,10 @@ __global__ void add_bias_fwd_kernel(const float* __restrict__ A, const float* __
 // order into out[n].  `PassThrough` also does dA += dC on the way (AddBias backward).
 template <bool PassThrough>
 __global__ void colsum_stage1_kernel(const float* __restrict__ dC, float* __restrict__ dA, float* __restrict__ partial,
-                                     int M, int N, int rows_per_chunk)
+                                     int M, int N, int rows_per_chunk, unsigned* __restrict__ counters, float* __restrict__ out)
 {
     __shared__ float sh[8][33];
+    __shared__ bool last;
     const int n = blockIdx.x * 32 + threadIdx.x;
     const int m0 = blockIdx.y * rows_per_chunk;
     const int m1 = min(M, m0 + rows_per_chunk);
@@ -222,6 +223,28 @@ __global__ void colsum_stage1_kernel(const float* __restrict__ dC, float* __rest
         for (int y = 0; y < 8; y++) t += sh[y][threadIdx.x];
         partial[(size_t)blockIdx.y * N + n] = t;
     }
+    if (!counters) return;   // the caller runs the second stage as its own kernel
+    // The chunk that finishes last for these 32 columns adds all chunk partials in chunk order (the same order whichever
+    // chunk that is: the result does not depend on the scheduling) and leaves the counter at zero for the next launch.
+    __threadfence();
+    __syncthreads();
+    if (threadIdx.x == 0 && threadIdx.y == 0) last = (atomicAdd(&counters[blockIdx.x], 1u) == gridDim.y - 1);
+    __syncthreads();
+    if (!last) return;
+    __threadfence();
+    float t = 0.0f;
+    if (n < N)
+        for (int c = threadIdx.y; c < (int)gridDim.y; c += 8) t += __ldcg(partial + (size_t)c * N + n);
+    __syncthreads();
+    sh[threadIdx.y][threadIdx.x] = t;
+    __syncthreads();
+    if (threadIdx.y == 0 && n < N) {
+        float u = 0.0f;
+#pragma unroll
+        for (int y = 0; y < 8; y++) u += sh[y][threadIdx.x];
+        out[n] += u;
+    }
+    if (threadIdx.x == 0 && threadIdx.y == 0) counters[blockIdx.x] = 0u;
 }
 
 // block = 32 columns x 8 lanes; lane y adds chunks y, y+8, ... in order, then the 8 lane sums are added in order
@@ -1309,11 +1332,15 @@ int znn_add_bias_bwd(const float* dC, float* dA, float* dbias, int M, int N)
     float* partial = (float*)workspace((size_t)chunks * N * sizeof(float));
     if (!partial) return fail(ZNN_ERR_NOMEM, "scratch for bias gradient");
     dim3 grid(ceil_div(N, 32), chunks), block(32, 8);
-    if (dA) colsum_stage1_kernel<true><<<grid, block, 0, stream()>>>(dC, dA, partial, M, N, rpc);
-    else colsum_stage1_kernel<false><<<grid, block, 0, stream()>>>(dC, nullptr, partial, M, N, rpc);
+    // one launch when the block counters are at hand (the last chunk of a column block finishes its sum), else two
+    unsigned* counters = (int)grid.x <= kScratchCounters ? scratch_counters() : nullptr;
+    if (dA) colsum_stage1_kernel<true><<<grid, block, 0, stream()>>>(dC, dA, partial, M, N, rpc, counters, dbias);
+    else colsum_stage1_kernel<false><<<grid, block, 0, stream()>>>(dC, nullptr, partial, M, N, rpc, counters, dbias);
     ZNN_LAUNCH_OK("colsum_stage1_kernel");
-    colsum_stage2_kernel<<<ceil_div(N, 32), dim3(32, 8), 0, stream()>>>(partial, dbias, chunks, N);
-    ZNN_LAUNCH_OK("colsum_stage2_kernel");
+    if (!counters) {
+        colsum_stage2_kernel<<<ceil_div(N, 32), dim3(32, 8), 0, stream()>>>(partial, dbias, chunks, N);
+        ZNN_LAUNCH_OK("colsum_stage2_kernel");
+    }
     return ZNN_OK;
 }
 

@@ -38,6 +38,7 @@ struct ScratchSet {
     bool used = false;
     void* ws[3] = {nullptr, nullptr, nullptr};
     size_t ws_bytes[3] = {0, 0, 0};
+    unsigned* counters = nullptr;   // kScratchCounters zeroed words for kernels that let their last block finish a reduction
 };
 constexpr int kMaxScratchSets = 16;
 
@@ -158,6 +159,26 @@ void* workspace_slot(int slot, size_t bytes)
     }
     set->ws_bytes[slot] = want;
     return set->ws[slot];
+}
+
+unsigned* scratch_counters()
+{
+    DeviceState* s = cur(true);
+    if (!s) return nullptr;
+    ScratchSet* set = scratch_set(s, stream());
+    if (!set) return nullptr;
+    if (!set->counters) {
+        cudaStreamCaptureStatus cap = cudaStreamCaptureStatusNone;
+        if (cudaStreamIsCapturing(stream(), &cap) == cudaSuccess && cap != cudaStreamCaptureStatusNone) return nullptr;
+        std::lock_guard<std::mutex> lk(g_mu);
+        if (!set->counters) {
+            unsigned* c = nullptr;
+            if (cudaMalloc((void**)&c, kScratchCounters * sizeof(unsigned)) != cudaSuccess) { cudaGetLastError(); return nullptr; }
+            if (cudaMemset(c, 0, kScratchCounters * sizeof(unsigned)) != cudaSuccess) { cudaFree(c); cudaGetLastError(); return nullptr; }
+            set->counters = c;
+        }
+    }
+    return set->counters;
 }
 
 unsigned long long workspace_generation()
