@@ -19,6 +19,10 @@ int znn_gemm_set_conv_mode(int mode);
 /* In-place path only: 1 (default) = persistent launch (one CTA pair per SM pair walks the output tiles, so the
  * next tile's main loop overlaps the previous tile's epilogue); 0 = one CTA pair per output tile. */
 int znn_gemm_set_persistent(int enable);
+/* 1 (default) = products of 8..64 rows against a wide, long matrix (N, K >= 512) are computed as the transposed product (N rows,
+ * at most 64 columns: many tiles instead of a quarter-filled one per column block) and written back transposed by a small
+ * kernel (znn_gemm_last_path reports 5); 0 = such products take the ordinary path. */
+int znn_gemm_set_skinny(int enable);
 /* In-place path only: 1 (default) = when the last round of the persistent walk would be less than 70 % full, its tiles
  * are cut into K-slices (whole accumulation chunks) run by otherwise idle CTA pairs; the slices' partial tiles are added
  * in slice order by a small second kernel (deterministic).  0 = every tile is one unit. */

@@ -395,6 +395,7 @@ def _gelu_grad64(h):
 def test_linear_with_activation_and_residual_epilogue(ops, M, K, N, act, res):
     """znn_linear_fwd_ex: the activation (src/autodiff.zig:148-165) and the residual add (src/nn.zig:996-1021) in the
     GEMM epilogue, against the same steps in float64; the pre-activation copy equals the plain fused Linear bit for bit."""
+    ops.set_gemm_path(0)
     r = np.random.default_rng(M + K + N + 7 * act)
     X = r.standard_normal((M, K), np.float32)
     W = (r.standard_normal((K, N)) / np.sqrt(K)).astype(np.float32)
@@ -422,6 +423,7 @@ def test_linear_with_activation_and_residual_epilogue(ops, M, K, N, act, res):
 @pytest.mark.parametrize("fresh", [1, 0])
 def test_linear_backward_with_activation_gradient_epilogue(ops, M, K, N, x_act, fresh):
     """znn_linear_bwd_ex: dX = (dY.W^T) o act'(x_pre) in the epilogue of the data-gradient product, stored or added."""
+    ops.set_gemm_path(0)
     r = np.random.default_rng(M + K + N + x_act)
     pre = r.standard_normal((M, K), np.float32)
     X = (np.maximum(pre, 0.0) if x_act == 1 else _gelu64(pre.astype(np.float64))).astype(np.float32)
@@ -446,3 +448,45 @@ def test_fused_epilogue_refuses_small_products(ops):
     X, W, b = np.ones((64, 32), np.float32), np.ones((32, 64), np.float32), np.zeros(64, np.float32)
     with pytest.raises(ZnnError):
         ops.linear_fwd_ex(X, W, b, act=1)
+
+
+@pytest.mark.parametrize("M,N,K", [(64, 4096, 4096), (8, 4096, 2048), (20, 3000, 1284), (32, 1028, 2048)])
+@pytest.mark.parametrize("ta,tb", [(111, 111), (111, 112), (112, 111), (112, 112)])
+def test_skinny_products_run_transposed(ops, M, N, K, ta, tb):
+    """8..64 rows against a wide, long matrix: computed as the transposed product and written back by a small kernel
+    (path 5); values against float64, with beta = 1 and a leading dimension wider than N, and against the ordinary path."""
+    from znn_b200 import _lib
+    L = _lib.lib()
+    ops.set_gemm_path(0)
+    r = np.random.default_rng(M + N + K + ta + tb)
+    A = r.standard_normal((M, K) if ta == 111 else (K, M)).astype(np.float32)
+    B = r.standard_normal((K, N) if tb == 111 else (N, K)).astype(np.float32)
+    ldc = N + 8
+    C0 = r.standard_normal((M, ldc)).astype(np.float32)
+    opA = A if ta == 111 else A.T
+    opB = B if tb == 111 else B.T
+    want = 0.5 * (opA.astype(np.float64) @ opB.astype(np.float64)) + C0[:, :N]
+    got = ops.sgemm(ta, tb, M, N, K, 0.5, A, A.shape[1], B, B.shape[1], 1.0, C0.copy(), ldc)
+    assert L.dll.znn_gemm_last_path() == 5
+    scale = float(np.abs(want).max())
+    assert float(np.abs(got[:, :N] - want).max()) <= 1e-5 * scale
+    np.testing.assert_array_equal(got[:, N:], C0[:, N:])          # the padding columns are not touched
+    L.call("znn_gemm_set_skinny", 0)
+    try:
+        ref = ops.sgemm(ta, tb, M, N, K, 0.5, A, A.shape[1], B, B.shape[1], 1.0, C0.copy(), ldc)
+        assert L.dll.znn_gemm_last_path() != 5
+    finally:
+        L.call("znn_gemm_set_skinny", 1)
+    assert float(np.abs(got[:, :N] - ref[:, :N]).max()) <= 1e-5 * scale   # (below 64 rows the ordinary path is the fp32-FMA kernel)
+
+
+def test_skinny_linear_with_bias(ops):
+    """The fused Linear of a 64-row batch (decode): bias added by the write-back kernel."""
+    ops.set_gemm_path(0)
+    r = np.random.default_rng(64)
+    X = r.standard_normal((64, 768)).astype(np.float32)
+    W = (r.standard_normal((768, 3072)) / 28.0).astype(np.float32)
+    b = r.standard_normal(3072).astype(np.float32)
+    got = ops.linear_fwd(X, W, b)
+    want = X.astype(np.float64) @ W.astype(np.float64) + b
+    assert float(np.abs(got - want).max()) <= 1e-5 * float(np.abs(want).max())

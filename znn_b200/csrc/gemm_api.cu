@@ -105,6 +105,29 @@ sgemm_fma_kernel(int M, int N, int K, float alpha, const float* __restrict__ A, 
     }
 }
 
+// C[m][n] = T[n][m] + bias[n] + beta * C[m][n]: the last step of a skinny product that was computed transposed
+__global__ void transpose_finish_kernel(const float* __restrict__ T, int M, int N, const float* __restrict__ bias, float beta,
+                                        float* __restrict__ C, long long ldc)
+{
+    __shared__ float tile[32][33];
+    const int n0 = blockIdx.x * 32, m0 = blockIdx.y * 32;
+    for (int j = threadIdx.y; j < 32; j += 8) {
+        const int n = n0 + j, m = m0 + threadIdx.x;
+        tile[j][threadIdx.x] = (n < N && m < M) ? T[(size_t)n * M + m] : 0.0f;
+    }
+    __syncthreads();
+    for (int j = threadIdx.y; j < 32; j += 8) {
+        const int m = m0 + j, n = n0 + threadIdx.x;
+        if (m < M && n < N) {
+            float o = tile[threadIdx.x][j];
+            if (bias) o += bias[n];
+            float* dst = C + (size_t)m * ldc + n;
+            if (beta != 0.0f) o += beta * (*dst);
+            *dst = o;
+        }
+    }
+}
+
 // beta pass for the degenerate cases (K == 0 or alpha == 0), cblas.zig:56-70.
 __global__ void scale_c_kernel(float* C, long long ldc, long long stride_c, int M, int N, float beta)
 {
@@ -117,6 +140,7 @@ __global__ void scale_c_kernel(float* C, long long ldc, long long stride_c, int 
     }
 }
 
+static thread_local bool t_skinny = true;  // products of at most 64 rows are computed transposed (znn_gemm_set_skinny)
 static thread_local int t_path = 0;       // requested
 static thread_local int t_last_path = 0;  // taken by the last call
 
@@ -153,6 +177,24 @@ static int gemm_dispatch(int ta, int tb, int M, int N, int K, float alpha, const
     if (ep_p || ep_act != 0 || ep_res) {   // the fused epilogues exist on the in-place tensor-core path only
         if (!direct_ok) return fail(ZNN_ERR_UNSUPPORTED, "fused epilogue: operands not readable in place");
         path = 4;
+    }
+    if (path == 0 && t_skinny && batch == 1 && tri == 0 && M >= 8 && M <= 64 && (M & 3) == 0 && N >= 512 && K >= 512 &&
+        2.0 * M * N * (double)K >= 1.3e8 && gemm_tc_direct_eligible(B, ldb, 0, A, lda, 0, 1)) {
+        // A few rows against a wide matrix (a 64-row batch against a weight matrix: decode, the sweep's skinny shapes):
+        // as it stands the product would fill a quarter of one 256-row tile per column block and leave most SMs idle.
+        // The transposed product C^T = op(B)^T . op(A)^T has N rows (many tiles, split over K as well) and M <= 64
+        // columns; a small kernel writes it back transposed, adding bias and beta * C on the way.
+        float* T = (float*)workspace_slot(1, (size_t)N * M * sizeof(float));
+        if (T) {
+            const int ta2 = (tb == ZNN_NO_TRANS) ? ZNN_TRANS : ZNN_NO_TRANS, tb2 = (ta == ZNN_NO_TRANS) ? ZNN_TRANS : ZNN_NO_TRANS;
+            int rc = gemm_tc_direct(ta2, tb2, N, M, K, alpha, B, ldb, 0, A, lda, 0, 0.0f, T, M, 0, 1, nullptr, 0, nullptr, nullptr,
+                                    0, nullptr, nullptr, nullptr);
+            if (rc) return rc;
+            transpose_finish_kernel<<<dim3(ceil_div(N, 32), ceil_div(M, 32)), dim3(32, 8), 0, stream()>>>(T, M, N, bias, beta, C, ldc);
+            ZNN_LAUNCH_OK("transpose_finish_kernel");
+            t_last_path = 5;
+            return ZNN_OK;
+        }
     }
     if (path == 0) {
         // The tensor-core paths cost extra launches; below ~0.13 GFLOP per call the FMA kernel finishes sooner.
@@ -320,6 +362,12 @@ int znn_gemm_set_path(int path)
 }
 
 int znn_gemm_last_path(void) { return t_last_path; }
+
+int znn_gemm_set_skinny(int enable)
+{
+    t_skinny = (enable != 0);
+    return ZNN_OK;
+}
 
 int znn_gemm_set_chunk(int k_elements)
 {
