@@ -69,7 +69,7 @@ struct AttnCfg {
     static constexpr int kZTile = 64 * 32 * 4;                 // 64 contraction rows x this CTA's 32 output columns
     static constexpr int kZStage = 2 * kZTile;
 #ifndef ZNN_ATT_STAGES1
-#define ZNN_ATT_STAGES1 3      // three stages measured faster than six (161 against 175 us on the forward at 96 x 1024 x 64)
+#define ZNN_ATT_STAGES1 3      // three ring stages measured faster than six (161 against 175 us on the forward at 96 x 1024 x 64)
 #endif
     static constexpr int NYS = NX == 2 ? 3 : ZNN_ATT_STAGES1;
     static constexpr int NZS = NX == 2 ? 3 : ZNN_ATT_STAGES1;
@@ -450,11 +450,7 @@ attn_kernel(const __grid_constant__ CUtensorMap mx2, const __grid_constant__ CUt
             };
             auto wait_full = [&](uint32_t bar, uint32_t ph) -> bool {
                 bool got = true;
-                #ifdef ZNN_ATT_CONV_SLEEPY
-                if (lane == 0) got = ATT_PROF_WAIT(15 + pslot, mbar_wait_bounded(bar, ph, p.wait_limit));
-#else
                 if (lane == 0) got = ATT_PROF_WAIT(15 + pslot, mbar_wait_bounded_tight(bar, ph, p.wait_limit));
-#endif
                 return __shfl_sync(0xffffffffu, (int)got, 0) != 0;
             };
             auto done = [&](uint32_t leader_bar) {
@@ -488,13 +484,8 @@ attn_kernel(const __grid_constant__ CUtensorMap mx2, const __grid_constant__ CUt
                         const int s = it % NZS;
                         if (!(got = wait_full(z_full0 + 8u * s, (it / NZS) & 1))) break;
                         uint8_t* st = smem_gen + Cfg::kXBytes + NYS * Cfg::kYStage + s * Cfg::kZStage;
-#ifdef ZNN_ATT_SKIP_ZCONV
-                        (void)st;
-                        if (lane == 0) mbar_arrive_remote(z_conv_l0 + 8u * s);     // timing experiment only: results are wrong
-#else
                         convert(st, 512, Cfg::kZTile, lane, 32);
                         done(z_conv_l0 + 8u * s);
-#endif
                     }
                 }
             }
@@ -521,11 +512,7 @@ attn_kernel(const __grid_constant__ CUtensorMap mx2, const __grid_constant__ CUt
             // every lane polls (one warp-wide instruction per poll; no broadcast afterwards); the vote keeps the warp's
             // decision uniform should the limit run out for some lanes only
             auto wait_bar = [&](uint32_t bar, uint32_t ph, int slot) -> bool {
-#ifdef ZNN_ATT_XF_SLEEPY
-                const bool ok = ATT_PROF_WAIT(slot, mbar_wait_bounded(bar, ph, p.wait_limit));
-#else
                 const bool ok = ATT_PROF_WAIT(slot, mbar_wait_bounded_tight(bar, ph, p.wait_limit));
-#endif
                 return __all_sync(0xffffffffu, ok);
             };
             auto pair_sync = [&]() { asm volatile("bar.sync %0, 64;" ::"r"(1 + q) : "memory"); };   // the two warps of a lane quarter
