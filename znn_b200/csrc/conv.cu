@@ -284,6 +284,7 @@ conv2d_bwd_weight_smallk_kernel(const float* __restrict__ X, const float* __rest
         }
         const float* const xn = X + (size_t)n * Ci * HW;
         const float* const dyn = dY + (size_t)n * Co * HoWo + hw;
+#pragma unroll 4
         for (int row = grp; row < K1 + Co; row += kSkThreads / kSkTile) {
             if (row < K1) {
                 float v = 0.0f;
@@ -321,18 +322,24 @@ conv2d_bwd_weight_smallk_kernel(const float* __restrict__ X, const float* __rest
     if (i1 < pairs) partial[(size_t)blockIdx.x * pairs + i1] = acc1;
 }
 
+// One warp per (co, k) pair: lane l adds blocks l, l + 32, ... in order, then the 32 lane sums are added in lane order
+// (a fixed order, whatever the scheduling).
 __global__ void conv2d_bwd_weight_smallk_reduce_kernel(const float* __restrict__ partial, int blocks, int Co, int K,
                                                        float* __restrict__ dW, float* __restrict__ dbias)
 {
     const int K1 = K + 1, pairs = Co * K1;
-    const int i = blockIdx.x * blockDim.x + threadIdx.x;
+    const int i = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5), lane = threadIdx.x & 31;
     if (i >= pairs) return;
     const int co = i / K1, k = i - co * K1;
     if ((k == K) ? !dbias : !dW) return;
     float s = 0.0f;
-    for (int b = 0; b < blocks; b++) s += partial[(size_t)b * pairs + i];
-    if (k == K) dbias[co] += s;
-    else dW[(size_t)co * K + k] += s;
+    for (int b = lane; b < blocks; b += 32) s += partial[(size_t)b * pairs + i];
+    float t = 0.0f;
+    for (int l = 0; l < 32; l++) t += __shfl_sync(0xffffffffu, s, l);
+    if (lane == 0) {
+        if (k == K) dbias[co] += t;
+        else dW[(size_t)co * K + k] += t;
+    }
 }
 
 // the tensor-core path (conv_tc.cu)
@@ -438,7 +445,7 @@ int znn_conv2d_bwd(const float* X, const float* W, const float* dY, float* dX, f
         conv2d_bwd_weight_smallk_kernel<<<used, kSkThreads, smem, stream()>>>(X, dY, part, Ci, H, Wd, Co, KH, KW, pad, Ho, Wo,
                                                                               (int)P, (int)per);
         ZNN_LAUNCH_OK("conv2d_bwd_weight_smallk_kernel");
-        conv2d_bwd_weight_smallk_reduce_kernel<<<(pairs + 127) / 128, 128, 0, stream()>>>(part, used, Co, K, dW, dbias);
+        conv2d_bwd_weight_smallk_reduce_kernel<<<(pairs + 7) / 8, 256, 0, stream()>>>(part, used, Co, K, dW, dbias);
         ZNN_LAUNCH_OK("conv2d_bwd_weight_smallk_reduce_kernel");
         dW = nullptr;
         dbias = nullptr;

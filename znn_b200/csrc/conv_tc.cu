@@ -474,8 +474,17 @@ __global__ void conv_wgrad_reduce_kernel(const float* __restrict__ partial, int 
     if (k == K && !dbias) return;
     if (k < K && !dW) return;
     const float* src = partial + (size_t)k * nt + co;
+    const size_t pitch = (size_t)rows * nt;
     float s = 0.0f;
-    for (int sp = 0; sp < splits; sp++) s += src[(size_t)sp * rows * nt];
+    int sp = 0;
+    for (; sp + 8 <= splits; sp += 8) {   // eight loads in flight, added in split order
+        float v[8];
+#pragma unroll
+        for (int u = 0; u < 8; u++) v[u] = src[(size_t)(sp + u) * pitch];
+#pragma unroll
+        for (int u = 0; u < 8; u++) s += v[u];
+    }
+    for (; sp < splits; sp++) s += src[(size_t)sp * pitch];
     if (k == K) dbias[co] += s;
     else dW[(size_t)co * K + k] += s;
 }
@@ -579,7 +588,7 @@ int conv_tc_wgrad(const float* X, const float* dY, float* dW, float* dbias, floa
     int rc = Co <= 32 ? launch_conv_tc<CV_WGRAD, 32>(p) : launch_conv_tc<CV_WGRAD, 64>(p);
     if (rc) return rc;
     const int total = (p.K + 1) * Co;
-    conv_wgrad_reduce_kernel<<<(total + 255) / 256, 256, 0, stream()>>>(scratch, splits, p.rows, nt, p.K, Co, dW, dbias);
+    conv_wgrad_reduce_kernel<<<(total + 63) / 64, 64, 0, stream()>>>(scratch, splits, p.rows, nt, p.K, Co, dW, dbias);
     ZNN_LAUNCH_OK("conv_wgrad_reduce_kernel");
     return ZNN_OK;
 }
