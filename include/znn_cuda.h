@@ -267,12 +267,19 @@ int znn_layernorm_bwd(const float* X, const float* G, const float* dY, float eps
  * pad = 0 is the reference; pad > 0 (zero padding) is an extension. bias may be NULL. */
 int znn_conv2d_fwd(const float* X, const float* W, const float* bias, float* Y,
                    int N, int Ci, int H, int Wd, int Co, int KH, int KW, int pad);
+/* The same with the following Relu (examples/cnn.zig:35-56: relu(conv(x))) applied as the result is stored: act = 1.
+ * Y = max(0, conv(X) + bias); the pre-activation is not kept (Relu backward only needs the sign, which Y has). */
+int znn_conv2d_fwd_act(const float* X, const float* W, const float* bias, float* Y, int N, int Ci, int H, int Wd, int Co,
+                       int KH, int KW, int pad, int act);
 int znn_conv2d_bwd(const float* X, const float* W, const float* dY, float* dX, float* dW, float* dbias,
                    int N, int Ci, int H, int Wd, int Co, int KH, int KW, int pad);
 /* MaxPool2D: :389-434 / :996-1053. idx (may be NULL) receives, per output, the offset inside
  * the (n,c) input plane of the first maximum in (ph,pw) order. */
 int znn_maxpool2d_fwd(const float* X, float* Y, int32_t* idx, int N, int C, int H, int W, int pool, int stride);
 int znn_maxpool2d_bwd(const float* X, const float* dY, float* dX, int N, int C, int H, int W, int pool, int stride);
+/* MaxPool2D backward followed by the backward of the Relu that produced the pool's input X (src/autodiff.zig:996-1053,
+ * :673-683) in one pass: dX is the gradient of the Relu's INPUT; the window's winner receives g where X > 0. */
+int znn_maxpool2d_bwd_relu(const float* X, const float* dY, float* dX, int N, int C, int H, int W, int pool, int stride);
 /* Embedding (ids carried as fp32, as in the reference): :532-553 / :1183-1207.
  * The backward scatter-add is deterministic: rows with the same id are summed in (b,t) order.
  * The reference asserts id < vocab (:547); here an id outside [0, vocab) is never dereferenced: the forward writes a zero

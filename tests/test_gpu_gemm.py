@@ -390,7 +390,7 @@ def _gelu_grad64(h):
     return cdf + h * np.exp(-0.5 * h * h) / sqrt(2.0 * pi)
 
 
-@pytest.mark.parametrize("M,K,N", [(512, 512, 256), (1000, 200, 516), (1024, 256, 1280), (2048, 768, 3072)])
+@pytest.mark.parametrize("M,K,N", [(1024, 384, 256), (1000, 200, 516), (1024, 256, 1280), (2048, 768, 3072)])
 @pytest.mark.parametrize("act,res", [(0, True), (1, False), (2, False), (1, True)])
 def test_linear_with_activation_and_residual_epilogue(ops, M, K, N, act, res):
     """znn_linear_fwd_ex: the activation (src/autodiff.zig:148-165) and the residual add (src/nn.zig:996-1021) in the
@@ -418,7 +418,7 @@ def test_linear_with_activation_and_residual_epilogue(ops, M, K, N, act, res):
         assert float(np.abs(Y - ops.gelu_fwd(H)).max()) <= 1e-6 * scale
 
 
-@pytest.mark.parametrize("M,K,N", [(512, 256, 512), (1000, 516, 200), (2048, 3072, 768)])
+@pytest.mark.parametrize("M,K,N", [(1024, 256, 384), (1000, 516, 200), (2048, 3072, 768)])
 @pytest.mark.parametrize("x_act", [1, 2])
 @pytest.mark.parametrize("fresh", [1, 0])
 def test_linear_backward_with_activation_gradient_epilogue(ops, M, K, N, x_act, fresh):

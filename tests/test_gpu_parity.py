@@ -437,3 +437,35 @@ def test_adam_step(ops, zo, n):
         np.testing.assert_array_equal(m1, m2)
         np.testing.assert_array_equal(v1, v2)
         close(w1, w2, rtol=1e-6, what="adam weights")
+
+
+@pytest.mark.parametrize("N,Ci,H,W,Co,K,pad", [(64, 1, 28, 28, 4, 3, 0), (256, 32, 14, 14, 64, 3, 1), (3, 5, 9, 7, 11, 3, 1)])
+def test_conv2d_with_relu_and_pool_backward_with_relu(ops, zo, N, Ci, H, W, Co, K, pad):
+    """znn_conv2d_fwd_act(act = 1) equals Relu of znn_conv2d_fwd bit for bit (direct and tensor-core path), and
+    znn_maxpool2d_bwd_relu equals MaxPool2D backward followed by Relu backward (src/autodiff.zig:996-1053, :673-683)."""
+    import ctypes as C
+    from znn_b200 import _lib
+    L = _lib.lib()
+    r = rng(N + Ci + H + Co)
+    X = r.standard_normal((N, Ci, H, W), np.float32)
+    Wt = (r.standard_normal((Co, Ci, K, K)) * 0.3).astype(np.float32)
+    b = (r.standard_normal(Co) * 0.1).astype(np.float32)
+    Y = ops.conv2d_fwd(X, Wt, b, pad)
+    Ho, Wo = Y.shape[2], Y.shape[3]
+    x, w, bb = ops._up(X), ops._up(Wt), ops._up(b)
+    yr = ops.DevBuf(Y.size * 4)
+    L.call("znn_conv2d_fwd_act", x.ptr, w.ptr, bb.ptr, yr.ptr, N, Ci, H, W, Co, K, K, pad, 1)
+    R = yr.to_host(Y.shape)
+    np.testing.assert_array_equal(R, np.maximum(Y, 0.0))
+    # pool backward with the Relu mask, against the two reference arms run one after the other
+    dYp = r.standard_normal((N, Co, Ho // 2, Wo // 2), np.float32)
+    dA = np.zeros_like(R)
+    zo.maxpool2d_bwd(R, dYp, dA, 2, 2)
+    want = r.standard_normal(R.shape, np.float32)
+    got0 = want.copy()
+    zo.relu_bwd(Y, dA, want)
+    g = ops._up(got0)
+    dy = ops._up(dYp)
+    L.call("znn_maxpool2d_bwd_relu", yr.ptr, dy.ptr, g.ptr, N, Co, Ho, Wo, 2, 2)
+    g.into(got0)
+    np.testing.assert_array_equal(got0, want)

@@ -129,9 +129,11 @@ pub extern fn znn_rmsnorm_bwd(X: ?[*]const f32, G: ?[*]const f32, dY: ?[*]const 
 pub extern fn znn_layernorm_fwd(X: ?[*]const f32, G: ?[*]const f32, B: ?[*]const f32, eps: f32, Y: ?[*]f32, rows: usize, D: c_int) c_int;
 pub extern fn znn_layernorm_bwd(X: ?[*]const f32, G: ?[*]const f32, dY: ?[*]const f32, eps: f32, dX: ?[*]f32, dG: ?[*]f32, dB: ?[*]f32, rows: usize, D: c_int) c_int;
 pub extern fn znn_conv2d_fwd(X: ?[*]const f32, W: ?[*]const f32, bias: ?[*]const f32, Y: ?[*]f32, N: c_int, Ci: c_int, H: c_int, Wd: c_int, Co: c_int, KH: c_int, KW: c_int, pad: c_int) c_int;
+pub extern fn znn_conv2d_fwd_act(X: ?[*]const f32, W: ?[*]const f32, bias: ?[*]const f32, Y: ?[*]f32, N: c_int, Ci: c_int, H: c_int, Wd: c_int, Co: c_int, KH: c_int, KW: c_int, pad: c_int, act: c_int) c_int;
 pub extern fn znn_conv2d_bwd(X: ?[*]const f32, W: ?[*]const f32, dY: ?[*]const f32, dX: ?[*]f32, dW: ?[*]f32, dbias: ?[*]f32, N: c_int, Ci: c_int, H: c_int, Wd: c_int, Co: c_int, KH: c_int, KW: c_int, pad: c_int) c_int;
 pub extern fn znn_maxpool2d_fwd(X: ?[*]const f32, Y: ?[*]f32, idx: ?[*]i32, N: c_int, C: c_int, H: c_int, W: c_int, pool: c_int, stride: c_int) c_int;
 pub extern fn znn_maxpool2d_bwd(X: ?[*]const f32, dY: ?[*]const f32, dX: ?[*]f32, N: c_int, C: c_int, H: c_int, W: c_int, pool: c_int, stride: c_int) c_int;
+pub extern fn znn_maxpool2d_bwd_relu(X: ?[*]const f32, dY: ?[*]const f32, dX: ?[*]f32, N: c_int, C: c_int, H: c_int, W: c_int, pool: c_int, stride: c_int) c_int;
 pub extern fn znn_embedding_fwd(W: ?[*]const f32, ids: ?[*]const f32, Y: ?[*]f32, n: usize, D: c_int, vocab: c_int) c_int;
 pub extern fn znn_embedding_bwd(ids: ?[*]const f32, dY: ?[*]const f32, dW: ?[*]f32, n: usize, D: c_int, vocab: c_int) c_int;
 pub extern fn znn_transpose_fwd(A: ?[*]const f32, C: ?[*]f32, dims: ?[*]const i64, rank: c_int, d0: c_int, d1: c_int) c_int;

@@ -19,6 +19,7 @@ constexpr int kCoTile = 8;  // output channels per thread
 
 // One thread: one output pixel (n, h, w) for kCoTile consecutive output channels.
 // The weights of the channel tile sit in shared memory.
+template <bool Relu>
 __global__ void conv2d_fwd_kernel(const float* __restrict__ X, const float* __restrict__ W, const float* __restrict__ bias,
                                   float* __restrict__ Y, int N, int Ci, int H, int Wd, int Co, int KH, int KW, int pad,
                                   int Ho, int Wo)
@@ -55,7 +56,7 @@ __global__ void conv2d_fwd_kernel(const float* __restrict__ X, const float* __re
         }
 #pragma unroll
     for (int c = 0; c < kCoTile; c++)
-        if (co0 + c < Co) Y[(((size_t)n * Co + co0 + c) * Ho + h) * Wo + w] = acc[c];
+        if (co0 + c < Co) Y[(((size_t)n * Co + co0 + c) * Ho + h) * Wo + w] = Relu ? fmaxf(acc[c], 0.0f) : acc[c];
 }
 
 // dX[n,ci,ih,iw] += sum_{co,kh,kw} dY[n,co,ih-kh+pad,iw-kw+pad] * W[co,ci,kh,kw]  (gather form)
@@ -171,7 +172,9 @@ __global__ void maxpool2d_fwd_kernel(const float* __restrict__ X, float* __restr
     }
 }
 
-template <bool Overlap>
+// ReluMask: X is the output of a ReLU and dX the gradient of the ReLU's input: the winner receives g only where X > 0
+// (MaxPool2D backward and Relu backward, src/autodiff.zig:996-1053 and :673-683, in one pass).
+template <bool Overlap, bool ReluMask>
 __global__ void maxpool2d_bwd_kernel(const float* __restrict__ X, const float* __restrict__ dY, float* __restrict__ dX,
                                      size_t planes, int H, int W, int Ho, int Wo, int pool, int stride)
 {
@@ -183,6 +186,7 @@ __global__ void maxpool2d_bwd_kernel(const float* __restrict__ X, const float* _
         const size_t pl = e / ((size_t)Wo * Ho);
         float best;
         const int bi = pool_argmax(X + pl * H * W, H, W, h, w, pool, stride, best);
+        if (ReluMask && !(best > 0.0f)) continue;
         // windows are disjoint when stride >= pool: a plain add is race-free
         if (Overlap) atomicAdd(dX + pl * H * W + bi, g); else dX[pl * H * W + bi] += g;
     }
@@ -373,26 +377,36 @@ int znn_debug_conv_profile(long long* out16)
     return conv_profile_read(out16);
 }
 
-int znn_conv2d_fwd(const float* X, const float* W, const float* bias, float* Y, int N, int Ci, int H, int Wd, int Co,
-                   int KH, int KW, int pad)
+int znn_conv2d_fwd_act(const float* X, const float* W, const float* bias, float* Y, int N, int Ci, int H, int Wd, int Co,
+                       int KH, int KW, int pad, int act)
 {
     ZNN_REQUIRE(N >= 0 && Ci > 0 && Co > 0 && KH > 0 && KW > 0 && pad >= 0, "bad conv shape");
+    ZNN_REQUIRE(act == 0 || act == 1, "act is 0 (none) or 1 (ReLU)");
     const int Ho = H + 2 * pad - KH + 1, Wo = Wd + 2 * pad - KW + 1;
     ZNN_REQUIRE(Ho > 0 && Wo > 0, "kernel larger than padded input");
     if (N == 0) return ZNN_OK;
     if (!stream()) return fail(ZNN_ERR_CUDA, "no CUDA device state; call znn_init (no CPU fallback)");
     ZNN_REQUIRE(X && W && Y, "NULL pointer");
     if (conv_tc_applicable(N, Ci, H, Wd, Co, KH, KW, Ho, Wo))   // implicit-im2col GEMM on the tensor cores
-        return conv_tc_forward(X, W, bias, Y, N, Ci, H, Wd, Co, KH, KW, pad, pad, 0);
+        return conv_tc_forward(X, W, bias, Y, N, Ci, H, Wd, Co, KH, KW, pad, pad, act ? 2 : 0);
     const size_t smem = (size_t)kCoTile * Ci * KH * KW * sizeof(float);
     ZNN_REQUIRE(smem <= 96 * 1024, "Ci*KH*KW = %d is beyond what the direct kernel keeps in shared memory", Ci * KH * KW);
-    if (smem > 48 * 1024)
-        ZNN_CUDA_OK(cudaFuncSetAttribute(conv2d_fwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    if (smem > 48 * 1024) {
+        ZNN_CUDA_OK(cudaFuncSetAttribute(conv2d_fwd_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+        ZNN_CUDA_OK(cudaFuncSetAttribute(conv2d_fwd_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    }
     const size_t npix = (size_t)N * Ho * Wo;
     dim3 grid((unsigned)((npix + 127) / 128), ceil_div(Co, kCoTile));
-    conv2d_fwd_kernel<<<grid, 128, smem, stream()>>>(X, W, bias, Y, N, Ci, H, Wd, Co, KH, KW, pad, Ho, Wo);
+    if (act) conv2d_fwd_kernel<true><<<grid, 128, smem, stream()>>>(X, W, bias, Y, N, Ci, H, Wd, Co, KH, KW, pad, Ho, Wo);
+    else conv2d_fwd_kernel<false><<<grid, 128, smem, stream()>>>(X, W, bias, Y, N, Ci, H, Wd, Co, KH, KW, pad, Ho, Wo);
     ZNN_LAUNCH_OK("conv2d_fwd_kernel");
     return ZNN_OK;
+}
+
+int znn_conv2d_fwd(const float* X, const float* W, const float* bias, float* Y, int N, int Ci, int H, int Wd, int Co,
+                   int KH, int KW, int pad)
+{
+    return znn_conv2d_fwd_act(X, W, bias, Y, N, Ci, H, Wd, Co, KH, KW, pad, 0);
 }
 
 int znn_conv2d_bwd(const float* X, const float* W, const float* dY, float* dX, float* dW, float* dbias, int N, int Ci,
@@ -529,7 +543,8 @@ int znn_maxpool2d_fwd(const float* X, float* Y, int32_t* idx, int N, int C, int 
     return ZNN_OK;
 }
 
-int znn_maxpool2d_bwd(const float* X, const float* dY, float* dX, int N, int C, int H, int W, int pool, int stride)
+static int maxpool2d_bwd_impl(const float* X, const float* dY, float* dX, int N, int C, int H, int W, int pool, int stride,
+                              bool relu_mask)
 {
     ZNN_REQUIRE(pool > 0 && stride > 0, "bad pooling parameters");
     const int Ho = H / stride, Wo = W / stride;
@@ -540,12 +555,26 @@ int znn_maxpool2d_bwd(const float* X, const float* dY, float* dX, int N, int C, 
     size_t blocks = (total + 255) / 256;
     const size_t cap = (size_t)sm_count() * 32;
     if (blocks > cap) blocks = cap;
-    if (stride < pool)
-        maxpool2d_bwd_kernel<true><<<(unsigned)blocks, 256, 0, stream()>>>(X, dY, dX, planes, H, W, Ho, Wo, pool, stride);
-    else
-        maxpool2d_bwd_kernel<false><<<(unsigned)blocks, 256, 0, stream()>>>(X, dY, dX, planes, H, W, Ho, Wo, pool, stride);
+    const unsigned nb = (unsigned)blocks;
+    if (stride < pool) {
+        if (relu_mask) maxpool2d_bwd_kernel<true, true><<<nb, 256, 0, stream()>>>(X, dY, dX, planes, H, W, Ho, Wo, pool, stride);
+        else maxpool2d_bwd_kernel<true, false><<<nb, 256, 0, stream()>>>(X, dY, dX, planes, H, W, Ho, Wo, pool, stride);
+    } else {
+        if (relu_mask) maxpool2d_bwd_kernel<false, true><<<nb, 256, 0, stream()>>>(X, dY, dX, planes, H, W, Ho, Wo, pool, stride);
+        else maxpool2d_bwd_kernel<false, false><<<nb, 256, 0, stream()>>>(X, dY, dX, planes, H, W, Ho, Wo, pool, stride);
+    }
     ZNN_LAUNCH_OK("maxpool2d_bwd_kernel");
     return ZNN_OK;
+}
+
+int znn_maxpool2d_bwd(const float* X, const float* dY, float* dX, int N, int C, int H, int W, int pool, int stride)
+{
+    return maxpool2d_bwd_impl(X, dY, dX, N, C, H, W, pool, stride, false);
+}
+
+int znn_maxpool2d_bwd_relu(const float* X, const float* dY, float* dX, int N, int C, int H, int W, int pool, int stride)
+{
+    return maxpool2d_bwd_impl(X, dY, dX, N, C, H, W, pool, stride, true);
 }
 
 }  // extern "C"

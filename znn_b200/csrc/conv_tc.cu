@@ -74,6 +74,7 @@ struct ConvTcParams {
     int nunits;          // forward: row tiles; weight gradient: splits * (rows / 128)
     long long P;         // N*Ho*Wo
     int accumulate;      // forward: out += product (no bias)
+    int relu;            // forward, storing form: out = max(0, product + bias)
     int* status;
     unsigned long long wait_limit;
 };
@@ -442,7 +443,10 @@ __global__ void __launch_bounds__(kCvThreads, 1) conv_tc_kernel(const ConvTcPara
                         }
 #pragma unroll
                         for (int j = 0; j < 16; j++)
-                            if (c0 + j < p.Co) o[(long long)(c0 + j) * HoWo] = acc[c0 + j] + add[j];
+                            if (c0 + j < p.Co) {
+                                const float v = acc[c0 + j] + add[j];
+                                o[(long long)(c0 + j) * HoWo] = p.relu ? fmaxf(v, 0.0f) : v;
+                            }
                     }
                 }
             } else {
@@ -549,6 +553,9 @@ int conv_tc_forward(const float* src, const float* wm, const float* bias, float*
                     int KH, int KW, int pad_h, int pad_w, int accumulate)
 {
     ConvTcParams p{};
+    // accumulate: 0 = store product + bias, 1 = add the product to out (no bias), 2 = store max(0, product + bias)
+    p.relu = (accumulate == 2);
+    if (accumulate == 2) accumulate = 0;
     p.src = src; p.bmat = wm; p.bias = accumulate ? nullptr : bias; p.out = out;
     p.C = C; p.H = H; p.W = W; p.KH = KH; p.KW = KW; p.pad_h = pad_h; p.pad_w = pad_w;
     p.Ho = H + 2 * pad_h - KH + 1; p.Wo = W + 2 * pad_w - KW + 1;

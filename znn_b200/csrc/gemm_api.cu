@@ -20,6 +20,7 @@ int gemm_tc_direct(int ta, int tb, int M, int N, int K, float alpha, const float
                    int ep_act, float* ep_out2, const float* ep_res, const float* ep_dpre);
 int launch_splitk_reduce(const float* partial, int splits, int M, int N, int batch, float alpha, float beta, float* C,
                          long long ldc, long long stride_c, const float* bias);
+bool tc_plan_splits_k(int M, int N, int K);
 int tc_profile_enable(int enable);
 void tc_set_chunk_kblocks(int v);
 void tc_set_splitk(int on);
@@ -332,6 +333,8 @@ int znn_linear_fwd_ex(const float* X, const float* W, const float* bias, float* 
     // the epilogue forms live on the tensor-core path: shapes the dispatcher sends to the FMA kernel keep the two-op form
     if (!(2.0 * M * N * (double)K >= 1.3e8 && M >= 64 && N >= 32 && K >= 32))
         return fail(ZNN_ERR_UNSUPPORTED, "fused epilogue: product too small for the tensor-core path");
+    if (tc_plan_splits_k(M, N, K))   // few tiles, long contraction: the split-K form (partials + reduce kernel) is faster
+        return fail(ZNN_ERR_UNSUPPORTED, "fused epilogue: this product is split over K");
     return gemm_dispatch(ZNN_NO_TRANS, ZNN_NO_TRANS, M, N, K, 1.0f, X, K, 0, W, N, 0, 0.0f, Y, N, 0, 1, bias, 0, nullptr, nullptr,
                          act, pre, residual, nullptr);
 }
@@ -344,6 +347,7 @@ int znn_linear_bwd_ex(const float* X, const float* W, const float* dY, float* dX
     ZNN_REQUIRE(x_pre, "x_pre is NULL");
     if (!(2.0 * M * N * (double)K >= 1.3e8 && M >= 64 && K >= 32 && N >= 32))
         return fail(ZNN_ERR_UNSUPPORTED, "fused epilogue: product too small for the tensor-core path");
+    if (tc_plan_splits_k(M, K, N)) return fail(ZNN_ERR_UNSUPPORTED, "fused epilogue: this product is split over K");
     int rc;
     // dX (+)= (dY . W^T) o act'(x_pre): the gradient with respect to the pre-activation of the layer below
     if ((rc = gemm_dispatch(ZNN_NO_TRANS, ZNN_TRANS, M, K, N, 1.0f, dY, N, 0, W, N, 0, dx_fresh ? 0.0f : 1.0f, dX, K, 0, 1, nullptr,

@@ -1551,6 +1551,10 @@ static TcPlan make_plan(int M, int N, int K, int batch, int ctas, bool tail_ok =
 }
 
 // op(A) is M x K, op(B) is K x N.  ctas = 1 or 2.
+// True when the plan for this product cuts the contraction over several CTA pairs (few output tiles, long K): the
+// epilogue forms that finish the result in the GEMM kernel itself do not exist for such products.
+bool tc_plan_splits_k(int M, int N, int K) { return make_plan(M, N, K, 1, 2).splits > 1; }
+
 int gemm_tc(int ta, int tb, int M, int N, int K, float alpha, const float* A, long long lda, long long stride_a,
             const float* B, long long ldb, long long stride_b, float beta, float* C, long long ldc,
             long long stride_c, int batch, int ctas, const float* bias)

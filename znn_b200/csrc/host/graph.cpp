@@ -311,6 +311,24 @@ Tensor* Graph::conv2d(Tensor* A, Tensor* W, Tensor* bias, int pad)
     return C;
 }
 
+Tensor* Graph::conv2dRelu(Tensor* A, Tensor* W, Tensor* bias, int pad)
+{
+    if (A->shape.len != 4 || W->shape.len != 4 || A->shape.dims[1] != W->shape.dims[1])
+        throw Error(ZNN_ERR_INVALID, "conv2d: need NCHW input and [Co,Ci,KH,KW] weights with matching Ci");
+    const size_t Ho = A->shape.dims[2] + 2 * pad - W->shape.dims[2] + 1;
+    const size_t Wo = A->shape.dims[3] + 2 * pad - W->shape.dims[3] + 1;
+    Tensor* P = new_tensor(Shape{A->shape.dims[0], W->shape.dims[0], Ho, Wo}, any_grad({A, W, bias}), false);
+    Op* o = bias ? new_op(OpType::Conv2D, {A, W, bias}, P) : new_op(OpType::Conv2D, {A, W}, P);
+    o->pad = pad;
+    Tensor* R = new_tensor(P->shape, P->requires_grad, false);
+    new_op(OpType::Relu, {P}, R);
+    check(znn_conv2d_fwd_act(A->data, W->data, bias ? bias->data : nullptr, R->data, (int)A->shape.dims[0], (int)A->shape.dims[1],
+                             (int)A->shape.dims[2], (int)A->shape.dims[3], (int)W->shape.dims[0], (int)W->shape.dims[2],
+                             (int)W->shape.dims[3], pad, 1),
+          "Conv2D + Relu forward");
+    return R;
+}
+
 Tensor* Graph::maxpool2d(Tensor* A, int pool, int stride)
 {
     if (A->shape.len != 4 || pool <= 0 || stride <= 0) throw Error(ZNN_ERR_INVALID, "maxpool2d: bad arguments");
@@ -623,7 +641,8 @@ void Op::backward()
               "AddBias backward");
         break;
     case OpType::Relu:
-        if (A->requires_grad) check(znn_relu_bwd(A->data, C->grad, A->grad, A->numel()), "Relu backward");
+        // the mask is read from the output (max(0, a) > 0 exactly where a > 0): a fused producer need not keep a
+        if (A->requires_grad) check(znn_relu_bwd(C->data, C->grad, A->grad, A->numel()), "Relu backward");
         break;
     case OpType::Gelu:
         if (A->requires_grad) {
@@ -679,10 +698,24 @@ void Op::backward()
         break;
     }
     case OpType::MaxPool2D:
-        if (A->requires_grad)
+        if (A->requires_grad) {
+            // the pool's input is a Relu output nobody else reads: the winner's gradient goes straight to the Relu's
+            // input, masked by the sign, and the Relu's own backward is skipped
+            Op* prod = A->creator;
+            if ((g_fused_epilogue & 2) && prod && prod->type == OpType::Relu && A->consumers == 1 && prod->inputs[0]->requires_grad &&
+                prod->inputs[0]->grad && grad_is_fresh(A)) {
+                Tensor* P = prod->inputs[0];
+                ensure_grad(P);
+                check(znn_maxpool2d_bwd_relu(A->data, C->grad, P->grad, (int)A->shape.dims[0], (int)A->shape.dims[1],
+                                             (int)A->shape.dims[2], (int)A->shape.dims[3], pool, stride),
+                      "MaxPool2D + Relu backward");
+                prod->skip_backward = true;
+                break;
+            }
             check(znn_maxpool2d_bwd(A->data, C->grad, A->grad, (int)A->shape.dims[0], (int)A->shape.dims[1], (int)A->shape.dims[2],
                                     (int)A->shape.dims[3], pool, stride),
                   "MaxPool2D backward");
+        }
         break;
     case OpType::Softmax:
         if (A->requires_grad) {

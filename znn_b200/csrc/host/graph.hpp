@@ -185,6 +185,9 @@ public:
     Tensor* linearAct(Tensor* X, Tensor* W, Tensor* bias, OpType act);
     // add(R, linear(X, W, bias)): the residual is added in the GEMM's epilogue when the form applies
     Tensor* linearResidual(Tensor* X, Tensor* W, Tensor* bias, Tensor* R);
+    // relu(conv2d(A, W, bias)): the tape gets the Conv2D and the Relu op, one kernel stores max(0, .) (the pre-activation is
+    // not kept: no backward arm reads it)
+    Tensor* conv2dRelu(Tensor* A, Tensor* W, Tensor* bias, int pad);
 
     // `after_op(op)` is called after a tape op has run its
     // backward arm; data-parallel training uses it to start gradient all-reduces.

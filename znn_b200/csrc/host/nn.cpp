@@ -117,6 +117,12 @@ Conv2D::Conv2D(ParamStore& ps, const std::string& name, size_t in_ch, size_t out
 
 Tensor* Conv2D::forward(Graph& g, Tensor* x) const { return g.conv2d(x, weight, bias, pad); }
 
+Tensor* Conv2D::forward_relu(Graph& g, Tensor* x) const
+{
+    if (fused_epilogue() & 2) return g.conv2dRelu(x, weight, bias, pad);
+    return g.relu(g.conv2d(x, weight, bias, pad));
+}
+
 Embedding::Embedding(ParamStore& ps, const std::string& name, size_t vocab, size_t dim)
 {
     weight = ps.add(name + ".weight", Shape{vocab, dim}, dim);  // fan_in = n_embd (nn.zig:520)
@@ -304,16 +310,16 @@ Tensor* CnnNet::forward(Graph& g, Tensor* x) const
     Tensor* xr = g.reshape(x, Shape{B, 1, 28, 28});
     if (reference_shape) {
         // examples/cnn.zig:35-56
-        Tensor* p1 = g.maxpool2d(g.relu(conv1.forward(g, xr)), 2, 2);
-        Tensor* p2 = g.maxpool2d(g.relu(conv2.forward(g, p1)), 2, 2);
-        Tensor* a3 = g.relu(conv3.forward(g, p2));
+        Tensor* p1 = g.maxpool2d(conv1.forward_relu(g, xr), 2, 2);
+        Tensor* p2 = g.maxpool2d(conv2.forward_relu(g, p1), 2, 2);
+        Tensor* a3 = conv3.forward_relu(g, p2);
         Tensor* flat = g.reshape(a3, Shape{B, 144});
         return fc1.forward(g, flat);
     }
-    Tensor* p1 = g.maxpool2d(g.relu(conv1.forward(g, xr)), 2, 2);   // 32 @ 14x14
-    Tensor* p2 = g.maxpool2d(g.relu(conv2.forward(g, p1)), 2, 2);   // 64 @ 7x7
+    Tensor* p1 = g.maxpool2d(conv1.forward_relu(g, xr), 2, 2);   // 32 @ 14x14
+    Tensor* p2 = g.maxpool2d(conv2.forward_relu(g, p1), 2, 2);   // 64 @ 7x7
     Tensor* flat = g.reshape(p2, Shape{B, 3136});
-    Tensor* a = g.relu(fc1.forward(g, flat));
+    Tensor* a = fc1.forward_act(g, flat, OpType::Relu);
     return fc2.forward(g, a);
 }
 

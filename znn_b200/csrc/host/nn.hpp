@@ -78,6 +78,7 @@ struct Conv2D {
     Conv2D() = default;
     Conv2D(ParamStore& ps, const std::string& name, size_t in_ch, size_t out_ch, size_t k, int pad = 0);
     Tensor* forward(Graph& g, Tensor* x) const;
+    Tensor* forward_relu(Graph& g, Tensor* x) const;   // relu(forward(x))
 };
 
 // src/nn.zig:509-542
