@@ -180,6 +180,17 @@ int znn_rowdot(const float* A, const float* B, float* out, size_t rows, int D);
  * dbias += column sums of dY; NULL gradient pointers are skipped. */
 int znn_linear_fwd(const float* X, const float* W, const float* bias, float* Y, int M, int K, int N);
 int znn_linear_bwd(const float* X, const float* W, const float* dY, float* dX, float* dW, float* dbias, int M, int K, int N);
+/* Grouped products on the in-place tensor-core path (the three projections of CausalSelfAttention.forward share their
+ * input: src/nn.zig:776-793), `batch` slices at uniform strides (in floats); a stride of 0 means one matrix shared by all slices.
+ *   kcat = 0: C_s = alpha * op(A_s).op(B_s) + bias_s + beta * C_s for every slice (bias may be NULL; bias_s = bias + s*stride_bias).
+ *   kcat = 1: ONE product whose contraction runs through the slices one after the other,
+ *             C = alpha * sum_s op(A_s).op(B_s) + beta * C  (stride_c ignored, no bias, K a multiple of 32): the sum of the
+ *             slices' data gradients in one launch instead of `batch` accumulating ones.
+ * ZNN_ERR_UNSUPPORTED when the operands cannot be read in place (16-byte alignment) or the product is too small: the caller
+ * then makes `batch` znn_sgemm calls. */
+int znn_sgemm_grouped(int trans_a, int trans_b, int M, int N, int K, float alpha, const float* A, int lda, long long stride_a,
+                      const float* B, int ldb, long long stride_b, float beta, float* C, int ldc, long long stride_c, int batch,
+                      const float* bias, long long stride_bias, int kcat);
 /* Linear with the next elementwise step folded into the GEMM epilogue (src/nn.zig:660-668: gelu(c_fc(x)); :996-1021:
  * x + c_proj(...)):  h = X.W + bias (+ residual);  Y = act(h),  act = 0 none, 1 ReLU, 2 GELU (erf form, autodiff.zig:156-165).
  * pre (may be NULL) receives h, which the activation's backward needs; residual (may be NULL) has Y's shape.

@@ -490,3 +490,54 @@ def test_skinny_linear_with_bias(ops):
     got = ops.linear_fwd(X, W, b)
     want = X.astype(np.float64) @ W.astype(np.float64) + b
     assert float(np.abs(got - want).max()) <= 1e-5 * float(np.abs(want).max())
+
+
+def test_grouped_products_shared_input_and_bias_per_slice(ops):
+    """znn_sgemm_grouped, kcat = 0: three Linear layers on one input (the q, k, v projections, src/nn.zig:776-793) in one
+    launch: A shared (stride 0), weights and biases at a uniform stride inside one parameter block, outputs in slices."""
+    ops.set_gemm_path(0)
+    r = np.random.default_rng(301)
+    M, K, N, nb = 1024, 256, 384, 3
+    X = r.standard_normal((M, K)).astype(np.float32)
+    sW = K * N + N + 4                                   # weight, bias, a little padding: as in a parameter slab
+    params = r.standard_normal(nb * sW).astype(np.float32)
+    sY = 2 * M * N                                       # value and gradient buffers alternate in the arena
+    Y = np.zeros(nb * sY, np.float32)
+    ops.sgemm_grouped(111, 111, M, N, K, 1.0, X, K, 0, params, N, sW, 0.0, Y, N, sY, nb, bias=params[K * N:], sbias=sW)
+    for s_ in range(nb):
+        W = params[s_ * sW: s_ * sW + K * N].reshape(K, N).astype(np.float64)
+        b = params[s_ * sW + K * N: s_ * sW + K * N + N].astype(np.float64)
+        want = X.astype(np.float64) @ W + b
+        got = Y[s_ * sY: s_ * sY + M * N].reshape(M, N)
+        assert float(np.abs(got - want).max()) <= 1e-5 * float(np.abs(want).max())
+        assert not Y[s_ * sY + M * N: (s_ + 1) * sY].any()           # the gap between the slices is untouched
+
+
+def test_grouped_weight_gradients_and_concatenated_data_gradient(ops):
+    """kcat = 0 with beta = 1 (dW_s += X^T.dY_s, X shared) and kcat = 1 (dX += sum_s dY_s.W_s^T as one product whose
+    contraction runs through the slices)."""
+    ops.set_gemm_path(0)
+    r = np.random.default_rng(302)
+    M, K, N, nb = 2048, 256, 256, 3
+    X = r.standard_normal((M, K)).astype(np.float32)
+    sY = 2 * M * N
+    dY = np.zeros(nb * sY, np.float32)
+    for s_ in range(nb):
+        dY[s_ * sY: s_ * sY + M * N] = r.standard_normal(M * N).astype(np.float32)
+    sW = K * N + N + 4
+    W = r.standard_normal(nb * sW).astype(np.float32)
+    dW0 = r.standard_normal(nb * sW).astype(np.float32)
+    dW = dW0.copy()
+    ops.sgemm_grouped(112, 111, K, N, M, 1.0, X, K, 0, dY, N, sY, 1.0, dW, N, sW, nb)
+    dX0 = r.standard_normal((M, K)).astype(np.float32)
+    dX = dX0.copy()
+    ops.sgemm_grouped(111, 112, M, K, N, 1.0, dY, N, sY, W, N, sW, 1.0, dX, K, 0, nb, kcat=1)
+    want_dx = dX0.astype(np.float64)
+    for s_ in range(nb):
+        g = dY[s_ * sY: s_ * sY + M * N].reshape(M, N).astype(np.float64)
+        want = dW0[s_ * sW: s_ * sW + K * N].reshape(K, N) + X.astype(np.float64).T @ g
+        got = dW[s_ * sW: s_ * sW + K * N].reshape(K, N)
+        assert float(np.abs(got - want).max()) <= 1e-5 * float(np.abs(want).max())
+        np.testing.assert_array_equal(dW[s_ * sW + K * N: (s_ + 1) * sW], dW0[s_ * sW + K * N: (s_ + 1) * sW])
+        want_dx += g @ W[s_ * sW: s_ * sW + K * N].reshape(K, N).astype(np.float64).T
+    assert float(np.abs(dX - want_dx).max()) <= 1e-5 * float(np.abs(want_dx).max())

@@ -101,6 +101,7 @@ pub extern fn znn_attn_bwd(Q: ?[*]const f32, K: ?[*]const f32, V: ?[*]const f32,
 pub extern fn znn_rowdot(A: ?[*]const f32, B: ?[*]const f32, out: ?[*]f32, rows: usize, D: c_int) c_int;
 pub extern fn znn_linear_fwd(X: ?[*]const f32, W: ?[*]const f32, bias: ?[*]const f32, Y: ?[*]f32, M: c_int, K: c_int, N: c_int) c_int;
 pub extern fn znn_linear_bwd(X: ?[*]const f32, W: ?[*]const f32, dY: ?[*]const f32, dX: ?[*]f32, dW: ?[*]f32, dbias: ?[*]f32, M: c_int, K: c_int, N: c_int) c_int;
+pub extern fn znn_sgemm_grouped(trans_a: c_int, trans_b: c_int, M: c_int, N: c_int, K: c_int, alpha: f32, A: ?[*]const f32, lda: c_int, stride_a: c_longlong, B: ?[*]const f32, ldb: c_int, stride_b: c_longlong, beta: f32, C: ?[*]f32, ldc: c_int, stride_c: c_longlong, batch: c_int, bias: ?[*]const f32, stride_bias: c_longlong, kcat: c_int) c_int;
 pub extern fn znn_linear_fwd_ex(X: ?[*]const f32, W: ?[*]const f32, bias: ?[*]const f32, Y: ?[*]f32, pre: ?[*]f32, residual: ?[*]const f32, M: c_int, K: c_int, N: c_int, act: c_int) c_int;
 pub extern fn znn_linear_bwd_ex(X: ?[*]const f32, W: ?[*]const f32, dY: ?[*]const f32, dX: ?[*]f32, dW: ?[*]f32, dbias: ?[*]f32, M: c_int, K: c_int, N: c_int, x_pre: ?[*]const f32, x_act: c_int, dx_fresh: c_int) c_int;
 pub extern fn znn_gemm_set_path(path: c_int) c_int;

@@ -17,7 +17,7 @@ bool gemm_tc_direct_eligible(const float* A, long long lda, long long stride_a, 
 int gemm_tc_direct(int ta, int tb, int M, int N, int K, float alpha, const float* A, long long lda, long long stride_a,
                    const float* B, long long ldb, long long stride_b, float beta, float* C, long long ldc,
                    long long stride_c, int batch, const float* bias, int tri, const float* ep_p, const float* ep_d,
-                   int ep_act, float* ep_out2, const float* ep_res, const float* ep_dpre);
+                   int ep_act, float* ep_out2, const float* ep_res, const float* ep_dpre, long long stride_bias, int kcat);
 int launch_splitk_reduce(const float* partial, int splits, int M, int N, int batch, float alpha, float beta, float* C,
                          long long ldc, long long stride_c, const float* bias);
 bool tc_plan_splits_k(int M, int N, int K);
@@ -150,7 +150,8 @@ static int gemm_dispatch(int ta, int tb, int M, int N, int K, float alpha, const
                          long long stride_a, const float* B, long long ldb, long long stride_b, float beta, float* C,
                          long long ldc, long long stride_c, int batch, const float* bias = nullptr, int tri = 0,
                          const float* ep_p = nullptr, const float* ep_d = nullptr, int ep_act = 0, float* ep_out2 = nullptr,
-                         const float* ep_res = nullptr, const float* ep_dpre = nullptr)
+                         const float* ep_res = nullptr, const float* ep_dpre = nullptr, long long stride_bias = 0, int kcat = 0,
+                         bool grouped = false)
 {
     ZNN_REQUIRE(ta == ZNN_NO_TRANS || ta == ZNN_TRANS, "trans_a must be 111 or 112");
     ZNN_REQUIRE(tb == ZNN_NO_TRANS || tb == ZNN_TRANS, "trans_b must be 111 or 112");
@@ -175,11 +176,11 @@ static int gemm_dispatch(int ta, int tb, int M, int N, int K, float alpha, const
 
     int path = t_path;
     const bool direct_ok = gemm_tc_direct_eligible(A, lda, stride_a, B, ldb, stride_b, batch);
-    if (ep_p || ep_act != 0 || ep_res) {   // the fused epilogues exist on the in-place tensor-core path only
-        if (!direct_ok) return fail(ZNN_ERR_UNSUPPORTED, "fused epilogue: operands not readable in place");
+    if (ep_p || ep_act != 0 || ep_res || grouped) {   // the fused epilogues and the grouped forms exist on the in-place tensor-core path only
+        if (!direct_ok) return fail(ZNN_ERR_UNSUPPORTED, "fused epilogue / grouped product: operands not readable in place");
         path = 4;
     }
-    if (path == 0 && t_skinny && batch == 1 && tri == 0 && M >= 8 && M <= 64 && (M & 3) == 0 && N >= 512 && K >= 512 &&
+    if (path == 0 && t_skinny && batch == 1 && tri == 0 && !grouped && M >= 8 && M <= 64 && (M & 3) == 0 && N >= 512 && K >= 512 &&
         2.0 * M * N * (double)K >= 1.3e8 && gemm_tc_direct_eligible(B, ldb, 0, A, lda, 0, 1)) {
         // A few rows against a wide matrix (a 64-row batch against a weight matrix: decode, the sweep's skinny shapes):
         // as it stands the product would fill a quarter of one 256-row tile per column block and leave most SMs idle.
@@ -189,7 +190,7 @@ static int gemm_dispatch(int ta, int tb, int M, int N, int K, float alpha, const
         if (T) {
             const int ta2 = (tb == ZNN_NO_TRANS) ? ZNN_TRANS : ZNN_NO_TRANS, tb2 = (ta == ZNN_NO_TRANS) ? ZNN_TRANS : ZNN_NO_TRANS;
             int rc = gemm_tc_direct(ta2, tb2, N, M, K, alpha, B, ldb, 0, A, lda, 0, 0.0f, T, M, 0, 1, nullptr, 0, nullptr, nullptr,
-                                    0, nullptr, nullptr, nullptr);
+                                    0, nullptr, nullptr, nullptr, 0, 0);
             if (rc) return rc;
             transpose_finish_kernel<<<dim3(ceil_div(N, 32), ceil_div(M, 32)), dim3(32, 8), 0, stream()>>>(T, M, N, bias, beta, C, ldc);
             ZNN_LAUNCH_OK("transpose_finish_kernel");
@@ -213,7 +214,7 @@ static int gemm_dispatch(int ta, int tb, int M, int N, int K, float alpha, const
     t_last_path = path;
     if (path >= 2) {
         int rc = (path == 4) ? gemm_tc_direct(ta, tb, M, N, K, alpha, A, lda, stride_a, B, ldb, stride_b, beta, C, ldc,
-                                              stride_c, batch, bias, tri, ep_p, ep_d, ep_act, ep_out2, ep_res, ep_dpre)
+                                              stride_c, batch, bias, tri, ep_p, ep_d, ep_act, ep_out2, ep_res, ep_dpre, stride_bias, kcat)
                              : gemm_tc(ta, tb, M, N, K, alpha, A, lda, stride_a, B, ldb, stride_b, beta, C, ldc, stride_c,
                                        batch, path == 2 ? 1 : 2, bias);
         // Debug aid (environment ZNN_GEMM_CHECK=1): wait for every tensor-core product and name the first one
@@ -356,6 +357,22 @@ int znn_linear_bwd_ex(const float* X, const float* W, const float* dY, float* dX
     if (dbias && (rc = znn_add_bias_bwd(dY, nullptr, dbias, M, N))) return rc;
     if (dW && (rc = gemm_dispatch(ZNN_TRANS, ZNN_NO_TRANS, K, N, M, 1.0f, X, K, 0, dY, N, 0, 1.0f, dW, N, 0, 1))) return rc;
     return ZNN_OK;
+}
+
+int znn_sgemm_grouped(int trans_a, int trans_b, int M, int N, int K, float alpha, const float* A, int lda, long long stride_a,
+                      const float* B, int ldb, long long stride_b, float beta, float* C, int ldc, long long stride_c, int batch,
+                      const float* bias, long long stride_bias, int kcat)
+{
+    ZNN_REQUIRE(batch >= 1 && batch <= 64, "batch must be 1..64");
+    ZNN_REQUIRE(stride_a >= 0 && stride_b >= 0 && stride_c >= 0 && stride_bias >= 0, "negative stride");
+    ZNN_REQUIRE(kcat == 0 || kcat == 1, "kcat is 0 or 1");
+    if (!(2.0 * M * N * (double)K * batch >= 1.3e8 && M >= 64 && N >= 32 && K >= 32))
+        return fail(ZNN_ERR_UNSUPPORTED, "grouped product: too small for the tensor-core path");
+    if (kcat == 0 && batch > 1 && stride_c < (long long)M * ldc && stride_c != 0)
+        return fail(ZNN_ERR_INVALID, "grouped product: the slices of C overlap");
+    if (kcat == 0 && batch > 1 && stride_c == 0) return fail(ZNN_ERR_INVALID, "grouped product: every slice needs its own C");
+    return gemm_dispatch(trans_a, trans_b, M, N, K, alpha, A, lda, stride_a, B, ldb, stride_b, beta, C, ldc, stride_c, batch, bias, 0,
+                         nullptr, nullptr, 0, nullptr, nullptr, nullptr, stride_bias, kcat, true);
 }
 
 int znn_gemm_set_path(int path)

@@ -56,6 +56,12 @@ struct GemmTcParams {
     float* ep_out2;
     const float* ep_res;
     const float* ep_dpre;
+    // in-place kernel, grouped products: an operand shared by all slices (batch stride 0: its tensor map has one slice),
+    // a bias row per slice, and K-concatenation: kcat_segs > 1 makes the `kcat_segs` slices of A and B one product whose
+    // contraction runs through the slices one after the other (k-block kb lies in slice kb / kcat_kb), into one C.
+    int a_bcast, b_bcast;
+    long long stride_bias;
+    int kcat_segs, kcat_kb;
     // in-place kernel, triangular hint: the tiles of one slice that have work, dearest first (tile_m << 8 | tile_n);
     // units are then (table entry, slice) with the slice running fastest, so that the walk deals every CTA pair the
     // same mix of dear and cheap tiles.  tri_n = 0: no table (more than 64 tiles per slice), plain order.
@@ -954,23 +960,29 @@ gemm3x_direct_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_cons
                     const uint32_t ph = (it / S) & 1;
                     if (!ZNN_PROF_WAIT(mbar_wait_bounded(empty_bar(s), ph ^ 1, p.wait_limit))) { record_expiry(0, 0, u, it, cta_rank, pair); ok = false; break; }
                     const uint32_t st = smem_base + s * Cfg::kStageBytes;
-                    const int k0 = (d.kb_first + kb) * kBK;
+                    int kbl = d.kb_first + kb, slice = d.batch;
+                    if (p.kcat_segs > 1) {   // K-concatenated slices: which slice this k-block lies in
+                        slice = kbl / p.kcat_kb;
+                        kbl -= slice * p.kcat_kb;
+                    }
+                    const int k0 = kbl * kBK;
+                    const int sa = p.a_bcast ? 0 : slice, sbt = p.b_bcast ? 0 : slice;
                     mbar_arrive_expect_tx(full_bar(s), Cfg::kABytes + Cfg::kBBytes);
                     if (A_MN) {
 #pragma unroll
                         for (int j = 0; j < kTileM / 32; j++)
-                            tma_load_3d(st + j * 4096, &tm_a, full_bar(s), d.row0 + 32 * j, k0, d.batch);
+                            tma_load_3d(st + j * 4096, &tm_a, full_bar(s), d.row0 + 32 * j, k0, sa);
                     } else {
-                        tma_load_3d(st, &tm_a, full_bar(s), k0, d.row0, d.batch);
+                        tma_load_3d(st, &tm_a, full_bar(s), k0, d.row0, sa);
                     }
                     const uint32_t sb = st + 2 * Cfg::kABytes;
                     const int brow0 = d.col0 + cta_rank * Cfg::kBRows;
                     if (B_MN) {
 #pragma unroll
                         for (int j = 0; j < Cfg::kBRows / 32; j++)
-                            tma_load_3d(sb + j * 4096, &tm_b, full_bar(s), brow0 + 32 * j, k0, d.batch);
+                            tma_load_3d(sb + j * 4096, &tm_b, full_bar(s), brow0 + 32 * j, k0, sbt);
                     } else {
-                        tma_load_3d(sb, &tm_b, full_bar(s), k0, brow0, d.batch);
+                        tma_load_3d(sb, &tm_b, full_bar(s), k0, brow0, sbt);
                     }
                 }
             }
@@ -1138,15 +1150,16 @@ gemm3x_direct_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_cons
             }
             float* const out = to_partial ? p.partial + ((size_t)d.split * p.batch + d.batch) * (size_t)p.M * p.N
                                           : p.C + (size_t)d.batch * p.stride_c;
+            const float* const bias_s = bias ? bias + (size_t)d.batch * p.stride_bias : nullptr;
             const bool vec_ok = ((out_ld & 3) == 0) && ((reinterpret_cast<uintptr_t>(out) & 15) == 0) &&
-                                ((reinterpret_cast<uintptr_t>(bias) & 15) == 0);
+                                ((reinterpret_cast<uintptr_t>(bias_s) & 15) == 0);
             if (vec_ok)
-                epilogue_store_vec<CPT>(acc, stage, lane, d.row0 + q * 32, d.col0 + half * CPT, p.M, p.N, out, out_ld, alpha, beta, bias,
+                epilogue_store_vec<CPT>(acc, stage, lane, d.row0 + q * 32, d.col0 + half * CPT, p.M, p.N, out, out_ld, alpha, beta, bias_s,
                                         warp + pair, p.ep_p ? p.ep_p + (size_t)d.batch * p.stride_c : nullptr,
                                         p.ep_d ? p.ep_d + (size_t)d.batch * p.M : nullptr,
                                         EpiExt{p.ep_act, p.ep_out2, p.ep_res, p.ep_dpre});
             else
-                epilogue_store_rows<CPT>(acc, stage, lane, d.row0 + q * 32, d.col0 + half * CPT, p.M, p.N, out, out_ld, alpha, beta, bias);
+                epilogue_store_rows<CPT>(acc, stage, lane, d.row0 + q * 32, d.col0 + half * CPT, p.M, p.N, out, out_ld, alpha, beta, bias_s);
         }
         if (!got && lane == 0) atomicOr(p.status, ZNN_DEV_EPI_WAIT_EXPIRED);
         ZNN_PROF_END(3, pair == 0 && cta_rank == 0 && warp == kEpiWarp0 && lane == 0)
@@ -1232,8 +1245,9 @@ __global__ void tail_reduce_kernel(const GemmTcParams p)
     constexpr int kElems = 2 * kTileM * BN;
     const float4* base = reinterpret_cast<const float4*>(p.tail_partial + (size_t)j * p.tail_slices * (size_t)kElems);
     float* const Cb = p.C + (size_t)d.batch * p.stride_c;
+    const float* const bias_s = p.bias ? p.bias + (size_t)d.batch * p.stride_bias : nullptr;
     const bool vec = ((p.ldc & 3) == 0) && ((reinterpret_cast<uintptr_t>(Cb) & 15) == 0) &&
-                     ((reinterpret_cast<uintptr_t>(p.bias) & 15) == 0);
+                     ((reinterpret_cast<uintptr_t>(bias_s) & 15) == 0);
     const int e4 = blockIdx.x * blockDim.x + threadIdx.x;     // one float4 of the tile per thread
     if (e4 >= kElems / 4) return;
     const int r = e4 / (BN / 4), c = (e4 - r * (BN / 4)) * 4;
@@ -1250,8 +1264,8 @@ __global__ void tail_reduce_kernel(const GemmTcParams p)
     float o[4] = {p.alpha * sum.x, p.alpha * sum.y, p.alpha * sum.z, p.alpha * sum.w};
     float* dst = Cb + (size_t)row * p.ldc + col;
     if (vec && col + 3 < p.N) {
-        if (p.bias) {
-            const float4 b4 = *reinterpret_cast<const float4*>(p.bias + col);
+        if (bias_s) {
+            const float4 b4 = *reinterpret_cast<const float4*>(bias_s + col);
             o[0] += b4.x; o[1] += b4.y; o[2] += b4.z; o[3] += b4.w;
         }
         if (p.ep_act != 0 || p.ep_res) {
@@ -1269,7 +1283,7 @@ __global__ void tail_reduce_kernel(const GemmTcParams p)
         for (int e = 0; e < 4; e++) {
             if (col + e >= p.N) break;
             float t = o[e];
-            if (p.bias) t += p.bias[col + e];
+            if (bias_s) t += bias_s[col + e];
             if (p.beta != 0.0f) t += p.beta * dst[e];
             dst[e] = t;
         }
@@ -1607,6 +1621,7 @@ int gemm_tc(int ta, int tb, int M, int N, int K, float alpha, const float* A, lo
     p.ep_p = nullptr;
     p.ep_d = nullptr;
     p.ep_act = 0; p.ep_out2 = nullptr; p.ep_res = nullptr; p.ep_dpre = nullptr;
+    p.a_bcast = 0; p.b_bcast = 0; p.stride_bias = 0; p.kcat_segs = 0; p.kcat_kb = 0;
     p.conv_mode = 0;
     p.bias = bias;
     p.tiles_m = tiles_m;
@@ -1734,8 +1749,17 @@ bool gemm_tc_direct_eligible(const float* A, long long lda, long long stride_a, 
 int gemm_tc_direct(int ta, int tb, int M, int N, int K, float alpha, const float* A, long long lda, long long stride_a,
                    const float* B, long long ldb, long long stride_b, float beta, float* C, long long ldc,
                    long long stride_c, int batch, const float* bias, int tri, const float* ep_p, const float* ep_d,
-                   int ep_act, float* ep_out2, const float* ep_res, const float* ep_dpre)
+                   int ep_act, float* ep_out2, const float* ep_res, const float* ep_dpre, long long stride_bias, int kcat)
 {
+    // kcat != 0: the `batch` slices are one product, concatenated along K (C is a single matrix); K a multiple of 32
+    const int segs = kcat ? batch : 0;
+    const int seg_kb = (K + kBK - 1) / kBK;
+    if (kcat) {
+        if ((K % kBK) != 0 || bias || tri != 0 || ep_p || ep_act != 0 || ep_res)
+            return fail(ZNN_ERR_UNSUPPORTED, "K-concatenated product: K must be a multiple of 32, no epilogue forms");
+        K = K * batch;      // the plan, the k-block walk and the flop count see the whole contraction
+        batch = 1;
+    }
     int* status = device_status_word();
     if (!status) return fail(ZNN_ERR_CUDA, "no device state (call znn_init first)");
     const bool has_ex = ep_act != 0 || ep_res != nullptr;
@@ -1755,7 +1779,8 @@ int gemm_tc_direct(int ta, int tb, int M, int N, int K, float alpha, const float
     }
     const bool tail_ok = t_tail_split && t_persistent && tri == 0 && !ep_p;
     TcPlan pl = make_plan(M, N, K, batch, 2, tail_ok);
-    if ((tri != 0 || ep_p || has_ex) && pl.splits > 1) {   // the triangular k-ranges are per tile; no split-K on top of them
+    // (the split-K reduce kernel knows neither the epilogue forms nor a bias row per slice)
+    if ((tri != 0 || ep_p || has_ex || (bias && stride_bias != 0 && batch > 1)) && pl.splits > 1) {   // the triangular k-ranges are per tile; no split-K on top of them
         pl.splits = 1;
         pl.kbps = ((pl.k_blocks + pl.chunk - 1) / pl.chunk) * pl.chunk;
     }
@@ -1780,8 +1805,12 @@ int gemm_tc_direct(int ta, int tb, int M, int N, int K, float alpha, const float
     const bool a_mn = (ta == ZNN_TRANS), b_mn = (tb == ZNN_NO_TRANS);
     CUtensorMap ma, mb;
     int rc;
-    if ((rc = make_operand_map(&ma, A, a_mn, M, K, lda, stride_a, batch, kTileM))) return rc;
-    if ((rc = make_operand_map(&mb, B, b_mn, N, K, ldb, stride_b, batch, pl.bn / 2))) return rc;
+    // an operand with batch stride 0 is one matrix shared by all slices: its map has one slice, always read at 0
+    const int map_slices = kcat ? segs : batch;
+    const int map_k = kcat ? K / segs : K;
+    const bool a_bc = map_slices > 1 && stride_a == 0, b_bc = map_slices > 1 && stride_b == 0;
+    if ((rc = make_operand_map(&ma, A, a_mn, M, map_k, lda, stride_a, a_bc ? 1 : map_slices, kTileM))) return rc;
+    if ((rc = make_operand_map(&mb, B, b_mn, N, map_k, ldb, stride_b, b_bc ? 1 : map_slices, pl.bn / 2))) return rc;
     GemmTcParams p;
     p.M = M; p.N = N; p.k_blocks = pl.k_blocks; p.k_real = K; p.chunk_kblocks = pl.chunk;
     p.kblocks_per_split = pl.kbps;
@@ -1799,6 +1828,9 @@ int gemm_tc_direct(int ta, int tb, int M, int N, int K, float alpha, const float
     p.ep_p = ep_p;
     p.ep_d = ep_d;
     p.ep_act = ep_act; p.ep_out2 = ep_out2; p.ep_res = ep_res; p.ep_dpre = ep_dpre;
+    p.a_bcast = a_bc ? 1 : 0; p.b_bcast = b_bc ? 1 : 0;
+    p.stride_bias = stride_bias;
+    p.kcat_segs = segs; p.kcat_kb = seg_kb;
     // The hint works through a table of the slice's tiles (which have work, and which k-blocks); a slice of more than
     // 64 tiles is computed in full instead (the hint never changes values that may be read).
     p.tri_n = 0;

@@ -148,6 +148,17 @@ def sgemm_batched(ta, tb, M, N, K, alpha, A, lda, sa, B, ldb, sb, beta, Cm, ldc,
     return Cm
 
 
+def sgemm_grouped(ta, tb, M, N, K, alpha, A, lda, sa, B, ldb, sb, beta, Cm, ldc, sc, batch, bias=None, sbias=0, kcat=0):
+    """znn_sgemm_grouped on host arrays (flat float32 buffers holding the slices at the given strides)."""
+    _ensure()
+    dA, dB, dC, db = _up(A), _up(B), _up(Cm), _up(bias)
+    lib().call("znn_sgemm_grouped", ta, tb, M, N, K, alpha, dA.ptr, lda, sa, dB.ptr, ldb, sb, beta, dC.ptr, ldc, sc, batch,
+               _ptr(db), sbias, kcat)
+    check_device_status()
+    dC.into(Cm)
+    return Cm
+
+
 TRI_NONE, TRI_C_LOWER, TRI_A_LOWER, TRI_A_UPPER, TRI_B_LOWER = 0, 1, 2, 3, 4
 
 
