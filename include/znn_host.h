@@ -82,7 +82,9 @@ int znn_model_get_velocities(znn_model* m, float* host_slab);
  * of 4; needs fused_softmax; 0 = the separate products and softmax below), "fused_epilogue" (bit mask, process-wide, default 2: 1 = the residual add
  * after an output projection, 2 = ReLU after a Linear and its derivative in backward, 4 = GELU forward, 8 = GELU derivative
  * backward run in the epilogue of the neighbouring GEMM, znn_linear_fwd_ex / znn_linear_bwd_ex; the tape keeps the separate
- * ops; only the ReLU form is on by default: the others measured slower than the separate kernels on the GPT step), "fused_qkt" (1/0, process-wide: attention scores as one
+ * ops; only the ReLU form is on by default: the others measured slower than the separate kernels on the GPT step), "group_linear" (1/0, process-wide, default 1: the three attention projections, which share
+ * their input, run as grouped launches, znn_sgemm_grouped: one forward, one for the three weight gradients, one K-concatenated
+ * product for the sum of the three data gradients), "fused_qkt" (1/0, process-wide: attention scores as one
  * Q.K^T op instead of a transposed copy of K and a product), "alias_reshape_grad" (1/0, process-wide: Reshape views
  * share the gradient buffer of their input instead of adding into it in backward), "lazy_zero_grad" (1/0, process-wide:
  * gradient buffers of intermediates are zero-filled only when first added to; GEMM arms overwrite them with beta = 0), "dp_bucket_floats",

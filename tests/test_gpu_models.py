@@ -563,3 +563,36 @@ def test_cnn_fused_relu_forms_are_bit_identical(Model, kind, batch):
     for k in out[0][1]:
         np.testing.assert_array_equal(out[0][1][k], out[1][1][k])
     assert out[0][2] < out[1][2]        # (products that are split over K keep their separate Relu: the same kernels)
+
+
+def test_grouped_attention_projections_match_separate_launches(Model):
+    """Option group_linear (default on): the q, k, v projections of an attention layer share their input and run as one
+    grouped forward launch, one grouped weight-gradient launch and one K-concatenated data-gradient product
+    (znn_sgemm_grouped).  Loss and every gradient must equal the three separate Linear layers' to fp32 rounding."""
+    from znn_b200 import _lib
+    L = _lib.lib()
+    cfg = {"vocab_size": 128, "block_size": 768, "n_embd": 256, "n_head": 4, "n_layer": 2}
+    dims = (128, 768, 256, 4, 2)
+    r = np.random.default_rng(28)
+    P0 = models.init_params("gpt", cfg, seed=29)
+    x = r.integers(0, 128, (2, 768)).astype(np.float32)
+    t = r.integers(0, 128, (2, 768)).astype(np.int32)
+    res = []
+    try:
+        for grp in (1, 0):
+            m = Model("gpt", dims, arena_bytes=2 << 30)
+            m.set_params(P0)
+            m.set_option("group_linear", grp)
+            m.set_option("lr", 0.0)
+            loss, launches = _launches_of(L, lambda: m.train_step(x, t, seq=768))
+            res.append((loss, m.get_grads(), launches))
+            m.close()
+    finally:
+        m2 = Model("mlp", (784, 128, 64, 10), arena_bytes=64 << 20)
+        m2.set_option("group_linear", 1)
+        m2.close()
+    assert res[0][2] <= res[1][2] - 2 * 6          # per layer: 3 -> 1 forward, 3 -> 1 dW, 3 -> 1 dX launches
+    assert abs(res[0][0] - res[1][0]) <= 1e-6 * abs(res[1][0])
+    floor = 3e-2 * grad_floor(res[1][1])
+    for k in res[0][1]:
+        relclose(res[0][1][k], res[1][1][k], 1e-5, k, floor)

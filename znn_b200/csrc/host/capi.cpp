@@ -451,7 +451,7 @@ int znn_model_set_option(znn_model* m, const char* key, double value)
     const std::string k(key ? key : "");
     // every option that changes a baked-in kernel argument or the launch sequence invalidates a captured step
     if (k == "lr" || k == "momentum" || k.rfind("fused_", 0) == 0 || k == "causal_skip" || k == "alias_reshape_grad" ||
-        k == "lazy_zero_grad" || k == "fused_attention")
+        k == "lazy_zero_grad" || k == "fused_attention" || k == "group_linear")
         drop_graph(m);
     if (k == "lr") m->opt.lr = m->adam.lr = (float)value;
     else if (k == "optimizer") {
@@ -472,6 +472,7 @@ int znn_model_set_option(znn_model* m, const char* key, double value)
     else if (k == "fused_qkt") set_fused_qkt(value != 0.0);
     else if (k == "fused_attention") set_fused_attention(value != 0.0);
     else if (k == "fused_epilogue") set_fused_epilogue((int)value);
+    else if (k == "group_linear") set_group_linear(value != 0.0);
     else if (k == "fused_softmax_bwd") set_fused_softmax_bwd(value != 0.0);
     else if (k == "alias_reshape_grad") set_alias_reshape_grad(value != 0.0);
     else if (k == "lazy_zero_grad") set_lazy_zero_grad(value != 0.0);

@@ -126,6 +126,10 @@ static int g_fused_epilogue = 2;
 void set_fused_epilogue(int mask) { g_fused_epilogue = mask; }
 int fused_epilogue() { return g_fused_epilogue; }
 
+static bool g_group_linear = true;
+void set_group_linear(bool on) { g_group_linear = on; }
+bool group_linear() { return g_group_linear; }
+
 static bool g_fused_softmax_bwd = true;
 void set_fused_softmax_bwd(bool on) { g_fused_softmax_bwd = on; }
 bool fused_softmax_bwd() { return g_fused_softmax_bwd; }
@@ -155,7 +159,10 @@ Op* Graph::new_op(OpType type, std::initializer_list<Tensor*> inputs, Tensor* ou
     o->inputs.assign(inputs.begin(), inputs.end());
     o->outputs.push_back(out);
     out->creator = o;
-    for (Tensor* in : o->inputs) in->consumers++;
+    for (Tensor* in : o->inputs) {
+        in->consumers++;
+        in->last_consumer = o;
+    }
     ops_.push_back(o);
     return o;
 }
@@ -400,6 +407,47 @@ Tensor* Graph::linear(Tensor* X, Tensor* W, Tensor* bias)
     Tensor* Y = new_tensor(Shape{X->shape.dims[0], W->shape.dims[1]}, any_grad({X, W, bias}), false);
     new_op(OpType::LinearBias, {X, W, bias}, Y)->forward();
     return Y;
+}
+
+// distance in floats between consecutive pointers when it is the same, positive and a multiple of 4; else 0
+static long long uniform_stride(int n, const float* const* p)
+{
+    if (n < 2) return 0;
+    const long long d = p[1] - p[0];
+    if (d <= 0 || (d & 3)) return 0;
+    for (int i = 2; i < n; i++)
+        if (p[i] - p[i - 1] != d) return 0;
+    return d;
+}
+
+void Graph::linearGroup(Tensor* X, int n, Tensor* const* W, Tensor* const* bias, Tensor** out)
+{
+    if (n < 1 || n > 8) throw Error(ZNN_ERR_INVALID, "linearGroup: 1..8 members");
+    for (int i = 0; i < n; i++)
+        if (X->shape.len < 2 || W[i]->shape.len < 2 || X->shape.dims[1] != W[i]->shape.dims[0] ||
+            bias[i]->numel() != W[i]->shape.dims[1] || W[i]->shape.dims[1] != W[0]->shape.dims[1])
+            throw Error(ZNN_ERR_INVALID, "linearGroup: need X [M,K] and n times W [K,N], bias [N]");
+    const int M = (int)X->shape.dims[0], K = (int)X->shape.dims[1], N = (int)W[0]->shape.dims[1];
+    std::vector<Op*> ops;
+    for (int i = 0; i < n; i++) {
+        out[i] = new_tensor(Shape{X->shape.dims[0], W[i]->shape.dims[1]}, any_grad({X, W[i], bias[i]}), false);
+        ops.push_back(new_op(OpType::LinearBias, {X, W[i], bias[i]}, out[i]));
+    }
+    ops.back()->group = ops;
+    int rc = ZNN_ERR_UNSUPPORTED;
+    if (g_group_linear && n > 1) {
+        const float* w[8]; const float* b[8]; const float* y[8];
+        for (int i = 0; i < n; i++) { w[i] = W[i]->data; b[i] = bias[i]->data; y[i] = out[i]->data; }
+        const long long sw = uniform_stride(n, w), sb = uniform_stride(n, b), sy = uniform_stride(n, y);
+        if (sw && sb && sy)
+            rc = znn_sgemm_grouped(ZNN_NO_TRANS, ZNN_NO_TRANS, M, N, K, 1.0f, X->data, K, 0, W[0]->data, N, sw, 0.0f, out[0]->data, N,
+                                   sy, n, bias[0]->data, sb, 0);
+    }
+    if (rc == ZNN_ERR_UNSUPPORTED) {
+        for (Op* o : ops) o->forward();
+    } else {
+        check(rc, "grouped Linear forward");
+    }
 }
 
 Tensor* Graph::linearAct(Tensor* X, Tensor* W, Tensor* bias, OpType act)
@@ -755,6 +803,48 @@ void Op::backward()
         Tensor* W = inputs[1];
         Tensor* b = inputs[2];
         const int M = (int)A->shape.dims[0], K = (int)A->shape.dims[1], N = (int)W->shape.dims[1];
+        if (g_group_linear && group.size() > 1) {
+            // Last member of a group on one input (the tape runs it first): every member's output gradient is complete
+            // by now, so all weight gradients run as one grouped launch and the data gradients as one product whose
+            // contraction runs through the members; the other members' own backward is then skipped.
+            const int n = (int)group.size();
+            const float* w[8]; const float* wg[8]; const float* yg[8];
+            bool ok = n <= 8 && A->requires_grad;
+            // "complete" holds when one op reads all the outputs and nothing else does: it ran before any member
+            // (with separate consumers the tape may still owe a member's output gradient when the last member runs)
+            for (int i = 0; i < n && ok; i++)
+                ok = group[i]->outputs[0]->consumers == 1 && group[i]->outputs[0]->last_consumer == group[0]->outputs[0]->last_consumer;
+            for (int i = 0; i < n && ok; i++) {
+                Op* o = group[i];
+                ensure_grad(o->outputs[0]);
+                ok = o->inputs[1]->requires_grad && o->inputs[2]->requires_grad && !grad_is_fresh(o->inputs[1]);
+                w[i] = o->inputs[1]->data; wg[i] = o->inputs[1]->grad; yg[i] = o->outputs[0]->grad;
+            }
+            const long long sw = ok ? uniform_stride(n, w) : 0, swg = ok ? uniform_stride(n, wg) : 0, syg = ok ? uniform_stride(n, yg) : 0;
+            if (ok && sw && swg && syg) {
+                const bool fresh = grad_is_fresh(A);
+                int rc = znn_sgemm_grouped(ZNN_NO_TRANS, ZNN_TRANS, M, K, N, 1.0f, yg[0], N, syg, w[0], N, sw, fresh ? 0.0f : 1.0f,
+                                           A->grad, K, 0, n, nullptr, 0, 1);
+                if (rc == ZNN_OK) {
+                    mark_grad_written(A);
+                    rc = znn_sgemm_grouped(ZNN_TRANS, ZNN_NO_TRANS, K, N, M, 1.0f, A->data, K, 0, yg[0], N, syg, 1.0f,
+                                           const_cast<float*>(wg[0]), N, swg, n, nullptr, 0, 0);
+                    for (int i = 0; i < n; i++) {
+                        Op* o = group[i];
+                        ensure_grad(o->inputs[2]);
+                        check(znn_add_bias_bwd(yg[i], nullptr, o->inputs[2]->grad, M, N), "Linear backward dbias");
+                        if (rc == ZNN_ERR_UNSUPPORTED)
+                            check(znn_sgemm(ZNN_ROW_MAJOR, ZNN_TRANS, ZNN_NO_TRANS, K, N, M, 1.0f, A->data, K, yg[i], N, 1.0f,
+                                            o->inputs[1]->grad, N),
+                                  "Linear backward dW");
+                        if (o != this) o->skip_backward = true;
+                    }
+                    if (rc != ZNN_ERR_UNSUPPORTED) check(rc, "grouped Linear backward dW");
+                    break;
+                }
+                if (rc != ZNN_ERR_UNSUPPORTED) check(rc, "grouped Linear backward dX");
+            }
+        }
         // znn_linear_bwd in pieces, so that a fresh dX is overwritten (beta = 0) instead of zero-filled and added to
         if (b->requires_grad) {
             ensure_grad(b);

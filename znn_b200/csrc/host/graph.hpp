@@ -55,6 +55,7 @@ struct Tensor {
     bool grad_valid = true;
     Tensor* grad_owner = nullptr;
     int consumers = 0;   // ops that read this tensor (counted while the tape is built)
+    Op* last_consumer = nullptr;   // the latest of them
     size_t numel() const { return shape.numel(); }
 };
 
@@ -82,6 +83,9 @@ bool lazy_zero_grad();
 // element in the epilogue against bandwidth-bound stand-alone kernels).  ReLU is free (one max per element).
 void set_fused_epilogue(int mask);
 int fused_epilogue();
+// Linear layers that share their input run as grouped launches (Graph::linearGroup); default on.
+void set_group_linear(bool on);
+bool group_linear();
 
 // hot-path subset of src/autodiff.zig:14-40, plus two additions
 enum class OpType {
@@ -107,6 +111,7 @@ struct Op {
     int tri_role = 0;           // BatchMatMul next to a causal softmax: 1 = C are the scores, 2 = A are the probabilities
     float* scratch = nullptr;   // BatchMatMul role 2: one float per probability row (the D vector of the fused backward)
     bool skip_backward = false; // CausalSoftmax: its input gradient was already produced by the consumer's fused backward
+    std::vector<Op*> group;     // LinearBias, last of a group on one input (Graph::linearGroup): all members, in creation order
     float* probs = nullptr;     // SoftmaxCrossEntropy: device M x N
     int32_t* targets = nullptr; // SoftmaxCrossEntropy: device int32 labels (device bytes when targets_u8)
     bool targets_u8 = false;
@@ -188,6 +193,10 @@ public:
     // relu(conv2d(A, W, bias)): the tape gets the Conv2D and the Relu op, one kernel stores max(0, .) (the pre-activation is
     // not kept: no backward arm reads it)
     Tensor* conv2dRelu(Tensor* A, Tensor* W, Tensor* bias, int pad);
+    // n Linear layers of the same shape on one input (the q, k, v projections): n LinearBias ops on the tape; when their
+    // parameters and outputs lie at uniform strides the forward is one grouped launch, and the backward of the last one
+    // runs all members' weight gradients as one grouped launch and their data gradients as one K-concatenated product
+    void linearGroup(Tensor* X, int n, Tensor* const* W, Tensor* const* bias, Tensor** out);
 
     // `after_op(op)` is called after a tape op has run its
     // backward arm; data-parallel training uses it to start gradient all-reduces.

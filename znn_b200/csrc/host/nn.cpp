@@ -173,9 +173,18 @@ Tensor* CausalSelfAttention::forward(Graph& g, Tensor* x, Tensor* residual) cons
     const size_t B = x->shape.dims[0], T = x->shape.dims[1], C = x->shape.dims[2];
     const size_t nh = n_head, hs = C / nh;
     Tensor* x_2d = g.reshape(x, Shape{B * T, C});
-    Tensor* q_2d = q_attn.forward(g, x_2d);
-    Tensor* k_2d = k_attn.forward(g, x_2d);
-    Tensor* v_2d = v_attn.forward(g, x_2d);
+    Tensor *q_2d, *k_2d, *v_2d;
+    if (g_fused_linear && group_linear()) {   // the three projections share their input: grouped launches
+        Tensor* const W3[3] = {q_attn.weight, k_attn.weight, v_attn.weight};
+        Tensor* const b3[3] = {q_attn.bias, k_attn.bias, v_attn.bias};
+        Tensor* o3[3];
+        g.linearGroup(x_2d, 3, W3, b3, o3);
+        q_2d = o3[0]; k_2d = o3[1]; v_2d = o3[2];
+    } else {
+        q_2d = q_attn.forward(g, x_2d);
+        k_2d = k_attn.forward(g, x_2d);
+        v_2d = v_attn.forward(g, x_2d);
+    }
     // (short sequences keep the separate products: a 256-row unit of the fused kernel is mostly empty below T = 128)
     if (fused_softmax && g_fused_attention && (hs == 32 || hs == 64) && T % 4 == 0 && T >= 128) {
         // one op on the projections where they lie: the heads are read and written through strides
