@@ -247,6 +247,85 @@ __global__ void colsum_stage1_kernel(const float* __restrict__ dC, float* __rest
     if (threadIdx.x == 0 && threadIdx.y == 0) counters[blockIdx.x] = 0u;
 }
 
+// The same with 16-byte accesses: a block covers 128 columns (each lane four), its eight warps walk the chunk's rows
+// eight apart (512 contiguous bytes per warp and row instead of 128).  N a multiple of 4, 16-byte aligned pointers.
+template <bool PassThrough>
+__global__ void __launch_bounds__(256)
+colsum_vec_kernel(const float* __restrict__ dC, float* __restrict__ dA, float* __restrict__ partial, int M, int N,
+                  int rows_per_chunk, unsigned* __restrict__ counters, float* __restrict__ out)
+{
+    __shared__ float4 sh[8][33];
+    __shared__ bool last;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int n = blockIdx.x * 128 + 4 * lane;
+    const int m0 = blockIdx.y * rows_per_chunk;
+    const int m1 = min(M, m0 + rows_per_chunk);
+    float4 s = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+    if (n < N) {
+        int m = m0 + warp;
+        for (; m + 24 < m1; m += 32) {   // four rows in flight per lane
+            float4 g[4];
+#pragma unroll
+            for (int u = 0; u < 4; u++) g[u] = *reinterpret_cast<const float4*>(dC + (size_t)(m + 8 * u) * N + n);
+#pragma unroll
+            for (int u = 0; u < 4; u++) {
+                if (PassThrough) {
+                    float4* a = reinterpret_cast<float4*>(dA + (size_t)(m + 8 * u) * N + n);
+                    float4 o = *a;
+                    o.x += g[u].x; o.y += g[u].y; o.z += g[u].z; o.w += g[u].w;
+                    *a = o;
+                }
+                s.x += g[u].x; s.y += g[u].y; s.z += g[u].z; s.w += g[u].w;
+            }
+        }
+        for (; m < m1; m += 8) {
+            const float4 g = *reinterpret_cast<const float4*>(dC + (size_t)m * N + n);
+            if (PassThrough) {
+                float4* a = reinterpret_cast<float4*>(dA + (size_t)m * N + n);
+                float4 o = *a;
+                o.x += g.x; o.y += g.y; o.z += g.z; o.w += g.w;
+                *a = o;
+            }
+            s.x += g.x; s.y += g.y; s.z += g.z; s.w += g.w;
+        }
+    }
+    sh[warp][lane] = s;
+    __syncthreads();
+    if (warp == 0 && n < N) {
+        float4 t = sh[0][lane];
+#pragma unroll
+        for (int y = 1; y < 8; y++) { const float4 v = sh[y][lane]; t.x += v.x; t.y += v.y; t.z += v.z; t.w += v.w; }
+        *reinterpret_cast<float4*>(partial + (size_t)blockIdx.y * N + n) = t;
+    }
+    if (!counters) return;   // the caller runs the second stage as its own kernel
+    // the chunk that finishes last for these columns adds all chunk partials in chunk order and resets the counter
+    __threadfence();
+    __syncthreads();
+    if (threadIdx.x == 0) last = (atomicAdd(&counters[blockIdx.x], 1u) == gridDim.y - 1);
+    __syncthreads();
+    if (!last) return;
+    __threadfence();
+    float4 t = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+    if (n < N)
+        for (int c = warp; c < (int)gridDim.y; c += 8) {
+            const float4 v = __ldcg(reinterpret_cast<const float4*>(partial + (size_t)c * N + n));
+            t.x += v.x; t.y += v.y; t.z += v.z; t.w += v.w;
+        }
+    __syncthreads();
+    sh[warp][lane] = t;
+    __syncthreads();
+    if (warp == 0 && n < N) {
+        float4 u = sh[0][lane];
+#pragma unroll
+        for (int y = 1; y < 8; y++) { const float4 v = sh[y][lane]; u.x += v.x; u.y += v.y; u.z += v.z; u.w += v.w; }
+        float4* o = reinterpret_cast<float4*>(out + n);
+        float4 w = *o;
+        w.x += u.x; w.y += u.y; w.z += u.z; w.w += u.w;
+        *o = w;
+    }
+    if (threadIdx.x == 0) counters[blockIdx.x] = 0u;
+}
+
 // block = 32 columns x 8 lanes; lane y adds chunks y, y+8, ... in order, then the 8 lane sums are added in order
 __global__ void colsum_stage2_kernel(const float* __restrict__ partial, float* __restrict__ out, int chunks, int N)
 {
@@ -1331,6 +1410,19 @@ int znn_add_bias_bwd(const float* dC, float* dA, float* dbias, int M, int N)
     colsum_plan(M, chunks, rpc);
     float* partial = (float*)workspace((size_t)chunks * N * sizeof(float));
     if (!partial) return fail(ZNN_ERR_NOMEM, "scratch for bias gradient");
+    const bool vec = (N & 3) == 0 && ((((uintptr_t)dC | (uintptr_t)dA | (uintptr_t)dbias | (uintptr_t)partial)) & 15) == 0;
+    if (vec) {
+        dim3 vgrid(ceil_div(N, 128), chunks);
+        unsigned* vcounters = (int)vgrid.x <= kScratchCounters ? scratch_counters() : nullptr;
+        if (dA) colsum_vec_kernel<true><<<vgrid, 256, 0, stream()>>>(dC, dA, partial, M, N, rpc, vcounters, dbias);
+        else colsum_vec_kernel<false><<<vgrid, 256, 0, stream()>>>(dC, nullptr, partial, M, N, rpc, vcounters, dbias);
+        ZNN_LAUNCH_OK("colsum_vec_kernel");
+        if (!vcounters) {
+            colsum_stage2_kernel<<<ceil_div(N, 32), dim3(32, 8), 0, stream()>>>(partial, dbias, chunks, N);
+            ZNN_LAUNCH_OK("colsum_stage2_kernel");
+        }
+        return ZNN_OK;
+    }
     dim3 grid(ceil_div(N, 32), chunks), block(32, 8);
     // one launch when the block counters are at hand (the last chunk of a column block finishes its sum), else two
     unsigned* counters = (int)grid.x <= kScratchCounters ? scratch_counters() : nullptr;
