@@ -45,6 +45,12 @@ int znn_gemm_profile_read(double* kernel_ms, long long* launches, double* flops)
  * [16] converter proxy fence, [17] fence + arrival; transform: [18] score load, [19] W store + hand-off, [20] accumulator drain,
  * [21] load-to-hand-off of one block.  32 values. */
 int znn_debug_attn_profile(long long* out32);
+/* Fused attention, per host thread: 0 (default) = converter warps inside the kernel split every landed tile into its TF32
+ * head and fp32 remainder; 1 = the remainder (lo) planes of the operands that pass through shared memory are computed once
+ * by a pre-pass and loaded by TMA next to the values, straight to the MMA issuer's barrier (no converter role, no proxy
+ * fence).  Bit-identical results; measured no faster (the kernels wait for the tiles' arrival either way) and the pre-pass
+ * costs 16-32 us per call, hence not the default. */
+int znn_debug_set_attn_planes(int enable);
 
 /* Conv2D path of the calling host thread: 0 (default) = layers with Ci*KH*KW >= 64 taps, at most 64 output channels and at
  * least 4096 output pixels run as implicit-im2col GEMMs on the tensor cores; 1 = never (direct kernels and the explicit

@@ -106,3 +106,25 @@ def test_fused_attention_rejects_what_it_cannot_run(ops):
     with pytest.raises(ZnnError) as ei:
         lib().call("znn_attn_fwd", buf.ptr, buf.ptr, buf.ptr, buf.ptr, buf.ptr, 1, 1, 66, 64, 64, 66 * 64, 66 * 64, 0.1)
     assert ei.value.code == -6
+
+
+@pytest.mark.parametrize("layout", ["bhtd", "bthd"])
+def test_precomputed_remainder_planes_equal_in_kernel_conversion(ops, layout):
+    """Default form: converter warps split every landed tile inside the kernel.  The other form
+    (znn_debug_set_attn_planes(1)) makes the remainder (lo) planes of the shared-memory operands once in a pre-pass and
+    loads them by TMA.  Same arithmetic on the same values: every output bit-identical."""
+    from znn_b200._lib import lib
+    r = np.random.default_rng(77)
+    B, nh, T, hs = 2, 3, 712, 64
+    shape = (B, nh, T, hs) if layout == "bhtd" else (B, T, nh, hs)
+    Q, K, V, dO = (r.standard_normal(shape, np.float32) for _ in range(4))
+    res = []
+    try:
+        for planes in (1, 0):
+            lib().call("znn_debug_set_attn_planes", planes)
+            O, LSE = ops.attn_fwd(Q, K, V, 0.125, layout)
+            res.append((O, LSE) + tuple(ops.attn_bwd(Q, K, V, O, dO, LSE, 0.125, layout)))
+    finally:
+        lib().call("znn_debug_set_attn_planes", 0)
+    for a, b in zip(res[0], res[1]):
+        np.testing.assert_array_equal(a, b)

@@ -32,6 +32,7 @@
 // elements above the diagonal are masked by index (the reference adds -1e9, which makes exp exactly 0).
 // No TMA multicast.  Every mbarrier wait is bounded (status word + early exit, as in the GEMM kernels).
 #include "tc_ptx.cuh"
+#include "../../include/znn_debug.h"
 
 #include <math.h>
 #include <math_constants.h>
@@ -51,6 +52,8 @@ struct AttnParams {
     float* lse;                   // [nslices, T] base-2 log-sum-exp of the scaled scores: written by the forward, read by the others
     const float* dvec;            // [nslices, T] D = rowsum(dO o O) (dQ and dK)
     int accumulate;               // backward: 1 = add into out (the reference's +=), 0 = store
+    int planes;                   // 1: the remainder (lo) parts of the shared-memory operands come precomputed through their own
+                                  // tensor maps: TMA fills both halves of a stage and signals the MMA issuer's barrier directly
     int* status;
     unsigned long long wait_limit;
 };
@@ -154,7 +157,9 @@ __device__ __forceinline__ void split_hi_lo(float x, uint32_t& hi, uint32_t& lo)
 template <int MODE>
 __global__ void __launch_bounds__(kAttThreads, 1)
 attn_kernel(const __grid_constant__ CUtensorMap mx2, const __grid_constant__ CUtensorMap my1,
-            const __grid_constant__ CUtensorMap my2, const __grid_constant__ CUtensorMap mz, const AttnParams p)
+            const __grid_constant__ CUtensorMap my2, const __grid_constant__ CUtensorMap mz,
+            const __grid_constant__ CUtensorMap mx2l, const __grid_constant__ CUtensorMap my1l,
+            const __grid_constant__ CUtensorMap my2l, const __grid_constant__ CUtensorMap mzl, const AttnParams p)
 {
     using Cfg = AttnCfg<MODE>;
     constexpr int NX = Cfg::NX, NYS = Cfg::NYS, NZS = Cfg::NZS, NWB = Cfg::NWB;
@@ -214,17 +219,17 @@ attn_kernel(const __grid_constant__ CUtensorMap mx2, const __grid_constant__ CUt
     if (threadIdx.x == 0) {
         static_assert(8 * (4 + 3 * NYS + 3 * NZS + 6) + 8 <= 512, "barrier block overflows");
         mbar_init(x_full, 1);
-        mbar_init(x_conv, kAttConvWarps * 2);
+        mbar_init(x_conv, p.planes ? 1 : kAttConvWarps * 2);   // planes: the leader's producer arrives, TMA brings the bytes
         mbar_init(x_empty, 1);
         mbar_init(x1_ready, kAttXfWarps * 2);
         for (int s = 0; s < NYS; s++) {
             mbar_init(y_full0 + 8u * s, 1);
-            mbar_init(y_conv0 + 8u * s, 2);           // one converter warp per CTA
+            mbar_init(y_conv0 + 8u * s, p.planes ? 1 : 2);           // one converter warp per CTA
             mbar_init(y_empty0 + 8u * s, 1);
         }
         for (int s = 0; s < NZS; s++) {
             mbar_init(z_full0 + 8u * s, 1);
-            mbar_init(z_conv0 + 8u * s, 2);
+            mbar_init(z_conv0 + 8u * s, p.planes ? 1 : 2);
             mbar_init(z_empty0 + 8u * s, 1);
         }
         for (int b = 0; b < 2; b++) {
@@ -261,14 +266,32 @@ attn_kernel(const __grid_constant__ CUtensorMap mx2, const __grid_constant__ CUt
                 ATT_PROF_T0
                 for (int k = 0, u; (u = unit_of(k)) >= 0 && ok; k++, ul++) {
                     const AttnUnit d = attn_unit<MODE>(p, u);
+                    // planes: both halves (values, whose low mantissa bits the tensor core ignores, and precomputed
+                    // remainders) come by TMA, and the bytes of both CTAs are counted by the leader's "conv" barrier,
+                    // the one the MMA issuer waits on: no converter, no proxy fence, one hop less per tile
+                    const bool pl = p.planes != 0;
                     if (NX == 2) {
                         // the shared-memory row operand of this unit, once the previous unit's first products no longer read it
                         if (!ATT_PROF_WAIT(13, mbar_wait_bounded(x_empty, (ul & 1) ^ 1, p.wait_limit))) { ok = false; break; }
-                        mbar_arrive_expect_tx(x_full, (uint32_t)(kbh * 16384));
                         const int xrow = d.row0 + cta_rank * kRowsPerCta;
-                        for (int kb = 0; kb < kbh; kb++) {
-                            if (p.t_first) tma_load_4d(x_base + kb * 16384, &mx2, x_full, 32 * kb, xrow, d.h, d.b);
-                            else tma_load_4d(x_base + kb * 16384, &mx2, x_full, 32 * kb, d.h, xrow, d.b);
+                        if (pl) {
+                            const uint32_t fb = mapa_shared(x_conv, 0);
+                            if (leader) mbar_arrive_expect_tx(x_conv, (uint32_t)(4 * kbh * 16384));
+                            for (int kb = 0; kb < kbh; kb++) {
+                                if (p.t_first) {
+                                    tma_load_4d_pair(x_base + kb * 16384, &mx2, fb, 32 * kb, xrow, d.h, d.b);
+                                    tma_load_4d_pair(x_base + Cfg::kXTile + kb * 16384, &mx2l, fb, 32 * kb, xrow, d.h, d.b);
+                                } else {
+                                    tma_load_4d_pair(x_base + kb * 16384, &mx2, fb, 32 * kb, d.h, xrow, d.b);
+                                    tma_load_4d_pair(x_base + Cfg::kXTile + kb * 16384, &mx2l, fb, 32 * kb, d.h, xrow, d.b);
+                                }
+                            }
+                        } else {
+                            mbar_arrive_expect_tx(x_full, (uint32_t)(kbh * 16384));
+                            for (int kb = 0; kb < kbh; kb++) {
+                                if (p.t_first) tma_load_4d(x_base + kb * 16384, &mx2, x_full, 32 * kb, xrow, d.h, d.b);
+                                else tma_load_4d(x_base + kb * 16384, &mx2, x_full, 32 * kb, d.h, xrow, d.b);
+                            }
                         }
                     }
                     for (int c = 0; c < d.nb && ok; c++, it++) {
@@ -276,27 +299,66 @@ attn_kernel(const __grid_constant__ CUtensorMap mx2, const __grid_constant__ CUt
                         {   // Y: this CTA's 32 of the block's 64 columns, K-major
                             const int s = it % NYS;
                             if (!ATT_PROF_WAIT(13, mbar_wait_bounded(y_empty0 + 8u * s, ((it / NYS) & 1) ^ 1, p.wait_limit))) { ok = false; break; }
-                            const uint32_t fb = y_full0 + 8u * s, st = y_base + s * Cfg::kYStage;
-                            mbar_arrive_expect_tx(fb, (uint32_t)(NX * kbh * 4096));
+                            const uint32_t st = y_base + s * Cfg::kYStage;
                             const int yrow = col0 + cta_rank * 32;
-                            for (int kb = 0; kb < kbh; kb++) {
-                                if (p.t_first) tma_load_4d(st + kb * 4096, &my1, fb, 32 * kb, yrow, d.h, d.b);
-                                else tma_load_4d(st + kb * 4096, &my1, fb, 32 * kb, d.h, yrow, d.b);
-                                if (NX == 2) {
-                                    if (p.t_first) tma_load_4d(st + 2 * Cfg::kYTile + kb * 4096, &my2, fb, 32 * kb, yrow, d.h, d.b);
-                                    else tma_load_4d(st + 2 * Cfg::kYTile + kb * 4096, &my2, fb, 32 * kb, d.h, yrow, d.b);
+                            if (pl) {
+                                const uint32_t fb = mapa_shared(y_conv0 + 8u * s, 0);
+                                if (leader) mbar_arrive_expect_tx(y_conv0 + 8u * s, (uint32_t)(4 * NX * kbh * 4096));
+                                for (int kb = 0; kb < kbh; kb++) {
+                                    if (p.t_first) {
+                                        tma_load_4d_pair(st + kb * 4096, &my1, fb, 32 * kb, yrow, d.h, d.b);
+                                        tma_load_4d_pair(st + Cfg::kYTile + kb * 4096, &my1l, fb, 32 * kb, yrow, d.h, d.b);
+                                    } else {
+                                        tma_load_4d_pair(st + kb * 4096, &my1, fb, 32 * kb, d.h, yrow, d.b);
+                                        tma_load_4d_pair(st + Cfg::kYTile + kb * 4096, &my1l, fb, 32 * kb, d.h, yrow, d.b);
+                                    }
+                                    if (NX == 2) {
+                                        if (p.t_first) {
+                                            tma_load_4d_pair(st + 2 * Cfg::kYTile + kb * 4096, &my2, fb, 32 * kb, yrow, d.h, d.b);
+                                            tma_load_4d_pair(st + 3 * Cfg::kYTile + kb * 4096, &my2l, fb, 32 * kb, yrow, d.h, d.b);
+                                        } else {
+                                            tma_load_4d_pair(st + 2 * Cfg::kYTile + kb * 4096, &my2, fb, 32 * kb, d.h, yrow, d.b);
+                                            tma_load_4d_pair(st + 3 * Cfg::kYTile + kb * 4096, &my2l, fb, 32 * kb, d.h, yrow, d.b);
+                                        }
+                                    }
+                                }
+                            } else {
+                                const uint32_t fb = y_full0 + 8u * s;
+                                mbar_arrive_expect_tx(fb, (uint32_t)(NX * kbh * 4096));
+                                for (int kb = 0; kb < kbh; kb++) {
+                                    if (p.t_first) tma_load_4d(st + kb * 4096, &my1, fb, 32 * kb, yrow, d.h, d.b);
+                                    else tma_load_4d(st + kb * 4096, &my1, fb, 32 * kb, d.h, yrow, d.b);
+                                    if (NX == 2) {
+                                        if (p.t_first) tma_load_4d(st + 2 * Cfg::kYTile + kb * 4096, &my2, fb, 32 * kb, yrow, d.h, d.b);
+                                        else tma_load_4d(st + 2 * Cfg::kYTile + kb * 4096, &my2, fb, 32 * kb, d.h, yrow, d.b);
+                                    }
                                 }
                             }
                         }
                         {   // Z: the block's 64 contraction rows x this CTA's 32 output columns, MN-major
                             const int s = it % NZS;
                             if (!ATT_PROF_WAIT(13, mbar_wait_bounded(z_empty0 + 8u * s, ((it / NZS) & 1) ^ 1, p.wait_limit))) { ok = false; break; }
-                            const uint32_t fb = z_full0 + 8u * s, st = z_base + s * Cfg::kZStage;
-                            mbar_arrive_expect_tx(fb, 8192u);
+                            const uint32_t st = z_base + s * Cfg::kZStage;
                             const int d0 = cta_rank * 32;     // beyond hs (hs = 32, second CTA): the box is zero-filled
-                            for (int kk = 0; kk < 2; kk++) {
-                                if (p.t_first) tma_load_4d(st + kk * 4096, &mz, fb, d0, col0 + 32 * kk, d.h, d.b);
-                                else tma_load_4d(st + kk * 4096, &mz, fb, d0, d.h, col0 + 32 * kk, d.b);
+                            if (pl) {
+                                const uint32_t fb = mapa_shared(z_conv0 + 8u * s, 0);
+                                if (leader) mbar_arrive_expect_tx(z_conv0 + 8u * s, 4u * 8192u);
+                                for (int kk = 0; kk < 2; kk++) {
+                                    if (p.t_first) {
+                                        tma_load_4d_pair(st + kk * 4096, &mz, fb, d0, col0 + 32 * kk, d.h, d.b);
+                                        tma_load_4d_pair(st + Cfg::kZTile + kk * 4096, &mzl, fb, d0, col0 + 32 * kk, d.h, d.b);
+                                    } else {
+                                        tma_load_4d_pair(st + kk * 4096, &mz, fb, d0, d.h, col0 + 32 * kk, d.b);
+                                        tma_load_4d_pair(st + Cfg::kZTile + kk * 4096, &mzl, fb, d0, d.h, col0 + 32 * kk, d.b);
+                                    }
+                                }
+                            } else {
+                                const uint32_t fb = z_full0 + 8u * s;
+                                mbar_arrive_expect_tx(fb, 8192u);
+                                for (int kk = 0; kk < 2; kk++) {
+                                    if (p.t_first) tma_load_4d(st + kk * 4096, &mz, fb, d0, col0 + 32 * kk, d.h, d.b);
+                                    else tma_load_4d(st + kk * 4096, &mz, fb, d0, d.h, col0 + 32 * kk, d.b);
+                                }
                             }
                         }
                     }
@@ -465,7 +527,7 @@ attn_kernel(const __grid_constant__ CUtensorMap mx2, const __grid_constant__ CUt
             bool got = true;
             uint32_t it = 0, ul = 0;       // it: blocks seen so far (the ring counter of both streams)
             ATT_PROF_T0
-            for (int k = 0, u; (u = unit_of(k)) >= 0 && got; k++, ul++) {
+            for (int k = 0, u; !p.planes && (u = unit_of(k)) >= 0 && got; k++, ul++) {   // (planes: nothing to convert)
                 const AttnUnit d = attn_unit<MODE>(p, u);
                 if (NX == 2) {
                     if (!(got = wait_full(x_full, ul & 1))) break;
@@ -767,6 +829,28 @@ __global__ void attn_rowdot_kernel(const float* __restrict__ dO, const float* __
     if (ok && (lane % lpr) == 0) D[r] = s;
 }
 
+// Remainder planes: dst_i[j] = src_i[j] - (src_i[j] with the 13 low mantissa bits cleared), over the whole extent of up to
+// four tensors (blockIdx.y picks one).  The tensor core takes the values themselves as the TF32 heads (it ignores the low
+// bits), so a 3xTF32 operand that comes straight from TMA needs only this second plane.
+struct AttnLoArgs {
+    const float4* src[4];
+    float4* dst[4];
+};
+__global__ void attn_lo_kernel(const AttnLoArgs a, size_t n4)
+{
+    const float4* __restrict__ src = a.src[blockIdx.y];
+    float4* __restrict__ dst = a.dst[blockIdx.y];
+    for (size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x; i < n4; i += (size_t)gridDim.x * blockDim.x) {
+        const float4 x = src[i];
+        float4 l;
+        l.x = x.x - __uint_as_float(__float_as_uint(x.x) & 0xFFFFE000u);
+        l.y = x.y - __uint_as_float(__float_as_uint(x.y) & 0xFFFFE000u);
+        l.z = x.z - __uint_as_float(__float_as_uint(x.z) & 0xFFFFE000u);
+        l.w = x.w - __uint_as_float(__float_as_uint(x.w) & 0xFFFFE000u);
+        dst[i] = l;
+    }
+}
+
 // ---------------------------------------------------------------------------
 // host side
 // ---------------------------------------------------------------------------
@@ -832,9 +916,11 @@ int attn_profile_read(long long* out32)
     return ZNN_OK;
 }
 
+// X2l, Y1l, Y2l, Zl: the remainder planes of X2, Y1, Y2, Z (same layout), or all NULL: the kernel then converts in place
 template <int MODE>
 static int launch_attn(const float* X1, const float* X2, const float* Y1, const float* Y2, const float* Z, const AttnLayout& L,
-                       AttnParams p)
+                       AttnParams p, const float* X2l = nullptr, const float* Y1l = nullptr, const float* Y2l = nullptr,
+                       const float* Zl = nullptr)
 {
     using Cfg = AttnCfg<MODE>;
     auto kern = attn_kernel<MODE>;
@@ -854,6 +940,14 @@ static int launch_attn(const float* X1, const float* X2, const float* Y1, const 
     if ((rc = make_attn_map(&my1, Y1, L, 32))) return rc;
     if ((rc = make_attn_map(&my2, Y2 ? Y2 : Y1, L, 32))) return rc;
     if ((rc = make_attn_map(&mz, Z, L, 0))) return rc;
+    CUtensorMap mx2l = mx2, my1l = my1, my2l = my2, mzl = mz;
+    p.planes = (Y1l && Zl) ? 1 : 0;
+    if (p.planes) {
+        if ((rc = make_attn_map(&mx2l, X2l ? X2l : Y1l, L, kRowsPerCta))) return rc;
+        if ((rc = make_attn_map(&my1l, Y1l, L, 32))) return rc;
+        if ((rc = make_attn_map(&my2l, Y2l ? Y2l : Y1l, L, 32))) return rc;
+        if ((rc = make_attn_map(&mzl, Zl, L, 0))) return rc;
+    }
     cudaLaunchConfig_t cfg = {};
     cfg.blockDim = dim3(kAttThreads, 1, 1);
     cfg.dynamicSmemBytes = Cfg::kSmemBytes;
@@ -877,7 +971,7 @@ static int launch_attn(const float* X1, const float* X2, const float* Y1, const 
     const long units = (long)p.nslices * p.nrb;
     const long pairs = units < pairs_by_device[dev] ? units : pairs_by_device[dev];
     cfg.gridDim = dim3((unsigned)(2 * pairs), 1, 1);
-    ZNN_CUDA_OK(cudaLaunchKernelEx(&cfg, kern, mx2, my1, my2, mz, p));
+    ZNN_CUDA_OK(cudaLaunchKernelEx(&cfg, kern, mx2, my1, my2, mz, mx2l, my1l, my2l, mzl, p));
     count_launch();
     if (inject_launch_failure()) return fail(ZNN_ERR_CUDA, "launch of the attention kernel failed: injected failure (znn_debug_fail_after)");
     return ZNN_OK;
@@ -914,9 +1008,34 @@ static AttnParams attn_params(const AttnLayout& L, float scale)
     p.ld = L.ld; p.stride_h = L.stride_h; p.stride_b = L.stride_b;
     p.x1 = nullptr; p.out = nullptr; p.lse = nullptr; p.dvec = nullptr;
     p.accumulate = 0;
+    p.planes = 0;
     p.status = device_status_word();
     p.wait_limit = tc_wait_limit();
     return p;
+}
+
+static thread_local int t_attn_planes = 0;   // measured: no faster than the converter warps, and the pre-pass costs 16-32 us per call
+void attn_set_planes(int on) { t_attn_planes = on ? 1 : 0; }
+
+// Remainder planes of n (<= 4) tensors of layout L in scratch slot 1; dst[i] receives the plane of src[i].
+static int attn_make_lo_planes(const AttnLayout& L, int n, const float* const* src, const float** dst)
+{
+    const size_t span = (size_t)(L.B - 1) * L.stride_b + (size_t)(L.nh - 1) * L.stride_h + (size_t)(L.T - 1) * L.ld + L.hs;
+    const size_t span4 = (span + 3) / 4;            // (strides and hs are multiples of 4, so span is)
+    float* base = (float*)workspace_slot(1, (size_t)n * span4 * 4 * sizeof(float));
+    if (!base) return fail(ZNN_ERR_NOMEM, "scratch for the attention operands' remainder planes");
+    AttnLoArgs a{};
+    for (int i = 0; i < n; i++) {
+        a.src[i] = reinterpret_cast<const float4*>(src[i]);
+        a.dst[i] = reinterpret_cast<float4*>(base + (size_t)i * span4 * 4);
+        dst[i] = base + (size_t)i * span4 * 4;
+    }
+    size_t blocks = (span4 + 255) / 256;
+    const size_t cap = (size_t)sm_count() * 8;
+    if (blocks > cap) blocks = cap;
+    attn_lo_kernel<<<dim3((unsigned)blocks, (unsigned)n), 256, 0, stream()>>>(a, span4);
+    ZNN_LAUNCH_OK("attn_lo_kernel");
+    return ZNN_OK;
 }
 
 }  // namespace znn
@@ -924,6 +1043,12 @@ static AttnParams attn_params(const AttnLayout& L, float scale)
 using namespace znn;
 
 extern "C" {
+
+int znn_debug_set_attn_planes(int enable)
+{
+    attn_set_planes(enable);
+    return ZNN_OK;
+}
 
 int znn_debug_attn_profile(long long* out32)
 {
@@ -943,6 +1068,12 @@ int znn_attn_fwd(const float* Q, const float* K, const float* V, float* O, float
     if (!p.status) return fail(ZNN_ERR_CUDA, "no device state (call znn_init first)");
     p.out = O;
     p.lse = LSE;
+    if (t_attn_planes) {
+        const float* src[2] = {K, V};
+        const float* lo[2] = {nullptr, nullptr};
+        if ((rc = attn_make_lo_planes(L, 2, src, lo))) return rc;
+        return launch_attn<ATT_FWD>(Q, nullptr, K, nullptr, V, L, p, nullptr, lo[0], nullptr, lo[1]);
+    }
     return launch_attn<ATT_FWD>(Q, nullptr, K, nullptr, V, L, p);
 }
 
@@ -972,17 +1103,23 @@ int znn_attn_bwd(const float* Q, const float* K, const float* V, const float* O,
         ZNN_LAUNCH_OK("attn_rowdot_kernel");
         p.dvec = D;
     }
+    const float* lo[4] = {nullptr, nullptr, nullptr, nullptr};   // remainder planes of Q, K, V, dO
+    if (t_attn_planes) {
+        const float* src[4] = {Q, K, V, dO};
+        if ((rc = attn_make_lo_planes(L, 4, src, lo))) return rc;
+    }
+    const float *Ql = lo[0], *Kl = lo[1], *Vl = lo[2], *dOl = lo[3];
     if (dQ) {
         p.out = dQ;
-        if ((rc = launch_attn<ATT_BWD_Q>(Q, dO, K, V, K, L, p))) return rc;
+        if ((rc = launch_attn<ATT_BWD_Q>(Q, dO, K, V, K, L, p, dOl, Kl, Vl, Kl))) return rc;
     }
     if (dK) {
         p.out = dK;
-        if ((rc = launch_attn<ATT_BWD_K>(K, V, Q, dO, Q, L, p))) return rc;
+        if ((rc = launch_attn<ATT_BWD_K>(K, V, Q, dO, Q, L, p, Vl, Ql, dOl, Ql))) return rc;
     }
     if (dV) {
         p.out = dV;
-        if ((rc = launch_attn<ATT_BWD_V>(K, nullptr, Q, nullptr, dO, L, p))) return rc;
+        if ((rc = launch_attn<ATT_BWD_V>(K, nullptr, Q, nullptr, dO, L, p, nullptr, Ql, nullptr, dOl))) return rc;
     }
     return ZNN_OK;
 }

@@ -302,6 +302,16 @@ __device__ __forceinline__ void tma_load_4d(uint32_t dst, const CUtensorMap* tm,
         : "memory");
 }
 
+// CTA-pair form of the 4-d load: the box lands in this CTA's shared memory, the mbarrier (a shared::cluster address) may
+// be the pair leader's, so that one barrier collects the bytes of both CTAs.  No multicast.
+__device__ __forceinline__ void tma_load_4d_pair(uint32_t dst, const CUtensorMap* tm, uint32_t bar, int c0, int c1, int c2, int c3)
+{
+    asm volatile(
+        "cp.async.bulk.tensor.4d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5, %6}], [%2];"
+        ::"r"(dst), "l"(tm), "r"(bar), "r"(c0), "r"(c1), "r"(c2), "r"(c3)
+        : "memory");
+}
+
 // CTA-pair MMA whose A operand lies in tensor memory (K-major: lane = row, one column per tf32 element, the same
 // columns in both CTAs of the pair); B comes from shared memory through a descriptor.
 __device__ __forceinline__ void umma_tf32_ts_pair(uint32_t tmem_d, uint32_t tmem_a, uint64_t desc_b, uint32_t idesc, uint32_t accumulate)
