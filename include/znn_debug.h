@@ -51,6 +51,11 @@ int znn_debug_attn_profile(long long* out32);
  * fence).  Bit-identical results; measured no faster (the kernels wait for the tiles' arrival either way) and the pre-pass
  * costs 16-32 us per call, hence not the default. */
 int znn_debug_set_attn_planes(int enable);
+/* Fused attention, per host thread: 0 (default) = while the MMA issuer waits for a block's tile it issues the previous
+ * block's second product as soon as that product's own inputs are there; 1 = the fixed order first product of block g,
+ * second product of block g - 1, ... whatever arrives first.  Same instructions on the same buffers either way (results
+ * are bit-identical); the switch exists for A/B timing. */
+int znn_debug_set_attn_issue_order(int in_order);
 
 /* Conv2D path of the calling host thread: 0 (default) = layers with Ci*KH*KW >= 64 taps, at most 64 output channels and at
  * least 4096 output pixels run as implicit-im2col GEMMs on the tensor cores; 1 = never (direct kernels and the explicit

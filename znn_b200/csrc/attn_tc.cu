@@ -55,6 +55,7 @@ struct AttnParams {
     int planes;                   // 1: the remainder (lo) parts of the shared-memory operands come precomputed through their own
                                   // tensor maps: TMA fills both halves of a stage and signals the MMA issuer's barrier directly
     int* status;
+    int issue_in_order;           // 1: the MMA issuer keeps the fixed order P1(g), P2(g-1), P1(g+1), ... (A/B switch)
     unsigned long long wait_limit;
 };
 
@@ -120,7 +121,10 @@ __device__ __forceinline__ AttnUnit attn_unit(const AttnParams& p, int u)
 // znn_debug_attn_profile reads: [0] MMA loop, [1] x waits, [2] y_conv, [3] w_ready, [4] z_conv, [5] acc_empty, [6] issue of
 // the first products, [7] issue of the second products; [8] transform loop, [9] s_full, [10] acc_full, [11] row operand
 // load; [12] producer loop, [13] its waits; [14] converter loop, [15] its waits, [17] fence + arrival; transform:
-// [18] score load, [19] W store + hand-off, [20] accumulator drain, [21] load-to-hand-off of one block.
+// [18] score load, [19] W store + hand-off, [20] accumulator drain, [21] load-to-hand-off of one block.  The life of ring
+// slot 0 of the Y stream, summed over its tiles ([11] of them): [5] commit of the products that free the slot -> producer
+// sees it empty, [16] loads issued -> converter sees the bytes, [24] conversion, [30] converter's hand-off done -> MMA
+// issuer past its wait (slack when the issuer arrives late).
 __device__ long long g_attn_prof[32];
 #ifdef ZNN_ATTN_PROFILE
 #define ATT_PROF_T0 const long long prof_t0 = clock64();
@@ -299,6 +303,9 @@ attn_kernel(const __grid_constant__ CUtensorMap mx2, const __grid_constant__ CUt
                         {   // Y: this CTA's 32 of the block's 64 columns, K-major
                             const int s = it % NYS;
                             if (!ATT_PROF_WAIT(13, mbar_wait_bounded(y_empty0 + 8u * s, ((it / NYS) & 1) ^ 1, p.wait_limit))) { ok = false; break; }
+#ifdef ZNN_ATTN_PROFILE
+                            if (prof_on && s == 0 && it >= (uint32_t)NYS) { prof_acc[5] += clock64() - tstamp[8]; prof_acc[11] += 1; }
+#endif
                             const uint32_t st = y_base + s * Cfg::kYStage;
                             const int yrow = col0 + cta_rank * 32;
                             if (pl) {
@@ -334,6 +341,9 @@ attn_kernel(const __grid_constant__ CUtensorMap mx2, const __grid_constant__ CUt
                                     }
                                 }
                             }
+#ifdef ZNN_ATTN_PROFILE
+                            if (prof_on && s == 0) tstamp[9] = clock64();
+#endif
                         }
                         {   // Z: the block's 64 contraction rows x this CTA's 32 output columns, MN-major
                             const int s = it % NZS;
@@ -418,16 +428,44 @@ attn_kernel(const __grid_constant__ CUtensorMap mx2, const __grid_constant__ CUt
                     itz++;
                     return true;
                 };
+                // Waits for `bar`; while it is not there, the second product of the oldest block that still lacks it
+                // (block h, h < g: its first product has been issued) is issued as soon as its own inputs are, so that a
+                // late tile of block g does not hold back work that is ready.  The two products of different blocks use
+                // different score buffers, so their order is free; P1(g) only needs P2(g - 2) issued before it.
+                uint32_t h = 0;                               // second products issued so far
+                auto wait_or_second = [&](uint32_t bar, uint32_t parity) -> bool {
+                    if (p.issue_in_order) return warp_wait(bar, parity);
+                    const uint64_t t0 = wait_clock();
+                    for (uint32_t polls = 0;; polls++) {
+                        uint32_t st = 0;
+                        if (lane == 0) {
+                            st = mbar_test(bar, parity);
+                            if (!st && h < g) {
+                                const uint32_t zs = itz % NZS;
+                                if (mbar_test(w_ready0 + 8u * (h & 1), (h >> 1) & 1) && mbar_test(z_conv0 + 8u * zs, (itz / NZS) & 1)) st = 2;
+                            }
+                        }
+                        st = __shfl_sync(0xffffffffu, st, 0);
+                        if (st == 1) return true;
+                        if (st == 2) {
+                            if (!second(h)) return false;
+                            h++;
+                        } else if ((polls & 255u) == 255u && wait_clock() - t0 > p.wait_limit) return false;
+                    }
+                };
                 for (int k = 0, u; (u = unit_of(k)) >= 0 && ok; k++, ul++) {
                     const AttnUnit d = attn_unit<MODE>(p, u);
-                    if (!ATT_PROF_WAIT(1, warp_wait(x1_ready, ul & 1))) { ok = false; break; }
-                    if (NX == 2 && !ATT_PROF_WAIT(1, warp_wait(x_conv, ul & 1))) { ok = false; break; }
+                    if (!ATT_PROF_WAIT(1, wait_or_second(x1_ready, ul & 1))) { ok = false; break; }
+                    if (NX == 2 && !ATT_PROF_WAIT(1, wait_or_second(x_conv, ul & 1))) { ok = false; break; }
                     tc_fence_after();
                     for (int c = 0; c < d.nb && ok; c++, g++, it++) {
                         const uint32_t buf = g & 1;
                         const int s = it % NYS;
-                        if (!ATT_PROF_WAIT(2, warp_wait(y_conv0 + 8u * s, (it / NYS) & 1))) { ok = false; break; }
+                        if (!ATT_PROF_WAIT(2, wait_or_second(y_conv0 + 8u * s, (it / NYS) & 1))) { ok = false; break; }
                         tc_fence_after();
+#ifdef ZNN_ATTN_PROFILE
+                        if (prof_on && s == 0) prof_acc[30] += clock64() - tstamp[10];
+#endif
                         ATT_PROF_MARK2(pm)
                         if (elected) {
                             // descriptors differ from the base ones by constant offsets (in 16-byte units): k-step k lies in
@@ -467,6 +505,7 @@ attn_kernel(const __grid_constant__ CUtensorMap mx2, const __grid_constant__ CUt
                             umma_commit_pair(y_empty0 + 8u * s);
 #ifdef ZNN_ATTN_PROFILE
                             tstamp[g & 3] = clock64();
+                            if (s == 0) tstamp[8] = clock64();
 #endif
                             if (NX == 2 && c == d.nb - 1) umma_commit_pair(x_empty);   // the shared-memory row operand is free after these
                         }
@@ -474,10 +513,13 @@ attn_kernel(const __grid_constant__ CUtensorMap mx2, const __grid_constant__ CUt
                         ATT_PROF_ADD2(6, pm)
                         // the previous block's second product (of this unit or of the one before): program order
                         // P1(g), P2(g-1), P1(g+1), P2(g), ... runs on across units
-                        if (g >= 1 && !second(g - 1)) { ok = false; break; }
+                        if (h < g) {
+                            if (!second(h)) { ok = false; break; }
+                            h++;
+                        }
                     }
                 }
-                if (ok && g >= 1 && !second(g - 1)) ok = false;
+                if (ok && h < g && !second(h)) ok = false;
                 if (!ok && lane == 0) atomicOr(p.status, ZNN_DEV_MMA_WAIT_EXPIRED);
                 ATT_PROF_END(0)
             }
@@ -539,9 +581,19 @@ attn_kernel(const __grid_constant__ CUtensorMap mx2, const __grid_constant__ CUt
                     if (kind == 0) {
                         const int s = it % NYS;
                         if (!(got = wait_full(y_full0 + 8u * s, (it / NYS) & 1))) break;
+#ifdef ZNN_ATTN_PROFILE
+                        const long long tc0 = clock64();
+                        if (prof_on && s == 0) prof_acc[16] += tc0 - tstamp[9];
+#endif
                         uint8_t* st = smem_gen + Cfg::kXBytes + s * Cfg::kYStage;
                         for (int w = 0; w < NX; w++) convert(st + w * 2 * Cfg::kYTile, kbh * 256, Cfg::kYTile, lane, 32);
+#ifdef ZNN_ATTN_PROFILE
+                        if (prof_on && s == 0) prof_acc[24] += clock64() - tc0;
+#endif
                         done(y_conv_l0 + 8u * s);
+#ifdef ZNN_ATTN_PROFILE
+                        if (prof_on && s == 0) tstamp[10] = clock64();
+#endif
                     } else {
                         const int s = it % NZS;
                         if (!(got = wait_full(z_full0 + 8u * s, (it / NZS) & 1))) break;
@@ -906,6 +958,7 @@ static int make_attn_map(CUtensorMap* tm, const float* X, const AttnLayout& L, i
     return ZNN_OK;
 }
 
+static thread_local int t_attn_in_order = 0;
 unsigned long long tc_wait_limit();
 
 int attn_profile_read(long long* out32)
@@ -1009,11 +1062,13 @@ static AttnParams attn_params(const AttnLayout& L, float scale)
     p.x1 = nullptr; p.out = nullptr; p.lse = nullptr; p.dvec = nullptr;
     p.accumulate = 0;
     p.planes = 0;
+    p.issue_in_order = t_attn_in_order;
     p.status = device_status_word();
     p.wait_limit = tc_wait_limit();
     return p;
 }
 
+void attn_set_issue_order(int in_order) { t_attn_in_order = in_order ? 1 : 0; }
 static thread_local int t_attn_planes = 0;   // measured: no faster than the converter warps, and the pre-pass costs 16-32 us per call
 void attn_set_planes(int on) { t_attn_planes = on ? 1 : 0; }
 
@@ -1047,6 +1102,12 @@ extern "C" {
 int znn_debug_set_attn_planes(int enable)
 {
     attn_set_planes(enable);
+    return ZNN_OK;
+}
+
+int znn_debug_set_attn_issue_order(int in_order)
+{
+    attn_set_issue_order(in_order);
     return ZNN_OK;
 }
 
