@@ -384,10 +384,10 @@ attn_kernel(const __grid_constant__ CUtensorMap mx2, const __grid_constant__ CUt
             // between them), and cost about twice the issue time.
             if (leader) {
                 const bool elected = elect_one();
+                // every lane polls (one warp-wide instruction per poll, no broadcast of the answer); the vote keeps the
+                // warp's decision uniform should the limit run out for some lanes only
                 auto warp_wait = [&](uint32_t bar, uint32_t parity) -> bool {
-                    bool r = true;
-                    if (lane == 0) r = mbar_wait_bounded_tight(bar, parity, p.wait_limit);
-                    return __shfl_sync(0xffffffffu, (int)r, 0) != 0;
+                    return __all_sync(0xffffffffu, mbar_wait_bounded_tight(bar, parity, p.wait_limit));
                 };
                 constexpr uint32_t idesc1 = make_tf32_idesc_major(256, 64, false, false);
                 constexpr uint32_t idesc2 = make_tf32_idesc_major(256, 64, false, true);
@@ -434,6 +434,7 @@ attn_kernel(const __grid_constant__ CUtensorMap mx2, const __grid_constant__ CUt
                 // different score buffers, so their order is free; P1(g) only needs P2(g - 2) issued before it.
                 uint32_t h = 0;                               // second products issued so far
                 auto wait_or_second = [&](uint32_t bar, uint32_t parity) -> bool {
+                    if (__all_sync(0xffffffffu, mbar_test(bar, parity))) return true;
                     if (p.issue_in_order) return warp_wait(bar, parity);
                     const uint64_t t0 = wait_clock();
                     for (uint32_t polls = 0;; polls++) {
@@ -716,7 +717,6 @@ attn_kernel(const __grid_constant__ CUtensorMap mx2, const __grid_constant__ CUt
                     if (prof_on) { prof_acc[26] += clock64() - tstamp[g & 3]; prof_acc[28] += 1; }
 #endif
                     tc_fence_after();
-                    if (next_x1) store_x1(xn);
                     const uint32_t ts = tmem_base + lane_sel + kColS + 64u * buf + col_sel;
                     const uint32_t tl = tmem_base + lane_sel + kColWlo + 64u * wbuf + col_sel;
                     const uint32_t tdp = tmem_base + lane_sel + kColDp + 64u * buf + col_sel;
@@ -815,6 +815,9 @@ attn_kernel(const __grid_constant__ CUtensorMap mx2, const __grid_constant__ CUt
                     if (lane == 0) mbar_arrive_remote(w_ready_l0 + 8u * buf);
                     ATT_PROF_ADD2(19, ps)
                     ATT_PROF_ADD2(21, pt)
+                    // the next unit's rows go to tensor memory after this block's hand-off: the issuer needs the hand-off first
+                    // (the last second product of this unit, whose result the unit's epilogue below waits for)
+                    if (next_x1) store_x1(xn);
                     // two buffers: the previous block's second product has had this block's transform time to finish
                     if (NWB == 2 && c >= 1) got = drain(g - 1, corr_prev);
                     corr_prev = corr;
