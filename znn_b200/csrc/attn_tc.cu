@@ -79,7 +79,13 @@ struct AttnCfg {
     static constexpr int NZS = NX == 2 ? 3 : ZNN_ATT_STAGES1;
     static constexpr int kBarOff = kXBytes + NYS * kYStage + NZS * kZStage;
     static constexpr int kExchBytes = MODE == ATT_FWD ? 2048 : 0;   // row-maximum exchange between the two threads of a row
-    static constexpr int kSmemBytes = kBarOff + 1024 /*alignment*/ + 512 /*barriers*/ + kExchBytes;
+    // Row staging of the transform warps (rows enter and leave through full 128-byte lines although a thread owns a whole
+    // row): per warp kStageRows rows of 8 float4 at a pitch of 9 float4 (conflict-free both ways).  32 rows where shared
+    // memory allows, 8 rows (four passes) next to the 64 KB row operand of dQ / dK.
+    static constexpr int kStageRows = NX == 2 ? 8 : 32;
+    static constexpr int kStageWarpBytes = kStageRows * 144;
+    static constexpr int kStageOff = kBarOff + 512 + kExchBytes;
+    static constexpr int kSmemBytes = kBarOff + 1024 /*alignment*/ + 512 /*barriers*/ + kExchBytes + kAttXfWarps * kStageWarpBytes;
     static_assert(kSmemBytes <= 232448, "shared memory budget");
     // tensor-memory columns (512 allocated): X1 hi | X1 lo | S / W_hi [2] | then, forward and dV: W_lo [2], accumulator [2];
     // dQ and dK: dP [2], W_lo [1], accumulator [1]
@@ -633,17 +639,38 @@ attn_kernel(const __grid_constant__ CUtensorMap mx2, const __grid_constant__ CUt
             auto pair_sync = [&]() { asm volatile("bar.sync %0, 64;" ::"r"(1 + q) : "memory"); };   // the two warps of a lane quarter
             ATT_PROF_T0
             // This thread's 32 columns of its row of X1 for unit `un`: global memory -> registers ...
+            // (coalesced: lane l fetches float4 l % 8 of rows l / 8, l / 8 + 4, ..., i.e. four whole 128-byte rows per
+            // instruction; the rows change hands in shared memory inside store_x1)
+            float4* const stage = reinterpret_cast<float4*>(smem_gen + Cfg::kStageOff + (warp - kAttXfWarp0) * Cfg::kStageWarpBytes);
+            constexpr int CH = Cfg::kStageRows;
+            const int lr = lane >> 3, lc = lane & 7;
             auto load_x1 = [&](int un, float4 (&xr)[8]) {
                 const AttnUnit dn = attn_unit<MODE>(p, un);
-                const int rown = dn.row0 + cta_rank * kRowsPerCta + rloc;
-                const bool have = rown < p.T && 32 * half < hs;
-                const float* src = p.x1 + (size_t)dn.b * p.stride_b + (size_t)dn.h * p.stride_h + (size_t)rown * p.ld + 32 * half;
+                const int row_w = dn.row0 + cta_rank * kRowsPerCta + q * 32;      // the warp's first row
+                const float* src = p.x1 + (size_t)dn.b * p.stride_b + (size_t)dn.h * p.stride_h + (size_t)row_w * p.ld + 32 * half + 4 * lc;
 #pragma unroll
-                for (int i = 0; i < 8; i++) xr[i] = have ? *reinterpret_cast<const float4*>(src + 4 * i) : make_float4(0.f, 0.f, 0.f, 0.f);
+                for (int i = 0; i < 8; i++) {
+                    const int r = 4 * i + lr;
+                    const bool have = row_w + r < p.T && 32 * half < hs;
+                    xr[i] = have ? *reinterpret_cast<const float4*>(src + (size_t)r * p.ld) : make_float4(0.f, 0.f, 0.f, 0.f);
+                }
             };
             // ... -> hi / lo -> tensor memory, and the MMA issuer is told.  Called once the first products of the previous
             // unit have completed (they read the old rows).
-            auto store_x1 = [&](const float4 (&xr)[8]) {
+            auto store_x1 = [&](const float4 (&xf)[8]) {
+                // rows change hands: written as fetched, read back by the thread that owns the row
+                float4 xr[8];
+#pragma unroll
+                for (int ps = 0; ps < 32 / CH; ps++) {
+#pragma unroll
+                    for (int i = ps * (CH / 4); i < (ps + 1) * (CH / 4); i++) stage[(4 * i + lr - ps * CH) * 9 + lc] = xf[i];
+                    __syncwarp();
+                    if (lane / CH == ps) {
+#pragma unroll
+                        for (int j = 0; j < 8; j++) xr[j] = stage[(lane - ps * CH) * 9 + j];
+                    }
+                    __syncwarp();
+                }
                 uint32_t hi[32], lo[32];
 #pragma unroll
                 for (int i = 0; i < 8; i++) {
@@ -671,7 +698,6 @@ attn_kernel(const __grid_constant__ CUtensorMap mx2, const __grid_constant__ CUt
                 const int row = d.row0 + cta_rank * kRowsPerCta + rloc;       // absolute row inside the slice
                 const bool row_ok = row < p.T;
                 const size_t stat_off = (size_t)d.slice * p.T;
-                const size_t row_off = (size_t)d.b * p.stride_b + (size_t)d.h * p.stride_h + (size_t)row * p.ld + 32 * half;
                 float acc[32];
 #pragma unroll
                 for (int i = 0; i < 32; i++) acc[i] = 0.0f;
@@ -834,17 +860,32 @@ attn_kernel(const __grid_constant__ CUtensorMap mx2, const __grid_constant__ CUt
                     if (row_ok && got && half == 0) p.lse[stat_off + row] = m_run + log2f(l_all);
                     pair_sync();      // the slot may be rewritten by the next unit's first block (same parity)
                 }
-                if (row_ok && got) {
-                    float* dst = p.out + row_off;
+                // the rows leave through shared memory, four whole 128-byte rows per store instruction (a thread storing
+                // its own row touches 32 different lines per instruction)
+                if (32 * half < hs && __all_sync(0xffffffffu, got)) {
+                    const int row_w = d.row0 + cta_rank * kRowsPerCta + q * 32;
+                    float* const dst_w = p.out + (size_t)d.b * p.stride_b + (size_t)d.h * p.stride_h + (size_t)row_w * p.ld + 32 * half + 4 * lc;
 #pragma unroll
-                    for (int i = 0; i < 32; i += 4) {
-                        if (32 * half + i >= hs) continue;
-                        float4 o = make_float4(acc[i] * inv, acc[i + 1] * inv, acc[i + 2] * inv, acc[i + 3] * inv);
-                        if (MODE != ATT_FWD && p.accumulate) {
-                            const float4 old = *reinterpret_cast<const float4*>(dst + i);
-                            o.x += old.x; o.y += old.y; o.z += old.z; o.w += old.w;
+                    for (int ps = 0; ps < 32 / CH; ps++) {
+                        if (lane / CH == ps) {
+#pragma unroll
+                            for (int j = 0; j < 8; j++)
+                                stage[(lane - ps * CH) * 9 + j] = make_float4(acc[4 * j] * inv, acc[4 * j + 1] * inv, acc[4 * j + 2] * inv, acc[4 * j + 3] * inv);
                         }
-                        *reinterpret_cast<float4*>(dst + i) = o;
+                        __syncwarp();
+#pragma unroll
+                        for (int i = ps * (CH / 4); i < (ps + 1) * (CH / 4); i++) {
+                            const int r = 4 * i + lr;
+                            if (row_w + r >= p.T) continue;
+                            float4 o = stage[(r - ps * CH) * 9 + lc];
+                            float* const dst = dst_w + (size_t)r * p.ld;
+                            if (MODE != ATT_FWD && p.accumulate) {
+                                const float4 old = *reinterpret_cast<const float4*>(dst);
+                                o.x += old.x; o.y += old.y; o.z += old.z; o.w += old.w;
+                            }
+                            *reinterpret_cast<float4*>(dst) = o;
+                        }
+                        __syncwarp();
                     }
                 }
             }
