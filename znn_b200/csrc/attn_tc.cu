@@ -82,7 +82,10 @@ struct AttnCfg {
     // Row staging of the transform warps (rows enter and leave through full 128-byte lines although a thread owns a whole
     // row): per warp kStageRows rows of 8 float4 at a pitch of 9 float4 (conflict-free both ways).  32 rows where shared
     // memory allows, 8 rows (four passes) next to the 64 KB row operand of dQ / dK.
-    static constexpr int kStageRows = NX == 2 ? 8 : 32;
+#ifndef ZNN_ATT_STAGE_ROWS1
+#define ZNN_ATT_STAGE_ROWS1 32
+#endif
+    static constexpr int kStageRows = NX == 2 ? 8 : ZNN_ATT_STAGE_ROWS1;
     static constexpr int kStageWarpBytes = kStageRows * 144;
     static constexpr int kStageOff = kBarOff + 512 + kExchBytes;
     static constexpr int kSmemBytes = kBarOff + 1024 /*alignment*/ + 512 /*barriers*/ + kExchBytes + kAttXfWarps * kStageWarpBytes;
@@ -234,7 +237,7 @@ attn_kernel(const __grid_constant__ CUtensorMap mx2, const __grid_constant__ CUt
         mbar_init(x1_ready, kAttXfWarps * 2);
         for (int s = 0; s < NYS; s++) {
             mbar_init(y_full0 + 8u * s, 1);
-            mbar_init(y_conv0 + 8u * s, p.planes ? 1 : 2);           // one converter warp per CTA
+            mbar_init(y_conv0 + 8u * s, p.planes ? 1 : 2 * NX);      // one converter warp per tile and CTA
             mbar_init(y_empty0 + 8u * s, 1);
         }
         for (int s = 0; s < NZS; s++) {
@@ -532,12 +535,16 @@ attn_kernel(const __grid_constant__ CUtensorMap mx2, const __grid_constant__ CUt
             }
         } else {
             // ---------------- converters: lo = x - (x with the 13 low mantissa bits cleared), next to each landed tile ----------------
-            // Handing a converted tile to the tensor core (proxy fence, barrier arrival) costs a warp about 1500 cycles
-            // (measured), several times the conversion itself.  Each of the six warps therefore works alone on its own
-            // tiles: warps 0, 2, 4 take the Y tiles of blocks 0, 1, 2 (mod 3), warps 1, 3, 5 the Z tiles, so six hand-offs
-            // are in flight at a time.  The shared-memory row operand (dQ, dK) is converted by all six together.
+            // Handing a converted tile to the tensor core (proxy fence, barrier arrival) costs a warp 1500-2000 cycles per
+            // 8 KB tile here (measured; 16 cycles in a kernel that does nothing else), more than the conversion itself, and
+            // the time grows with the bytes the warp touched.  Each of the six warps therefore works alone on one 8 KB tile
+            // at a time: forward and dV (tiles Y, Z per block) warps 0, 2, 4 take the Y tiles of blocks 0, 1, 2 (mod 3) and
+            // warps 1, 3, 5 the Z tiles; dQ and dK (tiles Y1, Y2, Z per block) warps 0-2 take the three tiles of the even
+            // blocks and warps 3-5 those of the odd blocks.  The shared-memory row operand (dQ, dK) is converted by all six.
             const int cw = warp - kAttConvWarp0;                               // 0 .. 5
-            const int kind = cw & 1, turn = cw >> 1;                           // Y or Z; which blocks (mod 3)
+            constexpr int kJobs = NX + 1, kGroups = kAttConvWarps / kJobs;     // tiles per block; groups of warps taking blocks in turn
+            const int job = cw % kJobs, turn = cw / kJobs;
+            const int kind = job == NX ? 1 : 0;                                // Y (job = which of the NX tiles) or Z
             const int ct = threadIdx.x - 32 * kAttConvWarp0;                   // 0 .. 191 over all converter warps
             const uint32_t x_conv_l = mapa_shared(x_conv, 0), y_conv_l0 = mapa_shared(y_conv0, 0), z_conv_l0 = mapa_shared(z_conv0, 0);
             auto convert = [&](uint8_t* base, int nvec, int lo_off, int tid, int nthr) {
@@ -572,7 +579,6 @@ attn_kernel(const __grid_constant__ CUtensorMap mx2, const __grid_constant__ CUt
                 if (lane == 0) mbar_arrive_remote(leader_bar);
                 ATT_PROF_ADD2(17 + pslot, pf)
             };
-            static_assert(NYS % 3 == 0 && NZS % 3 == 0, "a converter warp always meets the same ring slots");
             bool got = true;
             uint32_t it = 0, ul = 0;       // it: blocks seen so far (the ring counter of both streams)
             ATT_PROF_T0
@@ -584,7 +590,7 @@ attn_kernel(const __grid_constant__ CUtensorMap mx2, const __grid_constant__ CUt
                     done(x_conv_l);
                 }
                 for (int c = 0; c < d.nb; c++, it++) {
-                    if ((int)(it % 3) != turn) continue;
+                    if ((int)(it % kGroups) != turn) continue;
                     if (kind == 0) {
                         const int s = it % NYS;
                         if (!(got = wait_full(y_full0 + 8u * s, (it / NYS) & 1))) break;
@@ -593,7 +599,7 @@ attn_kernel(const __grid_constant__ CUtensorMap mx2, const __grid_constant__ CUt
                         if (prof_on && s == 0) prof_acc[16] += tc0 - tstamp[9];
 #endif
                         uint8_t* st = smem_gen + Cfg::kXBytes + s * Cfg::kYStage;
-                        for (int w = 0; w < NX; w++) convert(st + w * 2 * Cfg::kYTile, kbh * 256, Cfg::kYTile, lane, 32);
+                        convert(st + job * 2 * Cfg::kYTile, kbh * 256, Cfg::kYTile, lane, 32);
 #ifdef ZNN_ATTN_PROFILE
                         if (prof_on && s == 0) prof_acc[24] += clock64() - tc0;
 #endif
