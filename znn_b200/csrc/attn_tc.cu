@@ -88,7 +88,11 @@ struct AttnCfg {
     static constexpr int kStageRows = NX == 2 ? 8 : ZNN_ATT_STAGE_ROWS1;
     static constexpr int kStageWarpBytes = kStageRows * 144;
     static constexpr int kStageOff = kBarOff + 512 + kExchBytes;
-    static constexpr int kSmemBytes = kBarOff + 1024 /*alignment*/ + 512 /*barriers*/ + kExchBytes + kAttXfWarps * kStageWarpBytes;
+    // dK and dV: the block's per-column statistics (log-sum-exp, D), fetched one column per lane ahead of the block and
+    // passed round the warp here
+    static constexpr int kColStatOff = kStageOff + kAttXfWarps * kStageWarpBytes;
+    static constexpr int kColStatBytes = (MODE == ATT_BWD_K || MODE == ATT_BWD_V) ? kAttXfWarps * 256 : 0;
+    static constexpr int kSmemBytes = kBarOff + 1024 /*alignment*/ + 512 /*barriers*/ + kExchBytes + kAttXfWarps * kStageWarpBytes + kColStatBytes;
     static_assert(kSmemBytes <= 232448, "shared memory budget");
     // tensor-memory columns (512 allocated): X1 hi | X1 lo | S / W_hi [2] | then, forward and dV: W_lo [2], accumulator [2];
     // dQ and dK: dP [2], W_lo [1], accumulator [1]
@@ -648,6 +652,7 @@ attn_kernel(const __grid_constant__ CUtensorMap mx2, const __grid_constant__ CUt
             // (coalesced: lane l fetches float4 l % 8 of rows l / 8, l / 8 + 4, ..., i.e. four whole 128-byte rows per
             // instruction; the rows change hands in shared memory inside store_x1)
             float4* const stage = reinterpret_cast<float4*>(smem_gen + Cfg::kStageOff + (warp - kAttXfWarp0) * Cfg::kStageWarpBytes);
+            float* const colstat = reinterpret_cast<float*>(smem_gen + Cfg::kColStatOff + (warp - kAttXfWarp0) * 256);
             constexpr int CH = Cfg::kStageRows;
             const int lr = lane >> 3, lc = lane & 7;
             auto load_x1 = [&](int un, float4 (&xr)[8]) {
@@ -739,6 +744,13 @@ attn_kernel(const __grid_constant__ CUtensorMap mx2, const __grid_constant__ CUt
                     const bool next_x1 = got && c == d.nb - 1 && unit_of(k + 1) >= 0;
                     float4 xn[8];
                     if (next_x1) load_x1(unit_of(k + 1), xn);
+                    // dK, dV: this lane's column of the block's statistics, asked for before the wait so that the answer is
+                    // there when the scores are
+                    float st_l = 0.0f, st_d = 0.0f;
+                    if ((MODE == ATT_BWD_K || MODE == ATT_BWD_V) && col0 + lane < p.T) {
+                        st_l = p.lse[stat_off + col0 + lane];
+                        if (MODE == ATT_BWD_K) st_d = p.dvec[stat_off + col0 + lane];
+                    }
                     if (got) got = wait_bar(s_full0 + 8u * buf, (g >> 1) & 1, 9);
                     if (!got) {
                         if (MODE == ATT_FWD) pair_sync();
@@ -785,11 +797,12 @@ attn_kernel(const __grid_constant__ CUtensorMap mx2, const __grid_constant__ CUt
                         m_run = mx;
                     } else if (MODE == ATT_BWD_V) {
                         // W = P^T: rows are keys, columns queries; statistics per column
+                        colstat[lane] = st_l;
+                        __syncwarp();
 #pragma unroll
                         for (int j4 = 0; j4 < 8; j4++) {
                             const int qc = col0 + 4 * j4;
-                            float4 l4 = make_float4(0.f, 0.f, 0.f, 0.f);
-                            if (qc < p.T) l4 = *reinterpret_cast<const float4*>(p.lse + stat_off + qc);
+                            const float4 l4 = *reinterpret_cast<const float4*>(colstat + 4 * j4);
                             const float ls[4] = {l4.x, l4.y, l4.z, l4.w};
 #pragma unroll
                             for (int e = 0; e < 4; e++) {
@@ -810,14 +823,14 @@ attn_kernel(const __grid_constant__ CUtensorMap mx2, const __grid_constant__ CUt
                                 split_hi_lo((pv * (dp[j] - d_r)) * p.scale, hi[j], lo[j]);
                             }
                         } else {   // ATT_BWD_K
+                            colstat[lane] = st_l;
+                            colstat[32 + lane] = st_d;
+                            __syncwarp();
 #pragma unroll
                             for (int j4 = 0; j4 < 8; j4++) {
                                 const int qc = col0 + 4 * j4;
-                                float4 l4 = make_float4(0.f, 0.f, 0.f, 0.f), d4 = l4;
-                                if (qc < p.T) {
-                                    l4 = *reinterpret_cast<const float4*>(p.lse + stat_off + qc);
-                                    d4 = *reinterpret_cast<const float4*>(p.dvec + stat_off + qc);
-                                }
+                                const float4 l4 = *reinterpret_cast<const float4*>(colstat + 4 * j4);
+                                const float4 d4 = *reinterpret_cast<const float4*>(colstat + 32 + 4 * j4);
                                 const float ls[4] = {l4.x, l4.y, l4.z, l4.w}, dd[4] = {d4.x, d4.y, d4.z, d4.w};
 #pragma unroll
                                 for (int e = 0; e < 4; e++) {
