@@ -765,8 +765,21 @@ attn_kernel(const __grid_constant__ CUtensorMap mx2, const __grid_constant__ CUt
                     const uint32_t tl = tmem_base + lane_sel + kColWlo + 64u * wbuf + col_sel;
                     const uint32_t tdp = tmem_base + lane_sel + kColDp + 64u * buf + col_sel;
                     float corr = 1.0f;
-                    float s[32];
-                    tmem_ld_32x32(ts, s);
+                    float s[32], dp[32];
+                    if (NX == 2) {
+                        // both loads in flight, one wait
+                        uint32_t rs[32], rd[32];
+                        tmem_ld_32x32_issue(ts, rs);
+                        tmem_ld_32x32_issue(tdp, rd);
+                        tmem_ld_wait2(rs, rd);
+#pragma unroll
+                        for (int j = 0; j < 32; j++) {
+                            s[j] = __uint_as_float(rs[j]);
+                            dp[j] = __uint_as_float(rd[j]);
+                        }
+                    } else {
+                        tmem_ld_32x32(ts, s);
+                    }
                     ATT_PROF_ADD2(18, pt)
                     uint32_t hi[32], lo[32];
                     if (MODE == ATT_FWD) {
@@ -813,8 +826,6 @@ attn_kernel(const __grid_constant__ CUtensorMap mx2, const __grid_constant__ CUt
                             }
                         }
                     } else {
-                        float dp[32];
-                        tmem_ld_32x32(tdp, dp);
                         if (MODE == ATT_BWD_Q) {
 #pragma unroll
                             for (int j = 0; j < 32; j++) {
