@@ -277,7 +277,11 @@ attn_kernel(const __grid_constant__ CUtensorMap mx2, const __grid_constant__ CUt
         if (aborted) {
         } else if (warp == 0) {
             // ---------------- TMA producer ----------------
-            if (lane == 0) {
+            // Two lanes, one stream each: lane 0 fetches the row operand of dQ / dK and the Y tiles, lane 1 the Z tiles.  A
+            // Z slot is freed late in a block's life (after its second product); in one thread that wait held back the
+            // next Y tile, the one the issuer needs first.
+            if (lane < 2) {
+                const bool do_y = lane == 0, do_z = lane == 1;
                 bool ok = true;
                 uint32_t it = 0, ul = 0;
                 ATT_PROF_T0
@@ -287,7 +291,7 @@ attn_kernel(const __grid_constant__ CUtensorMap mx2, const __grid_constant__ CUt
                     // remainders) come by TMA, and the bytes of both CTAs are counted by the leader's "conv" barrier,
                     // the one the MMA issuer waits on: no converter, no proxy fence, one hop less per tile
                     const bool pl = p.planes != 0;
-                    if (NX == 2) {
+                    if (NX == 2 && do_y) {
                         // the shared-memory row operand of this unit, once the previous unit's first products no longer read it
                         if (!ATT_PROF_WAIT(13, mbar_wait_bounded(x_empty, (ul & 1) ^ 1, p.wait_limit))) { ok = false; break; }
                         const int xrow = d.row0 + cta_rank * kRowsPerCta;
@@ -313,7 +317,7 @@ attn_kernel(const __grid_constant__ CUtensorMap mx2, const __grid_constant__ CUt
                     }
                     for (int c = 0; c < d.nb && ok; c++, it++) {
                         const int col0 = (d.cb0 + c) * kColBlock;
-                        {   // Y: this CTA's 32 of the block's 64 columns, K-major
+                        if (do_y) {   // Y: this CTA's 32 of the block's 64 columns, K-major
                             const int s = it % NYS;
                             if (!ATT_PROF_WAIT(13, mbar_wait_bounded(y_empty0 + 8u * s, ((it / NYS) & 1) ^ 1, p.wait_limit))) { ok = false; break; }
 #ifdef ZNN_ATTN_PROFILE
@@ -358,7 +362,7 @@ attn_kernel(const __grid_constant__ CUtensorMap mx2, const __grid_constant__ CUt
                             if (prof_on && s == 0) tstamp[9] = clock64();
 #endif
                         }
-                        {   // Z: the block's 64 contraction rows x this CTA's 32 output columns, MN-major
+                        if (do_z) {   // Z: the block's 64 contraction rows x this CTA's 32 output columns, MN-major
                             const int s = it % NZS;
                             if (!ATT_PROF_WAIT(13, mbar_wait_bounded(z_empty0 + 8u * s, ((it / NZS) & 1) ^ 1, p.wait_limit))) { ok = false; break; }
                             const uint32_t st = z_base + s * Cfg::kZStage;
