@@ -128,3 +128,23 @@ def test_precomputed_remainder_planes_equal_in_kernel_conversion(ops, layout):
         lib().call("znn_debug_set_attn_planes", 0)
     for a, b in zip(res[0], res[1]):
         np.testing.assert_array_equal(a, b)
+
+
+def test_issue_order_of_the_second_products_does_not_change_a_bit(ops):
+    """By default the MMA issuer issues a block's second product as soon as its inputs are there, possibly before the
+    next block's first product; znn_debug_set_attn_issue_order(1) keeps the fixed order.  The two products of different
+    blocks use different buffers, so every output is bit-identical."""
+    from znn_b200._lib import lib
+    r = np.random.default_rng(78)
+    B, nh, T, hs = 2, 5, 1000, 64
+    Q, K, V, dO = (r.standard_normal((B, T, nh, hs), np.float32) for _ in range(4))
+    res = []
+    try:
+        for in_order in (1, 0):
+            lib().call("znn_debug_set_attn_issue_order", in_order)
+            O, LSE = ops.attn_fwd(Q, K, V, 0.125, "bthd")
+            res.append((O, LSE) + tuple(ops.attn_bwd(Q, K, V, O, dO, LSE, 0.125, "bthd")))
+    finally:
+        lib().call("znn_debug_set_attn_issue_order", 0)
+    for a, b in zip(res[0], res[1]):
+        np.testing.assert_array_equal(a, b)

@@ -15,9 +15,10 @@
 //   dV        rows = keys,    columns = queries  S^T = K.Q^T                 P^T                      dV += P^T.dO
 //
 // Every product is 3xTF32 (lo*hi + hi*lo + hi*hi of a hi/lo split, as in the GEMM kernels).
-//  * The row operand X1 of the first product (Q or K) lives in TENSOR MEMORY for the whole unit: the transform threads
-//    read their rows from global memory, split them and store hi and lo with tcgen05.st; the product takes its A operand
-//    from there.  (With A in shared memory a 256 x 64 x 8 instruction reads 4 KB of A per SM for 44 cycles of math, which
+//  * The row operand X1 of the first product (Q or K) lives in TENSOR MEMORY for the whole unit: the transform warps
+//    fetch their rows from global memory (whole 128-byte lines per access, handed to the thread that owns the row
+//    through a small shared-memory stage), split them and store hi and lo with tcgen05.st; the product takes its A
+//    operand from there.  (With A in shared memory a 256 x 64 x 8 instruction reads 4 KB of A per SM for 44 cycles of math, which
 //    saturates the shared-memory port and starves TMA and the converter warps: measured.)
 //  * The second row operand of dQ / dK (dO or V) does not fit in tensor memory beside the rest and stays in shared
 //    memory (TMA + converter warps), as do all column operands: Y (K-major, for the first products) and Z (MN-major,
@@ -27,6 +28,11 @@
 //    again reads from tensor memory.  Each block's second product starts a fresh accumulator that the transform warps
 //    add into fp32 registers (round to nearest; the tensor core's own accumulation truncates), rescaled in the forward
 //    when the running row maximum moves.  Two S buffers let block c+1's first products run while block c is transformed.
+//  * The MMA issuer issues P1(g) (first products of block g) and P2(g - 1) in whichever order their inputs arrive: while
+//    it waits for block g's tile it issues the previous block's second product as soon as the transform warps have
+//    handed it over, so a late tile does not hold back work that is ready (the two use different score buffers).
+//  * Between units the pipeline drains; what shortens that: the next unit's rows are prefetched during the last block
+//    and stored to tensor memory right after that block's hand-off, and the unit's result rows leave as whole lines.
 //
 // Causal structure: forward and dQ walk the key blocks 0 .. diagonal; dK and dV walk the query blocks diagonal .. end;
 // elements above the diagonal are masked by index (the reference adds -1e9, which makes exp exactly 0).
