@@ -247,12 +247,12 @@ attn_kernel(const __grid_constant__ CUtensorMap mx2, const __grid_constant__ CUt
         mbar_init(x1_ready, kAttXfWarps * 2);
         for (int s = 0; s < NYS; s++) {
             mbar_init(y_full0 + 8u * s, 1);
-            mbar_init(y_conv0 + 8u * s, p.planes ? 1 : 2 * NX);      // one converter warp per tile and CTA
+            mbar_init(y_conv0 + 8u * s, p.planes ? 1 : 2 * NX * NX);   // per CTA: one warp per tile (forward, dV), two per tile (dQ, dK)
             mbar_init(y_empty0 + 8u * s, 1);
         }
         for (int s = 0; s < NZS; s++) {
             mbar_init(z_full0 + 8u * s, 1);
-            mbar_init(z_conv0 + 8u * s, p.planes ? 1 : 2);
+            mbar_init(z_conv0 + 8u * s, p.planes ? 1 : 2 * NX);
             mbar_init(z_empty0 + 8u * s, 1);
         }
         for (int b = 0; b < 2; b++) {
@@ -551,13 +551,18 @@ attn_kernel(const __grid_constant__ CUtensorMap mx2, const __grid_constant__ CUt
             // ---------------- converters: lo = x - (x with the 13 low mantissa bits cleared), next to each landed tile ----------------
             // Handing a converted tile to the tensor core (proxy fence, barrier arrival) costs a warp 1500-2000 cycles per
             // 8 KB tile here (measured; 16 cycles in a kernel that does nothing else), more than the conversion itself, and
-            // the time grows with the bytes the warp touched.  Each of the six warps therefore works alone on one 8 KB tile
-            // at a time: forward and dV (tiles Y, Z per block) warps 0, 2, 4 take the Y tiles of blocks 0, 1, 2 (mod 3) and
-            // warps 1, 3, 5 the Z tiles; dQ and dK (tiles Y1, Y2, Z per block) warps 0-2 take the three tiles of the even
-            // blocks and warps 3-5 those of the odd blocks.  The shared-memory row operand (dQ, dK) is converted by all six.
+            // the time grows with the bytes the warp touched.  The six warps therefore work apart, each on a small piece:
+            // forward and dV (tiles Y, Z per block) warps 0, 2, 4 take the Y tiles of blocks 0, 1, 2 (mod 3) and warps
+            // 1, 3, 5 the Z tiles; dQ and dK (tiles Y1, Y2, Z per block) two warps take half a tile each of every block.
+            // Either way a warp meets every ring slot it works on in turn (three stages, three groups; or every block), so
+            // when it waits for a slot's tile it has itself seen the slot's previous tile land: the parity wait cannot
+            // mistake an older phase for the new one.  The shared-memory row operand (dQ, dK) is converted by all six.
             const int cw = warp - kAttConvWarp0;                               // 0 .. 5
-            constexpr int kJobs = NX + 1, kGroups = kAttConvWarps / kJobs;     // tiles per block; groups of warps taking blocks in turn
-            const int job = cw % kJobs, turn = cw / kJobs;
+            constexpr int kJobs = NX + 1;                                      // tiles per block
+            constexpr int kSplit = NX;                                         // warps per tile
+            constexpr int kGroups = kAttConvWarps / (kJobs * kSplit);          // groups of warps taking blocks in turn: 3 or 1
+            static_assert(NYS % kGroups == 0 && NZS % kGroups == 0, "a converter warp always meets the same ring slots");
+            const int job = cw % kJobs, sub = (cw / kJobs) % kSplit, turn = cw / (kJobs * kSplit);
             const int kind = job == NX ? 1 : 0;                                // Y (job = which of the NX tiles) or Z
             const int ct = threadIdx.x - 32 * kAttConvWarp0;                   // 0 .. 191 over all converter warps
             const uint32_t x_conv_l = mapa_shared(x_conv, 0), y_conv_l0 = mapa_shared(y_conv0, 0), z_conv_l0 = mapa_shared(z_conv0, 0);
@@ -613,7 +618,7 @@ attn_kernel(const __grid_constant__ CUtensorMap mx2, const __grid_constant__ CUt
                         if (prof_on && s == 0) prof_acc[16] += tc0 - tstamp[9];
 #endif
                         uint8_t* st = smem_gen + Cfg::kXBytes + s * Cfg::kYStage;
-                        convert(st + job * 2 * Cfg::kYTile, kbh * 256, Cfg::kYTile, lane, 32);
+                        convert(st + job * 2 * Cfg::kYTile + sub * (kbh * 4096 / kSplit), kbh * 256 / kSplit, Cfg::kYTile, lane, 32);
 #ifdef ZNN_ATTN_PROFILE
                         if (prof_on && s == 0) prof_acc[24] += clock64() - tc0;
 #endif
@@ -625,7 +630,7 @@ attn_kernel(const __grid_constant__ CUtensorMap mx2, const __grid_constant__ CUt
                         const int s = it % NZS;
                         if (!(got = wait_full(z_full0 + 8u * s, (it / NZS) & 1))) break;
                         uint8_t* st = smem_gen + Cfg::kXBytes + NYS * Cfg::kYStage + s * Cfg::kZStage;
-                        convert(st, 512, Cfg::kZTile, lane, 32);
+                        convert(st + sub * (8192 / kSplit), 512 / kSplit, Cfg::kZTile, lane, 32);
                         done(z_conv_l0 + 8u * s);
                     }
                 }
