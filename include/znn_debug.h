@@ -56,6 +56,11 @@ int znn_debug_set_attn_planes(int enable);
  * second product of block g - 1, ... whatever arrives first.  Same instructions on the same buffers either way (results
  * are bit-identical); the switch exists for A/B timing. */
 int znn_debug_set_attn_issue_order(int in_order);
+/* Fused attention, per host thread: 1 (default) = the work units (256 rows of one batch x head slice each) are dealt to
+ * the CTA pairs by a table made on the host once per problem shape (longest unit to the least loaded pair); 0 = by the
+ * kernel's own arithmetic (units dealt round by round in alternating direction).  Every unit is computed by one pair
+ * with the same arithmetic either way: results are bit-identical. */
+int znn_debug_set_attn_schedule(int enable);
 
 /* Conv2D path of the calling host thread: 0 (default) = layers with Ci*KH*KW >= 64 taps, at most 64 output channels and at
  * least 4096 output pixels run as implicit-im2col GEMMs on the tensor cores; 1 = never (direct kernels and the explicit

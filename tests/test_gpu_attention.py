@@ -148,3 +148,23 @@ def test_issue_order_of_the_second_products_does_not_change_a_bit(ops):
         lib().call("znn_debug_set_attn_issue_order", 0)
     for a, b in zip(res[0], res[1]):
         np.testing.assert_array_equal(a, b)
+
+
+def test_unit_schedule_table_does_not_change_a_bit(ops):
+    """The work units are dealt to the CTA pairs by a host-made table (longest unit to the least loaded pair) or, with
+    znn_debug_set_attn_schedule(0), by the kernel's own arithmetic.  Each unit is computed by exactly one pair with the
+    same arithmetic: outputs are bit-identical.  96 units of 1-4 row blocks on 74 pairs: several units per pair."""
+    from znn_b200._lib import lib
+    r = np.random.default_rng(79)
+    B, nh, T, hs = 4, 12, 520, 64
+    Q, K, V, dO = (r.standard_normal((B, T, nh, hs), np.float32) for _ in range(4))
+    res = []
+    try:
+        for sched in (0, 1):
+            lib().call("znn_debug_set_attn_schedule", sched)
+            O, LSE = ops.attn_fwd(Q, K, V, 0.125, "bthd")
+            res.append((O, LSE) + tuple(ops.attn_bwd(Q, K, V, O, dO, LSE, 0.125, "bthd")))
+    finally:
+        lib().call("znn_debug_set_attn_schedule", 1)
+    for a, b in zip(res[0], res[1]):
+        np.testing.assert_array_equal(a, b)

@@ -43,6 +43,12 @@
 #include <math.h>
 #include <math_constants.h>
 
+#include <algorithm>
+#include <map>
+#include <mutex>
+#include <tuple>
+#include <vector>
+
 namespace znn {
 
 enum { ATT_FWD = 0, ATT_BWD_Q = 1, ATT_BWD_K = 2, ATT_BWD_V = 3 };
@@ -62,12 +68,15 @@ struct AttnParams {
                                   // tensor maps: TMA fills both halves of a stage and signals the MMA issuer's barrier directly
     int* status;
     int issue_in_order;           // 1: the MMA issuer keeps the fixed order P1(g), P2(g-1), P1(g+1), ... (A/B switch)
+    const int* sched;             // [pairs][sched_k] the units of every CTA pair in the order it takes them, -1 after the last; or NULL
+    int sched_k;                  // entries per pair (at most kAttSchedMax)
     unsigned long long wait_limit;
 };
 
 constexpr int kAttThreads = 512;   // warp 0 TMA, warp 1 MMA + TMEM, warps 2-7 converters, warps 8-15 transform
 constexpr int kAttConvWarps = 6, kAttConvWarp0 = 2, kAttXfWarp0 = 8, kAttXfWarps = 8;
 constexpr int kRowsPerCta = 128, kColBlock = 64;
+constexpr int kAttSchedMax = 32;   // units per CTA pair a schedule table may hold (a copy of the pair's row lives in shared memory)
 
 template <int MODE>
 struct AttnCfg {
@@ -223,10 +232,15 @@ attn_kernel(const __grid_constant__ CUtensorMap mx2, const __grid_constant__ CUt
     const int pair = blockIdx.x >> 1, npairs = gridDim.x >> 1;
     const int total_units = p.nslices * p.nrb;
     const int kbh = p.hs >> 5;                    // 32-float k-blocks across the head dimension (1 or 2)
-    // The k-th unit of this CTA pair, or -1.  Units are sorted dearest first; round k deals units k * npairs .. to the
-    // pairs in alternating direction, so that a pair that got a dear unit in one round gets a cheap one in the next
-    // (60 -> 56 blocks for the busiest pair at 96 slices x 1024 positions, against a mean of 51.9).
+    // The k-th unit of this CTA pair, or -1.  Units are numbered dearest first.  With a schedule table (made on the host:
+    // every unit, dearest first, goes to the pair with the least work so far) the pair's row of the table is read from
+    // shared memory; without one, round k deals units k * npairs .. to the pairs in alternating direction, so that a pair
+    // that got a dear unit in one round gets a cheap one in the next.  At 96 slices x 1024 positions the busiest pair
+    // then has 56 blocks in 5 or 6 units, with the table 52-53, against a mean of 51.9.
+    const int* const sched_s = reinterpret_cast<const int*>(smem_gen + Cfg::kBarOff + 256);   // kAttSchedMax entries
+    const bool have_sched = p.sched != nullptr;
     auto unit_of = [&](int k) -> int {
+        if (have_sched) return k < p.sched_k ? sched_s[k] : -1;
         const int u = k * npairs + ((k & 1) ? npairs - 1 - pair : pair);
         return u < total_units ? u : -1;
     };
@@ -239,8 +253,13 @@ attn_kernel(const __grid_constant__ CUtensorMap mx2, const __grid_constant__ CUt
     for (int i = 0; i < 32; i++) prof_acc[i] = 0;
 #endif
 
+    if (have_sched && threadIdx.x >= 32 && threadIdx.x < 32 + kAttSchedMax) {
+        const int k = threadIdx.x - 32;
+        reinterpret_cast<int*>(smem_gen + Cfg::kBarOff + 256)[k] = k < p.sched_k ? p.sched[(size_t)pair * p.sched_k + k] : -1;
+    }
     if (threadIdx.x == 0) {
-        static_assert(8 * (4 + 3 * NYS + 3 * NZS + 6) + 8 <= 512, "barrier block overflows");
+        static_assert(8 * (4 + 3 * NYS + 3 * NZS + 6) + 8 <= 256, "barrier block overflows into the schedule row");
+        static_assert(256 + 4 * kAttSchedMax <= 512 - 128, "schedule row overflows into the profile stamps");
         mbar_init(x_full, 1);
         mbar_init(x_conv, p.planes ? 1 : kAttConvWarps * 2);   // planes: the leader's producer arrives, TMA brings the bytes
         mbar_init(x_empty, 1);
@@ -1048,6 +1067,7 @@ static int make_attn_map(CUtensorMap* tm, const float* X, const AttnLayout& L, i
 }
 
 static thread_local int t_attn_in_order = 0;
+static thread_local int t_attn_sched = 1;     // 0: no schedule tables (units dealt to the pairs by arithmetic)
 unsigned long long tc_wait_limit();
 
 int attn_profile_read(long long* out32)
@@ -1059,6 +1079,69 @@ int attn_profile_read(long long* out32)
 }
 
 // X2l, Y1l, Y2l, Zl: the remainder planes of X2, Y1, Y2, Z (same layout), or all NULL: the kernel then converts in place
+// Schedule table of one problem shape on one device: units (numbered dearest first, as attn_unit counts them) dealt to the
+// CTA pairs by "longest job to the least loaded pair"; a unit costs its blocks plus about two blocks' worth of time for
+// the change of unit.  Tables are made once per shape and stay on the device (a few hundred bytes each); a shape first
+// met while the stream is being captured runs without one (the allocation and the copy are not stream operations).
+struct AttnSchedKey {
+    int dev, rows_first, nslices, nrb, ncb, T, pairs;
+    bool operator<(const AttnSchedKey& o) const
+    {
+        return std::tie(dev, rows_first, nslices, nrb, ncb, T, pairs) < std::tie(o.dev, o.rows_first, o.nslices, o.nrb, o.ncb, o.T, o.pairs);
+    }
+};
+struct AttnSched { const int* table; int k; };
+
+static AttnSched attn_schedule(int dev, bool rows_first, const AttnParams& p, int pairs)
+{
+    static std::mutex mu;
+    static std::map<AttnSchedKey, AttnSched> cache;
+    const AttnSchedKey key = {dev, rows_first ? 1 : 0, p.nslices, p.nrb, p.ncb, p.T, pairs};
+    std::lock_guard<std::mutex> lock(mu);
+    auto it = cache.find(key);
+    if (it != cache.end()) return it->second;
+    AttnSched none = {nullptr, 0};
+    cudaStreamCaptureStatus cap = cudaStreamCaptureStatusNone;
+    if (cudaStreamIsCapturing(stream(), &cap) != cudaSuccess || cap != cudaStreamCaptureStatusNone) {
+        cudaGetLastError();
+        return none;
+    }
+    const long total = (long)p.nslices * p.nrb;
+    std::vector<std::vector<int>> rows(pairs);
+    std::vector<double> load(pairs, 0.0);
+    for (long u = 0; u < total; u++) {
+        const int rbi = (int)(u / p.nslices);
+        int nb;
+        if (rows_first) {            // forward, dQ: rows are queries, the blocks run up to the diagonal (attn_unit)
+            const int rb = p.nrb - 1 - rbi;
+            const int last = std::min(p.T, rb * 256 + 256);
+            nb = (last + kColBlock - 1) / kColBlock;
+        } else {
+            nb = p.ncb - rbi * 256 / kColBlock;
+        }
+        int best = 0;
+        for (int i = 1; i < pairs; i++)
+            if (load[i] < load[best]) best = i;
+        load[best] += nb + 2.0;
+        rows[best].push_back((int)u);
+    }
+    size_t k = 0;
+    for (const auto& r : rows) k = std::max(k, r.size());
+    if (k > (size_t)kAttSchedMax) { cache[key] = none; return none; }
+    std::vector<int> flat((size_t)pairs * k, -1);
+    for (int i = 0; i < pairs; i++) std::copy(rows[i].begin(), rows[i].end(), flat.begin() + (size_t)i * k);
+    int* d = nullptr;
+    if (cudaMalloc(&d, flat.size() * sizeof(int)) != cudaSuccess ||
+        cudaMemcpy(d, flat.data(), flat.size() * sizeof(int), cudaMemcpyHostToDevice) != cudaSuccess) {
+        cudaGetLastError();
+        if (d) cudaFree(d);
+        return none;       // not cached: the next call tries again
+    }
+    const AttnSched made = {d, (int)k};
+    cache[key] = made;
+    return made;
+}
+
 template <int MODE>
 static int launch_attn(const float* X1, const float* X2, const float* Y1, const float* Y2, const float* Z, const AttnLayout& L,
                        AttnParams p, const float* X2l = nullptr, const float* Y1l = nullptr, const float* Y2l = nullptr,
@@ -1113,6 +1196,11 @@ static int launch_attn(const float* X1, const float* X2, const float* Y1, const 
     const long units = (long)p.nslices * p.nrb;
     const long pairs = units < pairs_by_device[dev] ? units : pairs_by_device[dev];
     cfg.gridDim = dim3((unsigned)(2 * pairs), 1, 1);
+    if (units > pairs && t_attn_sched) {       // (with a pair per unit there is nothing to deal)
+        const AttnSched sc = attn_schedule(dev, MODE == ATT_FWD || MODE == ATT_BWD_Q, p, (int)pairs);
+        p.sched = sc.table;
+        p.sched_k = sc.k;
+    }
     ZNN_CUDA_OK(cudaLaunchKernelEx(&cfg, kern, mx2, my1, my2, mz, mx2l, my1l, my2l, mzl, p));
     count_launch();
     if (inject_launch_failure()) return fail(ZNN_ERR_CUDA, "launch of the attention kernel failed: injected failure (znn_debug_fail_after)");
@@ -1152,6 +1240,8 @@ static AttnParams attn_params(const AttnLayout& L, float scale)
     p.accumulate = 0;
     p.planes = 0;
     p.issue_in_order = t_attn_in_order;
+    p.sched = nullptr;
+    p.sched_k = 0;
     p.status = device_status_word();
     p.wait_limit = tc_wait_limit();
     return p;
@@ -1191,6 +1281,12 @@ extern "C" {
 int znn_debug_set_attn_planes(int enable)
 {
     attn_set_planes(enable);
+    return ZNN_OK;
+}
+
+int znn_debug_set_attn_schedule(int enable)
+{
+    t_attn_sched = enable ? 1 : 0;
     return ZNN_OK;
 }
 
