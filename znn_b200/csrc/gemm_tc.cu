@@ -1051,12 +1051,14 @@ gemm3x_direct_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_cons
                 if ((int)(it % kConvGroups) != group) continue;
                 const int s = it % S;
                 const uint32_t ph = (it / S) & 1;
-                if (lane == 0) {
-                    got = ZNN_PROF_WAIT(mbar_wait_bounded(full_bar(s), ph, p.wait_limit));
-                    if (!got) record_expiry(2, 1, u, it, cta_rank, pair);
+                // every lane polls and the warp votes: a wait that passes at once costs 90 cycles this way, 240 with one
+                // polling lane and a broadcast of its answer (measured), and the hand-off of a tile is this role's latency
+                got = ZNN_PROF_WAIT(mbar_wait_bounded_tight(full_bar(s), ph, p.wait_limit));
+                got = __all_sync(0xffffffffu, got);
+                if (!got) {
+                    if (lane == 0) record_expiry(2, 1, u, it, cta_rank, pair);
+                    break;
                 }
-                got = __shfl_sync(0xffffffffu, (int)got, 0) != 0;
-                if (!got) break;
                 uint8_t* st = smem_gen + s * Cfg::kStageBytes;
                 // hi = x with the 13 low mantissa bits cleared (exactly a TF32 value); lo = x - hi is exact in
                 // fp32 and at most 2^-10 |x|; the tensor core drops lo's own low bits, a 2^-21 relative effect
@@ -1120,12 +1122,12 @@ gemm3x_direct_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_cons
             for (int i = 0; i < CPT; i++) acc[i] = 0.0f;
             for (int c = 0; c < d.nchunks; c++, cc++) {
                 const int buf = cc & 1;
-                if (lane == 0) {
-                    got = ZNN_PROF_WAIT(mbar_wait_bounded(acc_full_bar(buf), (cc >> 1) & 1, p.wait_limit));
-                    if (!got) record_expiry(3, 4, u, cc, cta_rank, pair);
+                got = ZNN_PROF_WAIT(mbar_wait_bounded_tight(acc_full_bar(buf), (cc >> 1) & 1, p.wait_limit));
+                got = __all_sync(0xffffffffu, got);
+                if (!got) {
+                    if (lane == 0) record_expiry(3, 4, u, cc, cta_rank, pair);
+                    break;
                 }
-                got = __shfl_sync(0xffffffffu, (int)got, 0) != 0;
-                if (!got) break;
                 tc_fence_after();
                 const uint32_t t0 = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(buf * BN + half * CPT);
 #pragma unroll
