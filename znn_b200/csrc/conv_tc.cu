@@ -280,8 +280,7 @@ __global__ void __launch_bounds__(kCvThreads, 1) conv_tc_kernel(const ConvTcPara
             CV_PROF(1)
             const int s = it % S;
             bool got = true;
-            if (lane == 0) got = mbar_wait_bounded(empty_bar(s), (uint32_t)(((it / S) & 1) ^ 1), p.wait_limit);
-            got = __shfl_sync(0xffffffffu, (int)got, 0) != 0;
+            got = __all_sync(0xffffffffu, mbar_wait_bounded_tight(empty_bar(s), (uint32_t)(((it / S) & 1) ^ 1), p.wait_limit));   // every lane polls, the warp votes
             if (!got) { ok = false; break; }
             CV_PROF(2)
             uint8_t* const st = smem_gen + s * kStageBytes;
@@ -357,13 +356,11 @@ __global__ void __launch_bounds__(kCvThreads, 1) conv_tc_kernel(const ConvTcPara
                 CV_PROF(9)
                 if (kb % kCvChunk == 0) {
                     // the drain of the chunk that used this accumulator two chunks ago
-                    if (lane == 0) got = mbar_wait_bounded(acc_empty_bar(buf), (uint32_t)(((cc >> 1) & 1) ^ 1), p.wait_limit);
-                    got = __shfl_sync(0xffffffffu, (int)got, 0) != 0;
+                    got = __all_sync(0xffffffffu, mbar_wait_bounded_tight(acc_empty_bar(buf), (uint32_t)(((cc >> 1) & 1) ^ 1), p.wait_limit));   // every lane polls, the warp votes
                     if (!got) { ok = false; break; }
                 }
                 CV_PROF(8)
-                if (lane == 0) got = mbar_wait_bounded(full_bar(s), (uint32_t)((it / S) & 1), p.wait_limit);
-                got = __shfl_sync(0xffffffffu, (int)got, 0) != 0;
+                got = __all_sync(0xffffffffu, mbar_wait_bounded_tight(full_bar(s), (uint32_t)((it / S) & 1), p.wait_limit));   // every lane polls, the warp votes
                 if (!got) { ok = false; break; }
                 CV_PROF(7)
                 tc_fence_after();
@@ -406,8 +403,7 @@ __global__ void __launch_bounds__(kCvThreads, 1) conv_tc_kernel(const ConvTcPara
                 const int buf = cc & 1;
                 bool got = true;
                 CV_PROF(13)
-                if (lane == 0) got = mbar_wait_bounded(acc_full_bar(buf), (uint32_t)((cc >> 1) & 1), p.wait_limit);
-                got = __shfl_sync(0xffffffffu, (int)got, 0) != 0;
+                got = __all_sync(0xffffffffu, mbar_wait_bounded_tight(acc_full_bar(buf), (uint32_t)((cc >> 1) & 1), p.wait_limit));   // every lane polls, the warp votes
                 if (!got) { ok = false; break; }
                 CV_PROF(11)
                 tc_fence_after();

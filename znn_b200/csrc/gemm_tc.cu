@@ -320,8 +320,7 @@ gemm3x_tf32_kernel(const __grid_constant__ CUtensorMap tm_a_hi, const __grid_con
         bool got = true;
         for (int c = 0; c < nchunks; c++) {
             const int buf = c & 1;
-            if (lane == 0) got = mbar_wait_bounded(acc_full_bar(buf), (c >> 1) & 1, p.wait_limit);
-            got = __shfl_sync(0xffffffffu, (int)got, 0) != 0;
+            got = __all_sync(0xffffffffu, mbar_wait_bounded_tight(acc_full_bar(buf), (c >> 1) & 1, p.wait_limit));   // every lane polls, the warp votes
             if (!got) break;
             tc_fence_after();
             const uint32_t t0 = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(buf * BN + half * CPT);
