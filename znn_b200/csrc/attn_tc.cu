@@ -480,17 +480,15 @@ attn_kernel(const __grid_constant__ CUtensorMap mx2, const __grid_constant__ CUt
                     if (p.issue_in_order) return warp_wait(bar, parity);
                     const uint64_t t0 = wait_clock();
                     for (uint32_t polls = 0;; polls++) {
-                        uint32_t st = 0;
-                        if (lane == 0) {
-                            st = mbar_test(bar, parity);
-                            if (!st && h < g) {
-                                const uint32_t zs = itz % NZS;
-                                if (mbar_test(w_ready0 + 8u * (h & 1), (h >> 1) & 1) && mbar_test(z_conv0 + 8u * zs, (itz / NZS) & 1)) st = 2;
-                            }
+                        // (every lane looks and the warp votes: no broadcast of one lane's answer)
+                        if (__all_sync(0xffffffffu, mbar_test(bar, parity))) return true;
+                        bool ready2 = false;
+                        if (h < g) {
+                            const uint32_t zs = itz % NZS;
+                            ready2 = __all_sync(0xffffffffu, mbar_test(w_ready0 + 8u * (h & 1), (h >> 1) & 1) &&
+                                                                 mbar_test(z_conv0 + 8u * zs, (itz / NZS) & 1));
                         }
-                        st = __shfl_sync(0xffffffffu, st, 0);
-                        if (st == 1) return true;
-                        if (st == 2) {
+                        if (ready2) {
                             if (!second(h)) return false;
                             h++;
                         } else if ((polls & 255u) == 255u && wait_clock() - t0 > p.wait_limit) return false;
