@@ -566,9 +566,8 @@ attn_kernel(const __grid_constant__ CUtensorMap mx2, const __grid_constant__ CUt
             }
         } else {
             // ---------------- converters: lo = x - (x with the 13 low mantissa bits cleared), next to each landed tile ----------------
-            // Handing a converted tile to the tensor core (proxy fence, barrier arrival) costs a warp 1500-2000 cycles per
-            // 8 KB tile here (measured; 16 cycles in a kernel that does nothing else), more than the conversion itself, and
-            // the time grows with the bytes the warp touched.  The six warps therefore work apart, each on a small piece:
+            // The conversion of a landed tile and its hand-off sit in the middle of the supply chain (producer -> TMA ->
+            // converter -> MMA issuer), so the six warps work apart, each on a small piece with its own hand-off:
             // forward and dV (tiles Y, Z per block) warps 0, 2, 4 take the Y tiles of blocks 0, 1, 2 (mod 3) and warps
             // 1, 3, 5 the Z tiles; dQ and dK (tiles Y1, Y2, Z per block) two warps take half a tile each of every block.
             // Either way a warp meets every ring slot it works on in turn (three stages, three groups; or every block), so
@@ -602,8 +601,9 @@ attn_kernel(const __grid_constant__ CUtensorMap mx2, const __grid_constant__ CUt
                     }
                 }
             };
-            // (every lane polls and the warp votes: 90 cycles for a wait that passes at once, against 240 for one polling
-            // lane and a broadcast of its answer; measured)
+            // Every lane polls and the warp votes.  With one polling lane and a broadcast of its answer a wait that passes at
+            // once cost 240 cycles against 90, and the warp stayed split through the conversion loop that follows (lane 0
+            // and the other 31 ran it one after the other: twice the time, both measured).
             auto wait_full = [&](uint32_t bar, uint32_t ph) -> bool {
                 const bool ok = ATT_PROF_WAIT(15 + pslot, mbar_wait_bounded_tight(bar, ph, p.wait_limit));
                 return __all_sync(0xffffffffu, ok);
