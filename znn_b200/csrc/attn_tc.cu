@@ -657,7 +657,7 @@ attn_kernel(const __grid_constant__ CUtensorMap mx2, const __grid_constant__ CUt
             ATT_PROF_END(14 + pslot)
         }
     } else {
-        asm volatile("setmaxnreg.inc.sync.aligned.u32 168;");
+        asm volatile("setmaxnreg.inc.sync.aligned.u32 176;");
         if (!aborted) {
             // ---------------- transform warps: two threads per row of this CTA's 128, 32 columns each ----------------
             // Warp w works on tensor-memory lanes 32 * (w & 3) .. + 31 (the quarter a warp may access) and on columns
