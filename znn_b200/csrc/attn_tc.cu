@@ -88,7 +88,7 @@ struct AttnCfg {
     static constexpr int kZTile = 64 * 32 * 4;                 // 64 contraction rows x this CTA's 32 output columns
     static constexpr int kZStage = 2 * kZTile;
 #ifndef ZNN_ATT_STAGES1
-#define ZNN_ATT_STAGES1 3      // three ring stages measured faster than six (161 against 175 us on the forward at 96 x 1024 x 64)
+#define ZNN_ATT_STAGES1 3      // ring stages of forward and dV; six measured no faster (and slower at 256 positions)
 #endif
     static constexpr int NYS = NX == 2 ? 3 : ZNN_ATT_STAGES1;
     static constexpr int NZS = NX == 2 ? 3 : ZNN_ATT_STAGES1;
@@ -247,7 +247,7 @@ attn_kernel(const __grid_constant__ CUtensorMap mx2, const __grid_constant__ CUt
 #ifdef ZNN_ATTN_PROFILE
     volatile long long* const tstamp = reinterpret_cast<volatile long long*>(smem_gen + Cfg::kBarOff + 512 - 128);   // 16 slots
     const bool prof_on = (pair == 0 && cta_rank == 0 && lane == 0 && (warp <= 3 || warp == kAttXfWarp0));
-    const int pslot = (warp == 3) ? 8 : 0;     // a Z converter warp reports in slots 22..25
+    const int pslot = (warp == 3) ? 8 : 0;     // the second converter warp (a Z tile; the second Y tile in dQ / dK) reports in slots 22..25
     long long prof_acc[32];      // in registers; written once at the end of the role
 #pragma unroll
     for (int i = 0; i < 32; i++) prof_acc[i] = 0;
@@ -420,8 +420,8 @@ attn_kernel(const __grid_constant__ CUtensorMap mx2, const __grid_constant__ CUt
             }
         } else if (warp == 1) {
             // ---------------- MMA issuer (leader CTA only) ----------------
-            // All 32 lanes run the loop and compute the (warp-uniform) descriptors; lane 0 polls the barriers and one
-            // elected lane issues the instructions.  Descriptors computed by a single diverged thread instead gave wrong
+            // All 32 lanes run the loop, poll the barriers and compute the (warp-uniform) descriptors; one elected lane
+            // issues the instructions.  Descriptors computed by a single diverged thread instead gave wrong
             // products once the instructions followed each other closely (measured: correct again with a pause
             // between them), and cost about twice the issue time.
             if (leader) {
