@@ -61,6 +61,12 @@ int znn_debug_set_attn_issue_order(int in_order);
  * kernel's own arithmetic (units dealt round by round in alternating direction).  Every unit is computed by one pair
  * with the same arithmetic either way: results are bit-identical. */
 int znn_debug_set_attn_schedule(int enable);
+/* Host arithmetic only (no device needed): how the fused attention kernels' work units of a problem with `nslices`
+ * (batch x head) slices of T positions are dealt to `pairs` CTA pairs.  rows_first = 1: forward and dQ (the blocks of a
+ * unit run up to the diagonal); 0: dK and dV.  table_form = 1: the host-made table; 0: the kernel's own dealing.
+ * units_per_pair[pairs] and blocks_per_pair[pairs] receive every pair's count of units and of 64-column blocks.
+ * ZNN_ERR_INVALID if the table would not hold every unit exactly once. */
+int znn_debug_attn_plan(int rows_first, int nslices, int T, int pairs, int table_form, int* units_per_pair, int* blocks_per_pair);
 
 /* Conv2D path of the calling host thread: 0 (default) = layers with Ci*KH*KW >= 64 taps, at most 64 output channels and at
  * least 4096 output pixels run as implicit-im2col GEMMs on the tensor cores; 1 = never (direct kernels and the explicit

@@ -1091,6 +1091,34 @@ struct AttnSchedKey {
 };
 struct AttnSched { const int* table; int k; };
 
+// blocks of unit u (units numbered dearest first, as attn_unit counts them)
+static int attn_unit_blocks(bool rows_first, int nslices, int nrb, int ncb, int T, long u)
+{
+    const int rbi = (int)(u / nslices);
+    if (rows_first) {            // forward, dQ: rows are queries, the blocks run up to the diagonal
+        const int rb = nrb - 1 - rbi;
+        const int last = std::min(T, rb * 256 + 256);
+        return (last + kColBlock - 1) / kColBlock;
+    }
+    return ncb - rbi * 256 / kColBlock;     // dK, dV: rows are keys, the blocks run from the diagonal to the end
+}
+
+// The units of every pair, in the order the pair takes them (host arithmetic only).
+static std::vector<std::vector<int>> attn_plan(bool rows_first, int nslices, int nrb, int ncb, int T, int pairs)
+{
+    const long total = (long)nslices * nrb;
+    std::vector<std::vector<int>> rows(pairs);
+    std::vector<double> load(pairs, 0.0);
+    for (long u = 0; u < total; u++) {
+        int best = 0;
+        for (int i = 1; i < pairs; i++)
+            if (load[i] < load[best]) best = i;
+        load[best] += attn_unit_blocks(rows_first, nslices, nrb, ncb, T, u) + 2.0;
+        rows[best].push_back((int)u);
+    }
+    return rows;
+}
+
 static AttnSched attn_schedule(int dev, bool rows_first, const AttnParams& p, int pairs)
 {
     static std::mutex mu;
@@ -1105,25 +1133,7 @@ static AttnSched attn_schedule(int dev, bool rows_first, const AttnParams& p, in
         cudaGetLastError();
         return none;
     }
-    const long total = (long)p.nslices * p.nrb;
-    std::vector<std::vector<int>> rows(pairs);
-    std::vector<double> load(pairs, 0.0);
-    for (long u = 0; u < total; u++) {
-        const int rbi = (int)(u / p.nslices);
-        int nb;
-        if (rows_first) {            // forward, dQ: rows are queries, the blocks run up to the diagonal (attn_unit)
-            const int rb = p.nrb - 1 - rbi;
-            const int last = std::min(p.T, rb * 256 + 256);
-            nb = (last + kColBlock - 1) / kColBlock;
-        } else {
-            nb = p.ncb - rbi * 256 / kColBlock;
-        }
-        int best = 0;
-        for (int i = 1; i < pairs; i++)
-            if (load[i] < load[best]) best = i;
-        load[best] += nb + 2.0;
-        rows[best].push_back((int)u);
-    }
+    const std::vector<std::vector<int>> rows = attn_plan(rows_first, p.nslices, p.nrb, p.ncb, p.T, pairs);
     size_t k = 0;
     for (const auto& r : rows) k = std::max(k, r.size());
     if (k > (size_t)kAttSchedMax) { cache[key] = none; return none; }
@@ -1280,6 +1290,37 @@ extern "C" {
 int znn_debug_set_attn_planes(int enable)
 {
     attn_set_planes(enable);
+    return ZNN_OK;
+}
+
+int znn_debug_attn_plan(int rows_first, int nslices, int T, int pairs, int table_form, int* units_per_pair, int* blocks_per_pair)
+{
+    ZNN_REQUIRE(nslices > 0 && T > 0 && pairs > 0 && units_per_pair && blocks_per_pair, "bad argument");
+    const int nrb = (T + 255) / 256, ncb = (T + kColBlock - 1) / kColBlock;
+    const long total = (long)nslices * nrb;
+    for (int i = 0; i < pairs; i++) units_per_pair[i] = blocks_per_pair[i] = 0;
+    if (table_form) {
+        const std::vector<std::vector<int>> rows = attn_plan(rows_first != 0, nslices, nrb, ncb, T, pairs);
+        std::vector<char> seen((size_t)total, 0);
+        for (int i = 0; i < pairs; i++)
+            for (int u : rows[i]) {
+                if (u < 0 || u >= total || seen[u]) return fail(ZNN_ERR_INVALID, "the plan names unit %d twice or out of range", u);
+                seen[u] = 1;
+                units_per_pair[i]++;
+                blocks_per_pair[i] += attn_unit_blocks(rows_first != 0, nslices, nrb, ncb, T, u);
+            }
+        for (long u = 0; u < total; u++)
+            if (!seen[u]) return fail(ZNN_ERR_INVALID, "the plan leaves out unit %ld", u);
+    } else {
+        // the kernel's own dealing: round k gives units k * pairs .. to the pairs in alternating direction
+        for (int i = 0; i < pairs; i++)
+            for (long k = 0;; k++) {
+                const long u = k * pairs + ((k & 1) ? pairs - 1 - i : i);
+                if (u >= total) break;
+                units_per_pair[i]++;
+                blocks_per_pair[i] += attn_unit_blocks(rows_first != 0, nslices, nrb, ncb, T, u);
+            }
+    }
     return ZNN_OK;
 }
 
