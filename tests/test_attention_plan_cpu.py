@@ -1,6 +1,7 @@
 """Host side of the fused attention kernels: how the work units are dealt to the CTA pairs (no GPU needed: the library
 loads without a device and znn_debug_attn_plan is host arithmetic)."""
 import ctypes as C
+import os
 
 import pytest
 
@@ -9,6 +10,9 @@ from znn_b200._lib import LIB_PATH
 
 @pytest.fixture(scope="module")
 def dll():
+    if not os.path.exists(LIB_PATH):
+        from znn_b200 import build
+        build.build()
     d = C.CDLL(LIB_PATH)
     d.znn_debug_attn_plan.restype = C.c_int
     d.znn_debug_attn_plan.argtypes = [C.c_int, C.c_int, C.c_int, C.c_int, C.c_int, C.POINTER(C.c_int), C.POINTER(C.c_int)]
