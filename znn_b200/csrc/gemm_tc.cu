@@ -1050,6 +1050,18 @@ gemm3x_direct_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_cons
                 if ((int)(it % kConvGroups) != group) continue;
                 const int s = it % S;
                 const uint32_t ph = (it / S) & 1;
+                // A parity wait cannot tell a phase from the one two uses earlier.  Where the groups do not divide the
+                // stages (three stages, two groups) the slot's previous tile was the other group's and this group has not
+                // seen it land; it therefore first waits until that tile has been consumed (the wait the producer makes
+                // before it refills the slot: no extra latency), after which the slot's "full" barrier can only be one
+                // phase away from the one waited for.
+                if (S % kConvGroups != 0) {
+                    got = __all_sync(0xffffffffu, mbar_wait_bounded_tight(empty_bar(s), ph ^ 1, p.wait_limit));
+                    if (!got) {
+                        if (lane == 0) record_expiry(2, 0, u, it, cta_rank, pair);
+                        break;
+                    }
+                }
                 // every lane polls and the warp votes: a wait that passes at once costs 90 cycles this way, 240 with one
                 // polling lane and a broadcast of its answer (measured), and the hand-off of a tile is this role's latency
                 got = ZNN_PROF_WAIT(mbar_wait_bounded_tight(full_bar(s), ph, p.wait_limit));
